@@ -1,0 +1,30 @@
+"""Regenerate codebooks.bin from the reference's own tables (run where the reference checker library is built).
+
+The IQ2_XXS and IQ3_S codebooks are data of the GGML formats (the reference derives them from its pinned llama.cpp,
+MIT licence: native/redlite_native_iq2_xxs.c:6-22, native/redlite_native_iq3_tables.h). They are not retyped: this
+script calls rl_native_iq2_xxs_build_grid and reads the arrays of redlite_native_iq3_tables.h through
+oracle/_ref/libredlite_ref.so, then stores them as raw little-endian bytes:
+
+    [0, 2048)      IQ2_XXS grid, 256 entries x 8 magnitudes (uint8)
+    [2048, 4096)   IQ3_S grid, 512 entries x 4 packed magnitudes (uint32)
+
+Usage: make -C oracle ref && python dwarfstar_red_lite_b200/data/make_codebooks.py
+"""
+import ctypes
+import os
+
+here = os.path.dirname(os.path.abspath(__file__))
+root = os.path.dirname(os.path.dirname(here))
+ref = ctypes.CDLL(os.path.join(root, "oracle", "_ref", "libredlite_ref.so"), mode=ctypes.RTLD_LOCAL)
+
+grid = (ctypes.c_uint8 * 2048)()
+err = ctypes.create_string_buffer(256)
+assert ref.rl_native_iq2_xxs_build_grid(grid, err, 256) == 1, err.value
+ref.redcuda_ref_iq3s_grid.restype = ctypes.POINTER(ctypes.c_uint32)
+n = ctypes.c_size_t(0)
+p = ref.redcuda_ref_iq3s_grid(ctypes.byref(n))
+assert n.value == 512
+iq3s = bytes(ctypes.cast(p, ctypes.POINTER(ctypes.c_uint8 * 2048)).contents)
+with open(os.path.join(here, "codebooks.bin"), "wb") as f:
+    f.write(bytes(grid) + iq3s)
+print("wrote codebooks.bin", 4096, "bytes")
