@@ -1,0 +1,309 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE-layer decode hot path on B200 (see DESIGN.md for the workload definition).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--layers L] [--tokens T]
+
+Workload (N = 1): ragged batched MoE decode — T = 64 concurrent sequences, one token each, through L distinct
+MoE layers (512 IQ2_XXS experts, top-10, Q6_K shared expert) whose router logits are DRAWN so that per-expert token
+counts follow Zipf(1.1). One step = one pass of the batch through all L layers; the L layers' weights (L x 415 MB) are
+far larger than L2, so every step reads its experts from HBM. Prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "moe_layer_decode_tokens_per_s"
+UNIT = "tokens/s"
+HBM_PEAK_FALLBACK = 6650.0
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return HBM_PEAK_FALLBACK, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        for r in self.rows:
+            try:
+                sm.append(int(float(r[0])))
+                mx = max(mx, int(float(r[1])))
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                pass
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def zipf_unique_experts(logits: np.ndarray, top_k: int) -> int:
+    sel = np.argpartition(-logits, top_k - 1, axis=1)[:, :top_k]
+    return int(np.unique(sel).size)
+
+
+def algorithmic_bytes(dims, ntok: int, unique: int, router_computed: bool):
+    """Bytes one MoE layer pass must move: distinct selected experts + shared expert + activations in/out (+ router)."""
+    from dwarfstar_red_lite_b200.synth import row_bytes
+    gu = dims.ffn * row_bytes(dims.type_gu, dims.hidden)
+    dn = dims.hidden * row_bytes(dims.type_down, dims.ffn)
+    sh = 2 * dims.ffn_sh * row_bytes(dims.type_sh, dims.hidden) + dims.hidden * row_bytes(dims.type_sh, dims.ffn_sh)
+    total = unique * (2 * gu + dn) + sh + dims.hidden * 4 + ntok * 2 * dims.hidden * 4
+    if router_computed:
+        total += dims.n_expert * dims.hidden * 4
+    return {"layer": total, "gateup": unique * 2 * gu + ntok * dims.hidden * 4, "down": unique * dn}
+
+
+def cpu_sample(layer_host, x: np.ndarray, logits: np.ndarray, threads: int, budget_s: float):
+    """Oracle port of ffn() (native/redlite_native_engine_cpu.c:329-386) over as many tokens of the batch as fit the budget."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    view = ol.moe_layer_c(layer_host)
+    t0 = time.perf_counter()
+    n = 0
+    while n < x.shape[0]:
+        ol.moe_ffn(layer_host, x[n], threads=threads, logits_in=logits[n], view=view)
+        n += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    dt = time.perf_counter() - t0
+    return n / dt, n, dt
+
+
+def host_layer_from_device(tensors: dict, dims):
+    from dwarfstar_red_lite_b200.synth import MoeLayer
+    g = lambda k: tensors[k].cpu().numpy()
+    return MoeLayer(dims, g("router"), g("gate").reshape(dims.n_expert, -1), g("up").reshape(dims.n_expert, -1),
+                    g("down").reshape(dims.n_expert, -1), g("sh_gate_inp"), g("sh_gate").reshape(dims.ffn_sh, -1),
+                    g("sh_up").reshape(dims.ffn_sh, -1), g("sh_down").reshape(dims.hidden, -1))
+
+
+def run_reference(args):
+    """The reference arm: the CPU path of the same workload (oracle port, every host thread), bounded sample per step."""
+    from dwarfstar_red_lite_b200 import synth
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    dims = synth.MoeDims()
+    threads = os.cpu_count() or 1
+    layer = synth.moe_layer(1234, dims)
+    rng = np.random.default_rng(1)
+    x = rng.normal(0, 1, size=(args.tokens, dims.hidden)).astype(np.float32)
+    logits = synth.zipf_routing_logits(77, args.tokens)
+    sample = max(1, min(args.tokens, args.ref_tokens))
+    for _ in range(args.warmup):
+        cpu_sample(layer, x[:1], logits[:1], threads, 1e9)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_sample(layer, x[:sample], logits[:sample], threads, 1e9)
+    dt = time.perf_counter() - t0
+    value = sample * args.steps / dt
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "config": workload_config(args, dims),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": f"{sample} of the {args.tokens} tokens of one layer per step (oracle port of ffn(); the reference's own routed CPU path rejects IQ2_XXS experts)"},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, dims):
+    return {"workload": "ragged batched MoE decode (BASELINE configs[1]): %d sequences x 1 token, %d experts top-%d IQ2_XXS + Q6_K shared expert, "
+                        "router logits drawn Zipf(1.1)" % (args.tokens, dims.n_expert, dims.top_k),
+            "tokens_per_step_per_gpu": args.tokens, "layers_per_step": args.layers, "hidden": dims.hidden, "ffn": dims.ffn,
+            "l2_policy": "inputs larger than L2: each step sweeps %d distinct layers' experts" % args.layers,
+            "parallelism": "single GPU" if args.gpus == 1 else f"ep{args.gpus}"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="redcuda", choices=["redcuda", "reference"])
+    ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--tokens", type=int, default=64)
+    ap.add_argument("--ref-tokens", type=int, default=8, help="tokens per step of the reference (CPU) arm")
+    ap.add_argument("--cpu-budget-s", type=float, default=15.0)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "redcuda" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import dwarfstar_red_lite_b200 as rc
+    from dwarfstar_red_lite_b200 import redcuda as rcm, synth, synth_device
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if world > 1:
+        raise SystemExit("expert-parallel bench path: see bench_ep in dwarfstar_red_lite_b200 (not wired in this build)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    rc.set_codebooks(device=local)
+    dims = synth.MoeDims()
+    L, T = args.layers, args.tokens
+
+    # ---- resident layers, inputs, drawn logits
+    layers, uniq = [], []
+    layer0_host = None
+    for l in range(L):
+        tens = synth_device.moe_layer_tensors(1000 + l, dims, dev)
+        layers.append(rc.MoeLayer(device_tensors=tens, dims=dims, max_tokens=T))
+        if l == 0 and not args.no_cpu:
+            layer0_host = host_layer_from_device(tens, dims)
+        del tens
+    torch.cuda.synchronize()
+    logits_h = np.stack([synth.zipf_routing_logits(500 + l, T) for l in range(L)])
+    uniq = [zipf_unique_experts(logits_h[l], dims.top_k) for l in range(L)]
+    gx = torch.Generator(device=dev)
+    gx.manual_seed(7)
+    x_d = torch.randn(L, T, dims.hidden, device=dev, generator=gx)
+    logits_d = torch.from_numpy(logits_h).to(dev)
+    out_d = torch.empty(L, T, dims.hidden, device=dev)
+    row = T * dims.hidden * 4
+
+    def step(stream):
+        for l in range(L):
+            layers[l].forward_device(T, x_d.data_ptr() + l * row, out_d.data_ptr() + l * row, stream, logits_ptr=logits_d.data_ptr() + l * T * dims.n_expert * 4)
+
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        n0 = rcm.lib().redcuda_launch_count()
+        step(side.cuda_stream)
+        launches_per_step = rcm.lib().redcuda_launch_count() - n0
+        for _ in range(args.warmup - 1):
+            step(side.cuda_stream)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step(side.cuda_stream)
+        graph.replay()
+        side.synchronize()
+        # ---- timed region: K graph replays, CUDA events on the launching stream
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clocks:
+            torch.cuda.synchronize()
+            e0.record(side)
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record(side)
+            torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        # ---- per-kernel durations (events around every launch, same stream, same inputs; separate from the timed region)
+        rcm.profile_enable(True)
+        prof_steps = 3
+        for _ in range(prof_steps):
+            step(side.cuda_stream)
+        side.synchronize()
+        prof = rcm.profile_report()
+        rcm.profile_enable(False)
+    ms_per_step = ms / args.steps
+    value = T * L / (ms_per_step * 1e-3)
+
+    # ---- roofline of the dominant kernel (routed gate/up)
+    peak, peak_kind = measured_peak()
+    ab = [algorithmic_bytes(dims, T, u, False) for u in uniq]
+    total_prof_ms = sum(v[1] for v in prof.values()) or 1.0
+    shares = {k: round(v[1] / total_prof_ms, 4) for k, v in prof.items()}
+    dom = max(prof, key=lambda k: prof[k][1])
+    key = {"moe_gateup": "gateup", "moe_down": "down"}.get(dom)
+    dom_bytes = float(np.mean([a[key] for a in ab])) if key else float(np.mean([a["layer"] for a in ab]))
+    dom_ms = prof[dom][1] / prof[dom][0]
+    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+    layer_bytes = float(np.mean([a["layer"] for a in ab]))
+    roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                "frac_of_nominal_8000": achieved / 8000.0, "traffic": None, "bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
+                "kernel_time_shares": shares,
+                "whole_layer": {"bytes": layer_bytes, "GBps": layer_bytes * L / (ms_per_step * 1e-3) / 1e9,
+                                "frac": layer_bytes * L / (ms_per_step * 1e-3) / 1e9 / peak}}
+
+    # ---- end to end through the host API: pinned host buffers in, host buffers out, every layer call synchronous
+    xh = torch.randn(L, T, dims.hidden).pin_memory()
+    lh = torch.from_numpy(logits_h).pin_memory()
+    oh = torch.empty(L, T, dims.hidden).pin_memory()
+    xn, ln, on = xh.numpy(), lh.numpy(), oh.numpy()
+
+    def e2e_step():
+        for l in range(L):
+            layers[l].forward(xn[l], logits_in=ln[l], out=on[l])
+
+    for _ in range(2):
+        e2e_step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e2e_steps = max(3, args.steps // 4)
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_dt = (time.perf_counter() - t0) / e2e_steps
+    e2e = {"value": T * L / e2e_dt, "unit": UNIT, "h2d_bytes_per_step": L * (T * dims.hidden * 4 + T * dims.n_expert * 4),
+           "d2h_bytes_per_step": L * T * dims.hidden * 4, "ms_per_step": e2e_dt * 1e3}
+
+    # ---- CPU baseline: the oracle port on this box's host cores, bounded sample of the same workload (layer 0)
+    cpu = None
+    if layer0_host is not None:
+        threads = os.cpu_count() or 1
+        v, n, dt = cpu_sample(layer0_host, x_d[0].cpu().numpy(), logits_h[0], threads, args.cpu_budget_s)
+        cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"{n} of the {T} tokens of layer 0 in {dt:.1f} s (oracle port of ffn(), rows spread over {threads} threads)"}
+
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": dict(workload_config(args, dims), unique_experts_per_layer_mean=float(np.mean(uniq))),
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches_per_step * args.steps),
+            "clocks": clocks.summary()}
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,60 @@
+// Shared host-side plumbing of the redcuda library: error reporting, launch accounting, device buffers, codebooks.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+#include <atomic>
+#include <string>
+
+#include "redcuda_formats.cuh"
+
+namespace rc {
+
+void set_error(const char *fmt, ...);
+extern std::atomic<uint64_t> g_launches;
+
+#define RC_CUDA(expr) do { cudaError_t rc_e_ = (expr); if (rc_e_ != cudaSuccess) { \
+    rc::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(rc_e_), __FILE__, __LINE__); return 0; } } while (0)
+// after a kernel launch: count it and surface launch-configuration errors at once
+#define RC_LAUNCHED() do { rc::g_launches.fetch_add(1, std::memory_order_relaxed); cudaError_t rc_e_ = cudaGetLastError(); \
+    if (rc_e_ != cudaSuccess) { rc::set_error("kernel launch failed: %s (%s:%d)", cudaGetErrorString(rc_e_), __FILE__, __LINE__); return 0; } } while (0)
+#define RC_REQUIRE(cond, ...) do { if (!(cond)) { rc::set_error(__VA_ARGS__); return 0; } } while (0)
+
+// Optional per-kernel timing: while enabled, every launch site brackets its kernel with a pair of CUDA events on the
+// launching stream (not usable while a stream is being captured into a graph).
+void prof_begin(const char *tag, cudaStream_t s);
+void prof_end(cudaStream_t s);
+
+// Fails (with a message) unless a CUDA device is usable: the library has no CPU path.
+int require_device();
+// Fails unless the codebooks have been set on the current device.
+int require_books(uint32_t ggml_type);
+// device pointers of the codebooks on the current device
+const uint8_t *books_iq2();
+const uint32_t *books_iq3s();
+
+struct DevMem {
+    void *p = nullptr; size_t bytes = 0;
+    int alloc(size_t n);
+    void release();
+    ~DevMem() { release(); }
+    DevMem() = default;
+    DevMem(const DevMem &) = delete;
+    DevMem &operator=(const DevMem &) = delete;
+    template <class T> T *as() const { return reinterpret_cast<T *>(p); }
+};
+
+// A weight matrix resident in HBM in planar layout (F32/F16 matrices stay plain row-major).
+struct DMat {
+    const uint8_t *base = nullptr;
+    uint32_t type = 0, nrows = 0, ncols = 0;
+    uint64_t nb = 0;       // blocks of 256 (quantised types)
+};
+
+// Upload one matrix of raw GGUF rows (host or device memory) into dst (device, 16-byte aligned, matrix_bytes long)
+// and re-lay it out planar. scratch must hold matrix_bytes when the type is quantised and the source is host memory.
+int upload_matrix(uint32_t type, uint32_t nrows, uint32_t ncols, const void *src, bool src_on_device, uint8_t *dst,
+                  uint8_t *scratch, cudaStream_t stream);
+
+}  // namespace rc

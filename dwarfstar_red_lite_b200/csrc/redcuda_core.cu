@@ -1,0 +1,442 @@
+// redcuda core: error state, codebooks, matrix upload/repack, dequantisation, generic multi-job GEMV, router top-k.
+#include "redcuda_common.cuh"
+#include "redcuda_dot.cuh"
+#include "redcuda_kernels.cuh"
+#include "../../include/redcuda.h"
+
+#include <math.h>
+#include <map>
+#include <mutex>
+#include <vector>
+
+namespace rc {
+
+static thread_local std::string t_err;
+std::atomic<uint64_t> g_launches{0};
+
+void set_error(const char *fmt, ...) {
+    char buf[1024];
+    va_list ap; va_start(ap, fmt); vsnprintf(buf, sizeof(buf), fmt, ap); va_end(ap);
+    t_err = buf;
+}
+
+// ---- per-kernel event timing ----
+struct ProfRec { const char *tag; cudaEvent_t a, b; };
+static bool g_prof_on = false;
+static std::vector<ProfRec> g_prof;
+static std::mutex g_prof_mu;
+
+void prof_begin(const char *tag, cudaStream_t s) {
+    if (!g_prof_on) return;
+    ProfRec r{tag, nullptr, nullptr};
+    if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess) return;
+    cudaEventRecord(r.a, s);
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    g_prof.push_back(r);
+}
+void prof_end(cudaStream_t s) {
+    if (!g_prof_on) return;
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    if (!g_prof.empty()) cudaEventRecord(g_prof.back().b, s);
+}
+
+int require_device() {
+    int n = 0;
+    const cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0) {
+        set_error("no usable CUDA device (%s); redcuda has no CPU path", e == cudaSuccess ? "device count 0" : cudaGetErrorString(e));
+        return 0;
+    }
+    return 1;
+}
+
+int DevMem::alloc(size_t n) {
+    release();
+    if (!n) n = 16;
+    RC_CUDA(cudaMalloc(&p, n));
+    bytes = n;
+    return 1;
+}
+void DevMem::release() { if (p) { cudaFree(p); p = nullptr; bytes = 0; } }
+
+// ---- codebooks: one copy per device, in global memory; kernels stage them into shared memory ----
+__device__ __align__(16) uint8_t d_iq2_grid[2048];
+__device__ __align__(16) uint32_t d_iq3s_grid[512];
+static std::mutex g_books_mu;
+static bool g_books_set[64] = {false};
+static const uint8_t *g_iq2_ptr[64] = {nullptr};
+static const uint32_t *g_iq3s_ptr[64] = {nullptr};
+
+int require_books(uint32_t t) {
+    if (t != RC_IQ2_XXS && t != RC_IQ3_S) return 1;
+    int dev = 0;
+    RC_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(g_books_mu);
+    RC_REQUIRE(dev < 64 && g_books_set[dev], "codebooks not set on device %d: call redcuda_set_codebooks first", dev);
+    return 1;
+}
+const uint8_t *books_iq2() { int dev = 0; cudaGetDevice(&dev); return g_iq2_ptr[dev & 63]; }
+const uint32_t *books_iq3s() { int dev = 0; cudaGetDevice(&dev); return g_iq3s_ptr[dev & 63]; }
+
+// ---- raw GGUF blocks -> planar ----
+__global__ void k_repack(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, uint32_t type, uint64_t nb, uint32_t units_per_block) {
+    // one thread per 2-byte unit of the raw matrix (every field of the three formats starts on an even offset)
+    const uint64_t total = nb * units_per_block;
+    for (uint64_t u = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; u < total; u += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t b = u / units_per_block;
+        const uint32_t off = (uint32_t)(u - b * units_per_block) * 2u;
+        const unsigned short v = reinterpret_cast<const unsigned short *>(src)[u];
+        *reinterpret_cast<unsigned short *>(dst + rc_planar_dst(type, nb, b, off)) = v;
+    }
+}
+
+int upload_matrix(uint32_t type, uint32_t nrows, uint32_t ncols, const void *src, bool src_on_device, uint8_t *dst,
+                  uint8_t *scratch, cudaStream_t stream) {
+    RC_REQUIRE(rc_type_supported(type), "unsupported ggml type %u", type);
+    const uint64_t bytes = rc_matrix_bytes(type, nrows, ncols);
+    RC_REQUIRE(bytes != 0, "matrix %ux%u of type %u has no valid row size", nrows, ncols, type);
+    RC_REQUIRE(((uintptr_t)dst & 15u) == 0, "matrix destination is not 16-byte aligned");
+    if (!rc_is_quant(type)) {
+        RC_REQUIRE(ncols % 64u == 0, "F32/F16 matrices need a row length that is a multiple of 64 (got %u)", ncols);
+        RC_CUDA(cudaMemcpyAsync(dst, src, bytes, src_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, stream));
+        return 1;
+    }
+    const uint8_t *raw = (const uint8_t *)src;
+    if (!src_on_device) {
+        RC_REQUIRE(scratch != nullptr, "upload_matrix needs scratch for host sources");
+        RC_CUDA(cudaMemcpyAsync(scratch, src, bytes, cudaMemcpyHostToDevice, stream));
+        raw = scratch;
+    }
+    RC_REQUIRE(((uintptr_t)raw & 1u) == 0, "raw matrix source is not 2-byte aligned");
+    const uint64_t nb = (uint64_t)nrows * (ncols / 256u);
+    const uint32_t upb = rc_block_bytes(type) / 2u;
+    const uint64_t total = nb * upb;
+    const uint32_t grid = (uint32_t)((total + 255u) / 256u < 148u * 16u ? (total + 255u) / 256u : 148u * 16u);
+    prof_begin("repack", stream);
+    k_repack<<<grid ? grid : 1u, 256, 0, stream>>>(raw, dst, type, nb, upb);
+    prof_end(stream);
+    RC_LAUNCHED();
+    return 1;
+}
+
+// ---- dequantisation: one thread per group of 8 values ----
+__global__ void k_dequant(const uint8_t *__restrict__ base, uint32_t type, uint64_t nb, const uint8_t *iq2, const uint32_t *iq3s, float *__restrict__ out) {
+    const RcBooks bk{iq2, iq3s};
+    const uint64_t total = nb * 32u;
+    for (uint64_t g = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; g < total; g += (uint64_t)gridDim.x * blockDim.x) {
+        float v[8];
+        rc_decode8(type, base, nb, g >> 5, (uint32_t)(g & 31u), bk, v);
+        float4 *o = reinterpret_cast<float4 *>(out + g * 8u);
+        o[0] = make_float4(v[0], v[1], v[2], v[3]);
+        o[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+}
+__global__ void k_dequant_f16(const unsigned short *__restrict__ src, uint64_t n, float *__restrict__ out) {
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        out[i] = __half2float(__ushort_as_half(src[i]));
+}
+
+// ---- generic multi-job GEMV ----
+// Each block takes one tile (a run of rows) of one job. All jobs of a launch read the same activation rows.
+template <int TYPE, int NT>
+__device__ __forceinline__ void gemv_tile(const GemvJob &J, uint32_t row0, uint32_t ntok_here, uint32_t tok0, uint32_t ntok,
+                                          const float *xs, uint32_t xstride, const SBooks &sb) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, nwarps = blockDim.x >> 5;
+    const uint32_t cpr = J.ncols >> 6;
+    uint32_t lpr = 32u;
+    while (lpr > cpr) lpr >>= 1;
+    const uint32_t rw = 32u / lpr, slot = lane / lpr, sub = lane % lpr;
+    const uint32_t row_end = min(row0 + J.rows_per_tile, J.nrows);
+    (void)ntok;
+    for (uint32_t r = row0 + warp * rw; r < row_end; r += nwarps * rw) {
+        const uint32_t row = r + slot;
+        const bool live = row < row_end;
+        const uint64_t rr = live ? row : (uint64_t)(row_end - 1u);   // idle slots recompute a valid row, never store
+        float a0[NT], a1[NT];
+        row_dot<TYPE, NT>(J.w0, J.nb, rr, J.ncols, lpr, sub, xs, xstride, sb, a0);
+        if (J.epi == GEMV_PAIR_SILU) row_dot<TYPE, NT>(J.w1, J.nb, rr, J.ncols, lpr, sub, xs, xstride, sb, a1);
+        if (live && sub == 0u) {
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                if ((uint32_t)t >= ntok_here) break;
+                float v = a0[t];
+                if (J.epi == GEMV_PAIR_SILU) v = silu_mul(a0[t], a1[t]);
+                else if (J.epi == GEMV_SIGMOID) v = 1.0f / (1.0f + expf(-v));
+                J.out[(size_t)(tok0 + t) * J.out_stride + row] = v;
+            }
+        }
+    }
+}
+
+template <int NT>
+__global__ void __launch_bounds__(256) k_gemv(const __grid_constant__ GemvArgs A) {
+    extern __shared__ __align__(16) float xs[];
+    __shared__ uint2 s_iq2[256];
+    __shared__ uint32_t s_iq3s[512];
+    uint32_t j = 0;
+    while (j + 1u < A.njobs && blockIdx.x >= A.job[j + 1u].tile_begin) ++j;
+    const GemvJob &J = A.job[j];
+    const uint32_t row0 = (blockIdx.x - J.tile_begin) * J.rows_per_tile;
+    load_books(s_iq2, s_iq3s, A.iq2, A.iq3s, 1u << J.type);
+    const SBooks sb{s_iq2, s_iq3s};
+    const uint32_t xstride = x_padded(J.ncols);
+    for (uint32_t tok0 = 0; tok0 < A.ntok; tok0 += NT) {
+        const uint32_t nt = min((uint32_t)NT, A.ntok - tok0);
+        __syncthreads();
+        stage_x<NT>(xs, xstride, A.x, A.x_stride, nullptr, tok0, nt, J.ncols);
+        __syncthreads();
+        switch (J.type) {
+            case RC_F32: gemv_tile<RC_F32, NT>(J, row0, nt, tok0, A.ntok, xs, xstride, sb); break;
+            case RC_F16: gemv_tile<RC_F16, NT>(J, row0, nt, tok0, A.ntok, xs, xstride, sb); break;
+            case RC_Q6_K: gemv_tile<RC_Q6_K, NT>(J, row0, nt, tok0, A.ntok, xs, xstride, sb); break;
+            case RC_IQ2_XXS: gemv_tile<RC_IQ2_XXS, NT>(J, row0, nt, tok0, A.ntok, xs, xstride, sb); break;
+            case RC_IQ3_S: gemv_tile<RC_IQ3_S, NT>(J, row0, nt, tok0, A.ntok, xs, xstride, sb); break;
+            default: break;
+        }
+    }
+}
+
+// Fill tile_begin / rows_per_tile of every job and launch. Jobs must share ncols (they read the same x rows).
+int launch_gemv(GemvArgs &A, cudaStream_t stream) {
+    RC_REQUIRE(A.njobs >= 1 && A.njobs <= RC_MAX_JOBS, "gemv: bad job count %u", A.njobs);
+    const uint32_t ncols = A.job[0].ncols;
+    RC_REQUIRE(ncols % 64u == 0 && ncols >= 64u, "gemv: row length %u is not a multiple of 64", ncols);
+    uint64_t total_rows = 0;
+    for (uint32_t j = 0; j < A.njobs; ++j) {
+        RC_REQUIRE(A.job[j].ncols == ncols, "gemv: jobs of one launch must share the row length");
+        RC_REQUIRE(rc_type_supported(A.job[j].type), "gemv: unsupported type %u", A.job[j].type);
+        RC_REQUIRE(!rc_is_quant(A.job[j].type) || ncols % 256u == 0, "gemv: quantised rows need a multiple of 256 columns");
+        total_rows += A.job[j].nrows;
+    }
+    uint32_t lpr = 32u;
+    while (lpr > (ncols >> 6)) lpr >>= 1;
+    const uint32_t rows_per_pass = 8u * (32u / lpr);                 // rows one block covers per sweep of its 8 warps
+    // aim at >= 4 blocks per SM when the work allows it, at most 8 sweeps per block
+    uint32_t sweeps = (uint32_t)(total_rows / ((uint64_t)rows_per_pass * 148u * 4u));
+    sweeps = sweeps < 1u ? 1u : sweeps > 8u ? 8u : sweeps;
+    uint32_t tiles = 0;
+    for (uint32_t j = 0; j < A.njobs; ++j) {
+        A.job[j].rows_per_tile = rows_per_pass * sweeps;
+        A.job[j].tile_begin = tiles;
+        tiles += (A.job[j].nrows + A.job[j].rows_per_tile - 1u) / A.job[j].rows_per_tile;
+    }
+    A.iq2 = books_iq2();
+    A.iq3s = books_iq3s();
+    const int nt = A.ntok <= 1u ? 1 : 4;
+    const size_t smem = (size_t)nt * x_padded(ncols) * sizeof(float);
+    RC_REQUIRE(smem <= 200u * 1024u, "gemv: row length %u too large for the shared-memory staging", ncols);
+    prof_begin(A.tag ? A.tag : "gemv", stream);
+    if (nt == 1) {
+        if (smem > 48u * 1024u) RC_CUDA(cudaFuncSetAttribute(k_gemv<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k_gemv<1><<<tiles, 256, smem, stream>>>(A);
+    } else {
+        if (smem > 48u * 1024u) RC_CUDA(cudaFuncSetAttribute(k_gemv<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k_gemv<4><<<tiles, 256, smem, stream>>>(A);
+    }
+    prof_end(stream);
+    RC_LAUNCHED();
+    return 1;
+}
+
+// ---- router: softmax + top-k, one block per token (router_exec.c:102-184 semantics, ties -> lower id) ----
+__global__ void __launch_bounds__(256) k_route(const float *__restrict__ logits, uint32_t n_expert, uint32_t top_k,
+                                               uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ probs_out) {
+    extern __shared__ float p[];                 // n_expert probabilities
+    __shared__ float s_redf[8];
+    __shared__ double s_redd[8];
+    __shared__ float s_bv[8];
+    __shared__ uint32_t s_bi[8];
+    __shared__ float s_selw[REDCUDA_MAX_TOPK];
+    const uint32_t tok = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const float *l = logits + (size_t)tok * n_expert;
+    float mx = -INFINITY;
+    for (uint32_t i = tid; i < n_expert; i += 256u) mx = fmaxf(mx, l[i]);
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (!lane) s_redf[warp] = mx;
+    __syncthreads();
+    mx = s_redf[0];
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, s_redf[w]);
+    double den = 0.0;
+    for (uint32_t i = tid; i < n_expert; i += 256u) { const float e = expf(l[i] - mx); p[i] = e; den += (double)e; }
+    for (int o = 16; o; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+    if (!lane) s_redd[warp] = den;
+    __syncthreads();
+    den = 0.0;
+    for (int w = 0; w < 8; ++w) den += s_redd[w];
+    const float inv = (float)(1.0 / den);
+    for (uint32_t i = tid; i < n_expert; i += 256u) { p[i] *= inv; if (probs_out) probs_out[(size_t)tok * n_expert + i] = p[i]; }
+    __syncthreads();
+    for (uint32_t k = 0; k < top_k; ++k) {
+        float bv = -INFINITY; uint32_t bi = 0xffffffffu;
+        for (uint32_t i = tid; i < n_expert; i += 256u) { const float v = p[i]; if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
+        for (int o = 16; o; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (!lane) { s_bv[warp] = bv; s_bi[warp] = bi; }
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 1; w < 8; ++w) if (s_bv[w] > bv || (s_bv[w] == bv && s_bi[w] < bi)) { bv = s_bv[w]; bi = s_bi[w]; }
+            ids[(size_t)tok * top_k + k] = bi;
+            s_selw[k] = bv;
+            if (bi < n_expert) p[bi] = -1.0f;   // selected: below every probability from now on
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        double sel = 0.0;
+        for (uint32_t k = 0; k < top_k; ++k) sel += (double)s_selw[k];
+        const float invs = (float)(1.0 / sel);
+        for (uint32_t k = 0; k < top_k; ++k) weights[(size_t)tok * top_k + k] = s_selw[k] * invs;
+    }
+}
+
+int launch_route(const float *logits_dev, uint32_t ntok, uint32_t n_expert, uint32_t top_k, uint32_t *ids_dev, float *weights_dev,
+                 float *probs_dev, cudaStream_t stream) {
+    RC_REQUIRE(top_k >= 1 && top_k <= REDCUDA_MAX_TOPK && top_k <= n_expert, "router: top_k %u out of range", top_k);
+    RC_REQUIRE(n_expert <= 8192u, "router: too many experts (%u)", n_expert);
+    if (!ntok) return 1;
+    prof_begin("route", stream);
+    k_route<<<ntok, 256, n_expert * sizeof(float), stream>>>(logits_dev, n_expert, top_k, ids_dev, weights_dev, probs_dev);
+    prof_end(stream);
+    RC_LAUNCHED();
+    return 1;
+}
+
+}  // namespace rc
+
+using namespace rc;
+
+// ================================================================================================= C ABI
+extern "C" {
+
+uint32_t redcuda_abi_version(void) { return REDCUDA_ABI_VERSION; }
+const char *redcuda_last_error(void) { return rc::t_err.c_str(); }
+uint64_t redcuda_launch_count(void) { return rc::g_launches.load(); }
+
+int redcuda_profile_enable(int on) {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    for (auto &r : g_prof) { if (r.a) cudaEventDestroy(r.a); if (r.b) cudaEventDestroy(r.b); }
+    g_prof.clear();
+    g_prof_on = on != 0;
+    return 1;
+}
+
+int redcuda_profile_report(char *buf, size_t cap) {
+    if (!buf || !cap) return 0;
+    cudaDeviceSynchronize();
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    std::map<std::string, std::pair<uint64_t, double>> agg;
+    for (auto &r : g_prof) {
+        float ms = 0.f;
+        if (r.a && r.b && cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) { auto &e = agg[r.tag]; e.first += 1; e.second += ms; }
+    }
+    cudaGetLastError();
+    size_t pos = 0; int n = 0;
+    buf[0] = 0;
+    for (auto &kv : agg) {
+        const int w = snprintf(buf + pos, cap - pos, "%s %llu %.6f\n", kv.first.c_str(), (unsigned long long)kv.second.first, kv.second.second);
+        if (w < 0 || (size_t)w >= cap - pos) break;
+        pos += (size_t)w; ++n;
+    }
+    return n;
+}
+
+int redcuda_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+
+int redcuda_set_device(int device) {
+    if (!require_device()) return 0;
+    RC_CUDA(cudaSetDevice(device));
+    return 1;
+}
+
+int redcuda_set_codebooks(const uint8_t *iq2xxs_grid, uint32_t iq2xxs_bytes, const uint32_t *iq3s_grid, uint32_t iq3s_count) {
+    if (!require_device()) return 0;
+    RC_REQUIRE(iq2xxs_grid && iq2xxs_bytes == 2048u, "IQ2_XXS grid must be 256 x 8 bytes");
+    RC_REQUIRE(iq3s_grid && iq3s_count == 512u, "IQ3_S grid must be 512 entries");
+    for (uint32_t i = 0; i < 2048u; ++i) RC_REQUIRE(iq2xxs_grid[i] == 0x08 || iq2xxs_grid[i] == 0x19 || iq2xxs_grid[i] == 0x2b, "IQ2_XXS grid byte %u is not one of 0x08/0x19/0x2b", i);
+    int dev = 0;
+    RC_CUDA(cudaGetDevice(&dev));
+    RC_REQUIRE(dev < 64, "device index %d out of range", dev);
+    RC_CUDA(cudaMemcpyToSymbol(d_iq2_grid, iq2xxs_grid, 2048));
+    RC_CUDA(cudaMemcpyToSymbol(d_iq3s_grid, iq3s_grid, 2048));
+    void *p2 = nullptr, *p3 = nullptr;
+    RC_CUDA(cudaGetSymbolAddress(&p2, d_iq2_grid));
+    RC_CUDA(cudaGetSymbolAddress(&p3, d_iq3s_grid));
+    std::lock_guard<std::mutex> lk(g_books_mu);
+    g_iq2_ptr[dev] = (const uint8_t *)p2;
+    g_iq3s_ptr[dev] = (const uint32_t *)p3;
+    g_books_set[dev] = true;
+    return 1;
+}
+
+int redcuda_quant_dequant_rows(uint32_t type, const uint8_t *rows, uint32_t nrows, uint32_t ncols, float *out) {
+    if (!require_device() || !require_books(type)) return 0;
+    RC_REQUIRE(rows && out && nrows && ncols, "dequant: null or empty argument");
+    RC_REQUIRE(rc_type_supported(type), "dequant: unsupported ggml type %u", type);
+    const uint64_t bytes = rc_matrix_bytes(type, nrows, ncols);
+    RC_REQUIRE(bytes, "dequant: %u columns is not a valid row length for type %u", ncols, type);
+    const size_t n = (size_t)nrows * ncols;
+    if (type == RC_F32) { memcpy(out, rows, n * 4u); return 1; }   // a copy, as in the reference (quant_cpu.c:159)
+    DevMem raw, planar, o;
+    if (!raw.alloc(bytes) || !planar.alloc(bytes) || !o.alloc(n * 4u)) return 0;
+    cudaStream_t s = 0;
+    if (type == RC_F16) {
+        RC_CUDA(cudaMemcpyAsync(raw.p, rows, bytes, cudaMemcpyHostToDevice, s));
+        k_dequant_f16<<<(unsigned)((n + 255u) / 256u < 4096u ? (n + 255u) / 256u : 4096u), 256, 0, s>>>(raw.as<unsigned short>(), n, o.as<float>());
+        RC_LAUNCHED();
+    } else {
+        if (!upload_matrix(type, nrows, ncols, rows, false, planar.as<uint8_t>(), raw.as<uint8_t>(), s)) return 0;
+        const uint64_t nb = (uint64_t)nrows * (ncols / 256u), groups = nb * 32u;
+        k_dequant<<<(unsigned)((groups + 255u) / 256u < 4096u ? (groups + 255u) / 256u : 4096u), 256, 0, s>>>(planar.as<uint8_t>(), type, nb, books_iq2(), books_iq3s(), o.as<float>());
+        RC_LAUNCHED();
+    }
+    RC_CUDA(cudaMemcpyAsync(out, o.p, n * 4u, cudaMemcpyDeviceToHost, s));
+    RC_CUDA(cudaStreamSynchronize(s));
+    return 1;
+}
+
+int redcuda_quant_matvec(uint32_t type, const uint8_t *w, uint32_t nrows, uint32_t ncols, const float *x, uint32_t ntok, float *out) {
+    if (!require_device() || !require_books(type)) return 0;
+    RC_REQUIRE(w && x && out && nrows && ncols && ntok, "matvec: null or empty argument");
+    RC_REQUIRE(rc_type_supported(type), "matvec: unsupported ggml type %u", type);
+    const uint64_t bytes = rc_matrix_bytes(type, nrows, ncols);
+    RC_REQUIRE(bytes, "matvec: %u columns is not a valid row length for type %u", ncols, type);
+    DevMem raw, planar, xd, od;
+    if (!raw.alloc(bytes) || !planar.alloc(bytes) || !xd.alloc((size_t)ntok * ncols * 4u) || !od.alloc((size_t)ntok * nrows * 4u)) return 0;
+    cudaStream_t s = 0;
+    if (!upload_matrix(type, nrows, ncols, w, false, planar.as<uint8_t>(), raw.as<uint8_t>(), s)) return 0;
+    RC_CUDA(cudaMemcpyAsync(xd.p, x, (size_t)ntok * ncols * 4u, cudaMemcpyHostToDevice, s));
+    GemvArgs A{};
+    A.njobs = 1; A.ntok = ntok; A.x = xd.as<float>(); A.x_stride = ncols;
+    A.job[0].w0 = planar.as<uint8_t>(); A.job[0].w1 = nullptr; A.job[0].out = od.as<float>(); A.job[0].nb = (uint64_t)nrows * (ncols / 256u);
+    A.job[0].type = type; A.job[0].nrows = nrows; A.job[0].ncols = ncols; A.job[0].out_stride = nrows; A.job[0].epi = GEMV_STORE;
+    if (!launch_gemv(A, s)) return 0;
+    RC_CUDA(cudaMemcpyAsync(out, od.p, (size_t)ntok * nrows * 4u, cudaMemcpyDeviceToHost, s));
+    RC_CUDA(cudaStreamSynchronize(s));
+    return 1;
+}
+
+int redcuda_router_select_softmax_topk(const float *logits, uint32_t ntok, uint32_t n_expert, uint32_t top_k,
+                                       uint32_t *ids, float *weights, float *probs) {
+    if (!require_device()) return 0;
+    RC_REQUIRE(logits && ids && weights && n_expert && top_k && top_k <= n_expert, "invalid router top-k selection arguments");
+    if (!ntok) return 1;
+    DevMem l, i, w, p;
+    if (!l.alloc((size_t)ntok * n_expert * 4u) || !i.alloc((size_t)ntok * top_k * 4u) || !w.alloc((size_t)ntok * top_k * 4u)) return 0;
+    if (probs && !p.alloc((size_t)ntok * n_expert * 4u)) return 0;
+    cudaStream_t s = 0;
+    RC_CUDA(cudaMemcpyAsync(l.p, logits, (size_t)ntok * n_expert * 4u, cudaMemcpyHostToDevice, s));
+    if (!launch_route(l.as<float>(), ntok, n_expert, top_k, i.as<uint32_t>(), w.as<float>(), probs ? p.as<float>() : nullptr, s)) return 0;
+    RC_CUDA(cudaMemcpyAsync(ids, i.p, (size_t)ntok * top_k * 4u, cudaMemcpyDeviceToHost, s));
+    RC_CUDA(cudaMemcpyAsync(weights, w.p, (size_t)ntok * top_k * 4u, cudaMemcpyDeviceToHost, s));
+    if (probs) RC_CUDA(cudaMemcpyAsync(probs, p.p, (size_t)ntok * n_expert * 4u, cudaMemcpyDeviceToHost, s));
+    RC_CUDA(cudaStreamSynchronize(s));
+    return 1;
+}
+
+}  // extern "C"

@@ -1,0 +1,174 @@
+// Gated DeltaNet decode step between the projections (deltanet_branch, native/redlite_native_engine_cpu.c:148-230).
+//
+//   k_dn_prep   beta = sigmoid(b), gate = softplus(a + dt_bias) * A; causal depthwise conv over [conv state, new
+//               sample] + SiLU; conv window shifted in place; q and k L2-normalised per key head (fp64 for the small
+//               reductions, as the CPU path)
+//   k_dn_state  the fp32 delta rule, one warp per state row: the row (d_state floats) is loaded once into the warp's
+//               registers, decayed, corrected and read out, then stored — one read and one write of the state,
+//               where the CPU path sweeps it four times
+//   k_dn_tail   per value head RMSNorm(core) * w * SiLU(z)
+#include "redcuda_common.cuh"
+#include "redcuda_kernels.cuh"
+#include "../../include/redcuda.h"
+
+#include <new>
+
+namespace rc {
+
+struct DnDims { uint32_t d_conv, S, groups, rank, d_inner, channels; float eps; };
+
+__device__ __forceinline__ double sigmoid_stable(double x) { if (x >= 0.0) { const double z = exp(-x); return 1.0 / (1.0 + z); } const double z = exp(x); return z / (1.0 + z); }
+__device__ __forceinline__ double softplus_stable(double x) { if (x > 20.0) return x; if (x < -20.0) return exp(x); return log1p(exp(x)); }
+
+// grid.x = 2*groups (q/k heads) + d_inner/S (v runs) + 1 (beta/gate); grid.y = batch; block = S threads
+__global__ void k_dn_prep(DnDims D, const float *__restrict__ conv_kernel, const float *__restrict__ dt_bias, const float *__restrict__ ssm_a,
+                          const float *__restrict__ qkv, const float *__restrict__ ba, float *__restrict__ conv_state,
+                          float *__restrict__ qk, float *__restrict__ v, float *__restrict__ beta, float *__restrict__ gate) {
+    __shared__ double red[32];
+    const uint32_t seq = blockIdx.y, tid = threadIdx.x, S = D.S, ns = D.d_conv - 1u;
+    const uint32_t n_qk = 2u * D.groups, n_v = D.d_inner / S;
+    if (blockIdx.x == n_qk + n_v) {   // beta / gate of every value head
+        const uint32_t width = D.rank / D.groups, stride = 2u * width;
+        for (uint32_t h = tid; h < D.rank; h += blockDim.x) {
+            const uint32_t g = h / width, l = h - g * width;
+            const float *b = ba + (size_t)seq * 2u * D.rank;
+            beta[(size_t)seq * D.rank + h] = (float)sigmoid_stable((double)b[g * stride + l]);
+            gate[(size_t)seq * D.rank + h] = (float)(softplus_stable((double)b[g * stride + width + l] + (double)dt_bias[h]) * (double)ssm_a[h]);
+        }
+        return;
+    }
+    const uint32_t c = blockIdx.x * S + tid;          // channel: q heads, then k heads, then v
+    float *cs = conv_state + ((size_t)seq * D.channels + c) * ns;
+    const float *kr = conv_kernel + (size_t)c * D.d_conv;
+    const float xnew = qkv[(size_t)seq * D.channels + c];
+    double acc = 0.0;
+    for (uint32_t j = 0; j < ns; ++j) acc += (double)cs[j] * (double)kr[j];
+    acc += (double)xnew * (double)kr[ns];
+    for (uint32_t j = 0; j + 1u < ns; ++j) cs[j] = cs[j + 1u];
+    cs[ns - 1u] = xnew;
+    const float y = (float)(acc / (1.0 + exp(-acc)));
+    if (blockIdx.x >= n_qk) { v[(size_t)seq * D.d_inner + (c - n_qk * S)] = y; return; }
+    // L2 normalisation over the head (block)
+    double ss = (double)y * (double)y;
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((tid & 31u) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    double tot = 0.0;
+    for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
+    const double inv = 1.0 / fmax(sqrt(tot), (double)D.eps);
+    qk[(size_t)seq * n_qk * S + c] = (float)((double)y * inv);
+}
+
+// one warp per (seq, value head, state row); VPL = S / 32 values per lane, element i = lane + 32 * v
+template <int VPL>
+__global__ void __launch_bounds__(256) k_dn_state(DnDims D, uint32_t batch, const float *__restrict__ qk, const float *__restrict__ v,
+                                                  const float *__restrict__ beta, const float *__restrict__ gate,
+                                                  float *__restrict__ state, float *__restrict__ core) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t gw = (blockIdx.x * (uint64_t)blockDim.x + threadIdx.x) >> 5;
+    const uint32_t S = D.S;
+    const uint64_t rows = (uint64_t)batch * D.rank * S;
+    if (gw >= rows) return;
+    const uint32_t j = (uint32_t)(gw % S), h = (uint32_t)((gw / S) % D.rank), seq = (uint32_t)(gw / ((uint64_t)S * D.rank));
+    const uint32_t kh = h / (D.rank / D.groups);
+    const float *q = qk + ((size_t)seq * 2u * D.groups + kh) * S;
+    const float *k = qk + ((size_t)seq * 2u * D.groups + D.groups + kh) * S;
+    float *row = state + (((size_t)seq * D.rank + h) * S + j) * S;
+    const float decay = expf(gate[(size_t)seq * D.rank + h]);
+    float m[VPL], kv[VPL];
+    float sum = 0.f;
+#pragma unroll
+    for (int t = 0; t < VPL; ++t) { kv[t] = k[lane + 32 * t]; m[t] = row[lane + 32 * t] * decay; sum += m[t] * kv[t]; }
+    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float delta = (v[(size_t)seq * D.d_inner + (size_t)h * S + j] - sum) * beta[(size_t)seq * D.rank + h];
+    float o_acc = 0.f;
+#pragma unroll
+    for (int t = 0; t < VPL; ++t) { m[t] += kv[t] * delta; o_acc += m[t] * q[lane + 32 * t]; row[lane + 32 * t] = m[t]; }
+    for (int o = 16; o; o >>= 1) o_acc += __shfl_xor_sync(0xffffffffu, o_acc, o);
+    if (lane == 0) core[(size_t)seq * D.d_inner + (size_t)h * S + j] = o_acc * (1.0f / sqrtf((float)S));
+}
+
+// grid (rank, batch), block S threads
+__global__ void k_dn_tail(DnDims D, const float *__restrict__ core, const float *__restrict__ z, const float *__restrict__ norm_w, float *__restrict__ out) {
+    __shared__ double red[32];
+    const uint32_t h = blockIdx.x, seq = blockIdx.y, i = threadIdx.x, S = D.S;
+    const size_t idx = (size_t)seq * D.d_inner + (size_t)h * S + i;
+    const float x = core[idx], g = z[idx];
+    double ss = (double)x * (double)x;
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((i & 31u) == 0) red[i >> 5] = ss;
+    __syncthreads();
+    double tot = 0.0;
+    for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
+    const float inv = 1.0f / sqrtf((float)(tot / (double)S) + D.eps);
+    const float silu = g / (1.0f + expf(-g));
+    out[idx] = x * inv * norm_w[i] * silu;
+}
+
+int launch_deltanet(const DnDims &D, uint32_t batch, const float *conv_kernel, const float *dt_bias, const float *ssm_a, const float *norm_w,
+                    const float *qkv, const float *z, const float *ba, float *conv_state, float *rec_state,
+                    float *qk, float *v, float *beta, float *gate, float *core, float *out, cudaStream_t s) {
+    RC_REQUIRE(D.S >= 32u && D.S <= 256u && D.S % 32u == 0 && (D.S == 32u || D.S == 64u || D.S == 128u || D.S == 256u), "deltanet: state size %u not in {32,64,128,256}", D.S);
+    RC_REQUIRE(D.rank && D.groups && D.rank % D.groups == 0 && D.d_inner == D.rank * D.S && D.channels == 2u * D.S * D.groups + D.d_inner && D.d_conv >= 2u,
+               "deltanet: inconsistent dimensions");
+    if (!batch) return 1;
+    const dim3 gp(2u * D.groups + D.d_inner / D.S + 1u, batch);
+    prof_begin("dn_prep", s);
+    k_dn_prep<<<gp, D.S, 0, s>>>(D, conv_kernel, dt_bias, ssm_a, qkv, ba, conv_state, qk, v, beta, gate);
+    prof_end(s);
+    RC_LAUNCHED();
+    prof_begin("dn_state", s);
+    const uint64_t warps = (uint64_t)batch * D.rank * D.S;
+    const uint32_t blocks = (uint32_t)((warps + 7u) / 8u);
+    switch (D.S) {
+        case 32: k_dn_state<1><<<blocks, 256, 0, s>>>(D, batch, qk, v, beta, gate, rec_state, core); break;
+        case 64: k_dn_state<2><<<blocks, 256, 0, s>>>(D, batch, qk, v, beta, gate, rec_state, core); break;
+        case 128: k_dn_state<4><<<blocks, 256, 0, s>>>(D, batch, qk, v, beta, gate, rec_state, core); break;
+        default: k_dn_state<8><<<blocks, 256, 0, s>>>(D, batch, qk, v, beta, gate, rec_state, core); break;
+    }
+    prof_end(s);
+    RC_LAUNCHED();
+    prof_begin("dn_tail", s);
+    k_dn_tail<<<dim3(D.rank, batch), D.S, 0, s>>>(D, core, z, norm_w, out);
+    prof_end(s);
+    RC_LAUNCHED();
+    return 1;
+}
+
+}  // namespace rc
+
+using namespace rc;
+
+extern "C" int redcuda_deltanet_step(const redcuda_deltanet_params *p, uint32_t batch, const float *qkv, const float *z, const float *ba,
+                                     float *conv_state, float *rec_state, float *out) {
+    if (!require_device()) return 0;
+    RC_REQUIRE(p && qkv && z && ba && conv_state && rec_state && out && batch, "deltanet step: null or empty argument");
+    RC_REQUIRE(p->conv_kernel && p->dt_bias && p->ssm_a && p->ssm_norm, "deltanet step: null parameter array");
+    const DnDims D{p->d_conv, p->d_state, p->n_group, p->dt_rank, p->d_inner, p->channels, p->rms_eps};
+    RC_REQUIRE(D.rank && D.S && D.groups && D.d_conv >= 2u, "deltanet step: zero dimension");
+    const size_t ns = D.d_conv - 1u, nqk = 2u * (size_t)D.groups * D.S;
+    const size_t b_ck = (size_t)D.channels * D.d_conv * 4u, b_r = (size_t)D.rank * 4u, b_nw = (size_t)D.S * 4u;
+    const size_t b_qkv = (size_t)batch * D.channels * 4u, b_z = (size_t)batch * D.d_inner * 4u, b_ba = (size_t)batch * 2u * D.rank * 4u;
+    const size_t b_cs = (size_t)batch * D.channels * ns * 4u, b_rs = (size_t)batch * D.rank * D.S * D.S * 4u;
+    DevMem ck, dt, sa, nw, dq, dz, dba, cs, rs, qk, v, beta, gate, core, o;
+    if (!ck.alloc(b_ck) || !dt.alloc(b_r) || !sa.alloc(b_r) || !nw.alloc(b_nw) || !dq.alloc(b_qkv) || !dz.alloc(b_z) || !dba.alloc(b_ba) ||
+        !cs.alloc(b_cs) || !rs.alloc(b_rs) || !qk.alloc(batch * nqk * 4u) || !v.alloc(b_z) || !beta.alloc(batch * b_r) || !gate.alloc(batch * b_r) ||
+        !core.alloc(b_z) || !o.alloc(b_z)) return 0;
+    cudaStream_t s = 0;
+    RC_CUDA(cudaMemcpyAsync(ck.p, p->conv_kernel, b_ck, cudaMemcpyHostToDevice, s));
+    RC_CUDA(cudaMemcpyAsync(dt.p, p->dt_bias, b_r, cudaMemcpyHostToDevice, s));
+    RC_CUDA(cudaMemcpyAsync(sa.p, p->ssm_a, b_r, cudaMemcpyHostToDevice, s));
+    RC_CUDA(cudaMemcpyAsync(nw.p, p->ssm_norm, b_nw, cudaMemcpyHostToDevice, s));
+    RC_CUDA(cudaMemcpyAsync(dq.p, qkv, b_qkv, cudaMemcpyHostToDevice, s));
+    RC_CUDA(cudaMemcpyAsync(dz.p, z, b_z, cudaMemcpyHostToDevice, s));
+    RC_CUDA(cudaMemcpyAsync(dba.p, ba, b_ba, cudaMemcpyHostToDevice, s));
+    RC_CUDA(cudaMemcpyAsync(cs.p, conv_state, b_cs, cudaMemcpyHostToDevice, s));
+    RC_CUDA(cudaMemcpyAsync(rs.p, rec_state, b_rs, cudaMemcpyHostToDevice, s));
+    if (!launch_deltanet(D, batch, ck.as<float>(), dt.as<float>(), sa.as<float>(), nw.as<float>(), dq.as<float>(), dz.as<float>(), dba.as<float>(),
+                         cs.as<float>(), rs.as<float>(), qk.as<float>(), v.as<float>(), beta.as<float>(), gate.as<float>(), core.as<float>(), o.as<float>(), s)) return 0;
+    RC_CUDA(cudaMemcpyAsync(conv_state, cs.p, b_cs, cudaMemcpyDeviceToHost, s));
+    RC_CUDA(cudaMemcpyAsync(rec_state, rs.p, b_rs, cudaMemcpyDeviceToHost, s));
+    RC_CUDA(cudaMemcpyAsync(out, o.p, b_z, cudaMemcpyDeviceToHost, s));
+    RC_CUDA(cudaStreamSynchronize(s));
+    return 1;
+}

@@ -1,0 +1,37 @@
+// Launch-level interfaces shared between the translation units of the redcuda library.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rc {
+
+enum GemvEpilogue : uint32_t {
+    GEMV_STORE = 0,       // out[t][row] = W0[row] . x[t]
+    GEMV_PAIR_SILU = 1,   // out[t][row] = SiLU(W0[row] . x[t]) * (W1[row] . x[t])   (gate/up pair of an FFN)
+    GEMV_SIGMOID = 2,     // out[t][row] = sigmoid(W0[row] . x[t])                    (shared-expert scalar gate)
+};
+
+struct GemvJob {
+    const uint8_t *w0, *w1;
+    float *out;
+    uint64_t nb;
+    uint32_t type, nrows, ncols, out_stride, epi;
+    uint32_t tile_begin, rows_per_tile;     // filled by launch_gemv
+};
+
+#define RC_MAX_JOBS 6u
+struct GemvArgs {
+    GemvJob job[RC_MAX_JOBS];
+    uint32_t njobs, ntok;
+    const float *x;            // [ntok][x_stride] device
+    uint32_t x_stride;
+    const uint8_t *iq2;        // filled by launch_gemv
+    const uint32_t *iq3s;
+    const char *tag;           // name under which the launch is timed when profiling is on (host side only)
+};
+
+int launch_gemv(GemvArgs &A, cudaStream_t stream);
+int launch_route(const float *logits_dev, uint32_t ntok, uint32_t n_expert, uint32_t top_k, uint32_t *ids_dev, float *weights_dev,
+                 float *probs_dev, cudaStream_t stream);
+
+}  // namespace rc

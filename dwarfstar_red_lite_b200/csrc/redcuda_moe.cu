@@ -1,0 +1,443 @@
+// Resident MoE layer: router, expert-grouped routed FFN, sigmoid-gated shared expert.
+//
+// Pass structure (one stream, no host round trip; the reference's GPU path needs the same dependency chain,
+// native/redmetal_engine.m:1733-1863):
+//   1. one multi-job GEMV over the token activations: router logits (F32 rows, fp64 accumulation), shared gate/up with
+//      SiLU*mul fused, shared-expert scalar gate with the sigmoid fused
+//   2. softmax + top-k per token (ties -> lower id)
+//   3. (token, expert) pairs grouped by expert on the device — the layout the reference builds on the CPU for its
+//      batched path (expert_start / pair_token, native/redmetal_topk.h:182-190)
+//   4. gate/up of every selected expert over the tokens routed to it (weights decoded once per pass of up to 4 tokens)
+//   5. shared down projection
+//   6. down projection per pair
+//   7. per-token combine in router order: out = resid + sum_k w_k * expert_k + shared * scalar
+#include "redcuda_common.cuh"
+#include "redcuda_dot.cuh"
+#include "redcuda_kernels.cuh"
+#include "../../include/redcuda.h"
+
+#include <new>
+
+namespace rc {
+
+struct MoeArgs {
+    const uint8_t *w0, *w1;        // expert matrices of the shard, back to back (gate / up, or down / unused)
+    uint64_t mat_bytes, nb;        // bytes and blocks of one expert matrix
+    uint32_t type, nrows, ncols;   // per expert matrix
+    uint32_t expert_begin, rows_per_tile;
+    const uint32_t *sorted, *uexp, *ustart, *n_unique;
+    const float *x; uint32_t x_stride, x_div;   // activation row of pair p = x + (p / x_div) * x_stride
+    float *out; uint32_t out_stride;            // result row of pair p = out + p * out_stride
+    uint32_t pair_silu;                         // 1: out = SiLU(w0.x) * (w1.x); 0: out = w0.x
+    const uint8_t *iq2; const uint32_t *iq3s;
+};
+
+template <int TYPE, int NT>
+__device__ __forceinline__ void moe_tile(const MoeArgs &A, const uint8_t *m0, const uint8_t *m1, uint32_t row0, uint32_t p0, uint32_t nt,
+                                         const float *xs, uint32_t xstride, const SBooks &sb) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, nwarps = blockDim.x >> 5;
+    const uint32_t cpr = A.ncols >> 6;
+    uint32_t lpr = 32u;
+    while (lpr > cpr) lpr >>= 1;
+    const uint32_t rw = 32u / lpr, slot = lane / lpr, sub = lane % lpr;
+    const uint32_t row_end = min(row0 + A.rows_per_tile, A.nrows);
+    for (uint32_t r = row0 + warp * rw; r < row_end; r += nwarps * rw) {
+        const uint32_t row = r + slot;
+        const bool live = row < row_end;
+        const uint64_t rr = live ? row : (uint64_t)(row_end - 1u);
+        float a0[NT], a1[NT];
+        row_dot<TYPE, NT>(m0, A.nb, rr, A.ncols, lpr, sub, xs, xstride, sb, a0);
+        if (A.pair_silu) row_dot<TYPE, NT>(m1, A.nb, rr, A.ncols, lpr, sub, xs, xstride, sb, a1);
+        if (live && sub == 0u) {
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                if ((uint32_t)t >= nt) break;
+                const uint32_t p = A.sorted[p0 + t];
+                A.out[(size_t)p * A.out_stride + row] = A.pair_silu ? silu_mul(a0[t], a1[t]) : a0[t];
+            }
+        }
+    }
+}
+
+template <int NT>
+__global__ void __launch_bounds__(256) k_moe_experts(const __grid_constant__ MoeArgs A) {
+    extern __shared__ __align__(16) float xs[];
+    __shared__ uint2 s_iq2[256];
+    __shared__ uint32_t s_iq3s[512];
+    const uint32_t u = blockIdx.y;
+    if (u >= *A.n_unique) return;
+    const uint32_t e = A.uexp[u] - A.expert_begin, ps = A.ustart[u], pe = A.ustart[u + 1u];
+    const uint8_t *m0 = A.w0 + (size_t)e * A.mat_bytes, *m1 = A.w1 ? A.w1 + (size_t)e * A.mat_bytes : nullptr;
+    const uint32_t row0 = blockIdx.x * A.rows_per_tile;
+    load_books(s_iq2, s_iq3s, A.iq2, A.iq3s, 1u << A.type);
+    const SBooks sb{s_iq2, s_iq3s};
+    const uint32_t xstride = x_padded(A.ncols);
+    for (uint32_t p0 = ps; p0 < pe; p0 += NT) {
+        const uint32_t nt = min((uint32_t)NT, pe - p0);
+        __syncthreads();
+        {   // stage the activation rows of pairs [p0, p0 + nt)
+            const uint32_t n4 = A.ncols >> 2;
+            for (uint32_t i = threadIdx.x; i < NT * n4; i += blockDim.x) {
+                const uint32_t t = i / n4, k = (i - t * n4) << 2;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (t < nt) v = *reinterpret_cast<const float4 *>(A.x + (size_t)(A.sorted[p0 + t] / A.x_div) * A.x_stride + k);
+                *reinterpret_cast<float4 *>(xs + t * xstride + xi(k)) = v;
+            }
+        }
+        __syncthreads();
+        switch (A.type) {
+            case RC_IQ2_XXS: moe_tile<RC_IQ2_XXS, NT>(A, m0, m1, row0, p0, nt, xs, xstride, sb); break;
+            case RC_IQ3_S: moe_tile<RC_IQ3_S, NT>(A, m0, m1, row0, p0, nt, xs, xstride, sb); break;
+            case RC_Q6_K: moe_tile<RC_Q6_K, NT>(A, m0, m1, row0, p0, nt, xs, xstride, sb); break;
+            default: break;
+        }
+    }
+}
+
+// Group pairs by expert: sorted[] = pair ids, expert by expert (ascending expert id); uexp / ustart list the experts
+// that received at least one pair; n_unique their count. One block of 1024 threads, expert_count <= 1024.
+__global__ void __launch_bounds__(1024) k_group_pairs(const uint32_t *__restrict__ pair_expert, uint32_t npairs, uint32_t expert_begin,
+                                                      uint32_t expert_count, uint32_t *__restrict__ sorted, uint32_t *__restrict__ uexp,
+                                                      uint32_t *__restrict__ ustart, uint32_t *__restrict__ n_unique, uint32_t *__restrict__ bad) {
+    __shared__ uint32_t cnt[1024], start[1024], wsum[32], wsum2[32];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    cnt[tid] = 0;
+    __syncthreads();
+    for (uint32_t p = tid; p < npairs; p += 1024u) {
+        const uint32_t e = pair_expert[p] - expert_begin;
+        if (e < expert_count) atomicAdd(&cnt[e], 1u); else atomicAdd(bad, 1u);   // a pair outside the shard is reported, not run
+    }
+    __syncthreads();
+    // exclusive scans over experts of (count) and (count > 0)
+    const uint32_t c = tid < expert_count ? cnt[tid] : 0u, f = c ? 1u : 0u;
+    uint32_t sc = c, sf = f;
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t a = __shfl_up_sync(0xffffffffu, sc, o), b = __shfl_up_sync(0xffffffffu, sf, o);
+        if ((int)lane >= o) { sc += a; sf += b; }
+    }
+    if (lane == 31u) { wsum[warp] = sc; wsum2[warp] = sf; }
+    __syncthreads();
+    if (warp == 0) {
+        uint32_t a = wsum[lane], b = wsum2[lane];
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t ua = __shfl_up_sync(0xffffffffu, a, o), ub = __shfl_up_sync(0xffffffffu, b, o);
+            if ((int)lane >= o) { a += ua; b += ub; }
+        }
+        wsum[lane] = a; wsum2[lane] = b;
+    }
+    __syncthreads();
+    const uint32_t basec = warp ? wsum[warp - 1u] : 0u, basef = warp ? wsum2[warp - 1u] : 0u;
+    const uint32_t exc = basec + sc - c, exf = basef + sf - f;
+    start[tid] = exc;
+    if (f) { uexp[exf] = expert_begin + tid; ustart[exf] = exc; }
+    if (tid == 1023u) { const uint32_t nu = exf + f; *n_unique = nu; ustart[nu] = exc + c; }
+    cnt[tid] = 0;
+    __syncthreads();
+    for (uint32_t p = tid; p < npairs; p += 1024u) {
+        const uint32_t e = pair_expert[p] - expert_begin;
+        if (e < expert_count) sorted[start[e] + atomicAdd(&cnt[e], 1u)] = p;
+    }
+}
+
+// Single-token case: the k selected experts are distinct, so every pair is its own group.
+__global__ void k_group_trivial(const uint32_t *__restrict__ pair_expert, uint32_t npairs, uint32_t *__restrict__ sorted,
+                                uint32_t *__restrict__ uexp, uint32_t *__restrict__ ustart, uint32_t *__restrict__ n_unique) {
+    const uint32_t i = threadIdx.x;
+    if (i < npairs) { sorted[i] = i; uexp[i] = pair_expert[i]; ustart[i] = i; }
+    if (i == 0) { ustart[npairs] = npairs; *n_unique = npairs; }
+}
+
+// out[t] = resid[t] + (sum_k w[t][k] * pair_out[t*k + kk] + shared[t] * scalar[t]); k may be 0 (shared part only).
+__global__ void __launch_bounds__(256) k_moe_combine(const float *__restrict__ pair_out, const float *__restrict__ w, uint32_t top_k,
+                                                     const float *__restrict__ shared, const float *__restrict__ scalar,
+                                                     const float *__restrict__ resid, float *__restrict__ out, uint32_t hidden) {
+    const uint32_t t = blockIdx.y;
+    const uint32_t r = (blockIdx.x * 256u + threadIdx.x) * 4u;
+    if (r >= hidden) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t k = 0; k < top_k; ++k) {
+        const float wk = w[(size_t)t * top_k + k];
+        const float4 v = *reinterpret_cast<const float4 *>(pair_out + ((size_t)t * top_k + k) * hidden + r);
+        acc.x += wk * v.x; acc.y += wk * v.y; acc.z += wk * v.z; acc.w += wk * v.w;
+    }
+    if (shared) {
+        const float s = scalar[t];
+        const float4 v = *reinterpret_cast<const float4 *>(shared + (size_t)t * hidden + r);
+        acc.x += v.x * s; acc.y += v.y * s; acc.z += v.z * s; acc.w += v.w * s;
+    }
+    if (resid) {
+        const float4 v = *reinterpret_cast<const float4 *>(resid + (size_t)t * hidden + r);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4 *>(out + (size_t)t * hidden + r) = acc;
+}
+
+}  // namespace rc
+
+using namespace rc;
+
+struct redcuda_moe {
+    redcuda_moe_desc d;
+    int device = 0;
+    DevMem wmem, ws;
+    DMat router, sh_gate_inp, sh_gate, sh_up, sh_down;
+    uint8_t *gate = nullptr, *up = nullptr, *down = nullptr;
+    uint64_t gu_bytes = 0, down_bytes = 0, gu_nb = 0, down_nb = 0;
+    // workspace
+    float *x = nullptr, *logits = nullptr, *wk = nullptr, *scalar = nullptr, *sh_act = nullptr, *sh_out = nullptr, *act = nullptr, *tmp = nullptr, *out = nullptr;
+    uint32_t *ids = nullptr, *sorted = nullptr, *uexp = nullptr, *ustart = nullptr, *n_unique = nullptr, *bad = nullptr;
+    uint32_t max_pairs = 0;
+    cudaStream_t stream = nullptr;
+};
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static int moe_gemv_pre(redcuda_moe *m, uint32_t ntok, const float *x, bool with_router, bool with_shared, cudaStream_t s) {
+    GemvArgs A{};
+    A.ntok = ntok; A.x = x; A.x_stride = m->d.hidden;
+    uint32_t j = 0;
+    auto add = [&](const DMat &w0, const DMat *w1, float *out, uint32_t stride, uint32_t epi) {
+        GemvJob &J = A.job[j++];
+        J.w0 = w0.base; J.w1 = w1 ? w1->base : nullptr; J.out = out; J.nb = w0.nb; J.type = w0.type; J.nrows = w0.nrows; J.ncols = w0.ncols;
+        J.out_stride = stride; J.epi = epi;
+    };
+    if (with_router) add(m->router, nullptr, m->logits, m->d.n_expert, GEMV_STORE);
+    if (with_shared) {
+        add(m->sh_gate, &m->sh_up, m->sh_act, m->d.ffn_sh, GEMV_PAIR_SILU);
+        add(m->sh_gate_inp, nullptr, m->scalar, 1u, GEMV_SIGMOID);
+    }
+    if (!j) return 1;
+    A.njobs = j;
+    A.tag = "moe_pre_gemv";
+    return launch_gemv(A, s);
+}
+
+static int moe_shared_down(redcuda_moe *m, uint32_t ntok, cudaStream_t s) {
+    GemvArgs A{};
+    A.ntok = ntok; A.x = m->sh_act; A.x_stride = m->d.ffn_sh; A.njobs = 1;
+    GemvJob &J = A.job[0];
+    J.w0 = m->sh_down.base; J.out = m->sh_out; J.nb = m->sh_down.nb; J.type = m->sh_down.type; J.nrows = m->sh_down.nrows; J.ncols = m->sh_down.ncols;
+    J.out_stride = m->d.hidden; J.epi = GEMV_STORE;
+    A.tag = "moe_shared_down_gemv";
+    return launch_gemv(A, s);
+}
+
+static int moe_launch_experts(redcuda_moe *m, bool gateup, uint32_t npairs, bool single_token, const float *x, uint32_t x_stride, uint32_t x_div,
+                              float *out, uint32_t out_stride, cudaStream_t s) {
+    MoeArgs A{};
+    A.w0 = gateup ? m->gate : m->down; A.w1 = gateup ? m->up : nullptr;
+    A.mat_bytes = gateup ? m->gu_bytes : m->down_bytes; A.nb = gateup ? m->gu_nb : m->down_nb;
+    A.type = gateup ? m->d.type_gu : m->d.type_down;
+    A.nrows = gateup ? m->d.ffn : m->d.hidden; A.ncols = gateup ? m->d.hidden : m->d.ffn;
+    A.expert_begin = m->d.expert_begin;
+    A.sorted = m->sorted; A.uexp = m->uexp; A.ustart = m->ustart; A.n_unique = m->n_unique;
+    A.x = x; A.x_stride = x_stride; A.x_div = x_div; A.out = out; A.out_stride = out_stride; A.pair_silu = gateup ? 1u : 0u;
+    A.iq2 = books_iq2(); A.iq3s = books_iq3s();
+    uint32_t lpr = 32u;
+    while (lpr > (A.ncols >> 6)) lpr >>= 1;
+    const uint32_t rows_per_pass = 8u * (32u / lpr);
+    const uint32_t groups = npairs < m->d.expert_count ? npairs : m->d.expert_count;   // upper bound of experts that got a pair
+    // >= 2 blocks per SM when the row count allows, at most 8 sweeps per block
+    uint32_t sweeps = (uint32_t)(((uint64_t)A.nrows * groups) / ((uint64_t)rows_per_pass * 148u * 2u));
+    sweeps = sweeps < 1u ? 1u : sweeps > 8u ? 8u : sweeps;
+    A.rows_per_tile = rows_per_pass * sweeps;
+    const dim3 grid((A.nrows + A.rows_per_tile - 1u) / A.rows_per_tile, groups);
+    const int nt = single_token ? 1 : 4;
+    const size_t smem = (size_t)nt * x_padded(A.ncols) * sizeof(float);
+    RC_REQUIRE(smem <= 200u * 1024u, "moe: row length %u too large for the shared-memory staging", A.ncols);
+    prof_begin(gateup ? "moe_gateup" : "moe_down", s);
+    if (nt == 1) {
+        if (smem > 48u * 1024u) RC_CUDA(cudaFuncSetAttribute(k_moe_experts<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k_moe_experts<1><<<grid, 256, smem, s>>>(A);
+    } else {
+        if (smem > 48u * 1024u) RC_CUDA(cudaFuncSetAttribute(k_moe_experts<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k_moe_experts<4><<<grid, 256, smem, s>>>(A);
+    }
+    prof_end(s);
+    RC_LAUNCHED();
+    return 1;
+}
+
+static int moe_group(redcuda_moe *m, const uint32_t *pair_expert, uint32_t npairs, bool distinct, cudaStream_t s) {
+    RC_REQUIRE(npairs <= m->max_pairs, "moe: %u pairs exceed the workspace (%u)", npairs, m->max_pairs);
+    prof_begin("moe_group", s);
+    if (distinct && npairs <= 64u) {
+        k_group_trivial<<<1, 64, 0, s>>>(pair_expert, npairs, m->sorted, m->uexp, m->ustart, m->n_unique);
+    } else {
+        k_group_pairs<<<1, 1024, 0, s>>>(pair_expert, npairs, m->d.expert_begin, m->d.expert_count, m->sorted, m->uexp, m->ustart, m->n_unique, m->bad);
+    }
+    prof_end(s);
+    RC_LAUNCHED();
+    return 1;
+}
+
+static int moe_combine(redcuda_moe *m, uint32_t ntok, const float *pair_out, const float *wk, uint32_t top_k, bool shared, const float *resid,
+                       float *out, cudaStream_t s) {
+    const dim3 grid((m->d.hidden / 4u + 255u) / 256u, ntok);
+    prof_begin("moe_combine", s);
+    k_moe_combine<<<grid, 256, 0, s>>>(pair_out, wk, top_k, shared ? m->sh_out : nullptr, m->scalar, resid, out, m->d.hidden);
+    prof_end(s);
+    RC_LAUNCHED();
+    return 1;
+}
+
+static int moe_forward_on(redcuda_moe *m, uint32_t ntok, const float *x, const float *logits_in, const float *resid, float *out, cudaStream_t s) {
+    RC_REQUIRE(m->d.expert_begin == 0 && m->d.expert_count == m->d.n_expert, "moe forward needs every expert on this device; use the route/experts/shared pieces under expert parallelism");
+    RC_REQUIRE(ntok >= 1 && ntok <= m->d.max_tokens, "moe forward: ntok %u outside [1, %u]", ntok, m->d.max_tokens);
+    const uint32_t k = m->d.top_k, npairs = ntok * k;
+    if (!moe_gemv_pre(m, ntok, x, logits_in == nullptr, true, s)) return 0;
+    if (!launch_route(logits_in ? logits_in : m->logits, ntok, m->d.n_expert, k, m->ids, m->wk, nullptr, s)) return 0;
+    if (!moe_group(m, m->ids, npairs, ntok == 1u, s)) return 0;
+    if (!moe_launch_experts(m, true, npairs, ntok == 1u, x, m->d.hidden, k, m->act, m->d.ffn, s)) return 0;
+    if (!moe_shared_down(m, ntok, s)) return 0;
+    if (!moe_launch_experts(m, false, npairs, ntok == 1u, m->act, m->d.ffn, 1u, m->tmp, m->d.hidden, s)) return 0;
+    return moe_combine(m, ntok, m->tmp, m->wk, k, true, resid, out, s);
+}
+
+extern "C" {
+
+redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
+    if (!require_device()) return nullptr;
+    if (!desc) { set_error("moe create: null descriptor"); return nullptr; }
+    const redcuda_moe_desc &d = *desc;
+    auto fail = [](const char *msg) -> redcuda_moe * { set_error("moe create: %s", msg); return nullptr; };
+    if (!d.hidden || !d.n_expert || !d.top_k || !d.ffn || !d.ffn_sh || !d.max_tokens) return fail("zero dimension");
+    if (d.top_k > REDCUDA_MAX_TOPK || d.top_k > d.n_expert) return fail("top_k out of range");
+    if (d.hidden % 256u || d.ffn % 256u || d.ffn_sh % 256u) return fail("hidden / ffn sizes must be multiples of 256");
+    if (!rc_is_quant(d.type_gu) || !rc_is_quant(d.type_down) || !rc_is_quant(d.type_sh)) return fail("expert matrices must be IQ2_XXS, IQ3_S or Q6_K");
+    if (d.expert_count == 0 || d.expert_begin + d.expert_count > d.n_expert || d.expert_count > 1024u) return fail("bad expert shard");
+    if (!d.router || !d.gate_exps || !d.up_exps || !d.down_exps || !d.sh_gate_inp || !d.sh_gate || !d.sh_up || !d.sh_down) return fail("null weight pointer");
+    if (!require_books(d.type_gu) || !require_books(d.type_down) || !require_books(d.type_sh)) return nullptr;
+
+    redcuda_moe *m = new (std::nothrow) redcuda_moe();
+    if (!m) return fail("out of host memory");
+    m->d = d;
+    cudaGetDevice(&m->device);
+    auto bail = [&]() -> redcuda_moe * { redcuda_moe_destroy(m); return nullptr; };
+    if (cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess) { set_error("moe create: stream creation failed"); return bail(); }
+
+    m->gu_bytes = rc_matrix_bytes(d.type_gu, d.ffn, d.hidden);
+    m->down_bytes = rc_matrix_bytes(d.type_down, d.hidden, d.ffn);
+    m->gu_nb = (uint64_t)d.ffn * (d.hidden / 256u);
+    m->down_nb = (uint64_t)d.hidden * (d.ffn / 256u);
+    if (m->gu_bytes % 16u || m->down_bytes % 16u) { set_error("moe create: expert matrix size is not a multiple of 16 bytes"); return bail(); }
+    const size_t router_b = (size_t)d.n_expert * d.hidden * 4u, gvec_b = (size_t)d.hidden * 4u;
+    const size_t shgu_b = rc_matrix_bytes(d.type_sh, d.ffn_sh, d.hidden), shd_b = rc_matrix_bytes(d.type_sh, d.hidden, d.ffn_sh);
+    size_t off = 0;
+    const size_t o_router = off; off = align_up(off + router_b, 256);
+    const size_t o_gate = off; off = align_up(off + m->gu_bytes * d.expert_count, 256);
+    const size_t o_up = off; off = align_up(off + m->gu_bytes * d.expert_count, 256);
+    const size_t o_down = off; off = align_up(off + m->down_bytes * d.expert_count, 256);
+    const size_t o_gvec = off; off = align_up(off + gvec_b, 256);
+    const size_t o_shg = off; off = align_up(off + shgu_b, 256);
+    const size_t o_shu = off; off = align_up(off + shgu_b, 256);
+    const size_t o_shd = off; off = align_up(off + shd_b, 256);
+    if (!m->wmem.alloc(off)) return bail();
+    uint8_t *W = m->wmem.as<uint8_t>();
+    m->gate = W + o_gate; m->up = W + o_up; m->down = W + o_down;
+    m->router = DMat{W + o_router, RC_F32, d.n_expert, d.hidden, 0};
+    m->sh_gate_inp = DMat{W + o_gvec, RC_F32, 1u, d.hidden, 0};
+    m->sh_gate = DMat{W + o_shg, d.type_sh, d.ffn_sh, d.hidden, (uint64_t)d.ffn_sh * (d.hidden / 256u)};
+    m->sh_up = DMat{W + o_shu, d.type_sh, d.ffn_sh, d.hidden, (uint64_t)d.ffn_sh * (d.hidden / 256u)};
+    m->sh_down = DMat{W + o_shd, d.type_sh, d.hidden, d.ffn_sh, (uint64_t)d.hidden * (d.ffn_sh / 256u)};
+
+    // upload + planar repack; host sources go through a bounded staging buffer, expert by expert
+    const bool dev = d.weights_on_device != 0;
+    DevMem scratch;
+    const size_t big = m->gu_bytes > m->down_bytes ? m->gu_bytes : m->down_bytes;
+    const size_t sc_b = big > shgu_b ? (big > shd_b ? big : shd_b) : (shgu_b > shd_b ? shgu_b : shd_b);
+    if (!dev && !scratch.alloc(sc_b)) return bail();
+    cudaStream_t s = m->stream;
+    int ok = upload_matrix(RC_F32, d.n_expert, d.hidden, d.router, dev, W + o_router, nullptr, s) &&
+             upload_matrix(RC_F32, 1u, d.hidden, d.sh_gate_inp, dev, W + o_gvec, nullptr, s) &&
+             upload_matrix(d.type_sh, d.ffn_sh, d.hidden, d.sh_gate, dev, W + o_shg, scratch.as<uint8_t>(), s) &&
+             upload_matrix(d.type_sh, d.ffn_sh, d.hidden, d.sh_up, dev, W + o_shu, scratch.as<uint8_t>(), s) &&
+             upload_matrix(d.type_sh, d.hidden, d.ffn_sh, d.sh_down, dev, W + o_shd, scratch.as<uint8_t>(), s);
+    for (uint32_t e = 0; ok && e < d.expert_count; ++e) {
+        ok = upload_matrix(d.type_gu, d.ffn, d.hidden, d.gate_exps + (size_t)e * m->gu_bytes, dev, m->gate + (size_t)e * m->gu_bytes, scratch.as<uint8_t>(), s) &&
+             upload_matrix(d.type_gu, d.ffn, d.hidden, d.up_exps + (size_t)e * m->gu_bytes, dev, m->up + (size_t)e * m->gu_bytes, scratch.as<uint8_t>(), s) &&
+             upload_matrix(d.type_down, d.hidden, d.ffn, d.down_exps + (size_t)e * m->down_bytes, dev, m->down + (size_t)e * m->down_bytes, scratch.as<uint8_t>(), s);
+    }
+    if (!ok) return bail();
+
+    // workspace
+    const size_t T = d.max_tokens, P = T * d.top_k;
+    m->max_pairs = (uint32_t)P;
+    size_t w = 0;
+    auto take = [&](size_t bytes) { const size_t o = w; w = align_up(w + bytes, 256); return o; };
+    const size_t o_x = take(T * d.hidden * 4u), o_log = take(T * d.n_expert * 4u), o_wk = take(P * 4u), o_sca = take(T * 4u),
+                 o_sha = take(T * d.ffn_sh * 4u), o_sho = take(T * d.hidden * 4u), o_act = take(P * d.ffn * 4u), o_tmp = take(P * d.hidden * 4u),
+                 o_out = take(T * d.hidden * 4u), o_ids = take(P * 4u), o_sorted = take(P * 4u), o_uexp = take((size_t)(d.expert_count + 1u) * 4u),
+                 o_ustart = take((size_t)(d.expert_count + 2u) * 4u), o_nu = take(16), o_bad = take(16);
+    if (!m->ws.alloc(w)) return bail();
+    uint8_t *B = m->ws.as<uint8_t>();
+    m->x = (float *)(B + o_x); m->logits = (float *)(B + o_log); m->wk = (float *)(B + o_wk); m->scalar = (float *)(B + o_sca);
+    m->sh_act = (float *)(B + o_sha); m->sh_out = (float *)(B + o_sho); m->act = (float *)(B + o_act); m->tmp = (float *)(B + o_tmp);
+    m->out = (float *)(B + o_out); m->ids = (uint32_t *)(B + o_ids); m->sorted = (uint32_t *)(B + o_sorted); m->uexp = (uint32_t *)(B + o_uexp);
+    m->ustart = (uint32_t *)(B + o_ustart); m->n_unique = (uint32_t *)(B + o_nu); m->bad = (uint32_t *)(B + o_bad);
+    if (cudaMemsetAsync(B, 0, w, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) {
+        set_error("moe create: weight upload failed: %s", cudaGetErrorString(cudaGetLastError()));
+        return bail();
+    }
+    m->d.router = nullptr; m->d.gate_exps = m->d.up_exps = m->d.down_exps = nullptr; m->d.sh_gate_inp = nullptr; m->d.sh_gate = m->d.sh_up = m->d.sh_down = nullptr;
+    return m;
+}
+
+void redcuda_moe_destroy(redcuda_moe *m) {
+    if (!m) return;
+    if (m->stream) { cudaStreamSynchronize(m->stream); cudaStreamDestroy(m->stream); }
+    delete m;
+}
+
+uint64_t redcuda_moe_resident_bytes(const redcuda_moe *m) { return m ? m->wmem.bytes : 0; }
+
+int redcuda_moe_forward_device(redcuda_moe *m, uint32_t ntok, const float *x_dev, const float *logits_in_dev, const float *resid_dev,
+                               float *out_dev, void *stream) {
+    RC_REQUIRE(m && x_dev && out_dev, "moe forward: null argument");
+    return moe_forward_on(m, ntok, x_dev, logits_in_dev, resid_dev, out_dev, (cudaStream_t)stream);
+}
+
+int redcuda_moe_forward(redcuda_moe *m, uint32_t ntok, const float *x, const float *logits_in, float *out,
+                        uint32_t *ids_out, float *weights_out, float *logits_out) {
+    RC_REQUIRE(m && x && out, "moe forward: null argument");
+    RC_REQUIRE(ntok >= 1 && ntok <= m->d.max_tokens, "moe forward: ntok %u outside [1, %u]", ntok, m->d.max_tokens);
+    RC_CUDA(cudaSetDevice(m->device));
+    cudaStream_t s = m->stream;
+    const size_t xb = (size_t)ntok * m->d.hidden * 4u, lb = (size_t)ntok * m->d.n_expert * 4u, kb = (size_t)ntok * m->d.top_k * 4u;
+    RC_CUDA(cudaMemcpyAsync(m->x, x, xb, cudaMemcpyHostToDevice, s));
+    if (logits_in) RC_CUDA(cudaMemcpyAsync(m->logits, logits_in, lb, cudaMemcpyHostToDevice, s));
+    if (!moe_forward_on(m, ntok, m->x, logits_in ? m->logits : nullptr, nullptr, m->out, s)) return 0;
+    RC_CUDA(cudaMemcpyAsync(out, m->out, xb, cudaMemcpyDeviceToHost, s));
+    if (ids_out) RC_CUDA(cudaMemcpyAsync(ids_out, m->ids, kb, cudaMemcpyDeviceToHost, s));
+    if (weights_out) RC_CUDA(cudaMemcpyAsync(weights_out, m->wk, kb, cudaMemcpyDeviceToHost, s));
+    if (logits_out) RC_CUDA(cudaMemcpyAsync(logits_out, m->logits, lb, cudaMemcpyDeviceToHost, s));
+    RC_CUDA(cudaStreamSynchronize(s));
+    return 1;
+}
+
+int redcuda_moe_route_device(redcuda_moe *m, uint32_t ntok, const float *x_dev, const float *logits_in_dev, uint32_t *ids_dev, float *weights_dev, void *stream) {
+    RC_REQUIRE(m && ids_dev && weights_dev && (x_dev || logits_in_dev), "moe route: null argument");
+    RC_REQUIRE(ntok >= 1 && ntok <= m->d.max_tokens, "moe route: ntok %u outside [1, %u]", ntok, m->d.max_tokens);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!logits_in_dev && !moe_gemv_pre(m, ntok, x_dev, true, false, s)) return 0;
+    return launch_route(logits_in_dev ? logits_in_dev : m->logits, ntok, m->d.n_expert, m->d.top_k, ids_dev, weights_dev, nullptr, s);
+}
+
+int redcuda_moe_experts_device(redcuda_moe *m, uint32_t npairs, const float *pair_x_dev, const uint32_t *pair_expert_dev, float *pair_out_dev, void *stream) {
+    RC_REQUIRE(m && pair_x_dev && pair_expert_dev && pair_out_dev, "moe experts: null argument");
+    if (!npairs) return 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!moe_group(m, pair_expert_dev, npairs, false, s)) return 0;
+    if (!moe_launch_experts(m, true, npairs, false, pair_x_dev, m->d.hidden, 1u, m->act, m->d.ffn, s)) return 0;
+    return moe_launch_experts(m, false, npairs, false, m->act, m->d.ffn, 1u, pair_out_dev, m->d.hidden, s);
+}
+
+int redcuda_moe_shared_device(redcuda_moe *m, uint32_t ntok, const float *x_dev, float *out_dev, void *stream) {
+    RC_REQUIRE(m && x_dev && out_dev, "moe shared: null argument");
+    RC_REQUIRE(ntok >= 1 && ntok <= m->d.max_tokens, "moe shared: ntok %u outside [1, %u]", ntok, m->d.max_tokens);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!moe_gemv_pre(m, ntok, x_dev, false, true, s) || !moe_shared_down(m, ntok, s)) return 0;
+    return moe_combine(m, ntok, nullptr, nullptr, 0u, true, nullptr, out_dev, s);
+}
+
+}  // extern "C"

@@ -1,0 +1,140 @@
+/*
+ * redcuda — C ABI of the B200 (sm_100a) backend for Red Lite's Qwen3-Next decode hot path.
+ *
+ * Plain C linkage, plain pointers and sizes; no C++ or torch types cross this boundary. Conventions follow the
+ * reference (native/redlite_native_engine.h:89-93, native/redmetal_topk.h:13-14): functions return 1 on success and
+ * 0 on failure; the message of the last failure on the calling thread is read with redcuda_last_error(). Output
+ * buffers are caller-owned. Unless a function says "device", pointers are HOST pointers and the call is synchronous
+ * (it returns after the results are in the caller's buffer), like redmetal_topk_pool_execute. "Device" variants take
+ * CUDA device pointers and a cudaStream_t passed as void*, return right after the launches, and never allocate.
+ *
+ * ggml type ids: 0 F32, 1 F16, 14 Q6_K, 16 IQ2_XXS, 21 IQ3_S. Matrices are GGUF rows (row-major, the row length is
+ * the input dimension), exactly the bytes of the GGUF tensor; the library re-lays them out in HBM at load.
+ *
+ * There is no CPU fallback: every entry point fails with a message when no CUDA device is usable.
+ */
+#ifndef REDCUDA_H
+#define REDCUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define REDCUDA_ABI_VERSION 1u
+#define REDCUDA_MAX_TOPK 64u          /* RL_ENGINE_MAX_TOPK, native/redlite_native_engine_internal.h:19 */
+
+/* replaces redmetal_topk_abi_version / redmetal_topk_last_error (native/redmetal_topk.h:13-14) */
+uint32_t redcuda_abi_version(void);
+const char *redcuda_last_error(void);
+/* number of usable CUDA devices (0 when none); selects the device for every later call on this thread's objects */
+int redcuda_device_count(void);
+int redcuda_set_device(int device);
+
+/*
+ * Codebooks of the IQ formats, supplied by the host exactly as the reference supplies its grids to the Metal pool
+ * (iq2_xs_grid / iq1_m_grid arguments of redmetal_topk_pool_create, native/redmetal_topk.h:16-24):
+ * iq2xxs_grid = 256 entries x 8 magnitude bytes (rl_native_iq2_xxs_build_grid, native/redlite_native_iq2_xxs.c:39),
+ * iq3s_grid = 512 packed entries (rl_iq3s_grid, native/redlite_native_iq3_tables.h). Must be called once per
+ * device before any IQ2_XXS / IQ3_S data is decoded.
+ */
+int redcuda_set_codebooks(const uint8_t *iq2xxs_grid, uint32_t iq2xxs_bytes, const uint32_t *iq3s_grid, uint32_t iq3s_count);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Stage entry points (host pointers, synchronous). Each replaces one CPU reference function of the path.
+ * ---------------------------------------------------------------------------------------------------------- */
+
+/* rl_quant_dequant_row (native/redlite_native_quant_cpu.c:155-196) for nrows rows at once: out[nrows][ncols]. */
+int redcuda_quant_dequant_rows(uint32_t ggml_type, const uint8_t *rows, uint32_t nrows, uint32_t ncols, float *out);
+
+/* rl_quant_row_dot over every row and ntok input vectors (native/redlite_native_quant_cpu.c:198-280; the row-parallel
+ * matvec of native/redlite_native_engine_cpu.c:54-92): out[t][r] = dot(W[r], x[t]). x[ntok][ncols], out[ntok][nrows]. */
+int redcuda_quant_matvec(uint32_t ggml_type, const uint8_t *w, uint32_t nrows, uint32_t ncols,
+                         const float *x, uint32_t ntok, float *out);
+
+/* rl_native_router_select_softmax_topk (native/redlite_native_router_exec.c:102-184) for ntok rows of logits:
+ * ids[ntok][top_k], weights[ntok][top_k] (renormalised over the selection), probs[ntok][n_expert] (may be NULL).
+ * Ties go to the lower expert id. */
+int redcuda_router_select_softmax_topk(const float *logits, uint32_t ntok, uint32_t n_expert, uint32_t top_k,
+                                       uint32_t *ids, float *weights, float *probs);
+
+/* Gated DeltaNet decode step between the projections, for `batch` independent sequences
+ * (deltanet_branch, native/redlite_native_engine_cpu.c:148-230; stage tools native/redmetal_deltanet_state.m,
+ * native/redmetal_deltanet_tail.m). Per sequence: qkv[channels], z[d_inner], ba[2*dt_rank] in,
+ * conv_state[channels][d_conv-1] and rec_state[dt_rank][d_state][d_state] updated in place, out[d_inner]. */
+typedef struct {
+    uint32_t d_conv, d_state, n_group, dt_rank, d_inner, channels;
+    float rms_eps;
+    const float *conv_kernel;   /* [channels][d_conv] */
+    const float *dt_bias;       /* [dt_rank] */
+    const float *ssm_a;         /* [dt_rank] */
+    const float *ssm_norm;      /* [d_state] */
+} redcuda_deltanet_params;
+int redcuda_deltanet_step(const redcuda_deltanet_params *p, uint32_t batch, const float *qkv, const float *z, const float *ba,
+                          float *conv_state, float *rec_state, float *out);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Resident MoE layer: router + routed experts + sigmoid-gated shared expert of one layer, every expert in HBM.
+ * Replaces ffn() of native/redlite_native_engine_cpu.c:329-386 and, on the GPU side, the expert pool with its LRU
+ * (native/redmetal_topk.h, native/redlite_native_cache.h): with every expert resident, residency bookkeeping is a
+ * no-op and the expert id is the slot id.
+ * ---------------------------------------------------------------------------------------------------------- */
+typedef struct redcuda_moe redcuda_moe;
+
+typedef struct {
+    uint32_t hidden, n_expert, top_k, ffn, ffn_sh;
+    uint32_t type_gu, type_down, type_sh;  /* routed gate/up, routed down, shared-expert matrices */
+    uint32_t expert_begin, expert_count;   /* experts held by this object: [expert_begin, expert_begin + expert_count);
+                                              (0, n_expert) on one GPU, one shard per rank under expert parallelism */
+    uint32_t max_tokens;                   /* largest ntok of a forward call (workspace is sized once, at create) */
+    uint32_t weights_on_device;            /* 0: the pointers below are host memory; 1: CUDA device memory */
+    const float *router;                   /* [n_expert][hidden] F32 */
+    const uint8_t *gate_exps, *up_exps;    /* expert_count matrices [ffn][hidden], back to back (GGUF expert-major) */
+    const uint8_t *down_exps;              /* expert_count matrices [hidden][ffn] */
+    const float *sh_gate_inp;              /* [hidden] F32 */
+    const uint8_t *sh_gate, *sh_up;        /* [ffn_sh][hidden] */
+    const uint8_t *sh_down;                /* [hidden][ffn_sh] */
+} redcuda_moe_desc;
+
+redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc);
+void redcuda_moe_destroy(redcuda_moe *m);
+uint64_t redcuda_moe_resident_bytes(const redcuda_moe *m);
+
+/* One MoE FFN pass over ntok tokens (host pointers, synchronous): out[t] = routed(x[t]) + shared(x[t]) * sigmoid(g.x[t]).
+ * logits_in, when not NULL, replaces the router matvec ([ntok][n_expert], the "drawn logits" of the ragged-batch
+ * workload). ids_out [ntok][top_k], weights_out [ntok][top_k], logits_out [ntok][n_expert] may be NULL. */
+int redcuda_moe_forward(redcuda_moe *m, uint32_t ntok, const float *x, const float *logits_in, float *out,
+                        uint32_t *ids_out, float *weights_out, float *logits_out);
+
+/* Same pass with device pointers on `stream` (cudaStream_t). Never allocates or synchronises, so it can be captured
+ * in a CUDA graph. resid_dev, when not NULL, is added to the output (x_out = resid + ffn). */
+int redcuda_moe_forward_device(redcuda_moe *m, uint32_t ntok, const float *x_dev, const float *logits_in_dev,
+                               const float *resid_dev, float *out_dev, void *stream);
+
+/* Expert-parallel pieces (device pointers, `stream`), the two halves either side of the all-to-all exchange:
+ *   route:   ids_dev[ntok][top_k], weights_dev[ntok][top_k] from x_dev (or logits_in_dev)
+ *   experts: routed experts of THIS shard over (token, expert) pairs already grouped by the caller:
+ *            pair_x_dev[npairs][hidden] activations, pair_expert_dev[npairs] global expert ids (all within the
+ *            shard), result pair_out_dev[npairs][hidden] (unweighted expert outputs)
+ *   shared:  out_dev[t] = shared(x[t]) * sigmoid(g.x[t]) */
+int redcuda_moe_route_device(redcuda_moe *m, uint32_t ntok, const float *x_dev, const float *logits_in_dev,
+                             uint32_t *ids_dev, float *weights_dev, void *stream);
+int redcuda_moe_experts_device(redcuda_moe *m, uint32_t npairs, const float *pair_x_dev, const uint32_t *pair_expert_dev,
+                               float *pair_out_dev, void *stream);
+int redcuda_moe_shared_device(redcuda_moe *m, uint32_t ntok, const float *x_dev, float *out_dev, void *stream);
+
+/* Per-kernel timing for benchmarks: while enabled, every kernel launch is bracketed by CUDA events on its stream
+ * (do not enable while capturing a CUDA graph). report() waits for the device and writes one line per kernel name,
+ * "name launches total_ms\n", into buf; returns the number of lines. enable(0/1) clears the records. */
+int redcuda_profile_enable(int on);
+int redcuda_profile_report(char *buf, size_t cap);
+
+/* number of kernel launches the library has issued on this thread's device since load (for bench accounting) */
+uint64_t redcuda_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -356,7 +356,12 @@ int ro_routed_experts(uint32_t type_gu, uint32_t type_down, const uint8_t *gate_
     return ok;
 }
 
-int ro_moe_ffn(const ro_moe_layer *L, const float *x, float *out, uint32_t *ids_out, float *weights_out, float *logits_out, int threads) {   /* engine_cpu.c:329-386 */
+int ro_moe_ffn(const ro_moe_layer *L, const float *x, float *out, uint32_t *ids_out, float *weights_out, float *logits_out, int threads) {
+    return ro_moe_ffn2(L, x, NULL, out, ids_out, weights_out, logits_out, threads);
+}
+
+int ro_moe_ffn2(const ro_moe_layer *L, const float *x, const float *logits_in, float *out, uint32_t *ids_out, float *weights_out,
+                float *logits_out, int threads) {   /* engine_cpu.c:329-386 */
     const uint32_t hidden = L->hidden, ne = L->n_expert, k = L->top_k;
     if (k > RO_MAX_TOPK) return 0;
     float *logits = (float *)malloc(sizeof(float) * ne), *probs = (float *)malloc(sizeof(float) * ne);
@@ -365,7 +370,9 @@ int ro_moe_ffn(const ro_moe_layer *L, const float *x, float *out, uint32_t *ids_
     double *routed = (double *)malloc(sizeof(double) * hidden);
     uint32_t ids[RO_MAX_TOPK]; float w[RO_MAX_TOPK];
     int ok = logits && probs && shg && shu && act && sho && routed;
-    ok = ok && ro_router_logits(L->router, x, ne, hidden, logits) && ro_router_select(logits, ne, k, ids, w, probs);
+    if (ok && logits_in) memcpy(logits, logits_in, sizeof(float) * ne);
+    else ok = ok && ro_router_logits(L->router, x, ne, hidden, logits);
+    ok = ok && ro_router_select(logits, ne, k, ids, w, probs);
     ok = ok && ro_routed_experts(L->type_gu, L->type_down, L->gate_all, L->up_all, L->down_all, ids, w, k, hidden, L->ffn, x, routed, threads);
     ok = ok && ro_matvec(L->type_sh, L->sh_gate, L->ffn_sh, hidden, x, shg, threads) && ro_matvec(L->type_sh, L->sh_up, L->ffn_sh, hidden, x, shu, threads);
     if (ok) {

@@ -58,6 +58,9 @@ typedef struct {
  * ids_out/weights_out (top_k entries) and logits_out (n_expert) may be NULL. */
 int ro_moe_ffn(const ro_moe_layer *L, const float *x, float *out, uint32_t *ids_out, float *weights_out,
                float *logits_out, int threads);
+/* same, with the router matvec replaced by given logits when logits_in is not NULL (drawn-logits workloads) */
+int ro_moe_ffn2(const ro_moe_layer *L, const float *x, const float *logits_in, float *out, uint32_t *ids_out, float *weights_out,
+                float *logits_out, int threads);
 
 typedef struct {
     uint32_t d_conv, d_state, n_group, dt_rank, d_inner, channels;

@@ -195,17 +195,19 @@ def moe_layer_c(layer) -> tuple[MoeLayerC, list]:
     return L, keep
 
 
-def moe_ffn(layer, x: np.ndarray, threads: int = 1):
-    """-> (out f32[hidden], ids u32[k], weights f32[k], logits f32[n_expert])"""
+def moe_ffn(layer, x: np.ndarray, threads: int = 1, logits_in: np.ndarray | None = None, view=None):
+    """-> (out f32[hidden], ids u32[k], weights f32[k], logits f32[n_expert]); view = a cached moe_layer_c(layer)"""
     lib = own()
-    L, keep = moe_layer_c(layer)
+    L, keep = view if view is not None else moe_layer_c(layer)
     d = layer.dims
     x = np.ascontiguousarray(x, np.float32)
     out = np.empty(d.hidden, np.float32)
     ids = np.empty(d.top_k, np.uint32)
     w = np.empty(d.top_k, np.float32)
     logits = np.empty(d.n_expert, np.float32)
-    ok = lib.ro_moe_ffn(C.byref(L), ptr(x, f32p), ptr(out, f32p), ptr(ids, u32p), ptr(w, f32p), ptr(logits, f32p), C.c_int(threads))
+    li = None if logits_in is None else np.ascontiguousarray(logits_in, np.float32)
+    ok = lib.ro_moe_ffn2(C.byref(L), ptr(x, f32p), None if li is None else ptr(li, f32p), ptr(out, f32p), ptr(ids, u32p), ptr(w, f32p),
+                         ptr(logits, f32p), C.c_int(threads))
     assert ok == 1
     return out, ids, w, logits
 
