@@ -2,6 +2,7 @@
 #include "redcuda_common.cuh"
 #include "redcuda_dot.cuh"
 #include "redcuda_kernels.cuh"
+#include "redcuda_moe_mma.cuh"
 #include "../../include/redcuda.h"
 
 #include <math.h>
@@ -367,6 +368,7 @@ int redcuda_set_codebooks(const uint8_t *iq2xxs_grid, uint32_t iq2xxs_bytes, con
     void *p2 = nullptr, *p3 = nullptr;
     RC_CUDA(cudaGetSymbolAddress(&p2, d_iq2_grid));
     RC_CUDA(cudaGetSymbolAddress(&p3, d_iq3s_grid));
+    if (!mma_set_luts(iq2xxs_grid)) return 0;
     std::lock_guard<std::mutex> lk(g_books_mu);
     g_iq2_ptr[dev] = (const uint8_t *)p2;
     g_iq3s_ptr[dev] = (const uint32_t *)p3;

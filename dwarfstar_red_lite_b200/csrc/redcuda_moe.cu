@@ -14,9 +14,11 @@
 #include "redcuda_common.cuh"
 #include "redcuda_dot.cuh"
 #include "redcuda_kernels.cuh"
+#include "redcuda_moe_mma.cuh"
 #include "../../include/redcuda.h"
 
 #include <new>
+#include <stdlib.h>
 
 namespace rc {
 
@@ -186,7 +188,10 @@ struct redcuda_moe {
     // workspace
     float *x = nullptr, *logits = nullptr, *wk = nullptr, *scalar = nullptr, *sh_act = nullptr, *sh_out = nullptr, *act = nullptr, *tmp = nullptr, *out = nullptr;
     uint32_t *ids = nullptr, *sorted = nullptr, *uexp = nullptr, *ustart = nullptr, *n_unique = nullptr, *bad = nullptr;
+    int8_t *xq_x = nullptr, *xq_act = nullptr;      // activation digits for the tensor-core path
+    float *sx_x = nullptr, *sx_act = nullptr;
     uint32_t max_pairs = 0;
+    bool use_mma = false;                           // IQ2_XXS experts on the integer tensor-core path
     cudaStream_t stream = nullptr;
 };
 
@@ -233,6 +238,18 @@ static int moe_launch_experts(redcuda_moe *m, bool gateup, uint32_t npairs, bool
     A.sorted = m->sorted; A.uexp = m->uexp; A.ustart = m->ustart; A.n_unique = m->n_unique;
     A.x = x; A.x_stride = x_stride; A.x_div = x_div; A.out = out; A.out_stride = out_stride; A.pair_silu = gateup ? 1u : 0u;
     A.iq2 = books_iq2(); A.iq3s = books_iq3s();
+    if (m->use_mma && A.type == RC_IQ2_XXS && A.ncols % 512u == 0 && A.nrows % 16u == 0) {
+        const uint32_t xrows = (npairs + x_div - 1u) / x_div;
+        int8_t *xq = gateup ? m->xq_x : m->xq_act;
+        float *sx = gateup ? m->sx_x : m->sx_act;
+        if (!launch_quant_act(x, x_stride, xrows, A.ncols, xq, sx, s)) return 0;
+        MmaArgs M{};
+        M.w0 = A.w0; M.w1 = A.w1; M.mat_bytes = A.mat_bytes; M.nb = A.nb; M.nrows = A.nrows; M.ncols = A.ncols; M.expert_begin = A.expert_begin;
+        M.sorted = A.sorted; M.uexp = A.uexp; M.ustart = A.ustart; M.n_unique = A.n_unique;
+        M.xq = xq; M.sx = sx; M.x_div = x_div; M.out = out; M.out_stride = out_stride;
+        const uint32_t grp = npairs < m->d.expert_count ? npairs : m->d.expert_count;
+        return launch_moe_mma(M, grp, single_token, s);
+    }
     uint32_t lpr = 32u;
     while (lpr > (A.ncols >> 6)) lpr >>= 1;
     const uint32_t rows_per_pass = 8u * (32u / lpr);
@@ -368,13 +385,19 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
     const size_t o_x = take(T * d.hidden * 4u), o_log = take(T * d.n_expert * 4u), o_wk = take(P * 4u), o_sca = take(T * 4u),
                  o_sha = take(T * d.ffn_sh * 4u), o_sho = take(T * d.hidden * 4u), o_act = take(P * d.ffn * 4u), o_tmp = take(P * d.hidden * 4u),
                  o_out = take(T * d.hidden * 4u), o_ids = take(P * 4u), o_sorted = take(P * 4u), o_uexp = take((size_t)(d.expert_count + 1u) * 4u),
-                 o_ustart = take((size_t)(d.expert_count + 2u) * 4u), o_nu = take(16), o_bad = take(16);
+                 o_ustart = take((size_t)(d.expert_count + 2u) * 4u), o_nu = take(16), o_bad = take(16),
+                 o_xqx = take(P * 3u * d.hidden), o_sxx = take(P * 4u), o_xqa = take(P * 3u * d.ffn), o_sxa = take(P * 4u);
     if (!m->ws.alloc(w)) return bail();
     uint8_t *B = m->ws.as<uint8_t>();
     m->x = (float *)(B + o_x); m->logits = (float *)(B + o_log); m->wk = (float *)(B + o_wk); m->scalar = (float *)(B + o_sca);
     m->sh_act = (float *)(B + o_sha); m->sh_out = (float *)(B + o_sho); m->act = (float *)(B + o_act); m->tmp = (float *)(B + o_tmp);
     m->out = (float *)(B + o_out); m->ids = (uint32_t *)(B + o_ids); m->sorted = (uint32_t *)(B + o_sorted); m->uexp = (uint32_t *)(B + o_uexp);
     m->ustart = (uint32_t *)(B + o_ustart); m->n_unique = (uint32_t *)(B + o_nu); m->bad = (uint32_t *)(B + o_bad);
+    m->xq_x = (int8_t *)(B + o_xqx); m->sx_x = (float *)(B + o_sxx); m->xq_act = (int8_t *)(B + o_xqa); m->sx_act = (float *)(B + o_sxa);
+    {   // RC_MOE_PATH=cuda keeps the IQ2_XXS experts on the CUDA-core kernels (A/B switch for profiling)
+        const char *pth = getenv("RC_MOE_PATH");
+        m->use_mma = !(pth && pth[0] == 'c');
+    }
     if (cudaMemsetAsync(B, 0, w, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) {
         set_error("moe create: weight upload failed: %s", cudaGetErrorString(cudaGetLastError()));
         return bail();

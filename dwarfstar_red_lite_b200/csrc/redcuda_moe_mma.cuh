@@ -1,0 +1,29 @@
+// Launch interface of the integer tensor-core path for IQ2_XXS expert matrices (redcuda_moe_mma.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rc {
+
+struct MmaArgs {
+    const uint8_t *w0, *w1;        // planar IQ2_XXS expert matrices of the shard, back to back (gate/up, or down/nullptr)
+    uint64_t mat_bytes, nb;        // bytes and 256-blocks of one expert matrix
+    uint32_t nrows, ncols;         // per expert matrix
+    uint32_t expert_begin;
+    const uint32_t *sorted, *uexp, *ustart, *n_unique;   // pairs grouped by expert (k_group_pairs)
+    const int8_t *xq;              // activation digits [row][3][ncols]; row of pair p = p / x_div
+    const float *sx;               // activation scale per row
+    uint32_t x_div;
+    float *out; uint32_t out_stride;                     // result row of pair p = out + p * out_stride
+    const uint2 *lut_grid, *lut_sign;                    // filled by launch_moe_mma
+    uint32_t S, tiles_per_warp;                          // filled by launch_moe_mma
+};
+
+// Builds the magnitude and sign tables of the tensor-core path from the IQ2_XXS codebook (current device).
+int mma_set_luts(const uint8_t *iq2_grid_host);
+// x[rows][x_stride] (first ncols of each row) -> digits xq[rows][3][ncols] and scales sx[rows]
+int launch_quant_act(const float *x, uint32_t x_stride, uint32_t rows, uint32_t ncols, int8_t *xq, float *sx, cudaStream_t s);
+// groups = upper bound of experts that received a pair (grid.y); few_tokens: every expert has at most 2 pairs
+int launch_moe_mma(MmaArgs &A, uint32_t groups, bool few_tokens, cudaStream_t s);
+
+}  // namespace rc
