@@ -264,6 +264,7 @@ def main():
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                 "frac_of_nominal_8000": achieved / 8000.0, "traffic": None, "bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
                 "kernel_time_shares": shares,
+                "kernel_us_per_layer": {k: round(1e3 * v[1] / (prof_steps * L), 2) for k, v in prof.items()},
                 "whole_layer": {"bytes": layer_bytes, "GBps": layer_bytes * L / (ms_per_step * 1e-3) / 1e9,
                                 "frac": layer_bytes * L / (ms_per_step * 1e-3) / 1e9 / peak}}
 

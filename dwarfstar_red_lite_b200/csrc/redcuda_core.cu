@@ -292,13 +292,91 @@ __global__ void __launch_bounds__(256) k_route(const float *__restrict__ logits,
     }
 }
 
+// Warp-per-token variant for n_expert <= 1024: the probabilities of a token live in the warp's registers (32 per lane
+// at most), every selection round is a register scan plus a 5-step shuffle argmax — no block barriers, so the k rounds
+// cost a few hundred dependent instructions instead of 2k barriers. Same arithmetic and tie rule as k_route.
+__global__ void __launch_bounds__(256) k_route_warp(const float *__restrict__ logits, uint32_t ntok, uint32_t n_expert, uint32_t top_k,
+                                                    uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ probs_out) {
+    const uint32_t lane = threadIdx.x & 31u, tok = blockIdx.x * 8u + (threadIdx.x >> 5);
+    if (tok >= ntok) return;
+    const float *l = logits + (size_t)tok * n_expert;
+    float p[32];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) { const uint32_t i = lane + 32u * j; p[j] = i < n_expert ? l[i] : -INFINITY; mx = fmaxf(mx, p[j]); }
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    double den = 0.0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) { const uint32_t i = lane + 32u * j; const float e = i < n_expert ? expf(p[j] - mx) : 0.f; p[j] = e; den += (double)e; }
+    for (int o = 16; o; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+    const float inv = (float)(1.0 / den);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const uint32_t i = lane + 32u * j;
+        p[j] = i < n_expert ? p[j] * inv : -2.0f;
+        if (probs_out && i < n_expert) probs_out[(size_t)tok * n_expert + i] = p[j];
+    }
+    double sel = 0.0;
+    float myw = 0.f;                   // lane k keeps the weight of selection k (top_k <= 64: two per lane)
+    float myw2 = 0.f;
+    for (uint32_t k = 0; k < top_k; ++k) {
+        float bv = -3.0f; uint32_t bi = 0xffffffffu;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { const uint32_t i = lane + 32u * j; if (p[j] > bv) { bv = p[j]; bi = i; } }   // ascending i: first maximum = lowest id
+        for (int o = 16; o; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (lane + 32u * j == bi) p[j] = -1.0f;
+        if (lane == 0) ids[(size_t)tok * top_k + k] = bi;
+        if (lane == (k & 31u)) { if (k < 32u) myw = bv; else myw2 = bv; }
+        sel += (double)bv;
+    }
+    const float invs = (float)(1.0 / sel);
+    if (lane < top_k) weights[(size_t)tok * top_k + lane] = myw * invs;
+    if (lane + 32u < top_k) weights[(size_t)tok * top_k + lane + 32u] = myw2 * invs;
+}
+
 int launch_route(const float *logits_dev, uint32_t ntok, uint32_t n_expert, uint32_t top_k, uint32_t *ids_dev, float *weights_dev,
                  float *probs_dev, cudaStream_t stream) {
     RC_REQUIRE(top_k >= 1 && top_k <= REDCUDA_MAX_TOPK && top_k <= n_expert, "router: top_k %u out of range", top_k);
     RC_REQUIRE(n_expert <= 8192u, "router: too many experts (%u)", n_expert);
     if (!ntok) return 1;
     prof_begin("route", stream);
-    k_route<<<ntok, 256, n_expert * sizeof(float), stream>>>(logits_dev, n_expert, top_k, ids_dev, weights_dev, probs_dev);
+    if (n_expert <= 1024u) k_route_warp<<<(ntok + 7u) / 8u, 256, 0, stream>>>(logits_dev, ntok, n_expert, top_k, ids_dev, weights_dev, probs_dev);
+    else k_route<<<ntok, 256, n_expert * sizeof(float), stream>>>(logits_dev, n_expert, top_k, ids_dev, weights_dev, probs_dev);
+    prof_end(stream);
+    RC_LAUNCHED();
+    return 1;
+}
+
+// out[t] = sigmoid(w . x[t]) for one F32 row w (the shared-expert gate), fp64 accumulation; one block per token.
+__global__ void __launch_bounds__(256) k_vec_sigmoid(const float *__restrict__ w, const float *__restrict__ x, uint32_t x_stride, uint32_t ncols,
+                                                     float *__restrict__ out) {
+    __shared__ double red[8];
+    const uint32_t t = blockIdx.x, tid = threadIdx.x;
+    const float *xr = x + (size_t)t * x_stride;
+    double acc = 0.0;
+    for (uint32_t k = tid * 4u; k < ncols; k += 1024u) {
+        const float4 a = *reinterpret_cast<const float4 *>(w + k), b = *reinterpret_cast<const float4 *>(xr + k);
+        acc += (double)a.x * b.x + (double)a.y * b.y + (double)a.z * b.z + (double)a.w * b.w;
+    }
+    for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((tid & 31u) == 0) red[tid >> 5] = acc;
+    __syncthreads();
+    if (tid == 0) {
+        double tot = 0.0;
+        for (int i = 0; i < 8; ++i) tot += red[i];
+        out[t] = (float)(1.0 / (1.0 + exp(-tot)));
+    }
+}
+
+int launch_vec_sigmoid(const float *w, const float *x, uint32_t x_stride, uint32_t ncols, uint32_t ntok, float *out, cudaStream_t stream) {
+    RC_REQUIRE(ncols % 4u == 0, "vec_sigmoid: %u columns is not a multiple of 4", ncols);
+    if (!ntok) return 1;
+    prof_begin("moe_shared_gate", stream);
+    k_vec_sigmoid<<<ntok, 256, 0, stream>>>(w, x, x_stride, ncols, out);
     prof_end(stream);
     RC_LAUNCHED();
     return 1;

@@ -15,8 +15,6 @@
 
 namespace rc {
 
-struct DnDims { uint32_t d_conv, S, groups, rank, d_inner, channels; float eps; };
-
 __device__ __forceinline__ double sigmoid_stable(double x) { if (x >= 0.0) { const double z = exp(-x); return 1.0 / (1.0 + z); } const double z = exp(x); return z / (1.0 + z); }
 __device__ __forceinline__ double softplus_stable(double x) { if (x > 20.0) return x; if (x < -20.0) return exp(x); return log1p(exp(x)); }
 

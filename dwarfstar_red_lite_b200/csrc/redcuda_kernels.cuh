@@ -34,4 +34,13 @@ int launch_gemv(GemvArgs &A, cudaStream_t stream);
 int launch_route(const float *logits_dev, uint32_t ntok, uint32_t n_expert, uint32_t top_k, uint32_t *ids_dev, float *weights_dev,
                  float *probs_dev, cudaStream_t stream);
 
+// Gated DeltaNet step between the projections (redcuda_deltanet.cu). All pointers are device memory; qk, v, beta,
+// gate, core are scratch of batch * {2*groups*S, d_inner, rank, rank, d_inner} floats.
+struct DnDims { uint32_t d_conv, S, groups, rank, d_inner, channels; float eps; };
+int launch_deltanet(const DnDims &D, uint32_t batch, const float *conv_kernel, const float *dt_bias, const float *ssm_a, const float *norm_w,
+                    const float *qkv, const float *z, const float *ba, float *conv_state, float *rec_state,
+                    float *qk, float *v, float *beta, float *gate, float *core, float *out, cudaStream_t s);
+
+int launch_vec_sigmoid(const float *w, const float *x, uint32_t x_stride, uint32_t ncols, uint32_t ntok, float *out, cudaStream_t stream);
+
 }  // namespace rc

@@ -97,11 +97,14 @@ __global__ void __launch_bounds__(256) k_moe_experts(const __grid_constant__ Moe
 }
 
 // Group pairs by expert: sorted[] = pair ids, expert by expert (ascending expert id); uexp / ustart list the experts
-// that received at least one pair; n_unique their count. One block of 1024 threads, expert_count <= 1024.
+// that received at least one pair; n_unique their count. Every expert's pairs are also cut into work items of at most
+// item_tok pairs (item_u = slot in uexp, item_p0 = first position in sorted[]), so that kernels which take one item
+// per block see equal-sized work whatever the routing skew. One block of 1024 threads, expert_count <= 1024.
 __global__ void __launch_bounds__(1024) k_group_pairs(const uint32_t *__restrict__ pair_expert, uint32_t npairs, uint32_t expert_begin,
-                                                      uint32_t expert_count, uint32_t *__restrict__ sorted, uint32_t *__restrict__ uexp,
-                                                      uint32_t *__restrict__ ustart, uint32_t *__restrict__ n_unique, uint32_t *__restrict__ bad) {
-    __shared__ uint32_t cnt[1024], start[1024], wsum[32], wsum2[32];
+                                                      uint32_t expert_count, uint32_t item_tok, uint32_t *__restrict__ sorted, uint32_t *__restrict__ uexp,
+                                                      uint32_t *__restrict__ ustart, uint32_t *__restrict__ n_unique, uint32_t *__restrict__ item_u,
+                                                      uint32_t *__restrict__ item_p0, uint32_t *__restrict__ n_items, uint32_t *__restrict__ bad) {
+    __shared__ uint32_t cnt[1024], start[1024], wsum[32], wsum2[32], wsum3[32];
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     cnt[tid] = 0;
     __syncthreads();
@@ -110,29 +113,30 @@ __global__ void __launch_bounds__(1024) k_group_pairs(const uint32_t *__restrict
         if (e < expert_count) atomicAdd(&cnt[e], 1u); else atomicAdd(bad, 1u);   // a pair outside the shard is reported, not run
     }
     __syncthreads();
-    // exclusive scans over experts of (count) and (count > 0)
-    const uint32_t c = tid < expert_count ? cnt[tid] : 0u, f = c ? 1u : 0u;
-    uint32_t sc = c, sf = f;
+    // exclusive scans over experts of (count), (count > 0) and (items)
+    const uint32_t c = tid < expert_count ? cnt[tid] : 0u, f = c ? 1u : 0u, it = (c + item_tok - 1u) / item_tok;
+    uint32_t sc = c, sf = f, si = it;
     for (int o = 1; o < 32; o <<= 1) {
-        const uint32_t a = __shfl_up_sync(0xffffffffu, sc, o), b = __shfl_up_sync(0xffffffffu, sf, o);
-        if ((int)lane >= o) { sc += a; sf += b; }
+        const uint32_t a = __shfl_up_sync(0xffffffffu, sc, o), b = __shfl_up_sync(0xffffffffu, sf, o), d = __shfl_up_sync(0xffffffffu, si, o);
+        if ((int)lane >= o) { sc += a; sf += b; si += d; }
     }
-    if (lane == 31u) { wsum[warp] = sc; wsum2[warp] = sf; }
+    if (lane == 31u) { wsum[warp] = sc; wsum2[warp] = sf; wsum3[warp] = si; }
     __syncthreads();
     if (warp == 0) {
-        uint32_t a = wsum[lane], b = wsum2[lane];
+        uint32_t a = wsum[lane], b = wsum2[lane], d = wsum3[lane];
         for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t ua = __shfl_up_sync(0xffffffffu, a, o), ub = __shfl_up_sync(0xffffffffu, b, o);
-            if ((int)lane >= o) { a += ua; b += ub; }
+            const uint32_t ua = __shfl_up_sync(0xffffffffu, a, o), ub = __shfl_up_sync(0xffffffffu, b, o), ud = __shfl_up_sync(0xffffffffu, d, o);
+            if ((int)lane >= o) { a += ua; b += ub; d += ud; }
         }
-        wsum[lane] = a; wsum2[lane] = b;
+        wsum[lane] = a; wsum2[lane] = b; wsum3[lane] = d;
     }
     __syncthreads();
-    const uint32_t basec = warp ? wsum[warp - 1u] : 0u, basef = warp ? wsum2[warp - 1u] : 0u;
-    const uint32_t exc = basec + sc - c, exf = basef + sf - f;
+    const uint32_t basec = warp ? wsum[warp - 1u] : 0u, basef = warp ? wsum2[warp - 1u] : 0u, basei = warp ? wsum3[warp - 1u] : 0u;
+    const uint32_t exc = basec + sc - c, exf = basef + sf - f, exi = basei + si - it;
     start[tid] = exc;
     if (f) { uexp[exf] = expert_begin + tid; ustart[exf] = exc; }
-    if (tid == 1023u) { const uint32_t nu = exf + f; *n_unique = nu; ustart[nu] = exc + c; }
+    for (uint32_t j = 0; j < it; ++j) { item_u[exi + j] = exf; item_p0[exi + j] = exc + j * item_tok; }
+    if (tid == 1023u) { const uint32_t nu = exf + f; *n_unique = nu; ustart[nu] = exc + c; *n_items = exi + it; }
     cnt[tid] = 0;
     __syncthreads();
     for (uint32_t p = tid; p < npairs; p += 1024u) {
@@ -141,12 +145,13 @@ __global__ void __launch_bounds__(1024) k_group_pairs(const uint32_t *__restrict
     }
 }
 
-// Single-token case: the k selected experts are distinct, so every pair is its own group.
+// Single-token case: the k selected experts are distinct, so every pair is its own group and its own work item.
 __global__ void k_group_trivial(const uint32_t *__restrict__ pair_expert, uint32_t npairs, uint32_t *__restrict__ sorted,
-                                uint32_t *__restrict__ uexp, uint32_t *__restrict__ ustart, uint32_t *__restrict__ n_unique) {
+                                uint32_t *__restrict__ uexp, uint32_t *__restrict__ ustart, uint32_t *__restrict__ n_unique,
+                                uint32_t *__restrict__ item_u, uint32_t *__restrict__ item_p0, uint32_t *__restrict__ n_items) {
     const uint32_t i = threadIdx.x;
-    if (i < npairs) { sorted[i] = i; uexp[i] = pair_expert[i]; ustart[i] = i; }
-    if (i == 0) { ustart[npairs] = npairs; *n_unique = npairs; }
+    if (i < npairs) { sorted[i] = i; uexp[i] = pair_expert[i]; ustart[i] = i; item_u[i] = i; item_p0[i] = i; }
+    if (i == 0) { ustart[npairs] = npairs; *n_unique = npairs; *n_items = npairs; }
 }
 
 // out[t] = resid[t] + (sum_k w[t][k] * pair_out[t*k + kk] + shared[t] * scalar[t]); k may be 0 (shared part only).
@@ -188,16 +193,27 @@ struct redcuda_moe {
     // workspace
     float *x = nullptr, *logits = nullptr, *wk = nullptr, *scalar = nullptr, *sh_act = nullptr, *sh_out = nullptr, *act = nullptr, *tmp = nullptr, *out = nullptr;
     uint32_t *ids = nullptr, *sorted = nullptr, *uexp = nullptr, *ustart = nullptr, *n_unique = nullptr, *bad = nullptr;
-    int8_t *xq_x = nullptr, *xq_act = nullptr;      // activation digits for the tensor-core path
-    float *sx_x = nullptr, *sx_act = nullptr;
+    uint32_t *item_u = nullptr, *item_p0 = nullptr, *n_items = nullptr;
+    int8_t *xq_x = nullptr, *xq_act = nullptr, *xq_sh = nullptr;      // activation digits for the tensor-core paths
+    float *sx_x = nullptr, *sx_act = nullptr, *sx_sh = nullptr;
     uint32_t max_pairs = 0;
-    bool use_mma = false;                           // IQ2_XXS experts on the integer tensor-core path
+    bool use_mma = false;      // IQ2_XXS experts (and the Q6_K shared expert of a batch) on the integer tensor-core path
     cudaStream_t stream = nullptr;
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-static int moe_gemv_pre(redcuda_moe *m, uint32_t ntok, const float *x, bool with_router, bool with_shared, cudaStream_t s) {
+// tensor-core path of the routed experts: IQ2_XXS gate/up/down with tile-able shapes
+static bool moe_experts_mma(const redcuda_moe *m) {
+    return m->use_mma && m->d.type_gu == RC_IQ2_XXS && m->d.type_down == RC_IQ2_XXS && m->d.hidden % 512u == 0 && m->d.ffn % 512u == 0;
+}
+// tensor-core path of the shared expert: Q6_K and at least 3 tokens (below that the CUDA-core GEMV wins)
+static bool moe_shared_mma(const redcuda_moe *m, uint32_t ntok) {
+    return m->use_mma && m->d.type_sh == RC_Q6_K && ntok >= 3u && m->d.ffn_sh % 16u == 0 && m->d.hidden % 16u == 0;
+}
+
+// x_quantised: xq_x / sx_x already hold the digits of x
+static int moe_gemv_pre(redcuda_moe *m, uint32_t ntok, const float *x, bool with_router, bool with_shared, bool x_quantised, cudaStream_t s) {
     GemvArgs A{};
     A.ntok = ntok; A.x = x; A.x_stride = m->d.hidden;
     uint32_t j = 0;
@@ -208,8 +224,13 @@ static int moe_gemv_pre(redcuda_moe *m, uint32_t ntok, const float *x, bool with
     };
     if (with_router) add(m->router, nullptr, m->logits, m->d.n_expert, GEMV_STORE);
     if (with_shared) {
-        add(m->sh_gate, &m->sh_up, m->sh_act, m->d.ffn_sh, GEMV_PAIR_SILU);
-        add(m->sh_gate_inp, nullptr, m->scalar, 1u, GEMV_SIGMOID);
+        if (moe_shared_mma(m, ntok) && x_quantised) {
+            if (!launch_q6k_mma(m->sh_gate.base, m->sh_up.base, m->sh_gate.nb, m->d.ffn_sh, m->d.hidden, ntok, m->xq_x, m->sx_x, m->sh_act, m->d.ffn_sh,
+                                "moe_shared_gateup_mma", s)) return 0;
+        } else add(m->sh_gate, &m->sh_up, m->sh_act, m->d.ffn_sh, GEMV_PAIR_SILU);
+        // the scalar gate is a single row: as a GEMV job it would be one block sweeping every token
+        if (ntok >= 3u) { if (!launch_vec_sigmoid((const float *)m->sh_gate_inp.base, x, m->d.hidden, m->d.hidden, ntok, m->scalar, s)) return 0; }
+        else add(m->sh_gate_inp, nullptr, m->scalar, 1u, GEMV_SIGMOID);
     }
     if (!j) return 1;
     A.njobs = j;
@@ -218,6 +239,11 @@ static int moe_gemv_pre(redcuda_moe *m, uint32_t ntok, const float *x, bool with
 }
 
 static int moe_shared_down(redcuda_moe *m, uint32_t ntok, cudaStream_t s) {
+    if (moe_shared_mma(m, ntok)) {
+        if (!launch_quant_act(m->sh_act, m->d.ffn_sh, ntok, m->d.ffn_sh, m->xq_sh, m->sx_sh, s)) return 0;
+        return launch_q6k_mma(m->sh_down.base, nullptr, m->sh_down.nb, m->d.hidden, m->d.ffn_sh, ntok, m->xq_sh, m->sx_sh, m->sh_out, m->d.hidden,
+                              "moe_shared_down_mma", s);
+    }
     GemvArgs A{};
     A.ntok = ntok; A.x = m->sh_act; A.x_stride = m->d.ffn_sh; A.njobs = 1;
     GemvJob &J = A.job[0];
@@ -227,29 +253,34 @@ static int moe_shared_down(redcuda_moe *m, uint32_t ntok, cudaStream_t s) {
     return launch_gemv(A, s);
 }
 
+// gate/up (x = token or pair activations) or down (x = act) of the grouped pairs. x_quantised: digits already in place.
 static int moe_launch_experts(redcuda_moe *m, bool gateup, uint32_t npairs, bool single_token, const float *x, uint32_t x_stride, uint32_t x_div,
-                              float *out, uint32_t out_stride, cudaStream_t s) {
+                              bool x_quantised, float *out, uint32_t out_stride, cudaStream_t s) {
+    const uint32_t nrows = gateup ? m->d.ffn : m->d.hidden, ncols = gateup ? m->d.hidden : m->d.ffn;
+    if (moe_experts_mma(m)) {
+        int8_t *xq = gateup ? m->xq_x : m->xq_act;
+        float *sx = gateup ? m->sx_x : m->sx_act;
+        if (!x_quantised && !launch_quant_act(x, x_stride, (npairs + x_div - 1u) / x_div, ncols, xq, sx, s)) return 0;
+        MmaArgs M{};
+        M.w0 = gateup ? m->gate : m->down; M.w1 = gateup ? m->up : nullptr;
+        M.mat_bytes = gateup ? m->gu_bytes : m->down_bytes; M.nb = gateup ? m->gu_nb : m->down_nb;
+        M.nrows = nrows; M.ncols = ncols; M.expert_begin = m->d.expert_begin;
+        M.sorted = m->sorted; M.uexp = m->uexp; M.ustart = m->ustart; M.item_u = m->item_u; M.item_p0 = m->item_p0; M.n_items = m->n_items;
+        M.xq = xq; M.sx = sx; M.x_div = x_div; M.out = out; M.out_stride = out_stride;
+        const uint32_t tok = mma_item_tokens(single_token);
+        const uint32_t live = npairs < m->d.expert_count ? npairs : m->d.expert_count;
+        const uint32_t max_items = single_token ? npairs : (npairs / tok + live < npairs ? npairs / tok + live : npairs);
+        return launch_moe_mma(M, max_items, single_token, s);
+    }
     MoeArgs A{};
     A.w0 = gateup ? m->gate : m->down; A.w1 = gateup ? m->up : nullptr;
     A.mat_bytes = gateup ? m->gu_bytes : m->down_bytes; A.nb = gateup ? m->gu_nb : m->down_nb;
     A.type = gateup ? m->d.type_gu : m->d.type_down;
-    A.nrows = gateup ? m->d.ffn : m->d.hidden; A.ncols = gateup ? m->d.hidden : m->d.ffn;
+    A.nrows = nrows; A.ncols = ncols;
     A.expert_begin = m->d.expert_begin;
     A.sorted = m->sorted; A.uexp = m->uexp; A.ustart = m->ustart; A.n_unique = m->n_unique;
     A.x = x; A.x_stride = x_stride; A.x_div = x_div; A.out = out; A.out_stride = out_stride; A.pair_silu = gateup ? 1u : 0u;
     A.iq2 = books_iq2(); A.iq3s = books_iq3s();
-    if (m->use_mma && A.type == RC_IQ2_XXS && A.ncols % 512u == 0 && A.nrows % 16u == 0) {
-        const uint32_t xrows = (npairs + x_div - 1u) / x_div;
-        int8_t *xq = gateup ? m->xq_x : m->xq_act;
-        float *sx = gateup ? m->sx_x : m->sx_act;
-        if (!launch_quant_act(x, x_stride, xrows, A.ncols, xq, sx, s)) return 0;
-        MmaArgs M{};
-        M.w0 = A.w0; M.w1 = A.w1; M.mat_bytes = A.mat_bytes; M.nb = A.nb; M.nrows = A.nrows; M.ncols = A.ncols; M.expert_begin = A.expert_begin;
-        M.sorted = A.sorted; M.uexp = A.uexp; M.ustart = A.ustart; M.n_unique = A.n_unique;
-        M.xq = xq; M.sx = sx; M.x_div = x_div; M.out = out; M.out_stride = out_stride;
-        const uint32_t grp = npairs < m->d.expert_count ? npairs : m->d.expert_count;
-        return launch_moe_mma(M, grp, single_token, s);
-    }
     uint32_t lpr = 32u;
     while (lpr > (A.ncols >> 6)) lpr >>= 1;
     const uint32_t rows_per_pass = 8u * (32u / lpr);
@@ -279,9 +310,10 @@ static int moe_group(redcuda_moe *m, const uint32_t *pair_expert, uint32_t npair
     RC_REQUIRE(npairs <= m->max_pairs, "moe: %u pairs exceed the workspace (%u)", npairs, m->max_pairs);
     prof_begin("moe_group", s);
     if (distinct && npairs <= 64u) {
-        k_group_trivial<<<1, 64, 0, s>>>(pair_expert, npairs, m->sorted, m->uexp, m->ustart, m->n_unique);
+        k_group_trivial<<<1, 64, 0, s>>>(pair_expert, npairs, m->sorted, m->uexp, m->ustart, m->n_unique, m->item_u, m->item_p0, m->n_items);
     } else {
-        k_group_pairs<<<1, 1024, 0, s>>>(pair_expert, npairs, m->d.expert_begin, m->d.expert_count, m->sorted, m->uexp, m->ustart, m->n_unique, m->bad);
+        k_group_pairs<<<1, 1024, 0, s>>>(pair_expert, npairs, m->d.expert_begin, m->d.expert_count, mma_item_tokens(false), m->sorted, m->uexp, m->ustart,
+                                         m->n_unique, m->item_u, m->item_p0, m->n_items, m->bad);
     }
     prof_end(s);
     RC_LAUNCHED();
@@ -302,14 +334,19 @@ static int moe_forward_on(redcuda_moe *m, uint32_t ntok, const float *x, const f
     RC_REQUIRE(m->d.expert_begin == 0 && m->d.expert_count == m->d.n_expert, "moe forward needs every expert on this device; use the route/experts/shared pieces under expert parallelism");
     RC_REQUIRE(ntok >= 1 && ntok <= m->d.max_tokens, "moe forward: ntok %u outside [1, %u]", ntok, m->d.max_tokens);
     const uint32_t k = m->d.top_k, npairs = ntok * k;
-    if (!moe_gemv_pre(m, ntok, x, logits_in == nullptr, true, s)) return 0;
+    // one quantisation of the token activations serves the routed gate/up and the shared gate/up
+    const bool xq = moe_experts_mma(m) || moe_shared_mma(m, ntok);
+    if (xq && !launch_quant_act(x, m->d.hidden, ntok, m->d.hidden, m->xq_x, m->sx_x, s)) return 0;
+    if (!moe_gemv_pre(m, ntok, x, logits_in == nullptr, true, xq, s)) return 0;
     if (!launch_route(logits_in ? logits_in : m->logits, ntok, m->d.n_expert, k, m->ids, m->wk, nullptr, s)) return 0;
     if (!moe_group(m, m->ids, npairs, ntok == 1u, s)) return 0;
-    if (!moe_launch_experts(m, true, npairs, ntok == 1u, x, m->d.hidden, k, m->act, m->d.ffn, s)) return 0;
+    if (!moe_launch_experts(m, true, npairs, ntok == 1u, x, m->d.hidden, k, xq, m->act, m->d.ffn, s)) return 0;
     if (!moe_shared_down(m, ntok, s)) return 0;
-    if (!moe_launch_experts(m, false, npairs, ntok == 1u, m->act, m->d.ffn, 1u, m->tmp, m->d.hidden, s)) return 0;
+    if (!moe_launch_experts(m, false, npairs, ntok == 1u, m->act, m->d.ffn, 1u, false, m->tmp, m->d.hidden, s)) return 0;
     return moe_combine(m, ntok, m->tmp, m->wk, k, true, resid, out, s);
 }
+
+namespace rc { const uint32_t *moe_last_ids_device(const redcuda_moe *m) { return m->ids; } }
 
 extern "C" {
 
@@ -386,7 +423,8 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
                  o_sha = take(T * d.ffn_sh * 4u), o_sho = take(T * d.hidden * 4u), o_act = take(P * d.ffn * 4u), o_tmp = take(P * d.hidden * 4u),
                  o_out = take(T * d.hidden * 4u), o_ids = take(P * 4u), o_sorted = take(P * 4u), o_uexp = take((size_t)(d.expert_count + 1u) * 4u),
                  o_ustart = take((size_t)(d.expert_count + 2u) * 4u), o_nu = take(16), o_bad = take(16),
-                 o_xqx = take(P * 3u * d.hidden), o_sxx = take(P * 4u), o_xqa = take(P * 3u * d.ffn), o_sxa = take(P * 4u);
+                 o_xqx = take(P * 3u * d.hidden), o_sxx = take(P * 4u), o_xqa = take(P * 3u * d.ffn), o_sxa = take(P * 4u),
+                 o_xqs = take(T * 3u * d.ffn_sh), o_sxs = take(T * 4u), o_iu = take((P + 8u) * 4u), o_ip = take((P + 8u) * 4u), o_ni = take(16);
     if (!m->ws.alloc(w)) return bail();
     uint8_t *B = m->ws.as<uint8_t>();
     m->x = (float *)(B + o_x); m->logits = (float *)(B + o_log); m->wk = (float *)(B + o_wk); m->scalar = (float *)(B + o_sca);
@@ -394,6 +432,8 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
     m->out = (float *)(B + o_out); m->ids = (uint32_t *)(B + o_ids); m->sorted = (uint32_t *)(B + o_sorted); m->uexp = (uint32_t *)(B + o_uexp);
     m->ustart = (uint32_t *)(B + o_ustart); m->n_unique = (uint32_t *)(B + o_nu); m->bad = (uint32_t *)(B + o_bad);
     m->xq_x = (int8_t *)(B + o_xqx); m->sx_x = (float *)(B + o_sxx); m->xq_act = (int8_t *)(B + o_xqa); m->sx_act = (float *)(B + o_sxa);
+    m->xq_sh = (int8_t *)(B + o_xqs); m->sx_sh = (float *)(B + o_sxs); m->item_u = (uint32_t *)(B + o_iu); m->item_p0 = (uint32_t *)(B + o_ip);
+    m->n_items = (uint32_t *)(B + o_ni);
     {   // RC_MOE_PATH=cuda keeps the IQ2_XXS experts on the CUDA-core kernels (A/B switch for profiling)
         const char *pth = getenv("RC_MOE_PATH");
         m->use_mma = !(pth && pth[0] == 'c');
@@ -442,7 +482,7 @@ int redcuda_moe_route_device(redcuda_moe *m, uint32_t ntok, const float *x_dev, 
     RC_REQUIRE(m && ids_dev && weights_dev && (x_dev || logits_in_dev), "moe route: null argument");
     RC_REQUIRE(ntok >= 1 && ntok <= m->d.max_tokens, "moe route: ntok %u outside [1, %u]", ntok, m->d.max_tokens);
     cudaStream_t s = (cudaStream_t)stream;
-    if (!logits_in_dev && !moe_gemv_pre(m, ntok, x_dev, true, false, s)) return 0;
+    if (!logits_in_dev && !moe_gemv_pre(m, ntok, x_dev, true, false, false, s)) return 0;
     return launch_route(logits_in_dev ? logits_in_dev : m->logits, ntok, m->d.n_expert, m->d.top_k, ids_dev, weights_dev, nullptr, s);
 }
 
@@ -451,15 +491,17 @@ int redcuda_moe_experts_device(redcuda_moe *m, uint32_t npairs, const float *pai
     if (!npairs) return 1;
     cudaStream_t s = (cudaStream_t)stream;
     if (!moe_group(m, pair_expert_dev, npairs, false, s)) return 0;
-    if (!moe_launch_experts(m, true, npairs, false, pair_x_dev, m->d.hidden, 1u, m->act, m->d.ffn, s)) return 0;
-    return moe_launch_experts(m, false, npairs, false, m->act, m->d.ffn, 1u, pair_out_dev, m->d.hidden, s);
+    if (!moe_launch_experts(m, true, npairs, false, pair_x_dev, m->d.hidden, 1u, false, m->act, m->d.ffn, s)) return 0;
+    return moe_launch_experts(m, false, npairs, false, m->act, m->d.ffn, 1u, false, pair_out_dev, m->d.hidden, s);
 }
 
 int redcuda_moe_shared_device(redcuda_moe *m, uint32_t ntok, const float *x_dev, float *out_dev, void *stream) {
     RC_REQUIRE(m && x_dev && out_dev, "moe shared: null argument");
     RC_REQUIRE(ntok >= 1 && ntok <= m->d.max_tokens, "moe shared: ntok %u outside [1, %u]", ntok, m->d.max_tokens);
     cudaStream_t s = (cudaStream_t)stream;
-    if (!moe_gemv_pre(m, ntok, x_dev, false, true, s) || !moe_shared_down(m, ntok, s)) return 0;
+    const bool xq = moe_shared_mma(m, ntok);
+    if (xq && !launch_quant_act(x_dev, m->d.hidden, ntok, m->d.hidden, m->xq_x, m->sx_x, s)) return 0;
+    if (!moe_gemv_pre(m, ntok, x_dev, false, true, xq, s) || !moe_shared_down(m, ntok, s)) return 0;
     return moe_combine(m, ntok, nullptr, nullptr, 0u, true, nullptr, out_dev, s);
 }
 

@@ -188,9 +188,11 @@ template <int NMAT, int NTILE>
 __global__ void __launch_bounds__(256, 1) k_moe_mma(const __grid_constant__ MmaArgs A) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr uint32_t NCOL = NTILE * 8u, TOK = NCOL / 3u;
-    const uint32_t u = blockIdx.y;
-    if (u >= *A.n_unique) return;
-    const uint32_t e = A.uexp[u] - A.expert_begin, ps = A.ustart[u], pe = A.ustart[u + 1u];
+    // one work item = up to TOK pairs of one expert (k_group_pairs cuts every expert's pairs into such items, so that
+    // all blocks carry the same amount of work whatever the routing skew)
+    if (blockIdx.y >= *A.n_items) return;
+    const uint32_t u = A.item_u[blockIdx.y], p0 = A.item_p0[blockIdx.y];
+    const uint32_t e = A.uexp[u] - A.expert_begin, pe = A.ustart[u + 1u];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
     const uint32_t S = A.S, R = 8u / S, r = warp / S, ks = warp % S;
     const uint32_t bpr = A.ncols >> 8, nchunks = A.ncols / MMA_CHUNK_COLS, bpitch = mma_b_pitch(A.ncols);
@@ -217,9 +219,8 @@ __global__ void __launch_bounds__(256, 1) k_moe_mma(const __grid_constant__ MmaA
     for (uint32_t i = 0; i < A.tiles_per_warp; ++i) if (tile_first + i < ntile_rows) ++my_tiles;
     const uint32_t nunits = my_tiles * my_chunks;
 
-    for (uint32_t p0 = ps; p0 < pe; p0 += TOK) {
+    {
         const uint32_t nt = min(TOK, pe - p0);
-        __syncthreads();
         // ---- stage the activation digits of pairs [p0, p0 + nt): column = 3 * token + digit
         {
             const uint32_t v16 = A.ncols >> 4;
@@ -286,7 +287,7 @@ __global__ void __launch_bounds__(256, 1) k_moe_mma(const __grid_constant__ MmaA
                         sp[(size_t)g * NCOL] = out[m][n][0]; sp[(size_t)g * NCOL + 1u] = out[m][n][1];
                         sp[(size_t)(g + 8u) * NCOL] = out[m][n][2]; sp[(size_t)(g + 8u) * NCOL + 1u] = out[m][n][3];
                     }
-                if (S > 1u) __syncthreads(); else __syncwarp();       // S > 1 implies one tile per warp: every warp gets here once per pass
+                if (S > 1u) __syncthreads(); else __syncwarp();       // S > 1 implies one tile per warp: every warp gets here once
                 if (ks == 0u) {
                     for (uint32_t idx = lane; idx < 16u * nt; idx += 32u) {
                         const uint32_t row = idx & 15u, tk = idx >> 4;
