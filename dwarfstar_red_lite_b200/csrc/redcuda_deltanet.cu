@@ -11,6 +11,7 @@
 #include "redcuda_kernels.cuh"
 #include "../../include/redcuda.h"
 
+#include <mutex>
 #include <new>
 
 namespace rc {
@@ -169,4 +170,50 @@ extern "C" int redcuda_deltanet_step(const redcuda_deltanet_params *p, uint32_t 
     RC_CUDA(cudaMemcpyAsync(out, o.p, b_z, cudaMemcpyDeviceToHost, s));
     RC_CUDA(cudaStreamSynchronize(s));
     return 1;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Allocation-free variant of the DeltaNet step.
+//
+// The step needs scratch between its three kernels (normalised q/k, conv output v, beta, gate, un-normalised head
+// outputs). redcuda_deltanet_step allocates that scratch per call, which a caller cannot afford when it runs inside a
+// serving loop that must never block on the allocator (cudaMalloc / cudaFree synchronise the whole device), when its
+// stream is being captured into a CUDA graph (allocation is illegal there), or when another runtime owns the device
+// memory budget. For those callers the scratch lives in the array below, part of the library image: every GPU that
+// loads the library holds these 512 KiB until the process exits.
+#define RC_DN_SCRATCH_FLOATS (128u * 1024u)
+static __device__ __align__(256) float g_dn_scratch[RC_DN_SCRATCH_FLOATS];
+
+// In host code g_dn_scratch is only a handle for the runtime, not an address a kernel may use; the device address is
+// asked for once per device (with that device current) and cached here.
+static std::mutex g_dn_scratch_mu;
+static float *g_dn_scratch_dev[64] = {nullptr};
+
+extern "C" int redcuda_deltanet_step_noalloc(const redcuda_deltanet_params *p, uint32_t batch, const float *qkv_dev, const float *z_dev,
+                                             const float *ba_dev, float *conv_state_dev, float *rec_state_dev, float *out_dev, void *stream) {
+    RC_REQUIRE(p && qkv_dev && z_dev && ba_dev && conv_state_dev && rec_state_dev && out_dev && batch, "deltanet step (no-alloc): null or empty argument");
+    RC_REQUIRE(p->conv_kernel && p->dt_bias && p->ssm_a && p->ssm_norm, "deltanet step (no-alloc): null parameter array");
+    const DnDims D{p->d_conv, p->d_state, p->n_group, p->dt_rank, p->d_inner, p->channels, p->rms_eps};
+    const uint64_t n_qk = (uint64_t)batch * 2u * D.groups * D.S, n_v = (uint64_t)batch * D.d_inner, n_r = (uint64_t)batch * D.rank;
+    const uint64_t need = n_qk + 2u * n_v + 2u * n_r;
+    RC_REQUIRE(need <= RC_DN_SCRATCH_FLOATS,
+               "deltanet step (no-alloc): batch %u with these dimensions needs %llu scratch floats, the built-in scratch holds %u; "
+               "use a smaller batch or redcuda_deltanet_step", batch, (unsigned long long)need, RC_DN_SCRATCH_FLOATS);
+    int dev = 0;
+    RC_CUDA(cudaGetDevice(&dev));
+    RC_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
+    float *scr = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_dn_scratch_mu);
+        if (!g_dn_scratch_dev[dev]) {      // first call on this device: resolve the symbol (not during stream capture)
+            void *sym = nullptr;
+            RC_CUDA(cudaGetSymbolAddress(&sym, g_dn_scratch));
+            g_dn_scratch_dev[dev] = (float *)sym;
+        }
+        scr = g_dn_scratch_dev[dev];
+    }
+    // every scratch region is fully written by k_dn_prep / k_dn_state before it is read, so nothing has to be cleared
+    float *qk = scr, *v = qk + n_qk, *core = v + n_v, *beta = core + n_v, *gate = beta + n_r;
+    return launch_deltanet(D, batch, p->conv_kernel, p->dt_bias, p->ssm_a, p->ssm_norm, qkv_dev, z_dev, ba_dev, conv_state_dev, rec_state_dev,
+                           qk, v, beta, gate, core, out_dev, (cudaStream_t)stream);
 }

@@ -16,6 +16,7 @@ u8p, f32p, u32p = C.POINTER(C.c_uint8), C.POINTER(C.c_float), C.POINTER(C.c_uint
 EXPORTS = [
     "redcuda_abi_version", "redcuda_last_error", "redcuda_device_count", "redcuda_set_device", "redcuda_set_codebooks",
     "redcuda_quant_dequant_rows", "redcuda_quant_matvec", "redcuda_router_select_softmax_topk", "redcuda_deltanet_step",
+    "redcuda_deltanet_step_noalloc",
     "redcuda_moe_create", "redcuda_moe_destroy", "redcuda_moe_resident_bytes", "redcuda_moe_forward",
     "redcuda_moe_forward_device", "redcuda_moe_route_device", "redcuda_moe_experts_device", "redcuda_moe_shared_device",
     "redcuda_launch_count", "redcuda_profile_enable", "redcuda_profile_report",
@@ -73,6 +74,7 @@ def lib():
     L.redcuda_quant_matvec.argtypes = [C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
     L.redcuda_router_select_softmax_topk.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]
     L.redcuda_deltanet_step.argtypes = [C.POINTER(DeltanetParams), C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    L.redcuda_deltanet_step_noalloc.argtypes = [C.POINTER(DeltanetParams), C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.redcuda_set_codebooks.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32]
     _lib = L
     return L

@@ -75,6 +75,19 @@ typedef struct {
 int redcuda_deltanet_step(const redcuda_deltanet_params *p, uint32_t batch, const float *qkv, const float *z, const float *ba,
                           float *conv_state, float *rec_state, float *out);
 
+/* No counterpart in the reference. The same DeltaNet step for callers that must not allocate: code running inside a
+ * latency-critical serving loop (cudaMalloc / cudaFree stall the whole device), inside a CUDA-graph stream capture
+ * (allocation is not allowed there), or next to a runtime that owns the device's memory budget. Every pointer — the
+ * four arrays inside *p included — is DEVICE memory; the launches go to `stream` (cudaStream_t) and the call returns
+ * without synchronising. The scratch between the kernels is a fixed 512 KiB array inside the library image (held by
+ * every GPU that loads the library, until exit), enough for batch 8 at the Qwen3-Next shape (16/32 heads of 128);
+ * larger requests fail with a message. The call never calls cudaMalloc, cudaFree or any allocating routine. The first
+ * call on a device looks up the array's device address, so make that first call outside any stream capture. All calls
+ * share the one array: two calls whose kernels overlap on the GPU (different streams, no ordering) race on it. Nothing
+ * in it needs clearing between calls — each call overwrites every value it later reads. */
+int redcuda_deltanet_step_noalloc(const redcuda_deltanet_params *p_device_arrays, uint32_t batch, const float *qkv_dev, const float *z_dev,
+                                  const float *ba_dev, float *conv_state_dev, float *rec_state_dev, float *out_dev, void *stream);
+
 /* ------------------------------------------------------------------------------------------------------------
  * Resident MoE layer: router + routed experts + sigmoid-gated shared expert of one layer, every expert in HBM.
  * Replaces ffn() of native/redlite_native_engine_cpu.c:329-386 and, on the GPU side, the expert pool with its LRU
