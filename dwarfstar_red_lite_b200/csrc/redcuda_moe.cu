@@ -157,18 +157,20 @@ __global__ void k_group_trivial(const uint32_t *__restrict__ pair_expert, uint32
 // out[t] = resid[t] + (sum_k w[t][k] * pair_out[t*k + kk] + shared[t] * scalar[t]); k may be 0 (shared part only).
 __global__ void __launch_bounds__(256) k_moe_combine(const float *__restrict__ pair_out, const float *__restrict__ w, uint32_t top_k,
                                                      const float *__restrict__ shared, const float *__restrict__ scalar,
-                                                     const float *__restrict__ resid, float *__restrict__ out, uint32_t hidden) {
+                                                     const float *__restrict__ resid, float *__restrict__ out, uint32_t hidden,
+                                                     const uint32_t *__restrict__ pair_row) {
     const uint32_t t = blockIdx.y;
     const uint32_t r = (blockIdx.x * 256u + threadIdx.x) * 4u;
     if (r >= hidden) return;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (uint32_t k = 0; k < top_k; ++k) {
         const float wk = w[(size_t)t * top_k + k];
-        const float4 v = *reinterpret_cast<const float4 *>(pair_out + ((size_t)t * top_k + k) * hidden + r);
+        const size_t prow = pair_row ? pair_row[(size_t)t * top_k + k] : (size_t)t * top_k + k;   // where the pair's expert output sits
+        const float4 v = *reinterpret_cast<const float4 *>(pair_out + prow * hidden + r);
         acc.x += wk * v.x; acc.y += wk * v.y; acc.z += wk * v.z; acc.w += wk * v.w;
     }
     if (shared) {
-        const float s = scalar[t];
+        const float s = scalar ? scalar[t] : 1.0f;
         const float4 v = *reinterpret_cast<const float4 *>(shared + (size_t)t * hidden + r);
         acc.x += v.x * s; acc.y += v.y * s; acc.z += v.z * s; acc.w += v.w * s;
     }
@@ -324,7 +326,7 @@ static int moe_combine(redcuda_moe *m, uint32_t ntok, const float *pair_out, con
                        float *out, cudaStream_t s) {
     const dim3 grid((m->d.hidden / 4u + 255u) / 256u, ntok);
     prof_begin("moe_combine", s);
-    k_moe_combine<<<grid, 256, 0, s>>>(pair_out, wk, top_k, shared ? m->sh_out : nullptr, m->scalar, resid, out, m->d.hidden);
+    k_moe_combine<<<grid, 256, 0, s>>>(pair_out, wk, top_k, shared ? m->sh_out : nullptr, m->scalar, resid, out, m->d.hidden, nullptr);
     prof_end(s);
     RC_LAUNCHED();
     return 1;
@@ -493,6 +495,18 @@ int redcuda_moe_experts_device(redcuda_moe *m, uint32_t npairs, const float *pai
     if (!moe_group(m, pair_expert_dev, npairs, false, s)) return 0;
     if (!moe_launch_experts(m, true, npairs, false, pair_x_dev, m->d.hidden, 1u, false, m->act, m->d.ffn, s)) return 0;
     return moe_launch_experts(m, false, npairs, false, m->act, m->d.ffn, 1u, false, pair_out_dev, m->d.hidden, s);
+}
+
+int redcuda_moe_combine_device(redcuda_moe *m, uint32_t ntok, const float *pair_out_dev, const uint32_t *pair_row_dev, const float *weights_dev,
+                               const float *add_dev, const float *resid_dev, float *out_dev, void *stream) {
+    RC_REQUIRE(m && pair_out_dev && weights_dev && out_dev && ntok, "moe combine: null or empty argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid((m->d.hidden / 4u + 255u) / 256u, ntok);
+    prof_begin("moe_combine", s);
+    k_moe_combine<<<grid, 256, 0, s>>>(pair_out_dev, weights_dev, m->d.top_k, add_dev, nullptr, resid_dev, out_dev, m->d.hidden, pair_row_dev);
+    prof_end(s);
+    RC_LAUNCHED();
+    return 1;
 }
 
 int redcuda_moe_shared_device(redcuda_moe *m, uint32_t ntok, const float *x_dev, float *out_dev, void *stream) {

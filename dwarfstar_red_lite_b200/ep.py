@@ -1,0 +1,113 @@
+"""Expert parallelism for the ragged-batch MoE layer: one process per GPU, experts sharded contiguously
+(expert e lives on rank e // (n_expert / world)), router and shared expert replicated, tokens stay with their rank.
+
+Per layer: route locally -> (token, expert) pairs sorted by destination rank -> all-to-all of the pair activations and
+expert ids (dispatch) -> the shard's expert FFN over the received pairs -> all-to-all of the expert outputs back
+(combine) -> per-token weighted sum in router order. This is the multi-GPU form of the reference's single-device pair
+layout (expert_start / pair_token / pair_weight, native/redmetal_topk.h:182-190); the reference itself has no
+multi-device path. torch.distributed is plumbing only (NCCL on GPUs, gloo in the CPU tests); the compute on either
+side of the exchange is the library's (`experts_fn`, `shared_fn`, `combine_fn`).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class DispatchPlan:
+    order: torch.Tensor          # [P] pair ids (t * top_k + k) sorted by destination rank (stable)
+    inverse: torch.Tensor        # [P] position of pair p in the sorted order (row of its result after the combine exchange)
+    send_counts: list[int]       # pairs sent to every rank
+    recv_counts: list[int]       # pairs received from every rank
+
+
+def expert_owner(ids: torch.Tensor, n_expert: int, world: int) -> torch.Tensor:
+    return (ids.to(torch.int64) // (n_expert // world)).to(torch.int64)
+
+
+def plan_dispatch(ids: torch.Tensor, n_expert: int, world: int, group=None) -> DispatchPlan:
+    """ids [T, top_k] (any integer dtype, on the device that will exchange). One tiny count exchange; the split sizes
+    have to be known on the host, so this is the one host synchronisation of a layer."""
+    flat = ids.reshape(-1)
+    dest = expert_owner(flat, n_expert, world)
+    order = torch.argsort(dest, stable=True)
+    inverse = torch.empty_like(order)
+    inverse[order] = torch.arange(order.numel(), device=order.device, dtype=order.dtype)
+    send = torch.bincount(dest, minlength=world).to(torch.int64)
+    recv = torch.empty_like(send)
+    if world > 1:
+        dist.all_to_all_single(recv, send, group=group)
+    else:
+        recv.copy_(send)
+    return DispatchPlan(order, inverse, [int(v) for v in send.tolist()], [int(v) for v in recv.tolist()])
+
+
+def exchange(rows: torch.Tensor, send_counts: list[int], recv_counts: list[int], group=None) -> torch.Tensor:
+    """all-to-all of rows [sum(send_counts), ...] -> [sum(recv_counts), ...]"""
+    out = rows.new_empty((sum(recv_counts),) + tuple(rows.shape[1:]))
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
+    else:
+        out.copy_(rows)
+    return out
+
+
+def ep_moe_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, n_expert: int, world: int, experts_fn, shared_fn, combine_fn,
+                   group=None):
+    """x [T, H] float32, ids / weights [T, top_k] from the router.
+    experts_fn(pair_x [P, H], pair_expert [P] int32) -> [P, H] unweighted outputs of this rank's experts
+    shared_fn(x) -> [T, H] shared-expert part (already gated), or None
+    combine_fn(pair_out [P, H], pair_row [P] int32, weights, add) -> [T, H]
+    Returns (out [T, H], plan)."""
+    T, k = ids.shape
+    plan = plan_dispatch(ids, n_expert, world, group)
+    tok_of_pair = (plan.order // k)
+    send_x = x.index_select(0, tok_of_pair)                                   # activations of the pairs, destination-major
+    send_e = ids.reshape(-1).index_select(0, plan.order).to(torch.int32)
+    recv_x = exchange(send_x, plan.send_counts, plan.recv_counts, group)
+    recv_e = exchange(send_e, plan.send_counts, plan.recv_counts, group)
+    shared = shared_fn(x) if shared_fn is not None else None                   # independent of the exchange
+    recv_out = experts_fn(recv_x, recv_e) if recv_x.shape[0] else recv_x.new_empty((0, x.shape[1]))
+    back = exchange(recv_out, plan.recv_counts, plan.send_counts, group)      # row i = result of pair plan.order[i]
+    out = combine_fn(back, plan.inverse.to(torch.int32), weights, shared)
+    return out, plan
+
+
+class EpMoeLayer:
+    """One MoE layer under expert parallelism on CUDA: wraps a redcuda MoeLayer that holds this rank's expert shard."""
+
+    def __init__(self, moe_shard, rank: int, world: int, max_tokens: int, group=None):
+        self.m, self.rank, self.world, self.group = moe_shard, rank, world, group
+        d = moe_shard.dims
+        self.dims = d
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.ids = torch.empty(max_tokens, d.top_k, dtype=torch.int32, device=dev)
+        self.w = torch.empty(max_tokens, d.top_k, dtype=torch.float32, device=dev)
+        self.shared = torch.empty(max_tokens, d.hidden, dtype=torch.float32, device=dev)
+        self.pair_counts_last = None
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, logits: torch.Tensor | None = None):
+        T = x.shape[0]
+        st = torch.cuda.current_stream().cuda_stream
+        ids, w = self.ids[:T], self.w[:T]
+        self.m.route_device(T, x.data_ptr(), ids.data_ptr(), w.data_ptr(), st, logits_ptr=0 if logits is None else logits.data_ptr())
+
+        def experts_fn(px, pe):
+            po = torch.empty_like(px)
+            self.m.experts_device(px.shape[0], px.data_ptr(), pe.data_ptr(), po.data_ptr(), st)
+            return po
+
+        def shared_fn(xx):
+            self.m.shared_device(T, xx.data_ptr(), self.shared.data_ptr(), st)
+            return self.shared[:T]
+
+        def combine_fn(back, pair_row, weights, add):
+            self.m.combine_device(T, back.data_ptr(), pair_row.data_ptr(), weights.data_ptr(), add.data_ptr(), 0, out.data_ptr(), st)
+            return out
+
+        _, plan = ep_moe_forward(x, ids, w, self.dims.n_expert, self.world, experts_fn, shared_fn, combine_fn, self.group)
+        self.pair_counts_last = sum(plan.recv_counts)
+        return out

@@ -19,6 +19,7 @@ EXPORTS = [
     "redcuda_deltanet_step_noalloc",
     "redcuda_moe_create", "redcuda_moe_destroy", "redcuda_moe_resident_bytes", "redcuda_moe_forward",
     "redcuda_moe_forward_device", "redcuda_moe_route_device", "redcuda_moe_experts_device", "redcuda_moe_shared_device",
+    "redcuda_moe_combine_device",
     "redcuda_launch_count", "redcuda_profile_enable", "redcuda_profile_report",
     # engine ABI (include/rl_engine.h)
     "rl_engine_config_default", "rl_engine_open", "rl_engine_close", "rl_engine_info_get", "rl_engine_reset", "rl_engine_position",
@@ -70,6 +71,7 @@ def lib():
     L.redcuda_moe_route_device.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.redcuda_moe_experts_device.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.redcuda_moe_shared_device.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]
+    L.redcuda_moe_combine_device.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.redcuda_quant_dequant_rows.argtypes = [C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]
     L.redcuda_quant_matvec.argtypes = [C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
     L.redcuda_router_select_softmax_topk.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]
@@ -251,6 +253,10 @@ class MoeLayer:
 
     def experts_device(self, npairs: int, pair_x_ptr: int, pair_expert_ptr: int, pair_out_ptr: int, stream: int):
         _check(lib().redcuda_moe_experts_device(self._h, npairs, pair_x_ptr, pair_expert_ptr, pair_out_ptr, stream or None))
+
+    def combine_device(self, ntok: int, pair_out_ptr: int, pair_row_ptr: int, weights_ptr: int, add_ptr: int, resid_ptr: int, out_ptr: int, stream: int):
+        _check(lib().redcuda_moe_combine_device(self._h, ntok, pair_out_ptr, pair_row_ptr or None, weights_ptr, add_ptr or None, resid_ptr or None,
+                                                out_ptr, stream or None))
 
     def shared_device(self, ntok: int, x_ptr: int, out_ptr: int, stream: int):
         _check(lib().redcuda_moe_shared_device(self._h, ntok, x_ptr, out_ptr, stream or None))

@@ -137,6 +137,11 @@ int redcuda_moe_route_device(redcuda_moe *m, uint32_t ntok, const float *x_dev, 
 int redcuda_moe_experts_device(redcuda_moe *m, uint32_t npairs, const float *pair_x_dev, const uint32_t *pair_expert_dev,
                                float *pair_out_dev, void *stream);
 int redcuda_moe_shared_device(redcuda_moe *m, uint32_t ntok, const float *x_dev, float *out_dev, void *stream);
+/*   combine: out_dev[t] = resid[t] + add[t] + sum_k weights[t][k] * pair_out[row(t,k)] in router order, the per-token sum of
+ *            redmetal_topk_sum_b (native/redmetal_topk.m:626-640); row(t,k) = pair_row_dev[t*top_k+k], or t*top_k+k when
+ *            pair_row_dev is NULL; add_dev (the shared-expert part) and resid_dev may be NULL */
+int redcuda_moe_combine_device(redcuda_moe *m, uint32_t ntok, const float *pair_out_dev, const uint32_t *pair_row_dev, const float *weights_dev,
+                               const float *add_dev, const float *resid_dev, float *out_dev, void *stream);
 
 /* Per-kernel timing for benchmarks: while enabled, every kernel launch is bracketed by CUDA events on its stream
  * (do not enable while capturing a CUDA graph). report() waits for the device and writes one line per kernel name,

@@ -197,3 +197,27 @@ def test_deltanet_step(B, shape):
             assert np.all(np.abs(rec_g[b] - rec[b]) <= 3e-6 + 3e-5 * np.abs(rec[b])), (step, b)
             assert np.array_equal(conv_g[b], conv[b])
             assert np.max(np.abs(out[b] - ref)) <= REL_OUT * np.max(np.abs(ref)), (step, b)
+
+
+def test_ep_pieces_single_rank_match_fused_forward(full_layer):
+    """route / experts / shared / combine device entry points (the expert-parallel halves) chained on one GPU with the
+    dispatch plan of ep.py must equal the fused forward bit-for-bit (same kernels, same order of sums)."""
+    import torch
+    from dwarfstar_red_lite_b200 import ep
+    rng = np.random.default_rng(12)
+    T = 24
+    x = rng.normal(0, 1, size=(T, 2048)).astype(np.float32)
+    logits = synth.zipf_routing_logits(79, T)
+    m = rc.MoeLayer(full_layer, max_tokens=T)
+    try:
+        want = m.forward(x, logits_in=logits)
+        dev = torch.device("cuda", 0)
+        xd, ld = torch.from_numpy(x).to(dev), torch.from_numpy(logits).to(dev)
+        out = torch.empty(T, 2048, device=dev)
+        layer = ep.EpMoeLayer(m, 0, 1, T)
+        layer.forward(xd, out, logits=ld)
+        torch.cuda.synchronize()
+        got = out.cpu().numpy()
+    finally:
+        m.close()
+    assert np.array_equal(got, want)
