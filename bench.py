@@ -160,6 +160,73 @@ def workload_config(args, dims):
             "parallelism": "single GPU" if args.gpus == 1 else f"ep{args.gpus}"}
 
 
+def run_ep(args, world, rank, local):
+    """N > 1: expert parallelism. Every rank keeps its own 64 tokens (weak scaling) and 512 / N experts of every layer;
+    per layer one all-to-all each way over NCCL. Timed with CUDA events per rank, maximum over ranks."""
+    import torch
+    import torch.distributed as dist
+    import dwarfstar_red_lite_b200 as rc
+    from dwarfstar_red_lite_b200 import ep, redcuda as rcm, synth, synth_device
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    rc.set_codebooks(device=local)
+    dims = synth.MoeDims()
+    L, T = args.layers, args.tokens
+    ec = dims.n_expert // world
+    layers = []
+    for l in range(L):
+        tens = synth_device.moe_layer_tensors(1000 + l, dims, dev, expert_begin=rank * ec, expert_count=ec)
+        m = rc.MoeLayer(device_tensors=tens, dims=dims, max_tokens=T * world, expert_begin=rank * ec, expert_count=ec)
+        layers.append(ep.EpMoeLayer(m, rank, world, T))
+        del tens
+    logits_h = np.stack([synth.zipf_routing_logits(500 + l + 1000 * rank, T) for l in range(L)])
+    gx = torch.Generator(device=dev)
+    gx.manual_seed(7 + rank)
+    x_d = torch.randn(L, T, dims.hidden, device=dev, generator=gx)
+    logits_d = torch.from_numpy(logits_h).to(dev)
+    out_d = torch.empty(L, T, dims.hidden, device=dev)
+
+    def step():
+        for l in range(L):
+            layers[l].forward(x_d[l], out_d[l], logits=logits_d[l])
+
+    n0 = rcm.lib().redcuda_launch_count()
+    step()
+    launches_per_step = rcm.lib().redcuda_launch_count() - n0
+    for _ in range(args.warmup - 1):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    pairs = torch.tensor([float(sum(lay.pair_counts_last or 0 for lay in layers)) / L], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    allpairs = [torch.zeros_like(pairs) for _ in range(world)]
+    dist.all_gather(allpairs, pairs)
+    dist.barrier()
+    if rank == 0:
+        ms_per_step = float(ms.item()) / args.steps
+        value = T * world * L / (ms_per_step * 1e-3)
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": dict(workload_config(args, dims), experts_per_gpu=ec, pairs_received_per_rank_per_layer=[float(p.item()) for p in allpairs],
+                               exchange="2 x NCCL all_to_all_single per layer (activations fp32 out, expert outputs fp32 back) + one count exchange"),
+                "roofline": None, "cpu_baseline": None,
+                "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                        "note": "multi-GPU runs keep activations on the devices; the host-buffer path is measured at N=1"},
+                "gpu_launches": int(launches_per_step * args.steps), "clocks": clocks.summary()}
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -186,7 +253,7 @@ def main():
     if args.gpus != world and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     if world > 1:
-        raise SystemExit("expert-parallel bench path: see bench_ep in dwarfstar_red_lite_b200 (not wired in this build)")
+        return run_ep(args, world, rank, local)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     rc.set_codebooks(device=local)

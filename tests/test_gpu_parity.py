@@ -201,7 +201,8 @@ def test_deltanet_step(B, shape):
 
 def test_ep_pieces_single_rank_match_fused_forward(full_layer):
     """route / experts / shared / combine device entry points (the expert-parallel halves) chained on one GPU with the
-    dispatch plan of ep.py must equal the fused forward bit-for-bit (same kernels, same order of sums)."""
+    dispatch plan of ep.py must equal the fused forward (same kernels; the shared part is rounded once more on its way
+    through its own buffer, hence a few ulp)."""
     import torch
     from dwarfstar_red_lite_b200 import ep
     rng = np.random.default_rng(12)
@@ -220,4 +221,4 @@ def test_ep_pieces_single_rank_match_fused_forward(full_layer):
         got = out.cpu().numpy()
     finally:
         m.close()
-    assert np.array_equal(got, want)
+    assert np.max(np.abs(got - want)) <= 2e-6 * np.max(np.abs(want))
