@@ -227,6 +227,99 @@ def run_ep(args, world, rank, local):
     dist.destroy_process_group()
 
 
+def run_decode48(args):
+    """BASELINE configs[3]: the whole 48-layer random-init model, batch 1, greedy decode at a long context. The model is
+    written as a synthetic GGUF file (seeded), opened through rl_engine_open, and decoded with
+    rl_engine_generate_greedy; the CPU baseline is the oracle port of rl_engine_cpu_step on the same file."""
+    import dwarfstar_red_lite_b200 as rc
+    from dwarfstar_red_lite_b200 import gguf_writer, synth
+    from dwarfstar_red_lite_b200.engine import Engine
+    os.environ.setdefault("RL_KV_F16", "1")
+    dims = synth.ModelDims(n_layer=args.layers, context=args.context)
+    tmp = os.environ.get("REDCUDA_TMP", "/tmp")
+    path = os.path.join(tmp, f"redcuda_synth_{args.layers}l_seed{args.seed}.gguf")
+    t0 = time.perf_counter()
+    if not os.path.exists(path):
+        size = gguf_writer.write_gguf_streaming(path, args.seed, dims)
+    else:
+        size = os.path.getsize(path)
+    t_write = time.perf_counter() - t0
+    rc.set_codebooks()
+    t0 = time.perf_counter()
+    eng = Engine(path, context=dims.context)
+    t_open = time.perf_counter() - t0
+    info = eng.info
+    new_tokens, start_pos = args.new_tokens, max(0, dims.context - args.new_tokens - 1)
+    result = {}
+    # ---- parity: greedy tokens from an empty state against the CPU oracle
+    check = None
+    if args.check_steps > 0:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import oracle_lib as ol
+        om = ol.OracleModel(gguf_writer.load_gguf(path, dims), kv_f16=True, context=dims.context)
+        got, _ = eng.generate_greedy(args.first_token, args.check_steps)
+        tok, want, t0 = args.first_token, [], time.perf_counter()
+        for _ in range(args.check_steps):
+            tok = int(np.argmax(om.step(tok, threads=os.cpu_count() or 1)))
+            want.append(tok)
+        cpu_s = (time.perf_counter() - t0) / args.check_steps
+        same = int(np.sum(np.array(want) == got))
+        first_diff = next((i for i, (a, b) in enumerate(zip(want, got)) if a != b), None)
+        check = {"greedy_steps": args.check_steps, "tokens_equal": same, "first_difference": first_diff, "cpu_s_per_token": cpu_s}
+        eng.reset()
+        del om
+    # ---- timed decode at long context
+    rng = np.random.default_rng(args.seed)
+    for _ in range(args.warmup):
+        eng.set_position(start_pos)
+        eng.generate_greedy(int(rng.integers(dims.vocab)), 4)
+    times = []
+    with ClockSampler(0) as clocks:
+        for _ in range(args.steps):
+            eng.set_position(start_pos)
+            _, ms = eng.generate_greedy(int(rng.integers(dims.vocab)), new_tokens)
+            times.append(ms)
+    ms_run = float(np.median(times))
+    tok_s = new_tokens / (ms_run * 1e-3)
+    eng.set_position(dims.context - 1 - new_tokens // 2)
+    step_bytes = eng.step_bytes()
+    # ---- end to end per token: rl_engine_step with the logits copied to the host every token
+    eng.set_position(start_pos)
+    logits = np.empty(info.vocab, np.float32)
+    tok, t0, n_e2e = 5, time.perf_counter(), min(32, new_tokens)
+    for _ in range(n_e2e):
+        eng.step(tok, logits=logits)
+        tok = int(np.argmax(logits))
+    e2e_tok_s = n_e2e / (time.perf_counter() - t0)
+    # ---- CPU baseline: the oracle port, all host threads, a bounded number of tokens from an empty state
+    cpu = None
+    if not args.no_cpu:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import oracle_lib as ol
+        om = ol.OracleModel(gguf_writer.load_gguf(path, dims), kv_f16=True, context=dims.context)
+        threads = os.cpu_count() or 1
+        t0, n = time.perf_counter(), 0
+        tok = 5
+        while n < 8 and (n == 0 or time.perf_counter() - t0 < args.cpu_budget_s):
+            tok = int(np.argmax(om.step(tok, threads=threads)))
+            n += 1
+        dt = time.perf_counter() - t0
+        cpu = {"value": n / dt, "unit": "tokens/s", "cores": threads, "kind": "port",
+               "sample": f"{n} greedy tokens from an empty state in {dt:.1f} s (oracle port of rl_engine_cpu_step; short context, which favours the CPU)"}
+    peak, peak_kind = measured_peak()
+    gbs = step_bytes * tok_s / 1e9
+    line = {"metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_run, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"BASELINE configs[3]: {info.n_layer}-layer Qwen3-Next-shaped random-init model, batch 1, greedy, {new_tokens} new tokens ending at context {dims.context}, fp16 KV",
+                       "gguf_bytes": size, "write_s": round(t_write, 1), "open_s": round(t_open, 1), "l2_policy": "one token reads ~%.2f GB of weights and state" % (step_bytes / 1e9)},
+            "roofline": {"bound": "hbm", "kernel": "whole decode step", "achieved": gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": gbs / peak,
+                         "traffic": None, "bytes_per_token": step_bytes},
+            "cpu_baseline": cpu, "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": int(info.vocab * 4 + info.n_layer * info.hidden * 4)},
+            "parity": check, "gpu_launches": None, "clocks": clocks.summary()}
+    print(json.dumps(line), flush=True)
+    eng.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -238,7 +331,17 @@ def main():
     ap.add_argument("--ref-tokens", type=int, default=8, help="tokens per step of the reference (CPU) arm")
     ap.add_argument("--cpu-budget-s", type=float, default=15.0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--workload", default="ragged64", choices=["ragged64", "decode48"],
+                    help="ragged64: BASELINE configs[1] (default, the headline); decode48: configs[3], whole-model decode")
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--new-tokens", type=int, default=128)
+    ap.add_argument("--check-steps", type=int, default=0, help="decode48: greedy tokens compared with the CPU oracle")
+    ap.add_argument("--first-token", type=int, default=7)
+    ap.add_argument("--seed", type=int, default=1)
     args = ap.parse_args()
+    if args.workload == "decode48":
+        args.warmup = max(args.warmup, 1)
+        return run_decode48(args)
     args.warmup = max(args.warmup, 3) if args.impl == "redcuda" else args.warmup
     if args.impl == "reference":
         return run_reference(args)

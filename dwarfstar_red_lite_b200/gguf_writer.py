@@ -12,7 +12,7 @@ import struct
 
 import numpy as np
 
-from .synth import ModelDims, SynthModel
+from .synth import ModelDims, SynthModel, iter_model_tensors, tensor_nbytes, tensor_spec
 
 _U32, _F32, _STR, _ARR = 4, 6, 8, 9
 ALIGNMENT = 32
@@ -90,3 +90,77 @@ def write_gguf(path: str, model: SynthModel) -> int:
             f.write(np.ascontiguousarray(arr).reshape(-1).view(np.uint8).data)
             f.write(b"\0" * ((-arr.nbytes) % ALIGNMENT))
         return f.tell()
+
+
+def write_gguf_streaming(path: str, seed: int, dims: ModelDims, expert_scale: float = 0.2) -> int:
+    """Same file as write_gguf(path, synth.model(seed, dims, expert_scale)), written tensor by tensor as it is generated
+    (peak memory: one layer). Returns the file size."""
+    kv = metadata(dims)
+    spec = tensor_spec(dims)
+    directory, offset = [], 0
+    for name, t, shape in spec:
+        directory.append(_s(name.encode()) + struct.pack("<I", len(shape)) + b"".join(struct.pack("<Q", s) for s in shape) + struct.pack("<IQ", t, offset))
+        offset += tensor_nbytes(t, shape)
+        offset += (-offset) % ALIGNMENT
+    with open(path, "wb") as f:
+        f.write(b"GGUF" + struct.pack("<IQQ", 3, len(spec), len(kv)))
+        for b in kv:
+            f.write(b)
+        for b in directory:
+            f.write(b)
+        f.write(b"\0" * ((-f.tell()) % ALIGNMENT))
+        for (name, t, shape), (gname, gt, gshape, arr) in zip(spec, iter_model_tensors(seed, dims, expert_scale)):
+            if (name, t, tuple(shape)) != (gname, gt, tuple(gshape)) or arr.nbytes != tensor_nbytes(t, shape):
+                raise RuntimeError(f"tensor spec and generator disagree at {name} / {gname}")
+            f.write(np.ascontiguousarray(arr).reshape(-1).view(np.uint8).data)
+            f.write(b"\0" * ((-arr.nbytes) % ALIGNMENT))
+        return f.tell()
+
+
+def load_gguf(path: str, dims: ModelDims) -> SynthModel:
+    """Memory-mapped view of a file written by this module (tensor payloads are np.memmap slices, nothing is copied)."""
+    mm = np.memmap(path, dtype=np.uint8, mode="r")
+    pos = 4
+    version, n_tensors, n_kv = struct.unpack_from("<IQQ", mm, pos)
+    pos += 20
+    scalar = {0: 1, 1: 1, 2: 2, 3: 2, 4: 4, 5: 4, 6: 4, 7: 1, 10: 8, 11: 8, 12: 8}
+
+    def rd_str(p):
+        n, = struct.unpack_from("<Q", mm, p)
+        return bytes(mm[p + 8:p + 8 + n]).decode(), p + 8 + n
+
+    for _ in range(n_kv):
+        _, pos = rd_str(pos)
+        t, = struct.unpack_from("<I", mm, pos)
+        pos += 4
+        if t == 8:
+            _, pos = rd_str(pos)
+        elif t == 9:
+            sub, cnt = struct.unpack_from("<IQ", mm, pos)
+            pos += 12
+            if sub == 8:
+                for _ in range(cnt):
+                    n, = struct.unpack_from("<Q", mm, pos)
+                    pos += 8 + n
+            else:
+                pos += cnt * scalar[sub]
+        else:
+            pos += scalar[t]
+    entries = []
+    for _ in range(n_tensors):
+        name, pos = rd_str(pos)
+        nd, = struct.unpack_from("<I", mm, pos)
+        pos += 4
+        shape = struct.unpack_from("<" + "Q" * nd, mm, pos)
+        pos += 8 * nd
+        t, off = struct.unpack_from("<IQ", mm, pos)
+        pos += 12
+        entries.append((name, t, tuple(int(v) for v in shape), off))
+    base = pos + (-pos) % ALIGNMENT
+    m = SynthModel(dims)
+    for name, t, shape, off in entries:
+        nb = tensor_nbytes(t, shape)
+        raw = mm[base + off:base + off + nb]
+        arr = raw.view(np.float32) if t == 0 else raw
+        m.tensors[name] = (t, shape, arr)
+    return m

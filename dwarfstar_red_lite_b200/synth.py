@@ -33,7 +33,7 @@ def quant_matrix(rng: np.random.Generator, ggml_type: int, nrows: int, ncols: in
     For Q6_K the 16 int8 sub-block scales are drawn from sub_scale_range (default the full int8 range)."""
     nb = nrows * (ncols // 256)
     bb = BLOCK_BYTES[ggml_type]
-    blocks = rng.integers(0, 256, size=(nb, bb), dtype=np.uint8)
+    blocks = np.frombuffer(rng.bytes(nb * bb), dtype=np.uint8).reshape(nb, bb).copy()     # random payload bytes (fast path of the generator)
     d = rng.uniform(d_lo, d_hi, size=nb).astype(np.float16)
     off = D_OFFSET[ggml_type]
     blocks[:, off:off + 2] = d.view(np.uint8).reshape(nb, 2)
@@ -170,54 +170,92 @@ def _dense(rng, t, nrows, ncols, scale=1.0):
     return quant_matrix(rng, t, nrows, ncols, lo, hi, (-64, 63) if t == Q6_K else None)
 
 
-def model(seed: int, dims: ModelDims, expert_scale: float = 0.2) -> SynthModel:
-    """Whole random-init Qwen3-Next-shaped model under the tensor names the reference audits
-    (native/redlite_native_engine.c:117-183). GGUF shapes list the row length first."""
-    m = SynthModel(dims)
-    T = m.tensors
+def iter_model_tensors(seed: int, dims: ModelDims, expert_scale: float = 0.2):
+    """Yields (name, ggml_type, GGUF shape, payload) tensor by tensor, generating each layer only when it is reached, so
+    that a 22 GB model can be streamed to a file without being held in memory. Whole random-init Qwen3-Next-shaped model
+    under the tensor names the reference audits (native/redlite_native_engine.c:117-183); GGUF shapes list the row
+    length first."""
     rng = np.random.default_rng(seed)
     h, td, te = dims.hidden, dims.type_dense, dims.type_experts
 
     def put(name, t, shape, arr):
-        T[name] = (t, tuple(int(s) for s in shape), np.ascontiguousarray(arr))
+        return (name, t, tuple(int(s) for s in shape), np.ascontiguousarray(arr))
 
     def norm_w(n):
         return (1.0 + rng.normal(0.0, 0.02, size=n)).astype(np.float32)
 
-    put("token_embd.weight", td, (h, dims.vocab), _dense(rng, td, dims.vocab, h, 40.0))
-    put("output_norm.weight", F32, (h,), norm_w(h))
-    put("output.weight", td, (h, dims.vocab), _dense(rng, td, dims.vocab, h))
+    yield put("token_embd.weight", td, (h, dims.vocab), _dense(rng, td, dims.vocab, h, 40.0))
+    yield put("output_norm.weight", F32, (h,), norm_w(h))
+    yield put("output.weight", td, (h, dims.vocab), _dense(rng, td, dims.vocab, h))
     for l in range(dims.n_layer):
         p = f"blk.{l}."
         lr = np.random.default_rng([seed, l + 1])
-        put(p + "attn_norm.weight", F32, (h,), norm_w(h))
-        put(p + "post_attention_norm.weight", F32, (h,), norm_w(h))
+        yield put(p + "attn_norm.weight", F32, (h,), norm_w(h))
+        yield put(p + "post_attention_norm.weight", F32, (h,), norm_w(h))
         if dims.is_attention(l):
             qc, kvc = dims.n_head * dims.head_dim, dims.n_head_kv * dims.head_dim
-            put(p + "attn_q.weight", td, (h, 2 * qc), _dense(lr, td, 2 * qc, h))
-            put(p + "attn_k.weight", td, (h, kvc), _dense(lr, td, kvc, h))
-            put(p + "attn_v.weight", td, (h, kvc), _dense(lr, td, kvc, h))
-            put(p + "attn_q_norm.weight", F32, (dims.head_dim,), (1.0 + lr.normal(0, 0.02, dims.head_dim)).astype(np.float32))
-            put(p + "attn_k_norm.weight", F32, (dims.head_dim,), (1.0 + lr.normal(0, 0.02, dims.head_dim)).astype(np.float32))
-            put(p + "attn_output.weight", td, (qc, h), _dense(lr, td, h, qc))
+            yield put(p + "attn_q.weight", td, (h, 2 * qc), _dense(lr, td, 2 * qc, h))
+            yield put(p + "attn_k.weight", td, (h, kvc), _dense(lr, td, kvc, h))
+            yield put(p + "attn_v.weight", td, (h, kvc), _dense(lr, td, kvc, h))
+            yield put(p + "attn_q_norm.weight", F32, (dims.head_dim,), (1.0 + lr.normal(0, 0.02, dims.head_dim)).astype(np.float32))
+            yield put(p + "attn_k_norm.weight", F32, (dims.head_dim,), (1.0 + lr.normal(0, 0.02, dims.head_dim)).astype(np.float32))
+            yield put(p + "attn_output.weight", td, (qc, h), _dense(lr, td, h, qc))
         else:
-            put(p + "attn_qkv.weight", td, (h, dims.channels), _dense(lr, td, dims.channels, h))
-            put(p + "attn_gate.weight", td, (h, dims.d_inner), _dense(lr, td, dims.d_inner, h))
-            put(p + "ssm_ba.weight", td, (h, 2 * dims.dt_rank), _dense(lr, td, 2 * dims.dt_rank, h))
-            put(p + "ssm_conv1d.weight", F32, (dims.d_conv, dims.channels),
+            yield put(p + "attn_qkv.weight", td, (h, dims.channels), _dense(lr, td, dims.channels, h))
+            yield put(p + "attn_gate.weight", td, (h, dims.d_inner), _dense(lr, td, dims.d_inner, h))
+            yield put(p + "ssm_ba.weight", td, (h, 2 * dims.dt_rank), _dense(lr, td, 2 * dims.dt_rank, h))
+            yield put(p + "ssm_conv1d.weight", F32, (dims.d_conv, dims.channels),
                 lr.normal(0.0, 0.5, size=(dims.channels, dims.d_conv)).astype(np.float32))
-            put(p + "ssm_dt.bias", F32, (dims.dt_rank,), lr.normal(0.0, 0.5, size=dims.dt_rank).astype(np.float32))
-            put(p + "ssm_a", F32, (dims.dt_rank,), (-np.exp(lr.normal(0.0, 0.5, size=dims.dt_rank))).astype(np.float32))
-            put(p + "ssm_norm.weight", F32, (dims.d_state,), (1.0 + lr.normal(0, 0.1, dims.d_state)).astype(np.float32))
-            put(p + "ssm_out.weight", td, (dims.d_inner, h), _dense(lr, td, h, dims.d_inner))
+            yield put(p + "ssm_dt.bias", F32, (dims.dt_rank,), lr.normal(0.0, 0.5, size=dims.dt_rank).astype(np.float32))
+            yield put(p + "ssm_a", F32, (dims.dt_rank,), (-np.exp(lr.normal(0.0, 0.5, size=dims.dt_rank))).astype(np.float32))
+            yield put(p + "ssm_norm.weight", F32, (dims.d_state,), (1.0 + lr.normal(0, 0.1, dims.d_state)).astype(np.float32))
+            yield put(p + "ssm_out.weight", td, (dims.d_inner, h), _dense(lr, td, h, dims.d_inner))
         md = MoeDims(h, dims.n_expert, dims.top_k, dims.ffn, dims.ffn_sh, te, te, td)
         ml = moe_layer(int(lr.integers(1 << 31)), md, expert_scale=expert_scale)
-        put(p + "ffn_gate_inp.weight", F32, (h, dims.n_expert), ml.router)
-        put(p + "ffn_gate_inp_shexp.weight", F32, (h,), ml.sh_gate_inp)
-        put(p + "ffn_gate_shexp.weight", td, (h, dims.ffn_sh), ml.sh_gate)
-        put(p + "ffn_up_shexp.weight", td, (h, dims.ffn_sh), ml.sh_up)
-        put(p + "ffn_down_shexp.weight", td, (dims.ffn_sh, h), ml.sh_down)
-        put(p + "ffn_gate_exps.weight", te, (h, dims.ffn, dims.n_expert), ml.gate)
-        put(p + "ffn_up_exps.weight", te, (h, dims.ffn, dims.n_expert), ml.up)
-        put(p + "ffn_down_exps.weight", te, (dims.ffn, h, dims.n_expert), ml.down)
+        yield put(p + "ffn_gate_inp.weight", F32, (h, dims.n_expert), ml.router)
+        yield put(p + "ffn_gate_inp_shexp.weight", F32, (h,), ml.sh_gate_inp)
+        yield put(p + "ffn_gate_shexp.weight", td, (h, dims.ffn_sh), ml.sh_gate)
+        yield put(p + "ffn_up_shexp.weight", td, (h, dims.ffn_sh), ml.sh_up)
+        yield put(p + "ffn_down_shexp.weight", td, (dims.ffn_sh, h), ml.sh_down)
+        yield put(p + "ffn_gate_exps.weight", te, (h, dims.ffn, dims.n_expert), ml.gate)
+        yield put(p + "ffn_up_exps.weight", te, (h, dims.ffn, dims.n_expert), ml.up)
+        yield put(p + "ffn_down_exps.weight", te, (dims.ffn, h, dims.n_expert), ml.down)
+
+
+def model(seed: int, dims: ModelDims, expert_scale: float = 0.2) -> SynthModel:
+    """The whole synthetic model in memory (small models: tests)."""
+    m = SynthModel(dims)
+    for name, t, shape, arr in iter_model_tensors(seed, dims, expert_scale):
+        m.tensors[name] = (t, shape, arr)
     return m
+
+
+def tensor_spec(dims: ModelDims) -> list:
+    """(name, ggml_type, GGUF shape) of every tensor in the order iter_model_tensors yields them, without any data."""
+    h, td, te = dims.hidden, dims.type_dense, dims.type_experts
+    spec = [("token_embd.weight", td, (h, dims.vocab)), ("output_norm.weight", F32, (h,)), ("output.weight", td, (h, dims.vocab))]
+    for l in range(dims.n_layer):
+        p = f"blk.{l}."
+        spec += [(p + "attn_norm.weight", F32, (h,)), (p + "post_attention_norm.weight", F32, (h,))]
+        if dims.is_attention(l):
+            qc, kvc = dims.n_head * dims.head_dim, dims.n_head_kv * dims.head_dim
+            spec += [(p + "attn_q.weight", td, (h, 2 * qc)), (p + "attn_k.weight", td, (h, kvc)), (p + "attn_v.weight", td, (h, kvc)),
+                     (p + "attn_q_norm.weight", F32, (dims.head_dim,)), (p + "attn_k_norm.weight", F32, (dims.head_dim,)),
+                     (p + "attn_output.weight", td, (qc, h))]
+        else:
+            spec += [(p + "attn_qkv.weight", td, (h, dims.channels)), (p + "attn_gate.weight", td, (h, dims.d_inner)),
+                     (p + "ssm_ba.weight", td, (h, 2 * dims.dt_rank)), (p + "ssm_conv1d.weight", F32, (dims.d_conv, dims.channels)),
+                     (p + "ssm_dt.bias", F32, (dims.dt_rank,)), (p + "ssm_a", F32, (dims.dt_rank,)), (p + "ssm_norm.weight", F32, (dims.d_state,)),
+                     (p + "ssm_out.weight", td, (dims.d_inner, h))]
+        spec += [(p + "ffn_gate_inp.weight", F32, (h, dims.n_expert)), (p + "ffn_gate_inp_shexp.weight", F32, (h,)),
+                 (p + "ffn_gate_shexp.weight", td, (h, dims.ffn_sh)), (p + "ffn_up_shexp.weight", td, (h, dims.ffn_sh)),
+                 (p + "ffn_down_shexp.weight", td, (dims.ffn_sh, h)), (p + "ffn_gate_exps.weight", te, (h, dims.ffn, dims.n_expert)),
+                 (p + "ffn_up_exps.weight", te, (h, dims.ffn, dims.n_expert)), (p + "ffn_down_exps.weight", te, (dims.ffn, h, dims.n_expert))]
+    return spec
+
+
+def tensor_nbytes(ggml_type: int, shape) -> int:
+    n = row_bytes(ggml_type, shape[0])
+    for s in shape[1:]:
+        n *= s
+    return n
