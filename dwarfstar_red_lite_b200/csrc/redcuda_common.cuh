@@ -25,6 +25,7 @@ extern std::atomic<uint64_t> g_launches;
 // launching stream (not usable while a stream is being captured into a graph).
 void prof_begin(const char *tag, cudaStream_t s);
 void prof_end(cudaStream_t s);
+bool prof_active();
 
 // Fails (with a message) unless a CUDA device is usable: the library has no CPU path.
 int require_device();

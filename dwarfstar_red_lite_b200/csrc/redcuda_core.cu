@@ -35,6 +35,7 @@ void prof_begin(const char *tag, cudaStream_t s) {
     std::lock_guard<std::mutex> lk(g_prof_mu);
     g_prof.push_back(r);
 }
+bool prof_active() { return g_prof_on; }
 void prof_end(cudaStream_t s) {
     if (!g_prof_on) return;
     std::lock_guard<std::mutex> lk(g_prof_mu);

@@ -82,11 +82,11 @@ __device__ __forceinline__ float from_kv(__half v) { return __half2float(v); }
 template <typename KV>
 __global__ void k_attn_prep(const float *__restrict__ qg, const float *__restrict__ kraw, const float *__restrict__ vraw,
                             const float *__restrict__ qn, const float *__restrict__ kn, uint32_t n_head, uint32_t n_kv, uint32_t hd,
-                            uint32_t rope_dims, float freq_base, float eps, uint32_t pos, float *__restrict__ query, float *__restrict__ gate,
+                            uint32_t rope_dims, float freq_base, float eps, const uint32_t *__restrict__ pos_p, float *__restrict__ query, float *__restrict__ gate,
                             KV *__restrict__ kcache, KV *__restrict__ vcache) {
     extern __shared__ float sh[];
     __shared__ double red[32];
-    const uint32_t b = blockIdx.x, tid = threadIdx.x;
+    const uint32_t b = blockIdx.x, tid = threadIdx.x, pos = *pos_p;      // the position lives in device memory: a captured graph replays for every token
     if (b >= n_head + n_kv) {      // value head: plain append
         const uint32_t kh = b - n_head - n_kv;
         vcache[((size_t)pos * n_kv + kh) * hd + tid] = to_kv<KV>(vraw[(size_t)kh * hd + tid]);
@@ -119,12 +119,14 @@ __global__ void k_attn_prep(const float *__restrict__ qg, const float *__restric
 // a lane VPL = head_dim/32 consecutive dimensions; online softmax per head. Partials: m, l and the accumulator.
 template <typename KV, int VPL, int G>
 __global__ void __launch_bounds__(256) k_attn_decode(const float *__restrict__ query, const KV *__restrict__ kcache, const KV *__restrict__ vcache,
-                                                     uint32_t n_kv, uint32_t seq_len, uint32_t nsplit, float scale,
+                                                     uint32_t n_kv, const uint32_t *__restrict__ pos_p, uint32_t nsplit, float scale,
                                                      float *__restrict__ part_m, float *__restrict__ part_l, float *__restrict__ part_acc) {
     extern __shared__ float sm[];            // [8][G][hd] accumulators, then [8][G] m, [8][G] l
     constexpr uint32_t hd = VPL * 32u;
     const uint32_t kvh = blockIdx.x, split = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint32_t per = (seq_len + nsplit - 1u) / nsplit, p_begin = split * per, p_end = min(seq_len, p_begin + per);
+    const uint32_t seq_len = *pos_p + 1u;
+    // slices of at least 32 positions; at short sequences the trailing blocks find an empty slice and report m = -inf
+    const uint32_t per = max((seq_len + nsplit - 1u) / nsplit, 32u), p_begin = min(split * per, seq_len), p_end = min(seq_len, p_begin + per);
     float q[G][VPL], acc[G][VPL], m[G], l[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -202,7 +204,11 @@ __global__ void k_attn_merge(const float *__restrict__ part_m, const float *__re
 }
 
 // argmax of n floats, ties to the lowest index; one block of 1024
-__global__ void __launch_bounds__(1024) k_argmax(const float *__restrict__ v, uint32_t n, uint32_t *__restrict__ out) {
+__global__ void k_advance(uint32_t *pos) { if (threadIdx.x == 0 && blockIdx.x == 0) *pos += 1u; }
+
+// gen_log / gen_count (optional): the chosen id is also appended to gen_log[*gen_count]
+__global__ void __launch_bounds__(1024) k_argmax(const float *__restrict__ v, uint32_t n, uint32_t *__restrict__ out, uint32_t *__restrict__ gen_log,
+                                                 uint32_t *__restrict__ gen_count) {
     __shared__ float bv[32];
     __shared__ uint32_t bi[32];
     float best = -INFINITY; uint32_t idx = 0xffffffffu;
@@ -216,6 +222,7 @@ __global__ void __launch_bounds__(1024) k_argmax(const float *__restrict__ v, ui
     if (threadIdx.x == 0) {
         for (int w = 1; w < 32; ++w) if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
         *out = idx;
+        if (gen_log) { gen_log[*gen_count] = idx; *gen_count += 1u; }
     }
 }
 
@@ -252,7 +259,10 @@ struct rl_engine {
     float *dn_qk = nullptr, *dn_v = nullptr, *dn_beta = nullptr, *dn_gate = nullptr, *dn_core = nullptr;
     float *qg = nullptr, *kraw = nullptr, *vraw = nullptr, *query = nullptr, *gate = nullptr, *gated = nullptr, *part_m = nullptr, *part_l = nullptr, *part_acc = nullptr;
     float *embed_d = nullptr, *layer_out_d = nullptr, *final_norm_d = nullptr, *logits_d = nullptr;
-    uint32_t *router_ids_d = nullptr, *token_d = nullptr, *gen_tokens_d = nullptr;
+    uint32_t *router_ids_d = nullptr, *token_d = nullptr, *gen_tokens_d = nullptr, *pos_d = nullptr, *gen_count_d = nullptr;
+    cudaGraphExec_t graph_greedy = nullptr;      // one greedy token (step + LM head + argmax), captured after the first eager token
+    bool graph_failed = false;
+    uint64_t graph_launches = 0;
     uint32_t max_split = 64;
     // host mirrors
     std::vector<float> embed_h, layer_out_h, final_norm_h;
@@ -281,15 +291,15 @@ static int eng_gemv(rl_engine *e, const DMat *mats, float *const *outs, uint32_t
 template <typename KV>
 static int eng_attention(rl_engine *e, const EngLayer &L, char *error, size_t cap) {
     const rl_engine_info &in = e->info;
-    const uint32_t hd = in.head_dim, nq = in.n_head, nkv = in.n_head_kv, G = nq / nkv, pos = e->position, seq_len = pos + 1u;
+    const uint32_t hd = in.head_dim, nq = in.n_head, nkv = in.n_head_kv, G = nq / nkv;
     const size_t kv_layer = (size_t)in.context * nkv * hd;
     KV *kc = (KV *)e->kcache + kv_layer * L.aidx, *vc = (KV *)e->vcache + kv_layer * L.aidx;
     cudaStream_t s = e->stream;
     prof_begin("attn_prep", s);
     k_attn_prep<KV><<<nq + 2u * nkv, hd, hd * sizeof(float), s>>>(e->qg, e->kraw, e->vraw, L.q_norm, L.k_norm, nq, nkv, hd, in.rope_dims, in.rope_freq_base,
-                                                                 in.rms_eps, pos, e->query, e->gate, kc, vc);
+                                                                 in.rms_eps, e->pos_d, e->query, e->gate, kc, vc);
     prof_end(s);
-    uint32_t nsplit = (seq_len + 63u) / 64u;
+    uint32_t nsplit = (in.context + 31u) / 32u;                 // fixed per engine (graph replay): enough slices for a full context
     nsplit = nsplit < 1u ? 1u : nsplit > e->max_split ? e->max_split : nsplit;
     const float scale = (float)(1.0 / sqrt((double)hd));
     const size_t smem = (size_t)(8u * G * hd + 16u * G) * sizeof(float);
@@ -297,7 +307,7 @@ static int eng_attention(rl_engine *e, const EngLayer &L, char *error, size_t ca
     prof_begin("attn_decode", s);
 #define ENG_ATTN(VPL_, G_) do { \
         if (smem > 48u * 1024u) ENG_CUDA(cudaFuncSetAttribute(k_attn_decode<KV, VPL_, G_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        k_attn_decode<KV, VPL_, G_><<<grid, 256, smem, s>>>(e->query, kc, vc, nkv, seq_len, nsplit, scale, e->part_m, e->part_l, e->part_acc); } while (0)
+        k_attn_decode<KV, VPL_, G_><<<grid, 256, smem, s>>>(e->query, kc, vc, nkv, e->pos_d, nsplit, scale, e->part_m, e->part_l, e->part_acc); } while (0)
     if (hd == 256u && G == 8u) ENG_ATTN(8, 8);
     else if (hd == 128u && G == 8u) ENG_ATTN(4, 8);
     else if (hd == 128u && G == 4u) ENG_ATTN(4, 4);
@@ -366,8 +376,19 @@ static int eng_step_device(rl_engine *e, bool want_logits, char *error, size_t c
         float *o1[1] = {e->logits_d};
         ENG_RC(eng_gemv(e, &e->output, o1, 1, e->final_norm_d, "lm_head_gemv"));
     }
+    k_advance<<<1, 32, 0, s>>>(e->pos_d);
+    g_launches.fetch_add(1);
     ENG_CUDA(cudaGetLastError());
     e->position++;
+    return 1;
+}
+
+static int eng_set_position(rl_engine *e, uint32_t position, char *error, size_t cap) {
+    ENG_CUDA(cudaStreamSynchronize(e->stream));
+    e->token_pin[2] = position;
+    ENG_CUDA(cudaMemcpyAsync(e->pos_d, e->token_pin + 2, 4, cudaMemcpyHostToDevice, e->stream));
+    ENG_CUDA(cudaStreamSynchronize(e->stream));
+    e->position = position;
     return 1;
 }
 
@@ -386,8 +407,7 @@ static int eng_copy_mirrors(rl_engine *e, float *logits, char *error, size_t cap
 static int eng_reset_state(rl_engine *e, char *error, size_t cap) {
     ENG_CUDA(cudaMemsetAsync(e->state.p, 0, e->state.bytes, e->stream));
     ENG_CUDA(cudaStreamSynchronize(e->stream));
-    e->position = 0;
-    return 1;
+    return eng_set_position(e, 0u, error, cap);
 }
 
 // upload one dense GGUF matrix [ncols = shape[0], nrows = shape[1]] into the arena at *off
@@ -556,6 +576,7 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
     e->query = (float *)(B + o_qu); e->gate = (float *)(B + o_ga); e->gated = (float *)(B + o_gd); e->part_m = (float *)(B + o_pm); e->part_l = (float *)(B + o_pl);
     e->part_acc = (float *)(B + o_pa); e->embed_d = (float *)(B + o_em); e->layer_out_d = (float *)(B + o_lo); e->final_norm_d = (float *)(B + o_fn);
     e->logits_d = (float *)(B + o_lg); e->router_ids_d = (uint32_t *)(B + o_ri); e->token_d = (uint32_t *)(B + o_tk); e->gen_tokens_d = (uint32_t *)(B + o_gt);
+    e->pos_d = e->token_d + 2; e->gen_count_d = e->token_d + 3;
     e->embed_h.assign(in.hidden, 0.f); e->layer_out_h.assign((size_t)in.n_layer * in.hidden, 0.f); e->final_norm_h.assign(in.hidden, 0.f);
     e->router_ids_h.assign((size_t)in.n_layer * RL_ENGINE_MAX_TOPK, 0u);
     ENG_CUDA(cudaMallocHost((void **)&e->token_pin, 64));
@@ -587,6 +608,7 @@ rl_engine *rl_engine_open(const char *model_path, const rl_engine_config *cfg, c
 void rl_engine_close(rl_engine *e) {
     if (!e) return;
     if (e->stream) cudaStreamSynchronize(e->stream);
+    if (e->graph_greedy) cudaGraphExecDestroy(e->graph_greedy);
     for (auto &L : e->layers) if (L.moe) redcuda_moe_destroy(L.moe);
     if (e->token_pin) cudaFreeHost(e->token_pin);
     if (e->stream) cudaStreamDestroy(e->stream);
@@ -605,8 +627,7 @@ uint32_t rl_engine_position(const rl_engine *e, rl_engine_backend backend) { ret
 int rl_engine_bench_set_position(rl_engine *e, rl_engine_backend backend, uint32_t position, char *error, size_t cap) {
     if (!e || backend != RL_BACKEND_GPU) { eng_err(error, cap, "backend not enabled"); return 0; }
     if (position >= e->info.context) { eng_err(error, cap, "position beyond the context"); return 0; }
-    e->position = position;
-    return 1;
+    return eng_set_position(e, position, error, cap);
 }
 
 int rl_engine_step(rl_engine *e, rl_engine_backend backend, uint32_t token, float *logits, rl_engine_step_stats *stats, char *error, size_t cap) {
@@ -654,11 +675,43 @@ int rl_engine_generate_greedy(rl_engine *e, uint32_t token, uint32_t n_new, uint
     ENG_CUDA(cudaSetDevice(e->device));
     e->token_pin[0] = token;
     ENG_CUDA(cudaMemcpyAsync(e->token_d, e->token_pin, 4, cudaMemcpyHostToDevice, e->stream));
-    for (uint32_t i = 0; i < n_new; ++i) {
+    if (e->position + n_new > e->info.context) { eng_err(error, cap, "not enough context left for the requested tokens"); return 0; }
+    ENG_CUDA(cudaMemsetAsync(e->gen_count_d, 0, 4, e->stream));
+    auto one_token = [&]() -> int {
         if (!eng_step_device(e, true, error, cap)) return 0;
-        k_argmax<<<1, 1024, 0, e->stream>>>(e->logits_d, e->info.vocab, e->token_d);
+        k_argmax<<<1, 1024, 0, e->stream>>>(e->logits_d, e->info.vocab, e->token_d, e->gen_tokens_d, e->gen_count_d);
         g_launches.fetch_add(1);
-        ENG_CUDA(cudaMemcpyAsync(e->gen_tokens_d + i, e->token_d, 4, cudaMemcpyDeviceToDevice, e->stream));
+        return 1;
+    };
+    for (uint32_t i = 0; i < n_new; ++i) {
+        // The first token of an engine runs eagerly (it also sets every kernel attribute); then one token is captured
+        // into a CUDA graph — position, token and output slot are read from device memory, so the same graph serves
+        // every later token. RL_CUDA_GRAPH=0 keeps everything eager.
+        static const bool want_graph = !(getenv("RL_CUDA_GRAPH") && atoi(getenv("RL_CUDA_GRAPH")) == 0);
+        if (e->graph_greedy) {
+            const uint64_t per_token = e->graph_launches;
+            ENG_CUDA(cudaGraphLaunch(e->graph_greedy, e->stream));
+            g_launches.fetch_add(per_token);
+            e->position++;
+            continue;
+        }
+        if (i >= 1u && want_graph && !e->graph_failed) {
+            cudaGraph_t g = nullptr;
+            const uint64_t before = g_launches.load();
+            const uint32_t pos_before = e->position;
+            bool ok = cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+            if (ok) {
+                const int rc_ = one_token();
+                const cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+                ok = rc_ && ce == cudaSuccess && g;
+                e->position = pos_before;                     // capturing ran nothing
+            }
+            if (ok) ok = cudaGraphInstantiate(&e->graph_greedy, g, 0) == cudaSuccess;
+            if (g) cudaGraphDestroy(g);
+            if (!ok) { cudaGetLastError(); e->graph_failed = true; e->graph_greedy = nullptr; g_launches.store(before); }
+            else { e->graph_launches = g_launches.load() - before; g_launches.store(before); --i; continue; }
+        }
+        if (!one_token()) return 0;
     }
     ENG_CUDA(cudaMemcpyAsync(out_tokens, e->gen_tokens_d, (size_t)n_new * 4u, cudaMemcpyDeviceToHost, e->stream));
     if (!eng_copy_mirrors(e, nullptr, error, cap)) return 0;

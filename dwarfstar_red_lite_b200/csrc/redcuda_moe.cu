@@ -201,6 +201,8 @@ struct redcuda_moe {
     uint32_t max_pairs = 0;
     bool use_mma = false;      // IQ2_XXS experts (and the Q6_K shared expert of a batch) on the integer tensor-core path
     cudaStream_t stream = nullptr;
+    cudaStream_t side = nullptr;                    // the shared expert runs here, beside the routed experts
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -339,12 +341,23 @@ static int moe_forward_on(redcuda_moe *m, uint32_t ntok, const float *x, const f
     // one quantisation of the token activations serves the routed gate/up and the shared gate/up
     const bool xq = moe_experts_mma(m) || moe_shared_mma(m, ntok);
     if (xq && !launch_quant_act(x, m->d.hidden, ntok, m->d.hidden, m->xq_x, m->sx_x, s)) return 0;
-    if (!moe_gemv_pre(m, ntok, x, logits_in == nullptr, true, xq, s)) return 0;
+    // The shared expert needs nothing from the router, so for a batch it runs on a side stream next to the routed
+    // experts and joins before the combine (both edges are events, so the fork is kept when the caller captures a graph).
+    // With profiling on, everything stays on one stream so that per-kernel times are not overlapped.
+    const bool fork = ntok >= 3u && !prof_active();
+    if (fork) {
+        RC_CUDA(cudaEventRecord(m->ev_fork, s));
+        RC_CUDA(cudaStreamWaitEvent(m->side, m->ev_fork, 0));
+        if (!moe_gemv_pre(m, ntok, x, false, true, xq, m->side) || !moe_shared_down(m, ntok, m->side)) return 0;
+        RC_CUDA(cudaEventRecord(m->ev_join, m->side));
+        if (!moe_gemv_pre(m, ntok, x, logits_in == nullptr, false, xq, s)) return 0;
+    } else if (!moe_gemv_pre(m, ntok, x, logits_in == nullptr, true, xq, s)) return 0;
     if (!launch_route(logits_in ? logits_in : m->logits, ntok, m->d.n_expert, k, m->ids, m->wk, nullptr, s)) return 0;
     if (!moe_group(m, m->ids, npairs, ntok == 1u, s)) return 0;
     if (!moe_launch_experts(m, true, npairs, ntok == 1u, x, m->d.hidden, k, xq, m->act, m->d.ffn, s)) return 0;
-    if (!moe_shared_down(m, ntok, s)) return 0;
+    if (!fork && !moe_shared_down(m, ntok, s)) return 0;
     if (!moe_launch_experts(m, false, npairs, ntok == 1u, m->act, m->d.ffn, 1u, false, m->tmp, m->d.hidden, s)) return 0;
+    if (fork) RC_CUDA(cudaStreamWaitEvent(s, m->ev_join, 0));
     return moe_combine(m, ntok, m->tmp, m->wk, k, true, resid, out, s);
 }
 
@@ -370,7 +383,10 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
     m->d = d;
     cudaGetDevice(&m->device);
     auto bail = [&]() -> redcuda_moe * { redcuda_moe_destroy(m); return nullptr; };
-    if (cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess) { set_error("moe create: stream creation failed"); return bail(); }
+    if (cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess || cudaStreamCreateWithFlags(&m->side, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming) != cudaSuccess || cudaEventCreateWithFlags(&m->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+        set_error("moe create: stream / event creation failed"); return bail();
+    }
 
     m->gu_bytes = rc_matrix_bytes(d.type_gu, d.ffn, d.hidden);
     m->down_bytes = rc_matrix_bytes(d.type_down, d.hidden, d.ffn);
@@ -451,6 +467,9 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
 void redcuda_moe_destroy(redcuda_moe *m) {
     if (!m) return;
     if (m->stream) { cudaStreamSynchronize(m->stream); cudaStreamDestroy(m->stream); }
+    if (m->side) { cudaStreamSynchronize(m->side); cudaStreamDestroy(m->side); }
+    if (m->ev_fork) cudaEventDestroy(m->ev_fork);
+    if (m->ev_join) cudaEventDestroy(m->ev_join);
     delete m;
 }
 

@@ -18,22 +18,27 @@
 // current 32-group, i.e. MMA k-slots {4t..4t+3, 16+4t..16+4t+3} stand for columns 8t..8t+7 of the group; the B
 // fragment of a lane is then simply the 8 consecutive activation digits at 32*group + 8t of column g.
 //
-// Weights are streamed with cp.async (16 B per lane, fully coalesced: a warp copies whole 128-byte row segments)
-// into per-warp double-buffered staging, rows padded to 144 B so that the 8-byte operand reads are conflict free.
-// Both lookup tables are replicated 16x in shared memory (entry stride 128 B, replica = lane%16) for the same reason.
+// Weights are streamed with cp.async (16 B per lane; a warp copies the 64-byte block segments of its 16 or 32 rows) into
+// per-warp double-buffered staging, rows padded to 80 B so that the 8-byte operand reads are conflict free. Activation
+// digits are read straight from global memory (a few KB per work item, L1-resident).
+// Both lookup tables are replicated in shared memory with an entry stride of 128 B (magnitudes: 8 copies of 8 B, replica =
+// lane%8, at worst a two-way conflict between the halves of a 16-lane phase; signs: 8 copies of 16 B holding the byte mask and its +1 carry term, replica = lane%8) for the same reason.
 #include "redcuda_common.cuh"
 #include "redcuda_kernels.cuh"
 #include "redcuda_moe_mma.cuh"
 
+#include <stdlib.h>
+
 namespace rc {
 
 __device__ __align__(16) uint2 d_lut_grid[256];   // codebook magnitudes, 8 bytes per entry
-__device__ __align__(16) uint2 d_lut_sign[128];   // 0xFF in every byte whose weight is negative (parity bit included)
+__device__ __align__(16) uint4 d_lut_sign[128];   // x,y: 0xFF in every byte whose weight is negative (parity bit included); z,w: 0x01 there
 static const uint2 *g_lut_grid_ptr[64] = {nullptr};
-static const uint2 *g_lut_sign_ptr[64] = {nullptr};
+static const uint4 *g_lut_sign_ptr[64] = {nullptr};
 
 int mma_set_luts(const uint8_t *iq2_grid_host) {
-    uint2 hg[256], hs[128];
+    uint2 hg[256];
+    uint4 hs[128];
     for (int e = 0; e < 256; ++e) {
         uint32_t lo = 0, hi = 0;
         for (int j = 0; j < 4; ++j) { lo |= (uint32_t)iq2_grid_host[e * 8 + j] << (8 * j); hi |= (uint32_t)iq2_grid_host[e * 8 + 4 + j] << (8 * j); }
@@ -43,7 +48,7 @@ int mma_set_luts(const uint8_t *iq2_grid_host) {
         const uint32_t s8 = rc_sign8(s7);
         uint32_t lo = 0, hi = 0;
         for (int j = 0; j < 4; ++j) { if ((s8 >> j) & 1u) lo |= 0xFFu << (8 * j); if ((s8 >> (j + 4)) & 1u) hi |= 0xFFu << (8 * j); }
-        hs[s7] = make_uint2(lo, hi);
+        hs[s7] = make_uint4(lo, hi, lo & 0x01010101u, hi & 0x01010101u);
     }
     int dev = 0;
     RC_CUDA(cudaGetDevice(&dev));
@@ -53,7 +58,7 @@ int mma_set_luts(const uint8_t *iq2_grid_host) {
     RC_CUDA(cudaGetSymbolAddress(&pg, d_lut_grid));
     RC_CUDA(cudaGetSymbolAddress(&ps, d_lut_sign));
     g_lut_grid_ptr[dev & 63] = (const uint2 *)pg;
-    g_lut_sign_ptr[dev & 63] = (const uint2 *)ps;
+    g_lut_sign_ptr[dev & 63] = (const uint4 *)ps;
     return 1;
 }
 
@@ -115,100 +120,114 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
 __device__ __forceinline__ void mma_s8_k32(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
                  : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
 // shared-memory geometry
-#define MMA_ROW_PITCH 144u                 // staged row segment: 128 B of qs (two blocks) + 16 B pad
-#define MMA_STAGES 2u
-#define MMA_CHUNK_COLS 512u                // columns per staged unit (two 256-blocks)
-__host__ __device__ __forceinline__ uint32_t mma_b_pitch(uint32_t ncols) { return ncols + 32u; }   // == 32 (mod 128)
+#define MMA_ROW_PITCH 80u                  // staged row segment: 64 B of qs (one 256-block) + 16 B pad (8-byte reads of 8 rows hit 8 bank pairs)
+#define MMA_STAGES 3u                      // units in flight per warp: two ahead of the one being multiplied (HBM latency ~ one unit of work)
+#define MMA_CHUNK_COLS 256u                // columns per staged unit (one block)
+#ifndef MMA_MINB
+#define MMA_MINB 2                         // blocks per SM the register allocation aims at
+#endif
+#ifndef MMA_KG_UNROLL
+#define MMA_KG_UNROLL 2                    // 32-column groups in flight per warp
+#endif
+#define RC_PRAGMA_(x) _Pragma(#x)
+#define RC_UNROLL(n) RC_PRAGMA_(unroll n)
 
-// One warp: 16 rows x one 512-column chunk of `NMAT` matrices against NTILE*8 activation columns. Each of the two
-// 256-blocks of the chunk is closed inside (integer accumulation over its 8 groups, then one fp32 scaling), so only
-// the fp32 accumulators out[m][tile][4] live across calls.
+// One warp: 16 rows x one 256-column block of `NMAT` matrices against the first `ntiles` of NTILE 8-column tiles.
+// Integer accumulation over the 8 groups of the block, then one fp32 scaling by d/8 into out[m][tile][4].
+// Bs: activation digits of the work item in shared memory, column-major with pitch bpitch (== 32 mod 128: the 8-byte
+// fragment reads of the 8 columns of a tile fall into 8 different bank groups).
 template <int NMAT, int NTILE>
-__device__ __forceinline__ void mma_unit(const uint8_t *stage, const float (&dsc)[NMAT][2][2], const int8_t *Bs, uint32_t bpitch, uint32_t kbase,
-                                         const uint8_t *lutg, const uint8_t *luts, uint32_t lane, float (&out)[NMAT][NTILE][4]) {
-    const uint32_t g = lane >> 2, t = lane & 3u, rep8 = (lane & 15u) * 8u;
+__device__ __forceinline__ void mma_unit(const uint8_t *stage, const float (&dsc)[NMAT][2], const int8_t *Bs, uint32_t bpitch, uint32_t kbase,
+                                         const uint8_t *lutg, const uint8_t *luts, uint32_t lane, uint32_t ntiles, float (&out)[NMAT][NTILE][4]) {
+    const uint32_t g = lane >> 2, t = lane & 3u, rep8 = (lane & 7u) * 8u, rep16 = (lane & 7u) * 16u;
     const uint32_t sel = 0x4440u + t, sh7 = 7u * t;
+    int blk[NMAT][NTILE][4];
 #pragma unroll
-    for (int b = 0; b < 2; ++b) {
-        int blk[NMAT][NTILE][4];
+    for (int m = 0; m < NMAT; ++m)
 #pragma unroll
-        for (int m = 0; m < NMAT; ++m)
+        for (int n = 0; n < NTILE; ++n) { blk[m][n][0] = blk[m][n][1] = blk[m][n][2] = blk[m][n][3] = 0; }
+    RC_UNROLL(MMA_KG_UNROLL)
+    for (int kg = 0; kg < 8; ++kg) {
+        uint32_t a[NMAT][4];
+        int sc[NMAT][2];
 #pragma unroll
-            for (int n = 0; n < NTILE; ++n) { blk[m][n][0] = blk[m][n][1] = blk[m][n][2] = blk[m][n][3] = 0; }
-#pragma unroll 2
-        for (int kg = 0; kg < 8; ++kg) {
-            const uint32_t goff = (uint32_t)(b * 8 + kg) * 8u;
-            uint32_t a[NMAT][4];
-            int sc[NMAT][2];
+        for (int m = 0; m < NMAT; ++m) {
 #pragma unroll
-            for (int m = 0; m < NMAT; ++m) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint2 q = *reinterpret_cast<const uint2 *>(stage + (uint32_t)(m * 16 + h * 8 + g) * MMA_ROW_PITCH + goff);
-                    const uint32_t gi = __byte_perm(q.x, 0u, sel);
-                    const uint32_t s7 = (q.y >> sh7) & 127u;
-                    const uint2 P = *reinterpret_cast<const uint2 *>(lutg + gi * 128u + rep8);
-                    const uint2 M = *reinterpret_cast<const uint2 *>(luts + s7 * 128u + rep8);
-                    a[m][h] = (P.x ^ M.x) + (M.x & 0x01010101u);         // bytes: +g or -g (no carry between bytes: g >= 1)
-                    a[m][2 + h] = (P.y ^ M.y) + (M.y & 0x01010101u);
-                    sc[m][h] = (int)(2u * (q.y >> 28) + 1u);
-                }
-            }
-#pragma unroll
-            for (int n = 0; n < NTILE; ++n) {
-                const uint2 bf = *reinterpret_cast<const uint2 *>(Bs + (uint32_t)(n * 8 + g) * bpitch + kbase + (uint32_t)(b * 8 + kg) * 32u + 8u * t);
-#pragma unroll
-                for (int m = 0; m < NMAT; ++m) {
-                    int d[4];
-                    mma_s8_k32(d, a[m][0], a[m][1], a[m][2], a[m][3], bf.x, bf.y);
-                    blk[m][n][0] += sc[m][0] * d[0]; blk[m][n][1] += sc[m][0] * d[1];
-                    blk[m][n][2] += sc[m][1] * d[2]; blk[m][n][3] += sc[m][1] * d[3];
-                }
+            for (int h = 0; h < 2; ++h) {
+                const uint2 q = *reinterpret_cast<const uint2 *>(stage + (uint32_t)(m * 16 + h * 8 + g) * MMA_ROW_PITCH + (uint32_t)kg * 8u);
+                const uint32_t gi = __byte_perm(q.x, 0u, sel);
+                const uint32_t s7 = (q.y >> sh7) & 127u;
+                const uint2 P = *reinterpret_cast<const uint2 *>(lutg + gi * 64u + rep8);
+                const uint4 M = *reinterpret_cast<const uint4 *>(luts + s7 * 128u + rep16);
+                a[m][h] = (P.x ^ M.x) + M.z;         // bytes: +g, or ~g + 1 = -g (no carry between bytes: g >= 1)
+                a[m][2 + h] = (P.y ^ M.y) + M.w;
+                sc[m][h] = (int)(2u * (q.y >> 28) + 1u);
             }
         }
 #pragma unroll
-        for (int m = 0; m < NMAT; ++m)
+        for (int n = 0; n < NTILE; ++n) {
+            if ((uint32_t)n >= ntiles) break;        // column tiles beyond the item's tokens hold zeros: skip them
+            const uint2 bf = *reinterpret_cast<const uint2 *>(Bs + (uint32_t)(n * 8 + g) * bpitch + kbase + (uint32_t)kg * 32u + 8u * t);
 #pragma unroll
-            for (int n = 0; n < NTILE; ++n) {
-                out[m][n][0] += dsc[m][b][0] * (float)blk[m][n][0]; out[m][n][1] += dsc[m][b][0] * (float)blk[m][n][1];
-                out[m][n][2] += dsc[m][b][1] * (float)blk[m][n][2]; out[m][n][3] += dsc[m][b][1] * (float)blk[m][n][3];
+            for (int m = 0; m < NMAT; ++m) {
+                int d[4];
+                mma_s8_k32(d, a[m][0], a[m][1], a[m][2], a[m][3], bf.x, bf.y);
+                blk[m][n][0] += sc[m][0] * d[0]; blk[m][n][1] += sc[m][0] * d[1];
+                blk[m][n][2] += sc[m][1] * d[2]; blk[m][n][3] += sc[m][1] * d[3];
             }
+        }
     }
+#pragma unroll
+    for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+        for (int n = 0; n < NTILE; ++n) {
+            if ((uint32_t)n >= ntiles) break;
+            out[m][n][0] += dsc[m][0] * (float)blk[m][n][0]; out[m][n][1] += dsc[m][0] * (float)blk[m][n][1];
+            out[m][n][2] += dsc[m][1] * (float)blk[m][n][2]; out[m][n][3] += dsc[m][1] * (float)blk[m][n][3];
+        }
 }
 
-// Block = 8 warps = R row tiles x S column splits (R*S == 8). Warp (r, ks) works on `tiles_per_warp` 16-row tiles
-// and on the 512-column chunks c with c % S == ks. grid = (row-tile groups, experts that received a pair).
+// Block = 8 warps = R row tiles x S column splits (R*S == 8). The NTILE == 1 instance (work items of one or two pairs:
+// four fifths of a Zipf-routed batch, and all of single-token decode) fits two blocks per SM (<= 128 registers, ~105 KB
+// shared memory), so that one block's table fill, first weight load and epilogue overlap the other's MMA loop.
+// item_class: 0 = take every item, 1 = only items of at most 2 pairs, 2 = only larger items (a batch is served by one
+// NTILE == 1 launch for the small items and one NTILE == 3 launch for the rest).
+// Warp (r, ks) works on `tiles_per_warp` 16-row tiles and on the 256-column blocks c with c % S == ks.
+// grid = (row-tile groups, work items); one work item = up to TOK pairs of one expert (k_group_pairs cuts every
+// expert's pairs into such items, so that all blocks carry the same amount of work whatever the routing skew).
 template <int NMAT, int NTILE>
-__global__ void __launch_bounds__(256, 1) k_moe_mma(const __grid_constant__ MmaArgs A) {
+__global__ void __launch_bounds__(256, NTILE == 1 ? MMA_MINB : 1) k_moe_mma(const __grid_constant__ MmaArgs A) {
     extern __shared__ __align__(16) uint8_t smem[];
-    constexpr uint32_t NCOL = NTILE * 8u, TOK = NCOL / 3u;
-    // one work item = up to TOK pairs of one expert (k_group_pairs cuts every expert's pairs into such items, so that
-    // all blocks carry the same amount of work whatever the routing skew)
+    constexpr uint32_t NCOL = NTILE * 8u;
     if (blockIdx.y >= *A.n_items) return;
     const uint32_t u = A.item_u[blockIdx.y], p0 = A.item_p0[blockIdx.y];
-    const uint32_t e = A.uexp[u] - A.expert_begin, pe = A.ustart[u + 1u];
+    const uint32_t e = A.uexp[u] - A.expert_begin, pe = A.ustart[u + 1u], nt = min(A.item_tok, pe - p0);
+    if ((A.item_class == 1u && nt > 2u) || (A.item_class == 2u && nt <= 2u)) return;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
     const uint32_t S = A.S, R = 8u / S, r = warp / S, ks = warp % S;
-    const uint32_t bpr = A.ncols >> 8, nchunks = A.ncols / MMA_CHUNK_COLS, bpitch = mma_b_pitch(A.ncols);
-    // carve shared memory
-    uint8_t *lutg = smem;                                   // 256 x 128 B
-    uint8_t *luts = lutg + 256u * 128u;                     // 128 x 128 B
-    int8_t *Bs = reinterpret_cast<int8_t *>(luts + 128u * 128u);                       // NCOL x bpitch
-    float *sxs = reinterpret_cast<float *>(Bs + (size_t)NCOL * bpitch);                // TOK (+pad) floats
-    uint8_t *stage0 = reinterpret_cast<uint8_t *>(sxs + 16);                           // 8 warps x STAGES x NMAT*16 rows x pitch
-    const uint32_t stage_bytes = NMAT * 16u * MMA_ROW_PITCH;
-    float *scratch0 = reinterpret_cast<float *>(stage0 + 8u * MMA_STAGES * stage_bytes);   // 8 warps x NMAT x 16 x NCOL floats
-    uint8_t *my_stage = stage0 + warp * MMA_STAGES * stage_bytes;
-    float *my_scratch = scratch0 + (size_t)warp * NMAT * 16u * NCOL;
+    const uint32_t bpr = A.ncols >> 8, nchunks = bpr;
+    // carve shared memory: tables, per-warp staging, per-warp epilogue scratch (aliased onto the staging when NMAT == 2)
+    uint8_t *lutg = smem;                                   // 256 x 64 B
+    uint8_t *luts = lutg + 256u * 64u;                      // 128 x 128 B
+    uint8_t *stage0 = luts + 128u * 128u;                   // 8 warps x STAGES x NMAT*16 rows x pitch
+    constexpr uint32_t stage_bytes = NMAT * 16u * MMA_ROW_PITCH, warp_stage = MMA_STAGES * stage_bytes;
+    constexpr uint32_t scratch_bytes = NMAT * 16u * NCOL * 4u;
+    static_assert(NMAT == 1 || scratch_bytes <= warp_stage, "the epilogue scratch of a gate/up warp must fit its staging area");
+    uint8_t *my_stage = stage0 + warp * warp_stage;
+    uint8_t *scratch_base = NMAT == 2 ? stage0 : stage0 + 8u * warp_stage;
+    const uint32_t bpitch = A.ncols + 32u;
+    int8_t *Bs = reinterpret_cast<int8_t *>(stage0 + 8u * warp_stage + (NMAT == 2 ? 0u : 8u * scratch_bytes));   // NCOL x bpitch
+    constexpr uint32_t scratch_pitch = NMAT == 2 ? warp_stage : scratch_bytes;
+    float *my_scratch = reinterpret_cast<float *>(scratch_base + warp * scratch_pitch);
 
-    for (uint32_t i = tid; i < 256u * 16u; i += 256u) reinterpret_cast<uint2 *>(lutg)[i] = A.lut_grid[i >> 4];
-    for (uint32_t i = tid; i < 128u * 16u; i += 256u) reinterpret_cast<uint2 *>(luts)[i] = A.lut_sign[i >> 4];
+    for (uint32_t i = tid; i < 256u * 8u; i += 256u) reinterpret_cast<uint2 *>(lutg)[i] = A.lut_grid[i >> 3];
+    for (uint32_t i = tid; i < 128u * 8u; i += 256u) reinterpret_cast<uint4 *>(luts)[i] = A.lut_sign[i >> 3];
 
     const uint8_t *w[2] = {A.w0 + (size_t)e * A.mat_bytes, A.w1 ? A.w1 + (size_t)e * A.mat_bytes : nullptr};
     const uint32_t tile_first = (blockIdx.x * R + r) * A.tiles_per_warp;            // in units of 16 rows
@@ -219,105 +238,102 @@ __global__ void __launch_bounds__(256, 1) k_moe_mma(const __grid_constant__ MmaA
     for (uint32_t i = 0; i < A.tiles_per_warp; ++i) if (tile_first + i < ntile_rows) ++my_tiles;
     const uint32_t nunits = my_tiles * my_chunks;
 
-    {
-        const uint32_t nt = min(TOK, pe - p0);
-        // ---- stage the activation digits of pairs [p0, p0 + nt): column = 3 * token + digit
-        {
-            const uint32_t v16 = A.ncols >> 4;
-            for (uint32_t i = tid; i < NCOL * v16; i += 256u) {
-                const uint32_t col = i / v16, k = (i - col * v16) << 4, tk = col / 3u, dg = col - tk * 3u;
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (tk < nt) {
-                    const size_t xr = A.sorted[p0 + tk] / A.x_div;
-                    v = *reinterpret_cast<const uint4 *>(A.xq + (xr * 3u + dg) * A.ncols + k);
-                }
-                *reinterpret_cast<uint4 *>(Bs + (size_t)col * bpitch + k) = v;
-            }
-            if (tid < TOK) sxs[tid] = tid < nt ? A.sx[A.sorted[p0 + tid] / A.x_div] : 0.f;
-        }
-        __syncthreads();
+    const uint32_t ntiles = (3u * nt + 7u) >> 3;
 
-        auto issue = [&](uint32_t unit, uint32_t buf) {
-            const uint32_t ti = unit / my_chunks, c = ks + (unit - ti * my_chunks) * S;
-            const uint32_t row0 = (tile_first + ti) << 4;
-            uint8_t *dst = my_stage + buf * stage_bytes;
+    auto issue = [&](uint32_t unit, uint32_t buf) {
+        const uint32_t ti = unit / my_chunks, c = ks + (unit - ti * my_chunks) * S;
+        const uint32_t row0 = (tile_first + ti) << 4;
+        uint8_t *dst = my_stage + buf * stage_bytes;
 #pragma unroll
-            for (uint32_t i = 0; i < NMAT * 4u; ++i) {
-                const uint32_t p = lane + 32u * i, rr = p >> 3, piece = p & 7u, m = rr >> 4, row = row0 + (rr & 15u);
-                cp_async16(dst + rr * MMA_ROW_PITCH + piece * 16u, w[m] + ((size_t)row * bpr + c * 2u) * 64u + piece * 16u);
-            }
-        };
+        for (uint32_t i = 0; i < NMAT * 2u; ++i) {
+            const uint32_t p = lane + 32u * i, rr = p >> 2, piece = p & 3u, m = rr >> 4, row = row0 + (rr & 15u);
+            cp_async16(dst + rr * MMA_ROW_PITCH + piece * 16u, w[m] + ((size_t)row * bpr + c) * 64u + piece * 16u);
+        }
+    };
 
-        float out[NMAT][NTILE][4];
-        if (nunits) { issue(0u, 0u); }
+    for (uint32_t i = 0; i + 1u < MMA_STAGES; ++i) {     // weights start streaming while the tables and the activations settle
+        if (i < nunits) issue(i, i);
         cp_async_commit();
-        for (uint32_t unit = 0; unit < nunits; ++unit) {
-            const uint32_t ti = unit / my_chunks, ci = unit - ti * my_chunks, c = ks + ci * S;
-            const uint32_t row0 = (tile_first + ti) << 4;
-            if (unit + 1u < nunits) issue(unit + 1u, (unit + 1u) & 1u);
-            cp_async_commit();
-            // block scales d/8 of rows g, g+8 for the two blocks of this chunk (plain loads, 2 B each)
-            float dsc[NMAT][2][2];
+    }
+    {   // activation digits of pairs [p0, p0 + nt): column = 3 * token + digit; only the tiles in use are filled
+        const uint32_t v16 = A.ncols >> 4;
+        for (uint32_t i = tid; i < ntiles * 8u * v16; i += 256u) {
+            const uint32_t col = i / v16, k = (i - col * v16) << 4, tk = col / 3u, dg = col - tk * 3u;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (tk < nt) v = *reinterpret_cast<const uint4 *>(A.xq + ((size_t)(A.sorted[p0 + tk] / A.x_div) * 3u + dg) * A.ncols + k);
+            *reinterpret_cast<uint4 *>(Bs + (size_t)col * bpitch + k) = v;
+        }
+    }
+    __syncthreads();
+
+    float out[NMAT][NTILE][4];
+    for (uint32_t unit = 0; unit < nunits; ++unit) {
+        const uint32_t ti = unit / my_chunks, ci = unit - ti * my_chunks, c = ks + ci * S;
+        const uint32_t row0 = (tile_first + ti) << 4;
+        if (unit + MMA_STAGES - 1u < nunits) issue(unit + MMA_STAGES - 1u, (unit + MMA_STAGES - 1u) % MMA_STAGES);
+        cp_async_commit();
+        float dsc[NMAT][2];              // d/8 of rows g, g+8 for this block (plain loads, 2 B each)
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const size_t bi = (size_t)(row0 + h * 8u + g) * bpr + c;
+                dsc[m][h] = 0.125f * __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short *>(w[m] + A.nb * 64u) + bi)));
+            }
+        if (ci == 0u) {
 #pragma unroll
             for (int m = 0; m < NMAT; ++m)
 #pragma unroll
-                for (int b = 0; b < 2; ++b)
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const size_t bi = (size_t)(row0 + h * 8u + g) * bpr + c * 2u + b;
-                        dsc[m][b][h] = 0.125f * __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short *>(w[m] + A.nb * 64u) + bi)));
-                    }
-            if (ci == 0u) {
-#pragma unroll
-                for (int m = 0; m < NMAT; ++m)
-#pragma unroll
-                    for (int n = 0; n < NTILE; ++n) { out[m][n][0] = out[m][n][1] = out[m][n][2] = out[m][n][3] = 0.f; }
-            }
-            cp_async_wait<1>();
-            __syncwarp();
-            mma_unit<NMAT, NTILE>(my_stage + (unit & 1u) * stage_bytes, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, out);
-            __syncwarp();
-            if (ci + 1u == my_chunks) {
-                // ---- tile finished for this warp: fragments -> scratch[m][row][col]
-#pragma unroll
-                for (int m = 0; m < NMAT; ++m)
-#pragma unroll
-                    for (int n = 0; n < NTILE; ++n) {
-                        float *sp = my_scratch + (size_t)m * 16u * NCOL + n * 8u + 2u * t;
-                        sp[(size_t)g * NCOL] = out[m][n][0]; sp[(size_t)g * NCOL + 1u] = out[m][n][1];
-                        sp[(size_t)(g + 8u) * NCOL] = out[m][n][2]; sp[(size_t)(g + 8u) * NCOL + 1u] = out[m][n][3];
-                    }
-                if (S > 1u) __syncthreads(); else __syncwarp();       // S > 1 implies one tile per warp: every warp gets here once
-                if (ks == 0u) {
-                    for (uint32_t idx = lane; idx < 16u * nt; idx += 32u) {
-                        const uint32_t row = idx & 15u, tk = idx >> 4;
-                        float val[NMAT];
-#pragma unroll
-                        for (int m = 0; m < NMAT; ++m) {
-                            float o0 = 0.f, o1 = 0.f, o2 = 0.f;
-                            for (uint32_t s = 0; s < S; ++s) {
-                                const float *sp = scratch0 + ((size_t)(warp + s) * NMAT + m) * 16u * NCOL + (size_t)row * NCOL + 3u * tk;
-                                o0 += sp[0]; o1 += sp[1]; o2 += sp[2];
-                            }
-                            val[m] = sxs[tk] * (16384.f * o2 + 128.f * o1 + o0);
-                        }
-                        const uint32_t p = A.sorted[p0 + tk];
-                        float v = val[0];
-                        if (NMAT == 2) { const float gte = val[0]; v = (gte / (1.0f + expf(-gte))) * val[NMAT - 1]; }
-                        A.out[(size_t)p * A.out_stride + row0 + row] = v;
-                    }
-                }
-                if (S > 1u) __syncthreads(); else __syncwarp();
-            }
+                for (int n = 0; n < NTILE; ++n) { out[m][n][0] = out[m][n][1] = out[m][n][2] = out[m][n][3] = 0.f; }
         }
-        cp_async_wait<0>();
-        if (S > 1u && nunits == 0u) { __syncthreads(); __syncthreads(); }   // keep barrier counts equal for warps without work
+        cp_async_wait<MMA_STAGES - 1>();
+        __syncwarp();
+        mma_unit<NMAT, NTILE>(my_stage + (unit % MMA_STAGES) * stage_bytes, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        __syncwarp();
+        if (ci + 1u == my_chunks) {
+            // ---- tile finished for this warp: fragments -> scratch[m][row][col]. With NMAT == 2 the scratch is the warp's own
+            // staging area: a gate/up warp has one tile (launcher), so nothing is in flight into it any more.
+            if (NMAT == 2) { cp_async_wait<0>(); __syncwarp(); }
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+                for (int n = 0; n < NTILE; ++n) {
+                    float *sp = my_scratch + (size_t)m * 16u * NCOL + n * 8u + 2u * t;
+                    const bool live = (uint32_t)n < ntiles;
+                    sp[(size_t)g * NCOL] = live ? out[m][n][0] : 0.f; sp[(size_t)g * NCOL + 1u] = live ? out[m][n][1] : 0.f;
+                    sp[(size_t)(g + 8u) * NCOL] = live ? out[m][n][2] : 0.f; sp[(size_t)(g + 8u) * NCOL + 1u] = live ? out[m][n][3] : 0.f;
+                }
+            if (S > 1u) __syncthreads(); else __syncwarp();       // S > 1 implies one tile per warp: every warp gets here once
+            if (ks == 0u) {
+                for (uint32_t idx = lane; idx < 16u * nt; idx += 32u) {
+                    const uint32_t row = idx & 15u, tk = idx >> 4;
+                    const uint32_t p = A.sorted[p0 + tk];
+                    const float sxv = A.sx[p / A.x_div];
+                    float val[NMAT];
+#pragma unroll
+                    for (int m = 0; m < NMAT; ++m) {
+                        float o0 = 0.f, o1 = 0.f, o2 = 0.f;
+                        for (uint32_t s = 0; s < S; ++s) {
+                            const float *sp = reinterpret_cast<const float *>(scratch_base + (warp + s) * scratch_pitch) + (size_t)m * 16u * NCOL + (size_t)row * NCOL + 3u * tk;
+                            o0 += sp[0]; o1 += sp[1]; o2 += sp[2];
+                        }
+                        val[m] = sxv * (16384.f * o2 + 128.f * o1 + o0);
+                    }
+                    float v = val[0];
+                    if (NMAT == 2) { const float gte = val[0]; v = (gte / (1.0f + expf(-gte))) * val[NMAT - 1]; }
+                    A.out[(size_t)p * A.out_stride + row0 + row] = v;
+                }
+            }
+            if (S > 1u) __syncthreads(); else __syncwarp();
+        }
     }
+    cp_async_wait<0>();
+    if (S > 1u && nunits == 0u) { __syncthreads(); __syncthreads(); }   // keep barrier counts equal for warps without work
 }
 
 size_t mma_smem_bytes(uint32_t nmat, uint32_t ntile, uint32_t ncols) {
-    const size_t ncol = ntile * 8u;
-    return 256u * 128u + 128u * 128u + ncol * mma_b_pitch(ncols) + 64u + 8u * MMA_STAGES * nmat * 16u * MMA_ROW_PITCH + 8u * nmat * 16u * ncol * 4u;
+    const size_t stages = 8u * MMA_STAGES * nmat * 16u * MMA_ROW_PITCH;
+    return 256u * 64u + 128u * 128u + stages + (nmat == 2u ? 0u : 8u * 16u * ntile * 8u * 4u) + (size_t)ntile * 8u * (ncols + 32u);
 }
 
 int launch_moe_mma(MmaArgs &A, uint32_t groups, bool few_tokens, cudaStream_t s) {
@@ -326,30 +342,37 @@ int launch_moe_mma(MmaArgs &A, uint32_t groups, bool few_tokens, cudaStream_t s)
     A.lut_grid = g_lut_grid_ptr[dev & 63];
     A.lut_sign = g_lut_sign_ptr[dev & 63];
     RC_REQUIRE(A.lut_grid && A.lut_sign, "IQ2_XXS tensor-core tables not set on device %d: call redcuda_set_codebooks first", dev);
-    RC_REQUIRE(A.ncols % MMA_CHUNK_COLS == 0 && A.nrows % 16u == 0, "moe mma: matrix %ux%u is not a multiple of 16 rows x 512 columns", A.nrows, A.ncols);
+    RC_REQUIRE(A.ncols % MMA_CHUNK_COLS == 0 && A.nrows % 16u == 0, "moe mma: matrix %ux%u is not a multiple of 16 rows x 256 columns", A.nrows, A.ncols);
     const uint32_t nmat = A.w1 ? 2u : 1u, nchunks = A.ncols / MMA_CHUNK_COLS, ntile_rows = A.nrows / 16u;
     // Single-token decode: few row tiles in total, so the wide matrices are also split along the columns (S warps
-    // share a row tile); batches: about four blocks per expert so that the tables and the activation tile of a block
-    // are staged once per 2^17..2^19 weights.
+    // share a row tile); batches: about four blocks per expert for the down projection (one tile per warp for gate/up,
+    // whose epilogue scratch lives in the warp's staging area).
     uint32_t S = 1u, tpw = 1u;
     if (few_tokens) {
-        while (S < 8u && S * 2u <= nchunks && nchunks % (S * 2u) == 0 && (uint64_t)ntile_rows * groups * S < 148u * 8u) S <<= 1;
-    } else {
+        while (S < 8u && S * 2u <= nchunks && nchunks % (S * 2u) == 0 && (uint64_t)ntile_rows * groups * S < 148u * 16u) S <<= 1;
+    } else if (nmat == 1u) {
         while (tpw < 8u && ntile_rows / (8u * tpw * 2u) >= 4u && ntile_rows % (8u * tpw * 2u) == 0) tpw <<= 1;
     }
     const uint32_t R = 8u / S;
     A.S = S; A.tiles_per_warp = tpw;
+    A.item_tok = mma_item_tokens(few_tokens);
     const dim3 grid((ntile_rows + R * tpw - 1u) / (R * tpw), groups);
-    const uint32_t ntile = few_tokens ? 1u : 3u;
-    const size_t smem = mma_smem_bytes(nmat, ntile, A.ncols);
-    RC_REQUIRE(smem <= 227u * 1024u, "moe mma: %zu bytes of shared memory needed for %u columns", smem, A.ncols);
     prof_begin(nmat == 2u ? "moe_gateup" : "moe_down", s);
-#define RC_MMA_LAUNCH(NM, NT) do { \
+#define RC_MMA_LAUNCH(NM, NT, CLS) do { \
+        const size_t smem = mma_smem_bytes(NM, NT, A.ncols); \
+        RC_REQUIRE(smem <= 227u * 1024u, "moe mma: %zu bytes of shared memory needed for %u columns", smem, A.ncols); \
+        A.item_class = CLS; \
         RC_CUDA(cudaFuncSetAttribute(k_moe_mma<NM, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        k_moe_mma<NM, NT><<<grid, 256, smem, s>>>(A); } while (0)
-    if (nmat == 2u) { if (ntile == 1u) RC_MMA_LAUNCH(2, 1); else RC_MMA_LAUNCH(2, 3); }
-    else { if (ntile == 1u) RC_MMA_LAUNCH(1, 1); else RC_MMA_LAUNCH(1, 3); }
+        k_moe_mma<NM, NT><<<grid, 256, smem, s>>>(A); g_launches.fetch_add(1, std::memory_order_relaxed); } while (0)
+    if (few_tokens) { if (nmat == 2u) RC_MMA_LAUNCH(2, 1, 0u); else RC_MMA_LAUNCH(1, 1, 0u); }
+    else {
+        static const bool split = getenv("RC_MMA_SPLIT") && atoi(getenv("RC_MMA_SPLIT")) != 0;   // A/B switch; measured: one launch for all items is faster (no serialised tails)
+        if (split) {      // large items first: they are the long blocks
+            if (nmat == 2u) { RC_MMA_LAUNCH(2, 3, 2u); RC_MMA_LAUNCH(2, 1, 1u); } else { RC_MMA_LAUNCH(1, 3, 2u); RC_MMA_LAUNCH(1, 1, 1u); }
+        } else { if (nmat == 2u) RC_MMA_LAUNCH(2, 3, 0u); else RC_MMA_LAUNCH(1, 3, 0u); }
+    }
 #undef RC_MMA_LAUNCH
+    g_launches.fetch_sub(1, std::memory_order_relaxed);     // RC_LAUNCHED below counts one of them
     prof_end(s);
     RC_LAUNCHED();
     return 1;

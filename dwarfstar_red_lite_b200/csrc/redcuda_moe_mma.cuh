@@ -16,8 +16,8 @@ struct MmaArgs {
     const float *sx;               // activation scale per row
     uint32_t x_div;
     float *out; uint32_t out_stride;                     // result row of pair p = out + p * out_stride
-    const uint2 *lut_grid, *lut_sign;                    // filled by launch_moe_mma
-    uint32_t S, tiles_per_warp;                          // filled by launch_moe_mma
+    const uint2 *lut_grid; const uint4 *lut_sign;        // filled by launch_moe_mma
+    uint32_t S, tiles_per_warp, item_tok, item_class;    // filled by launch_moe_mma
 };
 
 // Builds the magnitude and sign tables of the tensor-core path from the IQ2_XXS codebook (current device).

@@ -9,7 +9,7 @@ import os
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libredcuda.so")
+LIB_PATH = os.environ.get("REDCUDA_LIB") or os.path.join(HERE, "libredcuda.so")    # REDCUDA_LIB: an alternative build (A/B runs)
 
 u8p, f32p, u32p = C.POINTER(C.c_uint8), C.POINTER(C.c_float), C.POINTER(C.c_uint32)
 
