@@ -337,6 +337,150 @@ def run_decode48(args):
     eng.close()
 
 
+def _timed_graph(torch, step_fn, steps, warmup, device_index):
+    """warm up, capture step_fn(stream) into a CUDA graph on a side stream, time `steps` replays with CUDA events"""
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(max(1, warmup)):
+            step_fn(side.cuda_stream)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step_fn(side.cuda_stream)
+        graph.replay()
+        side.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(device_index) as clocks:
+            torch.cuda.synchronize()
+            e0.record(side)
+            for _ in range(steps):
+                graph.replay()
+            e1.record(side)
+            torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps, clocks.summary()
+
+
+def run_moe_b1(args):
+    """BASELINE configs[0]: one routed-MoE FFN layer, batch 1, router computed. A step sweeps `layers` distinct layers
+    (weights from HBM, not L2); value = token-layers per second."""
+    import torch
+    import dwarfstar_red_lite_b200 as rc
+    from dwarfstar_red_lite_b200 import synth, synth_device
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    rc.set_codebooks(device=0)
+    dims, L = synth.MoeDims(), args.layers
+    layers, layer0_host = [], None
+    for l in range(L):
+        tens = synth_device.moe_layer_tensors(1000 + l, dims, dev)
+        layers.append(rc.MoeLayer(device_tensors=tens, dims=dims, max_tokens=1))
+        if l == 0 and not args.no_cpu:
+            layer0_host = host_layer_from_device(tens, dims)
+        del tens
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+    x_d = torch.randn(L, 1, dims.hidden, device=dev, generator=g)
+    out_d = torch.empty_like(x_d)
+    row = dims.hidden * 4
+
+    def step(stream):
+        for l in range(L):
+            layers[l].forward_device(1, x_d.data_ptr() + l * row, out_d.data_ptr() + l * row, stream)
+
+    ms, clocks = _timed_graph(torch, step, args.steps, args.warmup, 0)
+    value = L / (ms * 1e-3)
+    xh, oh = x_d.cpu().numpy(), np.empty((L, 1, dims.hidden), np.float32)
+    t0 = time.perf_counter()
+    for l in range(L):
+        layers[l].forward(xh[l], out=oh[l])
+    e2e_v = L / (time.perf_counter() - t0)
+    bytes_layer = algorithmic_bytes(dims, 1, dims.top_k, True)["layer"]
+    peak, kind = measured_peak()
+    gbs = bytes_layer * value / 1e9
+    cpu = None
+    if layer0_host is not None:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import oracle_lib as ol
+        view, threads = ol.moe_layer_c(layer0_host), os.cpu_count() or 1
+        t0, n = time.perf_counter(), 0
+        while time.perf_counter() - t0 < args.cpu_budget_s and n < 64:
+            ol.moe_ffn(layer0_host, xh[0][0], threads=threads, view=view)
+            n += 1
+        cpu = {"value": n / (time.perf_counter() - t0), "unit": UNIT, "cores": threads, "kind": "port", "sample": f"{n} passes of one token through layer 0 (oracle port of ffn())"}
+    print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "BASELINE configs[0]: single routed-MoE FFN layer, batch 1, router computed, 512 IQ2_XXS experts top-10 + Q6_K shared expert",
+                                 "layers_per_step": L, "l2_policy": f"each step sweeps {L} distinct layers' weights"},
+                      "roofline": {"bound": "hbm", "kernel": "whole layer (9 launches)", "achieved": gbs, "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": gbs / peak,
+                                   "frac_of_nominal_8000": gbs / 8000.0, "traffic": None, "bytes_per_token_layer": bytes_layer, "us_per_layer": 1e3 * ms / L},
+                      "cpu_baseline": cpu, "e2e": {"value": e2e_v, "unit": UNIT, "h2d_bytes_per_step": L * row, "d2h_bytes_per_step": L * row},
+                      "gpu_launches": None, "clocks": clocks}), flush=True)
+
+
+def run_deltanet(args):
+    """BASELINE configs[2]: gated DeltaNet decode step (conv + SiLU + L2 norm, delta rule on the 128x128 fp32 states of
+    32 value heads, gated RMSNorm) for batch 1 and 8; a step sweeps enough distinct layer states to exceed L2."""
+    import ctypes as C
+    import torch
+    import dwarfstar_red_lite_b200 as rc
+    from dwarfstar_red_lite_b200.redcuda import DeltanetParams, f32p
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    lib = rc.lib()
+    S, groups, rank, d_conv = 128, 16, 32, 4
+    d_inner, channels = rank * S, 2 * S * groups + rank * S
+    g = torch.Generator(device=dev)
+    g.manual_seed(3)
+    pd = {"conv_kernel": torch.randn(channels, d_conv, device=dev, generator=g) * 0.5, "dt_bias": torch.zeros(rank, device=dev),
+          "ssm_a": -torch.ones(rank, device=dev), "ssm_norm": 1 + 0.1 * torch.randn(S, device=dev, generator=g)}
+    P = DeltanetParams(d_conv, S, groups, rank, d_inner, channels, 1e-6, *[C.cast(pd[k].data_ptr(), f32p) for k in ("conv_kernel", "dt_bias", "ssm_a", "ssm_norm")])
+    per_seq_bytes = 2 * rank * S * S * 4 + 2 * channels * (d_conv - 1) * 4 + channels * d_conv * 4 + (channels + 2 * d_inner + 2 * rank) * 4
+    results = {}
+    clocks = None
+    for B in (1, 8):
+        NL = max(8, int(400e6 // (B * rank * S * S * 4)))          # distinct states per step: ~400 MB of state
+        qkv = torch.randn(NL, B, channels, device=dev, generator=g)
+        z = torch.randn(NL, B, d_inner, device=dev, generator=g)
+        ba = torch.randn(NL, B, 2 * rank, device=dev, generator=g)
+        conv = torch.randn(NL, B, channels, d_conv - 1, device=dev, generator=g)
+        rec = torch.randn(NL, B, rank, S, S, device=dev, generator=g) * 0.05
+        out = torch.empty(NL, B, d_inner, device=dev)
+
+        def step(stream):
+            for l in range(NL):
+                ok = lib.redcuda_deltanet_step_noalloc(C.byref(P), B, qkv[l].data_ptr(), z[l].data_ptr(), ba[l].data_ptr(), conv[l].data_ptr(), rec[l].data_ptr(),
+                                                       out[l].data_ptr(), stream)
+                assert ok == 1, lib.redcuda_last_error().decode()
+
+        ms, clocks = _timed_graph(torch, step, args.steps, args.warmup, 0)
+        seq_layers_s = NL * B / (ms * 1e-3)
+        results[f"batch{B}"] = {"seq_layer_steps_per_s": seq_layers_s, "us_per_layer_call": 1e3 * ms / NL, "GBps": seq_layers_s * per_seq_bytes / 1e9, "layers_per_step": NL}
+        del qkv, z, ba, conv, rec, out
+    cpu = None
+    if not args.no_cpu:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import oracle_lib as ol
+        rng = np.random.default_rng(1)
+        p = dict(d_conv=d_conv, d_state=S, n_group=groups, dt_rank=rank, d_inner=d_inner, channels=channels, rms_eps=1e-6,
+                 conv_kernel=pd["conv_kernel"].cpu().numpy(), dt_bias=np.zeros(rank, np.float32), ssm_a=-np.ones(rank, np.float32), ssm_norm=pd["ssm_norm"].cpu().numpy())
+        cs, rs = rng.normal(0, 1, (channels, d_conv - 1)).astype(np.float32), rng.normal(0, 0.05, (rank, S, S)).astype(np.float32)
+        q1, z1, b1 = rng.normal(0, 1, channels).astype(np.float32), rng.normal(0, 1, d_inner).astype(np.float32), rng.normal(0, 1, 2 * rank).astype(np.float32)
+        t0, n = time.perf_counter(), 0
+        while time.perf_counter() - t0 < min(args.cpu_budget_s, 10.0):
+            ol.deltanet_mid(p, q1, z1, b1, cs, rs)
+            n += 1
+        cpu = {"value": n / (time.perf_counter() - t0), "unit": "sequence-layer steps/s", "cores": 1, "kind": "port", "sample": f"{n} single-sequence steps (oracle port of the deltanet_branch mid-section, one thread as in the reference)"}
+    peak, kind = measured_peak()
+    b8 = results["batch8"]
+    print(json.dumps({"metric": "deltanet_seq_layer_steps_per_s", "value": b8["seq_layer_steps_per_s"], "unit": "sequence-layer steps/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "BASELINE configs[2]: gated DeltaNet decode step, 16 key / 32 value heads, 128x128 fp32 state per head, batch 1 and 8", "results": results,
+                                 "l2_policy": "each step sweeps ~400 MB of distinct states"},
+                      "roofline": {"bound": "hbm", "kernel": "k_dn_prep + k_dn_state + k_dn_tail", "achieved": b8["GBps"], "peak": peak, "peak_kind": kind, "unit": "GB/s",
+                                   "frac": b8["GBps"] / peak, "traffic": None, "bytes_per_sequence_layer": per_seq_bytes, "batch1_GBps": results["batch1"]["GBps"]},
+                      "cpu_baseline": cpu, "e2e": None, "gpu_launches": None, "clocks": clocks}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -348,8 +492,9 @@ def main():
     ap.add_argument("--ref-tokens", type=int, default=8, help="tokens per step of the reference (CPU) arm")
     ap.add_argument("--cpu-budget-s", type=float, default=15.0)
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--workload", default="ragged64", choices=["ragged64", "decode48"],
-                    help="ragged64: BASELINE configs[1] (default, the headline); decode48: configs[3], whole-model decode")
+    ap.add_argument("--workload", default="ragged64", choices=["ragged64", "decode48", "moe_b1", "deltanet"],
+                    help="ragged64: BASELINE configs[1] (default, the headline); decode48: configs[3], whole-model decode; "
+                         "moe_b1: configs[0], one MoE layer at batch 1; deltanet: configs[2]")
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--new-tokens", type=int, default=128)
     ap.add_argument("--check-steps", type=int, default=0, help="decode48: greedy tokens compared with the CPU oracle")
@@ -359,6 +504,10 @@ def main():
     if args.workload == "decode48":
         args.warmup = max(args.warmup, 1)
         return run_decode48(args)
+    if args.workload == "moe_b1":
+        return run_moe_b1(args)
+    if args.workload == "deltanet":
+        return run_deltanet(args)
     args.warmup = max(args.warmup, 3) if args.impl == "redcuda" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
