@@ -35,6 +35,34 @@ int require_books(uint32_t ggml_type);
 const uint8_t *books_iq2();
 const uint32_t *books_iq3s();
 
+// Programmatic dependent launch: every kernel of the library is launched with the stream-serialisation attribute, so the
+// next kernel's blocks are scheduled (and run their prologue up to pdl_prologue's wait) while the previous kernel drains.
+// Every kernel calls pdl_prologue() first: it lets its own dependents start launching once all of its blocks have begun,
+// then waits until the kernels before it have completed and their writes are visible. RC_PDL=0 launches plainly.
+// Programmatic dependent launch: RC_PDL=0 never, RC_PDL=1 every kernel, unset = per source file (RC_PDL_DEFAULT:
+// on for the short latency-bound kernels, off for the expert kernels, where early-resident blocks measured slower).
+int pdl_mode();
+#ifndef RC_PDL_DEFAULT
+#define RC_PDL_DEFAULT 1
+#endif
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_prologue() {
+    asm volatile("griddepcontrol.launch_dependents;" ::);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+template <typename K, typename... Args>
+inline cudaError_t launch_kernel(int file_default, K kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = (pdl_mode() < 0 ? file_default : pdl_mode()) ? 1 : 0;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+#define RC_LAUNCH(kernel, grid, block, smem, stream, ...) rc::launch_kernel(RC_PDL_DEFAULT, kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__)
+#endif
+
 struct DevMem {
     void *p = nullptr; size_t bytes = 0;
     int alloc(size_t n);

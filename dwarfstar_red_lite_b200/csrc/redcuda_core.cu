@@ -6,6 +6,7 @@
 #include "../../include/redcuda.h"
 
 #include <math.h>
+#include <stdlib.h>
 #include <map>
 #include <mutex>
 #include <vector>
@@ -40,6 +41,11 @@ void prof_end(cudaStream_t s) {
     if (!g_prof_on) return;
     std::lock_guard<std::mutex> lk(g_prof_mu);
     if (!g_prof.empty()) cudaEventRecord(g_prof.back().b, s);
+}
+
+int pdl_mode() {
+    static const int mode = getenv("RC_PDL") ? (atoi(getenv("RC_PDL")) != 0) : -1;
+    return mode;
 }
 
 int require_device() {
@@ -82,6 +88,7 @@ const uint32_t *books_iq3s() { int dev = 0; cudaGetDevice(&dev); return g_iq3s_p
 
 // ---- raw GGUF blocks -> planar ----
 __global__ void k_repack(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, uint32_t type, uint64_t nb, uint32_t units_per_block) {
+    pdl_prologue();
     // one thread per 2-byte unit of the raw matrix (every field of the three formats starts on an even offset)
     const uint64_t total = nb * units_per_block;
     for (uint64_t u = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; u < total; u += (uint64_t)gridDim.x * blockDim.x) {
@@ -115,7 +122,7 @@ int upload_matrix(uint32_t type, uint32_t nrows, uint32_t ncols, const void *src
     const uint64_t total = nb * upb;
     const uint32_t grid = (uint32_t)((total + 255u) / 256u < 148u * 16u ? (total + 255u) / 256u : 148u * 16u);
     prof_begin("repack", stream);
-    k_repack<<<grid ? grid : 1u, 256, 0, stream>>>(raw, dst, type, nb, upb);
+    RC_LAUNCH((k_repack), grid ? grid : 1u, 256, 0, stream, raw, dst, type, nb, upb);
     prof_end(stream);
     RC_LAUNCHED();
     return 1;
@@ -123,6 +130,7 @@ int upload_matrix(uint32_t type, uint32_t nrows, uint32_t ncols, const void *src
 
 // ---- dequantisation: one thread per group of 8 values ----
 __global__ void k_dequant(const uint8_t *__restrict__ base, uint32_t type, uint64_t nb, const uint8_t *iq2, const uint32_t *iq3s, float *__restrict__ out) {
+    pdl_prologue();
     const RcBooks bk{iq2, iq3s};
     const uint64_t total = nb * 32u;
     for (uint64_t g = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; g < total; g += (uint64_t)gridDim.x * blockDim.x) {
@@ -134,6 +142,7 @@ __global__ void k_dequant(const uint8_t *__restrict__ base, uint32_t type, uint6
     }
 }
 __global__ void k_dequant_f16(const unsigned short *__restrict__ src, uint64_t n, float *__restrict__ out) {
+    pdl_prologue();
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
         out[i] = __half2float(__ushort_as_half(src[i]));
 }
@@ -172,6 +181,7 @@ __device__ __forceinline__ void gemv_tile(const GemvJob &J, uint32_t row0, uint3
 
 template <int NT>
 __global__ void __launch_bounds__(256) k_gemv(const __grid_constant__ GemvArgs A) {
+    pdl_prologue();
     extern __shared__ __align__(16) float xs[];
     __shared__ uint2 s_iq2[256];
     __shared__ uint32_t s_iq3s[512];
@@ -230,10 +240,10 @@ int launch_gemv(GemvArgs &A, cudaStream_t stream) {
     prof_begin(A.tag ? A.tag : "gemv", stream);
     if (nt == 1) {
         if (smem > 48u * 1024u) RC_CUDA(cudaFuncSetAttribute(k_gemv<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k_gemv<1><<<tiles, 256, smem, stream>>>(A);
+        RC_LAUNCH((k_gemv<1>), tiles, 256, smem, stream, A);
     } else {
         if (smem > 48u * 1024u) RC_CUDA(cudaFuncSetAttribute(k_gemv<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k_gemv<4><<<tiles, 256, smem, stream>>>(A);
+        RC_LAUNCH((k_gemv<4>), tiles, 256, smem, stream, A);
     }
     prof_end(stream);
     RC_LAUNCHED();
@@ -243,6 +253,7 @@ int launch_gemv(GemvArgs &A, cudaStream_t stream) {
 // ---- router: softmax + top-k, one block per token (router_exec.c:102-184 semantics, ties -> lower id) ----
 __global__ void __launch_bounds__(256) k_route(const float *__restrict__ logits, uint32_t n_expert, uint32_t top_k,
                                                uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ probs_out) {
+    pdl_prologue();
     extern __shared__ float p[];                 // n_expert probabilities
     __shared__ float s_redf[8];
     __shared__ double s_redd[8];
@@ -298,6 +309,7 @@ __global__ void __launch_bounds__(256) k_route(const float *__restrict__ logits,
 // cost a few hundred dependent instructions instead of 2k barriers. Same arithmetic and tie rule as k_route.
 __global__ void __launch_bounds__(256) k_route_warp(const float *__restrict__ logits, uint32_t ntok, uint32_t n_expert, uint32_t top_k,
                                                     uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ probs_out) {
+    pdl_prologue();
     const uint32_t lane = threadIdx.x & 31u, tok = blockIdx.x * 8u + (threadIdx.x >> 5);
     if (tok >= ntok) return;
     const float *l = logits + (size_t)tok * n_expert;
@@ -345,8 +357,8 @@ int launch_route(const float *logits_dev, uint32_t ntok, uint32_t n_expert, uint
     RC_REQUIRE(n_expert <= 8192u, "router: too many experts (%u)", n_expert);
     if (!ntok) return 1;
     prof_begin("route", stream);
-    if (n_expert <= 1024u) k_route_warp<<<(ntok + 7u) / 8u, 256, 0, stream>>>(logits_dev, ntok, n_expert, top_k, ids_dev, weights_dev, probs_dev);
-    else k_route<<<ntok, 256, n_expert * sizeof(float), stream>>>(logits_dev, n_expert, top_k, ids_dev, weights_dev, probs_dev);
+    if (n_expert <= 1024u) RC_LAUNCH((k_route_warp), (ntok + 7u) / 8u, 256, 0, stream, logits_dev, ntok, n_expert, top_k, ids_dev, weights_dev, probs_dev);
+    else RC_LAUNCH((k_route), ntok, 256, n_expert * sizeof(float), stream, logits_dev, n_expert, top_k, ids_dev, weights_dev, probs_dev);
     prof_end(stream);
     RC_LAUNCHED();
     return 1;
@@ -355,6 +367,7 @@ int launch_route(const float *logits_dev, uint32_t ntok, uint32_t n_expert, uint
 // out[t] = sigmoid(w . x[t]) for one F32 row w (the shared-expert gate), fp64 accumulation; one block per token.
 __global__ void __launch_bounds__(256) k_vec_sigmoid(const float *__restrict__ w, const float *__restrict__ x, uint32_t x_stride, uint32_t ncols,
                                                      float *__restrict__ out) {
+    pdl_prologue();
     __shared__ double red[8];
     const uint32_t t = blockIdx.x, tid = threadIdx.x;
     const float *xr = x + (size_t)t * x_stride;
@@ -377,7 +390,7 @@ int launch_vec_sigmoid(const float *w, const float *x, uint32_t x_stride, uint32
     RC_REQUIRE(ncols % 4u == 0, "vec_sigmoid: %u columns is not a multiple of 4", ncols);
     if (!ntok) return 1;
     prof_begin("moe_shared_gate", stream);
-    k_vec_sigmoid<<<ntok, 256, 0, stream>>>(w, x, x_stride, ncols, out);
+    RC_LAUNCH((k_vec_sigmoid), ntok, 256, 0, stream, w, x, x_stride, ncols, out);
     prof_end(stream);
     RC_LAUNCHED();
     return 1;
@@ -468,12 +481,12 @@ int redcuda_quant_dequant_rows(uint32_t type, const uint8_t *rows, uint32_t nrow
     cudaStream_t s = 0;
     if (type == RC_F16) {
         RC_CUDA(cudaMemcpyAsync(raw.p, rows, bytes, cudaMemcpyHostToDevice, s));
-        k_dequant_f16<<<(unsigned)((n + 255u) / 256u < 4096u ? (n + 255u) / 256u : 4096u), 256, 0, s>>>(raw.as<unsigned short>(), n, o.as<float>());
+        RC_LAUNCH((k_dequant_f16), (unsigned)((n + 255u) / 256u < 4096u ? (n + 255u) / 256u : 4096u), 256, 0, s, raw.as<unsigned short>(), n, o.as<float>());
         RC_LAUNCHED();
     } else {
         if (!upload_matrix(type, nrows, ncols, rows, false, planar.as<uint8_t>(), raw.as<uint8_t>(), s)) return 0;
         const uint64_t nb = (uint64_t)nrows * (ncols / 256u), groups = nb * 32u;
-        k_dequant<<<(unsigned)((groups + 255u) / 256u < 4096u ? (groups + 255u) / 256u : 4096u), 256, 0, s>>>(planar.as<uint8_t>(), type, nb, books_iq2(), books_iq3s(), o.as<float>());
+        RC_LAUNCH((k_dequant), (unsigned)((groups + 255u) / 256u < 4096u ? (groups + 255u) / 256u : 4096u), 256, 0, s, planar.as<uint8_t>(), type, nb, books_iq2(), books_iq3s(), o.as<float>());
         RC_LAUNCHED();
     }
     RC_CUDA(cudaMemcpyAsync(out, o.p, n * 4u, cudaMemcpyDeviceToHost, s));

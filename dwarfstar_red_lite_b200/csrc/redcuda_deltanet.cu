@@ -23,6 +23,7 @@ __device__ __forceinline__ double softplus_stable(double x) { if (x > 20.0) retu
 __global__ void k_dn_prep(DnDims D, const float *__restrict__ conv_kernel, const float *__restrict__ dt_bias, const float *__restrict__ ssm_a,
                           const float *__restrict__ qkv, const float *__restrict__ ba, float *__restrict__ conv_state,
                           float *__restrict__ qk, float *__restrict__ v, float *__restrict__ beta, float *__restrict__ gate) {
+    pdl_prologue();
     __shared__ double red[32];
     const uint32_t seq = blockIdx.y, tid = threadIdx.x, S = D.S, ns = D.d_conv - 1u;
     const uint32_t n_qk = 2u * D.groups, n_v = D.d_inner / S;
@@ -63,6 +64,7 @@ template <int VPL>
 __global__ void __launch_bounds__(256) k_dn_state(DnDims D, uint32_t batch, const float *__restrict__ qk, const float *__restrict__ v,
                                                   const float *__restrict__ beta, const float *__restrict__ gate,
                                                   float *__restrict__ state, float *__restrict__ core) {
+    pdl_prologue();
     const uint32_t lane = threadIdx.x & 31u;
     const uint64_t gw = (blockIdx.x * (uint64_t)blockDim.x + threadIdx.x) >> 5;
     const uint32_t S = D.S;
@@ -89,6 +91,7 @@ __global__ void __launch_bounds__(256) k_dn_state(DnDims D, uint32_t batch, cons
 
 // grid (rank, batch), block S threads
 __global__ void k_dn_tail(DnDims D, const float *__restrict__ core, const float *__restrict__ z, const float *__restrict__ norm_w, float *__restrict__ out) {
+    pdl_prologue();
     __shared__ double red[32];
     const uint32_t h = blockIdx.x, seq = blockIdx.y, i = threadIdx.x, S = D.S;
     const size_t idx = (size_t)seq * D.d_inner + (size_t)h * S + i;
@@ -113,22 +116,22 @@ int launch_deltanet(const DnDims &D, uint32_t batch, const float *conv_kernel, c
     if (!batch) return 1;
     const dim3 gp(2u * D.groups + D.d_inner / D.S + 1u, batch);
     prof_begin("dn_prep", s);
-    k_dn_prep<<<gp, D.S, 0, s>>>(D, conv_kernel, dt_bias, ssm_a, qkv, ba, conv_state, qk, v, beta, gate);
+    RC_LAUNCH((k_dn_prep), gp, D.S, 0, s, D, conv_kernel, dt_bias, ssm_a, qkv, ba, conv_state, qk, v, beta, gate);
     prof_end(s);
     RC_LAUNCHED();
     prof_begin("dn_state", s);
     const uint64_t warps = (uint64_t)batch * D.rank * D.S;
     const uint32_t blocks = (uint32_t)((warps + 7u) / 8u);
     switch (D.S) {
-        case 32: k_dn_state<1><<<blocks, 256, 0, s>>>(D, batch, qk, v, beta, gate, rec_state, core); break;
-        case 64: k_dn_state<2><<<blocks, 256, 0, s>>>(D, batch, qk, v, beta, gate, rec_state, core); break;
-        case 128: k_dn_state<4><<<blocks, 256, 0, s>>>(D, batch, qk, v, beta, gate, rec_state, core); break;
-        default: k_dn_state<8><<<blocks, 256, 0, s>>>(D, batch, qk, v, beta, gate, rec_state, core); break;
+        case 32: RC_LAUNCH((k_dn_state<1>), blocks, 256, 0, s, D, batch, qk, v, beta, gate, rec_state, core); break;
+        case 64: RC_LAUNCH((k_dn_state<2>), blocks, 256, 0, s, D, batch, qk, v, beta, gate, rec_state, core); break;
+        case 128: RC_LAUNCH((k_dn_state<4>), blocks, 256, 0, s, D, batch, qk, v, beta, gate, rec_state, core); break;
+        default: RC_LAUNCH((k_dn_state<8>), blocks, 256, 0, s, D, batch, qk, v, beta, gate, rec_state, core); break;
     }
     prof_end(s);
     RC_LAUNCHED();
     prof_begin("dn_tail", s);
-    k_dn_tail<<<dim3(D.rank, batch), D.S, 0, s>>>(D, core, z, norm_w, out);
+    RC_LAUNCH((k_dn_tail), dim3(D.rank, batch), D.S, 0, s, D, core, z, norm_w, out);
     prof_end(s);
     RC_LAUNCHED();
     return 1;

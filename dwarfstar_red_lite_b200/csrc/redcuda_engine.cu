@@ -28,6 +28,7 @@ static double now_ms() { return std::chrono::duration<double, std::milli>(std::c
 // x = dequantised embedding row of *token (block = 256 threads)
 __global__ void k_embed_row(const uint8_t *__restrict__ base, uint32_t type, uint64_t nb, uint32_t ncols, const uint32_t *__restrict__ token,
                             const uint8_t *iq2, const uint32_t *iq3s, float *__restrict__ out) {
+    pdl_prologue();
     const uint64_t row = *token;
     if (type == RC_F32) { for (uint32_t i = threadIdx.x; i < ncols; i += blockDim.x) out[i] = reinterpret_cast<const float *>(base)[row * ncols + i]; return; }
     if (type == RC_F16) { for (uint32_t i = threadIdx.x; i < ncols; i += blockDim.x) out[i] = __half2float(__ushort_as_half(reinterpret_cast<const unsigned short *>(base)[row * ncols + i])); return; }
@@ -54,6 +55,7 @@ __device__ __forceinline__ double block_sum_d(double v, double *red) {
 // normed = RMSNorm(x [+ branch]) * w (engine_cpu.c:96-101, 418-424); resid_out (optional) = x + branch. One block.
 __global__ void __launch_bounds__(1024) k_rmsnorm(const float *__restrict__ x, const float *__restrict__ branch, const float *__restrict__ w,
                                                   uint32_t n, float eps, float *__restrict__ resid_out, float *__restrict__ normed) {
+    pdl_prologue();
     __shared__ double red[32];
     double ss = 0.0;
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
@@ -84,6 +86,7 @@ __global__ void k_attn_prep(const float *__restrict__ qg, const float *__restric
                             const float *__restrict__ qn, const float *__restrict__ kn, uint32_t n_head, uint32_t n_kv, uint32_t hd,
                             uint32_t rope_dims, float freq_base, float eps, const uint32_t *__restrict__ pos_p, float *__restrict__ query, float *__restrict__ gate,
                             KV *__restrict__ kcache, KV *__restrict__ vcache) {
+    pdl_prologue();
     extern __shared__ float sh[];
     __shared__ double red[32];
     const uint32_t b = blockIdx.x, tid = threadIdx.x, pos = *pos_p;      // the position lives in device memory: a captured graph replays for every token
@@ -121,6 +124,7 @@ template <typename KV, int VPL, int G>
 __global__ void __launch_bounds__(256) k_attn_decode(const float *__restrict__ query, const KV *__restrict__ kcache, const KV *__restrict__ vcache,
                                                      uint32_t n_kv, const uint32_t *__restrict__ pos_p, uint32_t nsplit, float scale,
                                                      float *__restrict__ part_m, float *__restrict__ part_l, float *__restrict__ part_acc) {
+    pdl_prologue();
     extern __shared__ float sm[];            // [8][G][hd] accumulators, then [8][G] m, [8][G] l
     constexpr uint32_t hd = VPL * 32u;
     const uint32_t kvh = blockIdx.x, split = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -189,6 +193,7 @@ __global__ void __launch_bounds__(256) k_attn_decode(const float *__restrict__ q
 // merge the split partials, normalise, apply the sigmoid output gate (engine_cpu.c:312-317). grid = n_head, block = hd
 __global__ void k_attn_merge(const float *__restrict__ part_m, const float *__restrict__ part_l, const float *__restrict__ part_acc,
                              const float *__restrict__ gate, uint32_t nsplit, uint32_t hd, float *__restrict__ gated) {
+    pdl_prologue();
     const uint32_t h = blockIdx.x, d = threadIdx.x;
     float M = -INFINITY;
     for (uint32_t s = 0; s < nsplit; ++s) M = fmaxf(M, part_m[(size_t)h * nsplit + s]);
@@ -204,11 +209,13 @@ __global__ void k_attn_merge(const float *__restrict__ part_m, const float *__re
 }
 
 // argmax of n floats, ties to the lowest index; one block of 1024
-__global__ void k_advance(uint32_t *pos) { if (threadIdx.x == 0 && blockIdx.x == 0) *pos += 1u; }
+__global__ void k_advance(uint32_t *pos) {
+    pdl_prologue(); if (threadIdx.x == 0 && blockIdx.x == 0) *pos += 1u; }
 
 // gen_log / gen_count (optional): the chosen id is also appended to gen_log[*gen_count]
 __global__ void __launch_bounds__(1024) k_argmax(const float *__restrict__ v, uint32_t n, uint32_t *__restrict__ out, uint32_t *__restrict__ gen_log,
                                                  uint32_t *__restrict__ gen_count) {
+    pdl_prologue();
     __shared__ float bv[32];
     __shared__ uint32_t bi[32];
     float best = -INFINITY; uint32_t idx = 0xffffffffu;
@@ -296,7 +303,7 @@ static int eng_attention(rl_engine *e, const EngLayer &L, char *error, size_t ca
     KV *kc = (KV *)e->kcache + kv_layer * L.aidx, *vc = (KV *)e->vcache + kv_layer * L.aidx;
     cudaStream_t s = e->stream;
     prof_begin("attn_prep", s);
-    k_attn_prep<KV><<<nq + 2u * nkv, hd, hd * sizeof(float), s>>>(e->qg, e->kraw, e->vraw, L.q_norm, L.k_norm, nq, nkv, hd, in.rope_dims, in.rope_freq_base,
+    RC_LAUNCH((k_attn_prep<KV>), nq + 2u * nkv, hd, hd * sizeof(float), s, e->qg, e->kraw, e->vraw, L.q_norm, L.k_norm, nq, nkv, hd, in.rope_dims, in.rope_freq_base,
                                                                  in.rms_eps, e->pos_d, e->query, e->gate, kc, vc);
     prof_end(s);
     uint32_t nsplit = (in.context + 31u) / 32u;                 // fixed per engine (graph replay): enough slices for a full context
@@ -307,7 +314,7 @@ static int eng_attention(rl_engine *e, const EngLayer &L, char *error, size_t ca
     prof_begin("attn_decode", s);
 #define ENG_ATTN(VPL_, G_) do { \
         if (smem > 48u * 1024u) ENG_CUDA(cudaFuncSetAttribute(k_attn_decode<KV, VPL_, G_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        k_attn_decode<KV, VPL_, G_><<<grid, 256, smem, s>>>(e->query, kc, vc, nkv, e->pos_d, nsplit, scale, e->part_m, e->part_l, e->part_acc); } while (0)
+        RC_LAUNCH((k_attn_decode<KV, VPL_, G_>), grid, 256, smem, s, e->query, kc, vc, nkv, e->pos_d, nsplit, scale, e->part_m, e->part_l, e->part_acc); } while (0)
     if (hd == 256u && G == 8u) ENG_ATTN(8, 8);
     else if (hd == 128u && G == 8u) ENG_ATTN(4, 8);
     else if (hd == 128u && G == 4u) ENG_ATTN(4, 4);
@@ -318,7 +325,7 @@ static int eng_attention(rl_engine *e, const EngLayer &L, char *error, size_t ca
 #undef ENG_ATTN
     prof_end(s);
     prof_begin("attn_merge", s);
-    k_attn_merge<<<nq, hd, 0, s>>>(e->part_m, e->part_l, e->part_acc, e->gate, nsplit, hd, e->gated);
+    RC_LAUNCH((k_attn_merge), nq, hd, 0, s, e->part_m, e->part_l, e->part_acc, e->gate, nsplit, hd, e->gated);
     prof_end(s);
     g_launches.fetch_add(3);
     ENG_CUDA(cudaGetLastError());
@@ -331,7 +338,7 @@ static int eng_step_device(rl_engine *e, bool want_logits, char *error, size_t c
     cudaStream_t s = e->stream;
     if (e->position >= in.context) ENG_FAIL("context of %u positions is full", in.context);
     prof_begin("embed", s);
-    k_embed_row<<<1, 256, 0, s>>>(e->tok_embd.base, e->tok_embd.type, e->tok_embd.nb, in.hidden, e->token_d, books_iq2(), books_iq3s(), e->embed_d);
+    RC_LAUNCH((k_embed_row), 1, 256, 0, s, e->tok_embd.base, e->tok_embd.type, e->tok_embd.nb, in.hidden, e->token_d, books_iq2(), books_iq3s(), e->embed_d);
     prof_end(s);
     g_launches.fetch_add(1);
     const float *x = e->embed_d;
@@ -339,7 +346,7 @@ static int eng_step_device(rl_engine *e, bool want_logits, char *error, size_t c
     for (uint32_t l = 0; l < in.n_layer; ++l) {
         const EngLayer &L = e->layers[l];
         prof_begin("rmsnorm", s);
-        k_rmsnorm<<<1, 1024, 0, s>>>(x, nullptr, L.attn_norm, in.hidden, in.rms_eps, nullptr, e->normed);
+        RC_LAUNCH((k_rmsnorm), 1, 1024, 0, s, x, nullptr, L.attn_norm, in.hidden, in.rms_eps, nullptr, e->normed);
         prof_end(s);
         g_launches.fetch_add(1);
         if (L.recurrent) {
@@ -360,7 +367,7 @@ static int eng_step_device(rl_engine *e, bool want_logits, char *error, size_t c
             ENG_RC(eng_gemv(e, &L.o, o1, 1, e->gated, "attn_out_gemv"));
         }
         prof_begin("resid_rmsnorm", s);
-        k_rmsnorm<<<1, 1024, 0, s>>>(x, e->branch, L.post_norm, in.hidden, in.rms_eps, e->resid, e->normed);
+        RC_LAUNCH((k_rmsnorm), 1, 1024, 0, s, x, e->branch, L.post_norm, in.hidden, in.rms_eps, e->resid, e->normed);
         prof_end(s);
         g_launches.fetch_add(1);
         float *xo = e->layer_out_d + (size_t)l * in.hidden;
@@ -369,14 +376,14 @@ static int eng_step_device(rl_engine *e, bool want_logits, char *error, size_t c
         x = xo;
     }
     prof_begin("rmsnorm", s);
-    k_rmsnorm<<<1, 1024, 0, s>>>(x, nullptr, e->output_norm, in.hidden, in.rms_eps, nullptr, e->final_norm_d);
+    RC_LAUNCH((k_rmsnorm), 1, 1024, 0, s, x, nullptr, e->output_norm, in.hidden, in.rms_eps, nullptr, e->final_norm_d);
     prof_end(s);
     g_launches.fetch_add(1);
     if (want_logits) {
         float *o1[1] = {e->logits_d};
         ENG_RC(eng_gemv(e, &e->output, o1, 1, e->final_norm_d, "lm_head_gemv"));
     }
-    k_advance<<<1, 32, 0, s>>>(e->pos_d);
+    RC_LAUNCH((k_advance), 1, 32, 0, s, e->pos_d);
     g_launches.fetch_add(1);
     ENG_CUDA(cudaGetLastError());
     e->position++;
@@ -679,7 +686,7 @@ int rl_engine_generate_greedy(rl_engine *e, uint32_t token, uint32_t n_new, uint
     ENG_CUDA(cudaMemsetAsync(e->gen_count_d, 0, 4, e->stream));
     auto one_token = [&]() -> int {
         if (!eng_step_device(e, true, error, cap)) return 0;
-        k_argmax<<<1, 1024, 0, e->stream>>>(e->logits_d, e->info.vocab, e->token_d, e->gen_tokens_d, e->gen_count_d);
+        RC_LAUNCH((k_argmax), 1, 1024, 0, e->stream, e->logits_d, e->info.vocab, e->token_d, e->gen_tokens_d, e->gen_count_d);
         g_launches.fetch_add(1);
         return 1;
     };
@@ -738,7 +745,7 @@ int rl_engine_embed_token(const rl_engine *ce, uint32_t token, float *out, char 
     ENG_CUDA(cudaStreamSynchronize(e->stream));
     e->token_pin[1] = token;
     ENG_CUDA(cudaMemcpyAsync(e->token_d + 1, e->token_pin + 1, 4, cudaMemcpyHostToDevice, e->stream));
-    k_embed_row<<<1, 256, 0, e->stream>>>(e->tok_embd.base, e->tok_embd.type, e->tok_embd.nb, e->info.hidden, e->token_d + 1, books_iq2(), books_iq3s(), e->normed);
+    RC_LAUNCH((k_embed_row), 1, 256, 0, e->stream, e->tok_embd.base, e->tok_embd.type, e->tok_embd.nb, e->info.hidden, e->token_d + 1, books_iq2(), books_iq3s(), e->normed);
     g_launches.fetch_add(1);
     ENG_CUDA(cudaMemcpyAsync(out, e->normed, e->info.hidden * 4u, cudaMemcpyDeviceToHost, e->stream));
     ENG_CUDA(cudaStreamSynchronize(e->stream));

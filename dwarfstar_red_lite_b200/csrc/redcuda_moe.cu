@@ -11,6 +11,7 @@
 //   5. shared down projection
 //   6. down projection per pair
 //   7. per-token combine in router order: out = resid + sum_k w_k * expert_k + shared * scalar
+#define RC_PDL_DEFAULT 0
 #include "redcuda_common.cuh"
 #include "redcuda_dot.cuh"
 #include "redcuda_kernels.cuh"
@@ -63,6 +64,7 @@ __device__ __forceinline__ void moe_tile(const MoeArgs &A, const uint8_t *m0, co
 
 template <int NT>
 __global__ void __launch_bounds__(256) k_moe_experts(const __grid_constant__ MoeArgs A) {
+    pdl_prologue();
     extern __shared__ __align__(16) float xs[];
     __shared__ uint2 s_iq2[256];
     __shared__ uint32_t s_iq3s[512];
@@ -104,6 +106,7 @@ __global__ void __launch_bounds__(1024) k_group_pairs(const uint32_t *__restrict
                                                       uint32_t expert_count, uint32_t item_tok, uint32_t *__restrict__ sorted, uint32_t *__restrict__ uexp,
                                                       uint32_t *__restrict__ ustart, uint32_t *__restrict__ n_unique, uint32_t *__restrict__ item_u,
                                                       uint32_t *__restrict__ item_p0, uint32_t *__restrict__ n_items, uint32_t *__restrict__ bad) {
+    pdl_prologue();
     __shared__ uint32_t cnt[1024], start[1024], wsum[32], wsum2[32], wsum3[32];
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     cnt[tid] = 0;
@@ -149,6 +152,7 @@ __global__ void __launch_bounds__(1024) k_group_pairs(const uint32_t *__restrict
 __global__ void k_group_trivial(const uint32_t *__restrict__ pair_expert, uint32_t npairs, uint32_t *__restrict__ sorted,
                                 uint32_t *__restrict__ uexp, uint32_t *__restrict__ ustart, uint32_t *__restrict__ n_unique,
                                 uint32_t *__restrict__ item_u, uint32_t *__restrict__ item_p0, uint32_t *__restrict__ n_items) {
+    pdl_prologue();
     const uint32_t i = threadIdx.x;
     if (i < npairs) { sorted[i] = i; uexp[i] = pair_expert[i]; ustart[i] = i; item_u[i] = i; item_p0[i] = i; }
     if (i == 0) { ustart[npairs] = npairs; *n_unique = npairs; *n_items = npairs; }
@@ -159,6 +163,7 @@ __global__ void __launch_bounds__(256) k_moe_combine(const float *__restrict__ p
                                                      const float *__restrict__ shared, const float *__restrict__ scalar,
                                                      const float *__restrict__ resid, float *__restrict__ out, uint32_t hidden,
                                                      const uint32_t *__restrict__ pair_row) {
+    pdl_prologue();
     const uint32_t t = blockIdx.y;
     const uint32_t r = (blockIdx.x * 256u + threadIdx.x) * 4u;
     if (r >= hidden) return;
@@ -300,10 +305,10 @@ static int moe_launch_experts(redcuda_moe *m, bool gateup, uint32_t npairs, bool
     prof_begin(gateup ? "moe_gateup" : "moe_down", s);
     if (nt == 1) {
         if (smem > 48u * 1024u) RC_CUDA(cudaFuncSetAttribute(k_moe_experts<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k_moe_experts<1><<<grid, 256, smem, s>>>(A);
+        RC_LAUNCH((k_moe_experts<1>), grid, 256, smem, s, A);
     } else {
         if (smem > 48u * 1024u) RC_CUDA(cudaFuncSetAttribute(k_moe_experts<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k_moe_experts<4><<<grid, 256, smem, s>>>(A);
+        RC_LAUNCH((k_moe_experts<4>), grid, 256, smem, s, A);
     }
     prof_end(s);
     RC_LAUNCHED();
@@ -314,9 +319,9 @@ static int moe_group(redcuda_moe *m, const uint32_t *pair_expert, uint32_t npair
     RC_REQUIRE(npairs <= m->max_pairs, "moe: %u pairs exceed the workspace (%u)", npairs, m->max_pairs);
     prof_begin("moe_group", s);
     if (distinct && npairs <= 64u) {
-        k_group_trivial<<<1, 64, 0, s>>>(pair_expert, npairs, m->sorted, m->uexp, m->ustart, m->n_unique, m->item_u, m->item_p0, m->n_items);
+        RC_LAUNCH((k_group_trivial), 1, 64, 0, s, pair_expert, npairs, m->sorted, m->uexp, m->ustart, m->n_unique, m->item_u, m->item_p0, m->n_items);
     } else {
-        k_group_pairs<<<1, 1024, 0, s>>>(pair_expert, npairs, m->d.expert_begin, m->d.expert_count, mma_item_tokens(false), m->sorted, m->uexp, m->ustart,
+        RC_LAUNCH((k_group_pairs), 1, 1024, 0, s, pair_expert, npairs, m->d.expert_begin, m->d.expert_count, mma_item_tokens(false), m->sorted, m->uexp, m->ustart,
                                          m->n_unique, m->item_u, m->item_p0, m->n_items, m->bad);
     }
     prof_end(s);
@@ -328,7 +333,7 @@ static int moe_combine(redcuda_moe *m, uint32_t ntok, const float *pair_out, con
                        float *out, cudaStream_t s) {
     const dim3 grid((m->d.hidden / 4u + 255u) / 256u, ntok);
     prof_begin("moe_combine", s);
-    k_moe_combine<<<grid, 256, 0, s>>>(pair_out, wk, top_k, shared ? m->sh_out : nullptr, m->scalar, resid, out, m->d.hidden, nullptr);
+    RC_LAUNCH((k_moe_combine), grid, 256, 0, s, pair_out, wk, top_k, shared ? m->sh_out : nullptr, m->scalar, resid, out, m->d.hidden, nullptr);
     prof_end(s);
     RC_LAUNCHED();
     return 1;
@@ -522,7 +527,7 @@ int redcuda_moe_combine_device(redcuda_moe *m, uint32_t ntok, const float *pair_
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((m->d.hidden / 4u + 255u) / 256u, ntok);
     prof_begin("moe_combine", s);
-    k_moe_combine<<<grid, 256, 0, s>>>(pair_out_dev, weights_dev, m->d.top_k, add_dev, nullptr, resid_dev, out_dev, m->d.hidden, pair_row_dev);
+    RC_LAUNCH((k_moe_combine), grid, 256, 0, s, pair_out_dev, weights_dev, m->d.top_k, add_dev, nullptr, resid_dev, out_dev, m->d.hidden, pair_row_dev);
     prof_end(s);
     RC_LAUNCHED();
     return 1;

@@ -23,6 +23,7 @@
 // digits are read straight from global memory (a few KB per work item, L1-resident).
 // Both lookup tables are replicated in shared memory with an entry stride of 128 B (magnitudes: 8 copies of 8 B, replica =
 // lane%8, at worst a two-way conflict between the halves of a 16-lane phase; signs: 8 copies of 16 B holding the byte mask and its +1 carry term, replica = lane%8) for the same reason.
+#define RC_PDL_DEFAULT 0
 #include "redcuda_common.cuh"
 #include "redcuda_kernels.cuh"
 #include "redcuda_moe_mma.cuh"
@@ -66,6 +67,7 @@ int mma_set_luts(const uint8_t *iq2_grid_host) {
 // grid = rows, block = 256. xq[row][3][ncols] (digit 0 = least significant), sx[row].
 __global__ void __launch_bounds__(256) k_quant_act(const float *__restrict__ x, uint32_t x_stride, uint32_t ncols,
                                                    int8_t *__restrict__ xq, float *__restrict__ sx) {
+    pdl_prologue();
     __shared__ float red[8];
     const uint32_t row = blockIdx.x, tid = threadIdx.x;
     const float *xr = x + (size_t)row * x_stride;
@@ -105,7 +107,7 @@ int launch_quant_act(const float *x, uint32_t x_stride, uint32_t rows, uint32_t 
     RC_REQUIRE(ncols % 16u == 0, "quant_act: %u columns is not a multiple of 16", ncols);
     if (!rows) return 1;
     prof_begin("moe_quant_act", s);
-    k_quant_act<<<rows, 256, 0, s>>>(x, x_stride, ncols, xq, sx);
+    RC_LAUNCH((k_quant_act), rows, 256, 0, s, x, x_stride, ncols, xq, sx);
     prof_end(s);
     RC_LAUNCHED();
     return 1;
@@ -203,6 +205,7 @@ __device__ __forceinline__ void mma_unit(const uint8_t *stage, const float (&dsc
 // expert's pairs into such items, so that all blocks carry the same amount of work whatever the routing skew).
 template <int NMAT, int NTILE>
 __global__ void __launch_bounds__(256, NTILE == 1 ? MMA_MINB : 1) k_moe_mma(const __grid_constant__ MmaArgs A) {
+    pdl_prologue();
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr uint32_t NCOL = NTILE * 8u;
     if (blockIdx.y >= *A.n_items) return;
@@ -363,7 +366,7 @@ int launch_moe_mma(MmaArgs &A, uint32_t groups, bool few_tokens, cudaStream_t s)
         RC_REQUIRE(smem <= 227u * 1024u, "moe mma: %zu bytes of shared memory needed for %u columns", smem, A.ncols); \
         A.item_class = CLS; \
         RC_CUDA(cudaFuncSetAttribute(k_moe_mma<NM, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        k_moe_mma<NM, NT><<<grid, 256, smem, s>>>(A); g_launches.fetch_add(1, std::memory_order_relaxed); } while (0)
+        RC_LAUNCH((k_moe_mma<NM, NT>), grid, 256, smem, s, A); g_launches.fetch_add(1, std::memory_order_relaxed); } while (0)
     if (few_tokens) { if (nmat == 2u) RC_MMA_LAUNCH(2, 1, 0u); else RC_MMA_LAUNCH(1, 1, 0u); }
     else {
         static const bool split = getenv("RC_MMA_SPLIT") && atoi(getenv("RC_MMA_SPLIT")) != 0;   // A/B switch; measured: one launch for all items is faster (no serialised tails)

@@ -11,6 +11,7 @@
 //
 // Block = 8 warps = MS matrices x KS column splits x TGB groups of 8 tokens, for one tile of 16 rows; partial sums meet
 // in shared memory, where the epilogue (plain store or SiLU(gate)*up) is applied.
+#define RC_PDL_DEFAULT 0
 #include "redcuda_common.cuh"
 #include "redcuda_kernels.cuh"
 #include "redcuda_moe_mma.cuh"
@@ -34,6 +35,7 @@ struct Q6Args {
 };
 
 __global__ void __launch_bounds__(256) k_q6k_mma(const __grid_constant__ Q6Args A) {
+    pdl_prologue();
     __shared__ float part[8][16][8];        // per warp: 16 rows x 8 tokens
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
     const uint32_t MS = A.MS, KS = A.KS, TGB = 8u / (MS * KS);
@@ -118,7 +120,7 @@ int launch_q6k_mma(const uint8_t *w0, const uint8_t *w1, uint64_t nb, uint32_t n
     const uint32_t TGB = 8u / (A.MS * KS);
     const dim3 grid(tiles, (tgroups + TGB - 1u) / TGB);
     prof_begin(tag, s);
-    k_q6k_mma<<<grid, 256, 0, s>>>(A);
+    RC_LAUNCH((k_q6k_mma), grid, 256, 0, s, A);
     prof_end(s);
     RC_LAUNCHED();
     return 1;
