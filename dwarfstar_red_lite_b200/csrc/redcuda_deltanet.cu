@@ -107,6 +107,145 @@ __global__ void k_dn_tail(DnDims D, const float *__restrict__ core, const float 
     out[idx] = x * inv * norm_w[i] * silu;
 }
 
+// ---- sequence form: T consecutive tokens of ONE sequence (a prefill chunk) ----
+// k_dn_prep_seq   grid (2*groups + d_inner/S + 1, T): token t's conv window is the d_conv-1 samples before it (the conv
+//                 state for times before the chunk, chunk rows after); the state itself is rolled by k_dn_conv_roll
+// k_dn_state_seq  the delta rule over the T tokens with the state row held in registers: one read and one write of
+//                 the state per chunk instead of per token; the next token's q/k/v/beta/gate are fetched while the
+//                 current one is reduced
+// the tail kernel is k_dn_tail with the token as its batch index
+__global__ void k_dn_prep_seq(DnDims D, const float *__restrict__ conv_kernel, const float *__restrict__ dt_bias, const float *__restrict__ ssm_a,
+                              const float *__restrict__ qkv, const float *__restrict__ ba, const float *__restrict__ conv_state,
+                              float *__restrict__ qk, float *__restrict__ v, float *__restrict__ beta, float *__restrict__ gate) {
+    pdl_prologue();
+    __shared__ double red[32];
+    const uint32_t ti = blockIdx.y, tid = threadIdx.x, S = D.S, ns = D.d_conv - 1u;
+    const uint32_t n_qk = 2u * D.groups, n_v = D.d_inner / S;
+    if (blockIdx.x == n_qk + n_v) {
+        const uint32_t width = D.rank / D.groups, stride = 2u * width;
+        for (uint32_t h = tid; h < D.rank; h += blockDim.x) {
+            const uint32_t g = h / width, l = h - g * width;
+            const float *b = ba + (size_t)ti * 2u * D.rank;
+            beta[(size_t)ti * D.rank + h] = (float)sigmoid_stable((double)b[g * stride + l]);
+            gate[(size_t)ti * D.rank + h] = (float)(softplus_stable((double)b[g * stride + width + l] + (double)dt_bias[h]) * (double)ssm_a[h]);
+        }
+        return;
+    }
+    const uint32_t c = blockIdx.x * S + tid;
+    const float *cs = conv_state + (size_t)c * ns;
+    const float *kr = conv_kernel + (size_t)c * D.d_conv;
+    double acc = 0.0;
+    for (uint32_t j = 0; j < ns; ++j) {
+        const int tau = (int)ti + (int)j - (int)ns;        // time of tap j relative to the chunk start
+        const float smp = tau < 0 ? cs[(int)ns + tau] : qkv[(size_t)tau * D.channels + c];
+        acc += (double)smp * (double)kr[j];
+    }
+    acc += (double)qkv[(size_t)ti * D.channels + c] * (double)kr[ns];
+    const float y = (float)(acc / (1.0 + exp(-acc)));
+    if (blockIdx.x >= n_qk) { v[(size_t)ti * D.d_inner + (c - n_qk * S)] = y; return; }
+    double ss = (double)y * (double)y;
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((tid & 31u) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    double tot = 0.0;
+    for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
+    const double inv = 1.0 / fmax(sqrt(tot), (double)D.eps);
+    qk[(size_t)ti * n_qk * S + c] = (float)((double)y * inv);
+}
+
+// conv state <- the last d_conv-1 samples of [state, chunk]; one thread per channel
+__global__ void k_dn_conv_roll(DnDims D, uint32_t T, const float *__restrict__ qkv, float *__restrict__ conv_state) {
+    pdl_prologue();
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x, ns = D.d_conv - 1u;
+    if (c >= D.channels) return;
+    float *cs = conv_state + (size_t)c * ns;
+    for (uint32_t j = 0; j < ns; ++j) {                     // ascending: a kept sample moves down, so its source is still intact
+        const int tau = (int)T + (int)j - (int)ns;
+        cs[j] = tau < 0 ? cs[(int)ns + tau] : qkv[(size_t)tau * D.channels + c];
+    }
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(256) k_dn_state_seq(DnDims D, uint32_t T, const float *__restrict__ qk, const float *__restrict__ v,
+                                                      const float *__restrict__ beta, const float *__restrict__ gate,
+                                                      float *__restrict__ state, float *__restrict__ core) {
+    pdl_prologue();
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t gw = (blockIdx.x * (uint64_t)blockDim.x + threadIdx.x) >> 5;
+    const uint32_t S = D.S;
+    if (gw >= (uint64_t)D.rank * S) return;
+    const uint32_t j = (uint32_t)(gw % S), h = (uint32_t)(gw / S);
+    const uint32_t kh = h / (D.rank / D.groups);
+    const size_t tok_qk = (size_t)2u * D.groups * S;
+    const float *q = qk + (size_t)kh * S, *k = qk + (size_t)(D.groups + kh) * S;
+    float *row = state + ((size_t)h * S + j) * S;
+    const float scale = 1.0f / sqrtf((float)S);
+    float m[VPL], kc[VPL], qc[VPL];
+#pragma unroll
+    for (int t = 0; t < VPL; ++t) { m[t] = row[lane + 32 * t]; kc[t] = k[lane + 32 * t]; qc[t] = q[lane + 32 * t]; }
+    float g_c = gate[h], b_c = beta[h], v_c = v[(size_t)h * S + j];
+    for (uint32_t ti = 0; ti < T; ++ti) {
+        float kn[VPL], qn[VPL], g_n = 0.f, b_n = 0.f, v_n = 0.f;
+        if (ti + 1u < T) {
+            const size_t n1 = ti + 1u;
+#pragma unroll
+            for (int t = 0; t < VPL; ++t) { kn[t] = k[n1 * tok_qk + lane + 32 * t]; qn[t] = q[n1 * tok_qk + lane + 32 * t]; }
+            g_n = gate[n1 * D.rank + h]; b_n = beta[n1 * D.rank + h]; v_n = v[n1 * D.d_inner + (size_t)h * S + j];
+        } else {
+#pragma unroll
+            for (int t = 0; t < VPL; ++t) { kn[t] = 0.f; qn[t] = 0.f; }
+        }
+        const float decay = expf(g_c);
+        float sum = 0.f;
+#pragma unroll
+        for (int t = 0; t < VPL; ++t) { m[t] = m[t] * decay; sum += m[t] * kc[t]; }
+        for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float delta = (v_c - sum) * b_c;
+        float o_acc = 0.f;
+#pragma unroll
+        for (int t = 0; t < VPL; ++t) { m[t] += kc[t] * delta; o_acc += m[t] * qc[t]; }
+        for (int o = 16; o; o >>= 1) o_acc += __shfl_xor_sync(0xffffffffu, o_acc, o);
+        if (lane == 0) core[(size_t)ti * D.d_inner + (size_t)h * S + j] = o_acc * scale;
+#pragma unroll
+        for (int t = 0; t < VPL; ++t) { kc[t] = kn[t]; qc[t] = qn[t]; }
+        g_c = g_n; b_c = b_n; v_c = v_n;
+    }
+#pragma unroll
+    for (int t = 0; t < VPL; ++t) row[lane + 32 * t] = m[t];
+}
+
+int launch_deltanet_seq(const DnDims &D, uint32_t T, const float *conv_kernel, const float *dt_bias, const float *ssm_a, const float *norm_w,
+                        const float *qkv, const float *z, const float *ba, float *conv_state, float *rec_state,
+                        float *qk, float *v, float *beta, float *gate, float *core, float *out, cudaStream_t s) {
+    RC_REQUIRE(D.S == 32u || D.S == 64u || D.S == 128u || D.S == 256u, "deltanet: state size %u not in {32,64,128,256}", D.S);
+    RC_REQUIRE(D.rank && D.groups && D.rank % D.groups == 0 && D.d_inner == D.rank * D.S && D.channels == 2u * D.S * D.groups + D.d_inner && D.d_conv >= 2u,
+               "deltanet: inconsistent dimensions");
+    if (!T) return 1;
+    prof_begin("dn_prep_seq", s);
+    RC_LAUNCH((k_dn_prep_seq), dim3(2u * D.groups + D.d_inner / D.S + 1u, T), D.S, 0, s, D, conv_kernel, dt_bias, ssm_a, qkv, ba, (const float *)conv_state, qk, v, beta, gate);
+    prof_end(s);
+    RC_LAUNCHED();
+    prof_begin("dn_conv_roll", s);
+    RC_LAUNCH((k_dn_conv_roll), (D.channels + 255u) / 256u, 256, 0, s, D, T, qkv, conv_state);
+    prof_end(s);
+    RC_LAUNCHED();
+    prof_begin("dn_state_seq", s);
+    const uint32_t blocks = (D.rank * D.S + 7u) / 8u;
+    switch (D.S) {
+        case 32: RC_LAUNCH((k_dn_state_seq<1>), blocks, 256, 0, s, D, T, qk, v, beta, gate, rec_state, core); break;
+        case 64: RC_LAUNCH((k_dn_state_seq<2>), blocks, 256, 0, s, D, T, qk, v, beta, gate, rec_state, core); break;
+        case 128: RC_LAUNCH((k_dn_state_seq<4>), blocks, 256, 0, s, D, T, qk, v, beta, gate, rec_state, core); break;
+        default: RC_LAUNCH((k_dn_state_seq<8>), blocks, 256, 0, s, D, T, qk, v, beta, gate, rec_state, core); break;
+    }
+    prof_end(s);
+    RC_LAUNCHED();
+    prof_begin("dn_tail", s);
+    RC_LAUNCH((k_dn_tail), dim3(D.rank, T), D.S, 0, s, D, core, z, norm_w, out);
+    prof_end(s);
+    RC_LAUNCHED();
+    return 1;
+}
+
 int launch_deltanet(const DnDims &D, uint32_t batch, const float *conv_kernel, const float *dt_bias, const float *ssm_a, const float *norm_w,
                     const float *qkv, const float *z, const float *ba, float *conv_state, float *rec_state,
                     float *qk, float *v, float *beta, float *gate, float *core, float *out, cudaStream_t s) {

@@ -8,12 +8,14 @@
 // at the end of the step together with the logits.
 #include "redcuda_common.cuh"
 #include "redcuda_kernels.cuh"
+#include "redcuda_moe_mma.cuh"
 #include "redcuda_gguf.h"
 #include "../../include/redcuda.h"
 #include "../../include/rl_engine.h"
 
 #include <math.h>
 #include <stdlib.h>
+#include <algorithm>
 #include <chrono>
 #include <new>
 #include <vector>
@@ -25,11 +27,12 @@ const uint32_t *moe_last_ids_device(const redcuda_moe *m);   // redcuda_moe.cu
 static double now_ms() { return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
 
 // ---- small kernels ----
-// x = dequantised embedding row of *token (block = 256 threads)
+// out[b] = dequantised embedding row of token[b] (grid = tokens, block = 256 threads)
 __global__ void k_embed_row(const uint8_t *__restrict__ base, uint32_t type, uint64_t nb, uint32_t ncols, const uint32_t *__restrict__ token,
                             const uint8_t *iq2, const uint32_t *iq3s, float *__restrict__ out) {
     pdl_prologue();
-    const uint64_t row = *token;
+    const uint64_t row = token[blockIdx.x];
+    out += (size_t)blockIdx.x * ncols;
     if (type == RC_F32) { for (uint32_t i = threadIdx.x; i < ncols; i += blockDim.x) out[i] = reinterpret_cast<const float *>(base)[row * ncols + i]; return; }
     if (type == RC_F16) { for (uint32_t i = threadIdx.x; i < ncols; i += blockDim.x) out[i] = __half2float(__ushort_as_half(reinterpret_cast<const unsigned short *>(base)[row * ncols + i])); return; }
     const RcBooks bk{iq2, iq3s};
@@ -52,11 +55,15 @@ __device__ __forceinline__ double block_sum_d(double v, double *red) {
     return t;
 }
 
-// normed = RMSNorm(x [+ branch]) * w (engine_cpu.c:96-101, 418-424); resid_out (optional) = x + branch. One block.
+// normed = RMSNorm(x [+ branch]) * w (engine_cpu.c:96-101, 418-424); resid_out (optional) = x + branch. One block per token.
 __global__ void __launch_bounds__(1024) k_rmsnorm(const float *__restrict__ x, const float *__restrict__ branch, const float *__restrict__ w,
                                                   uint32_t n, float eps, float *__restrict__ resid_out, float *__restrict__ normed) {
     pdl_prologue();
     __shared__ double red[32];
+    const size_t tok_off = (size_t)blockIdx.x * n;
+    x += tok_off; normed += tok_off;
+    if (branch) branch += tok_off;
+    if (resid_out) resid_out += tok_off;
     double ss = 0.0;
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
         float v = x[i];
@@ -80,7 +87,7 @@ __device__ __forceinline__ float from_kv(float v) { return v; }
 __device__ __forceinline__ float from_kv(__half v) { return __half2float(v); }
 
 // Per-head RMSNorm of q and k, NeoX RoPE on the first rope_dims, K/V rows appended to the cache (engine_cpu.c:277-296).
-// grid = n_head + 2 * n_kv blocks of head_dim threads.
+// grid = (n_head + 2 * n_kv, tokens) blocks of head_dim threads; token z sits at position pos_p[z].
 template <typename KV>
 __global__ void k_attn_prep(const float *__restrict__ qg, const float *__restrict__ kraw, const float *__restrict__ vraw,
                             const float *__restrict__ qn, const float *__restrict__ kn, uint32_t n_head, uint32_t n_kv, uint32_t hd,
@@ -89,7 +96,9 @@ __global__ void k_attn_prep(const float *__restrict__ qg, const float *__restric
     pdl_prologue();
     extern __shared__ float sh[];
     __shared__ double red[32];
-    const uint32_t b = blockIdx.x, tid = threadIdx.x, pos = *pos_p;      // the position lives in device memory: a captured graph replays for every token
+    const uint32_t b = blockIdx.x, tid = threadIdx.x, z = blockIdx.y, pos = pos_p[z];   // the position lives in device memory: a captured graph replays for every token
+    qg += (size_t)z * n_head * 2u * hd; kraw += (size_t)z * n_kv * hd; vraw += (size_t)z * n_kv * hd;
+    query += (size_t)z * n_head * hd; gate += (size_t)z * n_head * hd;
     if (b >= n_head + n_kv) {      // value head: plain append
         const uint32_t kh = b - n_head - n_kv;
         vcache[((size_t)pos * n_kv + kh) * hd + tid] = to_kv<KV>(vraw[(size_t)kh * hd + tid]);
@@ -117,7 +126,8 @@ __global__ void k_attn_prep(const float *__restrict__ qg, const float *__restric
     else kcache[((size_t)pos * n_kv + h) * hd + tid] = to_kv<KV>(outv);
 }
 
-// Split-K decode attention. grid = (n_kv, nsplit), block = 256 (8 warps). Every block serves the G query heads of one
+// Split-K decode attention. grid = (n_kv, nsplit, tokens), block = 256 (8 warps); token z attends to positions <= pos_p[z]
+// (the K/V rows of a whole prefill chunk are appended before this runs, so the mask is the sequence length alone). Every block serves the G query heads of one
 // K/V head over a slice of positions (K and V rows are read once for all G heads); a warp takes every 8th position,
 // a lane VPL = head_dim/32 consecutive dimensions; online softmax per head. Partials: m, l and the accumulator.
 template <typename KV, int VPL, int G>
@@ -128,7 +138,10 @@ __global__ void __launch_bounds__(256) k_attn_decode(const float *__restrict__ q
     extern __shared__ float sm[];            // [8][G][hd] accumulators, then [8][G] m, [8][G] l
     constexpr uint32_t hd = VPL * 32u;
     const uint32_t kvh = blockIdx.x, split = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint32_t seq_len = *pos_p + 1u;
+    const uint32_t n_head = n_kv * G;
+    const uint32_t seq_len = pos_p[blockIdx.z] + 1u;
+    query += (size_t)blockIdx.z * n_head * hd;
+    part_m += (size_t)blockIdx.z * n_head * nsplit; part_l += (size_t)blockIdx.z * n_head * nsplit; part_acc += (size_t)blockIdx.z * n_head * nsplit * hd;
     // slices of at least 32 positions; at short sequences the trailing blocks find an empty slice and report m = -inf
     const uint32_t per = max((seq_len + nsplit - 1u) / nsplit, 32u), p_begin = min(split * per, seq_len), p_end = min(seq_len, p_begin + per);
     float q[G][VPL], acc[G][VPL], m[G], l[G];
@@ -190,11 +203,13 @@ __global__ void __launch_bounds__(256) k_attn_decode(const float *__restrict__ q
     }
 }
 
-// merge the split partials, normalise, apply the sigmoid output gate (engine_cpu.c:312-317). grid = n_head, block = hd
+// merge the split partials, normalise, apply the sigmoid output gate (engine_cpu.c:312-317). grid = (n_head, tokens), block = hd
 __global__ void k_attn_merge(const float *__restrict__ part_m, const float *__restrict__ part_l, const float *__restrict__ part_acc,
                              const float *__restrict__ gate, uint32_t nsplit, uint32_t hd, float *__restrict__ gated) {
     pdl_prologue();
     const uint32_t h = blockIdx.x, d = threadIdx.x;
+    const size_t zoff = (size_t)blockIdx.y * gridDim.x;
+    part_m += zoff * nsplit; part_l += zoff * nsplit; part_acc += zoff * nsplit * hd; gate += zoff * hd; gated += zoff * hd;
     float M = -INFINITY;
     for (uint32_t s = 0; s < nsplit; ++s) M = fmaxf(M, part_m[(size_t)h * nsplit + s]);
     float L = 0.f, A = 0.f;
@@ -270,7 +285,11 @@ struct rl_engine {
     cudaGraphExec_t graph_greedy = nullptr;      // one greedy token (step + LM head + argmax), captured after the first eager token
     bool graph_failed = false;
     uint64_t graph_launches = 0;
-    uint32_t max_split = 64;
+    uint32_t max_split = 64, pf_split = 8;
+    uint32_t pb = 1;                             // tokens per prefill chunk; every per-token scratch buffer holds pb rows
+    float *bx[2] = {nullptr, nullptr};           // layer input / output of a chunk (ping-pong)
+    int8_t *xq = nullptr; float *sx = nullptr;   // chunk activations as digit planes for the Q6_K tensor-core projections
+    uint32_t *tok_chunk_d = nullptr, *pos_chunk_d = nullptr;
     // host mirrors
     std::vector<float> embed_h, layer_out_h, final_norm_h;
     std::vector<uint32_t> router_ids_h;
@@ -295,26 +314,28 @@ static int eng_gemv(rl_engine *e, const DMat *mats, float *const *outs, uint32_t
     return launch_gemv(A, e->stream);
 }
 
+// ntok tokens at positions pos[0..ntok): decode passes e->pos_d (one token), a prefill chunk its position list
 template <typename KV>
-static int eng_attention(rl_engine *e, const EngLayer &L, char *error, size_t cap) {
+static int eng_attention(rl_engine *e, const EngLayer &L, uint32_t ntok, const uint32_t *pos, char *error, size_t cap) {
     const rl_engine_info &in = e->info;
     const uint32_t hd = in.head_dim, nq = in.n_head, nkv = in.n_head_kv, G = nq / nkv;
     const size_t kv_layer = (size_t)in.context * nkv * hd;
     KV *kc = (KV *)e->kcache + kv_layer * L.aidx, *vc = (KV *)e->vcache + kv_layer * L.aidx;
     cudaStream_t s = e->stream;
     prof_begin("attn_prep", s);
-    RC_LAUNCH((k_attn_prep<KV>), nq + 2u * nkv, hd, hd * sizeof(float), s, e->qg, e->kraw, e->vraw, L.q_norm, L.k_norm, nq, nkv, hd, in.rope_dims, in.rope_freq_base,
-                                                                 in.rms_eps, e->pos_d, e->query, e->gate, kc, vc);
+    RC_LAUNCH((k_attn_prep<KV>), dim3(nq + 2u * nkv, ntok), hd, hd * sizeof(float), s, e->qg, e->kraw, e->vraw, L.q_norm, L.k_norm, nq, nkv, hd, in.rope_dims, in.rope_freq_base,
+                                                                 in.rms_eps, pos, e->query, e->gate, kc, vc);
     prof_end(s);
     uint32_t nsplit = (in.context + 31u) / 32u;                 // fixed per engine (graph replay): enough slices for a full context
     nsplit = nsplit < 1u ? 1u : nsplit > e->max_split ? e->max_split : nsplit;
+    if (ntok > 1u && nsplit > e->pf_split) nsplit = e->pf_split;     // a chunk brings its own parallelism (and the partials are per token)
     const float scale = (float)(1.0 / sqrt((double)hd));
     const size_t smem = (size_t)(8u * G * hd + 16u * G) * sizeof(float);
-    const dim3 grid(nkv, nsplit);
+    const dim3 grid(nkv, nsplit, ntok);
     prof_begin("attn_decode", s);
 #define ENG_ATTN(VPL_, G_) do { \
         if (smem > 48u * 1024u) ENG_CUDA(cudaFuncSetAttribute(k_attn_decode<KV, VPL_, G_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        RC_LAUNCH((k_attn_decode<KV, VPL_, G_>), grid, 256, smem, s, e->query, kc, vc, nkv, e->pos_d, nsplit, scale, e->part_m, e->part_l, e->part_acc); } while (0)
+        RC_LAUNCH((k_attn_decode<KV, VPL_, G_>), grid, 256, smem, s, e->query, kc, vc, nkv, pos, nsplit, scale, e->part_m, e->part_l, e->part_acc); } while (0)
     if (hd == 256u && G == 8u) ENG_ATTN(8, 8);
     else if (hd == 128u && G == 8u) ENG_ATTN(4, 8);
     else if (hd == 128u && G == 4u) ENG_ATTN(4, 4);
@@ -325,7 +346,7 @@ static int eng_attention(rl_engine *e, const EngLayer &L, char *error, size_t ca
 #undef ENG_ATTN
     prof_end(s);
     prof_begin("attn_merge", s);
-    RC_LAUNCH((k_attn_merge), nq, hd, 0, s, e->part_m, e->part_l, e->part_acc, e->gate, nsplit, hd, e->gated);
+    RC_LAUNCH((k_attn_merge), dim3(nq, ntok), hd, 0, s, e->part_m, e->part_l, e->part_acc, e->gate, nsplit, hd, e->gated);
     prof_end(s);
     g_launches.fetch_add(3);
     ENG_CUDA(cudaGetLastError());
@@ -361,8 +382,8 @@ static int eng_step_device(rl_engine *e, bool want_logits, char *error, size_t c
             const DMat mats[3] = {L.q, L.k, L.v};
             float *outs[3] = {e->qg, e->kraw, e->vraw};
             ENG_RC(eng_gemv(e, mats, outs, 3, e->normed, "attn_proj_gemv"));
-            if (e->kv_half) { if (!eng_attention<__half>(e, L, error, cap)) return 0; }
-            else { if (!eng_attention<float>(e, L, error, cap)) return 0; }
+            if (e->kv_half) { if (!eng_attention<__half>(e, L, 1u, e->pos_d, error, cap)) return 0; }
+            else { if (!eng_attention<float>(e, L, 1u, e->pos_d, error, cap)) return 0; }
             float *o1[1] = {e->branch};
             ENG_RC(eng_gemv(e, &L.o, o1, 1, e->gated, "attn_out_gemv"));
         }
@@ -387,6 +408,94 @@ static int eng_step_device(rl_engine *e, bool want_logits, char *error, size_t c
     g_launches.fetch_add(1);
     ENG_CUDA(cudaGetLastError());
     e->position++;
+    return 1;
+}
+
+// Projections of a chunk: Q6_K matrices with >= 3 tokens go through the tensor-core kernel on the digit planes of x
+// (quantised once per input, `quantised` says whether e->xq already holds x), everything else through the GEMV.
+static int eng_proj(rl_engine *e, const DMat *mats, float *const *outs, uint32_t n, const float *x, uint32_t ntok, bool *quantised, const char *tag) {
+    static const bool want_mma = !(getenv("RC_MOE_PATH") && getenv("RC_MOE_PATH")[0] == 'c');
+    GemvArgs A{};
+    A.ntok = ntok; A.x = x; A.x_stride = mats[0].ncols; A.tag = tag;
+    uint32_t j = 0;
+    for (uint32_t i = 0; i < n; ++i) {
+        const DMat &M = mats[i];
+        if (want_mma && ntok >= 3u && M.type == RC_Q6_K && M.nrows % 16u == 0 && M.ncols % 256u == 0) {
+            if (!*quantised) { if (!launch_quant_act(x, M.ncols, ntok, M.ncols, e->xq, e->sx, e->stream)) return 0; *quantised = true; }
+            if (!launch_q6k_mma(M.base, nullptr, M.nb, M.nrows, M.ncols, ntok, e->xq, e->sx, outs[i], M.nrows, tag, e->stream)) return 0;
+            continue;
+        }
+        GemvJob &J = A.job[j++];
+        J.w0 = M.base; J.w1 = nullptr; J.out = outs[i]; J.nb = M.nb; J.type = M.type; J.nrows = M.nrows; J.ncols = M.ncols; J.out_stride = M.nrows; J.epi = GEMV_STORE;
+    }
+    if (!j) return 1;
+    A.njobs = j;
+    return launch_gemv(A, e->stream);
+}
+
+// A chunk of n consecutive tokens (ids in e->tok_chunk_d, positions in e->pos_chunk_d) through every layer at once:
+// projections, router and experts see the n tokens as a batch (each weight byte is read once per chunk); the DeltaNet
+// recurrence runs over the tokens inside one kernel with the state in registers; attention appends the chunk's K/V
+// rows and masks by position. The mirrors are left holding the last token's rows, as after n single steps
+// (the reference's chunked prefill, native/redlite_native_engine.c:600-640).
+static int eng_prefill_chunk(rl_engine *e, uint32_t n, bool want_logits, char *error, size_t cap) {
+    const rl_engine_info &in = e->info;
+    cudaStream_t s = e->stream;
+    if (e->position + n > in.context) ENG_FAIL("context of %u positions is full", in.context);
+    const DnDims D{in.d_conv, in.d_state, in.n_group, in.dt_rank, in.d_inner, in.channels, in.rms_eps};
+    const size_t last = (size_t)(n - 1u);
+    prof_begin("embed", s);
+    RC_LAUNCH((k_embed_row), n, 256, 0, s, e->tok_embd.base, e->tok_embd.type, e->tok_embd.nb, in.hidden, e->tok_chunk_d, books_iq2(), books_iq3s(), e->bx[0]);
+    prof_end(s);
+    g_launches.fetch_add(1);
+    ENG_CUDA(cudaMemcpyAsync(e->embed_d, e->bx[0] + last * in.hidden, in.hidden * 4u, cudaMemcpyDeviceToDevice, s));
+    const float *x = e->bx[0];
+    for (uint32_t l = 0; l < in.n_layer; ++l) {
+        const EngLayer &L = e->layers[l];
+        prof_begin("rmsnorm", s);
+        RC_LAUNCH((k_rmsnorm), n, 1024, 0, s, x, nullptr, L.attn_norm, in.hidden, in.rms_eps, nullptr, e->normed);
+        prof_end(s);
+        g_launches.fetch_add(1);
+        bool qd = false;
+        if (L.recurrent) {
+            const DMat mats[3] = {L.qkv, L.z, L.ba};
+            float *outs[3] = {e->qkv, e->z, e->ba};
+            ENG_RC(eng_proj(e, mats, outs, 3, e->normed, n, &qd, "dn_proj"));
+            ENG_RC(launch_deltanet_seq(D, n, L.conv_k, L.dt, L.a, L.ssm_norm, e->qkv, e->z, e->ba, e->conv + (size_t)L.ridx * (in.d_conv - 1u) * in.channels,
+                                       e->rec + (size_t)L.ridx * in.dt_rank * in.d_state * in.d_state, e->dn_qk, e->dn_v, e->dn_beta, e->dn_gate, e->dn_core, e->ng, s));
+            float *o1[1] = {e->branch};
+            qd = false;
+            ENG_RC(eng_proj(e, &L.ssm_out, o1, 1, e->ng, n, &qd, "dn_out"));
+        } else {
+            const DMat mats[3] = {L.q, L.k, L.v};
+            float *outs[3] = {e->qg, e->kraw, e->vraw};
+            ENG_RC(eng_proj(e, mats, outs, 3, e->normed, n, &qd, "attn_proj"));
+            if (e->kv_half) { if (!eng_attention<__half>(e, L, n, e->pos_chunk_d, error, cap)) return 0; }
+            else { if (!eng_attention<float>(e, L, n, e->pos_chunk_d, error, cap)) return 0; }
+            float *o1[1] = {e->branch};
+            qd = false;
+            ENG_RC(eng_proj(e, &L.o, o1, 1, e->gated, n, &qd, "attn_out"));
+        }
+        prof_begin("resid_rmsnorm", s);
+        RC_LAUNCH((k_rmsnorm), n, 1024, 0, s, x, e->branch, L.post_norm, in.hidden, in.rms_eps, e->resid, e->normed);
+        prof_end(s);
+        g_launches.fetch_add(1);
+        float *xo = e->bx[(l + 1u) & 1u];
+        ENG_RC(redcuda_moe_forward_device(L.moe, n, e->normed, nullptr, e->resid, xo, s));
+        ENG_CUDA(cudaMemcpyAsync(e->router_ids_d + (size_t)l * RL_ENGINE_MAX_TOPK, moe_last_ids_device(L.moe) + last * in.top_k, in.top_k * sizeof(uint32_t), cudaMemcpyDeviceToDevice, s));
+        ENG_CUDA(cudaMemcpyAsync(e->layer_out_d + (size_t)l * in.hidden, xo + last * in.hidden, in.hidden * 4u, cudaMemcpyDeviceToDevice, s));
+        x = xo;
+    }
+    prof_begin("rmsnorm", s);
+    RC_LAUNCH((k_rmsnorm), 1, 1024, 0, s, x + last * in.hidden, nullptr, e->output_norm, in.hidden, in.rms_eps, nullptr, e->final_norm_d);
+    prof_end(s);
+    g_launches.fetch_add(1);
+    if (want_logits) {
+        float *o1[1] = {e->logits_d};
+        ENG_RC(eng_gemv(e, &e->output, o1, 1, e->final_norm_d, "lm_head_gemv"));
+    }
+    ENG_CUDA(cudaGetLastError());
+    e->position += n;
     return 1;
 }
 
@@ -474,6 +583,10 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
     }
     ENG_CUDA(cudaGetDevice(&e->device));
     ENG_CUDA(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
+    // Prefill chunk: the reference defaults to 2048 tokens per batched dispatch (native/redlite_native_engine.h:37); here the
+    // chunk also sizes every layer's expert workspace, so the default is 128 and the ceiling 512. 1 = token by token.
+    e->pb = e->cfg.prefill_batch ? std::min(e->cfg.prefill_batch, 512u) : 128u;
+    if (e->pb > in.context) e->pb = in.context;
 
     // ---- layer kinds from tensor names (native/redlite_native_layer_map.c:114-124), sizes of the dense arena
     e->layers.resize(in.n_layer);
@@ -541,7 +654,7 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
         redcuda_moe_desc d;
         memset(&d, 0, sizeof(d));
         d.hidden = in.hidden; d.n_expert = in.n_expert; d.top_k = in.top_k; d.ffn = (uint32_t)ge->shape[1]; d.ffn_sh = (uint32_t)sg->shape[1];
-        d.type_gu = ge->type; d.type_down = de->type; d.type_sh = sg->type; d.expert_begin = 0; d.expert_count = in.n_expert; d.max_tokens = 1; d.weights_on_device = 0;
+        d.type_gu = ge->type; d.type_down = de->type; d.type_sh = sg->type; d.expert_begin = 0; d.expert_count = in.n_expert; d.max_tokens = e->pb; d.weights_on_device = 0;
         d.router = (const float *)g.data(tr); d.gate_exps = g.data(ge); d.up_exps = g.data(ue); d.down_exps = g.data(de);
         d.sh_gate_inp = (const float *)g.data(tg); d.sh_gate = g.data(sg); d.sh_up = g.data(su); d.sh_down = g.data(sd);
         e->ffn = d.ffn;
@@ -568,12 +681,16 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
     size_t w = 0;
     auto take = [&](size_t bytes) { const size_t o = w; w = (w + bytes + 255u) / 256u * 256u; return o; };
     const uint32_t qc = in.n_head * in.head_dim, kvc = in.n_head_kv * in.head_dim;
-    const size_t o_norm = take(in.hidden * 4u), o_br = take(in.hidden * 4u), o_res = take(in.hidden * 4u), o_qkv = take(in.channels * 4u), o_z = take(in.d_inner * 4u),
-                 o_ba = take(2u * in.dt_rank * 4u), o_ng = take(in.d_inner * 4u), o_dqk = take(2u * in.n_group * in.d_state * 4u), o_dv = take(in.d_inner * 4u),
-                 o_db = take(in.dt_rank * 4u), o_dg = take(in.dt_rank * 4u), o_dc = take(in.d_inner * 4u), o_qg = take(2u * qc * 4u), o_kr = take(kvc * 4u), o_vr = take(kvc * 4u),
-                 o_qu = take(qc * 4u), o_ga = take(qc * 4u), o_gd = take(qc * 4u), o_pm = take((size_t)in.n_head * e->max_split * 4u), o_pl = take((size_t)in.n_head * e->max_split * 4u),
-                 o_pa = take((size_t)in.n_head * e->max_split * in.head_dim * 4u), o_em = take(in.hidden * 4u), o_lo = take((size_t)in.n_layer * in.hidden * 4u),
-                 o_fn = take(in.hidden * 4u), o_lg = take((size_t)in.vocab * 4u), o_ri = take((size_t)in.n_layer * RL_ENGINE_MAX_TOPK * 4u), o_tk = take(16), o_gt = take(4096u * 4u);
+    const size_t T = e->pb;          // rows of every per-token buffer (decode uses row 0)
+    const size_t parts = std::max<size_t>(e->max_split, T * e->pf_split);
+    const uint32_t widest = std::max(std::max(in.hidden, in.d_inner), qc);
+    const size_t o_norm = take(T * in.hidden * 4u), o_br = take(T * in.hidden * 4u), o_res = take(T * in.hidden * 4u), o_qkv = take(T * in.channels * 4u), o_z = take(T * in.d_inner * 4u),
+                 o_ba = take(T * 2u * in.dt_rank * 4u), o_ng = take(T * in.d_inner * 4u), o_dqk = take(T * 2u * in.n_group * in.d_state * 4u), o_dv = take(T * in.d_inner * 4u),
+                 o_db = take(T * in.dt_rank * 4u), o_dg = take(T * in.dt_rank * 4u), o_dc = take(T * in.d_inner * 4u), o_qg = take(T * 2u * qc * 4u), o_kr = take(T * kvc * 4u), o_vr = take(T * kvc * 4u),
+                 o_qu = take(T * qc * 4u), o_ga = take(T * qc * 4u), o_gd = take(T * qc * 4u), o_pm = take((size_t)in.n_head * parts * 4u), o_pl = take((size_t)in.n_head * parts * 4u),
+                 o_pa = take((size_t)in.n_head * parts * in.head_dim * 4u), o_em = take(in.hidden * 4u), o_lo = take((size_t)in.n_layer * in.hidden * 4u),
+                 o_fn = take(in.hidden * 4u), o_lg = take((size_t)in.vocab * 4u), o_ri = take((size_t)in.n_layer * RL_ENGINE_MAX_TOPK * 4u), o_tk = take(16), o_gt = take(4096u * 4u),
+                 o_bx0 = take(T * in.hidden * 4u), o_bx1 = take(T * in.hidden * 4u), o_xq = take(T * 3u * widest), o_sx = take(T * 4u), o_tc = take(T * 4u), o_pc = take(T * 4u);
     if (!e->scratch.alloc(w)) ENG_FAIL("%s", redcuda_last_error());
     uint8_t *B = e->scratch.as<uint8_t>();
     ENG_CUDA(cudaMemsetAsync(B, 0, w, e->stream));
@@ -584,9 +701,11 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
     e->part_acc = (float *)(B + o_pa); e->embed_d = (float *)(B + o_em); e->layer_out_d = (float *)(B + o_lo); e->final_norm_d = (float *)(B + o_fn);
     e->logits_d = (float *)(B + o_lg); e->router_ids_d = (uint32_t *)(B + o_ri); e->token_d = (uint32_t *)(B + o_tk); e->gen_tokens_d = (uint32_t *)(B + o_gt);
     e->pos_d = e->token_d + 2; e->gen_count_d = e->token_d + 3;
+    e->bx[0] = (float *)(B + o_bx0); e->bx[1] = (float *)(B + o_bx1); e->xq = (int8_t *)(B + o_xq); e->sx = (float *)(B + o_sx);
+    e->tok_chunk_d = (uint32_t *)(B + o_tc); e->pos_chunk_d = (uint32_t *)(B + o_pc);
     e->embed_h.assign(in.hidden, 0.f); e->layer_out_h.assign((size_t)in.n_layer * in.hidden, 0.f); e->final_norm_h.assign(in.hidden, 0.f);
     e->router_ids_h.assign((size_t)in.n_layer * RL_ENGINE_MAX_TOPK, 0u);
-    ENG_CUDA(cudaMallocHost((void **)&e->token_pin, 64));
+    ENG_CUDA(cudaMallocHost((void **)&e->token_pin, 64u + 2u * T * 4u));      // [16 words][chunk tokens][chunk positions]
     if (!eng_reset_state(e, error, cap)) return 0;
     e->preload_ms = now_ms() - t_open;
     return 1;
@@ -655,24 +774,41 @@ int rl_engine_step(rl_engine *e, rl_engine_backend backend, uint32_t token, floa
 
 int rl_engine_prefill(rl_engine *e, rl_engine_backend backend, const uint32_t *tokens, uint32_t count, float *logits, rl_engine_step_stats *stats,
                       char *error, size_t cap) {
-    // token by token, like the reference's prefill_batch = 1 mode (native/redlite_native_engine.c:608-622); only the last token runs the LM head
+    // chunks of prefill_batch tokens (native/redlite_native_engine.c:600-640); a chunk of one token, and prefill_batch = 1,
+    // take the single-token path. Only the last token runs the LM head.
     if (!e || !tokens || !count) { eng_err(error, cap, "invalid prefill arguments"); return 0; }
     if (backend != RL_BACKEND_GPU) { eng_err(error, cap, "the CPU backend is not part of this library"); return 0; }
     const double t0 = now_ms();
     if (stats) memset(stats, 0, sizeof(*stats));
     ENG_CUDA(cudaSetDevice(e->device));
-    for (uint32_t i = 0; i < count; ++i) {
-        if (tokens[i] >= e->info.vocab) { eng_err(error, cap, "token id out of range"); return 0; }
-        ENG_CUDA(cudaStreamSynchronize(e->stream));      // token_pin is reused
-        e->token_pin[0] = tokens[i];
-        ENG_CUDA(cudaMemcpyAsync(e->token_d, e->token_pin, 4, cudaMemcpyHostToDevice, e->stream));
-        if (!eng_step_device(e, logits != nullptr && i + 1u == count, error, cap)) return 0;
+    for (uint32_t i = 0; i < count; ++i) if (tokens[i] >= e->info.vocab) { eng_err(error, cap, "token id out of range"); return 0; }
+    if (e->position + (uint64_t)count > e->info.context) { eng_err(error, cap, "prompt does not fit the context"); return 0; }
+    uint32_t *tok_pin = e->token_pin + 16, *pos_pin = tok_pin + e->pb;
+    for (uint32_t i = 0; i < count;) {
+        const uint32_t n = std::min(e->pb, count - i);
+        const bool last = i + n == count;
+        ENG_CUDA(cudaStreamSynchronize(e->stream));      // the pinned staging words are reused
+        if (n == 1u) {
+            e->token_pin[0] = tokens[i];
+            ENG_CUDA(cudaMemcpyAsync(e->token_d, e->token_pin, 4, cudaMemcpyHostToDevice, e->stream));
+            if (!eng_step_device(e, logits != nullptr && last, error, cap)) return 0;
+        } else {
+            for (uint32_t t = 0; t < n; ++t) { tok_pin[t] = tokens[i + t]; pos_pin[t] = e->position + t; }
+            e->token_pin[2] = e->position + n;
+            ENG_CUDA(cudaMemcpyAsync(e->tok_chunk_d, tok_pin, n * 4u, cudaMemcpyHostToDevice, e->stream));
+            ENG_CUDA(cudaMemcpyAsync(e->pos_chunk_d, pos_pin, n * 4u, cudaMemcpyHostToDevice, e->stream));
+            if (!eng_prefill_chunk(e, n, logits != nullptr && last, error, cap)) return 0;
+            ENG_CUDA(cudaMemcpyAsync(e->pos_d, e->token_pin + 2, 4, cudaMemcpyHostToDevice, e->stream));
+        }
+        i += n;
     }
     if (!eng_copy_mirrors(e, logits, error, cap)) return 0;
     if (stats) { stats->total_ms = now_ms() - t0; stats->gpu_ms = stats->total_ms; }
     if (error && cap) error[0] = '\0';
     return 1;
 }
+
+uint32_t rl_engine_prefill_batch(const rl_engine *e) { return e ? e->pb : 0u; }
 
 int rl_engine_generate_greedy(rl_engine *e, uint32_t token, uint32_t n_new, uint32_t *out_tokens, rl_engine_step_stats *stats, char *error, size_t cap) {
     if (!e || !out_tokens || !n_new || n_new > 4096u) { eng_err(error, cap, "invalid generate arguments (1..4096 new tokens)"); return 0; }

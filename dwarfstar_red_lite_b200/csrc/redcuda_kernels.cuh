@@ -40,6 +40,10 @@ struct DnDims { uint32_t d_conv, S, groups, rank, d_inner, channels; float eps; 
 int launch_deltanet(const DnDims &D, uint32_t batch, const float *conv_kernel, const float *dt_bias, const float *ssm_a, const float *norm_w,
                     const float *qkv, const float *z, const float *ba, float *conv_state, float *rec_state,
                     float *qk, float *v, float *beta, float *gate, float *core, float *out, cudaStream_t s);
+// T consecutive tokens of one sequence (prefill chunk): rows of qkv / z / ba / out and of the scratch are per token
+int launch_deltanet_seq(const DnDims &D, uint32_t T, const float *conv_kernel, const float *dt_bias, const float *ssm_a, const float *norm_w,
+                    const float *qkv, const float *z, const float *ba, float *conv_state, float *rec_state,
+                    float *qk, float *v, float *beta, float *gate, float *core, float *out, cudaStream_t s);
 
 int launch_vec_sigmoid(const float *w, const float *x, uint32_t x_stride, uint32_t ncols, uint32_t ntok, float *out, cudaStream_t stream);
 

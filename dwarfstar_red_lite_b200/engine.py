@@ -37,7 +37,7 @@ class RlStepStats(C.Structure):
 ENGINE_EXPORTS = ["rl_engine_config_default", "rl_engine_open", "rl_engine_close", "rl_engine_info_get", "rl_engine_reset", "rl_engine_position",
                   "rl_engine_bench_set_position", "rl_engine_step", "rl_engine_prefill", "rl_engine_last_embedding", "rl_engine_last_layer_output",
                   "rl_engine_last_final_norm", "rl_engine_last_router_ids", "rl_engine_experts_preloaded", "rl_engine_full_residency_mib",
-                  "rl_engine_embed_token", "rl_engine_generate_greedy", "rl_engine_step_bytes"]
+                  "rl_engine_embed_token", "rl_engine_generate_greedy", "rl_engine_step_bytes", "rl_engine_prefill_batch"]
 
 
 def _bind():
@@ -68,6 +68,8 @@ def _bind():
     L.rl_engine_full_residency_mib.restype = C.c_uint64
     L.rl_engine_full_residency_mib.argtypes = [C.c_void_p]
     L.rl_engine_embed_token.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_char_p, C.c_size_t]
+    L.rl_engine_prefill_batch.restype = C.c_uint32
+    L.rl_engine_prefill_batch.argtypes = [C.c_void_p]
     L.rl_engine_step_bytes.restype = C.c_uint64
     L.rl_engine_step_bytes.argtypes = [C.c_void_p]
     L._engine_bound = True
@@ -77,12 +79,12 @@ def _bind():
 class Engine:
     """rl_engine on the CUDA backend over a GGUF file."""
 
-    def __init__(self, path: str, context: int = 4096, top_k: int = 0):
+    def __init__(self, path: str, context: int = 4096, top_k: int = 0, prefill_batch: int = 0):
         _ensure_books()
         self.L = _bind()
         cfg = RlEngineConfig()
         self.L.rl_engine_config_default(C.byref(cfg))
-        cfg.context, cfg.top_k, cfg.enable_cpu, cfg.enable_gpu = context, top_k, 0, 1
+        cfg.context, cfg.top_k, cfg.enable_cpu, cfg.enable_gpu, cfg.prefill_batch = context, top_k, 0, 1, prefill_batch
         self._err = C.create_string_buffer(1024)
         self._e = self.L.rl_engine_open(path.encode(), C.byref(cfg), self._err, 1024)
         if not self._e:
@@ -151,6 +153,10 @@ class Engine:
         out = np.empty(self.info.hidden, np.float32)
         self._ok(self.L.rl_engine_embed_token(self._e, token, out.ctypes.data, self._err, 1024), "rl_engine_embed_token")
         return out
+
+    @property
+    def prefill_batch(self) -> int:
+        return int(self.L.rl_engine_prefill_batch(self._e))
 
     def step_bytes(self) -> int:
         return int(self.L.rl_engine_step_bytes(self._e))

@@ -25,7 +25,7 @@ EXPORTS = [
     "rl_engine_config_default", "rl_engine_open", "rl_engine_close", "rl_engine_info_get", "rl_engine_reset", "rl_engine_position",
     "rl_engine_bench_set_position", "rl_engine_step", "rl_engine_prefill", "rl_engine_last_embedding", "rl_engine_last_layer_output",
     "rl_engine_last_final_norm", "rl_engine_last_router_ids", "rl_engine_experts_preloaded", "rl_engine_full_residency_mib",
-    "rl_engine_embed_token", "rl_engine_generate_greedy", "rl_engine_step_bytes",
+    "rl_engine_embed_token", "rl_engine_generate_greedy", "rl_engine_step_bytes", "rl_engine_prefill_batch",
 ]
 
 

@@ -100,6 +100,77 @@ def test_midsize_model_full_head_shapes(tmp_path, monkeypatch):
         eng.close()
 
 
+def _compare_last(eng, om, dims, gl, ml, tag):
+    for l in range(dims.n_layer):
+        assert np.array_equal(eng.router_ids(l), om.router_ids(l)), (tag, l, eng.router_ids(l), om.router_ids(l))
+        a, b = eng.layer_out(l), om.layer_out(l)
+        assert np.max(np.abs(a - b)) <= REL_OUT * np.max(np.abs(b)), (tag, l, float(np.max(np.abs(a - b)) / np.max(np.abs(b))))
+    assert np.max(np.abs(gl - ml)) <= REL_OUT * np.max(np.abs(ml)) + 1e-6, tag
+    assert int(np.argmax(gl)) == int(np.argmax(ml)), tag
+
+
+@pytest.mark.parametrize("chunk", [1, 2, 5, 8, 64])
+def test_tiny_model_chunked_prefill(tmp_path, chunk, monkeypatch):
+    """rl_engine_prefill in chunks (ragged last chunk, chunk larger than the prompt, two calls in a row) leaves the same
+    mirrors, logits and state as the oracle's token-by-token pass; decode steps after it agree as well."""
+    monkeypatch.setenv("RL_KV_F16", "0")
+    dims = synth.tiny_model_dims(n_layer=8)
+    sm = synth.model(77, dims)
+    path = str(tmp_path / "tiny.gguf")
+    gguf_writer.write_gguf(path, sm)
+    eng = Engine(path, context=dims.context, prefill_batch=chunk)
+    om = ol.OracleModel(sm, kv_f16=False)
+    try:
+        assert eng.prefill_batch == chunk
+        prompt = np.random.default_rng(5).integers(0, dims.vocab, 21).astype(np.uint32)
+        gl = eng.prefill(prompt[:13])
+        for t in prompt[:13]:
+            ml = om.step(int(t), threads=os.cpu_count() or 1)
+        assert eng.position == 13
+        _compare_last(eng, om, dims, gl, ml, ("first call", chunk))
+        gl = eng.prefill(prompt[13:])                      # continues from position 13
+        for t in prompt[13:]:
+            ml = om.step(int(t), threads=os.cpu_count() or 1)
+        assert eng.position == 21
+        _compare_last(eng, om, dims, gl, ml, ("second call", chunk))
+        tok = int(np.argmax(ml))
+        for step in range(4):
+            tok = _compare_step(eng, om, dims, tok, step)
+        got, _ = eng.generate_greedy(tok, 5)
+        want = []
+        for _ in range(5):
+            tok = int(np.argmax(om.step(tok, threads=os.cpu_count() or 1)))
+            want.append(tok)
+        assert list(got) == want
+    finally:
+        eng.close()
+
+
+def test_midsize_model_chunked_prefill(tmp_path, monkeypatch):
+    """Full-size head shapes: the chunk takes the tensor-core projections (Q6_K dense matrices, >= 3 tokens), the in-register
+    DeltaNet scan over 128-wide states and the batched GQA attention."""
+    monkeypatch.setenv("RL_KV_F16", "1")
+    dims = synth.ModelDims(n_layer=4, vocab=2048, n_expert=32, top_k=10, context=48)
+    sm = synth.model(56, dims)
+    path = str(tmp_path / "mid.gguf")
+    gguf_writer.write_gguf(path, sm)
+    eng = Engine(path, context=dims.context, prefill_batch=16)
+    om = ol.OracleModel(sm, kv_f16=True, context=dims.context)
+    try:
+        prompt = np.random.default_rng(9).integers(0, dims.vocab, 37).astype(np.uint32)
+        gl = eng.prefill(prompt)
+        for t in prompt:
+            ml = om.step(int(t), threads=os.cpu_count() or 1)
+        _compare_last(eng, om, dims, gl, ml, "mid")
+        tok = int(np.argmax(ml))
+        for step in range(3):
+            tok = _compare_step(eng, om, dims, tok, step)
+        with pytest.raises(Exception):
+            eng.prefill(np.zeros(dims.context, np.uint32))      # does not fit what is left of the context
+    finally:
+        eng.close()
+
+
 def test_engine_errors(tmp_path):
     with pytest.raises(Exception):
         Engine(str(tmp_path / "missing.gguf"))
