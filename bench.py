@@ -337,6 +337,91 @@ def run_decode48(args):
     eng.close()
 
 
+def run_prefill(args):
+    """BASELINE configs[4] on one GPU: chunked prefill of a random prompt through the 48-layer random-init model
+    (rl_engine_prefill; chunk = --prefill-batch tokens). Tokens/s over the whole prompt, the last token's logits copied
+    to the host. The CPU baseline is the oracle port stepping a few prompt tokens (the reference's CPU prefill is
+    token by token as well)."""
+    import dwarfstar_red_lite_b200 as rc
+    from dwarfstar_red_lite_b200 import gguf_writer, synth
+    from dwarfstar_red_lite_b200.engine import Engine
+    os.environ.setdefault("RL_KV_F16", "1")
+    n_prompt = args.prompt_tokens
+    dims = synth.ModelDims(n_layer=args.layers, context=max(args.context, n_prompt + 8))
+    tmp = os.environ.get("REDCUDA_TMP", "/tmp")
+    path = os.path.join(tmp, f"redcuda_synth_{args.layers}l_seed{args.seed}.gguf")
+    t0 = time.perf_counter()
+    size = os.path.getsize(path) if os.path.exists(path) else gguf_writer.write_gguf_streaming(path, args.seed, dims)
+    t_write = time.perf_counter() - t0
+    rc.set_codebooks()
+    eng = Engine(path, context=dims.context, prefill_batch=args.prefill_batch)
+    info, chunk = eng.info, eng.prefill_batch
+    rng = np.random.default_rng(args.seed)
+    prompt = rng.integers(0, dims.vocab, n_prompt).astype(np.uint32)
+    check = None
+    if args.check_steps > 0:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import oracle_lib as ol
+        om = ol.OracleModel(gguf_writer.load_gguf(path, dims), kv_f16=True, context=dims.context)
+        n = args.check_steps
+        gl = eng.prefill(prompt[:n])
+        for t in prompt[:n]:
+            ml = om.step(int(t), threads=os.cpu_count() or 1)
+        worst = max(float(np.max(np.abs(eng.layer_out(l) - om.layer_out(l))) / np.max(np.abs(om.layer_out(l)))) for l in range(info.n_layer))
+        ids = sum(int(not np.array_equal(eng.router_ids(l), om.router_ids(l))) for l in range(info.n_layer))
+        check = {"prompt_tokens": n, "chunk": chunk, "max_layer_rel_err_last_token": worst, "max_logit_abs_err": float(np.max(np.abs(gl - ml))),
+                 "argmax_equal": bool(int(np.argmax(gl)) == int(np.argmax(ml))), "router_id_layer_mismatches_last_token": ids}
+        del om
+    for _ in range(args.warmup):
+        eng.reset()
+        eng.prefill(prompt[: min(n_prompt, 2 * chunk)])
+    times = []
+    launches0 = rc.lib().redcuda_launch_count()
+    with ClockSampler(0) as clocks:
+        for _ in range(args.steps):
+            eng.reset()
+            t0 = time.perf_counter()
+            eng.prefill(prompt)
+            times.append((time.perf_counter() - t0) * 1e3)
+    launches = (rc.lib().redcuda_launch_count() - launches0) // max(1, args.steps)
+    ms_run = float(np.median(times))
+    tok_s = n_prompt / (ms_run * 1e-3)
+    cpu = None
+    if not args.no_cpu:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import oracle_lib as ol
+        om = ol.OracleModel(gguf_writer.load_gguf(path, dims), kv_f16=True, context=dims.context)
+        threads = os.cpu_count() or 1
+        t0, n = time.perf_counter(), 0
+        while n < 8 and (n == 0 or time.perf_counter() - t0 < args.cpu_budget_s):
+            om.step(int(prompt[n]), threads=threads)
+            n += 1
+        dt = time.perf_counter() - t0
+        cpu = {"value": n / dt, "unit": "tokens/s", "cores": threads, "kind": "port",
+               "sample": f"the first {n} prompt tokens in {dt:.1f} s (oracle port of rl_engine_cpu_step, token by token; short context, which favours the CPU)"}
+    # weight bytes one chunk has to read: every dense matrix once, plus the experts the chunk's tokens select (expected count
+    # under uniform routing); states and K/V are small beside them
+    n_chunks = (n_prompt + chunk - 1) // chunk
+    per_expert = eng.full_residency_mib() * (1 << 20) / (info.n_layer * info.n_expert)
+    uniq = info.n_expert * (1.0 - (1.0 - info.top_k / info.n_expert) ** chunk)
+    eng.set_position(0)
+    dense_bytes = eng.step_bytes() - per_expert * info.top_k * info.n_layer
+    chunk_bytes = dense_bytes + per_expert * uniq * info.n_layer
+    peak, peak_kind = measured_peak()
+    gbs = chunk_bytes * n_chunks / (ms_run * 1e-3) / 1e9
+    line = {"metric": "prefill_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_run, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"BASELINE configs[4] on one GPU: chunked prefill of {n_prompt} random tokens, chunks of {chunk}, {info.n_layer}-layer Qwen3-Next-shaped random-init model, fp16 KV",
+                       "gguf_bytes": size, "write_s": round(t_write, 1), "l2_policy": "one chunk reads ~%.2f GB of weights" % (chunk_bytes / 1e9)},
+            "roofline": {"bound": "hbm", "kernel": "whole prefill (weight bytes per chunk x chunks)", "achieved": gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                         "frac": gbs / peak, "traffic": None, "bytes_per_chunk": chunk_bytes},
+            "cpu_baseline": cpu, "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": int(n_prompt * 8), "d2h_bytes_per_step": int(info.vocab * 4 + (2 * info.n_layer + 2) * info.hidden * 4),
+                                         "note": "the timed call is the host API itself: prompt ids from host memory, logits and mirrors back"},
+            "parity": check, "gpu_launches": int(launches), "clocks": clocks.summary()}
+    print(json.dumps(line), flush=True)
+    eng.close()
+
+
 def _timed_graph(torch, step_fn, steps, warmup, device_index):
     """warm up, capture step_fn(stream) into a CUDA graph on a side stream, time `steps` replays with CUDA events"""
     side = torch.cuda.Stream()
@@ -492,18 +577,22 @@ def main():
     ap.add_argument("--ref-tokens", type=int, default=8, help="tokens per step of the reference (CPU) arm")
     ap.add_argument("--cpu-budget-s", type=float, default=15.0)
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--workload", default="ragged64", choices=["ragged64", "decode48", "moe_b1", "deltanet"],
+    ap.add_argument("--workload", default="ragged64", choices=["ragged64", "decode48", "moe_b1", "deltanet", "prefill"],
                     help="ragged64: BASELINE configs[1] (default, the headline); decode48: configs[3], whole-model decode; "
                          "moe_b1: configs[0], one MoE layer at batch 1; deltanet: configs[2]")
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--new-tokens", type=int, default=128)
     ap.add_argument("--check-steps", type=int, default=0, help="decode48: greedy tokens compared with the CPU oracle")
     ap.add_argument("--first-token", type=int, default=7)
+    ap.add_argument("--prompt-tokens", type=int, default=8192, help="prefill: prompt length")
+    ap.add_argument("--prefill-batch", type=int, default=0, help="prefill: tokens per chunk (0 = engine default)")
     ap.add_argument("--seed", type=int, default=1)
     args = ap.parse_args()
     if args.workload == "decode48":
         args.warmup = max(args.warmup, 1)
         return run_decode48(args)
+    if args.workload == "prefill":
+        return run_prefill(args)
     if args.workload == "moe_b1":
         return run_moe_b1(args)
     if args.workload == "deltanet":

@@ -15,7 +15,7 @@ u8p, f32p, u32p = C.POINTER(C.c_uint8), C.POINTER(C.c_float), C.POINTER(C.c_uint
 
 EXPORTS = [
     "redcuda_abi_version", "redcuda_last_error", "redcuda_device_count", "redcuda_set_device", "redcuda_set_codebooks",
-    "redcuda_quant_dequant_rows", "redcuda_quant_matvec", "redcuda_router_select_softmax_topk", "redcuda_deltanet_step",
+    "redcuda_quant_dequant_rows", "redcuda_quant_matvec", "redcuda_quant_matmul_tc", "redcuda_router_select_softmax_topk", "redcuda_deltanet_step",
     "redcuda_deltanet_step_noalloc",
     "redcuda_moe_create", "redcuda_moe_destroy", "redcuda_moe_resident_bytes", "redcuda_moe_forward",
     "redcuda_moe_forward_device", "redcuda_moe_route_device", "redcuda_moe_experts_device", "redcuda_moe_shared_device",
@@ -74,6 +74,7 @@ def lib():
     L.redcuda_moe_combine_device.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.redcuda_quant_dequant_rows.argtypes = [C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]
     L.redcuda_quant_matvec.argtypes = [C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
+    L.redcuda_quant_matmul_tc.argtypes = [C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
     L.redcuda_router_select_softmax_topk.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]
     L.redcuda_deltanet_step.argtypes = [C.POINTER(DeltanetParams), C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.redcuda_deltanet_step_noalloc.argtypes = [C.POINTER(DeltanetParams), C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
@@ -146,6 +147,16 @@ def quant_matvec(ggml_type: int, w: np.ndarray, nrows: int, ncols: int, x: np.nd
     out = np.empty((x2.shape[0], nrows), np.float32)
     _check(lib().redcuda_quant_matvec(ggml_type, w.ctypes.data, nrows, ncols, x2.ctypes.data, x2.shape[0], out.ctypes.data))
     return out if np.ndim(x) > 1 else out[0]
+
+
+def quant_matmul_tc(ggml_type: int, w: np.ndarray, nrows: int, ncols: int, x: np.ndarray) -> np.ndarray:
+    """quant_matvec for a chunk of tokens on the tcgen05 tensor cores; x is [ntok, ncols]."""
+    _ensure_books()
+    w = np.ascontiguousarray(w).view(np.uint8)
+    x2 = np.ascontiguousarray(x, np.float32).reshape(-1, ncols)
+    out = np.empty((x2.shape[0], nrows), np.float32)
+    _check(lib().redcuda_quant_matmul_tc(ggml_type, w.ctypes.data, nrows, ncols, x2.ctypes.data, x2.shape[0], out.ctypes.data))
+    return out
 
 
 def router_select_softmax_topk(logits: np.ndarray, top_k: int, want_probs: bool = False):

@@ -54,6 +54,13 @@ int redcuda_quant_dequant_rows(uint32_t ggml_type, const uint8_t *rows, uint32_t
 int redcuda_quant_matvec(uint32_t ggml_type, const uint8_t *w, uint32_t nrows, uint32_t ncols,
                          const float *x, uint32_t ntok, float *out);
 
+/* The same contract as redcuda_quant_matvec for a chunk of tokens, computed on the tcgen05 tensor cores (block-quantised
+ * types only, ncols a multiple of 256): weights and activations are split into two fp16 digits each, products are
+ * accumulated in fp32 in tensor memory. This is the prefill form of the projections; the reference's counterpart is the
+ * dequantise + f32 GEMM pair of its batched prefill (native/redmetal_engine_prefill.m:205-227, 889-909). */
+int redcuda_quant_matmul_tc(uint32_t ggml_type, const uint8_t *w, uint32_t nrows, uint32_t ncols,
+                            const float *x, uint32_t ntok, float *out);
+
 /* rl_native_router_select_softmax_topk (native/redlite_native_router_exec.c:102-184) for ntok rows of logits:
  * ids[ntok][top_k], weights[ntok][top_k] (renormalised over the selection), probs[ntok][n_expert] (may be NULL).
  * Ties go to the lower expert id. */

@@ -81,6 +81,26 @@ def test_matvec_large_rows_and_kats():
     assert np.max(np.abs(got - ref)) <= 1e-4 * np.max(np.abs(ref))
 
 
+@pytest.mark.parametrize("t", [synth.Q6_K, synth.IQ2_XXS, synth.IQ3_S])
+@pytest.mark.parametrize("ntok,nrows,ncols", [(5, 64, 256), (40, 200, 512), (128, 384, 2048), (200, 130, 768)])
+def test_matmul_tensor_core(t, ntok, nrows, ncols):
+    """tcgen05 chunk GEMM against the oracle's row dots: ragged row tiles (64, 130, 200 rows), ragged and multiple token
+    tiles (5, 40, 200 tokens), every quantised format; activations of mixed magnitude exercise the per-token scaling."""
+    rng = np.random.default_rng(4000 + t + ntok)
+    rows = _rows(rng, t, nrows, ncols)
+    x = (rng.normal(0, 1, size=(ntok, ncols)) * np.exp(rng.uniform(-6, 6, size=(ntok, 1)))).astype(np.float32)
+    x[ntok // 2] = 0.0
+    got = rc.quant_matmul_tc(t, rows, nrows, ncols, x)
+    deq = ol.dequant_rows(t, rows, ncols).astype(np.float64)
+    worst = 0.0
+    for tk in range(ntok):
+        ref = ol.rows_dot(t, rows, x[tk])
+        mag = np.abs(deq * x[tk].astype(np.float64)).sum(axis=1) + 1e-30
+        worst = max(worst, float((np.abs(got[tk].astype(np.float64) - ref) / mag).max()))
+    assert np.all(got[ntok // 2] == 0.0)
+    assert worst <= REL_SUMABS, worst
+
+
 def test_router_topk_exact_incl_ties():
     rng = np.random.default_rng(7)
     n, k = 512, 10
