@@ -9,6 +9,7 @@
 #include "redcuda_common.cuh"
 #include "redcuda_kernels.cuh"
 #include "redcuda_moe_mma.cuh"
+#include "redcuda_tc_gemm.cuh"
 #include "redcuda_gguf.h"
 #include "../../include/redcuda.h"
 #include "../../include/rl_engine.h"
@@ -290,6 +291,7 @@ struct rl_engine {
     float *bx[2] = {nullptr, nullptr};           // layer input / output of a chunk (ping-pong)
     int8_t *xq = nullptr; float *sx = nullptr;   // chunk activations as digit planes for the Q6_K tensor-core projections
     uint32_t *tok_chunk_d = nullptr, *pos_chunk_d = nullptr;
+    __half *tc_xs = nullptr; float *tc_xinv = nullptr; uint32_t *tc_err = nullptr;   // tcgen05 GEMM: activation digits, per-token inverse scales, timeout flag
     // host mirrors
     std::vector<float> embed_h, layer_out_h, final_norm_h;
     std::vector<uint32_t> router_ids_h;
@@ -411,17 +413,29 @@ static int eng_step_device(rl_engine *e, bool want_logits, char *error, size_t c
     return 1;
 }
 
-// Projections of a chunk: Q6_K matrices with >= 3 tokens go through the tensor-core kernel on the digit planes of x
-// (quantised once per input, `quantised` says whether e->xq already holds x), everything else through the GEMV.
-static int eng_proj(rl_engine *e, const DMat *mats, float *const *outs, uint32_t n, const float *x, uint32_t ntok, bool *quantised, const char *tag) {
+// Projections of a chunk. From 8 tokens on, block-quantised matrices run on the tcgen05 GEMM (the matrices of one call
+// share the input, so its fp16 digits are prepared once and one launch covers them all); below that, or with
+// RL_PREFILL_TC=0, Q6_K matrices with >= 3 tokens take the mma.sync kernel on int8 digit planes and the rest the GEMV.
+static int eng_proj(rl_engine *e, const DMat *mats, float *const *outs, uint32_t n, const float *x, uint32_t ntok, const char *tag) {
     static const bool want_mma = !(getenv("RC_MOE_PATH") && getenv("RC_MOE_PATH")[0] == 'c');
+    static const bool want_tc = !(getenv("RL_PREFILL_TC") && atoi(getenv("RL_PREFILL_TC")) == 0);
+    bool all_quant = true;
+    for (uint32_t i = 0; i < n; ++i) all_quant = all_quant && rc_is_quant(mats[i].type) && mats[i].ncols == mats[0].ncols;
+    if (want_tc && all_quant && ntok >= 8u && n <= TC_MAX_JOBS && mats[0].ncols % 256u == 0) {
+        if (!launch_tc_prep_x(x, mats[0].ncols, ntok, mats[0].ncols, e->tc_xs, e->tc_xinv, e->stream)) return 0;
+        TcArgs A{};
+        A.njobs = n; A.ncols = mats[0].ncols; A.ntok = ntok; A.xs = e->tc_xs; A.x_inv = e->tc_xinv; A.err = e->tc_err;
+        for (uint32_t i = 0; i < n; ++i) A.job[i] = TcJob{mats[i].base, mats[i].nb, mats[i].type, mats[i].nrows, outs[i], mats[i].nrows, 0u};
+        return launch_tc_gemm(A, tag, e->stream);
+    }
     GemvArgs A{};
     A.ntok = ntok; A.x = x; A.x_stride = mats[0].ncols; A.tag = tag;
     uint32_t j = 0;
+    bool quantised = false;
     for (uint32_t i = 0; i < n; ++i) {
         const DMat &M = mats[i];
         if (want_mma && ntok >= 3u && M.type == RC_Q6_K && M.nrows % 16u == 0 && M.ncols % 256u == 0) {
-            if (!*quantised) { if (!launch_quant_act(x, M.ncols, ntok, M.ncols, e->xq, e->sx, e->stream)) return 0; *quantised = true; }
+            if (!quantised) { if (!launch_quant_act(x, M.ncols, ntok, M.ncols, e->xq, e->sx, e->stream)) return 0; quantised = true; }
             if (!launch_q6k_mma(M.base, nullptr, M.nb, M.nrows, M.ncols, ntok, e->xq, e->sx, outs[i], M.nrows, tag, e->stream)) return 0;
             continue;
         }
@@ -456,25 +470,22 @@ static int eng_prefill_chunk(rl_engine *e, uint32_t n, bool want_logits, char *e
         RC_LAUNCH((k_rmsnorm), n, 1024, 0, s, x, nullptr, L.attn_norm, in.hidden, in.rms_eps, nullptr, e->normed);
         prof_end(s);
         g_launches.fetch_add(1);
-        bool qd = false;
         if (L.recurrent) {
             const DMat mats[3] = {L.qkv, L.z, L.ba};
             float *outs[3] = {e->qkv, e->z, e->ba};
-            ENG_RC(eng_proj(e, mats, outs, 3, e->normed, n, &qd, "dn_proj"));
+            ENG_RC(eng_proj(e, mats, outs, 3, e->normed, n, "dn_proj"));
             ENG_RC(launch_deltanet_seq(D, n, L.conv_k, L.dt, L.a, L.ssm_norm, e->qkv, e->z, e->ba, e->conv + (size_t)L.ridx * (in.d_conv - 1u) * in.channels,
                                        e->rec + (size_t)L.ridx * in.dt_rank * in.d_state * in.d_state, e->dn_qk, e->dn_v, e->dn_beta, e->dn_gate, e->dn_core, e->ng, s));
             float *o1[1] = {e->branch};
-            qd = false;
-            ENG_RC(eng_proj(e, &L.ssm_out, o1, 1, e->ng, n, &qd, "dn_out"));
+            ENG_RC(eng_proj(e, &L.ssm_out, o1, 1, e->ng, n, "dn_out"));
         } else {
             const DMat mats[3] = {L.q, L.k, L.v};
             float *outs[3] = {e->qg, e->kraw, e->vraw};
-            ENG_RC(eng_proj(e, mats, outs, 3, e->normed, n, &qd, "attn_proj"));
+            ENG_RC(eng_proj(e, mats, outs, 3, e->normed, n, "attn_proj"));
             if (e->kv_half) { if (!eng_attention<__half>(e, L, n, e->pos_chunk_d, error, cap)) return 0; }
             else { if (!eng_attention<float>(e, L, n, e->pos_chunk_d, error, cap)) return 0; }
             float *o1[1] = {e->branch};
-            qd = false;
-            ENG_RC(eng_proj(e, &L.o, o1, 1, e->gated, n, &qd, "attn_out"));
+            ENG_RC(eng_proj(e, &L.o, o1, 1, e->gated, n, "attn_out"));
         }
         prof_begin("resid_rmsnorm", s);
         RC_LAUNCH((k_rmsnorm), n, 1024, 0, s, x, e->branch, L.post_norm, in.hidden, in.rms_eps, e->resid, e->normed);
@@ -690,7 +701,8 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
                  o_qu = take(T * qc * 4u), o_ga = take(T * qc * 4u), o_gd = take(T * qc * 4u), o_pm = take((size_t)in.n_head * parts * 4u), o_pl = take((size_t)in.n_head * parts * 4u),
                  o_pa = take((size_t)in.n_head * parts * in.head_dim * 4u), o_em = take(in.hidden * 4u), o_lo = take((size_t)in.n_layer * in.hidden * 4u),
                  o_fn = take(in.hidden * 4u), o_lg = take((size_t)in.vocab * 4u), o_ri = take((size_t)in.n_layer * RL_ENGINE_MAX_TOPK * 4u), o_tk = take(16), o_gt = take(4096u * 4u),
-                 o_bx0 = take(T * in.hidden * 4u), o_bx1 = take(T * in.hidden * 4u), o_xq = take(T * 3u * widest), o_sx = take(T * 4u), o_tc = take(T * 4u), o_pc = take(T * 4u);
+                 o_bx0 = take(T * in.hidden * 4u), o_bx1 = take(T * in.hidden * 4u), o_xq = take(T * 3u * widest), o_sx = take(T * 4u), o_tc = take(T * 4u), o_pc = take(T * 4u),
+                 o_txs = take(tc_xs_halves((uint32_t)T, widest, tc_token_tile((uint32_t)T)) * 2u), o_txi = take((T + 128u) * 4u), o_ter = take(16);
     if (!e->scratch.alloc(w)) ENG_FAIL("%s", redcuda_last_error());
     uint8_t *B = e->scratch.as<uint8_t>();
     ENG_CUDA(cudaMemsetAsync(B, 0, w, e->stream));
@@ -703,6 +715,7 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
     e->pos_d = e->token_d + 2; e->gen_count_d = e->token_d + 3;
     e->bx[0] = (float *)(B + o_bx0); e->bx[1] = (float *)(B + o_bx1); e->xq = (int8_t *)(B + o_xq); e->sx = (float *)(B + o_sx);
     e->tok_chunk_d = (uint32_t *)(B + o_tc); e->pos_chunk_d = (uint32_t *)(B + o_pc);
+    e->tc_xs = (__half *)(B + o_txs); e->tc_xinv = (float *)(B + o_txi); e->tc_err = (uint32_t *)(B + o_ter);
     e->embed_h.assign(in.hidden, 0.f); e->layer_out_h.assign((size_t)in.n_layer * in.hidden, 0.f); e->final_norm_h.assign(in.hidden, 0.f);
     e->router_ids_h.assign((size_t)in.n_layer * RL_ENGINE_MAX_TOPK, 0u);
     ENG_CUDA(cudaMallocHost((void **)&e->token_pin, 64u + 2u * T * 4u));      // [16 words][chunk tokens][chunk positions]
@@ -802,7 +815,9 @@ int rl_engine_prefill(rl_engine *e, rl_engine_backend backend, const uint32_t *t
         }
         i += n;
     }
+    ENG_CUDA(cudaMemcpyAsync(e->token_pin + 3, e->tc_err, 4, cudaMemcpyDeviceToHost, e->stream));
     if (!eng_copy_mirrors(e, logits, error, cap)) return 0;
+    if (e->token_pin[3]) ENG_FAIL("prefill: a tensor-core stage never signalled completion (bounded wait ran out)");
     if (stats) { stats->total_ms = now_ms() - t0; stats->gpu_ms = stats->total_ms; }
     if (error && cap) error[0] = '\0';
     return 1;

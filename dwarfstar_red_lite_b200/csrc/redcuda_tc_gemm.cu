@@ -9,7 +9,9 @@
 // tile for the weights, per token for the activations) keep hi in the normal fp16 range and are undone in the epilogue.
 //
 // One CTA = 128 weight rows (MMA M) x TN tokens (MMA N) x all columns, K in stages of 64:
-//   all 8 warps   decode 128 x 64 weights into the two fp16 digit tiles of the stage (canonical K-major core-matrix
+//   all 8 warps   stage the raw quant blocks of the 128 rows one 256-column block ahead (cp.async, 16-byte pieces, the
+//                 planar layout kept, so the exact decoder of the GEMV path reads them unchanged), decode 128 x 64
+//                 weights from shared memory into the two fp16 digit tiles of the stage (canonical K-major core-matrix
 //                 layout, no swizzle) and copy the stage's activation digits (laid out for the MMA by k_tc_prep_x)
 //   one thread    issues 4 k-steps x 3 tcgen05.mma (128 x TN x 16, kind::f16, fp32 accumulate) and a tcgen05.commit
 //                 on the stage buffer's mbarrier; the MMAs of a stage run while the warps decode the next one
@@ -64,6 +66,46 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
 
 __device__ __forceinline__ uint32_t tc_d_plane(uint32_t type, uint64_t nb) {
     return (uint32_t)(type == RC_Q6_K ? rc_q6_d(nb) : type == RC_IQ2_XXS ? rc_iq2_d(nb) : rc_iq3_d(nb));
+}
+
+__device__ __forceinline__ void cp_async_n(uint32_t dst, const void *src, uint32_t bytes) {
+    if (bytes == 16u) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(src) : "memory");
+    else if (bytes == 8u) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" :: "r"(dst), "l"(src) : "memory");
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(dst), "l"(src) : "memory");
+}
+
+// bytes of the raw staging area: the planar layout of a 128-block matrix of the type
+__host__ __device__ __forceinline__ uint32_t tc_raw_bytes(uint32_t type) { return TC_M * rc_block_bytes(type); }
+
+// Copy block column c of rows [row0, row0 + 128) into `raw`, laid out as a planar matrix of 128 blocks (block r = row r).
+// Every plane piece of 4 bytes or more goes by cp.async; the 2-byte block scales are returned in a register by the
+// threads that own a row (tid < 128) and stored by tc_put_d once the previous block column is no longer read.
+__device__ __forceinline__ unsigned short tc_stage_raw(uint32_t type, const uint8_t *w, uint64_t nb, uint32_t bpr, uint32_t row0, uint32_t nrows,
+                                                       uint32_t c, uint8_t *raw, uint32_t tid) {
+    const uint32_t raw_s = smem_u32(raw);
+    auto plane = [&](uint64_t off_g, uint32_t off_s, uint32_t piece) {
+        const uint32_t unit = piece >= 16u ? 16u : piece, per_row = piece / unit;
+        for (uint32_t i = tid; i < TC_M * per_row; i += TC_THREADS) {
+            const uint32_t r = i / per_row, u = i - r * per_row;
+            if (row0 + r < nrows) cp_async_n(raw_s + off_s + r * piece + u * unit, w + off_g + ((uint64_t)(row0 + r) * bpr + c) * piece + u * unit, unit);
+        }
+    };
+    if (type == RC_Q6_K) {
+        plane(0u, 0u, 128u); plane(rc_q6_qh(nb), (uint32_t)rc_q6_qh(TC_M), 64u); plane(rc_q6_sc(nb), (uint32_t)rc_q6_sc(TC_M), 16u);
+    } else if (type == RC_IQ2_XXS) {
+        plane(0u, 0u, 64u);
+    } else {
+        plane(0u, 0u, 64u); plane(rc_iq3_signs(nb), (uint32_t)rc_iq3_signs(TC_M), 32u); plane(rc_iq3_qh(nb), (uint32_t)rc_iq3_qh(TC_M), 8u);
+        plane(rc_iq3_scales(nb), (uint32_t)rc_iq3_scales(TC_M), 4u);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    unsigned short d = 0;
+    if (tid < TC_M && row0 + tid < nrows) d = __ldg(reinterpret_cast<const unsigned short *>(w + tc_d_plane(type, nb)) + (uint64_t)(row0 + tid) * bpr + c);
+    return d;
+}
+
+__device__ __forceinline__ void tc_put_d(uint32_t type, uint8_t *raw, uint32_t tid, unsigned short d) {
+    if (tid < TC_M) reinterpret_cast<unsigned short *>(raw + tc_d_plane(type, TC_M))[tid] = d;
 }
 
 // x [ntok][ncols] fp32 -> fp16 digits in the order the GEMM stages consume them:
@@ -161,22 +203,34 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
     const __half *xs_tile = A.xs + (size_t)blockIdx.y * nstage * (2u * B_DIGIT / 2u);
     const uint32_t idesc = tc_idesc((uint32_t)TN);
 
+    uint8_t *raw_buf[2] = {smem + 2u * BUF, smem + 2u * BUF + tc_raw_bytes(J.type)};
+    unsigned short d_next = tc_stage_raw(J.type, J.w, J.nb, bpr, row0, J.nrows, 0u, raw_buf[0], tid);
+
     for (uint32_t s = 0; s < nstage; ++s) {
         const uint32_t b = s & 1u;
         uint8_t *buf = smem + b * BUF;
+        const uint32_t c = (s * TC_KS) >> 8;                      // 256-column block of this stage
+        if (((s * TC_KS) & 255u) == 0u) {
+            // new block column: its raw bytes were requested one column ago; request the next one
+            tc_put_d(J.type, raw_buf[c & 1u], tid, d_next);
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            __syncthreads();                                       // raw[c & 1] complete, raw[(c + 1) & 1] no longer read
+            if (c + 1u < bpr) d_next = tc_stage_raw(J.type, J.w, J.nb, bpr, row0, J.nrows, c + 1u, raw_buf[(c + 1u) & 1u], tid);
+        }
+        const uint8_t *raw = raw_buf[c & 1u];
         // the MMAs that read this buffer two stages ago must have finished
         if (s >= 2u) {
             if (!mbar_wait(smem_u32(&mbar[b]), ((s >> 1) - 1u) & 1u)) fail = 1u;
         }
-        // ---- weights: thread -> (row, k-chunk of 8); rows fastest, so the 16-byte stores of a warp are contiguous
-        const uint32_t blk_in_row = (s * TC_KS) >> 8, g8_0 = ((s * TC_KS) & 255u) >> 3;
+        // ---- weights: thread -> (row, k-chunk of 8), 4 rows x 8 chunks per warp pass
+        const uint32_t g8_0 = ((s * TC_KS) & 255u) >> 3;
 #pragma unroll
         for (uint32_t it = 0; it < (TC_M * 8u) / TC_THREADS; ++it) {
-            const uint32_t item = it * TC_THREADS + tid, r = item & (TC_M - 1u), kc = item >> 7;
+            const uint32_t item = it * TC_THREADS + tid, r = item >> 3, kc = item & 7u;
             __half hi[8], lo[8];
             if (row0 + r < J.nrows) {
                 float v[8];
-                rc_decode8(J.type, J.w, J.nb, (uint64_t)(row0 + r) * bpr + blk_in_row, g8_0 + kc, bk, v);
+                rc_decode8(J.type, raw, TC_M, r, g8_0 + kc, bk, v);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const float vs = v[j] * w_scale;
@@ -273,7 +327,9 @@ int launch_tc_gemm(TcArgs &A, const char *tag, cudaStream_t s) {
     A.iq2 = books_iq2(); A.iq3s = books_iq3s();
     const uint32_t tn = tc_token_tile(A.ntok);
     const dim3 grid(tiles, (A.ntok + tn - 1u) / tn);
-    const size_t smem = 2u * (2u * TC_A_DIGIT + 2u * (size_t)tn * TC_KS * 2u);
+    uint32_t raw_max = 0;
+    for (uint32_t j = 0; j < A.njobs; ++j) raw_max = raw_max > tc_raw_bytes(A.job[j].type) ? raw_max : tc_raw_bytes(A.job[j].type);
+    const size_t smem = 2u * (2u * TC_A_DIGIT + 2u * (size_t)tn * TC_KS * 2u) + 2u * (size_t)raw_max;
     prof_begin(tag, s);
 #define RC_TC_LAUNCH(TN_) do { \
         RC_CUDA(cudaFuncSetAttribute(k_tc_gemm<TN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
