@@ -422,11 +422,14 @@ static int eng_proj(rl_engine *e, const DMat *mats, float *const *outs, uint32_t
     bool all_quant = true;
     for (uint32_t i = 0; i < n; ++i) all_quant = all_quant && rc_is_quant(mats[i].type) && mats[i].ncols == mats[0].ncols;
     if (want_tc && all_quant && ntok >= 8u && n <= TC_MAX_JOBS && mats[0].ncols % 256u == 0) {
-        if (!launch_tc_prep_x(x, mats[0].ncols, ntok, mats[0].ncols, e->tc_xs, e->tc_xinv, e->stream)) return 0;
+        uint32_t row_tiles = 0;
+        for (uint32_t i = 0; i < n; ++i) row_tiles += tc_row_tiles(mats[i].nrows);
+        const uint32_t tn = tc_token_tile(ntok, row_tiles);
+        if (!launch_tc_prep_x(x, mats[0].ncols, ntok, mats[0].ncols, tn, e->tc_xs, e->tc_xinv, e->stream)) return 0;
         TcArgs A{};
         A.njobs = n; A.ncols = mats[0].ncols; A.ntok = ntok; A.xs = e->tc_xs; A.x_inv = e->tc_xinv; A.err = e->tc_err;
         for (uint32_t i = 0; i < n; ++i) A.job[i] = TcJob{mats[i].base, mats[i].nb, mats[i].type, mats[i].nrows, outs[i], mats[i].nrows, 0u};
-        return launch_tc_gemm(A, tag, e->stream);
+        return launch_tc_gemm(A, tn, tag, e->stream);
     }
     GemvArgs A{};
     A.ntok = ntok; A.x = x; A.x_stride = mats[0].ncols; A.tag = tag;
@@ -702,7 +705,7 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
                  o_pa = take((size_t)in.n_head * parts * in.head_dim * 4u), o_em = take(in.hidden * 4u), o_lo = take((size_t)in.n_layer * in.hidden * 4u),
                  o_fn = take(in.hidden * 4u), o_lg = take((size_t)in.vocab * 4u), o_ri = take((size_t)in.n_layer * RL_ENGINE_MAX_TOPK * 4u), o_tk = take(16), o_gt = take(4096u * 4u),
                  o_bx0 = take(T * in.hidden * 4u), o_bx1 = take(T * in.hidden * 4u), o_xq = take(T * 3u * widest), o_sx = take(T * 4u), o_tc = take(T * 4u), o_pc = take(T * 4u),
-                 o_txs = take(tc_xs_halves((uint32_t)T, widest, tc_token_tile((uint32_t)T)) * 2u), o_txi = take((T + 128u) * 4u), o_ter = take(16);
+                 o_txs = take(tc_xs_halves((uint32_t)T, widest, 128u) * 2u), o_txi = take((T + 128u) * 4u), o_ter = take(16);
     if (!e->scratch.alloc(w)) ENG_FAIL("%s", redcuda_last_error());
     uint8_t *B = e->scratch.as<uint8_t>();
     ENG_CUDA(cudaMemsetAsync(B, 0, w, e->stream));

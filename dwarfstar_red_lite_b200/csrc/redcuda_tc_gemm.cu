@@ -27,7 +27,7 @@
 
 namespace rc {
 
-constexpr uint32_t TC_M = 128u, TC_KS = 64u, TC_THREADS = 256u;
+constexpr uint32_t TC_M = 128u, TC_KS = 64u, TC_THREADS = 512u, TC_WARPS = TC_THREADS / 32u;
 constexpr uint32_t TC_A_DIGIT = TC_M * TC_KS * 2u;            // bytes of one weight digit tile of a stage (16 KB)
 constexpr uint32_t TC_SPIN_LIMIT = 4u * 1000u * 1000u;        // polls of ~50 ns: far beyond any legitimate wait
 
@@ -69,34 +69,38 @@ __device__ __forceinline__ uint32_t tc_d_plane(uint32_t type, uint64_t nb) {
 }
 
 __device__ __forceinline__ void cp_async_n(uint32_t dst, const void *src, uint32_t bytes) {
-    if (bytes == 16u) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(src) : "memory");
-    else if (bytes == 8u) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" :: "r"(dst), "l"(src) : "memory");
+    if (bytes == 8u) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" :: "r"(dst), "l"(src) : "memory");
     else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(dst), "l"(src) : "memory");
 }
 
-// bytes of the raw staging area: the planar layout of a 128-block matrix of the type
-__host__ __device__ __forceinline__ uint32_t tc_raw_bytes(uint32_t type) { return TC_M * rc_block_bytes(type); }
+// ---- raw staging area: the quant blocks of one 256-column block of the tile's 128 rows, one plane per block field.
+// Row pitches are padded so that the 32 rows a warp decodes at once fall into distinct banks (8-byte reads: two
+// wavefronts, the minimum). Offsets in bytes from the start of the area:
+//   Q6_K     ql pitch 136 @0, qh pitch 72 @17408, scales pitch 20 @26624, d (fp16) @29184           -> 29440
+//   IQ2_XXS  qs pitch 72 @0, d @9216                                                                -> 9472
+//   IQ3_S    qs pitch 72 @0, signs pitch 40 @9216, qh pitch 12 @14336, scales pitch 4 @15872, d @16384 -> 16640
+__host__ __device__ __forceinline__ uint32_t tc_raw_bytes(uint32_t type) { return type == RC_Q6_K ? 29440u : type == RC_IQ2_XXS ? 9472u : 16640u; }
+__device__ __forceinline__ uint32_t tc_raw_d(uint32_t type) { return type == RC_Q6_K ? 29184u : type == RC_IQ2_XXS ? 9216u : 16384u; }
 
-// Copy block column c of rows [row0, row0 + 128) into `raw`, laid out as a planar matrix of 128 blocks (block r = row r).
-// Every plane piece of 4 bytes or more goes by cp.async; the 2-byte block scales are returned in a register by the
-// threads that own a row (tid < 128) and stored by tc_put_d once the previous block column is no longer read.
+// Request block column c of rows [row0, row0 + 128) into `raw` (cp.async, one commit group). The 2-byte block scales
+// come back in a register of the threads that own a row (tid < 128) and are stored by tc_put_d.
 __device__ __forceinline__ unsigned short tc_stage_raw(uint32_t type, const uint8_t *w, uint64_t nb, uint32_t bpr, uint32_t row0, uint32_t nrows,
                                                        uint32_t c, uint8_t *raw, uint32_t tid) {
     const uint32_t raw_s = smem_u32(raw);
-    auto plane = [&](uint64_t off_g, uint32_t off_s, uint32_t piece) {
-        const uint32_t unit = piece >= 16u ? 16u : piece, per_row = piece / unit;
+    auto plane = [&](uint64_t off_g, uint32_t off_s, uint32_t piece, uint32_t pitch, uint32_t unit) {
+        const uint32_t per_row = piece / unit;
         for (uint32_t i = tid; i < TC_M * per_row; i += TC_THREADS) {
             const uint32_t r = i / per_row, u = i - r * per_row;
-            if (row0 + r < nrows) cp_async_n(raw_s + off_s + r * piece + u * unit, w + off_g + ((uint64_t)(row0 + r) * bpr + c) * piece + u * unit, unit);
+            if (row0 + r < nrows) cp_async_n(raw_s + off_s + r * pitch + u * unit, w + off_g + ((uint64_t)(row0 + r) * bpr + c) * piece + u * unit, unit);
         }
     };
     if (type == RC_Q6_K) {
-        plane(0u, 0u, 128u); plane(rc_q6_qh(nb), (uint32_t)rc_q6_qh(TC_M), 64u); plane(rc_q6_sc(nb), (uint32_t)rc_q6_sc(TC_M), 16u);
+        plane(0u, 0u, 128u, 136u, 8u); plane(rc_q6_qh(nb), 17408u, 64u, 72u, 8u); plane(rc_q6_sc(nb), 26624u, 16u, 20u, 4u);
     } else if (type == RC_IQ2_XXS) {
-        plane(0u, 0u, 64u);
+        plane(0u, 0u, 64u, 72u, 8u);
     } else {
-        plane(0u, 0u, 64u); plane(rc_iq3_signs(nb), (uint32_t)rc_iq3_signs(TC_M), 32u); plane(rc_iq3_qh(nb), (uint32_t)rc_iq3_qh(TC_M), 8u);
-        plane(rc_iq3_scales(nb), (uint32_t)rc_iq3_scales(TC_M), 4u);
+        plane(0u, 0u, 64u, 72u, 8u); plane(rc_iq3_signs(nb), 9216u, 32u, 40u, 8u); plane(rc_iq3_qh(nb), 14336u, 8u, 12u, 4u);
+        plane(rc_iq3_scales(nb), 15872u, 4u, 4u, 4u);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     unsigned short d = 0;
@@ -105,7 +109,85 @@ __device__ __forceinline__ unsigned short tc_stage_raw(uint32_t type, const uint
 }
 
 __device__ __forceinline__ void tc_put_d(uint32_t type, uint8_t *raw, uint32_t tid, unsigned short d) {
-    if (tid < TC_M) reinterpret_cast<unsigned short *>(raw + tc_d_plane(type, TC_M))[tid] = d;
+    if (tid < TC_M) reinterpret_cast<unsigned short *>(raw + tc_raw_d(type))[tid] = d;
+}
+
+// byte j of w as a float without a conversion instruction: one PRMT builds the bits of 2^23 + byte
+__device__ __forceinline__ float tc_byte_f(uint32_t w, int j) { return __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7540u | (uint32_t)j)); }
+
+// two scaled values -> their fp16 digits: hi = the top 11 significant bits (the low 13 mantissa bits cleared, so the
+// conversion is exact in the normal fp16 range), lo = the rounded remainder; packed conversions, two values each
+__device__ __forceinline__ void tc_split2(float a, float b, uint32_t &hi, uint32_t &lo) {
+    const float ah = __uint_as_float(__float_as_uint(a) & 0xffffe000u), bh = __uint_as_float(__float_as_uint(b) & 0xffffe000u);
+    const __half2 hh = __floats2half2_rn(ah, bh), ll = __floats2half2_rn(a - ah, b - bh);
+    hi = *reinterpret_cast<const uint32_t *>(&hh); lo = *reinterpret_cast<const uint32_t *>(&ll);
+}
+
+// The 8 consecutive values [8*g8, 8*g8 + 8) of row r's block from the staging area, times the tile's power-of-two
+// scale, as two fp16 digits. The float operations are those of rc_decode8 with d replaced by d * scale (a power of two
+// commutes with every rounding), read with 8-byte shared-memory loads.
+template <uint32_t TYPE>
+__device__ __forceinline__ void tc_decode_split(const uint8_t *raw, uint32_t r, uint32_t g8, float scale, const RcBooks &bk, uint4 &hi, uint4 &lo) {
+    const float d = __half2float(__ushort_as_half(reinterpret_cast<const unsigned short *>(raw + tc_raw_d(TYPE))[r])) * scale;
+    float v[8];
+    if (TYPE == RC_Q6_K) {
+        const uint32_t k = g8 * 8u, half = k >> 7, quarter = (k & 127u) >> 5, l0 = k & 31u;
+        const uint2 ql = *reinterpret_cast<const uint2 *>(raw + r * 136u + half * 64u + (quarter & 1u) * 32u + l0);
+        const uint2 qh = *reinterpret_cast<const uint2 *>(raw + 17408u + r * 72u + half * 32u + l0);
+        const int sc = (int)(int8_t)raw[26624u + r * 20u + half * 8u + (l0 >> 4) + 2u * quarter];
+        const float ds = d * (float)sc;
+        const uint32_t nsh = quarter < 2u ? 0u : 4u, hsh = 2u * quarter;
+        const uint32_t w0 = ((ql.x >> nsh) & 0x0f0f0f0fu) | (((qh.x >> hsh) & 0x03030303u) << 4);
+        const uint32_t w1 = ((ql.y >> nsh) & 0x0f0f0f0fu) | (((qh.y >> hsh) & 0x03030303u) << 4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {      // 6-bit value 0..63: (2^23 + value) - (2^23 + 32) = value - 32, exactly
+            v[j] = ds * (tc_byte_f(w0, j) - 8388640.f);
+            v[j + 4] = ds * (tc_byte_f(w1, j) - 8388640.f);
+        }
+    } else if (TYPE == RC_IQ2_XXS) {
+        const uint32_t ib32 = g8 >> 2, l = g8 & 3u;
+        const uint2 aux = *reinterpret_cast<const uint2 *>(raw + r * 72u + ib32 * 8u);
+        const float db = d * (0.5f + (float)(aux.y >> 28)) * 0.25f;
+        const uint2 gv = __ldg(reinterpret_cast<const uint2 *>(bk.iq2 + ((aux.x >> (8u * l)) & 255u) * 8u));
+        const uint32_t s8 = rc_sign8((aux.y >> (7u * l)) & 127u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float m = db * (tc_byte_f(j < 4 ? gv.x : gv.y, j & 3) - 8388608.f);
+            v[j] = __uint_as_float(__float_as_uint(m) ^ ((s8 << (31 - j)) & 0x80000000u));
+        }
+    } else {
+        const uint32_t ib32 = g8 >> 2, l = g8 & 3u;
+        const uint8_t *qs = raw + r * 72u + 8u * ib32;
+        const uint32_t qh = raw[14336u + r * 12u + ib32];
+        const uint32_t sg = raw[9216u + r * 40u + 4u * ib32 + l];
+        const uint32_t scb = raw[15872u + r * 4u + (ib32 >> 1)];
+        const float db = d * (float)(1 + 2 * (int)((scb >> (4u * (ib32 & 1u))) & 0xfu));
+        const uint32_t i1 = qs[2u * l] | ((qh << (8u - 2u * l)) & 256u), i2 = qs[2u * l + 1u] | ((qh << (7u - 2u * l)) & 256u);
+        const uint32_t g1 = __ldg(bk.iq3s + i1), g2 = __ldg(bk.iq3s + i2);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float m1 = db * (tc_byte_f(g1, j) - 8388608.f), m2 = db * (tc_byte_f(g2, j) - 8388608.f);
+            v[j] = __uint_as_float(__float_as_uint(m1) ^ ((sg << (31 - j)) & 0x80000000u));
+            v[j + 4] = __uint_as_float(__float_as_uint(m2) ^ ((sg << (27 - j)) & 0x80000000u));
+        }
+    }
+    tc_split2(v[0], v[1], hi.x, lo.x); tc_split2(v[2], v[3], hi.y, lo.y);
+    tc_split2(v[4], v[5], hi.z, lo.z); tc_split2(v[6], v[7], hi.w, lo.w);
+}
+
+// the weight digits of one stage: thread -> (row, k-chunk of 8), 32 consecutive rows per warp pass (padded pitches: no
+// bank conflicts on the reads, and the 16-byte digit stores of a warp are contiguous)
+template <uint32_t TYPE>
+__device__ __forceinline__ void tc_decode_stage(const uint8_t *raw, uint8_t *abuf, uint32_t g8_0, uint32_t rows_live, float scale, const RcBooks &bk, uint32_t tid) {
+#pragma unroll
+    for (uint32_t it = 0; it < (TC_M * 8u) / TC_THREADS; ++it) {
+        const uint32_t item = it * TC_THREADS + tid, r = item & (TC_M - 1u), kc = item >> 7;
+        uint4 hi = make_uint4(0u, 0u, 0u, 0u), lo = hi;
+        if (r < rows_live) tc_decode_split<TYPE>(raw, r, g8_0 + kc, scale, bk, hi, lo);
+        const uint32_t off = kc * (TC_M * 16u) + r * 16u;          // [k chunk][row group][row in group][16 B]
+        *reinterpret_cast<uint4 *>(abuf + off) = hi;
+        *reinterpret_cast<uint4 *>(abuf + TC_A_DIGIT + off) = lo;
+    }
 }
 
 // x [ntok][ncols] fp32 -> fp16 digits in the order the GEMM stages consume them:
@@ -146,15 +228,21 @@ __global__ void k_tc_prep_x(const float *__restrict__ x, uint32_t x_stride, uint
     }
 }
 
+// number of activation stage buffers: the bulk copy of stage s + NB - 2 is issued when stage s begins
+template <int TN> struct TcCfg { static constexpr uint32_t NB = TN >= 128 ? 3u : 4u; };
+
 template <int TN>
 __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant__ TcArgs A) {
     pdl_prologue();
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr uint32_t B_DIGIT = (uint32_t)TN * TC_KS * 2u, BUF = 2u * TC_A_DIGIT + 2u * B_DIGIT;
+    constexpr uint32_t NB = TcCfg<TN>::NB;
+    constexpr uint32_t B_DIGIT = (uint32_t)TN * TC_KS * 2u, A_BUF = 2u * TC_A_DIGIT, B_BUF = 2u * B_DIGIT;
     constexpr uint32_t TMEM_COLS = TN < 32 ? 32u : (uint32_t)TN;
-    __shared__ __align__(8) uint64_t mbar[2];
-    __shared__ uint32_t tmem_slot, fail;
-    __shared__ float red[8];
+    __shared__ __align__(8) uint64_t mbar[2];        // MMAs that read A buffer b (and the B buffer of the same stage) are done
+    __shared__ __align__(8) uint64_t bfull[NB];      // the activation digits of a stage have landed
+    __shared__ uint32_t tmem_slot;
+    __shared__ volatile uint32_t fail;      // a bounded wait ran out: no more MMAs are issued, later waits are skipped
+    __shared__ float red[TC_WARPS];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
 
     // which matrix of the launch this row tile belongs to
@@ -164,24 +252,39 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
     const uint32_t row0 = (blockIdx.x - J.tile0) * TC_M, t0 = blockIdx.y * (uint32_t)TN;
     const uint32_t bpr = A.ncols >> 8, nstage = A.ncols / TC_KS;
     const RcBooks bk{A.iq2, A.iq3s};
+    uint8_t *a_base = smem, *b_base = smem + 2u * A_BUF, *raw_base = b_base + NB * B_BUF;
+    const __half *xs_tile = A.xs + (size_t)blockIdx.y * nstage * (B_BUF / 2u);
+
+    // one bulk copy (TMA engine, no tensor map: the digits are already laid out for the MMA) per stage
+    auto issue_b = [&](uint32_t stage) {
+        const uint32_t j = stage % NB, bar = smem_u32(&bfull[j]);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(B_BUF) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     :: "r"(smem_u32(b_base + j * B_BUF)), "l"(xs_tile + (size_t)stage * (B_BUF / 2u)), "r"(B_BUF), "r"(bar) : "memory");
+    };
 
     if (tid == 0) {
         fail = 0u;
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&mbar[0])));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&mbar[1])));
+        for (uint32_t j = 0; j < NB; ++j) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&bfull[j])));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (uint32_t st = 0; st + 2u < NB && st < nstage; ++st) issue_b(st);
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    uint8_t *raw_buf[2] = {raw_base, raw_base + tc_raw_bytes(J.type)};
+    unsigned short d_next = tc_stage_raw(J.type, J.w, J.nb, bpr, row0, J.nrows, 0u, raw_buf[0], tid);
     // power-of-two scale of the tile: the largest block scale d times the largest integer factor of the format
     float dmax = 0.f;
     {
         const unsigned short *dp = reinterpret_cast<const unsigned short *>(J.w + tc_d_plane(J.type, J.nb));
         for (uint32_t i = tid; i < TC_M * bpr; i += TC_THREADS) {
             const uint32_t r = row0 + i / bpr;
-            if (r < J.nrows) dmax = fmaxf(dmax, fabsf(__half2float(__ushort_as_half(dp[(size_t)r * bpr + (i % bpr)]))));
+            if (r < J.nrows) dmax = fmaxf(dmax, fabsf(__half2float(__ushort_as_half(__ldg(dp + (size_t)r * bpr + (i % bpr))))));
         }
         for (int o = 16; o; o >>= 1) dmax = fmaxf(dmax, __shfl_xor_sync(0xffffffffu, dmax, o));
         if (lane == 0) red[warp] = dmax;
@@ -191,7 +294,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_slot;
     dmax = 0.f;
-    for (int w = 0; w < 8; ++w) dmax = fmaxf(dmax, red[w]);
+    for (uint32_t w = 0; w < TC_WARPS; ++w) dmax = fmaxf(dmax, red[w]);
     int we = 0;
     {
         const float bound = dmax * (J.type == RC_Q6_K ? 4096.f : J.type == RC_IQ2_XXS ? 256.f : 512.f);
@@ -199,16 +302,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
         we = we > 100 ? 100 : we < -100 ? -100 : we;
     }
     const float w_scale = exp2f((float)we), w_inv = exp2f((float)-we);
-
-    const __half *xs_tile = A.xs + (size_t)blockIdx.y * nstage * (2u * B_DIGIT / 2u);
     const uint32_t idesc = tc_idesc((uint32_t)TN);
-
-    uint8_t *raw_buf[2] = {smem + 2u * BUF, smem + 2u * BUF + tc_raw_bytes(J.type)};
-    unsigned short d_next = tc_stage_raw(J.type, J.w, J.nb, bpr, row0, J.nrows, 0u, raw_buf[0], tid);
 
     for (uint32_t s = 0; s < nstage; ++s) {
         const uint32_t b = s & 1u;
-        uint8_t *buf = smem + b * BUF;
+        uint8_t *abuf = a_base + b * A_BUF;
         const uint32_t c = (s * TC_KS) >> 8;                      // 256-column block of this stage
         if (((s * TC_KS) & 255u) == 0u) {
             // new block column: its raw bytes were requested one column ago; request the next one
@@ -218,59 +316,44 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
             if (c + 1u < bpr) d_next = tc_stage_raw(J.type, J.w, J.nb, bpr, row0, J.nrows, c + 1u, raw_buf[(c + 1u) & 1u], tid);
         }
         const uint8_t *raw = raw_buf[c & 1u];
-        // the MMAs that read this buffer two stages ago must have finished
-        if (s >= 2u) {
+        // the MMAs of stage s - 2 read this A buffer and the activation buffer that stage s + NB - 2 will use
+        if (s >= 2u && !fail) {
             if (!mbar_wait(smem_u32(&mbar[b]), ((s >> 1) - 1u) & 1u)) fail = 1u;
         }
-        // ---- weights: thread -> (row, k-chunk of 8), 4 rows x 8 chunks per warp pass
-        const uint32_t g8_0 = ((s * TC_KS) & 255u) >> 3;
-#pragma unroll
-        for (uint32_t it = 0; it < (TC_M * 8u) / TC_THREADS; ++it) {
-            const uint32_t item = it * TC_THREADS + tid, r = item >> 3, kc = item & 7u;
-            __half hi[8], lo[8];
-            if (row0 + r < J.nrows) {
-                float v[8];
-                rc_decode8(J.type, raw, TC_M, r, g8_0 + kc, bk, v);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float vs = v[j] * w_scale;
-                    hi[j] = __float2half_rn(vs);
-                    lo[j] = __float2half_rn(vs - __half2float(hi[j]));
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) { hi[j] = __float2half_rn(0.f); lo[j] = hi[j]; }
-            }
-            const uint32_t off = kc * (TC_M * 16u) + r * 16u;          // [k chunk][row group][row in group][16 B]
-            *reinterpret_cast<uint4 *>(buf + off) = *reinterpret_cast<const uint4 *>(hi);
-            *reinterpret_cast<uint4 *>(buf + TC_A_DIGIT + off) = *reinterpret_cast<const uint4 *>(lo);
-        }
-        // ---- activations: the stage's two digit tiles are one contiguous run in xs
+        if (tid == 0 && s + NB - 2u < nstage && !fail) issue_b(s + NB - 2u);
+        // ---- weights of the stage -> fp16 digit tiles
         {
-            const uint4 *src = reinterpret_cast<const uint4 *>(xs_tile + (size_t)s * (2u * B_DIGIT / 2u));
-            uint4 *dst = reinterpret_cast<uint4 *>(buf + 2u * TC_A_DIGIT);
-            for (uint32_t i = tid; i < 2u * B_DIGIT / 16u; i += TC_THREADS) dst[i] = __ldg(src + i);
+            const uint32_t g8_0 = ((s * TC_KS) & 255u) >> 3, rows_live = J.nrows - row0 < TC_M ? J.nrows - row0 : TC_M;
+            if (J.type == RC_Q6_K) tc_decode_stage<RC_Q6_K>(raw, abuf, g8_0, rows_live, w_scale, bk, tid);
+            else if (J.type == RC_IQ2_XXS) tc_decode_stage<RC_IQ2_XXS>(raw, abuf, g8_0, rows_live, w_scale, bk, tid);
+            else tc_decode_stage<RC_IQ3_S>(raw, abuf, g8_0, rows_live, w_scale, bk, tid);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the tensor core
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
         if (tid == 0 && !fail) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_hi = smem_u32(buf), a_lo = a_hi + TC_A_DIGIT, b_hi = a_hi + 2u * TC_A_DIGIT, b_lo = b_hi + B_DIGIT;
-            constexpr uint32_t A_LBO = TC_M * 16u, B_LBO = (uint32_t)TN * 16u, SBO = 128u;
+            const uint32_t jb = s % NB;
+            if (!mbar_wait(smem_u32(&bfull[jb]), (s / NB) & 1u)) fail = 1u;
+            else {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_hi = smem_u32(abuf), a_lo = a_hi + TC_A_DIGIT, b_hi = smem_u32(b_base + jb * B_BUF), b_lo = b_hi + B_DIGIT;
+                constexpr uint32_t A_LBO = TC_M * 16u, B_LBO = (uint32_t)TN * 16u, SBO = 128u;
 #pragma unroll
-            for (uint32_t kk = 0; kk < TC_KS / 16u; ++kk) {
-                const uint64_t dah = tc_smem_desc(a_hi + 2u * kk * A_LBO, A_LBO, SBO), dal = tc_smem_desc(a_lo + 2u * kk * A_LBO, A_LBO, SBO);
-                const uint64_t dbh = tc_smem_desc(b_hi + 2u * kk * B_LBO, B_LBO, SBO), dbl = tc_smem_desc(b_lo + 2u * kk * B_LBO, B_LBO, SBO);
-                tc_mma(tmem, dah, dbh, idesc, (s | kk) ? 1u : 0u);
-                tc_mma(tmem, dah, dbl, idesc, 1u);
-                tc_mma(tmem, dal, dbh, idesc, 1u);
+                for (uint32_t kk = 0; kk < TC_KS / 16u; ++kk) {
+                    const uint64_t dah = tc_smem_desc(a_hi + 2u * kk * A_LBO, A_LBO, SBO), dal = tc_smem_desc(a_lo + 2u * kk * A_LBO, A_LBO, SBO);
+                    const uint64_t dbh = tc_smem_desc(b_hi + 2u * kk * B_LBO, B_LBO, SBO), dbl = tc_smem_desc(b_lo + 2u * kk * B_LBO, B_LBO, SBO);
+                    tc_mma(tmem, dah, dbh, idesc, (s | kk) ? 1u : 0u);
+                    tc_mma(tmem, dah, dbl, idesc, 1u);
+                    tc_mma(tmem, dal, dbh, idesc, 1u);
+                }
+                tc_commit(smem_u32(&mbar[b]));
             }
-            tc_commit(smem_u32(&mbar[b]));
         }
     }
-    // ---- all MMAs done? (the last commit of each buffer covers everything issued before it)
-    {
+    // ---- all MMAs done? (the last commit of each buffer covers everything issued before it). A timeout of thread 0
+    // inside the loop left a commit missing: the flag is read after a barrier and the waits below are bounded as well.
+    __syncthreads();
+    if (!fail) {
         const uint32_t last = nstage - 1u;
         if (!mbar_wait(smem_u32(&mbar[last & 1u]), (last >> 1) & 1u)) fail = 1u;
         if (nstage >= 2u && !mbar_wait(smem_u32(&mbar[(last - 1u) & 1u]), ((last - 1u) >> 1) & 1u)) fail = 1u;
@@ -278,19 +361,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __syncthreads();
     if (!fail) {
-        // warp w reads TMEM lanes 32*(w%4)..+31 (its quarter); warps w and w+4 share a quarter and split the columns
+        // warp w reads TMEM lanes 32*(w%4)..+31 (its quarter); the warps of a quarter split the columns
         const uint32_t q = warp & 3u, row = row0 + q * 32u + lane;
-        constexpr uint32_t HALF = (uint32_t)TN / 2u < 16u ? 16u : (uint32_t)TN / 2u;
-        const uint32_t c_begin = (warp >> 2) * HALF, c_end = c_begin + HALF > (uint32_t)TN ? (uint32_t)TN : c_begin + HALF;
-        for (uint32_t c = c_begin; c < c_end; c += 16u) {
-            uint32_t v[16];
-            asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                           "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        constexpr uint32_t PER = (uint32_t)TN / (TC_WARPS / 4u);          // columns per warp: 8, 16 or 32
+        const uint32_t c_begin = (warp >> 2) * PER;
+        for (uint32_t c = c_begin; c < c_begin + PER; c += 8u) {
+            uint32_t v[8];
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
                          : "r"(tmem + ((q * 32u) << 16) + c));
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
+            for (int j = 0; j < 8; ++j) {
                 const uint32_t t = t0 + c + j;
                 if (t < A.ntok && row < J.nrows) J.out[(size_t)t * J.out_stride + row] = __uint_as_float(v[j]) * w_inv * A.x_inv[t];
             }
@@ -303,11 +385,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
 
 size_t tc_xs_halves(uint32_t ntok, uint32_t ncols, uint32_t tn) { return (size_t)((ntok + tn - 1u) / tn) * tn * ncols * 2u; }
 
-uint32_t tc_token_tile(uint32_t ntok) { return ntok <= 32u ? 32u : ntok <= 64u ? 64u : 128u; }
+// Token tile (MMA N) of a launch: the largest of 32 / 64 / 128 that the chunk fills, halved while the grid would leave
+// most SMs idle (a CTA per 128 rows x tile; a smaller tile repeats the weight decode in more CTAs, which idle SMs absorb).
+uint32_t tc_token_tile(uint32_t ntok, uint32_t row_tiles) {
+    uint32_t tn = ntok <= 32u ? 32u : ntok <= 64u ? 64u : 128u;
+    while (tn > 32u && row_tiles * ((ntok + tn - 1u) / tn) < 96u) tn >>= 1;
+    return tn;
+}
+uint32_t tc_row_tiles(uint32_t nrows) { return (nrows + TC_M - 1u) / TC_M; }
 
-int launch_tc_prep_x(const float *x, uint32_t x_stride, uint32_t ntok, uint32_t ncols, __half *xs, float *x_inv, cudaStream_t s) {
+static size_t tc_smem_bytes(uint32_t tn, uint32_t raw_max) {
+    const uint32_t nb = tn >= 128u ? 3u : 4u;
+    return 2u * 2u * (size_t)TC_A_DIGIT + (size_t)nb * 2u * tn * TC_KS * 2u + 2u * (size_t)raw_max;
+}
+
+int launch_tc_prep_x(const float *x, uint32_t x_stride, uint32_t ntok, uint32_t ncols, uint32_t tn, __half *xs, float *x_inv, cudaStream_t s) {
     RC_REQUIRE(ncols % TC_KS == 0, "tc gemm: %u columns is not a multiple of %u", ncols, TC_KS);
-    const uint32_t tn = tc_token_tile(ntok), tiles = (ntok + tn - 1u) / tn;
+    RC_REQUIRE(tn == 32u || tn == 64u || tn == 128u, "tc gemm: token tile %u is not 32, 64 or 128", tn);
+    const uint32_t tiles = (ntok + tn - 1u) / tn;
     prof_begin("tc_prep_x", s);
     RC_LAUNCH((k_tc_prep_x), tiles * tn, 256, 0, s, x, x_stride, ntok, ncols, tn, xs, x_inv);
     prof_end(s);
@@ -315,7 +410,8 @@ int launch_tc_prep_x(const float *x, uint32_t x_stride, uint32_t ntok, uint32_t 
     return 1;
 }
 
-int launch_tc_gemm(TcArgs &A, const char *tag, cudaStream_t s) {
+int launch_tc_gemm(TcArgs &A, uint32_t tn, const char *tag, cudaStream_t s) {
+    RC_REQUIRE(tn == 32u || tn == 64u || tn == 128u, "tc gemm: token tile %u is not 32, 64 or 128", tn);
     RC_REQUIRE(A.njobs >= 1 && A.njobs <= TC_MAX_JOBS && A.ntok >= 1, "tc gemm: bad job count or no tokens");
     RC_REQUIRE(A.ncols % 256u == 0, "tc gemm: %u columns is not a multiple of 256", A.ncols);
     uint32_t tiles = 0;
@@ -325,11 +421,10 @@ int launch_tc_gemm(TcArgs &A, const char *tag, cudaStream_t s) {
         tiles += (A.job[j].nrows + TC_M - 1u) / TC_M;
     }
     A.iq2 = books_iq2(); A.iq3s = books_iq3s();
-    const uint32_t tn = tc_token_tile(A.ntok);
     const dim3 grid(tiles, (A.ntok + tn - 1u) / tn);
     uint32_t raw_max = 0;
     for (uint32_t j = 0; j < A.njobs; ++j) raw_max = raw_max > tc_raw_bytes(A.job[j].type) ? raw_max : tc_raw_bytes(A.job[j].type);
-    const size_t smem = 2u * (2u * TC_A_DIGIT + 2u * (size_t)tn * TC_KS * 2u) + 2u * (size_t)raw_max;
+    const size_t smem = tc_smem_bytes(tn, raw_max);
     prof_begin(tag, s);
 #define RC_TC_LAUNCH(TN_) do { \
         RC_CUDA(cudaFuncSetAttribute(k_tc_gemm<TN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
@@ -353,7 +448,7 @@ extern "C" int redcuda_quant_matmul_tc(uint32_t type, const uint8_t *w, uint32_t
     RC_REQUIRE(rc_is_quant(type), "matmul_tc: type %u is not a block-quantised format", type);
     RC_REQUIRE(ncols % 256u == 0, "matmul_tc: %u columns is not a multiple of 256", ncols);
     const uint64_t bytes = rc_matrix_bytes(type, nrows, ncols);
-    const uint32_t tn = tc_token_tile(ntok);
+    const uint32_t tn = tc_token_tile(ntok, tc_row_tiles(nrows));
     DevMem raw, planar, xd, od, xs, xinv, err;
     if (!raw.alloc(bytes) || !planar.alloc(bytes) || !xd.alloc((size_t)ntok * ncols * 4u) || !od.alloc((size_t)ntok * nrows * 4u) ||
         !xs.alloc(tc_xs_halves(ntok, ncols, tn) * 2u) || !xinv.alloc((size_t)((ntok + tn - 1u) / tn) * tn * 4u) || !err.alloc(4u)) return 0;
@@ -361,11 +456,11 @@ extern "C" int redcuda_quant_matmul_tc(uint32_t type, const uint8_t *w, uint32_t
     if (!upload_matrix(type, nrows, ncols, w, false, planar.as<uint8_t>(), raw.as<uint8_t>(), s)) return 0;
     RC_CUDA(cudaMemcpyAsync(xd.p, x, (size_t)ntok * ncols * 4u, cudaMemcpyHostToDevice, s));
     RC_CUDA(cudaMemsetAsync(err.p, 0, 4u, s));
-    if (!launch_tc_prep_x(xd.as<float>(), ncols, ntok, ncols, xs.as<__half>(), xinv.as<float>(), s)) return 0;
+    if (!launch_tc_prep_x(xd.as<float>(), ncols, ntok, ncols, tn, xs.as<__half>(), xinv.as<float>(), s)) return 0;
     TcArgs A{};
     A.njobs = 1; A.ncols = ncols; A.ntok = ntok; A.xs = xs.as<__half>(); A.x_inv = xinv.as<float>(); A.err = err.as<uint32_t>();
     A.job[0] = TcJob{planar.as<uint8_t>(), (uint64_t)nrows * (ncols / 256u), type, nrows, od.as<float>(), nrows, 0u};
-    if (!launch_tc_gemm(A, "tc_gemm", s)) return 0;
+    if (!launch_tc_gemm(A, tn, "tc_gemm", s)) return 0;
     uint32_t flag = 0;
     RC_CUDA(cudaMemcpyAsync(&flag, err.p, 4u, cudaMemcpyDeviceToHost, s));
     RC_CUDA(cudaMemcpyAsync(out, od.p, (size_t)ntok * nrows * 4u, cudaMemcpyDeviceToHost, s));

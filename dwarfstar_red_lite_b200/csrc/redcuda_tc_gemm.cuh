@@ -26,10 +26,11 @@ struct TcArgs {
     uint32_t *err;           // device flag: set to 1 when a bounded wait ran out
 };
 
-// halves of the digit buffer for ntok tokens of ncols columns (token tile = tc_token_tile(ntok))
+// halves of the digit buffer for ntok tokens of ncols columns with token tile tn (x_inv needs ntok rounded up to tn floats)
 size_t tc_xs_halves(uint32_t ntok, uint32_t ncols, uint32_t tn);
-uint32_t tc_token_tile(uint32_t ntok);
-int launch_tc_prep_x(const float *x, uint32_t x_stride, uint32_t ntok, uint32_t ncols, __half *xs, float *x_inv, cudaStream_t s);
-int launch_tc_gemm(TcArgs &A, const char *tag, cudaStream_t s);
+uint32_t tc_row_tiles(uint32_t nrows);
+uint32_t tc_token_tile(uint32_t ntok, uint32_t row_tiles);     // row_tiles = sum of tc_row_tiles over the launch's matrices
+int launch_tc_prep_x(const float *x, uint32_t x_stride, uint32_t ntok, uint32_t ncols, uint32_t tn, __half *xs, float *x_inv, cudaStream_t s);
+int launch_tc_gemm(TcArgs &A, uint32_t tn, const char *tag, cudaStream_t s);   // tn: the tile the digits were prepared with
 
 }  // namespace rc
