@@ -161,8 +161,9 @@ def workload_config(args, dims):
 
 
 def run_ep(args, world, rank, local):
-    """N > 1: expert parallelism. Every rank keeps its own 64 tokens (weak scaling) and 512 / N experts of every layer;
-    per layer one all-to-all each way over NCCL. Timed with CUDA events per rank, maximum over ranks."""
+    """N > 1: expert parallelism, all-gather form. Every rank keeps its own 64 tokens (weak scaling) and 512 / N experts of
+    every layer (expert e on rank e % N); per layer one all-gather of the token rows and one reduce-scatter of the
+    partial outputs over NCCL, no host synchronisation inside a step. Timed with CUDA events per rank, maximum over ranks."""
     import torch
     import torch.distributed as dist
     import dwarfstar_red_lite_b200 as rc
@@ -177,19 +178,18 @@ def run_ep(args, world, rank, local):
     layers = []
     for l in range(L):
         tens = synth_device.moe_layer_tensors(1000 + l, dims, dev, expert_begin=rank * ec, expert_count=ec)
-        m = rc.MoeLayer(device_tensors=tens, dims=dims, max_tokens=T * world, expert_begin=rank * ec, expert_count=ec)
-        layers.append(ep.EpMoeLayer(m, rank, world, T))
+        m = rc.MoeLayer(device_tensors=tens, dims=dims, max_tokens=T * world, expert_begin=rank, expert_count=ec, expert_stride=world)
+        layers.append(ep.EpGatherMoeLayer(m, rank, world, T))
         del tens
     logits_h = np.stack([synth.zipf_routing_logits(500 + l + 1000 * rank, T) for l in range(L)])
     gx = torch.Generator(device=dev)
     gx.manual_seed(7 + rank)
     x_d = torch.randn(L, T, dims.hidden, device=dev, generator=gx)
     logits_d = torch.from_numpy(logits_h).to(dev)
-    out_d = torch.empty(L, T, dims.hidden, device=dev)
 
     def step():
         for l in range(L):
-            layers[l].forward(x_d[l], out_d[l], logits=logits_d[l])
+            layers[l].forward(x_d[l], logits=logits_d[l])
 
     n0 = rcm.lib().redcuda_launch_count()
     step()
@@ -198,16 +198,47 @@ def run_ep(args, world, rank, local):
         step()
     torch.cuda.synchronize()
     dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(args.steps):
-            step()
-        e1.record()
-        torch.cuda.synchronize()
+    # The step has nothing data-dependent on the host, so it can be captured (collectives included) into one CUDA graph.
+    # Off unless RC_EP_GRAPH=1: replaying NCCL collectives from a graph did not complete on a 2-GPU run of this bench,
+    # so the default is the eager step, which the host queues without ever waiting for the devices.
+    graph = None
+    side = torch.cuda.Stream()
+    if os.environ.get("RC_EP_GRAPH", "0") == "1":
+        try:
+            with torch.cuda.stream(side):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    step()
+                graph = g
+        except Exception as exc:          # noqa: BLE001
+            sys.stderr.write(f"rank {rank}: CUDA graph capture of the EP step failed ({exc}); running eager\n")
+            graph = None
+        ok = torch.tensor([1.0 if graph is not None else 0.0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() < 1.0:
+            graph = None
+    run = (lambda: graph.replay()) if graph is not None else step
+    with torch.cuda.stream(side):
+        run()
+        side.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clocks:
+            torch.cuda.synchronize()
+            e0.record(side)
+            for _ in range(args.steps):
+                run()
+            e1.record(side)
+            torch.cuda.synchronize()
     ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    pairs = torch.tensor([float(sum(lay.pair_counts_last or 0 for lay in layers)) / L], device=dev)
+    # pairs this rank's experts served per layer (from the drawn logits of every rank: the same seeds on every rank)
+    mine = 0
+    for r in range(world):
+        for l in range(L):
+            lg = logits_h[l] if r == rank else synth.zipf_routing_logits(500 + l + 1000 * r, T)
+            top = np.argpartition(-lg, dims.top_k - 1, axis=1)[:, :dims.top_k]
+            mine += int(np.sum(top % world == rank))
+    pairs = torch.tensor([mine / L], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     allpairs = [torch.zeros_like(pairs) for _ in range(world)]
     dist.all_gather(allpairs, pairs)
@@ -217,8 +248,9 @@ def run_ep(args, world, rank, local):
         value = T * world * L / (ms_per_step * 1e-3)
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": dict(workload_config(args, dims), experts_per_gpu=ec, pairs_received_per_rank_per_layer=[float(p.item()) for p in allpairs],
-                               exchange="2 x NCCL all_to_all_single per layer (activations fp32 out, expert outputs fp32 back) + one count exchange"),
+                "config": dict(workload_config(args, dims), experts_per_gpu=ec, expert_placement="interleaved (expert e on rank e % N)",
+                               pairs_served_per_rank_per_layer=[float(p.item()) for p in allpairs], cuda_graph=graph is not None,
+                               exchange="per layer: NCCL all-gather of the token rows (fp32 activations + router ids/weights), reduce-scatter of the partial outputs; no host synchronisation"),
                 "roofline": None, "cpu_baseline": None,
                 "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                         "note": "multi-GPU runs keep activations on the devices; the host-buffer path is measured at N=1"},

@@ -386,6 +386,60 @@ __global__ void __launch_bounds__(256) k_vec_sigmoid(const float *__restrict__ w
     }
 }
 
+// Router logits of a batch: logits[t][e] = (float) sum_k (double) x[t][k] * (double) w[e][k], F32 weights
+// (rl_quant_row_dot on an F32 row accumulates in double, native/redlite_native_quant_cpu.c:198-212, and the top-k that
+// follows must not depend on a summation order). The multi-token GEMV re-reads the matrix for every four tokens; this
+// is a small tiled fp64 GEMM instead: block = 16 tokens x 32 experts, K in tiles of 64 staged as doubles in shared
+// memory (the next tile is fetched into registers while the current one is multiplied), thread = 1 token x 2 experts.
+constexpr uint32_t RL_TT = 16u, RL_TE = 32u, RL_KT = 64u, RL_PITCH = RL_KT + 1u;
+__global__ void __launch_bounds__(256) k_router_logits(const float *__restrict__ w, const float *__restrict__ x, uint32_t x_stride, uint32_t ntok,
+                                                       uint32_t n_expert, uint32_t ncols, float *__restrict__ logits) {
+    pdl_prologue();
+    __shared__ double xs[RL_TT * RL_PITCH], ws[RL_TE * RL_PITCH];
+    const uint32_t tid = threadIdx.x, ty = tid >> 4, tx = tid & 15u;
+    const uint32_t t0 = blockIdx.x * RL_TT, e0 = blockIdx.y * RL_TE;
+    // staging roles: the weight tile is 32 rows x 64 floats = 512 float4 (two per thread), the token tile 16 x 64 = 256 float4
+    const uint32_t wr = tid >> 4, wc = (tid & 15u) * 4u;               // rows wr and wr + 16
+    const uint32_t xr = tid >> 4, xc = (tid & 15u) * 4u;
+    const bool w_ok0 = e0 + wr < n_expert, w_ok1 = e0 + wr + 16u < n_expert, x_ok = t0 + xr < ntok;
+    const float *wp0 = w + (size_t)(e0 + wr) * ncols + wc, *wp1 = w + (size_t)(e0 + wr + 16u) * ncols + wc;
+    const float *xp = x + (size_t)(t0 + xr) * x_stride + xc;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 rw0 = w_ok0 ? __ldg(reinterpret_cast<const float4 *>(wp0)) : zero, rw1 = w_ok1 ? __ldg(reinterpret_cast<const float4 *>(wp1)) : zero;
+    float4 rx = x_ok ? *reinterpret_cast<const float4 *>(xp) : zero;
+    double acc0 = 0.0, acc1 = 0.0;
+    for (uint32_t k0 = 0; k0 < ncols; k0 += RL_KT) {
+        __syncthreads();                                   // the previous tile is no longer read
+        double *d0 = ws + wr * RL_PITCH + wc, *d1 = ws + (wr + 16u) * RL_PITCH + wc, *dx = xs + xr * RL_PITCH + xc;
+        d0[0] = rw0.x; d0[1] = rw0.y; d0[2] = rw0.z; d0[3] = rw0.w;
+        d1[0] = rw1.x; d1[1] = rw1.y; d1[2] = rw1.z; d1[3] = rw1.w;
+        dx[0] = rx.x; dx[1] = rx.y; dx[2] = rx.z; dx[3] = rx.w;
+        __syncthreads();
+        if (k0 + RL_KT < ncols) {
+            rw0 = w_ok0 ? __ldg(reinterpret_cast<const float4 *>(wp0 + k0 + RL_KT)) : zero;
+            rw1 = w_ok1 ? __ldg(reinterpret_cast<const float4 *>(wp1 + k0 + RL_KT)) : zero;
+            rx = x_ok ? *reinterpret_cast<const float4 *>(xp + k0 + RL_KT) : zero;
+        }
+        const double *a = xs + ty * RL_PITCH, *b0 = ws + tx * RL_PITCH, *b1 = ws + (tx + 16u) * RL_PITCH;
+#pragma unroll 16
+        for (uint32_t kk = 0; kk < RL_KT; ++kk) { const double av = a[kk]; acc0 = fma(av, b0[kk], acc0); acc1 = fma(av, b1[kk], acc1); }
+    }
+    if (t0 + ty < ntok) {
+        if (e0 + tx < n_expert) logits[(size_t)(t0 + ty) * n_expert + e0 + tx] = (float)acc0;
+        if (e0 + tx + 16u < n_expert) logits[(size_t)(t0 + ty) * n_expert + e0 + tx + 16u] = (float)acc1;
+    }
+}
+
+int launch_router_logits(const float *w, const float *x, uint32_t x_stride, uint32_t ntok, uint32_t n_expert, uint32_t ncols, float *logits, cudaStream_t stream) {
+    RC_REQUIRE(ncols % RL_KT == 0 && x_stride % 4u == 0, "router logits: %u columns (stride %u) is not a multiple of %u", ncols, x_stride, RL_KT);
+    if (!ntok) return 1;
+    prof_begin("moe_router_logits", stream);
+    RC_LAUNCH((k_router_logits), dim3((ntok + RL_TT - 1u) / RL_TT, (n_expert + RL_TE - 1u) / RL_TE), 256, 0, stream, w, x, x_stride, ntok, n_expert, ncols, logits);
+    prof_end(stream);
+    RC_LAUNCHED();
+    return 1;
+}
+
 int launch_vec_sigmoid(const float *w, const float *x, uint32_t x_stride, uint32_t ncols, uint32_t ntok, float *out, cudaStream_t stream) {
     RC_REQUIRE(ncols % 4u == 0, "vec_sigmoid: %u columns is not a multiple of 4", ncols);
     if (!ntok) return 1;

@@ -46,5 +46,7 @@ int launch_deltanet_seq(const DnDims &D, uint32_t T, const float *conv_kernel, c
                     float *qk, float *v, float *beta, float *gate, float *core, float *out, cudaStream_t s);
 
 int launch_vec_sigmoid(const float *w, const float *x, uint32_t x_stride, uint32_t ncols, uint32_t ntok, float *out, cudaStream_t stream);
+// logits[t][e] = dot(w[e], x[t]) accumulated in double, F32 weights [n_expert][ncols]; for batches (tiled fp64 GEMM)
+int launch_router_logits(const float *w, const float *x, uint32_t x_stride, uint32_t ntok, uint32_t n_expert, uint32_t ncols, float *logits, cudaStream_t stream);
 
 }  // namespace rc

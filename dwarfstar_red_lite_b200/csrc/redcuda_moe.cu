@@ -102,8 +102,18 @@ __global__ void __launch_bounds__(256) k_moe_experts(const __grid_constant__ Moe
 // that received at least one pair; n_unique their count. Every expert's pairs are also cut into work items of at most
 // item_tok pairs (item_u = slot in uexp, item_p0 = first position in sorted[]), so that kernels which take one item
 // per block see equal-sized work whatever the routing skew. One block of 1024 threads, expert_count <= 1024.
-__global__ void __launch_bounds__(1024) k_group_pairs(const uint32_t *__restrict__ pair_expert, uint32_t npairs, uint32_t expert_begin,
-                                                      uint32_t expert_count, uint32_t item_tok, uint32_t *__restrict__ sorted, uint32_t *__restrict__ uexp,
+// Ownership: expert g belongs to the shard when g = expert_begin + i * expert_stride for some i < expert_count (i is the
+// index of its matrices in the shard; uexp holds expert_begin + i). Pairs of other shards are counted in *bad, or just
+// left out when skip_foreign is set (the all-gather form of expert parallelism hands every rank every pair).
+__device__ __forceinline__ uint32_t shard_local(uint32_t g, uint32_t begin, uint32_t stride, uint32_t count) {
+    const uint32_t d = g - begin;
+    if (g < begin || d % stride) return 0xffffffffu;
+    const uint32_t i = d / stride;
+    return i < count ? i : 0xffffffffu;
+}
+
+__global__ void __launch_bounds__(1024) k_group_pairs(const uint32_t *__restrict__ pair_expert, uint32_t npairs, uint32_t expert_begin, uint32_t expert_stride,
+                                                      uint32_t skip_foreign, uint32_t expert_count, uint32_t item_tok, uint32_t *__restrict__ sorted, uint32_t *__restrict__ uexp,
                                                       uint32_t *__restrict__ ustart, uint32_t *__restrict__ n_unique, uint32_t *__restrict__ item_u,
                                                       uint32_t *__restrict__ item_p0, uint32_t *__restrict__ n_items, uint32_t *__restrict__ bad) {
     pdl_prologue();
@@ -112,8 +122,8 @@ __global__ void __launch_bounds__(1024) k_group_pairs(const uint32_t *__restrict
     cnt[tid] = 0;
     __syncthreads();
     for (uint32_t p = tid; p < npairs; p += 1024u) {
-        const uint32_t e = pair_expert[p] - expert_begin;
-        if (e < expert_count) atomicAdd(&cnt[e], 1u); else atomicAdd(bad, 1u);   // a pair outside the shard is reported, not run
+        const uint32_t e = shard_local(pair_expert[p], expert_begin, expert_stride, expert_count);
+        if (e != 0xffffffffu) atomicAdd(&cnt[e], 1u); else if (!skip_foreign) atomicAdd(bad, 1u);   // a pair outside the shard is reported, not run
     }
     __syncthreads();
     // exclusive scans over experts of (count), (count > 0) and (items)
@@ -143,8 +153,8 @@ __global__ void __launch_bounds__(1024) k_group_pairs(const uint32_t *__restrict
     cnt[tid] = 0;
     __syncthreads();
     for (uint32_t p = tid; p < npairs; p += 1024u) {
-        const uint32_t e = pair_expert[p] - expert_begin;
-        if (e < expert_count) sorted[start[e] + atomicAdd(&cnt[e], 1u)] = p;
+        const uint32_t e = shard_local(pair_expert[p], expert_begin, expert_stride, expert_count);
+        if (e != 0xffffffffu) sorted[start[e] + atomicAdd(&cnt[e], 1u)] = p;
     }
 }
 
@@ -170,6 +180,7 @@ __global__ void __launch_bounds__(256) k_moe_combine(const float *__restrict__ p
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (uint32_t k = 0; k < top_k; ++k) {
         const float wk = w[(size_t)t * top_k + k];
+        if (wk == 0.f) continue;           // also the mark of a pair that another shard computes: its row was never written
         const size_t prow = pair_row ? pair_row[(size_t)t * top_k + k] : (size_t)t * top_k + k;   // where the pair's expert output sits
         const float4 v = *reinterpret_cast<const float4 *>(pair_out + prow * hidden + r);
         acc.x += wk * v.x; acc.y += wk * v.y; acc.z += wk * v.z; acc.w += wk * v.w;
@@ -231,7 +242,12 @@ static int moe_gemv_pre(redcuda_moe *m, uint32_t ntok, const float *x, bool with
         J.w0 = w0.base; J.w1 = w1 ? w1->base : nullptr; J.out = out; J.nb = w0.nb; J.type = w0.type; J.nrows = w0.nrows; J.ncols = w0.ncols;
         J.out_stride = stride; J.epi = epi;
     };
-    if (with_router) add(m->router, nullptr, m->logits, m->d.n_expert, GEMV_STORE);
+    if (with_router) {
+        // batches: the tiled fp64 GEMM (one pass over the router matrix per 16 tokens of a block, from shared memory)
+        if (ntok >= 8u && m->router.type == RC_F32 && m->d.hidden % 64u == 0) {
+            if (!launch_router_logits((const float *)m->router.base, x, m->d.hidden, ntok, m->d.n_expert, m->d.hidden, m->logits, s)) return 0;
+        } else add(m->router, nullptr, m->logits, m->d.n_expert, GEMV_STORE);
+    }
     if (with_shared) {
         if (moe_shared_mma(m, ntok) && x_quantised) {
             if (!launch_q6k_mma(m->sh_gate.base, m->sh_up.base, m->sh_gate.nb, m->d.ffn_sh, m->d.hidden, ntok, m->xq_x, m->sx_x, m->sh_act, m->d.ffn_sh,
@@ -315,13 +331,13 @@ static int moe_launch_experts(redcuda_moe *m, bool gateup, uint32_t npairs, bool
     return 1;
 }
 
-static int moe_group(redcuda_moe *m, const uint32_t *pair_expert, uint32_t npairs, bool distinct, cudaStream_t s) {
+static int moe_group(redcuda_moe *m, const uint32_t *pair_expert, uint32_t npairs, bool distinct, cudaStream_t s, bool skip_foreign = false) {
     RC_REQUIRE(npairs <= m->max_pairs, "moe: %u pairs exceed the workspace (%u)", npairs, m->max_pairs);
     prof_begin("moe_group", s);
-    if (distinct && npairs <= 64u) {
+    if (distinct && npairs <= 64u && !skip_foreign) {
         RC_LAUNCH((k_group_trivial), 1, 64, 0, s, pair_expert, npairs, m->sorted, m->uexp, m->ustart, m->n_unique, m->item_u, m->item_p0, m->n_items);
     } else {
-        RC_LAUNCH((k_group_pairs), 1, 1024, 0, s, pair_expert, npairs, m->d.expert_begin, m->d.expert_count, mma_item_tokens(false), m->sorted, m->uexp, m->ustart,
+        RC_LAUNCH((k_group_pairs), 1, 1024, 0, s, pair_expert, npairs, m->d.expert_begin, m->d.expert_stride, skip_foreign ? 1u : 0u, m->d.expert_count, mma_item_tokens(false), m->sorted, m->uexp, m->ustart,
                                          m->n_unique, m->item_u, m->item_p0, m->n_items, m->bad);
     }
     prof_end(s);
@@ -340,7 +356,7 @@ static int moe_combine(redcuda_moe *m, uint32_t ntok, const float *pair_out, con
 }
 
 static int moe_forward_on(redcuda_moe *m, uint32_t ntok, const float *x, const float *logits_in, const float *resid, float *out, cudaStream_t s) {
-    RC_REQUIRE(m->d.expert_begin == 0 && m->d.expert_count == m->d.n_expert, "moe forward needs every expert on this device; use the route/experts/shared pieces under expert parallelism");
+    RC_REQUIRE(m->d.expert_begin == 0 && m->d.expert_count == m->d.n_expert && m->d.expert_stride == 1u, "moe forward needs every expert on this device; use the route/experts/shared pieces under expert parallelism");
     RC_REQUIRE(ntok >= 1 && ntok <= m->d.max_tokens, "moe forward: ntok %u outside [1, %u]", ntok, m->d.max_tokens);
     const uint32_t k = m->d.top_k, npairs = ntok * k;
     // one quantisation of the token activations serves the routed gate/up and the shared gate/up
@@ -379,13 +395,15 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
     if (d.top_k > REDCUDA_MAX_TOPK || d.top_k > d.n_expert) return fail("top_k out of range");
     if (d.hidden % 256u || d.ffn % 256u || d.ffn_sh % 256u) return fail("hidden / ffn sizes must be multiples of 256");
     if (!rc_is_quant(d.type_gu) || !rc_is_quant(d.type_down) || !rc_is_quant(d.type_sh)) return fail("expert matrices must be IQ2_XXS, IQ3_S or Q6_K");
-    if (d.expert_count == 0 || d.expert_begin + d.expert_count > d.n_expert || d.expert_count > 1024u) return fail("bad expert shard");
+    const uint32_t stride = d.expert_stride ? d.expert_stride : 1u;
+    if (d.expert_count == 0 || d.expert_count > 1024u || (uint64_t)d.expert_begin + (uint64_t)(d.expert_count - 1u) * stride >= d.n_expert) return fail("bad expert shard");
     if (!d.router || !d.gate_exps || !d.up_exps || !d.down_exps || !d.sh_gate_inp || !d.sh_gate || !d.sh_up || !d.sh_down) return fail("null weight pointer");
     if (!require_books(d.type_gu) || !require_books(d.type_down) || !require_books(d.type_sh)) return nullptr;
 
     redcuda_moe *m = new (std::nothrow) redcuda_moe();
     if (!m) return fail("out of host memory");
     m->d = d;
+    m->d.expert_stride = stride;
     cudaGetDevice(&m->device);
     auto bail = [&]() -> redcuda_moe * { redcuda_moe_destroy(m); return nullptr; };
     if (cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess || cudaStreamCreateWithFlags(&m->side, cudaStreamNonBlocking) != cudaSuccess ||
@@ -519,6 +537,38 @@ int redcuda_moe_experts_device(redcuda_moe *m, uint32_t npairs, const float *pai
     if (!moe_group(m, pair_expert_dev, npairs, false, s)) return 0;
     if (!moe_launch_experts(m, true, npairs, false, pair_x_dev, m->d.hidden, 1u, false, m->act, m->d.ffn, s)) return 0;
     return moe_launch_experts(m, false, npairs, false, m->act, m->d.ffn, 1u, false, pair_out_dev, m->d.hidden, s);
+}
+
+// Contiguous copies of the pairs' expert ids and of their router weights, the weight zeroed when the expert lives on
+// another shard (ids / w rows are meta_stride elements apart)
+__global__ void k_mask_weights(const uint32_t *__restrict__ ids, const float *__restrict__ w, uint32_t ntok, uint32_t top_k, uint32_t meta_stride,
+                               uint32_t begin, uint32_t stride, uint32_t count, uint32_t *__restrict__ ids_out, float *__restrict__ w_local) {
+    pdl_prologue();
+    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= ntok * top_k) return;
+    const uint32_t t = p / top_k, k = p - t * top_k;
+    const uint32_t g = ids[(size_t)t * meta_stride + k];
+    ids_out[p] = g;
+    w_local[p] = shard_local(g, begin, stride, count) != 0xffffffffu ? w[(size_t)t * meta_stride + k] : 0.f;
+}
+
+int redcuda_moe_partial_device(redcuda_moe *m, uint32_t ntok, const float *x_dev, uint32_t x_stride, const uint32_t *ids_dev, const float *weights_dev,
+                               uint32_t meta_stride, float *out_dev, void *stream) {
+    RC_REQUIRE(m && x_dev && ids_dev && weights_dev && out_dev, "moe partial: null argument");
+    RC_REQUIRE(ntok >= 1 && ntok <= m->d.max_tokens, "moe partial: ntok %u outside [1, %u]", ntok, m->d.max_tokens);
+    RC_REQUIRE(x_stride >= m->d.hidden && x_stride % 4u == 0 && meta_stride >= m->d.top_k, "moe partial: bad row strides (%u, %u)", x_stride, meta_stride);
+    cudaStream_t s = (cudaStream_t)stream;
+    const uint32_t k = m->d.top_k, npairs = ntok * k;
+    const bool xq = moe_experts_mma(m);
+    if (xq && !launch_quant_act(x_dev, x_stride, ntok, m->d.hidden, m->xq_x, m->sx_x, s)) return 0;
+    prof_begin("moe_mask_weights", s);
+    RC_LAUNCH((k_mask_weights), (npairs + 255u) / 256u, 256, 0, s, ids_dev, weights_dev, ntok, k, meta_stride, m->d.expert_begin, m->d.expert_stride, m->d.expert_count, m->ids, m->wk);
+    prof_end(s);
+    RC_LAUNCHED();
+    if (!moe_group(m, m->ids, npairs, false, s, true)) return 0;
+    if (!moe_launch_experts(m, true, npairs, false, x_dev, x_stride, k, xq, m->act, m->d.ffn, s)) return 0;
+    if (!moe_launch_experts(m, false, npairs, false, m->act, m->d.ffn, 1u, false, m->tmp, m->d.hidden, s)) return 0;
+    return moe_combine(m, ntok, m->tmp, m->wk, k, false, nullptr, out_dev, s);
 }
 
 int redcuda_moe_combine_device(redcuda_moe *m, uint32_t ntok, const float *pair_out_dev, const uint32_t *pair_row_dev, const float *weights_dev,

@@ -1,5 +1,13 @@
-"""Expert parallelism for the ragged-batch MoE layer: one process per GPU, experts sharded contiguously
-(expert e lives on rank e // (n_expert / world)), router and shared expert replicated, tokens stay with their rank.
+"""Expert parallelism for the ragged-batch MoE layer: one process per GPU, router and shared expert replicated, tokens
+stay with their rank. Two forms:
+
+* all-gather form (EpGatherMoeLayer, the one bench.py runs): experts interleaved over the ranks (expert e on rank
+  e % world, so a skewed routing loads the ranks evenly); per layer every rank all-gathers the step's token rows with
+  their router ids / weights (a decode batch is small: 64 tokens x 8 KB per rank), runs its own experts over the pairs
+  that select them, and a reduce-scatter sums the ranks' partial outputs back to the tokens' owners. Two fixed-size
+  collectives per layer, nothing data-dependent on the host, so the whole step is queued without a synchronisation.
+* dispatch form (EpMoeLayer): experts sharded contiguously (expert e on rank e // (n_expert / world)), pairs sent to
+  their experts' ranks by all-to-all with data-dependent split sizes (one host synchronisation per layer).
 
 Per layer: route locally -> (token, expert) pairs sorted by destination rank -> all-to-all of the pair activations and
 expert ids (dispatch) -> the shard's expert FFN over the received pairs -> all-to-all of the expert outputs back
@@ -111,3 +119,63 @@ class EpMoeLayer:
         _, plan = ep_moe_forward(x, ids, w, self.dims.n_expert, self.world, experts_fn, shared_fn, combine_fn, self.group)
         self.pair_counts_last = sum(plan.recv_counts)
         return out
+
+
+def gather_moe_forward(packed: torch.Tensor, hidden: int, top_k: int, world: int, partial_fn, shared_fn, group=None):
+    """All-gather form of one layer. packed [T, hidden + 2*top_k] float32: the token's activation row followed by its
+    router ids (int32 bits) and weights. partial_fn(all_packed [world*T, hidden + 2*top_k]) -> [world*T, hidden] partial
+    sums of this rank's experts; shared_fn(packed) -> [T, hidden] or None (runs while the all-gather is in flight).
+    Returns routed [T, hidden] (+ shared)."""
+    T = packed.shape[0]
+    if world > 1:
+        all_packed = packed.new_empty((world * T, packed.shape[1]))
+        work = dist.all_gather_into_tensor(all_packed, packed, group=group, async_op=True)
+        shared = shared_fn(packed) if shared_fn is not None else None
+        work.wait()
+    else:
+        all_packed = packed
+        shared = shared_fn(packed) if shared_fn is not None else None
+    partial = partial_fn(all_packed)
+    if world > 1:
+        routed = partial.new_empty((T, hidden))
+        dist.reduce_scatter_tensor(routed, partial, op=dist.ReduceOp.SUM, group=group)
+    else:
+        routed = partial
+    return routed if shared is None else routed.add_(shared)
+
+
+class EpGatherMoeLayer:
+    """One MoE layer under the all-gather form on CUDA: wraps a redcuda MoeLayer created with expert_begin = rank,
+    expert_stride = world, max_tokens >= world * tokens."""
+
+    def __init__(self, moe_shard, rank: int, world: int, tokens: int, group=None):
+        self.m, self.rank, self.world, self.group, self.T = moe_shard, rank, world, group, tokens
+        d = moe_shard.dims
+        self.dims = d
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.width = d.hidden + 2 * d.top_k
+        self.packed = torch.zeros(tokens, self.width, dtype=torch.float32, device=dev)       # x | ids | weights
+        self.ids = torch.empty(tokens, d.top_k, dtype=torch.int32, device=dev)
+        self.w = torch.empty(tokens, d.top_k, dtype=torch.float32, device=dev)
+        self.shared = torch.empty(tokens, d.hidden, dtype=torch.float32, device=dev)
+        self.partial = torch.empty(world * tokens, d.hidden, dtype=torch.float32, device=dev)
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor | None = None) -> torch.Tensor:
+        d, T = self.dims, self.T
+        st = torch.cuda.current_stream().cuda_stream
+        self.packed[:, :d.hidden].copy_(x)
+        self.m.route_device(T, x.data_ptr(), self.ids.data_ptr(), self.w.data_ptr(), st, logits_ptr=0 if logits is None else logits.data_ptr())
+        self.packed[:, d.hidden:d.hidden + d.top_k].copy_(self.ids.view(torch.float32))
+        self.packed[:, d.hidden + d.top_k:].copy_(self.w)
+
+        def partial_fn(allp):
+            n = allp.shape[0]
+            base = allp.data_ptr()
+            self.m.partial_device(n, base, self.width, base + 4 * d.hidden, base + 4 * (d.hidden + d.top_k), self.width, self.partial.data_ptr(), st)
+            return self.partial[:n]
+
+        def shared_fn(pk):
+            self.m.shared_device(T, x.data_ptr(), self.shared.data_ptr(), st)
+            return self.shared
+
+        return gather_moe_forward(self.packed, d.hidden, d.top_k, self.world, partial_fn, shared_fn, self.group)

@@ -19,7 +19,7 @@ EXPORTS = [
     "redcuda_deltanet_step_noalloc",
     "redcuda_moe_create", "redcuda_moe_destroy", "redcuda_moe_resident_bytes", "redcuda_moe_forward",
     "redcuda_moe_forward_device", "redcuda_moe_route_device", "redcuda_moe_experts_device", "redcuda_moe_shared_device",
-    "redcuda_moe_combine_device",
+    "redcuda_moe_combine_device", "redcuda_moe_partial_device",
     "redcuda_launch_count", "redcuda_profile_enable", "redcuda_profile_report",
     # engine ABI (include/rl_engine.h)
     "rl_engine_config_default", "rl_engine_open", "rl_engine_close", "rl_engine_info_get", "rl_engine_reset", "rl_engine_position",
@@ -43,7 +43,7 @@ class MoeDesc(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ["hidden", "n_expert", "top_k", "ffn", "ffn_sh", "type_gu", "type_down", "type_sh",
                                           "expert_begin", "expert_count", "max_tokens", "weights_on_device"]] + \
                [("router", C.c_void_p), ("gate_exps", C.c_void_p), ("up_exps", C.c_void_p), ("down_exps", C.c_void_p),
-                ("sh_gate_inp", C.c_void_p), ("sh_gate", C.c_void_p), ("sh_up", C.c_void_p), ("sh_down", C.c_void_p)]
+                ("sh_gate_inp", C.c_void_p), ("sh_gate", C.c_void_p), ("sh_up", C.c_void_p), ("sh_down", C.c_void_p), ("expert_stride", C.c_uint32)]
 
 
 _lib = None
@@ -72,6 +72,7 @@ def lib():
     L.redcuda_moe_experts_device.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.redcuda_moe_shared_device.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]
     L.redcuda_moe_combine_device.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    L.redcuda_moe_partial_device.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
     L.redcuda_quant_dequant_rows.argtypes = [C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]
     L.redcuda_quant_matvec.argtypes = [C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
     L.redcuda_quant_matmul_tc.argtypes = [C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
@@ -192,7 +193,7 @@ class MoeLayer:
     """One resident MoE layer (router + every routed expert + shared expert in HBM)."""
 
     def __init__(self, layer=None, max_tokens: int = 64, expert_begin: int = 0, expert_count: int | None = None, device_tensors: dict | None = None,
-                 dims=None):
+                 dims=None, expert_stride: int = 1):
         """layer: a synth.MoeLayer with host arrays; or device_tensors: dict of torch CUDA uint8/float32 tensors with the
         same field names (raw GGUF bytes on the device), with dims given."""
         _ensure_books()
@@ -200,7 +201,8 @@ class MoeLayer:
         d = dims if dims is not None else layer.dims
         self.dims = d
         self.max_tokens = max_tokens
-        ec = d.n_expert - expert_begin if expert_count is None else expert_count
+        st = max(1, expert_stride)
+        ec = (d.n_expert - expert_begin + st - 1) // st if expert_count is None else expert_count
         names = ["router", "gate", "up", "down", "sh_gate_inp", "sh_gate", "sh_up", "sh_down"]
         if device_tensors is not None:
             ptrs = [device_tensors[n].data_ptr() for n in names]
@@ -210,12 +212,13 @@ class MoeLayer:
             keep = [np.ascontiguousarray(getattr(layer, n)) for n in names]
             # an expert shard takes the slice of the expert-major arrays
             gu, dn = keep[1].reshape(d.n_expert, -1), keep[3].reshape(d.n_expert, -1)
-            keep[1] = np.ascontiguousarray(gu[expert_begin:expert_begin + ec])
-            keep[2] = np.ascontiguousarray(keep[2].reshape(d.n_expert, -1)[expert_begin:expert_begin + ec])
-            keep[3] = np.ascontiguousarray(dn[expert_begin:expert_begin + ec])
+            sel = slice(expert_begin, expert_begin + (ec - 1) * st + 1, st)
+            keep[1] = np.ascontiguousarray(gu[sel])
+            keep[2] = np.ascontiguousarray(keep[2].reshape(d.n_expert, -1)[sel])
+            keep[3] = np.ascontiguousarray(dn[sel])
             ptrs = [a.ctypes.data for a in keep]
             on_dev = 0
-        desc = MoeDesc(d.hidden, d.n_expert, d.top_k, d.ffn, d.ffn_sh, d.type_gu, d.type_down, d.type_sh, expert_begin, ec, max_tokens, on_dev, *ptrs)
+        desc = MoeDesc(d.hidden, d.n_expert, d.top_k, d.ffn, d.ffn_sh, d.type_gu, d.type_down, d.type_sh, expert_begin, ec, max_tokens, on_dev, *ptrs, st)
         h = lib().redcuda_moe_create(C.byref(desc))
         del keep
         if not h:
@@ -268,6 +271,10 @@ class MoeLayer:
     def combine_device(self, ntok: int, pair_out_ptr: int, pair_row_ptr: int, weights_ptr: int, add_ptr: int, resid_ptr: int, out_ptr: int, stream: int):
         _check(lib().redcuda_moe_combine_device(self._h, ntok, pair_out_ptr, pair_row_ptr or None, weights_ptr, add_ptr or None, resid_ptr or None,
                                                 out_ptr, stream or None))
+
+    def partial_device(self, ntok: int, x_ptr: int, x_stride: int, ids_ptr: int, weights_ptr: int, meta_stride: int, out_ptr: int, stream: int):
+        """out[t] = sum over token t's pairs whose expert lives on this shard of weight * expert(x[t])"""
+        _check(lib().redcuda_moe_partial_device(self._h, ntok, x_ptr, x_stride, ids_ptr, weights_ptr, meta_stride, out_ptr, stream or None))
 
     def shared_device(self, ntok: int, x_ptr: int, out_ptr: int, stream: int):
         _check(lib().redcuda_moe_shared_device(self._h, ntok, x_ptr, out_ptr, stream or None))

@@ -116,11 +116,23 @@ typedef struct {
     const float *sh_gate_inp;              /* [hidden] F32 */
     const uint8_t *sh_gate, *sh_up;        /* [ffn_sh][hidden] */
     const uint8_t *sh_down;                /* [hidden][ffn_sh] */
+    uint32_t expert_stride;                /* 0 or 1: the shard is the contiguous range above. s > 1: the shard holds experts
+                                              expert_begin + i * s, i < expert_count (interleaved placement, which spreads the
+                                              hot experts of a skewed routing over the ranks); matrix i belongs to that expert */
 } redcuda_moe_desc;
 
 redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc);
 void redcuda_moe_destroy(redcuda_moe *m);
 uint64_t redcuda_moe_resident_bytes(const redcuda_moe *m);
+
+/* Expert parallelism, all-gather form (no reference counterpart: the reference is single-device; the pair layout is its
+ * expert_start / pair_token / pair_weight of native/redmetal_topk.h:182-190). Every rank holds every token of the step
+ * (x rows x_stride floats apart) with its router ids / weights (rows meta_stride elements apart) and computes
+ * out[t] = sum over the pairs of token t whose expert lives on THIS shard of weight * expert(x[t]); pairs of other shards
+ * are skipped, a token without local pairs gets zeros. The sum of the ranks' outputs (a reduce-scatter) is the routed
+ * part of the layer. Device pointers, asynchronous on `stream`; ntok <= max_tokens. */
+int redcuda_moe_partial_device(redcuda_moe *m, uint32_t ntok, const float *x_dev, uint32_t x_stride, const uint32_t *ids_dev,
+                               const float *weights_dev, uint32_t meta_stride, float *out_dev, void *stream);
 
 /* One MoE FFN pass over ntok tokens (host pointers, synchronous): out[t] = routed(x[t]) + shared(x[t]) * sigmoid(g.x[t]).
  * logits_in, when not NULL, replaces the router matvec ([ntok][n_expert], the "drawn logits" of the ragged-batch

@@ -242,3 +242,44 @@ def test_ep_pieces_single_rank_match_fused_forward(full_layer):
     finally:
         m.close()
     assert np.max(np.abs(got - want)) <= 2e-6 * np.max(np.abs(want))
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_ep_gather_form_shards_sum_to_fused_forward(full_layer, world):
+    """The all-gather form of expert parallelism, its ranks emulated one after the other on one GPU: `world` shards with
+    interleaved experts (expert e on shard e % world) each compute the partial sums of their own experts over every
+    token; the partial sums plus the shared expert equal the fused single-GPU forward."""
+    import torch
+    rng = np.random.default_rng(31 + world)
+    T = 40
+    x = rng.normal(0, 1, size=(T, 2048)).astype(np.float32)
+    logits = synth.zipf_routing_logits(91, T)
+    full = rc.MoeLayer(full_layer, max_tokens=T)
+    try:
+        want, ids, w, _ = full.forward(x, logits_in=logits, want_routing=True)
+    finally:
+        full.close()
+    dev = torch.device("cuda", 0)
+    d = full_layer.dims
+    width = d.hidden + 2 * d.top_k
+    packed = torch.zeros(T, width, device=dev)
+    packed[:, :d.hidden] = torch.from_numpy(x).to(dev)
+    packed[:, d.hidden:d.hidden + d.top_k] = torch.from_numpy(ids.view(np.float32)).to(dev)
+    packed[:, d.hidden + d.top_k:] = torch.from_numpy(w).to(dev)
+    total = torch.zeros(T, d.hidden, device=dev)
+    part = torch.empty(T, d.hidden, device=dev)
+    shared = torch.empty(T, d.hidden, device=dev)
+    for r in range(world):
+        m = rc.MoeLayer(full_layer, max_tokens=T, expert_begin=r, expert_stride=world)
+        try:
+            base = packed.data_ptr()
+            m.partial_device(T, base, width, base + 4 * d.hidden, base + 4 * (d.hidden + d.top_k), width, part.data_ptr(), 0)
+            if r == 0:
+                xd = packed[:, :d.hidden].contiguous()
+                m.shared_device(T, xd.data_ptr(), shared.data_ptr(), 0)
+            torch.cuda.synchronize()
+            total += part
+        finally:
+            m.close()
+    got = (total + shared).cpu().numpy()
+    assert np.max(np.abs(got - want)) <= 4e-6 * np.max(np.abs(want))
