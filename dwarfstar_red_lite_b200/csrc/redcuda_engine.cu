@@ -598,8 +598,9 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
     ENG_CUDA(cudaGetDevice(&e->device));
     ENG_CUDA(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
     // Prefill chunk: the reference defaults to 2048 tokens per batched dispatch (native/redlite_native_engine.h:37); here the
-    // chunk also sizes every layer's expert workspace, so the default is 128 and the ceiling 512. 1 = token by token.
-    e->pb = e->cfg.prefill_batch ? std::min(e->cfg.prefill_batch, 512u) : 128u;
+    // chunk also sizes every layer's expert workspace (about 65 MB per layer at 512), so default and ceiling are 512.
+    // 1 = token by token.
+    e->pb = e->cfg.prefill_batch ? std::min(e->cfg.prefill_batch, 512u) : 512u;
     if (e->pb > in.context) e->pb = in.context;
 
     // ---- layer kinds from tensor names (native/redlite_native_layer_map.c:114-124), sizes of the dense arena

@@ -69,7 +69,7 @@ int rl_engine_step(rl_engine *engine, rl_engine_backend backend, uint32_t token,
 /* a token sequence from the current position; logits (may be NULL) are those of the last token — :120-121 */
 int rl_engine_prefill(rl_engine *engine, rl_engine_backend backend, const uint32_t *tokens, uint32_t count, float *logits,
                       rl_engine_step_stats *stats, char *error, size_t error_cap);
-/* effective prefill chunk: cfg.prefill_batch (capped at 512), or the default of 128; 1 = token by token — :146 */
+/* effective prefill chunk: cfg.prefill_batch (capped at 512), or the default of 512; 1 = token by token — :146 */
 uint32_t rl_engine_prefill_batch(const rl_engine *engine);
 /* host views of the last step's intermediates (hidden floats each; router ids: top_k entries) — :124-129 */
 const float *rl_engine_last_embedding(const rl_engine *engine, rl_engine_backend backend);
