@@ -718,8 +718,14 @@ def main():
     dom_ms = prof[dom][1] / prof[dom][0]
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
     layer_bytes = float(np.mean([a["layer"] for a in ab]))
+    # DRAM traffic per launch: ncu (dram__bytes_read + dram__bytes_write) on a 2-layer capture of the same kernels gave
+    # 114.93 MB for a gate/up launch of 105.41 MB algorithmic bytes and 57.22 MB for a down launch of 52.4 MB
+    # (profiles/k_moe_mma_ragged64.md); traffic grows with the distinct experts read, so it is scaled by the bytes.
+    ncu_ratio = {"moe_gateup": 114.93 / 105.41, "moe_down": 57.22 / 52.4}.get(dom)
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                "frac_of_nominal_8000": achieved / 8000.0, "traffic": None, "bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
+                "frac_of_nominal_8000": achieved / 8000.0, "traffic": dom_bytes * ncu_ratio if ncu_ratio else None,
+                "traffic_source": "ncu capture of a 2-layer run, scaled by algorithmic bytes" if ncu_ratio else None,
+                "bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
                 "kernel_time_shares": shares,
                 "kernel_us_per_layer": {k: round(1e3 * v[1] / (prof_steps * L), 2) for k, v in prof.items()},
                 "whole_layer": {"bytes": layer_bytes, "GBps": layer_bytes * L / (ms_per_step * 1e-3) / 1e9,
