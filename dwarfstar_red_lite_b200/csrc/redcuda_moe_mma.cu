@@ -334,6 +334,101 @@ __global__ void __launch_bounds__(256, NTILE == 1 ? MMA_MINB : 1) k_moe_mma(cons
     if (S > 1u && nunits == 0u) { __syncthreads(); __syncthreads(); }   // keep barrier counts equal for warps without work
 }
 
+// Gate/up of a batch with 16 warps per block: warps 0-7 take the gate rows of eight 16-row tiles, warps 8-15 the up rows
+// of the same tiles, each with the single-matrix MMA loop (92 registers instead of the 142 of the fused two-matrix loop),
+// so twice as many warps hide the dependent table lookups. A block-wide barrier hands the up values to the gate warps,
+// which apply SiLU(gate) * up. Same shared-memory budget as the 8-warp kernel (the staging is per 16 rows).
+template <int NTILE>
+__global__ void __launch_bounds__(512, 1) k_moe_gateup16(const __grid_constant__ MmaArgs A) {
+    pdl_prologue();
+    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr uint32_t NCOL = NTILE * 8u;
+    if (blockIdx.y >= *A.n_items) return;
+    const uint32_t u = A.item_u[blockIdx.y], p0 = A.item_p0[blockIdx.y];
+    const uint32_t e = A.uexp[u] - A.expert_begin, pe = A.ustart[u + 1u], nt = min(A.item_tok, pe - p0);
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
+    const uint32_t bpr = A.ncols >> 8;
+    uint8_t *lutg = smem, *luts = lutg + 256u * 64u, *stage0 = luts + 128u * 128u;
+    constexpr uint32_t stage_bytes = 16u * MMA_ROW_PITCH, warp_stage = MMA_STAGES * stage_bytes;
+    static_assert(16u * NCOL * 4u <= warp_stage, "the epilogue scratch of a warp must fit its staging area");
+    uint8_t *my_stage = stage0 + warp * warp_stage;
+    const uint32_t bpitch = A.ncols + 32u;
+    int8_t *Bs = reinterpret_cast<int8_t *>(stage0 + 16u * warp_stage);
+
+    for (uint32_t i = tid; i < 256u * 8u; i += 512u) reinterpret_cast<uint2 *>(lutg)[i] = A.lut_grid[i >> 3];
+    for (uint32_t i = tid; i < 128u * 8u; i += 512u) reinterpret_cast<uint4 *>(luts)[i] = A.lut_sign[i >> 3];
+
+    const uint32_t is_up = warp >> 3;
+    const uint8_t *w = (is_up ? A.w1 : A.w0) + (size_t)e * A.mat_bytes;
+    const uint32_t tile = blockIdx.x * 8u + (warp & 7u), row0 = tile << 4;
+    const bool live_tile = tile < (A.nrows >> 4);
+    const uint32_t nunits = live_tile ? bpr : 0u;
+    const uint32_t ntiles = (3u * nt + 7u) >> 3;
+
+    auto issue = [&](uint32_t c, uint32_t buf) {
+        uint8_t *dst = my_stage + buf * stage_bytes;
+#pragma unroll
+        for (uint32_t i = 0; i < 2u; ++i) {
+            const uint32_t p = lane + 32u * i, rr = p >> 2, piece = p & 3u;
+            cp_async16(dst + rr * MMA_ROW_PITCH + piece * 16u, w + ((size_t)(row0 + rr) * bpr + c) * 64u + piece * 16u);
+        }
+    };
+    for (uint32_t i = 0; i + 1u < MMA_STAGES; ++i) {
+        if (i < nunits) issue(i, i);
+        cp_async_commit();
+    }
+    {
+        const uint32_t v16 = A.ncols >> 4;
+        for (uint32_t i = tid; i < ntiles * 8u * v16; i += 512u) {
+            const uint32_t col = i / v16, k = (i - col * v16) << 4, tk = col / 3u, dg = col - tk * 3u;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (tk < nt) v = *reinterpret_cast<const uint4 *>(A.xq + ((size_t)(A.sorted[p0 + tk] / A.x_div) * 3u + dg) * A.ncols + k);
+            *reinterpret_cast<uint4 *>(Bs + (size_t)col * bpitch + k) = v;
+        }
+    }
+    __syncthreads();
+
+    float out[1][NTILE][4];
+#pragma unroll
+    for (int n = 0; n < NTILE; ++n) { out[0][n][0] = out[0][n][1] = out[0][n][2] = out[0][n][3] = 0.f; }
+    for (uint32_t c = 0; c < nunits; ++c) {
+        if (c + MMA_STAGES - 1u < nunits) issue(c + MMA_STAGES - 1u, (c + MMA_STAGES - 1u) % MMA_STAGES);
+        cp_async_commit();
+        float dsc[1][2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const size_t bi = (size_t)(row0 + h * 8u + g) * bpr + c;
+            dsc[0][h] = 0.125f * __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short *>(w + A.nb * 64u) + bi)));
+        }
+        cp_async_wait<MMA_STAGES - 1>();
+        __syncwarp();
+        mma_unit<1, NTILE>(my_stage + (c % MMA_STAGES) * stage_bytes, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+    __syncwarp();
+    float *my_scratch = reinterpret_cast<float *>(my_stage);          // nothing is in flight into the staging any more
+#pragma unroll
+    for (int n = 0; n < NTILE; ++n) {
+        float *sp = my_scratch + n * 8u + 2u * t;
+        const bool live = (uint32_t)n < ntiles;
+        sp[(size_t)g * NCOL] = live ? out[0][n][0] : 0.f; sp[(size_t)g * NCOL + 1u] = live ? out[0][n][1] : 0.f;
+        sp[(size_t)(g + 8u) * NCOL] = live ? out[0][n][2] : 0.f; sp[(size_t)(g + 8u) * NCOL + 1u] = live ? out[0][n][3] : 0.f;
+    }
+    __syncthreads();
+    if (!is_up && live_tile) {
+        const float *gs = my_scratch, *us = reinterpret_cast<const float *>(my_stage + 8u * warp_stage);
+        for (uint32_t idx = lane; idx < 16u * nt; idx += 32u) {
+            const uint32_t row = idx & 15u, tk = idx >> 4;
+            const uint32_t p = A.sorted[p0 + tk];
+            const float sxv = A.sx[p / A.x_div];
+            const float *a = gs + (size_t)row * NCOL + 3u * tk, *b = us + (size_t)row * NCOL + 3u * tk;
+            const float gte = sxv * (16384.f * a[2] + 128.f * a[1] + a[0]), upv = sxv * (16384.f * b[2] + 128.f * b[1] + b[0]);
+            A.out[(size_t)p * A.out_stride + row0 + row] = (gte / (1.0f + expf(-gte))) * upv;
+        }
+    }
+}
+
 size_t mma_smem_bytes(uint32_t nmat, uint32_t ntile, uint32_t ncols) {
     const size_t stages = 8u * MMA_STAGES * nmat * 16u * MMA_ROW_PITCH;
     return 256u * 64u + 128u * 128u + stages + (nmat == 2u ? 0u : 8u * 16u * ntile * 8u * 4u) + (size_t)ntile * 8u * (ncols + 32u);
@@ -372,7 +467,17 @@ int launch_moe_mma(MmaArgs &A, uint32_t groups, bool few_tokens, cudaStream_t s)
         static const bool split = getenv("RC_MMA_SPLIT") && atoi(getenv("RC_MMA_SPLIT")) != 0;   // A/B switch; measured: one launch for all items is faster (no serialised tails)
         if (split) {      // large items first: they are the long blocks
             if (nmat == 2u) { RC_MMA_LAUNCH(2, 3, 2u); RC_MMA_LAUNCH(2, 1, 1u); } else { RC_MMA_LAUNCH(1, 3, 2u); RC_MMA_LAUNCH(1, 1, 1u); }
-        } else { if (nmat == 2u) RC_MMA_LAUNCH(2, 3, 0u); else RC_MMA_LAUNCH(1, 3, 0u); }
+        } else if (nmat == 2u) {
+            static const bool gu16 = !(getenv("RC_MMA_GU16") && atoi(getenv("RC_MMA_GU16")) == 0);   // A/B switch
+            if (gu16 && tpw == 1u && S == 1u) {
+                const size_t smem = 256u * 64u + 128u * 128u + 16u * MMA_STAGES * 16u * MMA_ROW_PITCH + (size_t)24u * (A.ncols + 32u);
+                RC_REQUIRE(smem <= 227u * 1024u, "moe mma: %zu bytes of shared memory needed for %u columns", smem, A.ncols);
+                A.item_class = 0u;
+                RC_CUDA(cudaFuncSetAttribute(k_moe_gateup16<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                RC_LAUNCH((k_moe_gateup16<3>), dim3((ntile_rows + 7u) / 8u, groups), 512, smem, s, A);
+                g_launches.fetch_add(1, std::memory_order_relaxed);
+            } else RC_MMA_LAUNCH(2, 3, 0u);
+        } else RC_MMA_LAUNCH(1, 3, 0u);
     }
 #undef RC_MMA_LAUNCH
     g_launches.fetch_sub(1, std::memory_order_relaxed);     // RC_LAUNCHED below counts one of them
