@@ -144,9 +144,11 @@ __device__ __forceinline__ void mma_s8_k32(int (&d)[4], uint32_t a0, uint32_t a1
 // Integer accumulation over the 8 groups of the block, then one fp32 scaling by d/8 into out[m][tile][4].
 // Bs: activation digits of the work item in shared memory, column-major with pitch bpitch (== 32 mod 128: the 8-byte
 // fragment reads of the 8 columns of a tile fall into 8 different bank groups).
-template <int NMAT, int NTILE>
+// NUSED > 0: the number of column tiles in use is a compile-time constant (no per-tile tests in the loop).
+template <int NMAT, int NTILE, int NUSED = 0>
 __device__ __forceinline__ void mma_unit(const uint8_t *stage, const float (&dsc)[NMAT][2], const int8_t *Bs, uint32_t bpitch, uint32_t kbase,
                                          const uint8_t *lutg, const uint8_t *luts, uint32_t lane, uint32_t ntiles, float (&out)[NMAT][NTILE][4]) {
+    if (NUSED > 0) ntiles = NUSED;
     const uint32_t g = lane >> 2, t = lane & 3u, rep8 = (lane & 7u) * 8u, rep16 = (lane & 7u) * 16u;
     const uint32_t sel = 0x4440u + t, sh7 = 7u * t;
     int blk[NMAT][NTILE][4];
@@ -174,7 +176,7 @@ __device__ __forceinline__ void mma_unit(const uint8_t *stage, const float (&dsc
         }
 #pragma unroll
         for (int n = 0; n < NTILE; ++n) {
-            if ((uint32_t)n >= ntiles) break;        // column tiles beyond the item's tokens hold zeros: skip them
+            if (NUSED > 0 ? n >= NUSED : (uint32_t)n >= ntiles) break;        // column tiles beyond the item's tokens hold zeros: skip them
             const uint2 bf = *reinterpret_cast<const uint2 *>(Bs + (uint32_t)(n * 8 + g) * bpitch + kbase + (uint32_t)kg * 32u + 8u * t);
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
@@ -189,7 +191,7 @@ __device__ __forceinline__ void mma_unit(const uint8_t *stage, const float (&dsc
     for (int m = 0; m < NMAT; ++m)
 #pragma unroll
         for (int n = 0; n < NTILE; ++n) {
-            if ((uint32_t)n >= ntiles) break;
+            if (NUSED > 0 ? n >= NUSED : (uint32_t)n >= ntiles) break;
             out[m][n][0] += dsc[m][0] * (float)blk[m][n][0]; out[m][n][1] += dsc[m][0] * (float)blk[m][n][1];
             out[m][n][2] += dsc[m][1] * (float)blk[m][n][2]; out[m][n][3] += dsc[m][1] * (float)blk[m][n][3];
         }
@@ -291,7 +293,12 @@ __global__ void __launch_bounds__(256, NTILE == 1 ? MMA_MINB : 1) k_moe_mma(cons
         }
         cp_async_wait<MMA_STAGES - 1>();
         __syncwarp();
-        mma_unit<NMAT, NTILE>(my_stage + (unit % MMA_STAGES) * stage_bytes, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        {
+            const uint8_t *st = my_stage + (unit % MMA_STAGES) * stage_bytes;
+            if (NTILE == 3 && ntiles == 1u) mma_unit<NMAT, NTILE, 1>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+            else if (NTILE == 3 && ntiles == 2u) mma_unit<NMAT, NTILE, 2>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+            else mma_unit<NMAT, NTILE, NTILE>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        }
         __syncwarp();
         if (ci + 1u == my_chunks) {
             // ---- tile finished for this warp: fragments -> scratch[m][row][col]. With NMAT == 2 the scratch is the warp's own
@@ -402,7 +409,10 @@ __global__ void __launch_bounds__(512, 1) k_moe_gateup16(const __grid_constant__
         }
         cp_async_wait<MMA_STAGES - 1>();
         __syncwarp();
-        mma_unit<1, NTILE>(my_stage + (c % MMA_STAGES) * stage_bytes, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        const uint8_t *st = my_stage + (c % MMA_STAGES) * stage_bytes;
+        if (NTILE == 3 && ntiles == 1u) mma_unit<1, NTILE, 1>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else if (NTILE == 3 && ntiles == 2u) mma_unit<1, NTILE, 2>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else mma_unit<1, NTILE, NTILE>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
         __syncwarp();
     }
     cp_async_wait<0>();
