@@ -362,10 +362,10 @@ static int moe_forward_on(redcuda_moe *m, uint32_t ntok, const float *x, const f
     // one quantisation of the token activations serves the routed gate/up and the shared gate/up
     const bool xq = moe_experts_mma(m) || moe_shared_mma(m, ntok);
     if (xq && !launch_quant_act(x, m->d.hidden, ntok, m->d.hidden, m->xq_x, m->sx_x, s)) return 0;
-    // The shared expert needs nothing from the router, so for a batch it runs on a side stream next to the routed
+    // The shared expert needs nothing from the router, so it runs on a side stream next to the routed
     // experts and joins before the combine (both edges are events, so the fork is kept when the caller captures a graph).
     // With profiling on, everything stays on one stream so that per-kernel times are not overlapped.
-    const bool fork = ntok >= 3u && !prof_active();
+    const bool fork = !prof_active();
     if (fork) {
         RC_CUDA(cudaEventRecord(m->ev_fork, s));
         RC_CUDA(cudaStreamWaitEvent(m->side, m->ev_fork, 0));

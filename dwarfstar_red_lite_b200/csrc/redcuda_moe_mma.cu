@@ -297,7 +297,7 @@ __global__ void __launch_bounds__(256, NTILE == 1 ? MMA_MINB : 1) k_moe_mma(cons
             const uint8_t *st = my_stage + (unit % MMA_STAGES) * stage_bytes;
             if (NTILE == 3 && ntiles == 1u) mma_unit<NMAT, NTILE, 1>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
             else if (NTILE == 3 && ntiles == 2u) mma_unit<NMAT, NTILE, 2>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
-            else mma_unit<NMAT, NTILE, NTILE>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+            else mma_unit<NMAT, NTILE, (NTILE == 3 ? 3 : 0)>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);   // NTILE == 1: the tested form measured faster
         }
         __syncwarp();
         if (ci + 1u == my_chunks) {
