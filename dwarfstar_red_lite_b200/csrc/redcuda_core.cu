@@ -308,7 +308,8 @@ __global__ void __launch_bounds__(256) k_route(const float *__restrict__ logits,
 // at most), every selection round is a register scan plus a 5-step shuffle argmax — no block barriers, so the k rounds
 // cost a few hundred dependent instructions instead of 2k barriers. Same arithmetic and tie rule as k_route.
 __global__ void __launch_bounds__(256) k_route_warp(const float *__restrict__ logits, uint32_t ntok, uint32_t n_expert, uint32_t top_k,
-                                                    uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ probs_out) {
+                                                    uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ probs_out,
+                                                    RouteGroup1 G) {
     pdl_prologue();
     const uint32_t lane = threadIdx.x & 31u, tok = blockIdx.x * 8u + (threadIdx.x >> 5);
     if (tok >= ntok) return;
@@ -342,22 +343,29 @@ __global__ void __launch_bounds__(256) k_route_warp(const float *__restrict__ lo
         }
 #pragma unroll
         for (int j = 0; j < 32; ++j) if (lane + 32u * j == bi) p[j] = -1.0f;
-        if (lane == 0) ids[(size_t)tok * top_k + k] = bi;
+        if (lane == 0) {
+            ids[(size_t)tok * top_k + k] = bi;
+            if (G.sorted) { G.sorted[k] = k; G.uexp[k] = bi; G.ustart[k] = k; G.item_u[k] = k; G.item_p0[k] = k; }      // single token: pair k = group k = item k
+            if (G.ids_mirror) G.ids_mirror[k] = bi;
+        }
         if (lane == (k & 31u)) { if (k < 32u) myw = bv; else myw2 = bv; }
         sel += (double)bv;
     }
     const float invs = (float)(1.0 / sel);
     if (lane < top_k) weights[(size_t)tok * top_k + lane] = myw * invs;
     if (lane + 32u < top_k) weights[(size_t)tok * top_k + lane + 32u] = myw2 * invs;
+    if (G.sorted && lane == 0) { G.ustart[top_k] = top_k; *G.n_unique = top_k; *G.n_items = top_k; }
 }
 
 int launch_route(const float *logits_dev, uint32_t ntok, uint32_t n_expert, uint32_t top_k, uint32_t *ids_dev, float *weights_dev,
-                 float *probs_dev, cudaStream_t stream) {
+                 float *probs_dev, cudaStream_t stream, const RouteGroup1 *group1) {
+    RC_REQUIRE(!group1 || (ntok == 1u && n_expert <= 1024u), "router: the fused grouping serves one token and at most 1024 experts");
+    const RouteGroup1 G = group1 ? *group1 : RouteGroup1{};
     RC_REQUIRE(top_k >= 1 && top_k <= REDCUDA_MAX_TOPK && top_k <= n_expert, "router: top_k %u out of range", top_k);
     RC_REQUIRE(n_expert <= 8192u, "router: too many experts (%u)", n_expert);
     if (!ntok) return 1;
     prof_begin("route", stream);
-    if (n_expert <= 1024u) RC_LAUNCH((k_route_warp), (ntok + 7u) / 8u, 256, 0, stream, logits_dev, ntok, n_expert, top_k, ids_dev, weights_dev, probs_dev);
+    if (n_expert <= 1024u) RC_LAUNCH((k_route_warp), (ntok + 7u) / 8u, 256, 0, stream, logits_dev, ntok, n_expert, top_k, ids_dev, weights_dev, probs_dev, G);
     else RC_LAUNCH((k_route), ntok, 256, n_expert * sizeof(float), stream, logits_dev, n_expert, top_k, ids_dev, weights_dev, probs_dev);
     prof_end(stream);
     RC_LAUNCHED();

@@ -24,6 +24,7 @@
 namespace rc {
 
 const uint32_t *moe_last_ids_device(const redcuda_moe *m);   // redcuda_moe.cu
+void moe_set_ids_mirror(redcuda_moe *m, uint32_t *dev_ptr);   // a single token's router ids are also written to dev_ptr
 
 static double now_ms() { return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
 
@@ -394,8 +395,8 @@ static int eng_step_device(rl_engine *e, bool want_logits, char *error, size_t c
         prof_end(s);
         g_launches.fetch_add(1);
         float *xo = e->layer_out_d + (size_t)l * in.hidden;
-        ENG_RC(redcuda_moe_forward_device(L.moe, 1u, e->normed, nullptr, e->resid, xo, s));
-        ENG_CUDA(cudaMemcpyAsync(e->router_ids_d + (size_t)l * RL_ENGINE_MAX_TOPK, moe_last_ids_device(L.moe), in.top_k * sizeof(uint32_t), cudaMemcpyDeviceToDevice, s));
+        ENG_RC(redcuda_moe_forward_device(L.moe, 1u, e->normed, nullptr, e->resid, xo, s));      // its router kernel also fills router_ids_d (mirror set at open)
+        if (in.n_expert > 1024u) ENG_CUDA(cudaMemcpyAsync(e->router_ids_d + (size_t)l * RL_ENGINE_MAX_TOPK, moe_last_ids_device(L.moe), in.top_k * sizeof(uint32_t), cudaMemcpyDeviceToDevice, s));
         x = xo;
     }
     prof_begin("rmsnorm", s);
@@ -719,6 +720,7 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
     e->pos_d = e->token_d + 2; e->gen_count_d = e->token_d + 3;
     e->bx[0] = (float *)(B + o_bx0); e->bx[1] = (float *)(B + o_bx1); e->xq = (int8_t *)(B + o_xq); e->sx = (float *)(B + o_sx);
     e->tok_chunk_d = (uint32_t *)(B + o_tc); e->pos_chunk_d = (uint32_t *)(B + o_pc);
+    for (uint32_t l = 0; l < in.n_layer; ++l) moe_set_ids_mirror(e->layers[l].moe, e->router_ids_d + (size_t)l * RL_ENGINE_MAX_TOPK);
     e->tc_xs = (__half *)(B + o_txs); e->tc_xinv = (float *)(B + o_txi); e->tc_err = (uint32_t *)(B + o_ter);
     e->embed_h.assign(in.hidden, 0.f); e->layer_out_h.assign((size_t)in.n_layer * in.hidden, 0.f); e->final_norm_h.assign(in.hidden, 0.f);
     e->router_ids_h.assign((size_t)in.n_layer * RL_ENGINE_MAX_TOPK, 0u);

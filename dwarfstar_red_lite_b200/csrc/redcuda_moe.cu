@@ -212,6 +212,7 @@ struct redcuda_moe {
     float *x = nullptr, *logits = nullptr, *wk = nullptr, *scalar = nullptr, *sh_act = nullptr, *sh_out = nullptr, *act = nullptr, *tmp = nullptr, *out = nullptr;
     uint32_t *ids = nullptr, *sorted = nullptr, *uexp = nullptr, *ustart = nullptr, *n_unique = nullptr, *bad = nullptr;
     uint32_t *item_u = nullptr, *item_p0 = nullptr, *n_items = nullptr;
+    uint32_t *ids_mirror = nullptr;       // optional: a single token's ids are also written here (the engine's per-layer view)
     int8_t *xq_x = nullptr, *xq_act = nullptr, *xq_sh = nullptr;      // activation digits for the tensor-core paths
     float *sx_x = nullptr, *sx_act = nullptr, *sx_sh = nullptr;
     uint32_t max_pairs = 0;
@@ -373,8 +374,13 @@ static int moe_forward_on(redcuda_moe *m, uint32_t ntok, const float *x, const f
         RC_CUDA(cudaEventRecord(m->ev_join, m->side));
         if (!moe_gemv_pre(m, ntok, x, logits_in == nullptr, false, xq, s)) return 0;
     } else if (!moe_gemv_pre(m, ntok, x, logits_in == nullptr, true, xq, s)) return 0;
-    if (!launch_route(logits_in ? logits_in : m->logits, ntok, m->d.n_expert, k, m->ids, m->wk, nullptr, s)) return 0;
-    if (!moe_group(m, m->ids, npairs, ntok == 1u, s)) return 0;
+    if (ntok == 1u && m->d.n_expert <= 1024u) {      // one token: the router kernel also writes the (trivial) grouping
+        const RouteGroup1 G{m->sorted, m->uexp, m->ustart, m->n_unique, m->item_u, m->item_p0, m->n_items, m->ids_mirror};
+        if (!launch_route(logits_in ? logits_in : m->logits, ntok, m->d.n_expert, k, m->ids, m->wk, nullptr, s, &G)) return 0;
+    } else {
+        if (!launch_route(logits_in ? logits_in : m->logits, ntok, m->d.n_expert, k, m->ids, m->wk, nullptr, s)) return 0;
+        if (!moe_group(m, m->ids, npairs, ntok == 1u, s)) return 0;
+    }
     if (!moe_launch_experts(m, true, npairs, ntok == 1u, x, m->d.hidden, k, xq, m->act, m->d.ffn, s)) return 0;
     if (!fork && !moe_shared_down(m, ntok, s)) return 0;
     if (!moe_launch_experts(m, false, npairs, ntok == 1u, m->act, m->d.ffn, 1u, false, m->tmp, m->d.hidden, s)) return 0;
@@ -382,7 +388,10 @@ static int moe_forward_on(redcuda_moe *m, uint32_t ntok, const float *x, const f
     return moe_combine(m, ntok, m->tmp, m->wk, k, true, resid, out, s);
 }
 
-namespace rc { const uint32_t *moe_last_ids_device(const redcuda_moe *m) { return m->ids; } }
+namespace rc {
+const uint32_t *moe_last_ids_device(const redcuda_moe *m) { return m->ids; }
+void moe_set_ids_mirror(redcuda_moe *m, uint32_t *dev_ptr) { m->ids_mirror = dev_ptr; }
+}
 
 extern "C" {
 
