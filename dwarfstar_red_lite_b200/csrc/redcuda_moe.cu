@@ -219,7 +219,7 @@ struct redcuda_moe {
     bool use_mma = false;      // IQ2_XXS experts (and the Q6_K shared expert of a batch) on the integer tensor-core path
     cudaStream_t stream = nullptr;
     cudaStream_t side = nullptr;                    // the shared expert runs here, beside the routed experts
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_quant = nullptr;
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -293,10 +293,10 @@ static int moe_launch_experts(redcuda_moe *m, bool gateup, uint32_t npairs, bool
         M.nrows = nrows; M.ncols = ncols; M.expert_begin = m->d.expert_begin;
         M.sorted = m->sorted; M.uexp = m->uexp; M.ustart = m->ustart; M.item_u = m->item_u; M.item_p0 = m->item_p0; M.n_items = m->n_items;
         M.xq = xq; M.sx = sx; M.x_div = x_div; M.out = out; M.out_stride = out_stride;
-        const uint32_t tok = mma_item_tokens(single_token);
+        const uint32_t tok = mma_item_tokens(single_token, npairs, m->d.expert_count);
         const uint32_t live = npairs < m->d.expert_count ? npairs : m->d.expert_count;
         const uint32_t max_items = single_token ? npairs : (npairs / tok + live < npairs ? npairs / tok + live : npairs);
-        return launch_moe_mma(M, max_items, single_token, s);
+        return launch_moe_mma(M, max_items, tok, s);
     }
     MoeArgs A{};
     A.w0 = gateup ? m->gate : m->down; A.w1 = gateup ? m->up : nullptr;
@@ -338,7 +338,7 @@ static int moe_group(redcuda_moe *m, const uint32_t *pair_expert, uint32_t npair
     if (distinct && npairs <= 64u && !skip_foreign) {
         RC_LAUNCH((k_group_trivial), 1, 64, 0, s, pair_expert, npairs, m->sorted, m->uexp, m->ustart, m->n_unique, m->item_u, m->item_p0, m->n_items);
     } else {
-        RC_LAUNCH((k_group_pairs), 1, 1024, 0, s, pair_expert, npairs, m->d.expert_begin, m->d.expert_stride, skip_foreign ? 1u : 0u, m->d.expert_count, mma_item_tokens(false), m->sorted, m->uexp, m->ustart,
+        RC_LAUNCH((k_group_pairs), 1, 1024, 0, s, pair_expert, npairs, m->d.expert_begin, m->d.expert_stride, skip_foreign ? 1u : 0u, m->d.expert_count, mma_item_tokens(false, npairs, m->d.expert_count), m->sorted, m->uexp, m->ustart,
                                          m->n_unique, m->item_u, m->item_p0, m->n_items, m->bad);
     }
     prof_end(s);
@@ -362,14 +362,22 @@ static int moe_forward_on(redcuda_moe *m, uint32_t ntok, const float *x, const f
     const uint32_t k = m->d.top_k, npairs = ntok * k;
     // one quantisation of the token activations serves the routed gate/up and the shared gate/up
     const bool xq = moe_experts_mma(m) || moe_shared_mma(m, ntok);
-    if (xq && !launch_quant_act(x, m->d.hidden, ntok, m->d.hidden, m->xq_x, m->sx_x, s)) return 0;
     // The shared expert needs nothing from the router, so it runs on a side stream next to the routed
     // experts and joins before the combine (both edges are events, so the fork is kept when the caller captures a graph).
     // With profiling on, everything stays on one stream so that per-kernel times are not overlapped.
     const bool fork = !prof_active();
+    // When only the routed gate/up reads the digits (the shared expert takes the GEMV for one or two tokens), the
+    // quantisation leaves the critical path too: it opens the side stream and the main stream waits for it only
+    // before the gate/up launch, behind the router GEMV and the selection.
+    const bool quant_aside = fork && xq && !moe_shared_mma(m, ntok);
+    if (xq && !quant_aside && !launch_quant_act(x, m->d.hidden, ntok, m->d.hidden, m->xq_x, m->sx_x, s)) return 0;
     if (fork) {
         RC_CUDA(cudaEventRecord(m->ev_fork, s));
         RC_CUDA(cudaStreamWaitEvent(m->side, m->ev_fork, 0));
+        if (quant_aside) {
+            if (!launch_quant_act(x, m->d.hidden, ntok, m->d.hidden, m->xq_x, m->sx_x, m->side)) return 0;
+            RC_CUDA(cudaEventRecord(m->ev_quant, m->side));
+        }
         if (!moe_gemv_pre(m, ntok, x, false, true, xq, m->side) || !moe_shared_down(m, ntok, m->side)) return 0;
         RC_CUDA(cudaEventRecord(m->ev_join, m->side));
         if (!moe_gemv_pre(m, ntok, x, logits_in == nullptr, false, xq, s)) return 0;
@@ -381,6 +389,7 @@ static int moe_forward_on(redcuda_moe *m, uint32_t ntok, const float *x, const f
         if (!launch_route(logits_in ? logits_in : m->logits, ntok, m->d.n_expert, k, m->ids, m->wk, nullptr, s)) return 0;
         if (!moe_group(m, m->ids, npairs, ntok == 1u, s)) return 0;
     }
+    if (quant_aside) RC_CUDA(cudaStreamWaitEvent(s, m->ev_quant, 0));
     if (!moe_launch_experts(m, true, npairs, ntok == 1u, x, m->d.hidden, k, xq, m->act, m->d.ffn, s)) return 0;
     if (!fork && !moe_shared_down(m, ntok, s)) return 0;
     if (!moe_launch_experts(m, false, npairs, ntok == 1u, m->act, m->d.ffn, 1u, false, m->tmp, m->d.hidden, s)) return 0;
@@ -416,7 +425,8 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
     cudaGetDevice(&m->device);
     auto bail = [&]() -> redcuda_moe * { redcuda_moe_destroy(m); return nullptr; };
     if (cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess || cudaStreamCreateWithFlags(&m->side, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming) != cudaSuccess || cudaEventCreateWithFlags(&m->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+        cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming) != cudaSuccess || cudaEventCreateWithFlags(&m->ev_join, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&m->ev_quant, cudaEventDisableTiming) != cudaSuccess) {
         set_error("moe create: stream / event creation failed"); return bail();
     }
 
@@ -502,6 +512,7 @@ void redcuda_moe_destroy(redcuda_moe *m) {
     if (m->side) { cudaStreamSynchronize(m->side); cudaStreamDestroy(m->side); }
     if (m->ev_fork) cudaEventDestroy(m->ev_fork);
     if (m->ev_join) cudaEventDestroy(m->ev_join);
+    if (m->ev_quant) cudaEventDestroy(m->ev_quant);
     delete m;
 }
 

@@ -206,7 +206,7 @@ __device__ __forceinline__ void mma_unit(const uint8_t *stage, const float (&dsc
 // grid = (row-tile groups, work items); one work item = up to TOK pairs of one expert (k_group_pairs cuts every
 // expert's pairs into such items, so that all blocks carry the same amount of work whatever the routing skew).
 template <int NMAT, int NTILE>
-__global__ void __launch_bounds__(256, NTILE == 1 ? MMA_MINB : 1) k_moe_mma(const __grid_constant__ MmaArgs A) {
+__global__ void __launch_bounds__(256, NTILE == 1 ? MMA_MINB : (NMAT == 1 && NTILE == 6 ? 2 : 1)) k_moe_mma(const __grid_constant__ MmaArgs A) {
     pdl_prologue();
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr uint32_t NCOL = NTILE * 8u;
@@ -295,9 +295,12 @@ __global__ void __launch_bounds__(256, NTILE == 1 ? MMA_MINB : 1) k_moe_mma(cons
         __syncwarp();
         {
             const uint8_t *st = my_stage + (unit % MMA_STAGES) * stage_bytes;
-            if (NTILE == 3 && ntiles == 1u) mma_unit<NMAT, NTILE, 1>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
-            else if (NTILE == 3 && ntiles == 2u) mma_unit<NMAT, NTILE, 2>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
-            else mma_unit<NMAT, NTILE, (NTILE == 3 ? 3 : 0)>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);   // NTILE == 1: the tested form measured faster
+            if (NTILE >= 3 && ntiles == 1u) mma_unit<NMAT, NTILE, 1>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+            else if (NTILE >= 3 && ntiles == 2u) mma_unit<NMAT, NTILE, 2>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+            else if (NTILE >= 3 && ntiles == 3u) mma_unit<NMAT, NTILE, (NTILE >= 3 ? 3 : 0)>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+            else if (NTILE == 6 && ntiles == 4u) mma_unit<NMAT, NTILE, (NTILE == 6 ? 4 : 0)>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+            else if (NTILE == 6 && ntiles == 5u) mma_unit<NMAT, NTILE, (NTILE == 6 ? 5 : 0)>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+            else mma_unit<NMAT, NTILE, (NTILE >= 3 ? NTILE : 0)>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);   // NTILE == 1: the tested form measured faster
         }
         __syncwarp();
         if (ci + 1u == my_chunks) {
@@ -410,8 +413,11 @@ __global__ void __launch_bounds__(512, 1) k_moe_gateup16(const __grid_constant__
         cp_async_wait<MMA_STAGES - 1>();
         __syncwarp();
         const uint8_t *st = my_stage + (c % MMA_STAGES) * stage_bytes;
-        if (NTILE == 3 && ntiles == 1u) mma_unit<1, NTILE, 1>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
-        else if (NTILE == 3 && ntiles == 2u) mma_unit<1, NTILE, 2>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        if (NTILE >= 3 && ntiles == 1u) mma_unit<1, NTILE, 1>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else if (NTILE >= 3 && ntiles == 2u) mma_unit<1, NTILE, 2>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else if (NTILE >= 3 && ntiles == 3u) mma_unit<1, NTILE, 3>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else if (NTILE == 6 && ntiles == 4u) mma_unit<1, NTILE, (NTILE == 6 ? 4 : NTILE)>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else if (NTILE == 6 && ntiles == 5u) mma_unit<1, NTILE, (NTILE == 6 ? 5 : NTILE)>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
         else mma_unit<1, NTILE, NTILE>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
         __syncwarp();
     }
@@ -444,7 +450,14 @@ size_t mma_smem_bytes(uint32_t nmat, uint32_t ntile, uint32_t ncols) {
     return 256u * 64u + 128u * 128u + stages + (nmat == 2u ? 0u : 8u * 16u * ntile * 8u * 4u) + (size_t)ntile * 8u * (ncols + 32u);
 }
 
-int launch_moe_mma(MmaArgs &A, uint32_t groups, bool few_tokens, cudaStream_t s) {
+uint32_t mma_item_tokens(bool few_tokens, uint32_t npairs, uint32_t n_experts) {
+    static const bool allow16 = !(getenv("RC_MMA_ITEM16") && atoi(getenv("RC_MMA_ITEM16")) == 0);   // A/B switch
+    return few_tokens ? 2u : (allow16 && npairs >= 6u * n_experts ? 16u : 8u);
+}
+
+int launch_moe_mma(MmaArgs &A, uint32_t groups, uint32_t item_tok, cudaStream_t s) {
+    const bool few_tokens = item_tok <= 2u, big_items = item_tok > 8u;
+    RC_REQUIRE(item_tok == 2u || item_tok == 8u || item_tok == 16u, "moe mma: work items of %u pairs are not built", item_tok);
     int dev = 0;
     RC_CUDA(cudaGetDevice(&dev));
     A.lut_grid = g_lut_grid_ptr[dev & 63];
@@ -463,7 +476,7 @@ int launch_moe_mma(MmaArgs &A, uint32_t groups, bool few_tokens, cudaStream_t s)
     }
     const uint32_t R = 8u / S;
     A.S = S; A.tiles_per_warp = tpw;
-    A.item_tok = mma_item_tokens(few_tokens);
+    A.item_tok = item_tok;
     const dim3 grid((ntile_rows + R * tpw - 1u) / (R * tpw), groups);
     prof_begin(nmat == 2u ? "moe_gateup" : "moe_down", s);
 #define RC_MMA_LAUNCH(NM, NT, CLS) do { \
@@ -475,19 +488,26 @@ int launch_moe_mma(MmaArgs &A, uint32_t groups, bool few_tokens, cudaStream_t s)
     if (few_tokens) { if (nmat == 2u) RC_MMA_LAUNCH(2, 1, 0u); else RC_MMA_LAUNCH(1, 1, 0u); }
     else {
         static const bool split = getenv("RC_MMA_SPLIT") && atoi(getenv("RC_MMA_SPLIT")) != 0;   // A/B switch; measured: one launch for all items is faster (no serialised tails)
-        if (split) {      // large items first: they are the long blocks
+        if (split && !big_items) {      // large items first: they are the long blocks
             if (nmat == 2u) { RC_MMA_LAUNCH(2, 3, 2u); RC_MMA_LAUNCH(2, 1, 1u); } else { RC_MMA_LAUNCH(1, 3, 2u); RC_MMA_LAUNCH(1, 1, 1u); }
         } else if (nmat == 2u) {
             static const bool gu16 = !(getenv("RC_MMA_GU16") && atoi(getenv("RC_MMA_GU16")) == 0);   // A/B switch
+            RC_REQUIRE(!big_items || (gu16 && tpw == 1u && S == 1u), "moe mma: work items of 16 pairs need the 16-warp gate/up kernel");
             if (gu16 && tpw == 1u && S == 1u) {
-                const size_t smem = 256u * 64u + 128u * 128u + 16u * MMA_STAGES * 16u * MMA_ROW_PITCH + (size_t)24u * (A.ncols + 32u);
+                const size_t smem = 256u * 64u + 128u * 128u + 16u * MMA_STAGES * 16u * MMA_ROW_PITCH + (size_t)(big_items ? 48u : 24u) * (A.ncols + 32u);
                 RC_REQUIRE(smem <= 227u * 1024u, "moe mma: %zu bytes of shared memory needed for %u columns", smem, A.ncols);
                 A.item_class = 0u;
-                RC_CUDA(cudaFuncSetAttribute(k_moe_gateup16<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                RC_LAUNCH((k_moe_gateup16<3>), dim3((ntile_rows + 7u) / 8u, groups), 512, smem, s, A);
+                if (big_items) {
+                    RC_CUDA(cudaFuncSetAttribute(k_moe_gateup16<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                    RC_LAUNCH((k_moe_gateup16<6>), dim3((ntile_rows + 7u) / 8u, groups), 512, smem, s, A);
+                } else {
+                    RC_CUDA(cudaFuncSetAttribute(k_moe_gateup16<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                    RC_LAUNCH((k_moe_gateup16<3>), dim3((ntile_rows + 7u) / 8u, groups), 512, smem, s, A);
+                }
                 g_launches.fetch_add(1, std::memory_order_relaxed);
             } else RC_MMA_LAUNCH(2, 3, 0u);
-        } else RC_MMA_LAUNCH(1, 3, 0u);
+        } else if (big_items) RC_MMA_LAUNCH(1, 6, 0u);
+        else RC_MMA_LAUNCH(1, 3, 0u);
     }
 #undef RC_MMA_LAUNCH
     g_launches.fetch_sub(1, std::memory_order_relaxed);     // RC_LAUNCHED below counts one of them

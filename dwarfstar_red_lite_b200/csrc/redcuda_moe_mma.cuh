@@ -24,10 +24,12 @@ struct MmaArgs {
 int mma_set_luts(const uint8_t *iq2_grid_host);
 // x[rows][x_stride] (first ncols of each row) -> digits xq[rows][3][ncols] and scales sx[rows]
 int launch_quant_act(const float *x, uint32_t x_stride, uint32_t rows, uint32_t ncols, int8_t *xq, float *sx, cudaStream_t s);
-// Pairs one work item of the tensor-core expert kernel covers: 2 in the few-token configuration, else 8.
-static inline uint32_t mma_item_tokens(bool few_tokens) { return few_tokens ? 2u : 8u; }
-// max_items = upper bound of work items (grid.y); few_tokens: items were cut with mma_item_tokens(true)
-int launch_moe_mma(MmaArgs &A, uint32_t max_items, bool few_tokens, cudaStream_t s);
+// Pairs one work item of the tensor-core expert kernel covers: 2 in the few-token configuration, 8 for a decode batch,
+// 16 when the experts see many pairs each (prefill chunks, expert-parallel shards): an expert's weights are decoded
+// once per item, so larger items halve that work where most experts would otherwise need two.
+uint32_t mma_item_tokens(bool few_tokens, uint32_t npairs = 0u, uint32_t n_experts = 1u);
+// max_items = upper bound of work items (grid.y); item_tok: the size the items were cut with (2, 8 or 16)
+int launch_moe_mma(MmaArgs &A, uint32_t max_items, uint32_t item_tok, cudaStream_t s);
 // Q6_K matrix (or gate/up pair with SiLU*mul when w1 != nullptr) x ntok activation rows given as digits (redcuda_q6k_mma.cu)
 int launch_q6k_mma(const uint8_t *w0, const uint8_t *w1, uint64_t nb, uint32_t nrows, uint32_t ncols, uint32_t ntok,
                    const int8_t *xq, const float *sx, float *out, uint32_t out_stride, const char *tag, cudaStream_t s);
