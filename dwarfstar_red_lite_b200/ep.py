@@ -159,6 +159,7 @@ class EpGatherMoeLayer:
         self.w = torch.empty(tokens, d.top_k, dtype=torch.float32, device=dev)
         self.shared = torch.empty(tokens, d.hidden, dtype=torch.float32, device=dev)
         self.partial = torch.empty(world * tokens, d.hidden, dtype=torch.float32, device=dev)
+        self.side = torch.cuda.Stream(device=dev)
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor | None = None) -> torch.Tensor:
         d, T = self.dims, self.T
@@ -175,7 +176,13 @@ class EpGatherMoeLayer:
             return self.partial[:n]
 
         def shared_fn(pk):
-            self.m.shared_device(T, x.data_ptr(), self.shared.data_ptr(), st)
-            return self.shared
+            # the shared expert needs neither the router nor the exchange: it runs on a side stream next to the
+            # collectives and the routed experts and is joined before the final add
+            self.side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.side):
+                self.m.shared_device(T, x.data_ptr(), self.shared.data_ptr(), self.side.cuda_stream)
+            return None
 
-        return gather_moe_forward(self.packed, d.hidden, d.top_k, self.world, partial_fn, shared_fn, self.group)
+        routed = gather_moe_forward(self.packed, d.hidden, d.top_k, self.world, partial_fn, shared_fn, self.group)
+        torch.cuda.current_stream().wait_stream(self.side)
+        return routed.add_(self.shared)

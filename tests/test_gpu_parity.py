@@ -283,3 +283,25 @@ def test_ep_gather_form_shards_sum_to_fused_forward(full_layer, world):
             m.close()
     got = (total + shared).cpu().numpy()
     assert np.max(np.abs(got - want)) <= 4e-6 * np.max(np.abs(want))
+
+
+def test_ep_gather_layer_single_rank_matches_fused_forward(full_layer):
+    """EpGatherMoeLayer.forward with one rank (no collectives): routing, packing, partial sums, the shared expert on its
+    side stream and the final add must reproduce the fused forward."""
+    import torch
+    from dwarfstar_red_lite_b200 import ep
+    rng = np.random.default_rng(17)
+    T = 24
+    x = rng.normal(0, 1, size=(T, 2048)).astype(np.float32)
+    logits = synth.zipf_routing_logits(83, T)
+    m = rc.MoeLayer(full_layer, max_tokens=T)
+    try:
+        want = m.forward(x, logits_in=logits)
+        dev = torch.device("cuda", 0)
+        layer = ep.EpGatherMoeLayer(m, 0, 1, T)
+        for _ in range(2):       # twice: buffers and the side stream are reused
+            got = layer.forward(torch.from_numpy(x).to(dev), logits=torch.from_numpy(logits).to(dev))
+            torch.cuda.synchronize()
+            assert np.max(np.abs(got.cpu().numpy() - want)) <= 4e-6 * np.max(np.abs(want))
+    finally:
+        m.close()
