@@ -719,9 +719,10 @@ def main():
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
     layer_bytes = float(np.mean([a["layer"] for a in ab]))
     # DRAM traffic per launch: ncu (dram__bytes_read + dram__bytes_write) on a 2-layer capture of the same kernels gave
-    # 114.93 MB for a gate/up launch of 105.41 MB algorithmic bytes and 57.22 MB for a down launch of 52.4 MB
-    # (profiles/k_moe_mma_ragged64.md); traffic grows with the distinct experts read, so it is scaled by the bytes.
-    ncu_ratio = {"moe_gateup": 114.93 / 105.41, "moe_down": 57.22 / 52.4}.get(dom)
+    # 114.93 MB for a gate/up launch of 105.41 MB algorithmic bytes and 51.39 MB for a down launch of 52.4 MB (part of
+    # its input still sits in L2) (profiles/k_moe_mma_ragged64.md); traffic grows with the distinct experts read, so
+    # it is scaled by the algorithmic bytes.
+    ncu_ratio = {"moe_gateup": 114.93 / 105.41, "moe_down": 51.39 / 52.4}.get(dom)
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                 "frac_of_nominal_8000": achieved / 8000.0, "traffic": dom_bytes * ncu_ratio if ncu_ratio else None,
                 "traffic_source": "ncu capture of a 2-layer run, scaled by algorithmic bytes" if ncu_ratio else None,
