@@ -398,13 +398,15 @@ __global__ void __launch_bounds__(256) k_vec_sigmoid(const float *__restrict__ w
 // (rl_quant_row_dot on an F32 row accumulates in double, native/redlite_native_quant_cpu.c:198-212, and the top-k that
 // follows must not depend on a summation order). The multi-token GEMV re-reads the matrix for every four tokens; this
 // is a small tiled fp64 GEMM instead: block = 16 tokens x 32 experts, K in tiles of 64 staged as doubles in shared
-// memory (the next tile is fetched into registers while the current one is multiplied), thread = 1 token x 2 experts.
-constexpr uint32_t RL_TT = 16u, RL_TE = 32u, RL_KT = 64u, RL_PITCH = RL_KT + 1u;
+// memory (the next tile is fetched into registers while the current one is multiplied); each of the 8 warps owns one
+// 8 x 8 tile of the result and advances it with the fp64 tensor-core instruction (mma.sync.m8n8k4.f64: one 8-byte
+// shared load per operand and lane per 256 multiply-adds; the row pitch of 68 doubles keeps those loads conflict-free).
+constexpr uint32_t RL_TT = 16u, RL_TE = 32u, RL_KT = 64u, RL_PITCH = RL_KT + 4u;
 __global__ void __launch_bounds__(256) k_router_logits(const float *__restrict__ w, const float *__restrict__ x, uint32_t x_stride, uint32_t ntok,
                                                        uint32_t n_expert, uint32_t ncols, float *__restrict__ logits) {
     pdl_prologue();
     __shared__ double xs[RL_TT * RL_PITCH], ws[RL_TE * RL_PITCH];
-    const uint32_t tid = threadIdx.x, ty = tid >> 4, tx = tid & 15u;
+    const uint32_t tid = threadIdx.x;
     const uint32_t t0 = blockIdx.x * RL_TT, e0 = blockIdx.y * RL_TE;
     // staging roles: the weight tile is 32 rows x 64 floats = 512 float4 (two per thread), the token tile 16 x 64 = 256 float4
     const uint32_t wr = tid >> 4, wc = (tid & 15u) * 4u;               // rows wr and wr + 16
@@ -415,6 +417,9 @@ __global__ void __launch_bounds__(256) k_router_logits(const float *__restrict__
     const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 rw0 = w_ok0 ? __ldg(reinterpret_cast<const float4 *>(wp0)) : zero, rw1 = w_ok1 ? __ldg(reinterpret_cast<const float4 *>(wp1)) : zero;
     float4 rx = x_ok ? *reinterpret_cast<const float4 *>(xp) : zero;
+    // warp -> (token half, expert quarter); lane -> A element (row lane/4, k lane%4), B element (k lane%4, column lane/4),
+    // C elements (row lane/4, columns 2*(lane%4), +1)
+    const uint32_t warp = tid >> 5, lane = tid & 31u, th = warp >> 2, eq = warp & 3u, fr = lane >> 2, fk = lane & 3u;
     double acc0 = 0.0, acc1 = 0.0;
     for (uint32_t k0 = 0; k0 < ncols; k0 += RL_KT) {
         __syncthreads();                                   // the previous tile is no longer read
@@ -428,13 +433,15 @@ __global__ void __launch_bounds__(256) k_router_logits(const float *__restrict__
             rw1 = w_ok1 ? __ldg(reinterpret_cast<const float4 *>(wp1 + k0 + RL_KT)) : zero;
             rx = x_ok ? *reinterpret_cast<const float4 *>(xp + k0 + RL_KT) : zero;
         }
-        const double *a = xs + ty * RL_PITCH, *b0 = ws + tx * RL_PITCH, *b1 = ws + (tx + 16u) * RL_PITCH;
-#pragma unroll 16
-        for (uint32_t kk = 0; kk < RL_KT; ++kk) { const double av = a[kk]; acc0 = fma(av, b0[kk], acc0); acc1 = fma(av, b1[kk], acc1); }
+        const double *a = xs + (th * 8u + fr) * RL_PITCH + fk, *b = ws + (eq * 8u + fr) * RL_PITCH + fk;
+#pragma unroll
+        for (uint32_t kk = 0; kk < RL_KT; kk += 4u)
+            asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};" : "+d"(acc0), "+d"(acc1) : "d"(a[kk]), "d"(b[kk]));
     }
-    if (t0 + ty < ntok) {
-        if (e0 + tx < n_expert) logits[(size_t)(t0 + ty) * n_expert + e0 + tx] = (float)acc0;
-        if (e0 + tx + 16u < n_expert) logits[(size_t)(t0 + ty) * n_expert + e0 + tx + 16u] = (float)acc1;
+    const uint32_t t = t0 + th * 8u + fr, e = e0 + eq * 8u + 2u * fk;
+    if (t < ntok) {
+        if (e < n_expert) logits[(size_t)t * n_expert + e] = (float)acc0;
+        if (e + 1u < n_expert) logits[(size_t)t * n_expert + e + 1u] = (float)acc1;
     }
 }
 
