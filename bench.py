@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the MoE-layer decode hot path on B200 (see DESIGN.md for the workload definition).
+"""Benchmark of the MoE-layer decode hot path on B200.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--layers L] [--tokens T]
 
@@ -7,6 +7,10 @@ Workload (N = 1): ragged batched MoE decode — T = 64 concurrent sequences, one
 MoE layers (512 IQ2_XXS experts, top-10, Q6_K shared expert) whose router logits are DRAWN so that per-expert token
 counts follow Zipf(1.1). One step = one pass of the batch through all L layers; the L layers' weights (L x 415 MB) are
 far larger than L2, so every step reads its experts from HBM. Prints ONE JSON line.
+
+Other workloads (--workload): moe_b1 (one token through the same layers, router computed), deltanet (gated DeltaNet
+decode step, batch 1 and 8), decode48 (48-layer model, greedy decode at a long context), prefill (chunked prefill of
+the same model). N > 1 (torchrun): the default workload under expert parallelism, 64 tokens per rank.
 """
 from __future__ import annotations
 
