@@ -165,50 +165,76 @@ __global__ void k_dn_conv_roll(DnDims D, uint32_t T, const float *__restrict__ q
     }
 }
 
+// Block = 8 warps = 8 consecutive state rows of ONE value head, so the eight warps need the same q / k rows and the same
+// beta / gate of every token: they are staged in shared memory TB tokens at a time by cp.async, one token block ahead
+// of the one being applied (a warp that fetched them itself waited for L2 on every token of its sequential chain).
+constexpr uint32_t DN_TB = 8u;          // tokens per staged block
 template <int VPL>
 __global__ void __launch_bounds__(256) k_dn_state_seq(DnDims D, uint32_t T, const float *__restrict__ qk, const float *__restrict__ v,
                                                       const float *__restrict__ beta, const float *__restrict__ gate,
                                                       float *__restrict__ state, float *__restrict__ core) {
     pdl_prologue();
-    const uint32_t lane = threadIdx.x & 31u;
-    const uint64_t gw = (blockIdx.x * (uint64_t)blockDim.x + threadIdx.x) >> 5;
-    const uint32_t S = D.S;
-    if (gw >= (uint64_t)D.rank * S) return;
-    const uint32_t j = (uint32_t)(gw % S), h = (uint32_t)(gw / S);
+    constexpr uint32_t S = VPL * 32u;
+    __shared__ __align__(16) float s_q[2][DN_TB][S], s_k[2][DN_TB][S];
+    __shared__ __align__(16) float s_v[2][DN_TB][8];
+    __shared__ float s_b[2][DN_TB], s_g[2][DN_TB];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t row0 = blockIdx.x * 8u;                       // first of the block's 8 rows, counted over (head, j)
+    const uint32_t h = row0 / S, j0 = row0 - h * S, j = j0 + warp;
     const uint32_t kh = h / (D.rank / D.groups);
     const size_t tok_qk = (size_t)2u * D.groups * S;
     const float *q = qk + (size_t)kh * S, *k = qk + (size_t)(D.groups + kh) * S;
     float *row = state + ((size_t)h * S + j) * S;
     const float scale = 1.0f / sqrtf((float)S);
-    float m[VPL], kc[VPL], qc[VPL];
-#pragma unroll
-    for (int t = 0; t < VPL; ++t) { m[t] = row[lane + 32 * t]; kc[t] = k[lane + 32 * t]; qc[t] = q[lane + 32 * t]; }
-    float g_c = gate[h], b_c = beta[h], v_c = v[(size_t)h * S + j];
-    for (uint32_t ti = 0; ti < T; ++ti) {
-        float kn[VPL], qn[VPL], g_n = 0.f, b_n = 0.f, v_n = 0.f;
-        if (ti + 1u < T) {
-            const size_t n1 = ti + 1u;
-#pragma unroll
-            for (int t = 0; t < VPL; ++t) { kn[t] = k[n1 * tok_qk + lane + 32 * t]; qn[t] = q[n1 * tok_qk + lane + 32 * t]; }
-            g_n = gate[n1 * D.rank + h]; b_n = beta[n1 * D.rank + h]; v_n = v[n1 * D.d_inner + (size_t)h * S + j];
-        } else {
-#pragma unroll
-            for (int t = 0; t < VPL; ++t) { kn[t] = 0.f; qn[t] = 0.f; }
+
+    auto stage = [&](uint32_t tb, uint32_t buf) {               // tokens [tb * DN_TB, ...) -> buffer buf
+        const uint32_t t0 = tb * DN_TB, n = min(DN_TB, T - t0);
+        constexpr uint32_t V4 = S / 4u;                          // float4 per q or k row
+        for (uint32_t i = tid; i < 2u * n * V4; i += 256u) {
+            const uint32_t which = i / (n * V4), r = i - which * n * V4, tt = r / V4, c = (r - tt * V4) * 4u;
+            const float *src = (which ? k : q) + (size_t)(t0 + tt) * tok_qk + c;
+            float *dst = (which ? &s_k[buf][tt][0] : &s_q[buf][tt][0]) + c;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
         }
-        const float decay = expf(g_c);
-        float sum = 0.f;
+        for (uint32_t i = tid; i < n * 2u; i += 256u) {          // v of the block's 8 rows: 32 bytes per token
+            const uint32_t tt = i >> 1, c = (i & 1u) * 4u;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"((uint32_t)__cvta_generic_to_shared(&s_v[buf][tt][c])),
+                         "l"(v + (size_t)(t0 + tt) * D.d_inner + (size_t)h * S + j0 + c) : "memory");
+        }
+        for (uint32_t i = tid; i < n * 2u; i += 256u) {
+            const uint32_t tt = i >> 1;
+            const float *src = (i & 1u ? gate : beta) + (size_t)(t0 + tt) * D.rank + h;
+            float *dst = i & 1u ? &s_g[buf][tt] : &s_b[buf][tt];
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    float m[VPL];
 #pragma unroll
-        for (int t = 0; t < VPL; ++t) { m[t] = m[t] * decay; sum += m[t] * kc[t]; }
-        for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        const float delta = (v_c - sum) * b_c;
-        float o_acc = 0.f;
+    for (int t = 0; t < VPL; ++t) m[t] = row[lane + 32 * t];
+    const uint32_t nblk = (T + DN_TB - 1u) / DN_TB;
+    stage(0u, 0u);
+    for (uint32_t tb = 0; tb < nblk; ++tb) {
+        const uint32_t buf = tb & 1u, n = min(DN_TB, T - tb * DN_TB);
+        if (tb + 1u < nblk) stage(tb + 1u, buf ^ 1u); else asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();                                         // block tb has landed for every warp
+        for (uint32_t tt = 0; tt < n; ++tt) {
+            const float decay = expf(s_g[buf][tt]);
+            float kc[VPL];
+            float sum = 0.f;
 #pragma unroll
-        for (int t = 0; t < VPL; ++t) { m[t] += kc[t] * delta; o_acc += m[t] * qc[t]; }
-        for (int o = 16; o; o >>= 1) o_acc += __shfl_xor_sync(0xffffffffu, o_acc, o);
-        if (lane == 0) core[(size_t)ti * D.d_inner + (size_t)h * S + j] = o_acc * scale;
+            for (int t = 0; t < VPL; ++t) { kc[t] = s_k[buf][tt][lane + 32 * t]; m[t] = m[t] * decay; sum += m[t] * kc[t]; }
+            for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            const float delta = (s_v[buf][tt][warp] - sum) * s_b[buf][tt];
+            float o_acc = 0.f;
 #pragma unroll
-        for (int t = 0; t < VPL; ++t) { kc[t] = kn[t]; qc[t] = qn[t]; }
-        g_c = g_n; b_c = b_n; v_c = v_n;
+            for (int t = 0; t < VPL; ++t) { m[t] += kc[t] * delta; o_acc += m[t] * s_q[buf][tt][lane + 32 * t]; }
+            for (int o = 16; o; o >>= 1) o_acc += __shfl_xor_sync(0xffffffffu, o_acc, o);
+            if (lane == 0) core[(size_t)(tb * DN_TB + tt) * D.d_inner + (size_t)h * S + j] = o_acc * scale;
+        }
+        __syncthreads();                                         // buffer buf may be refilled by the next stage() call
     }
 #pragma unroll
     for (int t = 0; t < VPL; ++t) row[lane + 32 * t] = m[t];
