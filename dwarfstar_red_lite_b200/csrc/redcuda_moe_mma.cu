@@ -19,10 +19,14 @@
 // fragment of a lane is then simply the 8 consecutive activation digits at 32*group + 8t of column g.
 //
 // Weights are streamed with cp.async (16 B per lane; a warp copies the 64-byte block segments of its 16 or 32 rows) into
-// per-warp double-buffered staging, rows padded to 80 B so that the 8-byte operand reads are conflict free. Activation
-// digits are read straight from global memory (a few KB per work item, L1-resident).
-// Both lookup tables are replicated in shared memory with an entry stride of 128 B (magnitudes: 8 copies of 8 B, replica =
-// lane%8, at worst a two-way conflict between the halves of a 16-lane phase; signs: 8 copies of 16 B holding the byte mask and its +1 carry term, replica = lane%8) for the same reason.
+// per-warp staging, three 256-column units in flight, rows padded to 80 B so that the 8-byte operand reads are conflict
+// free. The activation digits of a work item (<= 8 pairs, or <= 16 when experts see many pairs each) sit in shared memory,
+// column-major with a pitch that spreads the 8 columns of a tile over the banks.
+// Both lookup tables are replicated 8x in shared memory (magnitudes: 8 copies of 8 B, entry stride 64 B; signs: 8 copies
+// of 16 B holding the byte mask and its +1 carry term, entry stride 128 B; replica = lane % 8), since a lane's entry index
+// is data dependent.
+// Kernels: k_moe_mma<NMAT, NTILE> (8 warps; NMAT = 2 fuses gate and up with SiLU * mul, used for one or two tokens;
+// NMAT = 1 is the down projection) and k_moe_gateup16<NTILE> (16 warps: gate warps + up warps, used for batches).
 #define RC_PDL_DEFAULT 0
 #include "redcuda_common.cuh"
 #include "redcuda_kernels.cuh"
