@@ -141,6 +141,11 @@ __device__ __forceinline__ void mma_s8_k32(int (&d)[4], uint32_t a0, uint32_t a1
 #ifndef MMA_KG_UNROLL
 #define MMA_KG_UNROLL 2                    // 32-column groups in flight per warp
 #endif
+// copies of the magnitude table in shared memory (replica = lane % copies): 16 in the 16-warp gate/up kernel (measured
+// 9 % faster there: two lanes per replica, always the minimum of two wavefronts per lookup), 8 where shared memory
+// decides how many blocks fit an SM
+#define MMA_GREP 8u
+#define MMA_GREP_GU16 16u
 #define RC_PRAGMA_(x) _Pragma(#x)
 #define RC_UNROLL(n) RC_PRAGMA_(unroll n)
 
@@ -149,11 +154,11 @@ __device__ __forceinline__ void mma_s8_k32(int (&d)[4], uint32_t a0, uint32_t a1
 // Bs: activation digits of the work item in shared memory, column-major with pitch bpitch (== 32 mod 128: the 8-byte
 // fragment reads of the 8 columns of a tile fall into 8 different bank groups).
 // NUSED > 0: the number of column tiles in use is a compile-time constant (no per-tile tests in the loop).
-template <int NMAT, int NTILE, int NUSED = 0>
+template <int NMAT, int NTILE, int NUSED = 0, uint32_t GREP = MMA_GREP>
 __device__ __forceinline__ void mma_unit(const uint8_t *stage, const float (&dsc)[NMAT][2], const int8_t *Bs, uint32_t bpitch, uint32_t kbase,
                                          const uint8_t *lutg, const uint8_t *luts, uint32_t lane, uint32_t ntiles, float (&out)[NMAT][NTILE][4]) {
     if (NUSED > 0) ntiles = NUSED;
-    const uint32_t g = lane >> 2, t = lane & 3u, rep8 = (lane & 7u) * 8u, rep16 = (lane & 7u) * 16u;
+    const uint32_t g = lane >> 2, t = lane & 3u, rep8 = (lane & (GREP - 1u)) * 8u, rep16 = (lane & 7u) * 16u;
     const uint32_t sel = 0x4440u + t, sh7 = 7u * t;
     int blk[NMAT][NTILE][4];
 #pragma unroll
@@ -171,7 +176,7 @@ __device__ __forceinline__ void mma_unit(const uint8_t *stage, const float (&dsc
                 const uint2 q = *reinterpret_cast<const uint2 *>(stage + (uint32_t)(m * 16 + h * 8 + g) * MMA_ROW_PITCH + (uint32_t)kg * 8u);
                 const uint32_t gi = __byte_perm(q.x, 0u, sel);
                 const uint32_t s7 = (q.y >> sh7) & 127u;
-                const uint2 P = *reinterpret_cast<const uint2 *>(lutg + gi * 64u + rep8);
+                const uint2 P = *reinterpret_cast<const uint2 *>(lutg + gi * (GREP * 8u) + rep8);
                 const uint4 M = *reinterpret_cast<const uint4 *>(luts + s7 * 128u + rep16);
                 a[m][h] = (P.x ^ M.x) + M.z;         // bytes: +g, or ~g + 1 = -g (no carry between bytes: g >= 1)
                 a[m][2 + h] = (P.y ^ M.y) + M.w;
@@ -223,7 +228,7 @@ __global__ void __launch_bounds__(256, NTILE == 1 ? MMA_MINB : (NMAT == 1 && NTI
     const uint32_t bpr = A.ncols >> 8, nchunks = bpr;
     // carve shared memory: tables, per-warp staging, per-warp epilogue scratch (aliased onto the staging when NMAT == 2)
     uint8_t *lutg = smem;                                   // 256 x 64 B
-    uint8_t *luts = lutg + 256u * 64u;                      // 128 x 128 B
+    uint8_t *luts = lutg + 256u * MMA_GREP * 8u;            // 128 x 128 B
     uint8_t *stage0 = luts + 128u * 128u;                   // 8 warps x STAGES x NMAT*16 rows x pitch
     constexpr uint32_t stage_bytes = NMAT * 16u * MMA_ROW_PITCH, warp_stage = MMA_STAGES * stage_bytes;
     constexpr uint32_t scratch_bytes = NMAT * 16u * NCOL * 4u;
@@ -235,7 +240,7 @@ __global__ void __launch_bounds__(256, NTILE == 1 ? MMA_MINB : (NMAT == 1 && NTI
     constexpr uint32_t scratch_pitch = NMAT == 2 ? warp_stage : scratch_bytes;
     float *my_scratch = reinterpret_cast<float *>(scratch_base + warp * scratch_pitch);
 
-    for (uint32_t i = tid; i < 256u * 8u; i += 256u) reinterpret_cast<uint2 *>(lutg)[i] = A.lut_grid[i >> 3];
+    for (uint32_t i = tid; i < 256u * MMA_GREP; i += 256u) reinterpret_cast<uint2 *>(lutg)[i] = A.lut_grid[i / MMA_GREP];
     for (uint32_t i = tid; i < 128u * 8u; i += 256u) reinterpret_cast<uint4 *>(luts)[i] = A.lut_sign[i >> 3];
 
     const uint8_t *w[2] = {A.w0 + (size_t)e * A.mat_bytes, A.w1 ? A.w1 + (size_t)e * A.mat_bytes : nullptr};
@@ -362,14 +367,14 @@ __global__ void __launch_bounds__(512, 1) k_moe_gateup16(const __grid_constant__
     const uint32_t e = A.uexp[u] - A.expert_begin, pe = A.ustart[u + 1u], nt = min(A.item_tok, pe - p0);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
     const uint32_t bpr = A.ncols >> 8;
-    uint8_t *lutg = smem, *luts = lutg + 256u * 64u, *stage0 = luts + 128u * 128u;
+    uint8_t *lutg = smem, *luts = lutg + 256u * MMA_GREP_GU16 * 8u, *stage0 = luts + 128u * 128u;
     constexpr uint32_t stage_bytes = 16u * MMA_ROW_PITCH, warp_stage = MMA_STAGES * stage_bytes;
     static_assert(16u * NCOL * 4u <= warp_stage, "the epilogue scratch of a warp must fit its staging area");
     uint8_t *my_stage = stage0 + warp * warp_stage;
     const uint32_t bpitch = A.ncols + 32u;
     int8_t *Bs = reinterpret_cast<int8_t *>(stage0 + 16u * warp_stage);
 
-    for (uint32_t i = tid; i < 256u * 8u; i += 512u) reinterpret_cast<uint2 *>(lutg)[i] = A.lut_grid[i >> 3];
+    for (uint32_t i = tid; i < 256u * MMA_GREP_GU16; i += 512u) reinterpret_cast<uint2 *>(lutg)[i] = A.lut_grid[i / MMA_GREP_GU16];
     for (uint32_t i = tid; i < 128u * 8u; i += 512u) reinterpret_cast<uint4 *>(luts)[i] = A.lut_sign[i >> 3];
 
     const uint32_t is_up = warp >> 3;
@@ -417,12 +422,12 @@ __global__ void __launch_bounds__(512, 1) k_moe_gateup16(const __grid_constant__
         cp_async_wait<MMA_STAGES - 1>();
         __syncwarp();
         const uint8_t *st = my_stage + (c % MMA_STAGES) * stage_bytes;
-        if (NTILE >= 3 && ntiles == 1u) mma_unit<1, NTILE, 1>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
-        else if (NTILE >= 3 && ntiles == 2u) mma_unit<1, NTILE, 2>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
-        else if (NTILE >= 3 && ntiles == 3u) mma_unit<1, NTILE, 3>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
-        else if (NTILE == 6 && ntiles == 4u) mma_unit<1, NTILE, (NTILE == 6 ? 4 : NTILE)>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
-        else if (NTILE == 6 && ntiles == 5u) mma_unit<1, NTILE, (NTILE == 6 ? 5 : NTILE)>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
-        else mma_unit<1, NTILE, NTILE>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        if (NTILE >= 3 && ntiles == 1u) mma_unit<1, NTILE, 1, MMA_GREP_GU16>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else if (NTILE >= 3 && ntiles == 2u) mma_unit<1, NTILE, 2, MMA_GREP_GU16>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else if (NTILE >= 3 && ntiles == 3u) mma_unit<1, NTILE, 3, MMA_GREP_GU16>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else if (NTILE == 6 && ntiles == 4u) mma_unit<1, NTILE, (NTILE == 6 ? 4 : NTILE), MMA_GREP_GU16>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else if (NTILE == 6 && ntiles == 5u) mma_unit<1, NTILE, (NTILE == 6 ? 5 : NTILE), MMA_GREP_GU16>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else mma_unit<1, NTILE, NTILE, MMA_GREP_GU16>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
         __syncwarp();
     }
     cp_async_wait<0>();
@@ -451,7 +456,7 @@ __global__ void __launch_bounds__(512, 1) k_moe_gateup16(const __grid_constant__
 
 size_t mma_smem_bytes(uint32_t nmat, uint32_t ntile, uint32_t ncols) {
     const size_t stages = 8u * MMA_STAGES * nmat * 16u * MMA_ROW_PITCH;
-    return 256u * 64u + 128u * 128u + stages + (nmat == 2u ? 0u : 8u * 16u * ntile * 8u * 4u) + (size_t)ntile * 8u * (ncols + 32u);
+    return 256u * MMA_GREP * 8u + 128u * 128u + stages + (nmat == 2u ? 0u : 8u * 16u * ntile * 8u * 4u) + (size_t)ntile * 8u * (ncols + 32u);
 }
 
 uint32_t mma_item_tokens(bool few_tokens, uint32_t npairs, uint32_t n_experts) {
@@ -498,7 +503,7 @@ int launch_moe_mma(MmaArgs &A, uint32_t groups, uint32_t item_tok, cudaStream_t 
             static const bool gu16 = !(getenv("RC_MMA_GU16") && atoi(getenv("RC_MMA_GU16")) == 0);   // A/B switch
             RC_REQUIRE(!big_items || (gu16 && tpw == 1u && S == 1u), "moe mma: work items of 16 pairs need the 16-warp gate/up kernel");
             if (gu16 && tpw == 1u && S == 1u) {
-                const size_t smem = 256u * 64u + 128u * 128u + 16u * MMA_STAGES * 16u * MMA_ROW_PITCH + (size_t)(big_items ? 48u : 24u) * (A.ncols + 32u);
+                const size_t smem = 256u * MMA_GREP_GU16 * 8u + 128u * 128u + 16u * MMA_STAGES * 16u * MMA_ROW_PITCH + (size_t)(big_items ? 48u : 24u) * (A.ncols + 32u);
                 RC_REQUIRE(smem <= 227u * 1024u, "moe mma: %zu bytes of shared memory needed for %u columns", smem, A.ncols);
                 A.item_class = 0u;
                 if (big_items) {
