@@ -177,9 +177,15 @@ __device__ __forceinline__ void mma_unit(const uint8_t *stage, const float (&dsc
                 const uint32_t gi = __byte_perm(q.x, 0u, sel);
                 const uint32_t s7 = (q.y >> sh7) & 127u;
                 const uint2 P = *reinterpret_cast<const uint2 *>(lutg + gi * (GREP * 8u) + rep8);
-                const uint4 M = *reinterpret_cast<const uint4 *>(luts + s7 * 128u + rep16);
-                a[m][h] = (P.x ^ M.x) + M.z;         // bytes: +g, or ~g + 1 = -g (no carry between bytes: g >= 1)
-                a[m][2 + h] = (P.y ^ M.y) + M.w;
+                if (GREP == 16u) {      // 16 copies of the 8-byte sign mask; the +1 carry term is recomputed from it
+                    const uint2 M = *reinterpret_cast<const uint2 *>(luts + s7 * 128u + rep8);
+                    a[m][h] = (P.x ^ M.x) + (M.x & 0x01010101u);
+                    a[m][2 + h] = (P.y ^ M.y) + (M.y & 0x01010101u);
+                } else {
+                    const uint4 M = *reinterpret_cast<const uint4 *>(luts + s7 * 128u + rep16);
+                    a[m][h] = (P.x ^ M.x) + M.z;         // bytes: +g, or ~g + 1 = -g (no carry between bytes: g >= 1)
+                    a[m][2 + h] = (P.y ^ M.y) + M.w;
+                }
                 sc[m][h] = (int)(2u * (q.y >> 28) + 1u);
             }
         }
@@ -375,7 +381,7 @@ __global__ void __launch_bounds__(512, 1) k_moe_gateup16(const __grid_constant__
     int8_t *Bs = reinterpret_cast<int8_t *>(stage0 + 16u * warp_stage);
 
     for (uint32_t i = tid; i < 256u * MMA_GREP_GU16; i += 512u) reinterpret_cast<uint2 *>(lutg)[i] = A.lut_grid[i / MMA_GREP_GU16];
-    for (uint32_t i = tid; i < 128u * 8u; i += 512u) reinterpret_cast<uint4 *>(luts)[i] = A.lut_sign[i >> 3];
+    for (uint32_t i = tid; i < 128u * 16u; i += 512u) { const uint4 e4 = A.lut_sign[i >> 4]; reinterpret_cast<uint2 *>(luts)[i] = make_uint2(e4.x, e4.y); }
 
     const uint32_t is_up = warp >> 3;
     const uint8_t *w = (is_up ? A.w1 : A.w0) + (size_t)e * A.mat_bytes;
