@@ -460,6 +460,107 @@ __global__ void __launch_bounds__(512, 1) k_moe_gateup16(const __grid_constant__
     }
 }
 
+// Down projection of a batch with 16 warps per block sharing one set of tables (16 copies of both, as in the gate/up
+// kernel): warp w of block x takes the `tiles_per_warp` 16-row tiles starting at (16 x + w) * tiles_per_warp, one after
+// the other, each over all 256-column blocks of the row. The epilogue scratch is separate from the staging (the next
+// tile's weights are already in flight when a tile finishes).
+template <int NTILE>
+__global__ void __launch_bounds__(512, 1) k_moe_down16(const __grid_constant__ MmaArgs A) {
+    pdl_prologue();
+    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr uint32_t NCOL = NTILE * 8u;
+    if (blockIdx.y >= *A.n_items) return;
+    const uint32_t u = A.item_u[blockIdx.y], p0 = A.item_p0[blockIdx.y];
+    const uint32_t e = A.uexp[u] - A.expert_begin, pe = A.ustart[u + 1u], nt = min(A.item_tok, pe - p0);
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
+    const uint32_t bpr = A.ncols >> 8;
+    uint8_t *lutg = smem, *luts = lutg + 256u * MMA_GREP_GU16 * 8u, *stage0 = luts + 128u * 128u;
+    constexpr uint32_t stage_bytes = 16u * MMA_ROW_PITCH, warp_stage = MMA_STAGES * stage_bytes, scratch_bytes = 16u * NCOL * 4u;
+    uint8_t *my_stage = stage0 + warp * warp_stage;
+    float *my_scratch = reinterpret_cast<float *>(stage0 + 16u * warp_stage + warp * scratch_bytes);
+    const uint32_t bpitch = A.ncols + 32u;
+    int8_t *Bs = reinterpret_cast<int8_t *>(stage0 + 16u * warp_stage + 16u * scratch_bytes);
+
+    for (uint32_t i = tid; i < 256u * MMA_GREP_GU16; i += 512u) reinterpret_cast<uint2 *>(lutg)[i] = A.lut_grid[i / MMA_GREP_GU16];
+    for (uint32_t i = tid; i < 128u * 16u; i += 512u) { const uint4 e4 = A.lut_sign[i >> 4]; reinterpret_cast<uint2 *>(luts)[i] = make_uint2(e4.x, e4.y); }
+
+    const uint8_t *w = A.w0 + (size_t)e * A.mat_bytes;
+    const uint32_t tile_first = (blockIdx.x * 16u + warp) * A.tiles_per_warp, ntile_rows = A.nrows >> 4;
+    uint32_t my_tiles = 0;
+    for (uint32_t i = 0; i < A.tiles_per_warp; ++i) if (tile_first + i < ntile_rows) ++my_tiles;
+    const uint32_t nunits = my_tiles * bpr;
+    const uint32_t ntiles = (3u * nt + 7u) >> 3;
+
+    auto issue = [&](uint32_t unit, uint32_t buf) {
+        const uint32_t ti = unit / bpr, c = unit - ti * bpr, row0 = (tile_first + ti) << 4;
+        uint8_t *dst = my_stage + buf * stage_bytes;
+#pragma unroll
+        for (uint32_t i = 0; i < 2u; ++i) {
+            const uint32_t p = lane + 32u * i, rr = p >> 2, piece = p & 3u;
+            cp_async16(dst + rr * MMA_ROW_PITCH + piece * 16u, w + ((size_t)(row0 + rr) * bpr + c) * 64u + piece * 16u);
+        }
+    };
+    for (uint32_t i = 0; i + 1u < MMA_STAGES; ++i) {
+        if (i < nunits) issue(i, i);
+        cp_async_commit();
+    }
+    {
+        const uint32_t v16 = A.ncols >> 4;
+        for (uint32_t i = tid; i < ntiles * 8u * v16; i += 512u) {
+            const uint32_t col = i / v16, k = (i - col * v16) << 4, tk = col / 3u, dg = col - tk * 3u;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (tk < nt) v = *reinterpret_cast<const uint4 *>(A.xq + ((size_t)(A.sorted[p0 + tk] / A.x_div) * 3u + dg) * A.ncols + k);
+            *reinterpret_cast<uint4 *>(Bs + (size_t)col * bpitch + k) = v;
+        }
+    }
+    __syncthreads();
+
+    float out[1][NTILE][4];
+    for (uint32_t unit = 0; unit < nunits; ++unit) {
+        const uint32_t ti = unit / bpr, c = unit - ti * bpr, row0 = (tile_first + ti) << 4;
+        if (unit + MMA_STAGES - 1u < nunits) issue(unit + MMA_STAGES - 1u, (unit + MMA_STAGES - 1u) % MMA_STAGES);
+        cp_async_commit();
+        float dsc[1][2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const size_t bi = (size_t)(row0 + h * 8u + g) * bpr + c;
+            dsc[0][h] = 0.125f * __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short *>(w + A.nb * 64u) + bi)));
+        }
+        if (c == 0u) {
+#pragma unroll
+            for (int n = 0; n < NTILE; ++n) { out[0][n][0] = out[0][n][1] = out[0][n][2] = out[0][n][3] = 0.f; }
+        }
+        cp_async_wait<MMA_STAGES - 1>();
+        __syncwarp();
+        const uint8_t *st = my_stage + (unit % MMA_STAGES) * stage_bytes;
+        if (NTILE >= 3 && ntiles == 1u) mma_unit<1, NTILE, 1, MMA_GREP_GU16>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else if (NTILE >= 3 && ntiles == 2u) mma_unit<1, NTILE, 2, MMA_GREP_GU16>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else if (NTILE >= 3 && ntiles == 3u) mma_unit<1, NTILE, 3, MMA_GREP_GU16>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else if (NTILE == 6 && ntiles == 4u) mma_unit<1, NTILE, (NTILE == 6 ? 4 : NTILE), MMA_GREP_GU16>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else if (NTILE == 6 && ntiles == 5u) mma_unit<1, NTILE, (NTILE == 6 ? 5 : NTILE), MMA_GREP_GU16>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        else mma_unit<1, NTILE, NTILE, MMA_GREP_GU16>(st, dsc, Bs, bpitch, c * MMA_CHUNK_COLS, lutg, luts, lane, ntiles, out);
+        __syncwarp();
+        if (c + 1u == bpr) {      // tile finished: fragments -> the warp's scratch -> rows of the pairs
+#pragma unroll
+            for (int n = 0; n < NTILE; ++n) {
+                float *sp = my_scratch + n * 8u + 2u * t;
+                const bool live = (uint32_t)n < ntiles;
+                sp[(size_t)g * NCOL] = live ? out[0][n][0] : 0.f; sp[(size_t)g * NCOL + 1u] = live ? out[0][n][1] : 0.f;
+                sp[(size_t)(g + 8u) * NCOL] = live ? out[0][n][2] : 0.f; sp[(size_t)(g + 8u) * NCOL + 1u] = live ? out[0][n][3] : 0.f;
+            }
+            __syncwarp();
+            for (uint32_t idx = lane; idx < 16u * nt; idx += 32u) {
+                const uint32_t row = idx & 15u, tk = idx >> 4;
+                const uint32_t p = A.sorted[p0 + tk];
+                const float *a = my_scratch + (size_t)row * NCOL + 3u * tk;
+                A.out[(size_t)p * A.out_stride + row0 + row] = A.sx[p / A.x_div] * (16384.f * a[2] + 128.f * a[1] + a[0]);
+            }
+            __syncwarp();
+        }
+    }
+    cp_async_wait<0>();
+}
+
 size_t mma_smem_bytes(uint32_t nmat, uint32_t ntile, uint32_t ncols) {
     const size_t stages = 8u * MMA_STAGES * nmat * 16u * MMA_ROW_PITCH;
     return 256u * MMA_GREP * 8u + 128u * 128u + stages + (nmat == 2u ? 0u : 8u * 16u * ntile * 8u * 4u) + (size_t)ntile * 8u * (ncols + 32u);
@@ -521,8 +622,27 @@ int launch_moe_mma(MmaArgs &A, uint32_t groups, uint32_t item_tok, cudaStream_t 
                 }
                 g_launches.fetch_add(1, std::memory_order_relaxed);
             } else RC_MMA_LAUNCH(2, 3, 0u);
-        } else if (big_items) RC_MMA_LAUNCH(1, 6, 0u);
-        else RC_MMA_LAUNCH(1, 3, 0u);
+        } else {
+            // down projection: 16 warps per block when the tiles divide evenly (2 tiles per warp at the usual 2048 rows)
+            static const bool down16 = !(getenv("RC_MMA_DOWN16") && atoi(getenv("RC_MMA_DOWN16")) == 0);   // A/B switch
+            uint32_t tpw16 = 1u;
+            while (tpw16 < 8u && ntile_rows / (16u * tpw16 * 2u) >= 4u && ntile_rows % (16u * tpw16 * 2u) == 0) tpw16 <<= 1;
+            const uint32_t ncol = big_items ? 48u : 24u;
+            const size_t smem16 = 256u * MMA_GREP_GU16 * 8u + 128u * 128u + 16u * MMA_STAGES * 16u * MMA_ROW_PITCH + 16u * 16u * ncol * 4u + (size_t)ncol * (A.ncols + 32u);
+            if (down16 && ntile_rows % (16u * tpw16) == 0 && smem16 <= 227u * 1024u) {
+                A.tiles_per_warp = tpw16; A.item_class = 0u;
+                const dim3 grid16(ntile_rows / (16u * tpw16), groups);
+                if (big_items) {
+                    RC_CUDA(cudaFuncSetAttribute(k_moe_down16<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem16));
+                    RC_LAUNCH((k_moe_down16<6>), grid16, 512, smem16, s, A);
+                } else {
+                    RC_CUDA(cudaFuncSetAttribute(k_moe_down16<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem16));
+                    RC_LAUNCH((k_moe_down16<3>), grid16, 512, smem16, s, A);
+                }
+                g_launches.fetch_add(1, std::memory_order_relaxed);
+            } else if (big_items) RC_MMA_LAUNCH(1, 6, 0u);
+            else RC_MMA_LAUNCH(1, 3, 0u);
+        }
     }
 #undef RC_MMA_LAUNCH
     g_launches.fetch_sub(1, std::memory_order_relaxed);     // RC_LAUNCHED below counts one of them
