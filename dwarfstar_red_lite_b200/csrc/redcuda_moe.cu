@@ -366,10 +366,10 @@ static int moe_forward_on(redcuda_moe *m, uint32_t ntok, const float *x, const f
     // experts and joins before the combine (both edges are events, so the fork is kept when the caller captures a graph).
     // With profiling on, everything stays on one stream so that per-kernel times are not overlapped.
     const bool fork = !prof_active();
-    // When only the routed gate/up reads the digits (the shared expert takes the GEMV for one or two tokens), the
-    // quantisation leaves the critical path too: it opens the side stream and the main stream waits for it only
-    // before the gate/up launch, behind the router GEMV and the selection.
-    const bool quant_aside = fork && xq && !moe_shared_mma(m, ntok);
+    // The quantisation of x leaves the critical path too: it opens the side stream (the shared expert's tensor-core
+    // kernels, which read the digits as well, follow it there) and the main stream waits for it only before the
+    // gate/up launch, behind the router GEMV, the selection and the grouping.
+    const bool quant_aside = fork && xq;
     if (xq && !quant_aside && !launch_quant_act(x, m->d.hidden, ntok, m->d.hidden, m->xq_x, m->sx_x, s)) return 0;
     if (fork) {
         RC_CUDA(cudaEventRecord(m->ev_fork, s));
