@@ -244,7 +244,7 @@ def test_ep_pieces_single_rank_match_fused_forward(full_layer):
     assert np.max(np.abs(got - want)) <= 2e-6 * np.max(np.abs(want))
 
 
-@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
 def test_ep_gather_form_shards_sum_to_fused_forward(full_layer, world):
     """The all-gather form of expert parallelism, its ranks emulated one after the other on one GPU: `world` shards with
     interleaved experts (expert e on shard e % world) each compute the partial sums of their own experts over every
