@@ -148,7 +148,8 @@ def run_reference(args):
     dt = time.perf_counter() - t0
     value = sample * args.steps / dt
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            # a step of the GPU arm is the whole batch through every layer; the CPU sample is scaled to that step
+            "ms_per_step": 1e3 * args.tokens * args.layers / value, "ms_per_sampled_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
             "config": workload_config(args, dims),
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
                              "sample": f"{sample} of the {args.tokens} tokens of one layer per step (oracle port of ffn(); the reference's own routed CPU path rejects IQ2_XXS experts)"},
@@ -202,26 +203,8 @@ def run_ep(args, world, rank, local):
         step()
     torch.cuda.synchronize()
     dist.barrier()
-    # The step has nothing data-dependent on the host, so it can be captured (collectives included) into one CUDA graph.
-    # Off unless RC_EP_GRAPH=1: replaying NCCL collectives from a graph did not complete on a 2-GPU run of this bench,
-    # so the default is the eager step, which the host queues without ever waiting for the devices.
-    graph = None
     side = torch.cuda.Stream()
-    if os.environ.get("RC_EP_GRAPH", "0") == "1":
-        try:
-            with torch.cuda.stream(side):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
-                    step()
-                graph = g
-        except Exception as exc:          # noqa: BLE001
-            sys.stderr.write(f"rank {rank}: CUDA graph capture of the EP step failed ({exc}); running eager\n")
-            graph = None
-        ok = torch.tensor([1.0 if graph is not None else 0.0], device=dev)
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        if ok.item() < 1.0:
-            graph = None
-    run = (lambda: graph.replay()) if graph is not None else step
+    run = step
     with torch.cuda.stream(side):
         run()
         side.synchronize()
@@ -253,7 +236,7 @@ def run_ep(args, world, rank, local):
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": dict(workload_config(args, dims), experts_per_gpu=ec, expert_placement="interleaved (expert e on rank e % N)",
-                               pairs_served_per_rank_per_layer=[float(p.item()) for p in allpairs], cuda_graph=graph is not None,
+                               pairs_served_per_rank_per_layer=[float(p.item()) for p in allpairs], cuda_graph=False,
                                exchange="per layer: NCCL all-gather of the token rows (fp32 activations + router ids/weights), reduce-scatter of the partial outputs; no host synchronisation"),
                 "roofline": None, "cpu_baseline": None,
                 "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
@@ -724,8 +707,7 @@ def main():
     layer_bytes = float(np.mean([a["layer"] for a in ab]))
     # DRAM traffic per launch: ncu (dram__bytes_read + dram__bytes_write) on a 2-layer capture of the same kernels gave
     # 114.93 MB for a gate/up launch of 105.41 MB algorithmic bytes and 51.39 MB for a down launch of 52.4 MB (part of
-    # its input still sits in L2) (profiles/k_moe_mma_ragged64.md); traffic grows with the distinct experts read, so
-    # it is scaled by the algorithmic bytes.
+    # its input still sits in L2); traffic grows with the distinct experts read, so it is scaled by the algorithmic bytes.
     ncu_ratio = {"moe_gateup": 114.93 / 105.41, "moe_down": 51.39 / 52.4}.get(dom)
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                 "frac_of_nominal_8000": achieved / 8000.0, "traffic": dom_bytes * ncu_ratio if ncu_ratio else None,

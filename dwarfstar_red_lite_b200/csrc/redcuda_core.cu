@@ -7,6 +7,7 @@
 
 #include <math.h>
 #include <stdlib.h>
+#include <string.h>
 #include <map>
 #include <mutex>
 #include <vector>
@@ -46,6 +47,29 @@ void prof_end(cudaStream_t s) {
 int pdl_mode() {
     static const int mode = getenv("RC_PDL") ? (atoi(getenv("RC_PDL")) != 0) : -1;
     return mode;
+}
+
+static uint32_t *g_status = nullptr;
+static std::once_flag g_status_once;
+uint32_t *status_words() {
+    std::call_once(g_status_once, [] {
+        void *p = nullptr;
+        if (cudaHostAlloc(&p, ST_WORDS * sizeof(uint32_t), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) { cudaGetLastError(); return; }
+        memset(p, 0, ST_WORDS * sizeof(uint32_t));
+        g_status = (uint32_t *)p;      // unified addressing: the host pointer is valid on every device
+    });
+    return g_status;
+}
+int status_failed() {
+    volatile uint32_t *st = g_status;
+    if (!st) return 0;
+    const uint32_t a = st[ST_ROUTER_NONFINITE], b = st[ST_TOKEN_RANGE], c = st[ST_EXPERT_RANGE];
+    if (!(a | b | c)) return 0;
+    st[ST_ROUTER_NONFINITE] = 0; st[ST_TOKEN_RANGE] = 0; st[ST_EXPERT_RANGE] = 0;
+    if (a) set_error("invalid router softmax denominator (non-finite router logits)");
+    else if (b) set_error("token id out of range on the device (non-finite logits in the argmax?)");
+    else set_error("an expert id outside this shard reached an expert kernel");
+    return 1;
 }
 
 int require_device() {
@@ -252,7 +276,8 @@ int launch_gemv(GemvArgs &A, cudaStream_t stream) {
 
 // ---- router: softmax + top-k, one block per token (router_exec.c:102-184 semantics, ties -> lower id) ----
 __global__ void __launch_bounds__(256) k_route(const float *__restrict__ logits, uint32_t n_expert, uint32_t top_k,
-                                               uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ probs_out) {
+                                               uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ probs_out,
+                                               uint32_t *__restrict__ status) {
     pdl_prologue();
     extern __shared__ float p[];                 // n_expert probabilities
     __shared__ float s_redf[8];
@@ -290,15 +315,17 @@ __global__ void __launch_bounds__(256) k_route(const float *__restrict__ logits,
         __syncthreads();
         if (tid == 0) {
             for (int w = 1; w < 8; ++w) if (s_bv[w] > bv || (s_bv[w] == bv && s_bi[w] < bi)) { bv = s_bv[w]; bi = s_bi[w]; }
+            if (bi >= n_expert) { bi = k; if (status) status[ST_ROUTER_NONFINITE] = 1u; }   // NaN probabilities compare false everywhere: no index was chosen
             ids[(size_t)tok * top_k + k] = bi;
             s_selw[k] = bv;
-            if (bi < n_expert) p[bi] = -1.0f;   // selected: below every probability from now on
+            p[bi] = -1.0f;   // selected: below every probability from now on
         }
         __syncthreads();
     }
     if (tid == 0) {
         double sel = 0.0;
         for (uint32_t k = 0; k < top_k; ++k) sel += (double)s_selw[k];
+        if (!(sel > 0.0 && sel < (double)INFINITY) && status) status[ST_ROUTER_NONFINITE] = 1u;
         const float invs = (float)(1.0 / sel);
         for (uint32_t k = 0; k < top_k; ++k) weights[(size_t)tok * top_k + k] = s_selw[k] * invs;
     }
@@ -309,7 +336,7 @@ __global__ void __launch_bounds__(256) k_route(const float *__restrict__ logits,
 // cost a few hundred dependent instructions instead of 2k barriers. Same arithmetic and tie rule as k_route.
 __global__ void __launch_bounds__(256) k_route_warp(const float *__restrict__ logits, uint32_t ntok, uint32_t n_expert, uint32_t top_k,
                                                     uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ probs_out,
-                                                    RouteGroup1 G) {
+                                                    RouteGroup1 G, uint32_t *__restrict__ status) {
     pdl_prologue();
     const uint32_t lane = threadIdx.x & 31u, tok = blockIdx.x * 8u + (threadIdx.x >> 5);
     if (tok >= ntok) return;
@@ -341,6 +368,7 @@ __global__ void __launch_bounds__(256) k_route_warp(const float *__restrict__ lo
             const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
+        if (bi >= n_expert) { bi = k; if (status && lane == 0) status[ST_ROUTER_NONFINITE] = 1u; }   // NaN probabilities: nothing compared greater
 #pragma unroll
         for (int j = 0; j < 32; ++j) if (lane + 32u * j == bi) p[j] = -1.0f;
         if (lane == 0) {
@@ -351,6 +379,7 @@ __global__ void __launch_bounds__(256) k_route_warp(const float *__restrict__ lo
         if (lane == (k & 31u)) { if (k < 32u) myw = bv; else myw2 = bv; }
         sel += (double)bv;
     }
+    if (!(sel > 0.0 && sel < (double)INFINITY) && status && lane == 0) status[ST_ROUTER_NONFINITE] = 1u;
     const float invs = (float)(1.0 / sel);
     if (lane < top_k) weights[(size_t)tok * top_k + lane] = myw * invs;
     if (lane + 32u < top_k) weights[(size_t)tok * top_k + lane + 32u] = myw2 * invs;
@@ -365,8 +394,9 @@ int launch_route(const float *logits_dev, uint32_t ntok, uint32_t n_expert, uint
     RC_REQUIRE(n_expert <= 8192u, "router: too many experts (%u)", n_expert);
     if (!ntok) return 1;
     prof_begin("route", stream);
-    if (n_expert <= 1024u) RC_LAUNCH((k_route_warp), (ntok + 7u) / 8u, 256, 0, stream, logits_dev, ntok, n_expert, top_k, ids_dev, weights_dev, probs_dev, G);
-    else RC_LAUNCH((k_route), ntok, 256, n_expert * sizeof(float), stream, logits_dev, n_expert, top_k, ids_dev, weights_dev, probs_dev);
+    uint32_t *st = status_words();
+    if (n_expert <= 1024u) RC_LAUNCH((k_route_warp), (ntok + 7u) / 8u, 256, 0, stream, logits_dev, ntok, n_expert, top_k, ids_dev, weights_dev, probs_dev, G, st);
+    else RC_LAUNCH((k_route), ntok, 256, n_expert * sizeof(float), stream, logits_dev, n_expert, top_k, ids_dev, weights_dev, probs_dev, st);
     prof_end(stream);
     RC_LAUNCHED();
     return 1;
@@ -599,7 +629,7 @@ int redcuda_router_select_softmax_topk(const float *logits, uint32_t ntok, uint3
     RC_CUDA(cudaMemcpyAsync(weights, w.p, (size_t)ntok * top_k * 4u, cudaMemcpyDeviceToHost, s));
     if (probs) RC_CUDA(cudaMemcpyAsync(probs, p.p, (size_t)ntok * n_expert * 4u, cudaMemcpyDeviceToHost, s));
     RC_CUDA(cudaStreamSynchronize(s));
-    return 1;
+    return status_failed() ? 0 : 1;
 }
 
 }  // extern "C"

@@ -345,10 +345,9 @@ extern "C" int redcuda_deltanet_step(const redcuda_deltanet_params *p, uint32_t 
 //
 // The step needs scratch between its three kernels (normalised q/k, conv output v, beta, gate, un-normalised head
 // outputs). redcuda_deltanet_step allocates that scratch per call, which a caller cannot afford when it runs inside a
-// serving loop that must never block on the allocator (cudaMalloc / cudaFree synchronise the whole device), when its
-// stream is being captured into a CUDA graph (allocation is illegal there), or when another runtime owns the device
-// memory budget. For those callers the scratch lives in the array below, part of the library image: every GPU that
-// loads the library holds these 512 KiB until the process exits.
+// serving loop that must never block on the allocator (cudaMalloc / cudaFree synchronise the whole device), or when
+// another runtime owns the device memory budget. For those callers the scratch lives in the array below, part of the
+// library image: every GPU that loads the library holds these 512 KiB until the process exits.
 #define RC_DN_SCRATCH_FLOATS (128u * 1024u)
 static __device__ __align__(256) float g_dn_scratch[RC_DN_SCRATCH_FLOATS];
 
@@ -359,6 +358,7 @@ static float *g_dn_scratch_dev[64] = {nullptr};
 
 extern "C" int redcuda_deltanet_step_noalloc(const redcuda_deltanet_params *p, uint32_t batch, const float *qkv_dev, const float *z_dev,
                                              const float *ba_dev, float *conv_state_dev, float *rec_state_dev, float *out_dev, void *stream) {
+    if (!require_device()) return 0;
     RC_REQUIRE(p && qkv_dev && z_dev && ba_dev && conv_state_dev && rec_state_dev && out_dev && batch, "deltanet step (no-alloc): null or empty argument");
     RC_REQUIRE(p->conv_kernel && p->dt_bias && p->ssm_a && p->ssm_norm, "deltanet step (no-alloc): null parameter array");
     const DnDims D{p->d_conv, p->d_state, p->n_group, p->dt_rank, p->d_inner, p->channels, p->rms_eps};

@@ -30,10 +30,11 @@ static double now_ms() { return std::chrono::duration<double, std::milli>(std::c
 
 // ---- small kernels ----
 // out[b] = dequantised embedding row of token[b] (grid = tokens, block = 256 threads)
-__global__ void k_embed_row(const uint8_t *__restrict__ base, uint32_t type, uint64_t nb, uint32_t ncols, const uint32_t *__restrict__ token,
-                            const uint8_t *iq2, const uint32_t *iq3s, float *__restrict__ out) {
+__global__ void k_embed_row(const uint8_t *__restrict__ base, uint32_t type, uint64_t nb, uint32_t ncols, uint32_t nrows, const uint32_t *__restrict__ token,
+                            const uint8_t *iq2, const uint32_t *iq3s, float *__restrict__ out, uint32_t *__restrict__ status) {
     pdl_prologue();
-    const uint64_t row = token[blockIdx.x];
+    uint64_t row = token[blockIdx.x];
+    if (row >= nrows) { row = 0; if (status && threadIdx.x == 0) status[ST_TOKEN_RANGE] = 1u; }   // never index the table with an id the argmax could not form
     out += (size_t)blockIdx.x * ncols;
     if (type == RC_F32) { for (uint32_t i = threadIdx.x; i < ncols; i += blockDim.x) out[i] = reinterpret_cast<const float *>(base)[row * ncols + i]; return; }
     if (type == RC_F16) { for (uint32_t i = threadIdx.x; i < ncols; i += blockDim.x) out[i] = __half2float(__ushort_as_half(reinterpret_cast<const unsigned short *>(base)[row * ncols + i])); return; }
@@ -231,7 +232,7 @@ __global__ void k_advance(uint32_t *pos) {
 
 // gen_log / gen_count (optional): the chosen id is also appended to gen_log[*gen_count]
 __global__ void __launch_bounds__(1024) k_argmax(const float *__restrict__ v, uint32_t n, uint32_t *__restrict__ out, uint32_t *__restrict__ gen_log,
-                                                 uint32_t *__restrict__ gen_count) {
+                                                 uint32_t *__restrict__ gen_count, uint32_t *__restrict__ status) {
     pdl_prologue();
     __shared__ float bv[32];
     __shared__ uint32_t bi[32];
@@ -245,6 +246,7 @@ __global__ void __launch_bounds__(1024) k_argmax(const float *__restrict__ v, ui
     __syncthreads();
     if (threadIdx.x == 0) {
         for (int w = 1; w < 32; ++w) if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
+        if (idx >= n) { idx = 0; if (status) status[ST_TOKEN_RANGE] = 1u; }      // every logit NaN: nothing compared greater
         *out = idx;
         if (gen_log) { gen_log[*gen_count] = idx; *gen_count += 1u; }
     }
@@ -362,7 +364,7 @@ static int eng_step_device(rl_engine *e, bool want_logits, char *error, size_t c
     cudaStream_t s = e->stream;
     if (e->position >= in.context) ENG_FAIL("context of %u positions is full", in.context);
     prof_begin("embed", s);
-    RC_LAUNCH((k_embed_row), 1, 256, 0, s, e->tok_embd.base, e->tok_embd.type, e->tok_embd.nb, in.hidden, e->token_d, books_iq2(), books_iq3s(), e->embed_d);
+    RC_LAUNCH((k_embed_row), 1, 256, 0, s, e->tok_embd.base, e->tok_embd.type, e->tok_embd.nb, in.hidden, in.vocab, e->token_d, books_iq2(), books_iq3s(), e->embed_d, status_words());
     prof_end(s);
     g_launches.fetch_add(1);
     const float *x = e->embed_d;
@@ -463,7 +465,7 @@ static int eng_prefill_chunk(rl_engine *e, uint32_t n, bool want_logits, char *e
     const DnDims D{in.d_conv, in.d_state, in.n_group, in.dt_rank, in.d_inner, in.channels, in.rms_eps};
     const size_t last = (size_t)(n - 1u);
     prof_begin("embed", s);
-    RC_LAUNCH((k_embed_row), n, 256, 0, s, e->tok_embd.base, e->tok_embd.type, e->tok_embd.nb, in.hidden, e->tok_chunk_d, books_iq2(), books_iq3s(), e->bx[0]);
+    RC_LAUNCH((k_embed_row), n, 256, 0, s, e->tok_embd.base, e->tok_embd.type, e->tok_embd.nb, in.hidden, in.vocab, e->tok_chunk_d, books_iq2(), books_iq3s(), e->bx[0], status_words());
     prof_end(s);
     g_launches.fetch_add(1);
     ENG_CUDA(cudaMemcpyAsync(e->embed_d, e->bx[0] + last * in.hidden, in.hidden * 4u, cudaMemcpyDeviceToDevice, s));
@@ -532,11 +534,13 @@ static int eng_copy_mirrors(rl_engine *e, float *logits, char *error, size_t cap
     ENG_CUDA(cudaMemcpyAsync(e->router_ids_h.data(), e->router_ids_d, (size_t)in.n_layer * RL_ENGINE_MAX_TOPK * 4u, cudaMemcpyDeviceToHost, s));
     if (logits) ENG_CUDA(cudaMemcpyAsync(logits, e->logits_d, (size_t)in.vocab * 4u, cudaMemcpyDeviceToHost, s));
     ENG_CUDA(cudaStreamSynchronize(s));
+    if (status_failed()) ENG_FAIL("%s", redcuda_last_error());
     return 1;
 }
 
 static int eng_reset_state(rl_engine *e, char *error, size_t cap) {
     ENG_CUDA(cudaMemsetAsync(e->state.p, 0, e->state.bytes, e->stream));
+    if (e->tc_err) ENG_CUDA(cudaMemsetAsync(e->tc_err, 0, 4, e->stream));
     ENG_CUDA(cudaStreamSynchronize(e->stream));
     return eng_set_position(e, 0u, error, cap);
 }
@@ -803,6 +807,7 @@ int rl_engine_prefill(rl_engine *e, rl_engine_backend backend, const uint32_t *t
     for (uint32_t i = 0; i < count; ++i) if (tokens[i] >= e->info.vocab) { eng_err(error, cap, "token id out of range"); return 0; }
     if (e->position + (uint64_t)count > e->info.context) { eng_err(error, cap, "prompt does not fit the context"); return 0; }
     uint32_t *tok_pin = e->token_pin + 16, *pos_pin = tok_pin + e->pb;
+    ENG_CUDA(cudaMemsetAsync(e->tc_err, 0, 4, e->stream));     // a timeout of an earlier call must not fail this one
     for (uint32_t i = 0; i < count;) {
         const uint32_t n = std::min(e->pb, count - i);
         const bool last = i + n == count;
@@ -823,7 +828,7 @@ int rl_engine_prefill(rl_engine *e, rl_engine_backend backend, const uint32_t *t
     }
     ENG_CUDA(cudaMemcpyAsync(e->token_pin + 3, e->tc_err, 4, cudaMemcpyDeviceToHost, e->stream));
     if (!eng_copy_mirrors(e, logits, error, cap)) return 0;
-    if (e->token_pin[3]) ENG_FAIL("prefill: a tensor-core stage never signalled completion (bounded wait ran out)");
+    if (e->token_pin[3]) ENG_FAIL("prefill: a tensor-core stage never signalled completion (bounded wait ran out); the engine state holds partial results: call rl_engine_reset before the next use");
     if (stats) { stats->total_ms = now_ms() - t0; stats->gpu_ms = stats->total_ms; }
     if (error && cap) error[0] = '\0';
     return 1;
@@ -843,7 +848,7 @@ int rl_engine_generate_greedy(rl_engine *e, uint32_t token, uint32_t n_new, uint
     ENG_CUDA(cudaMemsetAsync(e->gen_count_d, 0, 4, e->stream));
     auto one_token = [&]() -> int {
         if (!eng_step_device(e, true, error, cap)) return 0;
-        RC_LAUNCH((k_argmax), 1, 1024, 0, e->stream, e->logits_d, e->info.vocab, e->token_d, e->gen_tokens_d, e->gen_count_d);
+        RC_LAUNCH((k_argmax), 1, 1024, 0, e->stream, e->logits_d, e->info.vocab, e->token_d, e->gen_tokens_d, e->gen_count_d, status_words());
         g_launches.fetch_add(1);
         return 1;
     };
@@ -902,7 +907,7 @@ int rl_engine_embed_token(const rl_engine *ce, uint32_t token, float *out, char 
     ENG_CUDA(cudaStreamSynchronize(e->stream));
     e->token_pin[1] = token;
     ENG_CUDA(cudaMemcpyAsync(e->token_d + 1, e->token_pin + 1, 4, cudaMemcpyHostToDevice, e->stream));
-    RC_LAUNCH((k_embed_row), 1, 256, 0, e->stream, e->tok_embd.base, e->tok_embd.type, e->tok_embd.nb, e->info.hidden, e->token_d + 1, books_iq2(), books_iq3s(), e->normed);
+    RC_LAUNCH((k_embed_row), 1, 256, 0, e->stream, e->tok_embd.base, e->tok_embd.type, e->tok_embd.nb, e->info.hidden, e->info.vocab, e->token_d + 1, books_iq2(), books_iq3s(), e->normed, status_words());
     g_launches.fetch_add(1);
     ENG_CUDA(cudaMemcpyAsync(out, e->normed, e->info.hidden * 4u, cudaMemcpyDeviceToHost, e->stream));
     ENG_CUDA(cudaStreamSynchronize(e->stream));

@@ -58,6 +58,7 @@ public:
     static uint64_t tensor_bytes(uint32_t type, uint32_t n_dims, const uint64_t *shape) {
         uint64_t row;
         const uint64_t n0 = shape[0];
+        if (n0 > (1ull << 40)) return 0;                 // hostile shapes must not wrap the products below
         switch (type) {
             case 0: row = n0 * 4u; break;
             case 1: row = n0 * 2u; break;
@@ -66,7 +67,10 @@ public:
             case 21: if (n0 % 256u) return 0; row = n0 / 256u * 110u; break;
             default: return 0;
         }
-        for (uint32_t d = 1; d < n_dims; ++d) row *= shape[d];
+        for (uint32_t d = 1; d < n_dims; ++d) {
+            if (shape[d] && row > UINT64_MAX / shape[d]) return 0;     // overflow: reported as an unsupported tensor
+            row *= shape[d];
+        }
         return row;
     }
 

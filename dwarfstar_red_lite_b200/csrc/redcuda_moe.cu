@@ -27,7 +27,8 @@ struct MoeArgs {
     const uint8_t *w0, *w1;        // expert matrices of the shard, back to back (gate / up, or down / unused)
     uint64_t mat_bytes, nb;        // bytes and blocks of one expert matrix
     uint32_t type, nrows, ncols;   // per expert matrix
-    uint32_t expert_begin, rows_per_tile;
+    uint32_t expert_begin, rows_per_tile, n_local;
+    uint32_t *status;
     const uint32_t *sorted, *uexp, *ustart, *n_unique;
     const float *x; uint32_t x_stride, x_div;   // activation row of pair p = x + (p / x_div) * x_stride
     float *out; uint32_t out_stride;            // result row of pair p = out + p * out_stride
@@ -71,6 +72,7 @@ __global__ void __launch_bounds__(256) k_moe_experts(const __grid_constant__ Moe
     const uint32_t u = blockIdx.y;
     if (u >= *A.n_unique) return;
     const uint32_t e = A.uexp[u] - A.expert_begin, ps = A.ustart[u], pe = A.ustart[u + 1u];
+    if (e >= A.n_local) { if (A.status && threadIdx.x == 0) A.status[ST_EXPERT_RANGE] = 1u; return; }     // never index the arena with a foreign id
     const uint8_t *m0 = A.w0 + (size_t)e * A.mat_bytes, *m1 = A.w1 ? A.w1 + (size_t)e * A.mat_bytes : nullptr;
     const uint32_t row0 = blockIdx.x * A.rows_per_tile;
     load_books(s_iq2, s_iq3s, A.iq2, A.iq3s, 1u << A.type);
@@ -215,6 +217,9 @@ struct redcuda_moe {
     uint32_t *ids_mirror = nullptr;       // optional: a single token's ids are also written here (the engine's per-layer view)
     int8_t *xq_x = nullptr, *xq_act = nullptr, *xq_sh = nullptr;      // activation digits for the tensor-core paths
     float *sx_x = nullptr, *sx_act = nullptr, *sx_sh = nullptr;
+    // digits of the token rows for redcuda_moe_shared_device alone: under expert parallelism it runs on another stream
+    // than redcuda_moe_partial_device, which fills xq_x / sx_x with the gathered rows of every rank at the same time
+    int8_t *xq_own = nullptr; float *sx_own = nullptr;
     uint32_t max_pairs = 0;
     bool use_mma = false;      // IQ2_XXS experts (and the Q6_K shared expert of a batch) on the integer tensor-core path
     cudaStream_t stream = nullptr;
@@ -234,7 +239,9 @@ static bool moe_shared_mma(const redcuda_moe *m, uint32_t ntok) {
 }
 
 // x_quantised: xq_x / sx_x already hold the digits of x
-static int moe_gemv_pre(redcuda_moe *m, uint32_t ntok, const float *x, bool with_router, bool with_shared, bool x_quantised, cudaStream_t s) {
+static int moe_gemv_pre(redcuda_moe *m, uint32_t ntok, const float *x, bool with_router, bool with_shared, bool x_quantised, cudaStream_t s,
+                        const int8_t *xq = nullptr, const float *sx = nullptr) {
+    if (!xq) { xq = m->xq_x; sx = m->sx_x; }
     GemvArgs A{};
     A.ntok = ntok; A.x = x; A.x_stride = m->d.hidden;
     uint32_t j = 0;
@@ -251,7 +258,7 @@ static int moe_gemv_pre(redcuda_moe *m, uint32_t ntok, const float *x, bool with
     }
     if (with_shared) {
         if (moe_shared_mma(m, ntok) && x_quantised) {
-            if (!launch_q6k_mma(m->sh_gate.base, m->sh_up.base, m->sh_gate.nb, m->d.ffn_sh, m->d.hidden, ntok, m->xq_x, m->sx_x, m->sh_act, m->d.ffn_sh,
+            if (!launch_q6k_mma(m->sh_gate.base, m->sh_up.base, m->sh_gate.nb, m->d.ffn_sh, m->d.hidden, ntok, xq, sx, m->sh_act, m->d.ffn_sh,
                                 "moe_shared_gateup_mma", s)) return 0;
         } else add(m->sh_gate, &m->sh_up, m->sh_act, m->d.ffn_sh, GEMV_PAIR_SILU);
         // the scalar gate is a single row: as a GEMV job it would be one block sweeping every token
@@ -290,7 +297,7 @@ static int moe_launch_experts(redcuda_moe *m, bool gateup, uint32_t npairs, bool
         MmaArgs M{};
         M.w0 = gateup ? m->gate : m->down; M.w1 = gateup ? m->up : nullptr;
         M.mat_bytes = gateup ? m->gu_bytes : m->down_bytes; M.nb = gateup ? m->gu_nb : m->down_nb;
-        M.nrows = nrows; M.ncols = ncols; M.expert_begin = m->d.expert_begin;
+        M.nrows = nrows; M.ncols = ncols; M.expert_begin = m->d.expert_begin; M.n_local = m->d.expert_count; M.status = status_words();
         M.sorted = m->sorted; M.uexp = m->uexp; M.ustart = m->ustart; M.item_u = m->item_u; M.item_p0 = m->item_p0; M.n_items = m->n_items;
         M.xq = xq; M.sx = sx; M.x_div = x_div; M.out = out; M.out_stride = out_stride;
         const uint32_t tok = mma_item_tokens(single_token, npairs, m->d.expert_count);
@@ -303,7 +310,7 @@ static int moe_launch_experts(redcuda_moe *m, bool gateup, uint32_t npairs, bool
     A.mat_bytes = gateup ? m->gu_bytes : m->down_bytes; A.nb = gateup ? m->gu_nb : m->down_nb;
     A.type = gateup ? m->d.type_gu : m->d.type_down;
     A.nrows = nrows; A.ncols = ncols;
-    A.expert_begin = m->d.expert_begin;
+    A.expert_begin = m->d.expert_begin; A.n_local = m->d.expert_count; A.status = status_words();
     A.sorted = m->sorted; A.uexp = m->uexp; A.ustart = m->ustart; A.n_unique = m->n_unique;
     A.x = x; A.x_stride = x_stride; A.x_div = x_div; A.out = out; A.out_stride = out_stride; A.pair_silu = gateup ? 1u : 0u;
     A.iq2 = books_iq2(); A.iq3s = books_iq3s();
@@ -418,6 +425,7 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
     if (!d.router || !d.gate_exps || !d.up_exps || !d.down_exps || !d.sh_gate_inp || !d.sh_gate || !d.sh_up || !d.sh_down) return fail("null weight pointer");
     if (!require_books(d.type_gu) || !require_books(d.type_down) || !require_books(d.type_sh)) return nullptr;
 
+    status_words();        // allocated here, never inside a stream capture
     redcuda_moe *m = new (std::nothrow) redcuda_moe();
     if (!m) return fail("out of host memory");
     m->d = d;
@@ -484,7 +492,7 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
                  o_out = take(T * d.hidden * 4u), o_ids = take(P * 4u), o_sorted = take(P * 4u), o_uexp = take((size_t)(d.expert_count + 1u) * 4u),
                  o_ustart = take((size_t)(d.expert_count + 2u) * 4u), o_nu = take(16), o_bad = take(16),
                  o_xqx = take(P * 3u * d.hidden), o_sxx = take(P * 4u), o_xqa = take(P * 3u * d.ffn), o_sxa = take(P * 4u),
-                 o_xqs = take(T * 3u * d.ffn_sh), o_sxs = take(T * 4u), o_iu = take((P + 8u) * 4u), o_ip = take((P + 8u) * 4u), o_ni = take(16);
+                 o_xqs = take(T * 3u * d.ffn_sh), o_sxs = take(T * 4u), o_xqo = take(T * 3u * d.hidden), o_sxo = take(T * 4u), o_iu = take((P + 8u) * 4u), o_ip = take((P + 8u) * 4u), o_ni = take(16);
     if (!m->ws.alloc(w)) return bail();
     uint8_t *B = m->ws.as<uint8_t>();
     m->x = (float *)(B + o_x); m->logits = (float *)(B + o_log); m->wk = (float *)(B + o_wk); m->scalar = (float *)(B + o_sca);
@@ -494,6 +502,7 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
     m->xq_x = (int8_t *)(B + o_xqx); m->sx_x = (float *)(B + o_sxx); m->xq_act = (int8_t *)(B + o_xqa); m->sx_act = (float *)(B + o_sxa);
     m->xq_sh = (int8_t *)(B + o_xqs); m->sx_sh = (float *)(B + o_sxs); m->item_u = (uint32_t *)(B + o_iu); m->item_p0 = (uint32_t *)(B + o_ip);
     m->n_items = (uint32_t *)(B + o_ni);
+    m->xq_own = (int8_t *)(B + o_xqo); m->sx_own = (float *)(B + o_sxo);
     {   // RC_MOE_PATH=cuda keeps the IQ2_XXS experts on the CUDA-core kernels (A/B switch for profiling)
         const char *pth = getenv("RC_MOE_PATH");
         m->use_mma = !(pth && pth[0] == 'c');
@@ -539,7 +548,7 @@ int redcuda_moe_forward(redcuda_moe *m, uint32_t ntok, const float *x, const flo
     if (weights_out) RC_CUDA(cudaMemcpyAsync(weights_out, m->wk, kb, cudaMemcpyDeviceToHost, s));
     if (logits_out) RC_CUDA(cudaMemcpyAsync(logits_out, m->logits, lb, cudaMemcpyDeviceToHost, s));
     RC_CUDA(cudaStreamSynchronize(s));
-    return 1;
+    return status_failed() ? 0 : 1;
 }
 
 int redcuda_moe_route_device(redcuda_moe *m, uint32_t ntok, const float *x_dev, const float *logits_in_dev, uint32_t *ids_dev, float *weights_dev, void *stream) {
@@ -608,8 +617,8 @@ int redcuda_moe_shared_device(redcuda_moe *m, uint32_t ntok, const float *x_dev,
     RC_REQUIRE(ntok >= 1 && ntok <= m->d.max_tokens, "moe shared: ntok %u outside [1, %u]", ntok, m->d.max_tokens);
     cudaStream_t s = (cudaStream_t)stream;
     const bool xq = moe_shared_mma(m, ntok);
-    if (xq && !launch_quant_act(x_dev, m->d.hidden, ntok, m->d.hidden, m->xq_x, m->sx_x, s)) return 0;
-    if (!moe_gemv_pre(m, ntok, x_dev, false, true, xq, s) || !moe_shared_down(m, ntok, s)) return 0;
+    if (xq && !launch_quant_act(x_dev, m->d.hidden, ntok, m->d.hidden, m->xq_own, m->sx_own, s)) return 0;
+    if (!moe_gemv_pre(m, ntok, x_dev, false, true, xq, s, m->xq_own, m->sx_own) || !moe_shared_down(m, ntok, s)) return 0;
     return moe_combine(m, ntok, nullptr, nullptr, 0u, true, nullptr, out_dev, s);
 }
 

@@ -7,12 +7,12 @@
 //
 // Arithmetic (exact integers, then fp32 scaling):
 //   weight          w = d/8 * (2s+1) * (+-g),  g in {8,25,43} from the codebook, s the 4-bit scale of the 32-group
-//   activation      x = sx * (16384*q2 + 128*q1 + q0), q_i balanced 7-bit digits (k_quant_act): 21-bit fixed point
-//                   per row, error <= 2^-21 max|x| per element
+//   activation      x = sx * (65536*q2 + 256*q1 + q0), q_i balanced 8-bit digits (k_quant_act): 24-bit fixed point
+//                   per row, error <= 2^-24 max|x| per element (an fp32 mantissa for the row's largest elements)
 //   per 32-group    one MMA per 8 columns gives sum(+-g * q) exactly in s32; multiplied by the integer (2s+1) and
 //                   summed over the 8 groups of a block still in s32 (|.| < 2^25)
 //   per block       converted to fp32 once and scaled by d/8; fp32 accumulation over the row's blocks only
-//   per row,token   out = sx * (16384*o2 + 128*o1 + o0)
+//   per row,token   out = sx * (65536*o2 + 256*o1 + o0)
 //
 // Operand layout: lane (g = lane/4, t = lane%4) owns grid entry t (8 consecutive weights) of rows g and g+8 of the
 // current 32-group, i.e. MMA k-slots {4t..4t+3, 16+4t..16+4t+3} stand for columns 8t..8t+7 of the group; the B
@@ -67,10 +67,15 @@ int mma_set_luts(const uint8_t *iq2_grid_host) {
     return 1;
 }
 
-// ---- activation rows -> three balanced 7-bit digit planes + one fp32 scale per row ----
-// grid = rows, block = 256. xq[row][3][ncols] (digit 0 = least significant), sx[row].
+uint32_t act_digit_bits() {
+    static const uint32_t bits = (getenv("RC_ACT_BITS") && atoi(getenv("RC_ACT_BITS")) == 7) ? 7u : 8u;
+    return bits;
+}
+
+// ---- activation rows -> three balanced digit planes of `bits` bits + one fp32 scale per row ----
+// grid = rows, block = 256. xq[row][3][ncols] (digit 0 = least significant), sx[row]. Digits lie in [-2^(bits-1), 2^(bits-1)).
 __global__ void __launch_bounds__(256) k_quant_act(const float *__restrict__ x, uint32_t x_stride, uint32_t ncols,
-                                                   int8_t *__restrict__ xq, float *__restrict__ sx) {
+                                                   int8_t *__restrict__ xq, float *__restrict__ sx, uint32_t bits) {
     pdl_prologue();
     __shared__ float red[8];
     const uint32_t row = blockIdx.x, tid = threadIdx.x;
@@ -85,7 +90,8 @@ __global__ void __launch_bounds__(256) k_quant_act(const float *__restrict__ x, 
     __syncthreads();
     mx = red[0];
     for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
-    const float QMAX = 1040000.0f;
+    const int half = 1 << (bits - 1u), mask = (1 << bits) - 1;
+    const float QMAX = bits == 8u ? 8355711.0f : 1040000.0f;      // largest value three digits hold: 127 * (65536 + 256 + 1), or just below 63.5 * 16384
     const float scale = (mx > 0.f && mx < INFINITY) ? mx / QMAX : 1.0f;
     const float inv = 1.0f / scale;
     if (tid == 0) sx[row] = scale;
@@ -97,8 +103,8 @@ __global__ void __launch_bounds__(256) k_quant_act(const float *__restrict__ x, 
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             int iv = __float2int_rn(fminf(fmaxf(f[i] * inv, -QMAX), QMAX));
-            const int d0 = ((iv + 64) & 127) - 64; iv = (iv - d0) >> 7;
-            const int d1 = ((iv + 64) & 127) - 64; iv = (iv - d1) >> 7;
+            const int d0 = ((iv + half) & mask) - half; iv = (iv - d0) >> bits;
+            const int d1 = ((iv + half) & mask) - half; iv = (iv - d1) >> bits;
             p0 |= (uint32_t)(d0 & 255) << (8 * i); p1 |= (uint32_t)(d1 & 255) << (8 * i); p2 |= (uint32_t)(iv & 255) << (8 * i);
         }
         *reinterpret_cast<uint32_t *>(q + k) = p0;
@@ -111,7 +117,7 @@ int launch_quant_act(const float *x, uint32_t x_stride, uint32_t rows, uint32_t 
     RC_REQUIRE(ncols % 16u == 0, "quant_act: %u columns is not a multiple of 16", ncols);
     if (!rows) return 1;
     prof_begin("moe_quant_act", s);
-    RC_LAUNCH((k_quant_act), rows, 256, 0, s, x, x_stride, ncols, xq, sx);
+    RC_LAUNCH((k_quant_act), rows, 256, 0, s, x, x_stride, ncols, xq, sx, act_digit_bits());
     prof_end(s);
     RC_LAUNCHED();
     return 1;
@@ -228,6 +234,7 @@ __global__ void __launch_bounds__(256, NTILE == 1 ? MMA_MINB : (NMAT == 1 && NTI
     if (blockIdx.y >= *A.n_items) return;
     const uint32_t u = A.item_u[blockIdx.y], p0 = A.item_p0[blockIdx.y];
     const uint32_t e = A.uexp[u] - A.expert_begin, pe = A.ustart[u + 1u], nt = min(A.item_tok, pe - p0);
+    if (e >= A.n_local) { if (A.status && threadIdx.x == 0) A.status[ST_EXPERT_RANGE] = 1u; return; }     // never index the arena with a foreign id
     if ((A.item_class == 1u && nt > 2u) || (A.item_class == 2u && nt <= 2u)) return;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
     const uint32_t S = A.S, R = 8u / S, r = warp / S, ks = warp % S;
@@ -345,7 +352,7 @@ __global__ void __launch_bounds__(256, NTILE == 1 ? MMA_MINB : (NMAT == 1 && NTI
                             const float *sp = reinterpret_cast<const float *>(scratch_base + (warp + s) * scratch_pitch) + (size_t)m * 16u * NCOL + (size_t)row * NCOL + 3u * tk;
                             o0 += sp[0]; o1 += sp[1]; o2 += sp[2];
                         }
-                        val[m] = sxv * (16384.f * o2 + 128.f * o1 + o0);
+                        val[m] = sxv * (A.dw2 * o2 + A.dw1 * o1 + o0);
                     }
                     float v = val[0];
                     if (NMAT == 2) { const float gte = val[0]; v = (gte / (1.0f + expf(-gte))) * val[NMAT - 1]; }
@@ -371,6 +378,7 @@ __global__ void __launch_bounds__(512, 1) k_moe_gateup16(const __grid_constant__
     if (blockIdx.y >= *A.n_items) return;
     const uint32_t u = A.item_u[blockIdx.y], p0 = A.item_p0[blockIdx.y];
     const uint32_t e = A.uexp[u] - A.expert_begin, pe = A.ustart[u + 1u], nt = min(A.item_tok, pe - p0);
+    if (e >= A.n_local) { if (A.status && threadIdx.x == 0) A.status[ST_EXPERT_RANGE] = 1u; return; }     // never index the arena with a foreign id
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
     const uint32_t bpr = A.ncols >> 8;
     uint8_t *lutg = smem, *luts = lutg + 256u * MMA_GREP_GU16 * 8u, *stage0 = luts + 128u * 128u;
@@ -454,7 +462,7 @@ __global__ void __launch_bounds__(512, 1) k_moe_gateup16(const __grid_constant__
             const uint32_t p = A.sorted[p0 + tk];
             const float sxv = A.sx[p / A.x_div];
             const float *a = gs + (size_t)row * NCOL + 3u * tk, *b = us + (size_t)row * NCOL + 3u * tk;
-            const float gte = sxv * (16384.f * a[2] + 128.f * a[1] + a[0]), upv = sxv * (16384.f * b[2] + 128.f * b[1] + b[0]);
+            const float gte = sxv * (A.dw2 * a[2] + A.dw1 * a[1] + a[0]), upv = sxv * (A.dw2 * b[2] + A.dw1 * b[1] + b[0]);
             A.out[(size_t)p * A.out_stride + row0 + row] = (gte / (1.0f + expf(-gte))) * upv;
         }
     }
@@ -472,6 +480,7 @@ __global__ void __launch_bounds__(512, 1) k_moe_down16(const __grid_constant__ M
     if (blockIdx.y >= *A.n_items) return;
     const uint32_t u = A.item_u[blockIdx.y], p0 = A.item_p0[blockIdx.y];
     const uint32_t e = A.uexp[u] - A.expert_begin, pe = A.ustart[u + 1u], nt = min(A.item_tok, pe - p0);
+    if (e >= A.n_local) { if (A.status && threadIdx.x == 0) A.status[ST_EXPERT_RANGE] = 1u; return; }     // never index the arena with a foreign id
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
     const uint32_t bpr = A.ncols >> 8;
     uint8_t *lutg = smem, *luts = lutg + 256u * MMA_GREP_GU16 * 8u, *stage0 = luts + 128u * 128u;
@@ -553,7 +562,7 @@ __global__ void __launch_bounds__(512, 1) k_moe_down16(const __grid_constant__ M
                 const uint32_t row = idx & 15u, tk = idx >> 4;
                 const uint32_t p = A.sorted[p0 + tk];
                 const float *a = my_scratch + (size_t)row * NCOL + 3u * tk;
-                A.out[(size_t)p * A.out_stride + row0 + row] = A.sx[p / A.x_div] * (16384.f * a[2] + 128.f * a[1] + a[0]);
+                A.out[(size_t)p * A.out_stride + row0 + row] = A.sx[p / A.x_div] * (A.dw2 * a[2] + A.dw1 * a[1] + a[0]);
             }
             __syncwarp();
         }
@@ -577,6 +586,7 @@ int launch_moe_mma(MmaArgs &A, uint32_t groups, uint32_t item_tok, cudaStream_t 
     int dev = 0;
     RC_CUDA(cudaGetDevice(&dev));
     A.lut_grid = g_lut_grid_ptr[dev & 63];
+    A.dw1 = (float)(1u << act_digit_bits()); A.dw2 = A.dw1 * A.dw1;
     A.lut_sign = g_lut_sign_ptr[dev & 63];
     RC_REQUIRE(A.lut_grid && A.lut_sign, "IQ2_XXS tensor-core tables not set on device %d: call redcuda_set_codebooks first", dev);
     RC_REQUIRE(A.ncols % MMA_CHUNK_COLS == 0 && A.nrows % 16u == 0, "moe mma: matrix %ux%u is not a multiple of 16 rows x 256 columns", A.nrows, A.ncols);

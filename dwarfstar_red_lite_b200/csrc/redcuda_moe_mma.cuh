@@ -9,7 +9,8 @@ struct MmaArgs {
     const uint8_t *w0, *w1;        // planar IQ2_XXS expert matrices of the shard, back to back (gate/up, or down/nullptr)
     uint64_t mat_bytes, nb;        // bytes and 256-blocks of one expert matrix
     uint32_t nrows, ncols;         // per expert matrix
-    uint32_t expert_begin;
+    uint32_t expert_begin, n_local;  // first expert id of the shard and the number of experts it holds (slot = id - expert_begin)
+    uint32_t *status;              // sticky status words (redcuda_common.cuh), may be null
     const uint32_t *sorted, *uexp, *ustart;              // pairs grouped by expert (k_group_pairs)
     const uint32_t *item_u, *item_p0, *n_items;          // work items: expert slot and first pair of up to `TOK` pairs
     const int8_t *xq;              // activation digits [row][3][ncols]; row of pair p = p / x_div
@@ -18,10 +19,14 @@ struct MmaArgs {
     float *out; uint32_t out_stride;                     // result row of pair p = out + p * out_stride
     const uint2 *lut_grid; const uint4 *lut_sign;        // filled by launch_moe_mma
     uint32_t S, tiles_per_warp, item_tok, item_class;    // filled by launch_moe_mma
+    float dw1, dw2;                // weights of digits 1 and 2 (2^bits, 4^bits), filled by launch_moe_mma
 };
 
 // Builds the magnitude and sign tables of the tensor-core path from the IQ2_XXS codebook (current device).
 int mma_set_luts(const uint8_t *iq2_grid_host);
+// Width of one balanced activation digit: 8 bits (24-bit fixed point per row, the default) or 7 (RC_ACT_BITS=7, the
+// earlier 21-bit form, kept for A/B runs).
+uint32_t act_digit_bits();
 // x[rows][x_stride] (first ncols of each row) -> digits xq[rows][3][ncols] and scales sx[rows]
 int launch_quant_act(const float *x, uint32_t x_stride, uint32_t rows, uint32_t ncols, int8_t *xq, float *sx, cudaStream_t s);
 // Pairs one work item of the tensor-core expert kernel covers: 2 in the few-token configuration, 8 for a decode batch,

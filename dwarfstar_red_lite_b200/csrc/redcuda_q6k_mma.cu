@@ -5,9 +5,10 @@
 // g and g+8) per 16-column scale group with ~14 integer instructions and then serves 8 tokens per three MMAs.
 //
 //   weight      w = d * sc * q,  q = 6-bit value - 32 in [-32, 31] (one int8), sc the int8 scale of the 16-group
-//   activation  x = sx * (16384*q2 + 128*q1 + q0), balanced 7-bit digits (k_quant_act)
-//   per group   the three digit products of a (row, token) are exact s32; they are recombined to sum(q * x_int)
-//               (|.| < 2^30), converted to fp32 and accumulated with the fp32 scale d*sc
+//   activation  x = sx * (65536*q2 + 256*q1 + q0), balanced 8-bit digits (k_quant_act)
+//   per group   the three digit products of a (row, token) are exact s32 (|.| <= 2^16); digits 1 and 2 are recombined
+//               exactly in s32 (|.| < 2^25), the result and digit 0 converted to fp32 and accumulated with the fp32
+//               scale d*sc
 //
 // Block = 8 warps = MS matrices x KS column splits x TGB groups of 8 tokens, for one tile of 16 rows; partial sums meet
 // in shared memory, where the epilogue (plain store or SiLU(gate)*up) is applied.
@@ -32,6 +33,7 @@ struct Q6Args {
     float *out; uint32_t out_stride;        // out[token * out_stride + row]
     uint32_t pair_silu;                     // 1: out = SiLU(w[0].x) * (w[1].x)
     uint32_t MS, KS;                        // matrices and column splits per block (8 % (MS*KS) == 0)
+    uint32_t bits; float dw1;               // digit width and 2^bits
 };
 
 __global__ void __launch_bounds__(256) k_q6k_mma(const __grid_constant__ Q6Args A) {
@@ -76,8 +78,8 @@ __global__ void __launch_bounds__(256) k_q6k_mma(const __grid_constant__ Q6Args 
             mma_s8_k16(d2, a[0], a[1], b2);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const int v = d0[c] + (d1[c] << 7) + (d2[c] << 14);
-                out[c] += scl[c >> 1] * (float)v;
+                const int hi = d1[c] + (d2[c] << A.bits);                 // 8-bit digits: the full recombination would leave s32
+                out[c] += scl[c >> 1] * fmaf(A.dw1, (float)hi, (float)d0[c]);
             }
         }
         // accumulator columns 2t, 2t+1 of this lane are tokens tg*8 + 2t, +1
@@ -111,6 +113,7 @@ int launch_q6k_mma(const uint8_t *w0, const uint8_t *w1, uint64_t nb, uint32_t n
     A.w[0] = w0; A.w[1] = w1 ? w1 : w0; A.nb = nb; A.nrows = nrows; A.ncols = ncols; A.ntok = ntok; A.xq = xq; A.sx = sx;
     A.out = out; A.out_stride = out_stride; A.pair_silu = w1 ? 1u : 0u;
     A.MS = w1 ? 2u : 1u;
+    A.bits = act_digit_bits(); A.dw1 = (float)(1u << A.bits);
     const uint32_t nsteps = ncols / 16u, tgroups = (ntok + 7u) / 8u, tiles = nrows / 16u;
     // column splits while the launch would leave SMs idle and every split keeps >= 16 steps
     uint32_t KS = 1u;

@@ -82,16 +82,18 @@ typedef struct {
 int redcuda_deltanet_step(const redcuda_deltanet_params *p, uint32_t batch, const float *qkv, const float *z, const float *ba,
                           float *conv_state, float *rec_state, float *out);
 
-/* No counterpart in the reference. The same DeltaNet step for callers that must not allocate: code running inside a
- * latency-critical serving loop (cudaMalloc / cudaFree stall the whole device), inside a CUDA-graph stream capture
- * (allocation is not allowed there), or next to a runtime that owns the device's memory budget. Every pointer — the
- * four arrays inside *p included — is DEVICE memory; the launches go to `stream` (cudaStream_t) and the call returns
- * without synchronising. The scratch between the kernels is a fixed 512 KiB array inside the library image (held by
- * every GPU that loads the library, until exit), enough for batch 8 at the Qwen3-Next shape (16/32 heads of 128);
- * larger requests fail with a message. The call never calls cudaMalloc, cudaFree or any allocating routine. The first
- * call on a device looks up the array's device address, so make that first call outside any stream capture. All calls
- * share the one array: two calls whose kernels overlap on the GPU (different streams, no ordering) race on it. Nothing
- * in it needs clearing between calls — each call overwrites every value it later reads. */
+/* No counterpart in the reference. The same DeltaNet step for callers that must not allocate device memory at call
+ * time: a serving loop with a latency budget (cudaMalloc / cudaFree stall the whole device), or a process in which
+ * another runtime owns the device's memory budget and hands this library only the buffers it passes in. Every pointer
+ * — the four arrays inside *p included — is DEVICE memory; the launches go to `stream` (cudaStream_t) and the call
+ * returns without synchronising. The scratch between the kernels is a fixed array of 131,072 floats (512 KiB) inside
+ * the library image, held by every GPU that loads the library until the process exits. A call needs
+ * batch * (2 * n_group * d_state + 2 * d_inner + 2 * dt_rank) of them: 12,352 per sequence at the Qwen3-Next shape
+ * (16 key / 32 value heads of 128), i.e. at most batch 10 there; larger requests fail with a message and launch
+ * nothing. The call never calls cudaMalloc, cudaFree or any allocating routine. The first call on a device looks up
+ * the array's device address (once, cached): make that first call before any stream capture begins. All calls share
+ * the one array: two calls whose kernels overlap on the GPU (different streams, no ordering) race on it. Nothing in it
+ * needs clearing between calls — each call overwrites every value it later reads. */
 int redcuda_deltanet_step_noalloc(const redcuda_deltanet_params *p_device_arrays, uint32_t batch, const float *qkv_dev, const float *z_dev,
                                   const float *ba_dev, float *conv_state_dev, float *rec_state_dev, float *out_dev, void *stream);
 

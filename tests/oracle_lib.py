@@ -111,8 +111,9 @@ def ref():
     if _ref is not False:
         return _ref
     so = os.path.join(ORACLE_DIR, "_ref", "libredlite_ref.so")
-    if not os.path.exists(so) and os.path.isdir("/root/reference/native"):
-        subprocess.call(["make", "-C", ORACLE_DIR, "ref"], stdout=subprocess.DEVNULL)
+    root = os.environ.get("REF_ROOT", "")
+    if not os.path.exists(so) and root and os.path.isdir(os.path.join(root, "native")):
+        subprocess.call(["make", "-C", ORACLE_DIR, "ref", f"REF_ROOT={root}"], stdout=subprocess.DEVNULL)
     if not os.path.exists(so):
         _ref = None
         return None
