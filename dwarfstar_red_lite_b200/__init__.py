@@ -5,5 +5,5 @@ thin Python host mirror of that ABI plus seeded synthetic inputs. There is no CP
 the library or a CUDA device is missing.
 """
 from . import synth  # noqa: F401
-from .redcuda import (MoeLayer, RedcudaError, deltanet_step, lib, quant_dequant_rows, quant_matmul_tc, quant_matvec,  # noqa: F401
+from .redcuda import (MoeLayer, RedcudaError, deltanet_step, lib, nib_dequant_rows, quant_dequant_rows, quant_matmul_tc, quant_matvec,  # noqa: F401
                       router_select_softmax_topk, set_codebooks)

@@ -383,7 +383,7 @@ __global__ void __launch_bounds__(256) k_route_warp(const float *__restrict__ lo
     const float invs = (float)(1.0 / sel);
     if (lane < top_k) weights[(size_t)tok * top_k + lane] = myw * invs;
     if (lane + 32u < top_k) weights[(size_t)tok * top_k + lane + 32u] = myw2 * invs;
-    if (G.sorted && lane == 0) { G.ustart[top_k] = top_k; *G.n_unique = top_k; *G.n_items = top_k; }
+    if (G.sorted && lane == 0) { G.ustart[top_k] = top_k; *G.n_unique = top_k; *G.n_items = top_k; if (G.work) { G.work[0] = 0u; G.work[1] = 0u; } }
 }
 
 int launch_route(const float *logits_dev, uint32_t ntok, uint32_t n_expert, uint32_t top_k, uint32_t *ids_dev, float *weights_dev,

@@ -33,7 +33,7 @@ struct GemvArgs {
 int launch_gemv(GemvArgs &A, cudaStream_t stream);
 // Where a single token's selection is also written as the (trivial) expert grouping the expert kernels read: every
 // selected expert is distinct, so pair k is its own group and its own work item.
-struct RouteGroup1 { uint32_t *sorted, *uexp, *ustart, *n_unique, *item_u, *item_p0, *n_items, *ids_mirror; };
+struct RouteGroup1 { uint32_t *sorted, *uexp, *ustart, *n_unique, *item_u, *item_p0, *n_items, *ids_mirror, *work; };   // work (may be null): two unit counters to zero
 // group1 (ntok == 1 only, may be null): fill the grouping arrays in the same kernel; ids_mirror (may be null) gets a copy of the ids
 int launch_route(const float *logits_dev, uint32_t ntok, uint32_t n_expert, uint32_t top_k, uint32_t *ids_dev, float *weights_dev,
                  float *probs_dev, cudaStream_t stream, const RouteGroup1 *group1 = nullptr);

@@ -117,8 +117,9 @@ __device__ __forceinline__ uint32_t shard_local(uint32_t g, uint32_t begin, uint
 __global__ void __launch_bounds__(1024) k_group_pairs(const uint32_t *__restrict__ pair_expert, uint32_t npairs, uint32_t expert_begin, uint32_t expert_stride,
                                                       uint32_t skip_foreign, uint32_t expert_count, uint32_t item_tok, uint32_t *__restrict__ sorted, uint32_t *__restrict__ uexp,
                                                       uint32_t *__restrict__ ustart, uint32_t *__restrict__ n_unique, uint32_t *__restrict__ item_u,
-                                                      uint32_t *__restrict__ item_p0, uint32_t *__restrict__ n_items, uint32_t *__restrict__ bad) {
+                                                      uint32_t *__restrict__ item_p0, uint32_t *__restrict__ n_items, uint32_t *__restrict__ bad, uint32_t *__restrict__ work) {
     pdl_prologue();
+    if (work && threadIdx.x < 2u) work[threadIdx.x] = 0u;      // unit counters of the persistent expert kernels that follow
     __shared__ uint32_t cnt[1024], start[1024], wsum[32], wsum2[32], wsum3[32];
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     cnt[tid] = 0;
@@ -163,9 +164,10 @@ __global__ void __launch_bounds__(1024) k_group_pairs(const uint32_t *__restrict
 // Single-token case: the k selected experts are distinct, so every pair is its own group and its own work item.
 __global__ void k_group_trivial(const uint32_t *__restrict__ pair_expert, uint32_t npairs, uint32_t *__restrict__ sorted,
                                 uint32_t *__restrict__ uexp, uint32_t *__restrict__ ustart, uint32_t *__restrict__ n_unique,
-                                uint32_t *__restrict__ item_u, uint32_t *__restrict__ item_p0, uint32_t *__restrict__ n_items) {
+                                uint32_t *__restrict__ item_u, uint32_t *__restrict__ item_p0, uint32_t *__restrict__ n_items, uint32_t *__restrict__ work) {
     pdl_prologue();
     const uint32_t i = threadIdx.x;
+    if (work && i < 2u) work[i] = 0u;
     if (i < npairs) { sorted[i] = i; uexp[i] = pair_expert[i]; ustart[i] = i; item_u[i] = i; item_p0[i] = i; }
     if (i == 0) { ustart[npairs] = npairs; *n_unique = npairs; *n_items = npairs; }
 }
@@ -222,6 +224,8 @@ struct redcuda_moe {
     int8_t *xq_own = nullptr; float *sx_own = nullptr;
     uint32_t max_pairs = 0;
     bool use_mma = false;      // IQ2_XXS experts (and the Q6_K shared expert of a batch) on the integer tensor-core path
+    bool nib = false;          // routed experts held in the nibble layout (redcuda_moe_nib.cu) instead of planar IQ2_XXS
+    uint32_t *work = nullptr;  // two unit counters of the persistent expert kernels (gate/up, down)
     cudaStream_t stream = nullptr;
     cudaStream_t side = nullptr;                    // the shared expert runs here, beside the routed experts
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_quant = nullptr;
@@ -231,7 +235,12 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // tensor-core path of the routed experts: IQ2_XXS gate/up/down with tile-able shapes
 static bool moe_experts_mma(const redcuda_moe *m) {
-    return m->use_mma && m->d.type_gu == RC_IQ2_XXS && m->d.type_down == RC_IQ2_XXS && m->d.hidden % 512u == 0 && m->d.ffn % 512u == 0;
+    return m->nib || (m->use_mma && m->d.type_gu == RC_IQ2_XXS && m->d.type_down == RC_IQ2_XXS && m->d.hidden % 512u == 0 && m->d.ffn % 512u == 0);
+}
+// pairs per work item: the nibble-layout kernels take at most 8
+static uint32_t moe_item_tokens(const redcuda_moe *m, bool single_token, uint32_t npairs) {
+    if (m->nib) return single_token ? 1u : 8u;
+    return mma_item_tokens(single_token, npairs, m->d.expert_count);
 }
 // tensor-core path of the shared expert: Q6_K and at least 3 tokens (below that the CUDA-core GEMV wins)
 static bool moe_shared_mma(const redcuda_moe *m, uint32_t ntok) {
@@ -300,9 +309,10 @@ static int moe_launch_experts(redcuda_moe *m, bool gateup, uint32_t npairs, bool
         M.nrows = nrows; M.ncols = ncols; M.expert_begin = m->d.expert_begin; M.n_local = m->d.expert_count; M.status = status_words();
         M.sorted = m->sorted; M.uexp = m->uexp; M.ustart = m->ustart; M.item_u = m->item_u; M.item_p0 = m->item_p0; M.n_items = m->n_items;
         M.xq = xq; M.sx = sx; M.x_div = x_div; M.out = out; M.out_stride = out_stride;
-        const uint32_t tok = mma_item_tokens(single_token, npairs, m->d.expert_count);
+        const uint32_t tok = moe_item_tokens(m, single_token, npairs);
         const uint32_t live = npairs < m->d.expert_count ? npairs : m->d.expert_count;
         const uint32_t max_items = single_token ? npairs : (npairs / tok + live < npairs ? npairs / tok + live : npairs);
+        if (m->nib) { M.item_tok = tok; M.work = m->work + (gateup ? 0 : 1); return launch_nib_experts(M, max_items, s); }
         return launch_moe_mma(M, max_items, tok, s);
     }
     MoeArgs A{};
@@ -343,10 +353,10 @@ static int moe_group(redcuda_moe *m, const uint32_t *pair_expert, uint32_t npair
     RC_REQUIRE(npairs <= m->max_pairs, "moe: %u pairs exceed the workspace (%u)", npairs, m->max_pairs);
     prof_begin("moe_group", s);
     if (distinct && npairs <= 64u && !skip_foreign) {
-        RC_LAUNCH((k_group_trivial), 1, 64, 0, s, pair_expert, npairs, m->sorted, m->uexp, m->ustart, m->n_unique, m->item_u, m->item_p0, m->n_items);
+        RC_LAUNCH((k_group_trivial), 1, 64, 0, s, pair_expert, npairs, m->sorted, m->uexp, m->ustart, m->n_unique, m->item_u, m->item_p0, m->n_items, m->work);
     } else {
-        RC_LAUNCH((k_group_pairs), 1, 1024, 0, s, pair_expert, npairs, m->d.expert_begin, m->d.expert_stride, skip_foreign ? 1u : 0u, m->d.expert_count, mma_item_tokens(false, npairs, m->d.expert_count), m->sorted, m->uexp, m->ustart,
-                                         m->n_unique, m->item_u, m->item_p0, m->n_items, m->bad);
+        RC_LAUNCH((k_group_pairs), 1, 1024, 0, s, pair_expert, npairs, m->d.expert_begin, m->d.expert_stride, skip_foreign ? 1u : 0u, m->d.expert_count, moe_item_tokens(m, false, npairs), m->sorted, m->uexp, m->ustart,
+                                         m->n_unique, m->item_u, m->item_p0, m->n_items, m->bad, m->work);
     }
     prof_end(s);
     RC_LAUNCHED();
@@ -390,7 +400,7 @@ static int moe_forward_on(redcuda_moe *m, uint32_t ntok, const float *x, const f
         if (!moe_gemv_pre(m, ntok, x, logits_in == nullptr, false, xq, s)) return 0;
     } else if (!moe_gemv_pre(m, ntok, x, logits_in == nullptr, true, xq, s)) return 0;
     if (ntok == 1u && m->d.n_expert <= 1024u) {      // one token: the router kernel also writes the (trivial) grouping
-        const RouteGroup1 G{m->sorted, m->uexp, m->ustart, m->n_unique, m->item_u, m->item_p0, m->n_items, m->ids_mirror};
+        const RouteGroup1 G{m->sorted, m->uexp, m->ustart, m->n_unique, m->item_u, m->item_p0, m->n_items, m->ids_mirror, m->work};
         if (!launch_route(logits_in ? logits_in : m->logits, ntok, m->d.n_expert, k, m->ids, m->wk, nullptr, s, &G)) return 0;
     } else {
         if (!launch_route(logits_in ? logits_in : m->logits, ntok, m->d.n_expert, k, m->ids, m->wk, nullptr, s)) return 0;
@@ -438,8 +448,14 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
         set_error("moe create: stream / event creation failed"); return bail();
     }
 
-    m->gu_bytes = rc_matrix_bytes(d.type_gu, d.ffn, d.hidden);
-    m->down_bytes = rc_matrix_bytes(d.type_down, d.hidden, d.ffn);
+    {   // RC_EXPERT_FMT: "nib4" keeps IQ2_XXS experts in the nibble layout (table-free decode, 2.09x the bytes), "iq2" in the
+        // planar GGUF bytes (the default)
+        const char *fmt = getenv("RC_EXPERT_FMT");
+        const bool want = fmt && fmt[0] == 'n';
+        m->nib = want && d.type_gu == RC_IQ2_XXS && d.type_down == RC_IQ2_XXS && nib_shape_ok(d.ffn, d.hidden) && nib_shape_ok(d.hidden, d.ffn);
+    }
+    m->gu_bytes = m->nib ? nib_matrix_bytes(d.ffn, d.hidden) : rc_matrix_bytes(d.type_gu, d.ffn, d.hidden);
+    m->down_bytes = m->nib ? nib_matrix_bytes(d.hidden, d.ffn) : rc_matrix_bytes(d.type_down, d.hidden, d.ffn);
     m->gu_nb = (uint64_t)d.ffn * (d.hidden / 256u);
     m->down_nb = (uint64_t)d.hidden * (d.ffn / 256u);
     if (m->gu_bytes % 16u || m->down_bytes % 16u) { set_error("moe create: expert matrix size is not a multiple of 16 bytes"); return bail(); }
@@ -465,8 +481,10 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
 
     // upload + planar repack; host sources go through a bounded staging buffer, expert by expert
     const bool dev = d.weights_on_device != 0;
-    DevMem scratch;
-    const size_t big = m->gu_bytes > m->down_bytes ? m->gu_bytes : m->down_bytes;
+    DevMem scratch, planar_tmp;
+    const size_t raw_gu = rc_matrix_bytes(d.type_gu, d.ffn, d.hidden), raw_down = rc_matrix_bytes(d.type_down, d.hidden, d.ffn);
+    if (m->nib && !planar_tmp.alloc(raw_gu > raw_down ? raw_gu : raw_down)) return bail();
+    const size_t big = raw_gu > raw_down ? raw_gu : raw_down;
     const size_t sc_b = big > shgu_b ? (big > shd_b ? big : shd_b) : (shgu_b > shd_b ? shgu_b : shd_b);
     if (!dev && !scratch.alloc(sc_b)) return bail();
     cudaStream_t s = m->stream;
@@ -475,10 +493,16 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
              upload_matrix(d.type_sh, d.ffn_sh, d.hidden, d.sh_gate, dev, W + o_shg, scratch.as<uint8_t>(), s) &&
              upload_matrix(d.type_sh, d.ffn_sh, d.hidden, d.sh_up, dev, W + o_shu, scratch.as<uint8_t>(), s) &&
              upload_matrix(d.type_sh, d.hidden, d.ffn_sh, d.sh_down, dev, W + o_shd, scratch.as<uint8_t>(), s);
+    // one expert matrix: raw GGUF rows -> planar (in place in the arena, or in a temporary when the arena holds the nibble layout)
+    auto put = [&](uint32_t type, uint32_t nrows, uint32_t ncols, const uint8_t *src, uint8_t *dst) -> int {
+        if (!m->nib) return upload_matrix(type, nrows, ncols, src, dev, dst, scratch.as<uint8_t>(), s);
+        return upload_matrix(type, nrows, ncols, src, dev, planar_tmp.as<uint8_t>(), scratch.as<uint8_t>(), s) &&
+               launch_nib_repack(planar_tmp.as<uint8_t>(), nrows, ncols, dst, s);
+    };
     for (uint32_t e = 0; ok && e < d.expert_count; ++e) {
-        ok = upload_matrix(d.type_gu, d.ffn, d.hidden, d.gate_exps + (size_t)e * m->gu_bytes, dev, m->gate + (size_t)e * m->gu_bytes, scratch.as<uint8_t>(), s) &&
-             upload_matrix(d.type_gu, d.ffn, d.hidden, d.up_exps + (size_t)e * m->gu_bytes, dev, m->up + (size_t)e * m->gu_bytes, scratch.as<uint8_t>(), s) &&
-             upload_matrix(d.type_down, d.hidden, d.ffn, d.down_exps + (size_t)e * m->down_bytes, dev, m->down + (size_t)e * m->down_bytes, scratch.as<uint8_t>(), s);
+        ok = put(d.type_gu, d.ffn, d.hidden, d.gate_exps + (size_t)e * raw_gu, m->gate + (size_t)e * m->gu_bytes) &&
+             put(d.type_gu, d.ffn, d.hidden, d.up_exps + (size_t)e * raw_gu, m->up + (size_t)e * m->gu_bytes) &&
+             put(d.type_down, d.hidden, d.ffn, d.down_exps + (size_t)e * raw_down, m->down + (size_t)e * m->down_bytes);
     }
     if (!ok) return bail();
 
@@ -492,7 +516,7 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
                  o_out = take(T * d.hidden * 4u), o_ids = take(P * 4u), o_sorted = take(P * 4u), o_uexp = take((size_t)(d.expert_count + 1u) * 4u),
                  o_ustart = take((size_t)(d.expert_count + 2u) * 4u), o_nu = take(16), o_bad = take(16),
                  o_xqx = take(P * 3u * d.hidden), o_sxx = take(P * 4u), o_xqa = take(P * 3u * d.ffn), o_sxa = take(P * 4u),
-                 o_xqs = take(T * 3u * d.ffn_sh), o_sxs = take(T * 4u), o_xqo = take(T * 3u * d.hidden), o_sxo = take(T * 4u), o_iu = take((P + 8u) * 4u), o_ip = take((P + 8u) * 4u), o_ni = take(16);
+                 o_xqs = take(T * 3u * d.ffn_sh), o_sxs = take(T * 4u), o_xqo = take(T * 3u * d.hidden), o_sxo = take(T * 4u), o_iu = take((P + 8u) * 4u), o_ip = take((P + 8u) * 4u), o_ni = take(16), o_wk2 = take(16);
     if (!m->ws.alloc(w)) return bail();
     uint8_t *B = m->ws.as<uint8_t>();
     m->x = (float *)(B + o_x); m->logits = (float *)(B + o_log); m->wk = (float *)(B + o_wk); m->scalar = (float *)(B + o_sca);
@@ -503,6 +527,7 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
     m->xq_sh = (int8_t *)(B + o_xqs); m->sx_sh = (float *)(B + o_sxs); m->item_u = (uint32_t *)(B + o_iu); m->item_p0 = (uint32_t *)(B + o_ip);
     m->n_items = (uint32_t *)(B + o_ni);
     m->xq_own = (int8_t *)(B + o_xqo); m->sx_own = (float *)(B + o_sxo);
+    m->work = (uint32_t *)(B + o_wk2);
     {   // RC_MOE_PATH=cuda keeps the IQ2_XXS experts on the CUDA-core kernels (A/B switch for profiling)
         const char *pth = getenv("RC_MOE_PATH");
         m->use_mma = !(pth && pth[0] == 'c');

@@ -20,6 +20,7 @@ struct MmaArgs {
     const uint2 *lut_grid; const uint4 *lut_sign;        // filled by launch_moe_mma
     uint32_t S, tiles_per_warp, item_tok, item_class;    // filled by launch_moe_mma
     float dw1, dw2;                // weights of digits 1 and 2 (2^bits, 4^bits), filled by launch_moe_mma
+    uint32_t *work;                // nibble-layout kernels: the launch's unit counter, zeroed by the grouping kernel
 };
 
 // Builds the magnitude and sign tables of the tensor-core path from the IQ2_XXS codebook (current device).
@@ -35,6 +36,13 @@ int launch_quant_act(const float *x, uint32_t x_stride, uint32_t rows, uint32_t 
 uint32_t mma_item_tokens(bool few_tokens, uint32_t npairs = 0u, uint32_t n_experts = 1u);
 // max_items = upper bound of work items (grid.y); item_tok: the size the items were cut with (2, 8 or 16)
 int launch_moe_mma(MmaArgs &A, uint32_t max_items, uint32_t item_tok, cudaStream_t s);
+// ---- nibble layout of IQ2_XXS expert matrices (redcuda_moe_nib.cu): 138 bytes per 256 weights, table-free decode ----
+uint64_t nib_matrix_bytes(uint32_t nrows, uint32_t ncols);
+bool nib_shape_ok(uint32_t nrows, uint32_t ncols);
+// planar IQ2_XXS matrix -> nibble layout (dst: nib_matrix_bytes, 16-byte aligned)
+int launch_nib_repack(const uint8_t *planar, uint32_t nrows, uint32_t ncols, uint8_t *dst, cudaStream_t s);
+// gate/up (A.w1 set) or down projection of the grouped pairs, work items of at most 8 pairs; persistent kernel
+int launch_nib_experts(MmaArgs &A, uint32_t max_items, cudaStream_t s);
 // Q6_K matrix (or gate/up pair with SiLU*mul when w1 != nullptr) x ntok activation rows given as digits (redcuda_q6k_mma.cu)
 int launch_q6k_mma(const uint8_t *w0, const uint8_t *w1, uint64_t nb, uint32_t nrows, uint32_t ncols, uint32_t ntok,
                    const int8_t *xq, const float *sx, float *out, uint32_t out_stride, const char *tag, cudaStream_t s);

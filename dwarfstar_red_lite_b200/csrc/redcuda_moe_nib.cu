@@ -1,0 +1,375 @@
+// Routed IQ2_XXS experts in the "nibble" layout: a load-time re-coding whose decode needs no table in shared memory.
+//
+// Why: IQ2_XXS stores 8 weights as one codebook index (8 bits) plus 7 sign bits; turning them into tensor-core operands
+// costs two dependent shared-memory lookups and ~10 integer instructions per 8 weights, and the expert kernels were
+// bound by instruction issue at a sixth of HBM speed (57 M warp instructions per gate/up launch of a 64-token batch).
+// Here every weight is re-coded once, at load, as a 4-bit code (bits 1:0 = which of the three codebook magnitudes
+// 8 / 25 / 43, bit 2 = sign); a lane then expands 4 weights into an int8 operand register with ONE instruction
+// (prmt against an 8-byte table held in two registers). Dequantised values are unchanged bit for bit
+// (redcuda_nib_dequant_rows against rl_quant_dequant_row, native/redlite_native_quant_cpu.c:166-191). The price is bytes:
+// 138 per 256 weights instead of 66, i.e. 2.09x the HBM footprint and traffic of the routed experts.
+//
+// Layout of one expert matrix [nrows][ncols], bpr = ncols / 256 blocks per row, nb = nrows * bpr:
+//   codes  @0         [row][block][t 0..3][kg 0..7] u32    word (t, kg) = the 8 weights 32*kg + 8*t .. +7 of the block,
+//                                                          weight j in bits 4j+3..4j (a lane's 8 words are 32 contiguous bytes)
+//   scales @nb * 128  [block][row][kg 0..7]         u8     2 * s + 1, s the 4-bit scale of the 32-weight group
+//   d      @nb * 136  [block][row]                  fp16   block scale
+// (block-major scale planes: the 16 rows of a tile are contiguous, one 128-byte and one 32-byte copy per tile and block).
+//
+// Arithmetic is the integer tensor-core scheme of redcuda_moe_mma.cu (mma.sync m16n8k32 s8, activations as three
+// balanced digits per value, s32 sums per 32-weight group scaled by the integer 2s+1, fp32 scaling by d/8 per block).
+//
+// Kernel: persistent CTAs of 8 warps, two per SM. A unit of work = one work item (<= 8 pairs of one expert, cut by
+// k_group_pairs) x a block of rows; CTAs draw units from an atomic counter, so the routing skew never leaves SMs idle
+// and nothing is set up per unit except the item's activation digits in shared memory. Every warp streams its 16-row
+// tiles through a private cp.async ring (three 256-column blocks in flight) that runs on across unit boundaries.
+// Column layout of the digits: items of one or two pairs pack (pair, digit) into one 8-column tile (cols 3*pair+digit);
+// larger items use one tile per digit (col = 8*digit + pair), so a lane holds all three digits of its two pairs and the
+// epilogue needs no exchange.
+#define RC_PDL_DEFAULT 0
+#include "redcuda_common.cuh"
+#include "redcuda_kernels.cuh"
+#include "redcuda_moe_mma.cuh"
+#include "../../include/redcuda.h"
+
+#include <stdlib.h>
+
+namespace rc {
+
+constexpr uint32_t NIB_BLOCK_BYTES = 138u;
+
+uint64_t nib_matrix_bytes(uint32_t nrows, uint32_t ncols) { return (uint64_t)nrows * (ncols / 256u) * NIB_BLOCK_BYTES; }
+bool nib_shape_ok(uint32_t nrows, uint32_t ncols) { return nrows % 16u == 0 && (ncols == 256u || ncols == 512u || ncols == 1024u || ncols == 2048u); }
+
+// ---- planar IQ2_XXS -> nibble layout: one thread per (block, group kg, quarter t) ----
+__global__ void k_nib_repack(const uint8_t *__restrict__ planar, uint64_t nb, uint32_t nrows, uint32_t bpr, const uint8_t *__restrict__ iq2,
+                             uint8_t *__restrict__ dst) {
+    pdl_prologue();
+    const uint64_t total = nb * 32u;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t b = i >> 5;
+        const uint32_t kg = ((uint32_t)i >> 2) & 7u, t = (uint32_t)i & 3u;
+        const uint32_t row = (uint32_t)(b / bpr), blk = (uint32_t)(b - (uint64_t)row * bpr);
+        const uint32_t auxg = *reinterpret_cast<const uint32_t *>(planar + b * 64u + kg * 8u), auxs = *reinterpret_cast<const uint32_t *>(planar + b * 64u + kg * 8u + 4u);
+        const uint8_t *gv = iq2 + ((auxg >> (8u * t)) & 255u) * 8u;
+        const uint32_t s8 = rc_sign8((auxs >> (7u * t)) & 127u);
+        uint32_t word = 0u;
+#pragma unroll
+        for (uint32_t j = 0; j < 8u; ++j) {
+            const uint32_t m = gv[j] == 0x19u ? 1u : gv[j] == 0x2bu ? 2u : 0u;
+            word |= (m | (((s8 >> j) & 1u) << 2)) << (4u * j);
+        }
+        *reinterpret_cast<uint32_t *>(dst + b * 128u + t * 32u + kg * 4u) = word;
+        if (t == 0u) {
+            dst[nb * 128u + ((uint64_t)blk * nrows + row) * 8u + kg] = (uint8_t)(2u * (auxs >> 28) + 1u);
+            if (kg == 0u) *reinterpret_cast<unsigned short *>(dst + nb * 136u + ((uint64_t)blk * nrows + row) * 2u) = *reinterpret_cast<const unsigned short *>(planar + rc_iq2_d(nb) + b * 2u);
+        }
+    }
+}
+
+int launch_nib_repack(const uint8_t *planar, uint32_t nrows, uint32_t ncols, uint8_t *dst, cudaStream_t s) {
+    RC_REQUIRE(nib_shape_ok(nrows, ncols), "nibble layout: matrix %ux%u is not tileable (16 rows, 256/512/1024/2048 columns)", nrows, ncols);
+    RC_REQUIRE(((uintptr_t)dst & 15u) == 0 && ((uintptr_t)planar & 15u) == 0, "nibble layout: unaligned matrix");
+    const uint64_t nb = (uint64_t)nrows * (ncols / 256u), total = nb * 32u;
+    const uint32_t grid = (uint32_t)((total + 255u) / 256u < 148u * 16u ? (total + 255u) / 256u : 148u * 16u);
+    prof_begin("nib_repack", s);
+    RC_LAUNCH((k_nib_repack), grid ? grid : 1u, 256, 0, s, planar, nb, nrows, ncols / 256u, books_iq2(), dst);
+    prof_end(s);
+    RC_LAUNCHED();
+    return 1;
+}
+
+// ---- nibble layout -> fp32, the float operations of rl_quant_dequant_row in the same order (exact) ----
+__global__ void k_nib_dequant(const uint8_t *__restrict__ nib, uint64_t nb, uint32_t nrows, uint32_t bpr, float *__restrict__ out) {
+    pdl_prologue();
+    const uint64_t total = nb * 32u;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t b = i >> 5;
+        const uint32_t kg = ((uint32_t)i >> 2) & 7u, t = (uint32_t)i & 3u;
+        const uint32_t row = (uint32_t)(b / bpr), blk = (uint32_t)(b - (uint64_t)row * bpr);
+        const uint32_t word = *reinterpret_cast<const uint32_t *>(nib + b * 128u + t * 32u + kg * 4u);
+        const uint32_t scb = nib[nb * 128u + ((uint64_t)blk * nrows + row) * 8u + kg];
+        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(nib + nb * 136u + ((uint64_t)blk * nrows + row) * 2u)));
+        const float db = d * (0.5f + (float)((scb - 1u) >> 1)) * 0.25f;
+        float *o = out + ((uint64_t)row * bpr + blk) * 256u + kg * 32u + t * 8u;
+#pragma unroll
+        for (uint32_t j = 0; j < 8u; ++j) {
+            const uint32_t code = (word >> (4u * j)) & 7u, m = code & 3u;
+            const float v = db * (m == 0u ? 8.0f : m == 1u ? 25.0f : 43.0f);
+            o[j] = (code & 4u) ? -v : v;
+        }
+    }
+}
+
+// ---- small PTX wrappers ----
+__device__ __forceinline__ void nb_cp_async16(void *smem_dst, const void *gsrc) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gsrc));
+}
+__device__ __forceinline__ void nb_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void nb_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void nb_mma(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// staged tile of one 256-column block: 16 rows x 128 code bytes (pitch 144: conflict-free 16-byte reads), 16 x 8 scale
+// bytes, 16 fp16 block scales
+constexpr uint32_t NIB_PITCH = 144u, NIB_SC_OFF = 16u * NIB_PITCH, NIB_D_OFF = NIB_SC_OFF + 128u, NIB_STAGE = NIB_D_OFF + 32u;
+constexpr uint32_t NIB_STAGES = 3u, NIB_WARPS = 8u;
+constexpr uint32_t NIB_TAB_POS = 0x002b1908u, NIB_TAB_NEG = 0x00d5e7f8u;      // bytes 8, 25, 43, 0 and -8, -25, -43, 0
+
+// One warp: 16 rows x one 256-column block against NT 8-column tiles of activation digits.
+// st: the staged tile; Bl: digits of column g of tile 0 at this block's first column + 8 t (tile n is n * 8 * BPITCH further).
+template <int NT, uint32_t BPITCH>
+__device__ __forceinline__ void nib_chunk(const uint8_t *st, const int8_t *Bl, uint32_t g, uint32_t t, float (&out)[3][4]) {
+    const uint4 qa0 = *reinterpret_cast<const uint4 *>(st + g * NIB_PITCH + t * 32u), qa1 = *reinterpret_cast<const uint4 *>(st + g * NIB_PITCH + t * 32u + 16u);
+    const uint4 qb0 = *reinterpret_cast<const uint4 *>(st + (g + 8u) * NIB_PITCH + t * 32u), qb1 = *reinterpret_cast<const uint4 *>(st + (g + 8u) * NIB_PITCH + t * 32u + 16u);
+    const uint2 sa = *reinterpret_cast<const uint2 *>(st + NIB_SC_OFF + g * 8u), sb = *reinterpret_cast<const uint2 *>(st + NIB_SC_OFF + (g + 8u) * 8u);
+    const float da = 0.125f * __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(st + NIB_D_OFF + g * 2u)));
+    const float db = 0.125f * __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(st + NIB_D_OFF + (g + 8u) * 2u)));
+    const uint32_t wa[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
+    const uint32_t wb[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
+    int blk[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) { blk[n][0] = blk[n][1] = blk[n][2] = blk[n][3] = 0; }
+#pragma unroll
+    for (int kg = 0; kg < 8; ++kg) {
+        const uint32_t a0 = __byte_perm(NIB_TAB_POS, NIB_TAB_NEG, wa[kg]), a2 = __byte_perm(NIB_TAB_POS, NIB_TAB_NEG, wa[kg] >> 16);
+        const uint32_t a1 = __byte_perm(NIB_TAB_POS, NIB_TAB_NEG, wb[kg]), a3 = __byte_perm(NIB_TAB_POS, NIB_TAB_NEG, wb[kg] >> 16);
+        const int sca = (int)__byte_perm(kg < 4 ? sa.x : sa.y, 0u, 0x4440u + (uint32_t)(kg & 3));
+        const int scb = (int)__byte_perm(kg < 4 ? sb.x : sb.y, 0u, 0x4440u + (uint32_t)(kg & 3));
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            const uint2 bf = *reinterpret_cast<const uint2 *>(Bl + (uint32_t)n * 8u * BPITCH + (uint32_t)kg * 32u);
+            int d[4];
+            nb_mma(d, a0, a1, a2, a3, bf.x, bf.y);
+            blk[n][0] += sca * d[0]; blk[n][1] += sca * d[1];
+            blk[n][2] += scb * d[2]; blk[n][3] += scb * d[3];
+        }
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        out[n][0] += da * (float)blk[n][0]; out[n][1] += da * (float)blk[n][1];
+        out[n][2] += db * (float)blk[n][2]; out[n][3] += db * (float)blk[n][3];
+    }
+}
+
+struct NibUnit {
+    const uint8_t *base;       // this warp's expert matrix
+    uint32_t item, p0, nt;     // work item, its first pair in sorted[], its pairs
+    uint32_t tile0, n;         // first 16-row tile of this warp and the number of 256-column blocks it streams in the unit
+};
+
+// GATEUP: warps 0-3 take the gate rows of 4 x TPW tiles, warps 4-7 the up rows of the same tiles; the up values cross a
+// small shared buffer and the gate warps store SiLU(gate) * up. Otherwise (down projection) 8 x TPW tiles per unit.
+template <bool GATEUP, uint32_t NCOLS>
+__global__ void __launch_bounds__(NIB_WARPS * 32u, 2) k_nib_experts(const __grid_constant__ MmaArgs A) {
+    pdl_prologue();
+    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr uint32_t BPR = NCOLS / 256u, TPW = BPR >= 8u ? 1u : 8u / BPR, WSLOTS = GATEUP ? 4u : 8u, UNIT_TILES = WSLOTS * TPW;
+    constexpr uint32_t BPITCH = NCOLS + 32u, V16 = NCOLS / 16u;
+    __shared__ uint32_t s_unit[2];
+    __shared__ __align__(16) float4 s_ex[GATEUP ? TPW : 1u][4][32];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
+    uint8_t *my_stage = smem + warp * (NIB_STAGES * NIB_STAGE);
+    int8_t *Bs = reinterpret_cast<int8_t *>(smem + NIB_WARPS * NIB_STAGES * NIB_STAGE);
+    const uint32_t ntile_rows = A.nrows >> 4, U = (ntile_rows + UNIT_TILES - 1u) / UNIT_TILES;
+    const uint32_t total = *A.n_items * U;
+    const bool is_up = GATEUP && warp >= 4u;
+    const uint32_t wslot = GATEUP ? (warp & 3u) : warp;
+    const uint8_t *wmat = is_up ? A.w1 : A.w0;
+    const uint64_t nb = A.nb;
+
+    auto decode = [&](uint32_t unit, NibUnit &I) {
+        const uint32_t item = unit / U, rb = unit - item * U;
+        const uint32_t u = A.item_u[item], p0 = A.item_p0[item];
+        uint32_t e = A.uexp[u] - A.expert_begin, nt = min(A.item_tok, A.ustart[u + 1u] - p0);
+        if (e >= A.n_local) { if (A.status && tid == 0) A.status[ST_EXPERT_RANGE] = 1u; e = 0u; nt = 0u; }     // never index the arena with a foreign id
+        I.base = wmat + (size_t)e * A.mat_bytes; I.item = item; I.p0 = p0; I.nt = nt;
+        I.tile0 = rb * UNIT_TILES + wslot * TPW;
+        const uint32_t tiles = I.tile0 >= ntile_rows ? 0u : min(TPW, ntile_rows - I.tile0);
+        I.n = nt ? tiles * BPR : 0u;
+    };
+    auto issue = [&](const NibUnit &I, uint32_t q, uint32_t slot) {
+        const uint32_t ti = q / BPR, c = q - ti * BPR, row0 = (I.tile0 + ti) << 4;
+        uint8_t *dst = my_stage + slot * NIB_STAGE;
+        const uint8_t *src = I.base + ((size_t)(row0 + (lane >> 3)) * BPR + c) * 128u + (lane & 7u) * 16u;
+#pragma unroll
+        for (uint32_t i = 0; i < 4u; ++i) nb_cp_async16(dst + ((lane >> 3) + 4u * i) * NIB_PITCH + (lane & 7u) * 16u, src + (size_t)i * 4u * BPR * 128u);
+        if (lane < 8u) nb_cp_async16(dst + NIB_SC_OFF + lane * 16u, I.base + nb * 128u + ((size_t)c * A.nrows + row0) * 8u + lane * 16u);
+        else if (lane < 10u) nb_cp_async16(dst + NIB_D_OFF + (lane - 8u) * 16u, I.base + nb * 136u + ((size_t)c * A.nrows + row0) * 2u + (lane - 8u) * 16u);
+    };
+
+    if (tid == 0) s_unit[0] = atomicAdd(A.work, 1u);
+    __syncthreads();
+    uint32_t cur = s_unit[0], par = 0u, cur_item = 0xffffffffu, base_slot = 0u;
+    bool prefetched = false;
+    NibUnit I{}, N{};
+    if (cur < total) decode(cur, I);
+    while (cur < total) {
+        if (tid == 0) s_unit[par ^ 1u] = atomicAdd(A.work, 1u);
+        if (!prefetched) {           // the ring is empty: start this unit's first blocks
+            nb_wait<0>();
+            for (uint32_t i = 0; i + 1u < NIB_STAGES; ++i) { if (i < I.n) issue(I, i, (base_slot + i) % NIB_STAGES); nb_commit(); }
+        }
+        const bool packed = I.nt <= 2u;
+        if (I.item != cur_item) {    // activation digits of the item (every warp passed the barrier that ended the last unit)
+            const uint32_t ncolb = packed ? 8u : 24u;
+            for (uint32_t i = tid; i < ncolb * V16; i += NIB_WARPS * 32u) {
+                const uint32_t col = i / V16, k = (i - col * V16) << 4;
+                const uint32_t tk = packed ? col / 3u : (col & 7u), dg = packed ? col - 3u * (col / 3u) : (col >> 3);
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (tk < I.nt) v = *reinterpret_cast<const uint4 *>(A.xq + ((size_t)(A.sorted[I.p0 + tk] / A.x_div) * 3u + dg) * NCOLS + k);
+                *reinterpret_cast<uint4 *>(Bs + (size_t)col * BPITCH + k) = v;
+            }
+            cur_item = I.item;
+        }
+        // the pairs this lane stores: packed -> pair t/2 on even t; one tile per digit -> pairs 2t, 2t+1
+        uint32_t prow[2] = {0u, 0u};
+        float sxv[2] = {0.f, 0.f};
+        bool ok[2];
+#pragma unroll
+        for (uint32_t j = 0; j < 2u; ++j) {
+            const uint32_t tk = packed ? (t >> 1) : 2u * t + j;
+            ok[j] = packed ? (j == 0u && (t & 1u) == 0u && tk < I.nt) : tk < I.nt;
+            if (ok[j]) { prow[j] = A.sorted[I.p0 + tk]; sxv[j] = A.sx[prow[j] / A.x_div]; }
+        }
+        __syncthreads();             // digits and the next unit's number are in shared memory
+        const uint32_t nxt = s_unit[par ^ 1u];
+        const bool nv = nxt < total;
+        if (nv) decode(nxt, N);
+        const bool ahead = nv && I.n + 1u >= NIB_STAGES;       // this unit is long enough to start the next one's ring
+
+        float out[3][4];
+        float gatev[TPW][4];
+        for (uint32_t q = 0; q < I.n; ++q) {
+            const uint32_t k = q + NIB_STAGES - 1u;
+            if (k < I.n) issue(I, k, (base_slot + k) % NIB_STAGES);
+            else if (ahead && k - I.n < N.n) issue(N, k - I.n, (base_slot + k) % NIB_STAGES);
+            nb_commit();
+            const uint32_t ti = q / BPR, c = q - ti * BPR;
+            if (c == 0u) {
+#pragma unroll
+                for (int n = 0; n < 3; ++n) { out[n][0] = out[n][1] = out[n][2] = out[n][3] = 0.f; }
+            }
+            nb_wait<NIB_STAGES - 1>();
+            __syncwarp();
+            const uint8_t *st = my_stage + ((base_slot + q) % NIB_STAGES) * NIB_STAGE;
+            const int8_t *Bl = Bs + (size_t)g * BPITCH + c * 256u + 8u * t;
+            if (packed) nib_chunk<1, BPITCH>(st, Bl, g, t, out);
+            else nib_chunk<3, BPITCH>(st, Bl, g, t, out);
+            __syncwarp();
+            if (c + 1u == BPR) {     // tile finished: digits -> values of (row g | g+8, pair)
+                float val[2][2];     // [row half][pair slot]
+                if (packed) {
+                    const uint32_t src = (lane & ~3u) + 1u;
+                    const float x0 = __shfl_sync(0xffffffffu, out[0][0], src), y0 = __shfl_sync(0xffffffffu, out[0][1], src);
+                    const float x1 = __shfl_sync(0xffffffffu, out[0][2], src), y1 = __shfl_sync(0xffffffffu, out[0][3], src);
+                    // t == 0: pair 0 = cols 0, 1 (own) and 2 (lane t = 1); t == 2: pair 1 = col 3 (lane t = 1) and cols 4, 5 (own)
+                    val[0][0] = t == 0u ? out[0][0] + A.dw1 * out[0][1] + A.dw2 * x0 : y0 + A.dw1 * out[0][0] + A.dw2 * out[0][1];
+                    val[1][0] = t == 0u ? out[0][2] + A.dw1 * out[0][3] + A.dw2 * x1 : y1 + A.dw1 * out[0][2] + A.dw2 * out[0][3];
+                    val[0][1] = val[1][1] = 0.f;
+                } else {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) val[h][j] = out[0][2 * h + j] + A.dw1 * out[1][2 * h + j] + A.dw2 * out[2][2 * h + j];
+                }
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) val[h][j] *= sxv[j];
+                const uint32_t row = ((I.tile0 + ti) << 4) + g;
+                if (GATEUP) {
+                    if (is_up) s_ex[ti][wslot][lane] = make_float4(val[0][0], val[0][1], val[1][0], val[1][1]);
+                    else { gatev[ti][0] = val[0][0]; gatev[ti][1] = val[0][1]; gatev[ti][2] = val[1][0]; gatev[ti][3] = val[1][1]; }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        if (ok[j]) {
+                            A.out[(size_t)prow[j] * A.out_stride + row] = val[0][j];
+                            A.out[(size_t)prow[j] * A.out_stride + row + 8u] = val[1][j];
+                        }
+                }
+            }
+        }
+        __syncthreads();             // the unit is done in every warp: up values are in s_ex, the digits may be replaced
+        if (GATEUP && !is_up) {
+            const uint32_t tiles = I.n / BPR;
+            for (uint32_t ti = 0; ti < tiles; ++ti) {
+                const float4 up = s_ex[ti][wslot][lane];
+                const float uv[4] = {up.x, up.y, up.z, up.w};
+                const uint32_t row = ((I.tile0 + ti) << 4) + g;
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+                    if (ok[j]) {
+                        const float g0 = gatev[ti][j], g1 = gatev[ti][2 + j];
+                        A.out[(size_t)prow[j] * A.out_stride + row] = (g0 / (1.0f + expf(-g0))) * uv[j];
+                        A.out[(size_t)prow[j] * A.out_stride + row + 8u] = (g1 / (1.0f + expf(-g1))) * uv[2 + j];
+                    }
+            }
+        }
+        base_slot = (base_slot + I.n) % NIB_STAGES;
+        prefetched = ahead && I.n != 0u;
+        cur = nxt; I = N; par ^= 1u;
+    }
+    nb_wait<0>();
+}
+
+static size_t nib_smem_bytes(uint32_t ncols) { return (size_t)NIB_WARPS * NIB_STAGES * NIB_STAGE + 24u * (size_t)(ncols + 32u); }
+
+// A.w0 / A.w1: nibble-layout expert matrices (gate and up, or down and nullptr); A.work: the unit counter of this launch
+// (zeroed by the grouping kernel); items are cut with at most 8 pairs. max_items bounds the number of work items.
+int launch_nib_experts(MmaArgs &A, uint32_t max_items, cudaStream_t s) {
+    const bool gateup = A.w1 != nullptr;
+    RC_REQUIRE(nib_shape_ok(A.nrows, A.ncols), "nibble experts: matrix %ux%u is not tileable", A.nrows, A.ncols);
+    RC_REQUIRE(A.work != nullptr && A.item_tok >= 1u && A.item_tok <= 8u, "nibble experts: work counter missing or items of %u pairs", A.item_tok);
+    A.dw1 = (float)(1u << act_digit_bits()); A.dw2 = A.dw1 * A.dw1;
+    static int sm_count = 0;
+    if (!sm_count) { int dev = 0; RC_CUDA(cudaGetDevice(&dev)); RC_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev)); }
+    const uint32_t bpr = A.ncols / 256u, tpw = bpr >= 8u ? 1u : 8u / bpr, unit_tiles = (gateup ? 4u : 8u) * tpw;
+    const uint64_t units = (uint64_t)max_items * ((A.nrows / 16u + unit_tiles - 1u) / unit_tiles);
+    const uint32_t grid = (uint32_t)(units < 2u * (uint64_t)sm_count ? (units ? units : 1u) : 2u * (uint64_t)sm_count);
+    const size_t smem = nib_smem_bytes(A.ncols);
+    prof_begin(gateup ? "moe_gateup" : "moe_down", s);
+#define RC_NIB_LAUNCH(GU, NC) do { \
+        RC_CUDA(cudaFuncSetAttribute(k_nib_experts<GU, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        RC_LAUNCH((k_nib_experts<GU, NC>), grid, NIB_WARPS * 32u, smem, s, A); } while (0)
+    if (gateup) {
+        if (A.ncols == 2048u) RC_NIB_LAUNCH(true, 2048u); else if (A.ncols == 1024u) RC_NIB_LAUNCH(true, 1024u);
+        else if (A.ncols == 512u) RC_NIB_LAUNCH(true, 512u); else RC_NIB_LAUNCH(true, 256u);
+    } else {
+        if (A.ncols == 2048u) RC_NIB_LAUNCH(false, 2048u); else if (A.ncols == 1024u) RC_NIB_LAUNCH(false, 1024u);
+        else if (A.ncols == 512u) RC_NIB_LAUNCH(false, 512u); else RC_NIB_LAUNCH(false, 256u);
+    }
+#undef RC_NIB_LAUNCH
+    prof_end(s);
+    RC_LAUNCHED();
+    return 1;
+}
+
+}  // namespace rc
+
+using namespace rc;
+
+// Host-buffer check of the layout: raw IQ2_XXS GGUF rows -> planar -> nibble layout -> fp32. Must equal
+// redcuda_quant_dequant_rows (and rl_quant_dequant_row) bit for bit.
+extern "C" int redcuda_nib_dequant_rows(const uint8_t *rows, uint32_t nrows, uint32_t ncols, float *out) {
+    if (!require_device() || !require_books(RC_IQ2_XXS)) return 0;
+    RC_REQUIRE(rows && out, "nib dequant: null argument");
+    RC_REQUIRE(nib_shape_ok(nrows, ncols), "nib dequant: matrix %ux%u is not tileable (16 rows, 256/512/1024/2048 columns)", nrows, ncols);
+    const uint64_t bytes = rc_matrix_bytes(RC_IQ2_XXS, nrows, ncols), nb = (uint64_t)nrows * (ncols / 256u);
+    DevMem raw, planar, nib, o;
+    if (!raw.alloc(bytes) || !planar.alloc(bytes) || !nib.alloc(nib_matrix_bytes(nrows, ncols)) || !o.alloc((size_t)nrows * ncols * 4u)) return 0;
+    cudaStream_t s = 0;
+    if (!upload_matrix(RC_IQ2_XXS, nrows, ncols, rows, false, planar.as<uint8_t>(), raw.as<uint8_t>(), s)) return 0;
+    if (!launch_nib_repack(planar.as<uint8_t>(), nrows, ncols, nib.as<uint8_t>(), s)) return 0;
+    const uint64_t total = nb * 32u;
+    RC_LAUNCH((k_nib_dequant), (unsigned)((total + 255u) / 256u < 4096u ? (total + 255u) / 256u : 4096u), 256, 0, s, nib.as<uint8_t>(), nb, nrows, ncols / 256u, o.as<float>());
+    RC_LAUNCHED();
+    RC_CUDA(cudaMemcpyAsync(out, o.p, (size_t)nrows * ncols * 4u, cudaMemcpyDeviceToHost, s));
+    RC_CUDA(cudaStreamSynchronize(s));
+    return 1;
+}

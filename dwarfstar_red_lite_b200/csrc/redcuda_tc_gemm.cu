@@ -7,6 +7,12 @@
 // rounded to one 16-bit value: both are split into two fp16 digits, v * 2^e = hi + lo (|error| <= 2^-22 |v|), and
 // three products are accumulated in fp32 in tensor memory: hi*hi + hi*lo + lo*hi. The power-of-two scales (per row
 // tile for the weights, per token for the activations) keep hi in the normal fp16 range and are undone in the epilogue.
+// The tensor core adds into its fp32 accumulator without rounding to nearest, so a long chain of accumulations drifts
+// (measured: 2e-5 of the result over 2048 columns, a hundred times the error of an fp32 sum). Two measures keep the
+// result at fp32 accuracy: the small cross products (hi*lo, lo*hi) have an accumulator of their own, so their
+// truncation is relative to their own size, and the accumulators only ever cover one 256-column block (16 MMAs for
+// hi*hi): they are double-buffered in tensor memory, read back with tcgen05.ld while the next block multiplies, and
+// summed over the blocks in fp32 registers with ordinary rounding.
 //
 // One CTA = 128 weight rows (MMA M) x TN tokens (MMA N) x all columns, K in stages of 64:
 //   all 8 warps   stage the raw quant blocks of the 128 rows one 256-column block ahead (cp.async, 16-byte pieces, the
@@ -15,7 +21,9 @@
 //                 layout, no swizzle) and copy the stage's activation digits (laid out for the MMA by k_tc_prep_x)
 //   one thread    issues 4 k-steps x 3 tcgen05.mma (128 x TN x 16, kind::f16, fp32 accumulate) and a tcgen05.commit
 //                 on the stage buffer's mbarrier; the MMAs of a stage run while the warps decode the next one
-//   epilogue      tcgen05.ld of the accumulator (lane = weight row, column = token), scaling, coalesced stores
+//   every block   tcgen05.ld of the finished block's two accumulators (lane = weight row, column = token) into fp32
+//                 register sums, one 256-column block behind the MMAs
+//   epilogue      scaling, stores
 // Every wait on an mbarrier is bounded; on a timeout the kernel raises a flag, frees its tensor memory and returns.
 #define RC_PDL_DEFAULT 0
 #include "redcuda_common.cuh"
@@ -237,8 +245,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr uint32_t NB = TcCfg<TN>::NB;
     constexpr uint32_t B_DIGIT = (uint32_t)TN * TC_KS * 2u, A_BUF = 2u * TC_A_DIGIT, B_BUF = 2u * B_DIGIT;
-    constexpr uint32_t TMEM_COLS = TN < 32 ? 32u : (uint32_t)TN;
+    constexpr uint32_t TMEM_COLS = 4u * (uint32_t)TN;     // two blocks in flight x (hi*hi accumulator, cross-product accumulator)
+    static_assert(TMEM_COLS >= 32u && TMEM_COLS <= 512u && (TMEM_COLS & (TMEM_COLS - 1u)) == 0u, "tensor-memory allocation must be a power of two in [32, 512]");
     __shared__ __align__(8) uint64_t mbar[2];        // MMAs that read A buffer b (and the B buffer of the same stage) are done
+    __shared__ __align__(8) uint64_t accfull[2];     // every MMA of a 256-column block has landed in accumulator pair b
     __shared__ __align__(8) uint64_t bfull[NB];      // the activation digits of a stage have landed
     __shared__ uint32_t tmem_slot;
     __shared__ volatile uint32_t fail;      // a bounded wait ran out: no more MMAs are issued, later waits are skipped
@@ -267,6 +277,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
         fail = 0u;
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&mbar[0])));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&mbar[1])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&accfull[0])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&accfull[1])));
         for (uint32_t j = 0; j < NB; ++j) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&bfull[j])));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -304,6 +316,32 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
     const float w_scale = exp2f((float)we), w_inv = exp2f((float)-we);
     const uint32_t idesc = tc_idesc((uint32_t)TN);
 
+    // fp32 sums over the 256-column blocks: warp w owns TMEM lanes 32*(w%4)..+31 (its quarter) and PER token columns
+    constexpr uint32_t PER = (uint32_t)TN / (TC_WARPS / 4u);              // columns per warp: 8, 16 or 32
+    const uint32_t qlane = (warp & 3u) * 32u, c_begin = (warp >> 2) * PER;
+    float acc[PER];
+#pragma unroll
+    for (uint32_t j = 0; j < PER; ++j) acc[j] = 0.f;
+    // adds block `blk`'s accumulators (pair blk & 1) to the register sums; every thread of the CTA calls it
+    auto drain = [&](uint32_t blk) {
+        if (fail) return;
+        if (!mbar_wait(smem_u32(&accfull[blk & 1u]), (blk >> 1) & 1u)) { fail = 1u; return; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t base = tmem + (qlane << 16) + (blk & 1u) * 2u * (uint32_t)TN + c_begin;
+#pragma unroll
+        for (uint32_t c = 0; c < PER; c += 8u) {
+            uint32_t m[8], x[8];
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                         : "=r"(m[0]), "=r"(m[1]), "=r"(m[2]), "=r"(m[3]), "=r"(m[4]), "=r"(m[5]), "=r"(m[6]), "=r"(m[7]) : "r"(base + c));
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                         : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]), "=r"(x[4]), "=r"(x[5]), "=r"(x[6]), "=r"(x[7]) : "r"(base + (uint32_t)TN + c));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[c + j] += __uint_as_float(m[j]) + __uint_as_float(x[j]);
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");     // the pair is overwritten two blocks later, after barriers
+    };
+
     for (uint32_t s = 0; s < nstage; ++s) {
         const uint32_t b = s & 1u;
         uint8_t *abuf = a_base + b * A_BUF;
@@ -321,6 +359,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
             if (!mbar_wait(smem_u32(&mbar[b]), ((s >> 1) - 1u) & 1u)) fail = 1u;
         }
         if (tid == 0 && s + NB - 2u < nstage && !fail) issue_b(s + NB - 2u);
+        if ((s & 3u) == 1u && s >= 4u) drain((s >> 2) - 1u);       // the previous block's MMAs were issued more than a stage ago
         // ---- weights of the stage -> fp16 digit tiles
         {
             const uint32_t g8_0 = ((s * TC_KS) & 255u) >> 3, rows_live = J.nrows - row0 < TC_M ? J.nrows - row0 : TC_M;
@@ -342,40 +381,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
                 for (uint32_t kk = 0; kk < TC_KS / 16u; ++kk) {
                     const uint64_t dah = tc_smem_desc(a_hi + 2u * kk * A_LBO, A_LBO, SBO), dal = tc_smem_desc(a_lo + 2u * kk * A_LBO, A_LBO, SBO);
                     const uint64_t dbh = tc_smem_desc(b_hi + 2u * kk * B_LBO, B_LBO, SBO), dbl = tc_smem_desc(b_lo + 2u * kk * B_LBO, B_LBO, SBO);
-                    tc_mma(tmem, dah, dbh, idesc, (s | kk) ? 1u : 0u);
-                    tc_mma(tmem, dah, dbl, idesc, 1u);
-                    tc_mma(tmem, dal, dbh, idesc, 1u);
+                    const uint32_t d_main = tmem + ((s >> 2) & 1u) * 2u * (uint32_t)TN, d_cross = d_main + (uint32_t)TN;
+                    const uint32_t first = ((s & 3u) | kk) ? 1u : 0u;       // a block's first MMA overwrites its accumulators
+                    tc_mma(d_main, dah, dbh, idesc, first);
+                    tc_mma(d_cross, dah, dbl, idesc, first);
+                    tc_mma(d_cross, dal, dbh, idesc, 1u);
                 }
                 tc_commit(smem_u32(&mbar[b]));
+                if ((s & 3u) == 3u) tc_commit(smem_u32(&accfull[(s >> 2) & 1u]));
             }
         }
     }
-    // ---- all MMAs done? (the last commit of each buffer covers everything issued before it). A timeout of thread 0
-    // inside the loop left a commit missing: the flag is read after a barrier and the waits below are bounded as well.
+    // ---- the last block (a timeout of thread 0 inside the loop left a commit missing: the flag is read after a barrier
+    // and the wait inside drain is bounded as well)
+    __syncthreads();
+    drain((nstage >> 2) - 1u);
     __syncthreads();
     if (!fail) {
-        const uint32_t last = nstage - 1u;
-        if (!mbar_wait(smem_u32(&mbar[last & 1u]), (last >> 1) & 1u)) fail = 1u;
-        if (nstage >= 2u && !mbar_wait(smem_u32(&mbar[(last - 1u) & 1u]), ((last - 1u) >> 1) & 1u)) fail = 1u;
-    }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (!fail) {
-        // warp w reads TMEM lanes 32*(w%4)..+31 (its quarter); the warps of a quarter split the columns
-        const uint32_t q = warp & 3u, row = row0 + q * 32u + lane;
-        constexpr uint32_t PER = (uint32_t)TN / (TC_WARPS / 4u);          // columns per warp: 8, 16 or 32
-        const uint32_t c_begin = (warp >> 2) * PER;
-        for (uint32_t c = c_begin; c < c_begin + PER; c += 8u) {
-            uint32_t v[8];
-            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                         : "r"(tmem + ((q * 32u) << 16) + c));
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const uint32_t row = row0 + qlane + lane;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const uint32_t t = t0 + c + j;
-                if (t < A.ntok && row < J.nrows) J.out[(size_t)t * J.out_stride + row] = __uint_as_float(v[j]) * w_inv * A.x_inv[t];
-            }
+        for (uint32_t j = 0; j < PER; ++j) {
+            const uint32_t t = t0 + c_begin + j;
+            if (t < A.ntok && row < J.nrows) J.out[(size_t)t * J.out_stride + row] = acc[j] * w_inv * A.x_inv[t];
         }
     } else if (tid == 0) atomicExch(A.err, 1u);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

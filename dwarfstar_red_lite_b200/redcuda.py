@@ -15,7 +15,7 @@ u8p, f32p, u32p = C.POINTER(C.c_uint8), C.POINTER(C.c_float), C.POINTER(C.c_uint
 
 EXPORTS = [
     "redcuda_abi_version", "redcuda_last_error", "redcuda_device_count", "redcuda_set_device", "redcuda_set_codebooks",
-    "redcuda_quant_dequant_rows", "redcuda_quant_matvec", "redcuda_quant_matmul_tc", "redcuda_router_select_softmax_topk", "redcuda_deltanet_step",
+    "redcuda_quant_dequant_rows", "redcuda_nib_dequant_rows", "redcuda_quant_matvec", "redcuda_quant_matmul_tc", "redcuda_router_select_softmax_topk", "redcuda_deltanet_step",
     "redcuda_deltanet_step_noalloc",
     "redcuda_moe_create", "redcuda_moe_destroy", "redcuda_moe_resident_bytes", "redcuda_moe_forward",
     "redcuda_moe_forward_device", "redcuda_moe_route_device", "redcuda_moe_experts_device", "redcuda_moe_shared_device",
@@ -132,6 +132,16 @@ def quant_dequant_rows(ggml_type: int, rows: np.ndarray, ncols: int) -> np.ndarr
     nrows = rows.size // max(1, _row_bytes(ggml_type, ncols))
     out = np.empty((nrows, ncols), np.float32)
     _check(lib().redcuda_quant_dequant_rows(ggml_type, rows.ctypes.data, nrows, ncols, out.ctypes.data))
+    return out
+
+
+def nib_dequant_rows(rows: np.ndarray, ncols: int) -> np.ndarray:
+    """IQ2_XXS rows dequantised through the nibble layout of the routed experts (must equal quant_dequant_rows(16, ...))."""
+    _ensure_books()
+    rows = np.ascontiguousarray(rows).view(np.uint8)
+    nrows = rows.size // _row_bytes(16, ncols)
+    out = np.empty((nrows, ncols), np.float32)
+    _check(lib().redcuda_nib_dequant_rows(rows.ctypes.data, nrows, ncols, out.ctypes.data))
     return out
 
 

@@ -49,6 +49,12 @@ int redcuda_set_codebooks(const uint8_t *iq2xxs_grid, uint32_t iq2xxs_bytes, con
 /* rl_quant_dequant_row (native/redlite_native_quant_cpu.c:155-196) for nrows rows at once: out[nrows][ncols]. */
 int redcuda_quant_dequant_rows(uint32_t ggml_type, const uint8_t *rows, uint32_t nrows, uint32_t ncols, float *out);
 
+/* The same values through the layout the routed IQ2_XXS experts are kept in (4-bit magnitude/sign codes, byte scales;
+ * dwarfstar_red_lite_b200/csrc/redcuda_moe_nib.cu): raw IQ2_XXS GGUF rows -> that layout -> fp32. The re-coding must not
+ * change a single value: out equals redcuda_quant_dequant_rows(16, ...) and rl_quant_dequant_row
+ * (native/redlite_native_quant_cpu.c:166-191) bit for bit. nrows a multiple of 16, ncols one of 256 / 512 / 1024 / 2048. */
+int redcuda_nib_dequant_rows(const uint8_t *rows, uint32_t nrows, uint32_t ncols, float *out);
+
 /* rl_quant_row_dot over every row and ntok input vectors (native/redlite_native_quant_cpu.c:198-280; the row-parallel
  * matvec of native/redlite_native_engine_cpu.c:54-92): out[t][r] = dot(W[r], x[t]). x[ntok][ncols], out[ntok][nrows]. */
 int redcuda_quant_matvec(uint32_t ggml_type, const uint8_t *w, uint32_t nrows, uint32_t ncols,

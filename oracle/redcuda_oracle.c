@@ -481,6 +481,7 @@ struct ro_state {
     uint32_t position, n_rec, n_att;
     float *conv, *rec, *kcache, *vcache, *layer_out, *final_norm;
     uint32_t *router_ids;
+    float *router_logits;       /* [layer][n_expert] of the last step: lets a test measure the margin of a selection */
     size_t conv_count, rec_count, kv_layer;
 };
 
@@ -499,12 +500,13 @@ ro_state *ro_state_create(const ro_model *m) {
     s->layer_out = (float *)calloc((size_t)m->n_layer * m->hidden, sizeof(float));
     s->final_norm = (float *)calloc(m->hidden, sizeof(float));
     s->router_ids = (uint32_t *)calloc((size_t)m->n_layer * RO_MAX_TOPK, sizeof(uint32_t));
-    if (!s->conv || !s->rec || !s->kcache || !s->vcache || !s->layer_out || !s->final_norm || !s->router_ids) { ro_state_free(s); return NULL; }
+    s->router_logits = (float *)calloc((size_t)m->n_layer * m->n_expert, sizeof(float));
+    if (!s->conv || !s->rec || !s->kcache || !s->vcache || !s->layer_out || !s->final_norm || !s->router_ids || !s->router_logits) { ro_state_free(s); return NULL; }
     return s;
 }
 void ro_state_free(ro_state *s) {
     if (!s) return;
-    free(s->conv); free(s->rec); free(s->kcache); free(s->vcache); free(s->layer_out); free(s->final_norm); free(s->router_ids); free(s);
+    free(s->conv); free(s->rec); free(s->kcache); free(s->vcache); free(s->layer_out); free(s->final_norm); free(s->router_ids); free(s->router_logits); free(s);
 }
 void ro_state_reset(ro_state *s) {
     s->position = 0;
@@ -517,6 +519,7 @@ uint32_t ro_state_position(const ro_state *s) { return s->position; }
 const float *ro_state_layer_out(const ro_state *s, uint32_t layer) { return s->layer_out + (size_t)layer * s->m->hidden; }
 const uint32_t *ro_state_router_ids(const ro_state *s, uint32_t layer) { return s->router_ids + (size_t)layer * RO_MAX_TOPK; }
 const float *ro_state_final_norm(const ro_state *s) { return s->final_norm; }
+const float *ro_state_router_logits(const ro_state *s, uint32_t layer) { return s->router_logits + (size_t)layer * s->m->n_expert; }
 float *ro_state_rec(ro_state *s, uint32_t i) { return s->rec + s->rec_count * i; }
 float *ro_state_conv(ro_state *s, uint32_t i) { return s->conv + s->conv_count * i; }
 
@@ -641,7 +644,7 @@ int ro_model_step(const ro_model *m, ro_state *s, uint32_t token, float *logits,
         M.router = (const float *)L->router.data; M.gate_all = L->gate_exps.data; M.up_all = L->up_exps.data; M.down_all = L->down_exps.data;
         M.sh_gate_inp = (const float *)L->sh_gate_inp.data; M.sh_gate = L->sh_gate.data; M.sh_up = L->sh_up.data; M.sh_down = L->sh_down.data;
         if (L->sh_up.type != M.type_sh || L->sh_down.type != M.type_sh || L->up_exps.type != M.type_gu) { ok = 0; break; }
-        ok = ro_moe_ffn(&M, normed, ffn_out, s->router_ids + (size_t)l * RO_MAX_TOPK, NULL, NULL, threads);
+        ok = ro_moe_ffn(&M, normed, ffn_out, s->router_ids + (size_t)l * RO_MAX_TOPK, NULL, s->router_logits + (size_t)l * m->n_expert, threads);
         if (!ok) break;
         for (uint32_t i = 0; i < hidden; ++i) x[i] = resid[i] + ffn_out[i];
         memcpy(s->layer_out + (size_t)l * hidden, x, sizeof(float) * hidden);

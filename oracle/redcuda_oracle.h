@@ -107,6 +107,7 @@ uint32_t ro_state_position(const ro_state *s);
 const float *ro_state_layer_out(const ro_state *s, uint32_t layer);
 const uint32_t *ro_state_router_ids(const ro_state *s, uint32_t layer);
 const float *ro_state_final_norm(const ro_state *s);
+const float *ro_state_router_logits(const ro_state *s, uint32_t layer);   /* [n_expert] router logits of the last step */
 float *ro_state_rec(ro_state *s, uint32_t recurrent_index);
 float *ro_state_conv(ro_state *s, uint32_t recurrent_index);
 /* one token; logits (vocab floats) may be NULL */

@@ -90,6 +90,8 @@ def own():
     lib.ro_state_router_ids.argtypes = [C.c_void_p, C.c_uint32]
     lib.ro_state_final_norm.restype = f32p
     lib.ro_state_final_norm.argtypes = [C.c_void_p]
+    lib.ro_state_router_logits.restype = f32p
+    lib.ro_state_router_logits.argtypes = [C.c_void_p, C.c_uint32]
     lib.ro_state_rec.restype = f32p
     lib.ro_state_rec.argtypes = [C.c_void_p, C.c_uint32]
     lib.ro_state_conv.restype = f32p
@@ -307,6 +309,9 @@ class OracleModel:
 
     def final_norm(self) -> np.ndarray:
         return np.ctypeslib.as_array(self.lib.ro_state_final_norm(self.state), (self.sm.dims.hidden,)).copy()
+
+    def router_logits(self, l: int) -> np.ndarray:
+        return np.ctypeslib.as_array(self.lib.ro_state_router_logits(self.state, l), (self.sm.dims.n_expert,)).copy()
 
 
 # ---------------------------------------------------------------------------------------------- reference engine

@@ -37,6 +37,22 @@ def test_dequant_bit_exact(t):
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (t, ncols)
 
 
+@pytest.mark.parametrize("nrows,ncols", [(16, 256), (48, 512), (32, 2048)])
+def test_nibble_layout_keeps_every_value(nrows, ncols):
+    """The routed experts are re-coded at load (4-bit magnitude/sign codes, byte scales); decoding that layout must give
+    the oracle's dequantised values bit for bit, subnormal and extreme block scales included."""
+    rng = np.random.default_rng(300 + ncols)
+    rows = _rows(rng, synth.IQ2_XXS, nrows, ncols).copy()
+    rb = rows.reshape(nrows, ncols // 256, 66)
+    rb[0, 0, 0:2] = np.frombuffer(np.float16(6e-8).tobytes(), np.uint8)       # fp16-subnormal d
+    rb[1, 0, 0:2] = np.frombuffer(np.float16(-3.5).tobytes(), np.uint8)       # negative d
+    rb[2, 0, 62:66] = 0xFF                                                    # scale 15, every sign bit set
+    rb[3, 0, 62:66] = 0x00
+    got = rc.nib_dequant_rows(rows, ncols)
+    want = ol.dequant_rows(synth.IQ2_XXS, rows, ncols)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
 def test_dequant_subnormal_block_scale():
     # Q6_K block whose fp16 d is the smallest subnormal (reference KAT, native/redlite_native_shared_exec_offline_test.c:32-44)
     blk = np.zeros((1, 210), np.uint8)
@@ -120,6 +136,31 @@ def test_router_topk_exact_incl_ties():
     assert list(ids[0]) == [3, 2] and abs(w[0, 0] - 0.7310585786) < 1e-6
     ids, _ = rc.router_select_softmax_topk(np.array([[1, 1, 0, 0]], np.float32), 2)
     assert list(ids[0]) == [0, 1]
+
+
+def test_non_finite_router_logits_are_an_error_not_an_address():
+    """NaN logits give no maximum, so no expert id: the reference fails with "invalid router softmax denominator"
+    (native/redlite_native_router_exec.c:135). Here the kernels clamp the id they could not form (nothing is read
+    out of bounds) and the synchronous entry points report the failure; the next call works again."""
+    logits = np.random.default_rng(2).normal(0, 1, size=(3, 64)).astype(np.float32)
+    logits[1, :] = np.nan
+    with pytest.raises(rc.RedcudaError, match="router softmax"):
+        rc.router_select_softmax_topk(logits, 4)
+    ids, _ = rc.router_select_softmax_topk(logits[:1], 4)
+    assert np.array_equal(ids[0], ol.router_select(logits[0], 4)[0])
+    dims = synth.MoeDims(hidden=512, n_expert=32, top_k=4, ffn=256, ffn_sh=256)
+    layer = synth.moe_layer(5, dims, expert_scale=0.5)
+    x = np.random.default_rng(3).normal(0, 1, size=(2, dims.hidden)).astype(np.float32)
+    bad = np.full((2, dims.n_expert), np.nan, np.float32)
+    m = rc.MoeLayer(layer, max_tokens=2)
+    try:
+        with pytest.raises(rc.RedcudaError, match="router softmax"):
+            m.forward(x, logits_in=bad)
+        out = m.forward(x)                       # the layer is usable afterwards
+        ro = ol.moe_ffn(layer, x[0], threads=4)[0]
+        assert np.max(np.abs(out[0] - ro)) <= REL_OUT * np.max(np.abs(ro))
+    finally:
+        m.close()
 
 
 def _check_moe(layer, x, logits_in=None, threads=8):
