@@ -32,7 +32,7 @@ bool prof_active();
 // them only in the failing case, and the host reads them after its next synchronisation without a copy. The kernels
 // clamp the offending index to a valid one, so nothing is read out of bounds; the synchronous entry points turn a set
 // word into an error, as the reference's CPU path does ("invalid router softmax denominator").
-enum StatusWord : uint32_t { ST_ROUTER_NONFINITE = 0, ST_TOKEN_RANGE = 1, ST_EXPERT_RANGE = 2, ST_WORDS = 4 };
+enum StatusWord : uint32_t { ST_ROUTER_NONFINITE = 0, ST_TOKEN_RANGE = 1, ST_EXPERT_RANGE = 2, ST_TIMEOUT = 3, ST_WORDS = 4 };
 uint32_t *status_words();          // device-visible pointer to ST_WORDS words (nullptr when the allocation failed)
 // Reads and clears the words; returns 0 when none was set, else writes a message with set_error and returns 1.
 int status_failed();

@@ -63,12 +63,13 @@ uint32_t *status_words() {
 int status_failed() {
     volatile uint32_t *st = g_status;
     if (!st) return 0;
-    const uint32_t a = st[ST_ROUTER_NONFINITE], b = st[ST_TOKEN_RANGE], c = st[ST_EXPERT_RANGE];
-    if (!(a | b | c)) return 0;
-    st[ST_ROUTER_NONFINITE] = 0; st[ST_TOKEN_RANGE] = 0; st[ST_EXPERT_RANGE] = 0;
+    const uint32_t a = st[ST_ROUTER_NONFINITE], b = st[ST_TOKEN_RANGE], c = st[ST_EXPERT_RANGE], d = st[ST_TIMEOUT];
+    if (!(a | b | c | d)) return 0;
+    st[ST_ROUTER_NONFINITE] = 0; st[ST_TOKEN_RANGE] = 0; st[ST_EXPERT_RANGE] = 0; st[ST_TIMEOUT] = 0;
     if (a) set_error("invalid router softmax denominator (non-finite router logits)");
     else if (b) set_error("token id out of range on the device (non-finite logits in the argmax?)");
-    else set_error("an expert id outside this shard reached an expert kernel");
+    else if (c) set_error("an expert id outside this shard reached an expert kernel");
+    else set_error("an expert kernel gave up waiting for a weight copy (bounded wait ran out); its outputs are incomplete");
     return 1;
 }
 

@@ -449,9 +449,10 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
     }
 
     {   // RC_EXPERT_FMT: "nib4" keeps IQ2_XXS experts in the nibble layout (table-free decode, 2.09x the bytes), "iq2" in the
-        // planar GGUF bytes (the default)
+        // planar GGUF bytes; unset = nib4 where the shapes allow it (measured on the 64-token batch: gate/up 105 -> 69 us,
+        // down 74 -> 39 us per layer)
         const char *fmt = getenv("RC_EXPERT_FMT");
-        const bool want = fmt && fmt[0] == 'n';
+        const bool want = !(fmt && fmt[0] == 'i');
         m->nib = want && d.type_gu == RC_IQ2_XXS && d.type_down == RC_IQ2_XXS && nib_shape_ok(d.ffn, d.hidden) && nib_shape_ok(d.hidden, d.ffn);
     }
     m->gu_bytes = m->nib ? nib_matrix_bytes(d.ffn, d.hidden) : rc_matrix_bytes(d.type_gu, d.ffn, d.hidden);

@@ -131,10 +131,21 @@ __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-__device__ __forceinline__ void mma_s8_k32(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+// The accumulator input is a quad of registers that hold zero for the whole kernel (zero_quad): given a literal 0 the
+// compiler writes four moves in front of every MMA.
+__device__ __forceinline__ void mma_s8_k32(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1, const int (&z)[4]) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
                  : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z[0]), "r"(z[1]), "r"(z[2]), "r"(z[3]));
+}
+__device__ __forceinline__ void zero_quad(int (&z)[4]) {
+    asm volatile("mov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\tmov.b32 %2, 0;\n\tmov.b32 %3, 0;" : "=r"(z[0]), "=r"(z[1]), "=r"(z[2]), "=r"(z[3]));
+}
+// byte permute with the selector as it is (the intrinsic first masks bit 3 of every selector nibble: one more instruction)
+__device__ __forceinline__ uint32_t prmt_raw(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
 }
 
 // shared-memory geometry
@@ -164,6 +175,8 @@ template <int NMAT, int NTILE, int NUSED = 0, uint32_t GREP = MMA_GREP>
 __device__ __forceinline__ void mma_unit(const uint8_t *stage, const float (&dsc)[NMAT][2], const int8_t *Bs, uint32_t bpitch, uint32_t kbase,
                                          const uint8_t *lutg, const uint8_t *luts, uint32_t lane, uint32_t ntiles, float (&out)[NMAT][NTILE][4]) {
     if (NUSED > 0) ntiles = NUSED;
+    int z[4];
+    zero_quad(z);
     const uint32_t g = lane >> 2, t = lane & 3u, rep8 = (lane & (GREP - 1u)) * 8u, rep16 = (lane & 7u) * 16u;
     const uint32_t sel = 0x4440u + t, sh7 = 7u * t;
     int blk[NMAT][NTILE][4];
@@ -180,7 +193,7 @@ __device__ __forceinline__ void mma_unit(const uint8_t *stage, const float (&dsc
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const uint2 q = *reinterpret_cast<const uint2 *>(stage + (uint32_t)(m * 16 + h * 8 + g) * MMA_ROW_PITCH + (uint32_t)kg * 8u);
-                const uint32_t gi = __byte_perm(q.x, 0u, sel);
+                const uint32_t gi = prmt_raw(q.x, 0u, sel);
                 const uint32_t s7 = (q.y >> sh7) & 127u;
                 const uint2 P = *reinterpret_cast<const uint2 *>(lutg + gi * (GREP * 8u) + rep8);
                 if (GREP == 16u) {      // 16 copies of the 8-byte sign mask; the +1 carry term is recomputed from it
@@ -202,7 +215,7 @@ __device__ __forceinline__ void mma_unit(const uint8_t *stage, const float (&dsc
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
                 int d[4];
-                mma_s8_k32(d, a[m][0], a[m][1], a[m][2], a[m][3], bf.x, bf.y);
+                mma_s8_k32(d, a[m][0], a[m][1], a[m][2], a[m][3], bf.x, bf.y, z);
                 blk[m][n][0] += sc[m][0] * d[0]; blk[m][n][1] += sc[m][0] * d[1];
                 blk[m][n][2] += sc[m][1] * d[2]; blk[m][n][3] += sc[m][1] * d[3];
             }

@@ -9,20 +9,23 @@
 // (redcuda_nib_dequant_rows against rl_quant_dequant_row, native/redlite_native_quant_cpu.c:166-191). The price is bytes:
 // 138 per 256 weights instead of 66, i.e. 2.09x the HBM footprint and traffic of the routed experts.
 //
-// Layout of one expert matrix [nrows][ncols], bpr = ncols / 256 blocks per row, nb = nrows * bpr:
-//   codes  @0         [row][block][t 0..3][kg 0..7] u32    word (t, kg) = the 8 weights 32*kg + 8*t .. +7 of the block,
-//                                                          weight j in bits 4j+3..4j (a lane's 8 words are 32 contiguous bytes)
-//   scales @nb * 128  [block][row][kg 0..7]         u8     2 * s + 1, s the 4-bit scale of the 32-weight group
-//   d      @nb * 136  [block][row]                  fp16   block scale
-// (block-major scale planes: the 16 rows of a tile are contiguous, one 128-byte and one 32-byte copy per tile and block).
-//
+// Layout of one expert matrix [nrows][ncols], bpr = ncols / 256 blocks per row: one contiguous RECORD of 2208 bytes per
+// (16-row tile, 256-column block), records ordered [tile][block], so that a warp fetches everything it needs for one
+// block of its tile with a single bulk copy:
+//   codes  @0     16 rows x 128 B; logical byte 32 t + 4 kg of a row = u32 word (t, kg) = the 8 weights 32 kg + 8 t .. +7
+//                 of the block, weight j in bits 4j+3..4j (a lane's 8 words are 32 contiguous bytes). The 16-byte
+//                 pieces of odd rows are stored pairwise swapped (piece p at p ^ 1): a record lands in shared memory
+//                 as it is, and with the swap the 16-byte reads of a quarter warp hit eight different bank groups
+//   scales @2048  16 rows x 8 B, byte kg = 2 s + 1, s the 4-bit scale of the 32-weight group
+//   d      @2176  16 fp16 block scales
 // Arithmetic is the integer tensor-core scheme of redcuda_moe_mma.cu (mma.sync m16n8k32 s8, activations as three
 // balanced digits per value, s32 sums per 32-weight group scaled by the integer 2s+1, fp32 scaling by d/8 per block).
 //
 // Kernel: persistent CTAs of 8 warps, two per SM. A unit of work = one work item (<= 8 pairs of one expert, cut by
 // k_group_pairs) x a block of rows; CTAs draw units from an atomic counter, so the routing skew never leaves SMs idle
 // and nothing is set up per unit except the item's activation digits in shared memory. Every warp streams its 16-row
-// tiles through a private cp.async ring (three 256-column blocks in flight) that runs on across unit boundaries.
+// tiles through a private ring of three records (one cp.async.bulk and one mbarrier each; the ring runs on across unit
+// boundaries). Waits on the mbarriers are bounded: a warp that gives up raises the status word and the CTA winds down.
 // Column layout of the digits: items of one or two pairs pack (pair, digit) into one 8-column tile (cols 3*pair+digit);
 // larger items use one tile per digit (col = 8*digit + pair), so a lane holds all three digits of its two pairs and the
 // epilogue needs no exchange.
@@ -37,6 +40,13 @@
 namespace rc {
 
 constexpr uint32_t NIB_BLOCK_BYTES = 138u;
+// one record = one 16-row tile x one 256-column block
+constexpr uint32_t NIB_SC_OFF = 2048u, NIB_D_OFF = 2176u, NIB_REC = 2208u;
+// byte offset of code word (t, kg) of row rr inside a record (16-byte pieces of odd rows pairwise swapped)
+__host__ __device__ __forceinline__ uint32_t nib_code_off(uint32_t rr, uint32_t t, uint32_t kg) {
+    const uint32_t piece = (2u * t + (kg >> 2)) ^ (rr & 1u);
+    return rr * 128u + piece * 16u + (kg & 3u) * 4u;
+}
 
 uint64_t nib_matrix_bytes(uint32_t nrows, uint32_t ncols) { return (uint64_t)nrows * (ncols / 256u) * NIB_BLOCK_BYTES; }
 bool nib_shape_ok(uint32_t nrows, uint32_t ncols) { return nrows % 16u == 0 && (ncols == 256u || ncols == 512u || ncols == 1024u || ncols == 2048u); }
@@ -59,10 +69,12 @@ __global__ void k_nib_repack(const uint8_t *__restrict__ planar, uint64_t nb, ui
             const uint32_t m = gv[j] == 0x19u ? 1u : gv[j] == 0x2bu ? 2u : 0u;
             word |= (m | (((s8 >> j) & 1u) << 2)) << (4u * j);
         }
-        *reinterpret_cast<uint32_t *>(dst + b * 128u + t * 32u + kg * 4u) = word;
+        uint8_t *rec = dst + ((uint64_t)(row >> 4) * bpr + blk) * NIB_REC;
+        const uint32_t rr = row & 15u;
+        *reinterpret_cast<uint32_t *>(rec + nib_code_off(rr, t, kg)) = word;
         if (t == 0u) {
-            dst[nb * 128u + ((uint64_t)blk * nrows + row) * 8u + kg] = (uint8_t)(2u * (auxs >> 28) + 1u);
-            if (kg == 0u) *reinterpret_cast<unsigned short *>(dst + nb * 136u + ((uint64_t)blk * nrows + row) * 2u) = *reinterpret_cast<const unsigned short *>(planar + rc_iq2_d(nb) + b * 2u);
+            rec[NIB_SC_OFF + rr * 8u + kg] = (uint8_t)(2u * (auxs >> 28) + 1u);
+            if (kg == 0u) *reinterpret_cast<unsigned short *>(rec + NIB_D_OFF + rr * 2u) = *reinterpret_cast<const unsigned short *>(planar + rc_iq2_d(nb) + b * 2u);
         }
     }
 }
@@ -87,9 +99,11 @@ __global__ void k_nib_dequant(const uint8_t *__restrict__ nib, uint64_t nb, uint
         const uint64_t b = i >> 5;
         const uint32_t kg = ((uint32_t)i >> 2) & 7u, t = (uint32_t)i & 3u;
         const uint32_t row = (uint32_t)(b / bpr), blk = (uint32_t)(b - (uint64_t)row * bpr);
-        const uint32_t word = *reinterpret_cast<const uint32_t *>(nib + b * 128u + t * 32u + kg * 4u);
-        const uint32_t scb = nib[nb * 128u + ((uint64_t)blk * nrows + row) * 8u + kg];
-        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(nib + nb * 136u + ((uint64_t)blk * nrows + row) * 2u)));
+        const uint8_t *rec = nib + ((uint64_t)(row >> 4) * bpr + blk) * NIB_REC;
+        const uint32_t rr = row & 15u;
+        const uint32_t word = *reinterpret_cast<const uint32_t *>(rec + nib_code_off(rr, t, kg));
+        const uint32_t scb = rec[NIB_SC_OFF + rr * 8u + kg];
+        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(rec + NIB_D_OFF + rr * 2u)));
         const float db = d * (0.5f + (float)((scb - 1u) >> 1)) * 0.25f;
         float *o = out + ((uint64_t)row * bpr + blk) * 256u + kg * 32u + t * 8u;
 #pragma unroll
@@ -102,30 +116,48 @@ __global__ void k_nib_dequant(const uint8_t *__restrict__ nib, uint64_t nb, uint
 }
 
 // ---- small PTX wrappers ----
-__device__ __forceinline__ void nb_cp_async16(void *smem_dst, const void *gsrc) {
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gsrc));
-}
-__device__ __forceinline__ void nb_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void nb_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-__device__ __forceinline__ void nb_mma(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+__device__ __forceinline__ uint32_t nb_smem(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// z: four registers that hold zero for the whole kernel, the accumulator input of every MMA (each 32-weight group gets
+// its own exact s32 product sum, scaled by the group's integer scale afterwards)
+__device__ __forceinline__ void nb_mma(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1, const int (&z)[4]) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z[0]), "r"(z[1]), "r"(z[2]), "r"(z[3]));
+}
+// byte permute with the selector taken as it is (the intrinsic masks bit 3 of every selector nibble first, one more
+// instruction per use; the 4-bit codes never set it)
+__device__ __forceinline__ uint32_t nb_prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+// one record into a ring slot: the copy engine signals the slot's mbarrier with the bytes it delivered
+__device__ __forceinline__ void nb_fetch(uint32_t dst, const void *src, uint32_t bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(NIB_REC) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(dst), "l"(src), "r"(NIB_REC), "r"(bar) : "memory");
+}
+constexpr uint32_t NIB_SPIN_LIMIT = 1u << 22;      // polls of the (itself time-limited) try_wait: far beyond any real wait
+__device__ __forceinline__ bool nb_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < NIB_SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
 }
 
-// staged tile of one 256-column block: 16 rows x 128 code bytes (pitch 144: conflict-free 16-byte reads), 16 x 8 scale
-// bytes, 16 fp16 block scales
-constexpr uint32_t NIB_PITCH = 144u, NIB_SC_OFF = 16u * NIB_PITCH, NIB_D_OFF = NIB_SC_OFF + 128u, NIB_STAGE = NIB_D_OFF + 32u;
 constexpr uint32_t NIB_STAGES = 3u, NIB_WARPS = 8u;
 constexpr uint32_t NIB_TAB_POS = 0x002b1908u, NIB_TAB_NEG = 0x00d5e7f8u;      // bytes 8, 25, 43, 0 and -8, -25, -43, 0
 
-// One warp: 16 rows x one 256-column block against NT 8-column tiles of activation digits.
-// st: the staged tile; Bl: digits of column g of tile 0 at this block's first column + 8 t (tile n is n * 8 * BPITCH further).
+// One warp: 16 rows x one 256-column block (a record in shared memory) against NT 8-column tiles of activation digits.
+// Bl: digits of column g of tile 0 at this block's first column + 8 t (tile n is n * 8 * BPITCH further).
 template <int NT, uint32_t BPITCH>
-__device__ __forceinline__ void nib_chunk(const uint8_t *st, const int8_t *Bl, uint32_t g, uint32_t t, float (&out)[3][4]) {
-    const uint4 qa0 = *reinterpret_cast<const uint4 *>(st + g * NIB_PITCH + t * 32u), qa1 = *reinterpret_cast<const uint4 *>(st + g * NIB_PITCH + t * 32u + 16u);
-    const uint4 qb0 = *reinterpret_cast<const uint4 *>(st + (g + 8u) * NIB_PITCH + t * 32u), qb1 = *reinterpret_cast<const uint4 *>(st + (g + 8u) * NIB_PITCH + t * 32u + 16u);
+__device__ __forceinline__ void nib_chunk(const uint8_t *st, const int8_t *Bl, uint32_t g, uint32_t t, const int (&z)[4], float (&out)[3][4]) {
+    const uint32_t o0 = g * 128u + ((2u * t) ^ (g & 1u)) * 16u, o1 = g * 128u + ((2u * t + 1u) ^ (g & 1u)) * 16u;   // rows g and g + 8 have the same parity
+    const uint4 qa0 = *reinterpret_cast<const uint4 *>(st + o0), qa1 = *reinterpret_cast<const uint4 *>(st + o1);
+    const uint4 qb0 = *reinterpret_cast<const uint4 *>(st + 1024u + o0), qb1 = *reinterpret_cast<const uint4 *>(st + 1024u + o1);
     const uint2 sa = *reinterpret_cast<const uint2 *>(st + NIB_SC_OFF + g * 8u), sb = *reinterpret_cast<const uint2 *>(st + NIB_SC_OFF + (g + 8u) * 8u);
     const float da = 0.125f * __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(st + NIB_D_OFF + g * 2u)));
     const float db = 0.125f * __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(st + NIB_D_OFF + (g + 8u) * 2u)));
@@ -136,15 +168,15 @@ __device__ __forceinline__ void nib_chunk(const uint8_t *st, const int8_t *Bl, u
     for (int n = 0; n < NT; ++n) { blk[n][0] = blk[n][1] = blk[n][2] = blk[n][3] = 0; }
 #pragma unroll
     for (int kg = 0; kg < 8; ++kg) {
-        const uint32_t a0 = __byte_perm(NIB_TAB_POS, NIB_TAB_NEG, wa[kg]), a2 = __byte_perm(NIB_TAB_POS, NIB_TAB_NEG, wa[kg] >> 16);
-        const uint32_t a1 = __byte_perm(NIB_TAB_POS, NIB_TAB_NEG, wb[kg]), a3 = __byte_perm(NIB_TAB_POS, NIB_TAB_NEG, wb[kg] >> 16);
-        const int sca = (int)__byte_perm(kg < 4 ? sa.x : sa.y, 0u, 0x4440u + (uint32_t)(kg & 3));
-        const int scb = (int)__byte_perm(kg < 4 ? sb.x : sb.y, 0u, 0x4440u + (uint32_t)(kg & 3));
+        const uint32_t a0 = nb_prmt(NIB_TAB_POS, NIB_TAB_NEG, wa[kg]), a2 = nb_prmt(NIB_TAB_POS, NIB_TAB_NEG, wa[kg] >> 16);
+        const uint32_t a1 = nb_prmt(NIB_TAB_POS, NIB_TAB_NEG, wb[kg]), a3 = nb_prmt(NIB_TAB_POS, NIB_TAB_NEG, wb[kg] >> 16);
+        const int sca = (int)nb_prmt(kg < 4 ? sa.x : sa.y, 0u, 0x4440u + (uint32_t)(kg & 3));
+        const int scb = (int)nb_prmt(kg < 4 ? sb.x : sb.y, 0u, 0x4440u + (uint32_t)(kg & 3));
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
             const uint2 bf = *reinterpret_cast<const uint2 *>(Bl + (uint32_t)n * 8u * BPITCH + (uint32_t)kg * 32u);
             int d[4];
-            nb_mma(d, a0, a1, a2, a3, bf.x, bf.y);
+            nb_mma(d, a0, a1, a2, a3, bf.x, bf.y, z);
             blk[n][0] += sca * d[0]; blk[n][1] += sca * d[1];
             blk[n][2] += scb * d[2]; blk[n][3] += scb * d[3];
         }
@@ -157,10 +189,75 @@ __device__ __forceinline__ void nib_chunk(const uint8_t *st, const int8_t *Bl, u
 }
 
 struct NibUnit {
-    const uint8_t *base;       // this warp's expert matrix
+    const uint8_t *rec;        // first record of this warp's tiles in the unit (records of a tile, then of the next tile, are contiguous)
     uint32_t item, p0, nt;     // work item, its first pair in sorted[], its pairs
-    uint32_t tile0, n;         // first 16-row tile of this warp and the number of 256-column blocks it streams in the unit
+    uint32_t tile0, n;         // first 16-row tile of this warp and the number of records it streams in the unit
 };
+
+// A warp's private ring of NIB_STAGES record slots. Records are requested in stream order: first the rest of the
+// current unit (cur_*), then the first ones of the next unit (nxt_*), so the ring never drains at a unit boundary.
+// Between two reads exactly one request is made, which keeps NIB_STAGES - 1 records in flight behind the one being read.
+struct NibRing {
+    uint32_t stage_s, bar_s;           // shared-memory addresses of slot 0 and of its mbarrier
+    uint32_t prod, cons, phase;        // next slot to fill / to read; bit s = parity the next read of slot s waits for
+    const uint8_t *cur_src, *nxt_src;
+    uint32_t cur_rem, nxt_rem, nxt_taken;
+    uint32_t timed_out;
+};
+__device__ __forceinline__ void nib_request(NibRing &R, uint32_t lane) {
+    const uint8_t *src;
+    if (R.cur_rem) { src = R.cur_src; R.cur_src += NIB_REC; --R.cur_rem; }
+    else if (R.nxt_rem) { src = R.nxt_src; R.nxt_src += NIB_REC; --R.nxt_rem; ++R.nxt_taken; }
+    else return;
+    if (lane == 0) nb_fetch(R.stage_s + R.prod * NIB_REC, src, R.bar_s + 8u * R.prod);
+    R.prod = R.prod + 1u == NIB_STAGES ? 0u : R.prod + 1u;
+}
+// waits for the oldest record; returns its slot. After a wait ran out no further wait is attempted (the results of the
+// launch are void: the caller raises the status word).
+__device__ __forceinline__ uint32_t nib_acquire(NibRing &R) {
+    const uint32_t slot = R.cons;
+    if (!R.timed_out && !nb_wait(R.bar_s + 8u * slot, (R.phase >> slot) & 1u)) R.timed_out = 1u;
+    return slot;
+}
+__device__ __forceinline__ void nib_release(NibRing &R) {
+    __syncwarp();                      // every lane has read the slot: it may be refilled
+    R.phase ^= 1u << R.cons;
+    R.cons = R.cons + 1u == NIB_STAGES ? 0u : R.cons + 1u;
+}
+
+// All tiles of one unit for one warp, NT column tiles of digits in use (1: pairs packed into one tile, 3: a tile per digit).
+// vals[ti][.] = (row g, pair slot 0), (row g, pair slot 1), (row g + 8, slot 0), (row g + 8, slot 1), times the pair's scale.
+template <int NT, uint32_t BPR, uint32_t BPITCH, uint32_t TPW>
+__device__ __forceinline__ void nib_tiles(NibRing &R, const uint8_t *my_stage, const int8_t *Bbase, uint32_t tiles, uint32_t lane, uint32_t g, uint32_t t,
+                                          const int (&z)[4], float dw1, float dw2, const float (&sxv)[2], float (&vals)[TPW][4]) {
+    for (uint32_t ti = 0; ti < tiles; ++ti) {
+        float out[3][4];
+#pragma unroll
+        for (int n = 0; n < 3; ++n) { out[n][0] = out[n][1] = out[n][2] = out[n][3] = 0.f; }
+        for (uint32_t c = 0; c < BPR; ++c) {
+            nib_request(R, lane);
+            const uint32_t slot = nib_acquire(R);
+            nib_chunk<NT, BPITCH>(my_stage + slot * NIB_REC, Bbase + c * 256u, g, t, z, out);
+            nib_release(R);
+        }
+        float v[2][2];                 // [row half][pair slot]
+        if (NT == 1) {
+            const uint32_t src = (lane & ~3u) + 1u;
+            const float x0 = __shfl_sync(0xffffffffu, out[0][0], src), y0 = __shfl_sync(0xffffffffu, out[0][1], src);
+            const float x1 = __shfl_sync(0xffffffffu, out[0][2], src), y1 = __shfl_sync(0xffffffffu, out[0][3], src);
+            // t == 0: pair 0 = cols 0, 1 (own) and 2 (lane t = 1); t == 2: pair 1 = col 3 (lane t = 1) and cols 4, 5 (own)
+            v[0][0] = t == 0u ? out[0][0] + dw1 * out[0][1] + dw2 * x0 : y0 + dw1 * out[0][0] + dw2 * out[0][1];
+            v[1][0] = t == 0u ? out[0][2] + dw1 * out[0][3] + dw2 * x1 : y1 + dw1 * out[0][2] + dw2 * out[0][3];
+            v[0][1] = v[1][1] = 0.f;
+        } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) v[h][j] = out[0][2 * h + j] + dw1 * out[1][2 * h + j] + dw2 * out[2][2 * h + j];
+        }
+        vals[ti][0] = v[0][0] * sxv[0]; vals[ti][1] = v[0][1] * sxv[1]; vals[ti][2] = v[1][0] * sxv[0]; vals[ti][3] = v[1][1] * sxv[1];
+    }
+}
 
 // GATEUP: warps 0-3 take the gate rows of 4 x TPW tiles, warps 4-7 the up rows of the same tiles; the up values cross a
 // small shared buffer and the gate warps store SiLU(gate) * up. Otherwise (down projection) 8 x TPW tiles per unit.
@@ -171,49 +268,50 @@ __global__ void __launch_bounds__(NIB_WARPS * 32u, 2) k_nib_experts(const __grid
     constexpr uint32_t BPR = NCOLS / 256u, TPW = BPR >= 8u ? 1u : 8u / BPR, WSLOTS = GATEUP ? 4u : 8u, UNIT_TILES = WSLOTS * TPW;
     constexpr uint32_t BPITCH = NCOLS + 32u, V16 = NCOLS / 16u;
     __shared__ uint32_t s_unit[2];
+    __shared__ volatile uint32_t s_fail;
+    __shared__ __align__(8) uint64_t s_bar[NIB_WARPS][NIB_STAGES];
     __shared__ __align__(16) float4 s_ex[GATEUP ? TPW : 1u][4][32];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
-    uint8_t *my_stage = smem + warp * (NIB_STAGES * NIB_STAGE);
-    int8_t *Bs = reinterpret_cast<int8_t *>(smem + NIB_WARPS * NIB_STAGES * NIB_STAGE);
+    uint8_t *my_stage = smem + warp * (NIB_STAGES * NIB_REC);
+    int8_t *Bs = reinterpret_cast<int8_t *>(smem + NIB_WARPS * NIB_STAGES * NIB_REC);
     const uint32_t ntile_rows = A.nrows >> 4, U = (ntile_rows + UNIT_TILES - 1u) / UNIT_TILES;
     const uint32_t total = *A.n_items * U;
     const bool is_up = GATEUP && warp >= 4u;
     const uint32_t wslot = GATEUP ? (warp & 3u) : warp;
     const uint8_t *wmat = is_up ? A.w1 : A.w0;
-    const uint64_t nb = A.nb;
+    NibRing R{};
+    R.stage_s = nb_smem(my_stage); R.bar_s = nb_smem(&s_bar[warp][0]);
 
     auto decode = [&](uint32_t unit, NibUnit &I) {
         const uint32_t item = unit / U, rb = unit - item * U;
         const uint32_t u = A.item_u[item], p0 = A.item_p0[item];
         uint32_t e = A.uexp[u] - A.expert_begin, nt = min(A.item_tok, A.ustart[u + 1u] - p0);
         if (e >= A.n_local) { if (A.status && tid == 0) A.status[ST_EXPERT_RANGE] = 1u; e = 0u; nt = 0u; }     // never index the arena with a foreign id
-        I.base = wmat + (size_t)e * A.mat_bytes; I.item = item; I.p0 = p0; I.nt = nt;
+        I.item = item; I.p0 = p0; I.nt = nt;
         I.tile0 = rb * UNIT_TILES + wslot * TPW;
         const uint32_t tiles = I.tile0 >= ntile_rows ? 0u : min(TPW, ntile_rows - I.tile0);
         I.n = nt ? tiles * BPR : 0u;
-    };
-    auto issue = [&](const NibUnit &I, uint32_t q, uint32_t slot) {
-        const uint32_t ti = q / BPR, c = q - ti * BPR, row0 = (I.tile0 + ti) << 4;
-        uint8_t *dst = my_stage + slot * NIB_STAGE;
-        const uint8_t *src = I.base + ((size_t)(row0 + (lane >> 3)) * BPR + c) * 128u + (lane & 7u) * 16u;
-#pragma unroll
-        for (uint32_t i = 0; i < 4u; ++i) nb_cp_async16(dst + ((lane >> 3) + 4u * i) * NIB_PITCH + (lane & 7u) * 16u, src + (size_t)i * 4u * BPR * 128u);
-        if (lane < 8u) nb_cp_async16(dst + NIB_SC_OFF + lane * 16u, I.base + nb * 128u + ((size_t)c * A.nrows + row0) * 8u + lane * 16u);
-        else if (lane < 10u) nb_cp_async16(dst + NIB_D_OFF + (lane - 8u) * 16u, I.base + nb * 136u + ((size_t)c * A.nrows + row0) * 2u + (lane - 8u) * 16u);
+        I.rec = wmat + (size_t)e * A.mat_bytes + (size_t)I.tile0 * BPR * NIB_REC;
     };
 
-    if (tid == 0) s_unit[0] = atomicAdd(A.work, 1u);
+    if (tid == 0) { s_unit[0] = atomicAdd(A.work, 1u); s_fail = 0u; }
+    if (lane == 0) {
+        for (uint32_t i = 0; i < NIB_STAGES; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(R.bar_s + 8u * i));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
     __syncthreads();
-    uint32_t cur = s_unit[0], par = 0u, cur_item = 0xffffffffu, base_slot = 0u;
-    bool prefetched = false;
+    uint32_t cur = s_unit[0], par = 0u, cur_item = 0xffffffffu;
+    uint32_t ahead = 0u;             // records of the CURRENT unit already requested (while the previous unit was multiplying)
+    int zero[4];                     // opaque to the compiler: four registers that stay zero, the accumulator input of every MMA
+    asm volatile("mov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\tmov.b32 %2, 0;\n\tmov.b32 %3, 0;" : "=r"(zero[0]), "=r"(zero[1]), "=r"(zero[2]), "=r"(zero[3]));
     NibUnit I{}, N{};
     if (cur < total) decode(cur, I);
     while (cur < total) {
         if (tid == 0) s_unit[par ^ 1u] = atomicAdd(A.work, 1u);
-        if (!prefetched) {           // the ring is empty: start this unit's first blocks
-            nb_wait<0>();
-            for (uint32_t i = 0; i + 1u < NIB_STAGES; ++i) { if (i < I.n) issue(I, i, (base_slot + i) % NIB_STAGES); nb_commit(); }
-        }
+        // this unit's stream; NIB_STAGES - 1 of its records are put in flight before the first read
+        R.cur_src = I.rec + (size_t)ahead * NIB_REC; R.cur_rem = I.n - ahead; R.nxt_rem = 0u; R.nxt_taken = 0u;
+        for (uint32_t i = ahead; i + 1u < NIB_STAGES; ++i) nib_request(R, lane);
         const bool packed = I.nt <= 2u;
         if (I.item != cur_item) {    // activation digits of the item (every warp passed the barrier that ended the last unit)
             const uint32_t ncolb = packed ? 8u : 24u;
@@ -239,65 +337,30 @@ __global__ void __launch_bounds__(NIB_WARPS * 32u, 2) k_nib_experts(const __grid
         __syncthreads();             // digits and the next unit's number are in shared memory
         const uint32_t nxt = s_unit[par ^ 1u];
         const bool nv = nxt < total;
-        if (nv) decode(nxt, N);
-        const bool ahead = nv && I.n + 1u >= NIB_STAGES;       // this unit is long enough to start the next one's ring
+        if (nv) { decode(nxt, N); if (I.n + 1u >= NIB_STAGES) { R.nxt_src = N.rec; R.nxt_rem = N.n; } }     // a unit shorter than the ring does not look ahead
 
-        float out[3][4];
-        float gatev[TPW][4];
-        for (uint32_t q = 0; q < I.n; ++q) {
-            const uint32_t k = q + NIB_STAGES - 1u;
-            if (k < I.n) issue(I, k, (base_slot + k) % NIB_STAGES);
-            else if (ahead && k - I.n < N.n) issue(N, k - I.n, (base_slot + k) % NIB_STAGES);
-            nb_commit();
-            const uint32_t ti = q / BPR, c = q - ti * BPR;
-            if (c == 0u) {
-#pragma unroll
-                for (int n = 0; n < 3; ++n) { out[n][0] = out[n][1] = out[n][2] = out[n][3] = 0.f; }
-            }
-            nb_wait<NIB_STAGES - 1>();
-            __syncwarp();
-            const uint8_t *st = my_stage + ((base_slot + q) % NIB_STAGES) * NIB_STAGE;
-            const int8_t *Bl = Bs + (size_t)g * BPITCH + c * 256u + 8u * t;
-            if (packed) nib_chunk<1, BPITCH>(st, Bl, g, t, out);
-            else nib_chunk<3, BPITCH>(st, Bl, g, t, out);
-            __syncwarp();
-            if (c + 1u == BPR) {     // tile finished: digits -> values of (row g | g+8, pair)
-                float val[2][2];     // [row half][pair slot]
-                if (packed) {
-                    const uint32_t src = (lane & ~3u) + 1u;
-                    const float x0 = __shfl_sync(0xffffffffu, out[0][0], src), y0 = __shfl_sync(0xffffffffu, out[0][1], src);
-                    const float x1 = __shfl_sync(0xffffffffu, out[0][2], src), y1 = __shfl_sync(0xffffffffu, out[0][3], src);
-                    // t == 0: pair 0 = cols 0, 1 (own) and 2 (lane t = 1); t == 2: pair 1 = col 3 (lane t = 1) and cols 4, 5 (own)
-                    val[0][0] = t == 0u ? out[0][0] + A.dw1 * out[0][1] + A.dw2 * x0 : y0 + A.dw1 * out[0][0] + A.dw2 * out[0][1];
-                    val[1][0] = t == 0u ? out[0][2] + A.dw1 * out[0][3] + A.dw2 * x1 : y1 + A.dw1 * out[0][2] + A.dw2 * out[0][3];
-                    val[0][1] = val[1][1] = 0.f;
-                } else {
-#pragma unroll
-                    for (int h = 0; h < 2; ++h)
-#pragma unroll
-                        for (int j = 0; j < 2; ++j) val[h][j] = out[0][2 * h + j] + A.dw1 * out[1][2 * h + j] + A.dw2 * out[2][2 * h + j];
-                }
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) val[h][j] *= sxv[j];
+        float vals[TPW][4];
+        const uint32_t tiles = I.n / BPR;
+        const int8_t *Bbase = Bs + (size_t)g * BPITCH + 8u * t;
+        if (packed) nib_tiles<1, BPR, BPITCH, TPW>(R, my_stage, Bbase, tiles, lane, g, t, zero, A.dw1, A.dw2, sxv, vals);
+        else nib_tiles<3, BPR, BPITCH, TPW>(R, my_stage, Bbase, tiles, lane, g, t, zero, A.dw1, A.dw2, sxv, vals);
+        if (R.timed_out && lane == 0) { s_fail = 1u; if (A.status) A.status[ST_TIMEOUT] = 1u; }
+        if (GATEUP) {
+            if (is_up) for (uint32_t ti = 0; ti < tiles; ++ti) s_ex[ti][wslot][lane] = make_float4(vals[ti][0], vals[ti][1], vals[ti][2], vals[ti][3]);
+        } else {
+            for (uint32_t ti = 0; ti < tiles; ++ti) {
                 const uint32_t row = ((I.tile0 + ti) << 4) + g;
-                if (GATEUP) {
-                    if (is_up) s_ex[ti][wslot][lane] = make_float4(val[0][0], val[0][1], val[1][0], val[1][1]);
-                    else { gatev[ti][0] = val[0][0]; gatev[ti][1] = val[0][1]; gatev[ti][2] = val[1][0]; gatev[ti][3] = val[1][1]; }
-                } else {
 #pragma unroll
-                    for (int j = 0; j < 2; ++j)
-                        if (ok[j]) {
-                            A.out[(size_t)prow[j] * A.out_stride + row] = val[0][j];
-                            A.out[(size_t)prow[j] * A.out_stride + row + 8u] = val[1][j];
-                        }
-                }
+                for (int j = 0; j < 2; ++j)
+                    if (ok[j]) {
+                        A.out[(size_t)prow[j] * A.out_stride + row] = vals[ti][j];
+                        A.out[(size_t)prow[j] * A.out_stride + row + 8u] = vals[ti][2 + j];
+                    }
             }
         }
         __syncthreads();             // the unit is done in every warp: up values are in s_ex, the digits may be replaced
+        const bool fail = s_fail != 0u;      // written only between the two barriers of a unit, read only here: every warp sees the same value
         if (GATEUP && !is_up) {
-            const uint32_t tiles = I.n / BPR;
             for (uint32_t ti = 0; ti < tiles; ++ti) {
                 const float4 up = s_ex[ti][wslot][lane];
                 const float uv[4] = {up.x, up.y, up.z, up.w};
@@ -305,20 +368,19 @@ __global__ void __launch_bounds__(NIB_WARPS * 32u, 2) k_nib_experts(const __grid
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
                     if (ok[j]) {
-                        const float g0 = gatev[ti][j], g1 = gatev[ti][2 + j];
+                        const float g0 = vals[ti][j], g1 = vals[ti][2 + j];
                         A.out[(size_t)prow[j] * A.out_stride + row] = (g0 / (1.0f + expf(-g0))) * uv[j];
                         A.out[(size_t)prow[j] * A.out_stride + row + 8u] = (g1 / (1.0f + expf(-g1))) * uv[2 + j];
                     }
             }
         }
-        base_slot = (base_slot + I.n) % NIB_STAGES;
-        prefetched = ahead && I.n != 0u;
+        if (fail) break;             // some warp's copy never arrived (status word raised): stop drawing units
+        ahead = R.nxt_taken;
         cur = nxt; I = N; par ^= 1u;
     }
-    nb_wait<0>();
 }
 
-static size_t nib_smem_bytes(uint32_t ncols) { return (size_t)NIB_WARPS * NIB_STAGES * NIB_STAGE + 24u * (size_t)(ncols + 32u); }
+static size_t nib_smem_bytes(uint32_t ncols) { return (size_t)NIB_WARPS * NIB_STAGES * NIB_REC + 24u * (size_t)(ncols + 32u); }
 
 // A.w0 / A.w1: nibble-layout expert matrices (gate and up, or down and nullptr); A.work: the unit counter of this launch
 // (zeroed by the grouping kernel); items are cut with at most 8 pairs. max_items bounds the number of work items.

@@ -19,10 +19,11 @@
 
 namespace rc {
 
-__device__ __forceinline__ void mma_s8_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-    asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};\n"
+// z: a quad of registers holding zero for the whole kernel (a literal 0 costs four moves in front of every MMA)
+__device__ __forceinline__ void mma_s8_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, const int (&z)[4]) {
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};\n"
                  : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-                 : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(z[0]), "r"(z[1]), "r"(z[2]), "r"(z[3]));
 }
 
 struct Q6Args {
@@ -51,6 +52,8 @@ __global__ void __launch_bounds__(256) k_q6k_mma(const __grid_constant__ Q6Args 
     const bool tok_ok = tok < A.ntok;
     const int8_t *xrow = A.xq + (size_t)(tok_ok ? tok : 0u) * 3u * A.ncols + 4u * t;
     float out[4] = {0.f, 0.f, 0.f, 0.f};
+    int z[4];
+    asm volatile("mov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\tmov.b32 %2, 0;\n\tmov.b32 %3, 0;" : "=r"(z[0]), "=r"(z[1]), "=r"(z[2]), "=r"(z[3]));
     if (tg * 8u < A.ntok) {
 #pragma unroll 8
         for (uint32_t s = s_begin; s < s_end; ++s) {
@@ -73,9 +76,9 @@ __global__ void __launch_bounds__(256) k_q6k_mma(const __grid_constant__ Q6Args 
             const uint32_t b0 = tok_ok ? __ldg(reinterpret_cast<const uint32_t *>(xrow + 16u * s)) : 0u;
             const uint32_t b1 = tok_ok ? __ldg(reinterpret_cast<const uint32_t *>(xrow + A.ncols + 16u * s)) : 0u;
             const uint32_t b2 = tok_ok ? __ldg(reinterpret_cast<const uint32_t *>(xrow + 2u * A.ncols + 16u * s)) : 0u;
-            mma_s8_k16(d0, a[0], a[1], b0);
-            mma_s8_k16(d1, a[0], a[1], b1);
-            mma_s8_k16(d2, a[0], a[1], b2);
+            mma_s8_k16(d0, a[0], a[1], b0, z);
+            mma_s8_k16(d1, a[0], a[1], b1, z);
+            mma_s8_k16(d2, a[0], a[1], b2, z);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int hi = d1[c] + (d2[c] << A.bits);                 // 8-bit digits: the full recombination would leave s32
