@@ -493,6 +493,17 @@ def run_moe_b1(args):
 
     ms, clocks = _timed_graph(torch, step, args.steps, args.warmup, 0)
     value = L / (ms * 1e-3)
+    # per-kernel durations (CUDA events around every launch, eager, separate from the timed region)
+    from dwarfstar_red_lite_b200 import redcuda as rcm
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        rcm.profile_enable(True)
+        for _ in range(3):
+            step(side.cuda_stream)
+        side.synchronize()
+        prof = rcm.profile_report()
+        rcm.profile_enable(False)
+    kernel_us = {k: round(1e3 * v[1] / v[0], 2) for k, v in prof.items()}
     xh, oh = x_d.cpu().numpy(), np.empty((L, 1, dims.hidden), np.float32)
     t0 = time.perf_counter()
     for l in range(L):
@@ -515,7 +526,7 @@ def run_moe_b1(args):
                       "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                       "config": {"workload": "BASELINE configs[0]: single routed-MoE FFN layer, batch 1, router computed, 512 IQ2_XXS experts top-10 + Q6_K shared expert",
                                  "layers_per_step": L, "l2_policy": f"each step sweeps {L} distinct layers' weights"},
-                      "roofline": {"bound": "hbm", "kernel": "whole layer (9 launches)", "achieved": gbs, "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": gbs / peak,
+                      "roofline": {"bound": "hbm", "kernel": "whole layer (%d launches)" % len(kernel_us), "kernel_us_per_launch": kernel_us, "achieved": gbs, "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": gbs / peak,
                                    "frac_of_nominal_8000": gbs / 8000.0, "traffic": None, "bytes_per_token_layer": bytes_layer, "us_per_layer": 1e3 * ms / L},
                       "cpu_baseline": cpu, "e2e": {"value": e2e_v, "unit": UNIT, "h2d_bytes_per_step": L * row, "d2h_bytes_per_step": L * row},
                       "gpu_launches": None, "clocks": clocks}), flush=True)

@@ -172,6 +172,75 @@ __global__ void k_dequant_f16(const unsigned short *__restrict__ src, uint64_t n
         out[i] = __half2float(__ushort_as_half(src[i]));
 }
 
+// Softmax + top-k of one token's logits by one warp; NPL = probabilities per lane (expert i sits in lane i % 32, slot
+// i / 32). CG: the logits were written by other blocks of the same launch (read past L1).
+// A single warp runs this alone while the rest of the layer waits, so what counts is the length of the dependent chain,
+// not the instruction count: every round finds each lane's best slot with a pairwise tree (depth log2 NPL instead of a
+// scan of NPL dependent compares), then the warp's best with five shuffle steps; ties go to the lower expert id in both.
+template <bool CG, int NPL>
+__device__ __forceinline__ void route_one_token_n(const float *__restrict__ l, uint32_t n_expert, uint32_t top_k, uint32_t *__restrict__ ids_row,
+                                                  float *__restrict__ weights_row, float *__restrict__ probs_row, const RouteGroup1 &G,
+                                                  uint32_t *__restrict__ status, uint32_t lane) {
+    float p[NPL];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < NPL; ++j) { const uint32_t i = lane + 32u * j; p[j] = i < n_expert ? (CG ? __ldcg(l + i) : l[i]) : -INFINITY; mx = fmaxf(mx, p[j]); }
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    double den = 0.0;
+#pragma unroll
+    for (int j = 0; j < NPL; ++j) { const uint32_t i = lane + 32u * j; const float e = i < n_expert ? expf(p[j] - mx) : 0.f; p[j] = e; den += (double)e; }
+    for (int o = 16; o; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+    const float inv = (float)(1.0 / den);
+#pragma unroll
+    for (int j = 0; j < NPL; ++j) {
+        const uint32_t i = lane + 32u * j;
+        p[j] = i < n_expert ? p[j] * inv : -2.0f;
+        if (probs_row && i < n_expert) probs_row[i] = p[j];
+    }
+    double sel = 0.0;
+    float myw = 0.f;                   // lane k keeps the weight of selection k (top_k <= 64: two per lane)
+    float myw2 = 0.f;
+    for (uint32_t k = 0; k < top_k; ++k) {
+        // lane-local best: a tree over the slots; on equal values the lower slot (= lower expert id) wins
+        float tv[NPL]; uint32_t tj[NPL];
+#pragma unroll
+        for (int j = 0; j < NPL; ++j) { tv[j] = p[j]; tj[j] = (uint32_t)j; }
+#pragma unroll
+        for (int w = 1; w < NPL; w <<= 1)
+#pragma unroll
+            for (int j = 0; j + w < NPL; j += 2 * w)
+                if (tv[j + w] > tv[j]) { tv[j] = tv[j + w]; tj[j] = tj[j + w]; }
+        float bv = tv[0]; uint32_t bi = tv[0] > -3.0f ? lane + 32u * tj[0] : 0xffffffffu;      // NaN compares false: no index
+        for (int o = 16; o; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (bi >= n_expert) { bi = k; if (status && lane == 0) status[ST_ROUTER_NONFINITE] = 1u; }   // NaN probabilities: nothing compared greater
+#pragma unroll
+        for (int j = 0; j < NPL; ++j) if (lane + 32u * j == bi) p[j] = -1.0f;
+        if (lane == 0) {
+            ids_row[k] = bi;
+            if (G.sorted) { G.sorted[k] = k; G.uexp[k] = bi; G.ustart[k] = k; G.item_u[k] = k; G.item_p0[k] = k; }      // single token: pair k = group k = item k
+            if (G.ids_mirror) G.ids_mirror[k] = bi;
+        }
+        if (lane == (k & 31u)) { if (k < 32u) myw = bv; else myw2 = bv; }
+        sel += (double)bv;
+    }
+    if (!(sel > 0.0 && sel < (double)INFINITY) && status && lane == 0) status[ST_ROUTER_NONFINITE] = 1u;
+    const float invs = (float)(1.0 / sel);
+    if (lane < top_k) weights_row[lane] = myw * invs;
+    if (lane + 32u < top_k) weights_row[lane + 32u] = myw2 * invs;
+    if (G.sorted && lane == 0) { G.ustart[top_k] = top_k; *G.n_unique = top_k; *G.n_items = top_k; if (G.work) { G.work[0] = 0u; G.work[1] = 0u; } }
+}
+template <bool CG>
+__device__ __forceinline__ void route_one_token(const float *__restrict__ l, uint32_t n_expert, uint32_t top_k, uint32_t *__restrict__ ids_row,
+                                                float *__restrict__ weights_row, float *__restrict__ probs_row, const RouteGroup1 &G,
+                                                uint32_t *__restrict__ status, uint32_t lane) {
+    if (n_expert <= 128u) route_one_token_n<CG, 4>(l, n_expert, top_k, ids_row, weights_row, probs_row, G, status, lane);
+    else if (n_expert <= 512u) route_one_token_n<CG, 16>(l, n_expert, top_k, ids_row, weights_row, probs_row, G, status, lane);
+    else route_one_token_n<CG, 32>(l, n_expert, top_k, ids_row, weights_row, probs_row, G, status, lane);
+}
+
 // ---- generic multi-job GEMV ----
 // Each block takes one tile (a run of rows) of one job. All jobs of a launch read the same activation rows.
 template <int TYPE, int NT>
@@ -231,11 +300,26 @@ __global__ void __launch_bounds__(256) k_gemv(const __grid_constant__ GemvArgs A
             default: break;
         }
     }
+    if (NT == 1 && A.tail.ticket) {
+        // the block that draws the last ticket sees every block's logits (fence before the ticket, fence after it) and
+        // runs the selection for the launch's single token
+        __shared__ uint32_t s_last;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) s_last = atomicAdd(A.tail.ticket, 1u) == gridDim.x - 1u ? 1u : 0u;
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            if (threadIdx.x == 0) *A.tail.ticket = 0u;
+            if (threadIdx.x < 32u) route_one_token<true>(A.tail.logits, A.tail.n_expert, A.tail.top_k, A.tail.ids, A.tail.weights, nullptr, A.tail.G, A.tail.status, threadIdx.x);
+        }
+    }
 }
 
 // Fill tile_begin / rows_per_tile of every job and launch. Jobs must share ncols (they read the same x rows).
 int launch_gemv(GemvArgs &A, cudaStream_t stream) {
     RC_REQUIRE(A.njobs >= 1 && A.njobs <= RC_MAX_JOBS, "gemv: bad job count %u", A.njobs);
+    RC_REQUIRE(!A.tail.ticket || (A.ntok == 1u && A.tail.n_expert <= 1024u), "gemv: the routing tail serves one token and at most 1024 experts");
     const uint32_t ncols = A.job[0].ncols;
     RC_REQUIRE(ncols % 64u == 0 && ncols >= 64u, "gemv: row length %u is not a multiple of 64", ncols);
     uint64_t total_rows = 0;
@@ -341,50 +425,8 @@ __global__ void __launch_bounds__(256) k_route_warp(const float *__restrict__ lo
     pdl_prologue();
     const uint32_t lane = threadIdx.x & 31u, tok = blockIdx.x * 8u + (threadIdx.x >> 5);
     if (tok >= ntok) return;
-    const float *l = logits + (size_t)tok * n_expert;
-    float p[32];
-    float mx = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < 32; ++j) { const uint32_t i = lane + 32u * j; p[j] = i < n_expert ? l[i] : -INFINITY; mx = fmaxf(mx, p[j]); }
-    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    double den = 0.0;
-#pragma unroll
-    for (int j = 0; j < 32; ++j) { const uint32_t i = lane + 32u * j; const float e = i < n_expert ? expf(p[j] - mx) : 0.f; p[j] = e; den += (double)e; }
-    for (int o = 16; o; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
-    const float inv = (float)(1.0 / den);
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        const uint32_t i = lane + 32u * j;
-        p[j] = i < n_expert ? p[j] * inv : -2.0f;
-        if (probs_out && i < n_expert) probs_out[(size_t)tok * n_expert + i] = p[j];
-    }
-    double sel = 0.0;
-    float myw = 0.f;                   // lane k keeps the weight of selection k (top_k <= 64: two per lane)
-    float myw2 = 0.f;
-    for (uint32_t k = 0; k < top_k; ++k) {
-        float bv = -3.0f; uint32_t bi = 0xffffffffu;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) { const uint32_t i = lane + 32u * j; if (p[j] > bv) { bv = p[j]; bi = i; } }   // ascending i: first maximum = lowest id
-        for (int o = 16; o; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-        }
-        if (bi >= n_expert) { bi = k; if (status && lane == 0) status[ST_ROUTER_NONFINITE] = 1u; }   // NaN probabilities: nothing compared greater
-#pragma unroll
-        for (int j = 0; j < 32; ++j) if (lane + 32u * j == bi) p[j] = -1.0f;
-        if (lane == 0) {
-            ids[(size_t)tok * top_k + k] = bi;
-            if (G.sorted) { G.sorted[k] = k; G.uexp[k] = bi; G.ustart[k] = k; G.item_u[k] = k; G.item_p0[k] = k; }      // single token: pair k = group k = item k
-            if (G.ids_mirror) G.ids_mirror[k] = bi;
-        }
-        if (lane == (k & 31u)) { if (k < 32u) myw = bv; else myw2 = bv; }
-        sel += (double)bv;
-    }
-    if (!(sel > 0.0 && sel < (double)INFINITY) && status && lane == 0) status[ST_ROUTER_NONFINITE] = 1u;
-    const float invs = (float)(1.0 / sel);
-    if (lane < top_k) weights[(size_t)tok * top_k + lane] = myw * invs;
-    if (lane + 32u < top_k) weights[(size_t)tok * top_k + lane + 32u] = myw2 * invs;
-    if (G.sorted && lane == 0) { G.ustart[top_k] = top_k; *G.n_unique = top_k; *G.n_items = top_k; if (G.work) { G.work[0] = 0u; G.work[1] = 0u; } }
+    route_one_token<false>(logits + (size_t)tok * n_expert, n_expert, top_k, ids + (size_t)tok * top_k, weights + (size_t)tok * top_k,
+                           probs_out ? probs_out + (size_t)tok * n_expert : nullptr, G, status, lane);
 }
 
 int launch_route(const float *logits_dev, uint32_t ntok, uint32_t n_expert, uint32_t top_k, uint32_t *ids_dev, float *weights_dev,

@@ -148,7 +148,7 @@ __device__ __forceinline__ void chunk_plain(uint32_t type, const uint8_t *base, 
     const uint32_t k0 = c * 64u, x0 = xi(k0);
     if (type == RC_F32) {
         const float4 *wp = reinterpret_cast<const float4 *>(base + (row * ncols + k0) * 4u);
-#pragma unroll 4
+#pragma unroll 8              // eight 16-byte loads in flight per lane: a lane's 256 bytes arrive in two round trips, not four
         for (int i = 0; i < 16; ++i) {
             const float4 w = __ldg(wp + i);
 #pragma unroll

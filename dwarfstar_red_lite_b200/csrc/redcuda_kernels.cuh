@@ -19,6 +19,20 @@ struct GemvJob {
     uint32_t tile_begin, rows_per_tile;     // filled by launch_gemv
 };
 
+// Where a single token's selection is also written as the (trivial) expert grouping the expert kernels read: every
+// selected expert is distinct, so pair k is its own group and its own work item.
+struct RouteGroup1 { uint32_t *sorted, *uexp, *ustart, *n_unique, *item_u, *item_p0, *n_items, *ids_mirror, *work; };   // work (may be null): two unit counters to zero
+// Optional tail of a single-token GEMV launch: the block that finishes last (an atomic ticket) also runs the router's
+// softmax / top-k over the logits the launch produced, so the selection costs no launch of its own.
+struct RouteTail {
+    uint32_t *ticket;          // null = no tail; zero before the launch, left at zero by the last block
+    const float *logits;
+    uint32_t n_expert, top_k;
+    uint32_t *ids; float *weights;
+    RouteGroup1 G;
+    uint32_t *status;
+};
+
 #define RC_MAX_JOBS 6u
 struct GemvArgs {
     GemvJob job[RC_MAX_JOBS];
@@ -28,12 +42,10 @@ struct GemvArgs {
     const uint8_t *iq2;        // filled by launch_gemv
     const uint32_t *iq3s;
     const char *tag;           // name under which the launch is timed when profiling is on (host side only)
+    RouteTail tail;
 };
 
 int launch_gemv(GemvArgs &A, cudaStream_t stream);
-// Where a single token's selection is also written as the (trivial) expert grouping the expert kernels read: every
-// selected expert is distinct, so pair k is its own group and its own work item.
-struct RouteGroup1 { uint32_t *sorted, *uexp, *ustart, *n_unique, *item_u, *item_p0, *n_items, *ids_mirror, *work; };   // work (may be null): two unit counters to zero
 // group1 (ntok == 1 only, may be null): fill the grouping arrays in the same kernel; ids_mirror (may be null) gets a copy of the ids
 int launch_route(const float *logits_dev, uint32_t ntok, uint32_t n_expert, uint32_t top_k, uint32_t *ids_dev, float *weights_dev,
                  float *probs_dev, cudaStream_t stream, const RouteGroup1 *group1 = nullptr);

@@ -226,6 +226,7 @@ struct redcuda_moe {
     bool use_mma = false;      // IQ2_XXS experts (and the Q6_K shared expert of a batch) on the integer tensor-core path
     bool nib = false;          // routed experts held in the nibble layout (redcuda_moe_nib.cu) instead of planar IQ2_XXS
     uint32_t *work = nullptr;  // two unit counters of the persistent expert kernels (gate/up, down)
+    uint32_t *ticket = nullptr; // ticket counter of the single-token GEMV's routing tail (zero between launches)
     cudaStream_t stream = nullptr;
     cudaStream_t side = nullptr;                    // the shared expert runs here, beside the routed experts
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_quant = nullptr;
@@ -249,7 +250,7 @@ static bool moe_shared_mma(const redcuda_moe *m, uint32_t ntok) {
 
 // x_quantised: xq_x / sx_x already hold the digits of x
 static int moe_gemv_pre(redcuda_moe *m, uint32_t ntok, const float *x, bool with_router, bool with_shared, bool x_quantised, cudaStream_t s,
-                        const int8_t *xq = nullptr, const float *sx = nullptr) {
+                        const int8_t *xq = nullptr, const float *sx = nullptr, const RouteTail *tail = nullptr) {
     if (!xq) { xq = m->xq_x; sx = m->sx_x; }
     GemvArgs A{};
     A.ntok = ntok; A.x = x; A.x_stride = m->d.hidden;
@@ -277,6 +278,7 @@ static int moe_gemv_pre(redcuda_moe *m, uint32_t ntok, const float *x, bool with
     if (!j) return 1;
     A.njobs = j;
     A.tag = "moe_pre_gemv";
+    if (tail) A.tail = *tail;
     return launch_gemv(A, s);
 }
 
@@ -373,9 +375,39 @@ static int moe_combine(redcuda_moe *m, uint32_t ntok, const float *pair_out, con
     return 1;
 }
 
+// One token in three launches (the dependency chain of the layer, nothing else): (1) router logits + shared gate/up +
+// scalar gate in one multi-job GEMV whose last block also runs the softmax / top-k; (2) gate/up of the selected experts,
+// the token quantised inside the kernel; (3) down of the selected experts + shared down + weighted sum + residual.
+// The reference fuses the same tail (redmetal_topk_down_tail, native/redmetal_topk.m:254-280).
+static bool moe_fused1_ok(const redcuda_moe *m) {
+    static const bool want = !(getenv("RC_MOE_FUSE1") && atoi(getenv("RC_MOE_FUSE1")) == 0);     // A/B switch
+    return want && m->nib && m->d.type_sh == RC_Q6_K && m->d.n_expert <= 1024u && nib_tail_ok(m->d.top_k, m->d.hidden, m->d.ffn) &&
+           m->d.ffn_sh == m->d.ffn;
+}
+static int moe_forward_fused1(redcuda_moe *m, const float *x, const float *logits_in, const float *resid, float *out, cudaStream_t s) {
+    const uint32_t k = m->d.top_k;
+    RouteTail T{};
+    T.ticket = m->ticket; T.logits = logits_in ? logits_in : m->logits; T.n_expert = m->d.n_expert; T.top_k = k; T.ids = m->ids; T.weights = m->wk;
+    T.G = RouteGroup1{m->sorted, m->uexp, m->ustart, m->n_unique, m->item_u, m->item_p0, m->n_items, m->ids_mirror, m->work};
+    T.status = status_words();
+    if (!moe_gemv_pre(m, 1u, x, logits_in == nullptr, true, false, s, nullptr, nullptr, &T)) return 0;
+    MmaArgs M{};
+    M.w0 = m->gate; M.w1 = m->up; M.mat_bytes = m->gu_bytes; M.nb = m->gu_nb; M.nrows = m->d.ffn; M.ncols = m->d.hidden;
+    M.expert_begin = m->d.expert_begin; M.n_local = m->d.expert_count; M.status = status_words();
+    M.sorted = m->sorted; M.uexp = m->uexp; M.ustart = m->ustart; M.item_u = m->item_u; M.item_p0 = m->item_p0; M.n_items = m->n_items;
+    M.xq = nullptr; M.sx = nullptr; M.x_div = k; M.out = m->act; M.out_stride = m->d.ffn; M.item_tok = 1u; M.work = m->work; M.x_raw = x;
+    if (!launch_nib_experts(M, k, s)) return 0;
+    NibTailArgs D{};
+    D.w_down = m->down; D.mat_bytes = m->down_bytes; D.nrows = m->d.hidden; D.ncols = m->d.ffn; D.expert_begin = m->d.expert_begin; D.n_local = m->d.expert_count;
+    D.top_k = k; D.ids = m->ids; D.wk = m->wk; D.act = m->act; D.act_stride = m->d.ffn;
+    D.sh_down = m->sh_down.base; D.sh_nb = m->sh_down.nb; D.sh_act = m->sh_act; D.scalar = m->scalar; D.resid = resid; D.out = out; D.status = status_words();
+    return launch_nib_down_tail(D, s);
+}
+
 static int moe_forward_on(redcuda_moe *m, uint32_t ntok, const float *x, const float *logits_in, const float *resid, float *out, cudaStream_t s) {
     RC_REQUIRE(m->d.expert_begin == 0 && m->d.expert_count == m->d.n_expert && m->d.expert_stride == 1u, "moe forward needs every expert on this device; use the route/experts/shared pieces under expert parallelism");
     RC_REQUIRE(ntok >= 1 && ntok <= m->d.max_tokens, "moe forward: ntok %u outside [1, %u]", ntok, m->d.max_tokens);
+    if (ntok == 1u && moe_fused1_ok(m)) return moe_forward_fused1(m, x, logits_in, resid, out, s);
     const uint32_t k = m->d.top_k, npairs = ntok * k;
     // one quantisation of the token activations serves the routed gate/up and the shared gate/up
     const bool xq = moe_experts_mma(m) || moe_shared_mma(m, ntok);
@@ -528,7 +560,7 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
     m->xq_sh = (int8_t *)(B + o_xqs); m->sx_sh = (float *)(B + o_sxs); m->item_u = (uint32_t *)(B + o_iu); m->item_p0 = (uint32_t *)(B + o_ip);
     m->n_items = (uint32_t *)(B + o_ni);
     m->xq_own = (int8_t *)(B + o_xqo); m->sx_own = (float *)(B + o_sxo);
-    m->work = (uint32_t *)(B + o_wk2);
+    m->work = (uint32_t *)(B + o_wk2); m->ticket = m->work + 2;
     {   // RC_MOE_PATH=cuda keeps the IQ2_XXS experts on the CUDA-core kernels (A/B switch for profiling)
         const char *pth = getenv("RC_MOE_PATH");
         m->use_mma = !(pth && pth[0] == 'c');

@@ -90,9 +90,8 @@ __global__ void __launch_bounds__(256) k_quant_act(const float *__restrict__ x, 
     __syncthreads();
     mx = red[0];
     for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
-    const int half = 1 << (bits - 1u), mask = (1 << bits) - 1;
-    const float QMAX = bits == 8u ? 8355711.0f : 1040000.0f;      // largest value three digits hold: 127 * (65536 + 256 + 1), or just below 63.5 * 16384
-    const float scale = (mx > 0.f && mx < INFINITY) ? mx / QMAX : 1.0f;
+    const float QMAX = act_qmax(bits);
+    const float scale = act_scale(mx, QMAX);
     const float inv = 1.0f / scale;
     if (tid == 0) sx[row] = scale;
     int8_t *q = xq + (size_t)row * 3u * ncols;
@@ -102,10 +101,9 @@ __global__ void __launch_bounds__(256) k_quant_act(const float *__restrict__ x, 
         uint32_t p0 = 0, p1 = 0, p2 = 0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            int iv = __float2int_rn(fminf(fmaxf(f[i] * inv, -QMAX), QMAX));
-            const int d0 = ((iv + half) & mask) - half; iv = (iv - d0) >> bits;
-            const int d1 = ((iv + half) & mask) - half; iv = (iv - d1) >> bits;
-            p0 |= (uint32_t)(d0 & 255) << (8 * i); p1 |= (uint32_t)(d1 & 255) << (8 * i); p2 |= (uint32_t)(iv & 255) << (8 * i);
+            int d0, d1, d2;
+            act_digits(f[i], inv, QMAX, bits, d0, d1, d2);
+            p0 |= (uint32_t)(d0 & 255) << (8 * i); p1 |= (uint32_t)(d1 & 255) << (8 * i); p2 |= (uint32_t)(d2 & 255) << (8 * i);
         }
         *reinterpret_cast<uint32_t *>(q + k) = p0;
         *reinterpret_cast<uint32_t *>(q + ncols + k) = p1;

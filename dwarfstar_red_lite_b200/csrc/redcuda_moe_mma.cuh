@@ -21,6 +21,8 @@ struct MmaArgs {
     uint32_t S, tiles_per_warp, item_tok, item_class;    // filled by launch_moe_mma
     float dw1, dw2;                // weights of digits 1 and 2 (2^bits, 4^bits), filled by launch_moe_mma
     uint32_t *work;                // nibble-layout kernels: the launch's unit counter, zeroed by the grouping kernel
+    const float *x_raw;            // nibble-layout gate/up of a single token: its fp32 activation row, quantised inside the kernel (xq / sx unused)
+    uint32_t act_bits;             // digit width, filled by the launcher
 };
 
 // Builds the magnitude and sign tables of the tensor-core path from the IQ2_XXS codebook (current device).
@@ -43,6 +45,37 @@ bool nib_shape_ok(uint32_t nrows, uint32_t ncols);
 int launch_nib_repack(const uint8_t *planar, uint32_t nrows, uint32_t ncols, uint8_t *dst, cudaStream_t s);
 // gate/up (A.w1 set) or down projection of the grouped pairs, work items of at most 8 pairs; persistent kernel
 int launch_nib_experts(MmaArgs &A, uint32_t max_items, cudaStream_t s);
+// Single token, nibble layout: down projection of the token's top_k experts for one 16-row tile per block, the shared
+// expert's down rows, and the tail out = resid + sum_k w_k * expert_k + shared * scalar, in router order — the fusion of
+// redmetal_topk_down_tail (native/redmetal_topk.m:254-280). The act rows are quantised inside the kernel.
+struct NibTailArgs {
+    const uint8_t *w_down; uint64_t mat_bytes;       // nibble-layout down matrices of the shard, bytes of one
+    uint32_t nrows, ncols, expert_begin, n_local, top_k;
+    const uint32_t *ids; const float *wk;            // the token's experts and router weights [top_k]
+    const float *act; uint32_t act_stride;            // act[k][ncols]: SiLU(gate) * up of expert k
+    const uint8_t *sh_down; uint64_t sh_nb;           // shared expert's down matrix (planar Q6_K), or null
+    const float *sh_act, *scalar, *resid;             // shared activation [ncols], its scalar gate [1], residual [nrows] or null
+    float *out;
+    float dw1, dw2; uint32_t bits;                    // filled by the launcher
+    uint32_t *status;
+};
+bool nib_tail_ok(uint32_t top_k, uint32_t nrows, uint32_t ncols);
+int launch_nib_down_tail(NibTailArgs &A, cudaStream_t s);
+
+#ifdef __CUDACC__
+// the three balanced digits of one activation and the row scale: the arithmetic of k_quant_act, shared with the kernels
+// that quantise a row themselves
+__device__ __forceinline__ float act_qmax(uint32_t bits) { return bits == 8u ? 8355711.0f : 1040000.0f; }    // largest value three digits hold: 127 * (65536 + 256 + 1), or just below 63.5 * 16384
+__device__ __forceinline__ float act_scale(float mx, float qmax) { return (mx > 0.f && mx < INFINITY) ? mx / qmax : 1.0f; }
+__device__ __forceinline__ void act_digits(float f, float inv, float qmax, uint32_t bits, int &d0, int &d1, int &d2) {
+    const int half = 1 << (bits - 1u), mask = (1 << bits) - 1;
+    int iv = __float2int_rn(fminf(fmaxf(f * inv, -qmax), qmax));
+    d0 = ((iv + half) & mask) - half; iv = (iv - d0) >> bits;
+    d1 = ((iv + half) & mask) - half; iv = (iv - d1) >> bits;
+    d2 = iv;
+}
+#endif
+
 // Q6_K matrix (or gate/up pair with SiLU*mul when w1 != nullptr) x ntok activation rows given as digits (redcuda_q6k_mma.cu)
 int launch_q6k_mma(const uint8_t *w0, const uint8_t *w1, uint64_t nb, uint32_t nrows, uint32_t ncols, uint32_t ntok,
                    const int8_t *xq, const float *sx, float *out, uint32_t out_stride, const char *tag, cudaStream_t s);

@@ -31,6 +31,7 @@
 // epilogue needs no exchange.
 #define RC_PDL_DEFAULT 0
 #include "redcuda_common.cuh"
+#include "redcuda_dot.cuh"
 #include "redcuda_kernels.cuh"
 #include "redcuda_moe_mma.cuh"
 #include "../../include/redcuda.h"
@@ -148,7 +149,10 @@ __device__ __forceinline__ bool nb_wait(uint32_t bar, uint32_t parity) {
     return false;
 }
 
-constexpr uint32_t NIB_STAGES = 3u, NIB_WARPS = 8u;
+constexpr uint32_t NIB_WARPS = 8u;
+// records in flight per warp: 3 for batches (two blocks per SM), 8 for a single token (few units, one block per SM: a
+// warp requests its whole tile at once, one HBM round trip instead of three)
+constexpr uint32_t NIB_STAGES_BATCH = 3u, NIB_STAGES_ONE = 8u;
 constexpr uint32_t NIB_TAB_POS = 0x002b1908u, NIB_TAB_NEG = 0x00d5e7f8u;      // bytes 8, 25, 43, 0 and -8, -25, -43, 0
 
 // One warp: 16 rows x one 256-column block (a record in shared memory) against NT 8-column tiles of activation digits.
@@ -194,9 +198,9 @@ struct NibUnit {
     uint32_t tile0, n;         // first 16-row tile of this warp and the number of records it streams in the unit
 };
 
-// A warp's private ring of NIB_STAGES record slots. Records are requested in stream order: first the rest of the
+// A warp's private ring of STAGES record slots. Records are requested in stream order: first the rest of the
 // current unit (cur_*), then the first ones of the next unit (nxt_*), so the ring never drains at a unit boundary.
-// Between two reads exactly one request is made, which keeps NIB_STAGES - 1 records in flight behind the one being read.
+// Between two reads exactly one request is made, which keeps STAGES - 1 records in flight behind the one being read.
 struct NibRing {
     uint32_t stage_s, bar_s;           // shared-memory addresses of slot 0 and of its mbarrier
     uint32_t prod, cons, phase;        // next slot to fill / to read; bit s = parity the next read of slot s waits for
@@ -204,13 +208,14 @@ struct NibRing {
     uint32_t cur_rem, nxt_rem, nxt_taken;
     uint32_t timed_out;
 };
+template <uint32_t STAGES>
 __device__ __forceinline__ void nib_request(NibRing &R, uint32_t lane) {
     const uint8_t *src;
     if (R.cur_rem) { src = R.cur_src; R.cur_src += NIB_REC; --R.cur_rem; }
     else if (R.nxt_rem) { src = R.nxt_src; R.nxt_src += NIB_REC; --R.nxt_rem; ++R.nxt_taken; }
     else return;
     if (lane == 0) nb_fetch(R.stage_s + R.prod * NIB_REC, src, R.bar_s + 8u * R.prod);
-    R.prod = R.prod + 1u == NIB_STAGES ? 0u : R.prod + 1u;
+    R.prod = R.prod + 1u == STAGES ? 0u : R.prod + 1u;
 }
 // waits for the oldest record; returns its slot. After a wait ran out no further wait is attempted (the results of the
 // launch are void: the caller raises the status word).
@@ -219,15 +224,16 @@ __device__ __forceinline__ uint32_t nib_acquire(NibRing &R) {
     if (!R.timed_out && !nb_wait(R.bar_s + 8u * slot, (R.phase >> slot) & 1u)) R.timed_out = 1u;
     return slot;
 }
+template <uint32_t STAGES>
 __device__ __forceinline__ void nib_release(NibRing &R) {
     __syncwarp();                      // every lane has read the slot: it may be refilled
     R.phase ^= 1u << R.cons;
-    R.cons = R.cons + 1u == NIB_STAGES ? 0u : R.cons + 1u;
+    R.cons = R.cons + 1u == STAGES ? 0u : R.cons + 1u;
 }
 
 // All tiles of one unit for one warp, NT column tiles of digits in use (1: pairs packed into one tile, 3: a tile per digit).
 // vals[ti][.] = (row g, pair slot 0), (row g, pair slot 1), (row g + 8, slot 0), (row g + 8, slot 1), times the pair's scale.
-template <int NT, uint32_t BPR, uint32_t BPITCH, uint32_t TPW>
+template <int NT, uint32_t BPR, uint32_t BPITCH, uint32_t TPW, uint32_t STAGES>
 __device__ __forceinline__ void nib_tiles(NibRing &R, const uint8_t *my_stage, const int8_t *Bbase, uint32_t tiles, uint32_t lane, uint32_t g, uint32_t t,
                                           const int (&z)[4], float dw1, float dw2, const float (&sxv)[2], float (&vals)[TPW][4]) {
     for (uint32_t ti = 0; ti < tiles; ++ti) {
@@ -235,10 +241,10 @@ __device__ __forceinline__ void nib_tiles(NibRing &R, const uint8_t *my_stage, c
 #pragma unroll
         for (int n = 0; n < 3; ++n) { out[n][0] = out[n][1] = out[n][2] = out[n][3] = 0.f; }
         for (uint32_t c = 0; c < BPR; ++c) {
-            nib_request(R, lane);
+            nib_request<STAGES>(R, lane);
             const uint32_t slot = nib_acquire(R);
             nib_chunk<NT, BPITCH>(my_stage + slot * NIB_REC, Bbase + c * 256u, g, t, z, out);
-            nib_release(R);
+            nib_release<STAGES>(R);
         }
         float v[2][2];                 // [row half][pair slot]
         if (NT == 1) {
@@ -261,19 +267,19 @@ __device__ __forceinline__ void nib_tiles(NibRing &R, const uint8_t *my_stage, c
 
 // GATEUP: warps 0-3 take the gate rows of 4 x TPW tiles, warps 4-7 the up rows of the same tiles; the up values cross a
 // small shared buffer and the gate warps store SiLU(gate) * up. Otherwise (down projection) 8 x TPW tiles per unit.
-template <bool GATEUP, uint32_t NCOLS>
-__global__ void __launch_bounds__(NIB_WARPS * 32u, 2) k_nib_experts(const __grid_constant__ MmaArgs A) {
+template <bool GATEUP, uint32_t NCOLS, uint32_t STAGES>
+__global__ void __launch_bounds__(NIB_WARPS * 32u, STAGES == NIB_STAGES_BATCH ? 2 : 1) k_nib_experts(const __grid_constant__ MmaArgs A) {
     pdl_prologue();
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr uint32_t BPR = NCOLS / 256u, TPW = BPR >= 8u ? 1u : 8u / BPR, WSLOTS = GATEUP ? 4u : 8u, UNIT_TILES = WSLOTS * TPW;
     constexpr uint32_t BPITCH = NCOLS + 32u, V16 = NCOLS / 16u;
     __shared__ uint32_t s_unit[2];
     __shared__ volatile uint32_t s_fail;
-    __shared__ __align__(8) uint64_t s_bar[NIB_WARPS][NIB_STAGES];
+    __shared__ __align__(8) uint64_t s_bar[NIB_WARPS][STAGES];
     __shared__ __align__(16) float4 s_ex[GATEUP ? TPW : 1u][4][32];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
-    uint8_t *my_stage = smem + warp * (NIB_STAGES * NIB_REC);
-    int8_t *Bs = reinterpret_cast<int8_t *>(smem + NIB_WARPS * NIB_STAGES * NIB_REC);
+    uint8_t *my_stage = smem + warp * (STAGES * NIB_REC);
+    int8_t *Bs = reinterpret_cast<int8_t *>(smem + NIB_WARPS * STAGES * NIB_REC);
     const uint32_t ntile_rows = A.nrows >> 4, U = (ntile_rows + UNIT_TILES - 1u) / UNIT_TILES;
     const uint32_t total = *A.n_items * U;
     const bool is_up = GATEUP && warp >= 4u;
@@ -296,11 +302,45 @@ __global__ void __launch_bounds__(NIB_WARPS * 32u, 2) k_nib_experts(const __grid
 
     if (tid == 0) { s_unit[0] = atomicAdd(A.work, 1u); s_fail = 0u; }
     if (lane == 0) {
-        for (uint32_t i = 0; i < NIB_STAGES; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(R.bar_s + 8u * i));
+        for (uint32_t i = 0; i < STAGES; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(R.bar_s + 8u * i));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
+    __shared__ float s_red[NIB_WARPS], s_sx;
+    if (A.x_raw) {
+        // single token: every unit multiplies the same activation row, so the block turns it into digits itself (the
+        // arithmetic of k_quant_act) — columns 0..2 of the one tile in use, columns 3..7 zero
+        float mx = 0.f;
+        for (uint32_t k = tid * 4u; k < NCOLS; k += NIB_WARPS * 128u) {
+            const float4 v = *reinterpret_cast<const float4 *>(A.x_raw + k);
+            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        }
+        for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) s_red[warp] = mx;
+        __syncthreads();
+        mx = s_red[0];
+        for (uint32_t w = 1; w < NIB_WARPS; ++w) mx = fmaxf(mx, s_red[w]);
+        const float qmax = act_qmax(A.act_bits), scale = act_scale(mx, qmax), inv = 1.0f / scale;
+        if (tid == 0) s_sx = scale;
+        for (uint32_t k = tid * 4u; k < NCOLS; k += NIB_WARPS * 128u) {
+            const float4 v = *reinterpret_cast<const float4 *>(A.x_raw + k);
+            const float f[4] = {v.x, v.y, v.z, v.w};
+            uint32_t p0 = 0, p1 = 0, p2 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                int d0, d1, d2;
+                act_digits(f[i], inv, qmax, A.act_bits, d0, d1, d2);
+                p0 |= (uint32_t)(d0 & 255) << (8 * i); p1 |= (uint32_t)(d1 & 255) << (8 * i); p2 |= (uint32_t)(d2 & 255) << (8 * i);
+            }
+            *reinterpret_cast<uint32_t *>(Bs + k) = p0;
+            *reinterpret_cast<uint32_t *>(Bs + BPITCH + k) = p1;
+            *reinterpret_cast<uint32_t *>(Bs + 2u * BPITCH + k) = p2;
+#pragma unroll
+            for (uint32_t col = 3u; col < 8u; ++col) *reinterpret_cast<uint32_t *>(Bs + col * BPITCH + k) = 0u;
+        }
+        __syncthreads();
+    }
     uint32_t cur = s_unit[0], par = 0u, cur_item = 0xffffffffu;
     uint32_t ahead = 0u;             // records of the CURRENT unit already requested (while the previous unit was multiplying)
     int zero[4];                     // opaque to the compiler: four registers that stay zero, the accumulator input of every MMA
@@ -309,11 +349,11 @@ __global__ void __launch_bounds__(NIB_WARPS * 32u, 2) k_nib_experts(const __grid
     if (cur < total) decode(cur, I);
     while (cur < total) {
         if (tid == 0) s_unit[par ^ 1u] = atomicAdd(A.work, 1u);
-        // this unit's stream; NIB_STAGES - 1 of its records are put in flight before the first read
+        // this unit's stream; STAGES - 1 of its records are put in flight before the first read
         R.cur_src = I.rec + (size_t)ahead * NIB_REC; R.cur_rem = I.n - ahead; R.nxt_rem = 0u; R.nxt_taken = 0u;
-        for (uint32_t i = ahead; i + 1u < NIB_STAGES; ++i) nib_request(R, lane);
+        for (uint32_t i = ahead; i + 1u < STAGES; ++i) nib_request<STAGES>(R, lane);
         const bool packed = I.nt <= 2u;
-        if (I.item != cur_item) {    // activation digits of the item (every warp passed the barrier that ended the last unit)
+        if (!A.x_raw && I.item != cur_item) {    // activation digits of the item (every warp passed the barrier that ended the last unit)
             const uint32_t ncolb = packed ? 8u : 24u;
             for (uint32_t i = tid; i < ncolb * V16; i += NIB_WARPS * 32u) {
                 const uint32_t col = i / V16, k = (i - col * V16) << 4;
@@ -332,18 +372,18 @@ __global__ void __launch_bounds__(NIB_WARPS * 32u, 2) k_nib_experts(const __grid
         for (uint32_t j = 0; j < 2u; ++j) {
             const uint32_t tk = packed ? (t >> 1) : 2u * t + j;
             ok[j] = packed ? (j == 0u && (t & 1u) == 0u && tk < I.nt) : tk < I.nt;
-            if (ok[j]) { prow[j] = A.sorted[I.p0 + tk]; sxv[j] = A.sx[prow[j] / A.x_div]; }
+            if (ok[j]) { prow[j] = A.sorted[I.p0 + tk]; sxv[j] = A.x_raw ? s_sx : A.sx[prow[j] / A.x_div]; }
         }
         __syncthreads();             // digits and the next unit's number are in shared memory
         const uint32_t nxt = s_unit[par ^ 1u];
         const bool nv = nxt < total;
-        if (nv) { decode(nxt, N); if (I.n + 1u >= NIB_STAGES) { R.nxt_src = N.rec; R.nxt_rem = N.n; } }     // a unit shorter than the ring does not look ahead
+        if (nv) { decode(nxt, N); if (I.n + 1u >= STAGES) { R.nxt_src = N.rec; R.nxt_rem = N.n; } }     // a unit shorter than the ring does not look ahead
 
         float vals[TPW][4];
         const uint32_t tiles = I.n / BPR;
         const int8_t *Bbase = Bs + (size_t)g * BPITCH + 8u * t;
-        if (packed) nib_tiles<1, BPR, BPITCH, TPW>(R, my_stage, Bbase, tiles, lane, g, t, zero, A.dw1, A.dw2, sxv, vals);
-        else nib_tiles<3, BPR, BPITCH, TPW>(R, my_stage, Bbase, tiles, lane, g, t, zero, A.dw1, A.dw2, sxv, vals);
+        if (packed) nib_tiles<1, BPR, BPITCH, TPW, STAGES>(R, my_stage, Bbase, tiles, lane, g, t, zero, A.dw1, A.dw2, sxv, vals);
+        else nib_tiles<3, BPR, BPITCH, TPW, STAGES>(R, my_stage, Bbase, tiles, lane, g, t, zero, A.dw1, A.dw2, sxv, vals);
         if (R.timed_out && lane == 0) { s_fail = 1u; if (A.status) A.status[ST_TIMEOUT] = 1u; }
         if (GATEUP) {
             if (is_up) for (uint32_t ti = 0; ti < tiles; ++ti) s_ex[ti][wslot][lane] = make_float4(vals[ti][0], vals[ti][1], vals[ti][2], vals[ti][3]);
@@ -380,7 +420,135 @@ __global__ void __launch_bounds__(NIB_WARPS * 32u, 2) k_nib_experts(const __grid
     }
 }
 
-static size_t nib_smem_bytes(uint32_t ncols) { return (size_t)NIB_WARPS * NIB_STAGES * NIB_REC + 24u * (size_t)(ncols + 32u); }
+// ---- single token: down projection of the selected experts + shared expert's down rows + weighted sum + residual ----
+// grid = nrows / 16 (one 16-row tile per block), block = top_k + 2 warps: warp k < top_k takes expert k (its tile's
+// records arrive by bulk copy while the warp quantises expert k's activation row), the last two warps take the shared
+// expert's 16 rows (Q6_K, CUDA cores). Partial rows meet in shared memory and are summed in router order.
+constexpr uint32_t NIB_TAIL_MAX_K = 14u;
+template <uint32_t NCOLS>
+__global__ void __launch_bounds__((NIB_TAIL_MAX_K + 2u) * 32u) k_nib_down_tail(const __grid_constant__ NibTailArgs A) {
+    pdl_prologue();
+    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr uint32_t BPR = NCOLS / 256u, BPITCH = NCOLS + 32u, PER_LANE = NCOLS / 32u;
+    __shared__ __align__(8) uint64_t s_bar[NIB_TAIL_MAX_K];
+    __shared__ float s_part[NIB_TAIL_MAX_K][16], s_sh[16];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u, K = A.top_k;
+    uint8_t *recs = smem;                                                    // [K][BPR] records
+    int8_t *digits = reinterpret_cast<int8_t *>(smem + K * BPR * NIB_REC);   // [K][3][BPITCH]
+    int8_t *zrow = digits + K * 3u * BPITCH;                                 // one row of zeros: digit columns 3..7 of every tile
+    float *xs = reinterpret_cast<float *>(zrow + BPITCH);                    // shared expert's activation, padded rows of redcuda_dot.cuh
+    const uint32_t row0 = blockIdx.x * 16u;
+
+    for (uint32_t k = tid * 4u; k < BPITCH; k += blockDim.x * 4u) *reinterpret_cast<uint32_t *>(zrow + k) = 0u;
+    if (A.sh_down) for (uint32_t k = tid * 4u; k < NCOLS; k += blockDim.x * 4u) *reinterpret_cast<float4 *>(xs + xi(k)) = *reinterpret_cast<const float4 *>(A.sh_act + k);
+    if (tid < 16u) s_sh[tid] = 0.f;
+    if (warp < K && lane == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(nb_smem(&s_bar[warp])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp < K) {
+        uint32_t e = A.ids[warp] - A.expert_begin;
+        bool live = true;
+        if (e >= A.n_local) { if (A.status && lane == 0) A.status[ST_EXPERT_RANGE] = 1u; e = 0u; live = false; }      // never index the arena with a foreign id
+        uint8_t *my_rec = recs + warp * BPR * NIB_REC;
+        const uint32_t bar = nb_smem(&s_bar[warp]);
+        if (lane == 0) {
+            const uint8_t *src = A.w_down + (size_t)e * A.mat_bytes + (size_t)blockIdx.x * BPR * NIB_REC;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(BPR * NIB_REC) : "memory");
+            for (uint32_t c = 0; c < BPR; ++c)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             :: "r"(nb_smem(my_rec + c * NIB_REC)), "l"(src + (size_t)c * NIB_REC), "r"(NIB_REC), "r"(bar) : "memory");
+        }
+        // this expert's activation row -> digits (the arithmetic of k_quant_act), while the records are in flight
+        const float *ar = A.act + (size_t)warp * A.act_stride;
+        float v[PER_LANE];
+        float mx = 0.f;
+#pragma unroll
+        for (uint32_t i = 0; i < PER_LANE / 4u; ++i) {
+            const float4 q = *reinterpret_cast<const float4 *>(ar + lane * 4u + 128u * i);
+            v[4 * i] = q.x; v[4 * i + 1] = q.y; v[4 * i + 2] = q.z; v[4 * i + 3] = q.w;
+            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(q.x), fabsf(q.y)), fmaxf(fabsf(q.z), fabsf(q.w))));
+        }
+        for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float qmax = act_qmax(A.bits), sx = act_scale(mx, qmax), inv = 1.0f / sx;
+        int8_t *mine = digits + warp * 3u * BPITCH;
+#pragma unroll
+        for (uint32_t i = 0; i < PER_LANE / 4u; ++i) {
+            uint32_t p0 = 0, p1 = 0, p2 = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                int d0, d1, d2;
+                act_digits(v[4 * i + j], inv, qmax, A.bits, d0, d1, d2);
+                p0 |= (uint32_t)(d0 & 255) << (8 * j); p1 |= (uint32_t)(d1 & 255) << (8 * j); p2 |= (uint32_t)(d2 & 255) << (8 * j);
+            }
+            const uint32_t k = lane * 4u + 128u * i;
+            *reinterpret_cast<uint32_t *>(mine + k) = p0;
+            *reinterpret_cast<uint32_t *>(mine + BPITCH + k) = p1;
+            *reinterpret_cast<uint32_t *>(mine + 2u * BPITCH + k) = p2;
+        }
+        __syncwarp();
+        if (!__all_sync(0xffffffffu, nb_wait(bar, 0u))) { live = false; if (A.status && lane == 0) A.status[ST_TIMEOUT] = 1u; }
+        float out[3][4];
+#pragma unroll
+        for (int n = 0; n < 3; ++n) { out[n][0] = out[n][1] = out[n][2] = out[n][3] = 0.f; }
+        int zero[4];
+        asm volatile("mov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\tmov.b32 %2, 0;\n\tmov.b32 %3, 0;" : "=r"(zero[0]), "=r"(zero[1]), "=r"(zero[2]), "=r"(zero[3]));
+        const int8_t *Bl = (g < 3u ? mine + g * BPITCH : zrow) + 8u * t;       // columns 0..2 = the pair's three digits, the rest of the tile is zero
+        if (live) for (uint32_t c = 0; c < BPR; ++c) nib_chunk<1, BPITCH>(my_rec + c * NIB_REC, Bl + c * 256u, g, t, zero, out);
+        const uint32_t src = (lane & ~3u) + 1u;
+        const float x0 = __shfl_sync(0xffffffffu, out[0][0], src), x1 = __shfl_sync(0xffffffffu, out[0][2], src);
+        if (t == 0u) {
+            s_part[warp][g] = (out[0][0] + A.dw1 * out[0][1] + A.dw2 * x0) * sx;
+            s_part[warp][g + 8u] = (out[0][2] + A.dw1 * out[0][3] + A.dw2 * x1) * sx;
+        }
+    } else if (A.sh_down) {
+        const uint32_t sw = warp - K;                                       // 0 or 1: rows 8 sw .. 8 sw + 7 of the tile
+        uint32_t lpr = 32u;
+        while (lpr > (NCOLS >> 6)) lpr >>= 1;
+        const uint32_t rw = 32u / lpr, slot = lane / lpr, sub = lane % lpr;
+        const SBooks sb{nullptr, nullptr};
+        for (uint32_t r = 0; r < 8u; r += rw) {
+            const uint32_t rr = 8u * sw + r + slot;                         // rw <= 8 for every row length from 256 up
+            float a[1];
+            row_dot<RC_Q6_K, 1>(A.sh_down, A.sh_nb, (uint64_t)(row0 + rr), NCOLS, lpr, sub, xs, x_padded(NCOLS), sb, a);
+            if (sub == 0u) s_sh[rr] = a[0];
+        }
+    }
+    __syncthreads();
+    if (tid < 16u) {
+        const uint32_t row = row0 + tid;
+        float acc = 0.f;
+        for (uint32_t k = 0; k < K; ++k) { const float wk = A.wk[k]; if (wk != 0.f) acc += wk * s_part[k][tid]; }
+        if (A.sh_down) acc += s_sh[tid] * (A.scalar ? A.scalar[0] : 1.0f);
+        if (A.resid) acc += A.resid[row];
+        A.out[row] = acc;
+    }
+}
+
+bool nib_tail_ok(uint32_t top_k, uint32_t nrows, uint32_t ncols) {
+    return top_k >= 1u && top_k <= NIB_TAIL_MAX_K && nrows % 16u == 0 && (ncols == 256u || ncols == 512u || ncols == 1024u);
+}
+
+int launch_nib_down_tail(NibTailArgs &A, cudaStream_t s) {
+    RC_REQUIRE(nib_tail_ok(A.top_k, A.nrows, A.ncols), "nibble down tail: top_k %u, %ux%u is not a shape it serves", A.top_k, A.nrows, A.ncols);
+    A.bits = act_digit_bits(); A.dw1 = (float)(1u << A.bits); A.dw2 = A.dw1 * A.dw1;
+    const uint32_t bpr = A.ncols / 256u, bpitch = A.ncols + 32u;
+    const size_t smem = (size_t)A.top_k * bpr * NIB_REC + (size_t)A.top_k * 3u * bpitch + bpitch + (size_t)x_padded(A.ncols) * 4u + 16u;
+    const uint32_t threads = (A.top_k + 2u) * 32u, grid = A.nrows / 16u;
+    prof_begin("moe_down_tail", s);
+#define RC_TAIL_LAUNCH(NC) do { \
+        RC_CUDA(cudaFuncSetAttribute(k_nib_down_tail<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        RC_LAUNCH((k_nib_down_tail<NC>), grid, threads, smem, s, A); } while (0)
+    if (A.ncols == 256u) RC_TAIL_LAUNCH(256u); else if (A.ncols == 512u) RC_TAIL_LAUNCH(512u); else RC_TAIL_LAUNCH(1024u);
+#undef RC_TAIL_LAUNCH
+    prof_end(s);
+    RC_LAUNCHED();
+    return 1;
+}
+
+static size_t nib_smem_bytes(uint32_t ncols, uint32_t stages) { return (size_t)NIB_WARPS * stages * NIB_REC + 24u * (size_t)(ncols + 32u); }
 
 // A.w0 / A.w1: nibble-layout expert matrices (gate and up, or down and nullptr); A.work: the unit counter of this launch
 // (zeroed by the grouping kernel); items are cut with at most 8 pairs. max_items bounds the number of work items.
@@ -388,23 +556,29 @@ int launch_nib_experts(MmaArgs &A, uint32_t max_items, cudaStream_t s) {
     const bool gateup = A.w1 != nullptr;
     RC_REQUIRE(nib_shape_ok(A.nrows, A.ncols), "nibble experts: matrix %ux%u is not tileable", A.nrows, A.ncols);
     RC_REQUIRE(A.work != nullptr && A.item_tok >= 1u && A.item_tok <= 8u, "nibble experts: work counter missing or items of %u pairs", A.item_tok);
-    A.dw1 = (float)(1u << act_digit_bits()); A.dw2 = A.dw1 * A.dw1;
+    A.act_bits = act_digit_bits(); A.dw1 = (float)(1u << A.act_bits); A.dw2 = A.dw1 * A.dw1;
+    RC_REQUIRE(!A.x_raw || (gateup && A.item_tok == 1u), "nibble experts: in-kernel quantisation serves the gate/up of a single token");
     static int sm_count = 0;
     if (!sm_count) { int dev = 0; RC_CUDA(cudaGetDevice(&dev)); RC_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev)); }
     const uint32_t bpr = A.ncols / 256u, tpw = bpr >= 8u ? 1u : 8u / bpr, unit_tiles = (gateup ? 4u : 8u) * tpw;
     const uint64_t units = (uint64_t)max_items * ((A.nrows / 16u + unit_tiles - 1u) / unit_tiles);
-    const uint32_t grid = (uint32_t)(units < 2u * (uint64_t)sm_count ? (units ? units : 1u) : 2u * (uint64_t)sm_count);
-    const size_t smem = nib_smem_bytes(A.ncols);
+    const bool one = A.x_raw != nullptr;          // single token: deep rings, one block per SM
+    const uint32_t per_sm = one ? 1u : 2u, stages = one ? NIB_STAGES_ONE : NIB_STAGES_BATCH;
+    const uint32_t grid = (uint32_t)(units < per_sm * (uint64_t)sm_count ? (units ? units : 1u) : per_sm * (uint64_t)sm_count);
+    const size_t smem = nib_smem_bytes(A.ncols, stages);
     prof_begin(gateup ? "moe_gateup" : "moe_down", s);
-#define RC_NIB_LAUNCH(GU, NC) do { \
-        RC_CUDA(cudaFuncSetAttribute(k_nib_experts<GU, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        RC_LAUNCH((k_nib_experts<GU, NC>), grid, NIB_WARPS * 32u, smem, s, A); } while (0)
-    if (gateup) {
-        if (A.ncols == 2048u) RC_NIB_LAUNCH(true, 2048u); else if (A.ncols == 1024u) RC_NIB_LAUNCH(true, 1024u);
-        else if (A.ncols == 512u) RC_NIB_LAUNCH(true, 512u); else RC_NIB_LAUNCH(true, 256u);
+#define RC_NIB_LAUNCH(GU, NC, ST) do { \
+        RC_CUDA(cudaFuncSetAttribute(k_nib_experts<GU, NC, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        RC_LAUNCH((k_nib_experts<GU, NC, ST>), grid, NIB_WARPS * 32u, smem, s, A); } while (0)
+    if (one) {
+        if (A.ncols == 2048u) RC_NIB_LAUNCH(true, 2048u, NIB_STAGES_ONE); else if (A.ncols == 1024u) RC_NIB_LAUNCH(true, 1024u, NIB_STAGES_ONE);
+        else if (A.ncols == 512u) RC_NIB_LAUNCH(true, 512u, NIB_STAGES_ONE); else RC_NIB_LAUNCH(true, 256u, NIB_STAGES_ONE);
+    } else if (gateup) {
+        if (A.ncols == 2048u) RC_NIB_LAUNCH(true, 2048u, NIB_STAGES_BATCH); else if (A.ncols == 1024u) RC_NIB_LAUNCH(true, 1024u, NIB_STAGES_BATCH);
+        else if (A.ncols == 512u) RC_NIB_LAUNCH(true, 512u, NIB_STAGES_BATCH); else RC_NIB_LAUNCH(true, 256u, NIB_STAGES_BATCH);
     } else {
-        if (A.ncols == 2048u) RC_NIB_LAUNCH(false, 2048u); else if (A.ncols == 1024u) RC_NIB_LAUNCH(false, 1024u);
-        else if (A.ncols == 512u) RC_NIB_LAUNCH(false, 512u); else RC_NIB_LAUNCH(false, 256u);
+        if (A.ncols == 2048u) RC_NIB_LAUNCH(false, 2048u, NIB_STAGES_BATCH); else if (A.ncols == 1024u) RC_NIB_LAUNCH(false, 1024u, NIB_STAGES_BATCH);
+        else if (A.ncols == 512u) RC_NIB_LAUNCH(false, 512u, NIB_STAGES_BATCH); else RC_NIB_LAUNCH(false, 256u, NIB_STAGES_BATCH);
     }
 #undef RC_NIB_LAUNCH
     prof_end(s);
