@@ -681,3 +681,268 @@ int redcuda_moe_shared_device(redcuda_moe *m, uint32_t ntok, const float *x_dev,
 }
 
 }  // extern "C"
+
+// =====================================================================================================================
+// Expert-pool ABI v1 of the reference (include/redmetal_topk.h): a resident arena with the reference's bookkeeping kept
+// as counters. Slots hold raw GGUF bytes (the reference loads byte ranges without knowing their type); execute re-lays
+// the selected experts out planar into a scratch area and runs the CUDA-core expert kernel, which serves every
+// supported type — this is the parity entry point, not the decode path (that is redcuda_moe_*).
+// =====================================================================================================================
+#include "../../include/redmetal_topk.h"
+
+#include <fcntl.h>
+#include <unistd.h>
+#include <chrono>
+#include <vector>
+
+namespace {
+
+struct TopkPool {
+    int fd = -1, device = 0;
+    uint64_t slot_bytes = 0, bytes_read = 0, read_calls = 0;
+    double read_ms = 0.0;
+    uint32_t capacity = 0;
+    DevMem arena, scratch, table;
+    std::vector<uint32_t> generation, inflight;
+    std::vector<uint64_t> table_h;
+    uint32_t layers = 0, experts = 0;
+    uint8_t *pin = nullptr; size_t pin_bytes = 0;
+    cudaStream_t stream = nullptr;
+};
+
+double pool_now_ms() { return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
+
+int pool_arena(TopkPool *p) {
+    if (p->arena.p) return 1;
+    RC_CUDA(cudaSetDevice(p->device));
+    return p->arena.alloc((size_t)p->capacity * p->slot_bytes);
+}
+
+// gate/up + down + weighted sum of the selected slots on `s`; x_dev [hidden], out_dev [row_count]
+int pool_run(TopkPool *p, const uint32_t *slot_ids, const uint64_t *gate_bytes, const uint64_t *up_bytes, const uint64_t *down_bytes,
+             const float *router_weights, uint32_t top_k, uint32_t type_word, uint32_t hidden, uint32_t ffn, uint32_t row_start, uint32_t row_count,
+             const float *x_dev, float *out_dev, cudaStream_t s) {
+    const uint32_t tg = type_word & 255u, td = (type_word >> 8) & 255u ? (type_word >> 8) & 255u : tg;
+    RC_REQUIRE(rc_is_quant(tg) && rc_is_quant(td), "expert pool: ggml types %u / %u are not served (16, 14, 21)", tg, td);
+    RC_REQUIRE(top_k >= 1 && top_k <= REDCUDA_MAX_TOPK && hidden % 256u == 0 && ffn % 256u == 0, "expert pool: bad top_k or shape");
+    RC_REQUIRE(row_start + (uint64_t)row_count <= hidden && row_count, "expert pool: output rows outside the matrix");
+    if (!require_books(tg) || !require_books(td)) return 0;
+    const uint64_t gu_b = rc_matrix_bytes(tg, ffn, hidden), dn_b = rc_matrix_bytes(td, hidden, ffn);
+    RC_REQUIRE(gu_b % 16u == 0 && dn_b % 16u == 0, "expert pool: matrix sizes must be multiples of 16 bytes");
+    for (uint32_t k = 0; k < top_k; ++k) {
+        RC_REQUIRE(slot_ids[k] < p->capacity && p->generation[slot_ids[k]] != 0u, "expert pool: slot %u is empty or out of range", slot_ids[k]);
+        RC_REQUIRE(gate_bytes[k] == gu_b && up_bytes[k] == gu_b && down_bytes[k] == dn_b && gu_b * 2u + dn_b <= p->slot_bytes,
+                   "expert pool: slot %u byte counts do not match the type and shape", slot_ids[k]);
+    }
+    // scratch: planar copies of the selected experts, the grouping arrays, activations
+    const size_t a16 = 256;
+    size_t off = 0;
+    auto take = [&](size_t n) { const size_t o = off; off = (off + n + a16 - 1) / a16 * a16; return o; };
+    const size_t o_g = take(gu_b * top_k), o_u = take(gu_b * top_k), o_d = take(dn_b * top_k), o_idx = take((size_t)(3u * top_k + 8u) * 4u), o_w = take(top_k * 4u),
+                 o_act = take((size_t)top_k * ffn * 4u), o_tmp = take((size_t)top_k * hidden * 4u), o_out = take((size_t)hidden * 4u);
+    if (p->scratch.bytes < off && !p->scratch.alloc(off)) return 0;
+    uint8_t *S = p->scratch.as<uint8_t>();
+    const uint8_t *A0 = p->arena.as<uint8_t>();
+    for (uint32_t k = 0; k < top_k; ++k) {
+        const uint8_t *slot = A0 + (size_t)slot_ids[k] * p->slot_bytes;
+        if (!upload_matrix(tg, ffn, hidden, slot, true, S + o_g + k * gu_b, nullptr, s) || !upload_matrix(tg, ffn, hidden, slot + gu_b, true, S + o_u + k * gu_b, nullptr, s) ||
+            !upload_matrix(td, hidden, ffn, slot + 2u * gu_b, true, S + o_d + k * dn_b, nullptr, s)) return 0;
+    }
+    // grouping of a single token: pair k = group k = scratch expert k
+    uint32_t *hidx = reinterpret_cast<uint32_t *>(p->pin);
+    for (uint32_t k = 0; k < top_k; ++k) { hidx[k] = k; hidx[top_k + k] = k; hidx[2u * top_k + k] = k; }      // sorted | uexp | ustart
+    hidx[3u * top_k] = top_k; hidx[3u * top_k + 1u] = top_k;                                                  // ustart[top_k] | n_unique
+    memcpy(hidx + 3u * top_k + 8u, router_weights, top_k * 4u);
+    RC_CUDA(cudaMemcpyAsync(S + o_idx, hidx, (3u * top_k + 2u) * 4u, cudaMemcpyHostToDevice, s));
+    RC_CUDA(cudaMemcpyAsync(S + o_w, hidx + 3u * top_k + 8u, top_k * 4u, cudaMemcpyHostToDevice, s));
+    uint32_t *d_idx = reinterpret_cast<uint32_t *>(S + o_idx);
+    MoeArgs A{};
+    A.expert_begin = 0; A.n_local = top_k; A.status = status_words();
+    A.sorted = d_idx; A.uexp = d_idx + top_k; A.ustart = d_idx + 2u * top_k; A.n_unique = d_idx + 3u * top_k + 1u;
+    A.iq2 = books_iq2(); A.iq3s = books_iq3s();
+    for (int pass = 0; pass < 2; ++pass) {
+        const bool gu = pass == 0;
+        A.w0 = S + (gu ? o_g : o_d); A.w1 = gu ? S + o_u : nullptr; A.mat_bytes = gu ? gu_b : dn_b;
+        A.type = gu ? tg : td; A.nrows = gu ? ffn : hidden; A.ncols = gu ? hidden : ffn; A.nb = (uint64_t)A.nrows * (A.ncols / 256u);
+        A.x = gu ? x_dev : reinterpret_cast<const float *>(S + o_act); A.x_stride = gu ? hidden : ffn; A.x_div = gu ? top_k : 1u;
+        A.out = reinterpret_cast<float *>(S + (gu ? o_act : o_tmp)); A.out_stride = gu ? ffn : hidden; A.pair_silu = gu ? 1u : 0u;
+        uint32_t lpr = 32u;
+        while (lpr > (A.ncols >> 6)) lpr >>= 1;
+        A.rows_per_tile = 8u * (32u / lpr);
+        const dim3 grid((A.nrows + A.rows_per_tile - 1u) / A.rows_per_tile, top_k);
+        const size_t smem = (size_t)x_padded(A.ncols) * sizeof(float);
+        RC_REQUIRE(smem <= 200u * 1024u, "expert pool: row length %u too large", A.ncols);
+        if (smem > 48u * 1024u) RC_CUDA(cudaFuncSetAttribute(k_moe_experts<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        RC_LAUNCH((k_moe_experts<1>), grid, 256, smem, s, A);
+        RC_LAUNCHED();
+    }
+    RC_LAUNCH((k_moe_combine), dim3((hidden / 4u + 255u) / 256u, 1), 256, 0, s, reinterpret_cast<const float *>(S + o_tmp), reinterpret_cast<const float *>(S + o_w), top_k,
+              (const float *)nullptr, (const float *)nullptr, (const float *)nullptr, reinterpret_cast<float *>(S + o_out), hidden, (const uint32_t *)nullptr);
+    RC_LAUNCHED();
+    RC_CUDA(cudaMemcpyAsync(out_dev, S + o_out + (size_t)row_start * 4u, (size_t)row_count * 4u, cudaMemcpyDeviceToDevice, s));
+    return 1;
+}
+
+}  // namespace
+
+extern "C" {
+
+uint32_t redmetal_topk_abi_version(void) { return 1u; }
+const char *redmetal_topk_last_error(void) { return redcuda_last_error(); }
+
+redmetal_topk_pool_t redmetal_topk_pool_create(const char *model_path, uint64_t budget_bytes, uint64_t slot_bytes, uint32_t slots_per_slab,
+                                               const int8_t *, uint32_t, const int8_t *, uint32_t) {
+    (void)slots_per_slab;
+    if (!require_device()) return nullptr;
+    if (!model_path || !slot_bytes || slot_bytes % 16u || budget_bytes < slot_bytes) { set_error("expert pool: model path, a slot size that is a multiple of 16 and a budget of at least one slot are required"); return nullptr; }
+    TopkPool *p = new (std::nothrow) TopkPool();
+    if (!p) { set_error("expert pool: out of host memory"); return nullptr; }
+    p->fd = open(model_path, O_RDONLY);
+    if (p->fd < 0) { set_error("expert pool: cannot open %s", model_path); delete p; return nullptr; }
+    cudaGetDevice(&p->device);
+    p->slot_bytes = slot_bytes;
+    const uint64_t cap = budget_bytes / slot_bytes;
+    p->capacity = cap > 0xffffffffull ? 0xffffffffu : (uint32_t)cap;
+    p->generation.assign(p->capacity, 0u); p->inflight.assign(p->capacity, 0u);
+    p->pin_bytes = (size_t)slot_bytes > (1u << 16) ? (size_t)slot_bytes : (1u << 16);
+    if (cudaMallocHost((void **)&p->pin, p->pin_bytes) != cudaSuccess || cudaStreamCreateWithFlags(&p->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        set_error("expert pool: staging buffer or stream creation failed"); redmetal_topk_pool_destroy(p); return nullptr;
+    }
+    status_words();
+    return p;
+}
+
+void redmetal_topk_pool_destroy(redmetal_topk_pool_t h) {
+    TopkPool *p = (TopkPool *)h;
+    if (!p) return;
+    if (p->stream) { cudaStreamSynchronize(p->stream); cudaStreamDestroy(p->stream); }
+    if (p->pin) cudaFreeHost(p->pin);
+    if (p->fd >= 0) close(p->fd);
+    delete p;
+}
+
+int redmetal_topk_pool_set_classes(redmetal_topk_pool_t h, uint32_t n, const uint64_t *slot_bytes, const uint32_t *capacity) {
+    TopkPool *p = (TopkPool *)h;
+    RC_REQUIRE(p && n >= 1 && n <= 8u && slot_bytes && capacity, "expert pool: bad size classes");
+    uint64_t total = 0;
+    for (uint32_t i = 0; i < n; ++i) { RC_REQUIRE(slot_bytes[i] && slot_bytes[i] <= p->slot_bytes, "expert pool: class %u does not fit a slot", i); total += capacity[i]; }
+    RC_REQUIRE(total <= p->capacity && !p->arena.p, "expert pool: classes exceed the capacity, or slots are already in use");
+    return 1;       // one arena of full-size slots serves every class: nothing to re-partition
+}
+uint32_t redmetal_topk_pool_capacity(redmetal_topk_pool_t h) { return h ? ((TopkPool *)h)->capacity : 0u; }
+uint32_t redmetal_topk_pool_slab_count(redmetal_topk_pool_t h) { return h && ((TopkPool *)h)->arena.p ? 1u : 0u; }
+uint64_t redmetal_topk_pool_allocated_bytes(redmetal_topk_pool_t h) { return h ? ((TopkPool *)h)->arena.bytes : 0u; }
+uint64_t redmetal_topk_pool_bytes_read(redmetal_topk_pool_t h) { return h ? ((TopkPool *)h)->bytes_read : 0u; }
+uint64_t redmetal_topk_pool_read_calls(redmetal_topk_pool_t h) { return h ? ((TopkPool *)h)->read_calls : 0u; }
+double redmetal_topk_pool_read_ms(redmetal_topk_pool_t h) { return h ? ((TopkPool *)h)->read_ms : 0.0; }
+uint32_t redmetal_topk_pool_slot_generation(redmetal_topk_pool_t h, uint32_t slot) { TopkPool *p = (TopkPool *)h; return p && slot < p->capacity ? p->generation[slot] : 0u; }
+int redmetal_topk_pool_slot_inflight(redmetal_topk_pool_t h, uint32_t slot) { TopkPool *p = (TopkPool *)h; return p && slot < p->capacity ? (int)p->inflight[slot] : 0; }
+int redmetal_topk_pool_allocate_all(redmetal_topk_pool_t h) { RC_REQUIRE(h, "expert pool: null pool"); return pool_arena((TopkPool *)h); }
+
+int redmetal_topk_pool_load_expert(redmetal_topk_pool_t h, uint32_t slot, uint64_t g_off, uint64_t g_bytes, uint64_t u_off, uint64_t u_bytes, uint64_t d_off, uint64_t d_bytes,
+                                   uint64_t *bytes_read, double *elapsed_ms) {
+    TopkPool *p = (TopkPool *)h;
+    RC_REQUIRE(p && slot < p->capacity, "expert pool: slot %u out of range", slot);
+    RC_REQUIRE(g_bytes + u_bytes + d_bytes <= p->slot_bytes && g_bytes + u_bytes + d_bytes <= p->pin_bytes, "expert pool: expert of %llu bytes does not fit a slot",
+               (unsigned long long)(g_bytes + u_bytes + d_bytes));
+    RC_REQUIRE(p->inflight[slot] == 0u, "expert pool: slot %u is in flight", slot);
+    if (!pool_arena(p)) return 0;
+    const double t0 = pool_now_ms();
+    RC_CUDA(cudaStreamSynchronize(p->stream));          // the staging buffer is reused
+    const uint64_t offs[3] = {g_off, u_off, d_off}, lens[3] = {g_bytes, u_bytes, d_bytes};
+    size_t at = 0;
+    for (int i = 0; i < 3; ++i) {
+        size_t done = 0;
+        while (done < lens[i]) {
+            const ssize_t r = pread(p->fd, p->pin + at + done, lens[i] - done, (off_t)(offs[i] + done));
+            RC_REQUIRE(r > 0, "expert pool: short read at offset %llu", (unsigned long long)(offs[i] + done));
+            done += (size_t)r;
+        }
+        at += lens[i];
+    }
+    RC_CUDA(cudaMemcpyAsync(p->arena.as<uint8_t>() + (size_t)slot * p->slot_bytes, p->pin, at, cudaMemcpyHostToDevice, p->stream));
+    RC_CUDA(cudaStreamSynchronize(p->stream));
+    const double ms = pool_now_ms() - t0;
+    p->generation[slot] += 1u; p->bytes_read += at; p->read_calls += 3u; p->read_ms += ms;
+    if (bytes_read) *bytes_read = at;
+    if (elapsed_ms) *elapsed_ms = ms;
+    return 1;
+}
+
+int redmetal_topk_pool_slot_addresses(redmetal_topk_pool_t h, uint32_t slot, uint64_t g_bytes, uint64_t u_bytes, uint64_t d_bytes, uint64_t *ga, uint64_t *ua, uint64_t *da) {
+    TopkPool *p = (TopkPool *)h;
+    RC_REQUIRE(p && slot < p->capacity && ga && ua && da && g_bytes + u_bytes + d_bytes <= p->slot_bytes, "expert pool: bad slot or sizes");
+    if (!pool_arena(p)) return 0;
+    const uint64_t base = (uint64_t)(uintptr_t)(p->arena.as<uint8_t>() + (size_t)slot * p->slot_bytes);
+    *ga = base; *ua = base + g_bytes; *da = base + g_bytes + u_bytes;
+    return 1;
+}
+
+int redmetal_topk_pool_execute(redmetal_topk_pool_t h, const uint32_t *slot_ids, const uint64_t *gate_bytes, const uint64_t *up_bytes, const uint64_t *down_bytes,
+                               const float *router_weights, uint32_t top_k, uint32_t ggml_type, uint32_t hidden, uint32_t ffn, uint32_t row_start, uint32_t row_count,
+                               const float *input, uint32_t input_count, float *output, uint32_t output_count, double *elapsed_ms) {
+    TopkPool *p = (TopkPool *)h;
+    RC_REQUIRE(p && slot_ids && gate_bytes && up_bytes && down_bytes && router_weights && input && output, "expert pool: null argument");
+    RC_REQUIRE(input_count == hidden && output_count == row_count, "expert pool: input / output counts do not match the shape");
+    RC_REQUIRE(p->arena.p, "expert pool: no expert has been loaded");
+    RC_CUDA(cudaSetDevice(p->device));
+    const double t0 = pool_now_ms();
+    DevMem x, o;
+    if (!x.alloc((size_t)hidden * 4u) || !o.alloc((size_t)row_count * 4u)) return 0;
+    cudaStream_t s = p->stream;
+    RC_CUDA(cudaMemcpyAsync(x.p, input, (size_t)hidden * 4u, cudaMemcpyHostToDevice, s));
+    if (!pool_run(p, slot_ids, gate_bytes, up_bytes, down_bytes, router_weights, top_k, ggml_type, hidden, ffn, row_start, row_count, x.as<float>(), o.as<float>(), s)) return 0;
+    RC_CUDA(cudaMemcpyAsync(output, o.p, (size_t)row_count * 4u, cudaMemcpyDeviceToHost, s));
+    RC_CUDA(cudaStreamSynchronize(s));
+    if (status_failed()) return 0;
+    if (elapsed_ms) *elapsed_ms = pool_now_ms() - t0;
+    return 1;
+}
+
+int redmetal_topk_pool_encode(redmetal_topk_pool_t h, void *stream, const uint32_t *slot_ids, const uint64_t *gate_bytes, const uint64_t *up_bytes, const uint64_t *down_bytes,
+                              const float *router_weights, uint32_t top_k, uint32_t ggml_type, uint32_t hidden, uint32_t ffn, uint32_t row_start, uint32_t row_count,
+                              void *in_dev, uint64_t in_off, void *out_dev, uint64_t out_off) {
+    TopkPool *p = (TopkPool *)h;
+    RC_REQUIRE(p && slot_ids && gate_bytes && up_bytes && down_bytes && router_weights && in_dev && out_dev, "expert pool: null argument");
+    RC_REQUIRE(p->arena.p, "expert pool: no expert has been loaded");
+    RC_CUDA(cudaStreamSynchronize((cudaStream_t)stream));        // the pinned grouping words and the scratch are shared by the pool's calls
+    if (!pool_run(p, slot_ids, gate_bytes, up_bytes, down_bytes, router_weights, top_k, ggml_type, hidden, ffn, row_start, row_count,
+                  reinterpret_cast<const float *>((const uint8_t *)in_dev + in_off), reinterpret_cast<float *>((uint8_t *)out_dev + out_off), (cudaStream_t)stream)) return 0;
+    for (uint32_t k = 0; k < top_k; ++k) p->inflight[slot_ids[k]] += 1u;
+    return 1;
+}
+
+void redmetal_topk_pool_release(redmetal_topk_pool_t h, const uint32_t *slot_ids, uint32_t top_k) {
+    TopkPool *p = (TopkPool *)h;
+    if (!p || !slot_ids) return;
+    for (uint32_t k = 0; k < top_k; ++k) if (slot_ids[k] < p->capacity && p->inflight[slot_ids[k]]) p->inflight[slot_ids[k]] -= 1u;
+}
+
+int redmetal_topk_pool_residency_table_init(redmetal_topk_pool_t h, uint32_t layers, uint32_t experts) {
+    TopkPool *p = (TopkPool *)h;
+    RC_REQUIRE(p && layers && experts, "expert pool: bad residency table shape");
+    RC_CUDA(cudaSetDevice(p->device));
+    if (!p->table.alloc((size_t)layers * experts * 8u)) return 0;
+    RC_CUDA(cudaMemset(p->table.p, 0, (size_t)layers * experts * 8u));
+    p->table_h.assign((size_t)layers * experts, 0u); p->layers = layers; p->experts = experts;
+    return 1;
+}
+void *redmetal_topk_pool_residency_table(redmetal_topk_pool_t h) { return h ? ((TopkPool *)h)->table.p : nullptr; }
+int redmetal_topk_pool_residency_set(redmetal_topk_pool_t h, uint32_t layer, uint32_t expert, uint32_t slot) {
+    TopkPool *p = (TopkPool *)h;
+    RC_REQUIRE(p && p->table.p && layer < p->layers && expert < p->experts && slot < p->capacity, "expert pool: residency entry out of range");
+    if (!pool_arena(p)) return 0;
+    const size_t i = (size_t)layer * p->experts + expert;
+    p->table_h[i] = (uint64_t)(uintptr_t)(p->arena.as<uint8_t>() + (size_t)slot * p->slot_bytes);
+    RC_CUDA(cudaMemcpy(p->table.as<uint64_t>() + i, &p->table_h[i], 8u, cudaMemcpyHostToDevice));
+    return 1;
+}
+void redmetal_topk_pool_residency_clear(redmetal_topk_pool_t h, uint32_t layer, uint32_t expert) {
+    TopkPool *p = (TopkPool *)h;
+    if (!p || !p->table.p || layer >= p->layers || expert >= p->experts) return;
+    const size_t i = (size_t)layer * p->experts + expert;
+    p->table_h[i] = 0u;
+    cudaMemcpy(p->table.as<uint64_t>() + i, &p->table_h[i], 8u, cudaMemcpyHostToDevice);
+}
+
+}  // extern "C"

@@ -121,6 +121,7 @@ class Engine:
             logits = np.empty(self.info.vocab, np.float32)
         stats = RlStepStats()
         self._ok(self.L.rl_engine_step(self._e, RL_BACKEND_GPU, token, logits.ctypes.data if want_logits else None, C.byref(stats), self._err, 1024), "rl_engine_step")
+        self.last_stats = stats
         return logits
 
     def prefill(self, tokens, want_logits: bool = True):
@@ -157,6 +158,11 @@ class Engine:
     @property
     def prefill_batch(self) -> int:
         return int(self.L.rl_engine_prefill_batch(self._e))
+
+    def experts_preloaded(self) -> tuple[bool, float]:
+        """(every routed expert is resident, milliseconds the load took at open)"""
+        ms = C.c_double(0.0)
+        return self.L.rl_engine_experts_preloaded(self._e, C.byref(ms)) == 1, float(ms.value)
 
     def step_bytes(self) -> int:
         return int(self.L.rl_engine_step_bytes(self._e))

@@ -171,6 +171,30 @@ def test_midsize_model_chunked_prefill(tmp_path, monkeypatch):
         eng.close()
 
 
+def test_resident_engine_reports_no_expert_traffic(tmp_path, monkeypatch):
+    """Every expert is resident in HBM, so what the reference's expert LRU counts (native/redlite_native_cache.c:160-323,
+    surfaced through rl_engine_step_stats, native/redlite_native_engine.h:62-87) stays at zero after open: no loads, no
+    misses, no SSD reads, and every slot of every layer is resident."""
+    monkeypatch.setenv("RL_KV_F16", "1")
+    dims = synth.tiny_model_dims(n_layer=4)
+    sm = synth.model(12, dims)
+    path = str(tmp_path / "tiny.gguf")
+    gguf_writer.write_gguf(path, sm)
+    eng = Engine(path, context=dims.context)
+    try:
+        ok, ms = eng.experts_preloaded()
+        assert ok and ms > 0.0
+        assert eng.full_residency_mib() >= 1
+        tok = 1
+        for _ in range(8):
+            tok = int(np.argmax(eng.step(tok)))
+            st = eng.last_stats
+            assert st.expert_loads == 0 and st.cache_misses == 0 and st.ssd_reads == 0 and st.ssd_bytes == 0
+            assert st.resident_slots == st.slot_capacity == dims.n_layer * dims.n_expert
+    finally:
+        eng.close()
+
+
 def test_engine_errors(tmp_path):
     with pytest.raises(Exception):
         Engine(str(tmp_path / "missing.gguf"))
