@@ -167,8 +167,11 @@ def workload_config(args, dims):
 
 def run_ep(args, world, rank, local):
     """N > 1: expert parallelism, all-gather form. Every rank keeps its own 64 tokens (weak scaling) and 512 / N experts of
-    every layer (expert e on rank e % N); per layer one all-gather of the token rows and one reduce-scatter of the
-    partial outputs over NCCL, no host synchronisation inside a step. Timed with CUDA events per rank, maximum over ranks."""
+    every layer; per layer one all-gather of the token rows and one reduce-scatter of the partial outputs over NCCL, no
+    host synchronisation inside a step. Placement: interleaved (expert e on rank e % N, the default) or contiguous
+    (expert e on rank e // (512 / N)); --ep-permute draws the routing over a random permutation of the expert ids, so
+    that popularity is not ordered by id. Timed with CUDA events per rank, maximum over ranks; before the timed region
+    rank 0 checks layer 0's output of its first tokens against the CPU oracle."""
     import torch
     import torch.distributed as dist
     import dwarfstar_red_lite_b200 as rc
@@ -180,21 +183,68 @@ def run_ep(args, world, rank, local):
     dims = synth.MoeDims()
     L, T = args.layers, args.tokens
     ec = dims.n_expert // world
+    contiguous = args.ep_placement == "contiguous"
+    perm = np.random.default_rng(4242).permutation(dims.n_expert) if args.ep_permute else np.arange(dims.n_expert)
+
+    def owner_of(ids):           # rank that holds expert id
+        return ids // ec if contiguous else ids % world
+
+    def global_id(r, i):         # id of the i-th expert of rank r's shard
+        return r * ec + i if contiguous else r + i * world
+
     layers = []
     for l in range(L):
         tens = synth_device.moe_layer_tensors(1000 + l, dims, dev, expert_begin=rank * ec, expert_count=ec)
-        m = rc.MoeLayer(device_tensors=tens, dims=dims, max_tokens=T * world, expert_begin=rank, expert_count=ec, expert_stride=world)
+        m = rc.MoeLayer(device_tensors=tens, dims=dims, max_tokens=T * world, expert_begin=rank * ec if contiguous else rank, expert_count=ec,
+                        expert_stride=1 if contiguous else world)
         layers.append(ep.EpGatherMoeLayer(m, rank, world, T))
         del tens
-    logits_h = np.stack([synth.zipf_routing_logits(500 + l + 1000 * rank, T) for l in range(L)])
+
+    def drawn_logits(l, r):
+        lg = synth.zipf_routing_logits(500 + l + 1000 * r, T)
+        return lg[:, np.argsort(perm)] if args.ep_permute else lg      # column e of the result = popularity rank perm^-1(e)
+
+    logits_h = np.stack([drawn_logits(l, rank) for l in range(L)])
     gx = torch.Generator(device=dev)
     gx.manual_seed(7 + rank)
     x_d = torch.randn(L, T, dims.hidden, device=dev, generator=gx)
-    logits_d = torch.from_numpy(logits_h).to(dev)
+    logits_d = torch.from_numpy(np.ascontiguousarray(logits_h)).to(dev)
 
-    def step():
+    def step(mark=None):
         for l in range(L):
-            layers[l].forward(x_d[l], logits=logits_d[l])
+            layers[l].forward(x_d[l], logits=logits_d[l], mark=mark)
+
+    # ---- parity on the devices: layer 0's output of rank 0's first tokens against the oracle port of ffn()
+    parity = None
+    out0 = layers[0].forward(x_d[0], logits=logits_d[0]).clone()
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank == 0 and not args.no_cpu:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import oracle_lib as ol
+        from dwarfstar_red_lite_b200.synth import MoeLayer
+        full = {}
+        for r in range(world):       # every rank's shard of layer 0, regenerated from its seed, placed at its experts' global ids
+            tens = synth_device.moe_layer_tensors(1000, dims, dev, expert_begin=r * ec, expert_count=ec)
+            for k in ("gate", "up", "down"):
+                a = tens[k].cpu().numpy().reshape(ec, -1)
+                if k not in full:
+                    full[k] = np.empty((dims.n_expert, a.shape[1]), np.uint8)
+                for i in range(ec):
+                    full[k][global_id(r, i)] = a[i]
+            if r == 0:
+                rest = {k: tens[k].cpu().numpy() for k in ("router", "sh_gate_inp", "sh_gate", "sh_up", "sh_down")}
+            del tens
+        host = MoeLayer(dims, rest["router"], full["gate"], full["up"], full["down"], rest["sh_gate_inp"], rest["sh_gate"].reshape(dims.ffn_sh, -1),
+                        rest["sh_up"].reshape(dims.ffn_sh, -1), rest["sh_down"].reshape(dims.hidden, -1))
+        view = ol.moe_layer_c(host)
+        ntest, worst, ids_ok = min(4, T), 0.0, True
+        x0, got = x_d[0].cpu().numpy(), out0.cpu().numpy()
+        for t in range(ntest):
+            ro, rid, _, _ = ol.moe_ffn(host, x0[t], threads=os.cpu_count() or 1, logits_in=logits_h[0][t], view=view)
+            worst = max(worst, float(np.max(np.abs(got[t] - ro)) / np.max(np.abs(ro))))
+        parity = {"layer": 0, "tokens_checked": ntest, "max_rel_err_vs_cpu_oracle": worst, "bound": 1e-3, "ok": bool(worst <= 1e-3)}
+        del full, host
 
     n0 = rcm.lib().redcuda_launch_count()
     step()
@@ -204,41 +254,64 @@ def run_ep(args, world, rank, local):
     torch.cuda.synchronize()
     dist.barrier()
     side = torch.cuda.Stream()
-    run = step
     with torch.cuda.stream(side):
-        run()
+        step()
         side.synchronize()
         dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(local) as clocks:
             torch.cuda.synchronize()
+            t_host0 = time.perf_counter()
             e0.record(side)
             for _ in range(args.steps):
-                run()
+                step()
             e1.record(side)
+            t_enqueue = (time.perf_counter() - t_host0) / args.steps        # host time to queue a step (no synchronisation inside)
             torch.cuda.synchronize()
+        # ---- phase shares of one more step (events at the phase boundaries on this stream; outside the timed region)
+        marks = []
+
+        def mark(name):
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(side)
+            marks.append((name, ev))
+
+        mark("begin")
+        step(mark)
+        side.synchronize()
+    phases = {}
+    for (_, a), (name, bb) in zip(marks[:-1], marks[1:]):
+        phases[name] = phases.get(name, 0.0) + a.elapsed_time(bb)
     ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
     # pairs this rank's experts served per layer (from the drawn logits of every rank: the same seeds on every rank)
     mine = 0
     for r in range(world):
         for l in range(L):
-            lg = logits_h[l] if r == rank else synth.zipf_routing_logits(500 + l + 1000 * r, T)
+            lg = logits_h[l] if r == rank else drawn_logits(l, r)
             top = np.argpartition(-lg, dims.top_k - 1, axis=1)[:, :dims.top_k]
-            mine += int(np.sum(top % world == rank))
+            mine += int(np.sum(owner_of(top) == rank))
     pairs = torch.tensor([mine / L], device=dev)
+    enq = torch.tensor([t_enqueue * 1e3], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    dist.all_reduce(enq, op=dist.ReduceOp.MAX)
     allpairs = [torch.zeros_like(pairs) for _ in range(world)]
     dist.all_gather(allpairs, pairs)
     dist.barrier()
     if rank == 0:
         ms_per_step = float(ms.item()) / args.steps
         value = T * world * L / (ms_per_step * 1e-3)
+        tot = sum(phases.values()) or 1.0
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": dict(workload_config(args, dims), experts_per_gpu=ec, expert_placement="interleaved (expert e on rank e % N)",
+                "config": dict(workload_config(args, dims), experts_per_gpu=ec,
+                               expert_placement="contiguous (expert e on rank e // (512 / N))" if contiguous else "interleaved (expert e on rank e % N)",
+                               routing_ids_permuted=bool(args.ep_permute),
                                pairs_served_per_rank_per_layer=[float(p.item()) for p in allpairs], cuda_graph=False,
                                exchange="per layer: NCCL all-gather of the token rows (fp32 activations + router ids/weights), reduce-scatter of the partial outputs; no host synchronisation"),
-                "roofline": None, "cpu_baseline": None,
+                "roofline": None, "cpu_baseline": None, "parity": parity,
+                "breakdown": {"host_enqueue_ms_per_step_max_over_ranks": float(enq.item()), "device_ms_per_step": ms_per_step,
+                              "rank0_phase_ms_per_step": {k: round(v, 3) for k, v in phases.items()},
+                              "rank0_phase_share": {k: round(v / tot, 3) for k, v in phases.items()}},
                 "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                         "note": "multi-GPU runs keep activations on the devices; the host-buffer path is measured at N=1"},
                 "gpu_launches": int(launches_per_step * args.steps), "clocks": clocks.summary()}
@@ -464,12 +537,76 @@ def _timed_graph(torch, step_fn, steps, warmup, device_index):
     return e0.elapsed_time(e1) / steps, clocks.summary()
 
 
+def measure_config0(torch, layers, dims, x1_d, out1_d, steps, warmup, device_index):
+    """One token through every resident layer, router computed (the single-token path: three launches per layer).
+    Returns per-layer time, achieved GB/s on the algorithmic bytes of a token-layer and the launches per layer."""
+    import dwarfstar_red_lite_b200 as rc
+    L, row = len(layers), dims.hidden * 4
+
+    def step(stream):
+        for l in range(L):
+            layers[l].forward_device(1, x1_d.data_ptr() + l * row, out1_d.data_ptr() + l * row, stream)
+
+    n0 = rc.lib().redcuda_launch_count()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        step(side.cuda_stream)
+        side.synchronize()
+    launches = (rc.lib().redcuda_launch_count() - n0) / L
+    ms, clocks = _timed_graph(torch, step, steps, warmup, device_index)
+    us = 1e3 * ms / L
+    bytes_layer = algorithmic_bytes(dims, 1, dims.top_k, True)["layer"]
+    peak, kind = measured_peak()
+    gbs = bytes_layer / (us * 1e-6) / 1e9
+    return {"us_per_layer": us, "GBps": gbs, "frac": gbs / peak, "frac_of_nominal_8000": gbs / 8000.0, "launches_per_layer": launches,
+            "bytes_per_token_layer": bytes_layer, "layers_per_step": L, "token_layers_per_s": 1e6 / us}, clocks
+
+
+def measure_deltanet(torch, steps, warmup, device_index):
+    """Gated DeltaNet decode step for batch 1 and 8 over enough distinct layer states to exceed L2 (device pointers,
+    the allocation-free entry point). Returns {batchB: {...}}, bytes per sequence-layer and the parameter dict."""
+    import ctypes as C
+    import dwarfstar_red_lite_b200 as rc
+    from dwarfstar_red_lite_b200.redcuda import DeltanetParams, f32p
+    dev = torch.device("cuda", device_index)
+    lib = rc.lib()
+    S, groups, rank, d_conv = 128, 16, 32, 4
+    d_inner, channels = rank * S, 2 * S * groups + rank * S
+    g = torch.Generator(device=dev)
+    g.manual_seed(3)
+    pd = {"conv_kernel": torch.randn(channels, d_conv, device=dev, generator=g) * 0.5, "dt_bias": torch.zeros(rank, device=dev),
+          "ssm_a": -torch.ones(rank, device=dev), "ssm_norm": 1 + 0.1 * torch.randn(S, device=dev, generator=g)}
+    P = DeltanetParams(d_conv, S, groups, rank, d_inner, channels, 1e-6, *[C.cast(pd[k].data_ptr(), f32p) for k in ("conv_kernel", "dt_bias", "ssm_a", "ssm_norm")])
+    per_seq_bytes = 2 * rank * S * S * 4 + 2 * channels * (d_conv - 1) * 4 + channels * d_conv * 4 + (channels + 2 * d_inner + 2 * rank) * 4
+    results, clocks = {}, None
+    for B in (1, 8):
+        NL = max(8, int(400e6 // (B * rank * S * S * 4)))          # distinct states per step: ~400 MB of state
+        qkv = torch.randn(NL, B, channels, device=dev, generator=g)
+        z = torch.randn(NL, B, d_inner, device=dev, generator=g)
+        ba = torch.randn(NL, B, 2 * rank, device=dev, generator=g)
+        conv = torch.randn(NL, B, channels, d_conv - 1, device=dev, generator=g)
+        rec = torch.randn(NL, B, rank, S, S, device=dev, generator=g) * 0.05
+        out = torch.empty(NL, B, d_inner, device=dev)
+
+        def step(stream):
+            for l in range(NL):
+                ok = lib.redcuda_deltanet_step_noalloc(C.byref(P), B, qkv[l].data_ptr(), z[l].data_ptr(), ba[l].data_ptr(), conv[l].data_ptr(), rec[l].data_ptr(),
+                                                       out[l].data_ptr(), stream)
+                assert ok == 1, lib.redcuda_last_error().decode()
+
+        ms, clocks = _timed_graph(torch, step, steps, warmup, device_index)
+        seq_layers_s = NL * B / (ms * 1e-3)
+        results[f"batch{B}"] = {"seq_layer_steps_per_s": seq_layers_s, "us_per_layer_call": 1e3 * ms / NL, "GBps": seq_layers_s * per_seq_bytes / 1e9, "layers_per_step": NL}
+        del qkv, z, ba, conv, rec, out
+    return results, per_seq_bytes, pd, clocks
+
+
 def run_moe_b1(args):
     """BASELINE configs[0]: one routed-MoE FFN layer, batch 1, router computed. A step sweeps `layers` distinct layers
     (weights from HBM, not L2); value = token-layers per second."""
     import torch
     import dwarfstar_red_lite_b200 as rc
-    from dwarfstar_red_lite_b200 import synth, synth_device
+    from dwarfstar_red_lite_b200 import redcuda as rcm, synth, synth_device
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     rc.set_codebooks(device=0)
@@ -486,20 +623,15 @@ def run_moe_b1(args):
     x_d = torch.randn(L, 1, dims.hidden, device=dev, generator=g)
     out_d = torch.empty_like(x_d)
     row = dims.hidden * 4
-
-    def step(stream):
-        for l in range(L):
-            layers[l].forward_device(1, x_d.data_ptr() + l * row, out_d.data_ptr() + l * row, stream)
-
-    ms, clocks = _timed_graph(torch, step, args.steps, args.warmup, 0)
-    value = L / (ms * 1e-3)
+    c0, clocks = measure_config0(torch, layers, dims, x_d, out_d, args.steps, args.warmup, 0)
+    value = c0["token_layers_per_s"]
     # per-kernel durations (CUDA events around every launch, eager, separate from the timed region)
-    from dwarfstar_red_lite_b200 import redcuda as rcm
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
         rcm.profile_enable(True)
         for _ in range(3):
-            step(side.cuda_stream)
+            for l in range(L):
+                layers[l].forward_device(1, x_d.data_ptr() + l * row, out_d.data_ptr() + l * row, side.cuda_stream)
         side.synchronize()
         prof = rcm.profile_report()
         rcm.profile_enable(False)
@@ -509,9 +641,7 @@ def run_moe_b1(args):
     for l in range(L):
         layers[l].forward(xh[l], out=oh[l])
     e2e_v = L / (time.perf_counter() - t0)
-    bytes_layer = algorithmic_bytes(dims, 1, dims.top_k, True)["layer"]
     peak, kind = measured_peak()
-    gbs = bytes_layer * value / 1e9
     cpu = None
     if layer0_host is not None:
         sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -522,55 +652,27 @@ def run_moe_b1(args):
             ol.moe_ffn(layer0_host, xh[0][0], threads=threads, view=view)
             n += 1
         cpu = {"value": n / (time.perf_counter() - t0), "unit": UNIT, "cores": threads, "kind": "port", "sample": f"{n} passes of one token through layer 0 (oracle port of ffn())"}
-    print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+    print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e-3 * c0["us_per_layer"] * L,
                       "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                       "config": {"workload": "BASELINE configs[0]: single routed-MoE FFN layer, batch 1, router computed, 512 IQ2_XXS experts top-10 + Q6_K shared expert",
                                  "layers_per_step": L, "l2_policy": f"each step sweeps {L} distinct layers' weights"},
-                      "roofline": {"bound": "hbm", "kernel": "whole layer (%d launches)" % len(kernel_us), "kernel_us_per_launch": kernel_us, "achieved": gbs, "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": gbs / peak,
-                                   "frac_of_nominal_8000": gbs / 8000.0, "traffic": None, "bytes_per_token_layer": bytes_layer, "us_per_layer": 1e3 * ms / L},
+                      "roofline": {"bound": "hbm", "kernel": "whole layer (%d launches)" % round(c0["launches_per_layer"]), "kernel_us_per_launch": kernel_us, "achieved": c0["GBps"],
+                                   "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": c0["frac"], "frac_of_nominal_8000": c0["frac_of_nominal_8000"], "traffic": None,
+                                   "bytes_per_token_layer": c0["bytes_per_token_layer"], "us_per_layer": c0["us_per_layer"]},
                       "cpu_baseline": cpu, "e2e": {"value": e2e_v, "unit": UNIT, "h2d_bytes_per_step": L * row, "d2h_bytes_per_step": L * row},
-                      "gpu_launches": None, "clocks": clocks}), flush=True)
+                      "gpu_launches": int(round(c0["launches_per_layer"] * L * args.steps)), "clocks": clocks}), flush=True)
 
 
 def run_deltanet(args):
     """BASELINE configs[2]: gated DeltaNet decode step (conv + SiLU + L2 norm, delta rule on the 128x128 fp32 states of
     32 value heads, gated RMSNorm) for batch 1 and 8; a step sweeps enough distinct layer states to exceed L2."""
-    import ctypes as C
     import torch
-    import dwarfstar_red_lite_b200 as rc
-    from dwarfstar_red_lite_b200.redcuda import DeltanetParams, f32p
     torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
-    lib = rc.lib()
+    import dwarfstar_red_lite_b200 as rc
+    rc.lib()
+    results, per_seq_bytes, pd, clocks = measure_deltanet(torch, args.steps, args.warmup, 0)
     S, groups, rank, d_conv = 128, 16, 32, 4
     d_inner, channels = rank * S, 2 * S * groups + rank * S
-    g = torch.Generator(device=dev)
-    g.manual_seed(3)
-    pd = {"conv_kernel": torch.randn(channels, d_conv, device=dev, generator=g) * 0.5, "dt_bias": torch.zeros(rank, device=dev),
-          "ssm_a": -torch.ones(rank, device=dev), "ssm_norm": 1 + 0.1 * torch.randn(S, device=dev, generator=g)}
-    P = DeltanetParams(d_conv, S, groups, rank, d_inner, channels, 1e-6, *[C.cast(pd[k].data_ptr(), f32p) for k in ("conv_kernel", "dt_bias", "ssm_a", "ssm_norm")])
-    per_seq_bytes = 2 * rank * S * S * 4 + 2 * channels * (d_conv - 1) * 4 + channels * d_conv * 4 + (channels + 2 * d_inner + 2 * rank) * 4
-    results = {}
-    clocks = None
-    for B in (1, 8):
-        NL = max(8, int(400e6 // (B * rank * S * S * 4)))          # distinct states per step: ~400 MB of state
-        qkv = torch.randn(NL, B, channels, device=dev, generator=g)
-        z = torch.randn(NL, B, d_inner, device=dev, generator=g)
-        ba = torch.randn(NL, B, 2 * rank, device=dev, generator=g)
-        conv = torch.randn(NL, B, channels, d_conv - 1, device=dev, generator=g)
-        rec = torch.randn(NL, B, rank, S, S, device=dev, generator=g) * 0.05
-        out = torch.empty(NL, B, d_inner, device=dev)
-
-        def step(stream):
-            for l in range(NL):
-                ok = lib.redcuda_deltanet_step_noalloc(C.byref(P), B, qkv[l].data_ptr(), z[l].data_ptr(), ba[l].data_ptr(), conv[l].data_ptr(), rec[l].data_ptr(),
-                                                       out[l].data_ptr(), stream)
-                assert ok == 1, lib.redcuda_last_error().decode()
-
-        ms, clocks = _timed_graph(torch, step, args.steps, args.warmup, 0)
-        seq_layers_s = NL * B / (ms * 1e-3)
-        results[f"batch{B}"] = {"seq_layer_steps_per_s": seq_layers_s, "us_per_layer_call": 1e3 * ms / NL, "GBps": seq_layers_s * per_seq_bytes / 1e9, "layers_per_step": NL}
-        del qkv, z, ba, conv, rec, out
     cpu = None
     if not args.no_cpu:
         sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -591,7 +693,7 @@ def run_deltanet(args):
                       "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                       "config": {"workload": "BASELINE configs[2]: gated DeltaNet decode step, 16 key / 32 value heads, 128x128 fp32 state per head, batch 1 and 8", "results": results,
                                  "l2_policy": "each step sweeps ~400 MB of distinct states"},
-                      "roofline": {"bound": "hbm", "kernel": "k_dn_prep + k_dn_state + k_dn_tail", "achieved": b8["GBps"], "peak": peak, "peak_kind": kind, "unit": "GB/s",
+                      "roofline": {"bound": "hbm", "kernel": "DeltaNet decode step", "achieved": b8["GBps"], "peak": peak, "peak_kind": kind, "unit": "GB/s",
                                    "frac": b8["GBps"] / peak, "traffic": None, "bytes_per_sequence_layer": per_seq_bytes, "batch1_GBps": results["batch1"]["GBps"]},
                       "cpu_baseline": cpu, "e2e": None, "gpu_launches": None, "clocks": clocks}), flush=True)
 
@@ -617,6 +719,8 @@ def main():
     ap.add_argument("--prompt-tokens", type=int, default=8192, help="prefill: prompt length")
     ap.add_argument("--prefill-batch", type=int, default=0, help="prefill: tokens per chunk (0 = engine default)")
     ap.add_argument("--seed", type=int, default=1)
+    ap.add_argument("--ep-placement", default="interleaved", choices=["interleaved", "contiguous"], help="N > 1: which rank holds which expert")
+    ap.add_argument("--ep-permute", action="store_true", help="N > 1: draw the routing over a random permutation of the expert ids")
     args = ap.parse_args()
     if args.workload == "decode48":
         args.warmup = max(args.warmup, 1)
@@ -716,13 +820,19 @@ def main():
     dom_ms = prof[dom][1] / prof[dom][0]
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
     layer_bytes = float(np.mean([a["layer"] for a in ab]))
-    # DRAM traffic per launch: ncu (dram__bytes_read + dram__bytes_write) on a 2-layer capture of the same kernels gave
-    # 114.93 MB for a gate/up launch of 105.41 MB algorithmic bytes and 51.39 MB for a down launch of 52.4 MB (part of
-    # its input still sits in L2); traffic grows with the distinct experts read, so it is scaled by the algorithmic bytes.
-    ncu_ratio = {"moe_gateup": 114.93 / 105.41, "moe_down": 51.39 / 52.4}.get(dom)
+    # The routed experts are held in the nibble layout by default (138 bytes per 256 weights where the GGUF block has
+    # 66): `achieved` / `frac` are on the ALGORITHMIC bytes, `bytes_read_per_launch` is what the kernel really reads.
+    nib = not os.environ.get("RC_EXPERT_FMT", "nib4").startswith("i")
+    real = dom_bytes * (138.0 / 66.0) if (nib and key) else dom_bytes
+    # DRAM traffic per launch: ncu (dram__bytes_read + dram__bytes_write) of the nibble-layout kernels on a 2-layer
+    # capture: 231.2 MB read + 4.8 MB written by a gate/up launch whose expert records are 230.6 MB, 116.3 + 6.2 MB by a
+    # down launch of 115.3 MB; traffic grows with the distinct experts read, so it is scaled by the bytes read.
+    ncu_ratio = ({"moe_gateup": 236.0 / 230.6, "moe_down": 122.5 / 115.3} if nib else {"moe_gateup": 114.93 / 105.41, "moe_down": 51.39 / 52.4}).get(dom)
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                "frac_of_nominal_8000": achieved / 8000.0, "traffic": dom_bytes * ncu_ratio if ncu_ratio else None,
-                "traffic_source": "ncu capture of a 2-layer run, scaled by algorithmic bytes" if ncu_ratio else None,
+                "frac_of_nominal_8000": achieved / 8000.0, "traffic": real * ncu_ratio if ncu_ratio else None,
+                "traffic_source": ("ncu capture of a 2-layer run of the %s kernels, scaled by the bytes read" % ("nibble-layout" if nib else "planar-format")) if ncu_ratio else None,
+                "expert_layout": "nib4 (138 B per 256 weights)" if nib else "iq2 (66 B per 256 weights)",
+                "bytes_read_per_launch": real, "read_GBps": real / (dom_ms * 1e-3) / 1e9, "read_frac": real / (dom_ms * 1e-3) / 1e9 / peak,
                 "bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
                 "kernel_time_shares": shares,
                 "kernel_us_per_layer": {k: round(1e3 * v[1] / (prof_steps * L), 2) for k, v in prof.items()},
@@ -758,6 +868,26 @@ def main():
         v, n, dt = cpu_sample(layer0_host, x_d[0].cpu().numpy(), logits_h[0], threads, args.cpu_budget_s)
         cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
                "sample": f"{n} of the {T} tokens of layer 0 in {dt:.1f} s (oracle port of ffn(), rows spread over {threads} threads)"}
+
+    # ---- the other single-GPU configurations of the path, measured in the same process on the same resident layers:
+    # configs[0] (one token through every layer, router computed; what the >= 70 % target is phrased on) and configs[2]
+    # (the DeltaNet decode step). Reported inside `roofline` / `e2e` next to the headline numbers.
+    x1_d = torch.randn(L, 1, dims.hidden, device=dev, generator=gx)
+    out1_d = torch.empty_like(x1_d)
+    c0, _ = measure_config0(torch, layers, dims, x1_d, out1_d, max(5, args.steps // 2), 3, local)
+    x1h, o1h = x1_d.cpu().numpy(), np.empty((L, 1, dims.hidden), np.float32)
+    for l in range(L):
+        layers[l].forward(x1h[l], out=o1h[l])
+    t0 = time.perf_counter()
+    for l in range(L):
+        layers[l].forward(x1h[l], out=o1h[l])
+    c0_e2e = L / (time.perf_counter() - t0)
+    roofline["config0"] = {k: c0[k] for k in ("us_per_layer", "GBps", "frac", "frac_of_nominal_8000", "launches_per_layer", "bytes_per_token_layer")}
+    e2e["config0"] = {"value": c0_e2e, "unit": "token-layers/s", "h2d_bytes_per_step": dims.hidden * 4, "d2h_bytes_per_step": dims.hidden * 4}
+    dn, dn_bytes, _, _ = measure_deltanet(torch, max(5, args.steps // 2), 3, local)
+    roofline["config2"] = {"batch1": {"us_per_step": dn["batch1"]["us_per_layer_call"], "GBps": dn["batch1"]["GBps"], "frac": dn["batch1"]["GBps"] / peak},
+                           "batch8": {"us_per_step": dn["batch8"]["us_per_layer_call"], "GBps": dn["batch8"]["GBps"], "frac": dn["batch8"]["GBps"] / peak},
+                           "bytes_per_sequence_layer": dn_bytes}
 
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",

@@ -25,6 +25,8 @@ namespace rc {
 
 const uint32_t *moe_last_ids_device(const redcuda_moe *m);   // redcuda_moe.cu
 void moe_set_ids_mirror(redcuda_moe *m, uint32_t *dev_ptr);   // a single token's router ids are also written to dev_ptr
+size_t moe_workspace_bytes(const redcuda_moe_desc *d);
+redcuda_moe *moe_create_shared(const redcuda_moe_desc *d, void *workspace);   // workspace shared by layers that run on one stream
 
 static double now_ms() { return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
 
@@ -272,7 +274,7 @@ struct rl_engine {
     std::vector<EngLayer> layers;
     DMat tok_embd, output;
     const float *output_norm = nullptr;
-    DevMem dense, state, scratch;
+    DevMem dense, state, scratch, moe_ws;      // moe_ws: the expert workspace shared by every layer
     bool kv_half = false;
     uint32_t position = 0, ffn = 0, ffn_sh = 0;
     uint64_t expert_bytes = 0, dense_step_bytes = 0;
@@ -602,10 +604,10 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
     }
     ENG_CUDA(cudaGetDevice(&e->device));
     ENG_CUDA(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
-    // Prefill chunk: the reference defaults to 2048 tokens per batched dispatch (native/redlite_native_engine.h:37); here the
-    // chunk also sizes every layer's expert workspace (about 65 MB per layer at 512), so default and ceiling are 512.
-    // 1 = token by token.
-    e->pb = e->cfg.prefill_batch ? std::min(e->cfg.prefill_batch, 512u) : 512u;
+    // Prefill chunk: the reference defaults to 2048 tokens per batched dispatch (native/redlite_native_engine.h:37), and so
+    // does this engine (2048 is also the ceiling). The chunk sizes the expert workspace (about 0.5 GB at 2048), which all
+    // layers share: they run one after the other on the engine's stream. 1 = token by token.
+    e->pb = e->cfg.prefill_batch ? std::min(e->cfg.prefill_batch, 2048u) : 2048u;
     if (e->pb > in.context) e->pb = in.context;
 
     // ---- layer kinds from tensor names (native/redlite_native_layer_map.c:114-124), sizes of the dense arena
@@ -678,7 +680,11 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
         d.router = (const float *)g.data(tr); d.gate_exps = g.data(ge); d.up_exps = g.data(ue); d.down_exps = g.data(de);
         d.sh_gate_inp = (const float *)g.data(tg); d.sh_gate = g.data(sg); d.sh_up = g.data(su); d.sh_down = g.data(sd);
         e->ffn = d.ffn;
-        L.moe = redcuda_moe_create(&d);
+        {
+            const size_t need = moe_workspace_bytes(&d);
+            if (!e->moe_ws.p && !e->moe_ws.alloc(need)) ENG_FAIL("%s", redcuda_last_error());
+            L.moe = need <= e->moe_ws.bytes ? moe_create_shared(&d, e->moe_ws.p) : redcuda_moe_create(&d);
+        }
         if (!L.moe) ENG_FAIL("layer %u: %s", l, redcuda_last_error());
         e->expert_bytes += ge->bytes + ue->bytes + de->bytes;
         e->dense_step_bytes += tr->bytes + tg->bytes + sg->bytes + su->bytes + sd->bytes;

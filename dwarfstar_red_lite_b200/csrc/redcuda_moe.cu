@@ -16,9 +16,11 @@
 #include "redcuda_dot.cuh"
 #include "redcuda_kernels.cuh"
 #include "redcuda_moe_mma.cuh"
+#include "redcuda_tc_gemm.cuh"
 #include "../../include/redcuda.h"
 
 #include <new>
+#include <type_traits>
 #include <stdlib.h>
 
 namespace rc {
@@ -227,6 +229,10 @@ struct redcuda_moe {
     bool nib = false;          // routed experts held in the nibble layout (redcuda_moe_nib.cu) instead of planar IQ2_XXS
     uint32_t *work = nullptr;  // two unit counters of the persistent expert kernels (gate/up, down)
     uint32_t *ticket = nullptr; // ticket counter of the single-token GEMV's routing tail (zero between launches)
+    uint32_t *tc_err = nullptr; // timeout flag of the tcgen05 expert kernel
+    bool tc_ok = false;         // the tcgen05 expert kernel can serve this layer's shapes
+    bool tc_now = false;        // ... and serves the call in progress (set by moe_choose_path, read by the grouping and the launches)
+    bool ws_shared = false;     // the workspace belongs to the caller (rc::moe_create_shared)
     cudaStream_t stream = nullptr;
     cudaStream_t side = nullptr;                    // the shared expert runs here, beside the routed experts
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_quant = nullptr;
@@ -240,8 +246,20 @@ static bool moe_experts_mma(const redcuda_moe *m) {
 }
 // pairs per work item: the nibble-layout kernels take at most 8
 static uint32_t moe_item_tokens(const redcuda_moe *m, bool single_token, uint32_t npairs) {
+    if (m->tc_now && !single_token) return TCX_TN;
     if (m->nib) return single_token ? 1u : 8u;
     return mma_item_tokens(single_token, npairs, m->d.expert_count);
+}
+// Which expert kernels serve a call of npairs pairs (all_local: every pair belongs to this shard; otherwise the share
+// expert_count / n_expert of them): the tcgen05 kernel works on items of up to 64 pairs of one expert and decodes an
+// expert's weights once per item, so it needs experts that see many pairs each (prefill chunks, gathered
+// expert-parallel batches). RC_MOE_TC_MIN = pairs per expert from which it is used; unset or 0 = never: measured on
+// 2048-token chunks it is still slower than the mma.sync kernels with items of 8 pairs (gate/up 1.65 ms against 1.0 ms).
+static void moe_choose_path(redcuda_moe *m, uint32_t npairs, bool all_local) {
+    const char *v = getenv("RC_MOE_TC_MIN");
+    const uint32_t min_avg = v ? (uint32_t)atoi(v) : 0u;
+    const uint64_t local = all_local ? npairs : (uint64_t)npairs * m->d.expert_count / m->d.n_expert;
+    m->tc_now = m->tc_ok && min_avg && local >= (uint64_t)min_avg * m->d.expert_count;
 }
 // tensor-core path of the shared expert: Q6_K and at least 3 tokens (below that the CUDA-core GEMV wins)
 static bool moe_shared_mma(const redcuda_moe *m, uint32_t ntok) {
@@ -301,6 +319,24 @@ static int moe_shared_down(redcuda_moe *m, uint32_t ntok, cudaStream_t s) {
 static int moe_launch_experts(redcuda_moe *m, bool gateup, uint32_t npairs, bool single_token, const float *x, uint32_t x_stride, uint32_t x_div,
                               bool x_quantised, float *out, uint32_t out_stride, cudaStream_t s) {
     const uint32_t nrows = gateup ? m->d.ffn : m->d.hidden, ncols = gateup ? m->d.hidden : m->d.ffn;
+    if (m->tc_now && !single_token) {
+        // gate and up land in two plain [pair][ffn] buffers (out, and tmp as the second); the down launch's preparation
+        // reads both, applies SiLU(gate) * up and splits the product into digits
+        __half *xd = reinterpret_cast<__half *>(gateup ? m->xq_x : m->xq_act);
+        float *xinv = gateup ? m->sx_x : m->sx_act;
+        if (gateup) { if (!launch_tc_prep_rows(x, nullptr, x_stride, (npairs + x_div - 1u) / x_div, ncols, xd, xinv, s)) return 0; }
+        else if (!launch_tc_prep_rows(x, m->tmp, x_stride, npairs, ncols, xd, xinv, s)) return 0;
+        TcxArgs T{};
+        T.w[0] = gateup ? m->gate : m->down; T.w[1] = gateup ? m->up : nullptr; T.nmat = gateup ? 2u : 1u;
+        T.mat_bytes = gateup ? m->gu_bytes : m->down_bytes; T.nrows = nrows; T.ncols = ncols;
+        T.expert_begin = m->d.expert_begin; T.n_local = m->d.expert_count;
+        T.sorted = m->sorted; T.uexp = m->uexp; T.ustart = m->ustart; T.item_u = m->item_u; T.item_p0 = m->item_p0; T.n_items = m->n_items;
+        T.xd = xd; T.x_inv = xinv; T.x_div = gateup ? x_div : 1u;
+        T.out[0] = out; T.out[1] = gateup ? m->tmp : nullptr; T.out_stride = out_stride;
+        T.err = m->tc_err; T.status = status_words();
+        const uint32_t live = npairs < m->d.expert_count ? npairs : m->d.expert_count;
+        return launch_tc_experts(T, npairs / TCX_TN + live, gateup ? "moe_gateup_tc" : "moe_down_tc", s);
+    }
     if (moe_experts_mma(m)) {
         int8_t *xq = gateup ? m->xq_x : m->xq_act;
         float *sx = gateup ? m->sx_x : m->sx_act;
@@ -409,6 +445,7 @@ static int moe_forward_on(redcuda_moe *m, uint32_t ntok, const float *x, const f
     RC_REQUIRE(ntok >= 1 && ntok <= m->d.max_tokens, "moe forward: ntok %u outside [1, %u]", ntok, m->d.max_tokens);
     if (ntok == 1u && moe_fused1_ok(m)) return moe_forward_fused1(m, x, logits_in, resid, out, s);
     const uint32_t k = m->d.top_k, npairs = ntok * k;
+    moe_choose_path(m, npairs, true);
     // one quantisation of the token activations serves the routed gate/up and the shared gate/up
     const bool xq = moe_experts_mma(m) || moe_shared_mma(m, ntok);
     // The shared expert needs nothing from the router, so it runs on a side stream next to the routed
@@ -419,18 +456,22 @@ static int moe_forward_on(redcuda_moe *m, uint32_t ntok, const float *x, const f
     // kernels, which read the digits as well, follow it there) and the main stream waits for it only before the
     // gate/up launch, behind the router GEMV, the selection and the grouping.
     const bool quant_aside = fork && xq;
-    if (xq && !quant_aside && !launch_quant_act(x, m->d.hidden, ntok, m->d.hidden, m->xq_x, m->sx_x, s)) return 0;
+    // the tcgen05 expert path keeps its fp16 digits where the int8 digits of the routed experts would go, so the int8
+    // digits that the shared expert still reads move to the buffer of the stand-alone shared-expert call
+    int8_t *xqd = m->tc_now ? m->xq_own : m->xq_x;
+    float *sxd = m->tc_now ? m->sx_own : m->sx_x;
+    if (xq && !quant_aside && !launch_quant_act(x, m->d.hidden, ntok, m->d.hidden, xqd, sxd, s)) return 0;
     if (fork) {
         RC_CUDA(cudaEventRecord(m->ev_fork, s));
         RC_CUDA(cudaStreamWaitEvent(m->side, m->ev_fork, 0));
         if (quant_aside) {
-            if (!launch_quant_act(x, m->d.hidden, ntok, m->d.hidden, m->xq_x, m->sx_x, m->side)) return 0;
+            if (!launch_quant_act(x, m->d.hidden, ntok, m->d.hidden, xqd, sxd, m->side)) return 0;
             RC_CUDA(cudaEventRecord(m->ev_quant, m->side));
         }
-        if (!moe_gemv_pre(m, ntok, x, false, true, xq, m->side) || !moe_shared_down(m, ntok, m->side)) return 0;
+        if (!moe_gemv_pre(m, ntok, x, false, true, xq, m->side, xqd, sxd) || !moe_shared_down(m, ntok, m->side)) return 0;
         RC_CUDA(cudaEventRecord(m->ev_join, m->side));
-        if (!moe_gemv_pre(m, ntok, x, logits_in == nullptr, false, xq, s)) return 0;
-    } else if (!moe_gemv_pre(m, ntok, x, logits_in == nullptr, true, xq, s)) return 0;
+        if (!moe_gemv_pre(m, ntok, x, logits_in == nullptr, false, xq, s, xqd, sxd)) return 0;
+    } else if (!moe_gemv_pre(m, ntok, x, logits_in == nullptr, true, xq, s, xqd, sxd)) return 0;
     if (ntok == 1u && m->d.n_expert <= 1024u) {      // one token: the router kernel also writes the (trivial) grouping
         const RouteGroup1 G{m->sorted, m->uexp, m->ustart, m->n_unique, m->item_u, m->item_p0, m->n_items, m->ids_mirror, m->work};
         if (!launch_route(logits_in ? logits_in : m->logits, ntok, m->d.n_expert, k, m->ids, m->wk, nullptr, s, &G)) return 0;
@@ -438,22 +479,49 @@ static int moe_forward_on(redcuda_moe *m, uint32_t ntok, const float *x, const f
         if (!launch_route(logits_in ? logits_in : m->logits, ntok, m->d.n_expert, k, m->ids, m->wk, nullptr, s)) return 0;
         if (!moe_group(m, m->ids, npairs, ntok == 1u, s)) return 0;
     }
-    if (quant_aside) RC_CUDA(cudaStreamWaitEvent(s, m->ev_quant, 0));
-    if (!moe_launch_experts(m, true, npairs, ntok == 1u, x, m->d.hidden, k, xq, m->act, m->d.ffn, s)) return 0;
+    if (quant_aside && !m->tc_now) RC_CUDA(cudaStreamWaitEvent(s, m->ev_quant, 0));
+    if (!moe_launch_experts(m, true, npairs, ntok == 1u, x, m->d.hidden, k, xq && moe_experts_mma(m), m->act, m->d.ffn, s)) return 0;
     if (!fork && !moe_shared_down(m, ntok, s)) return 0;
     if (!moe_launch_experts(m, false, npairs, ntok == 1u, m->act, m->d.ffn, 1u, false, m->tmp, m->d.hidden, s)) return 0;
     if (fork) RC_CUDA(cudaStreamWaitEvent(s, m->ev_join, 0));
     return moe_combine(m, ntok, m->tmp, m->wk, k, true, resid, out, s);
 }
 
+// Carves the workspace of a layer out of B (m and B null: only the size is computed). Every piece is 256-byte aligned.
+static size_t moe_ws_layout(const redcuda_moe_desc &d, redcuda_moe *m, uint8_t *B) {
+    const size_t T = d.max_tokens, P = T * d.top_k;
+    size_t w = 0;
+    auto put = [&](auto &ptr, size_t bytes) {
+        if (m) ptr = reinterpret_cast<std::remove_reference_t<decltype(ptr)>>(B + w);
+        w = align_up(w + bytes, 256);
+    };
+    redcuda_moe scratch_names;            // pointer members to aim at when only the size is wanted
+    redcuda_moe &r = m ? *m : scratch_names;
+    put(r.x, T * d.hidden * 4u); put(r.logits, T * d.n_expert * 4u); put(r.wk, P * 4u); put(r.scalar, T * 4u);
+    put(r.sh_act, T * d.ffn_sh * 4u); put(r.sh_out, T * d.hidden * 4u); put(r.act, P * d.ffn * 4u); put(r.tmp, P * d.hidden * 4u);
+    put(r.out, T * d.hidden * 4u); put(r.ids, P * 4u); put(r.sorted, P * 4u); put(r.uexp, (size_t)(d.expert_count + 1u) * 4u);
+    put(r.ustart, (size_t)(d.expert_count + 2u) * 4u); put(r.n_unique, 16); put(r.bad, 16);
+    // digits of the routed experts' inputs: three int8 digits per value (mma.sync kernels) or two fp16 digits (tcgen05 kernel)
+    put(r.xq_x, P * 4u * d.hidden); put(r.sx_x, P * 4u); put(r.xq_act, P * 4u * d.ffn); put(r.sx_act, P * 4u);
+    put(r.xq_sh, T * 3u * d.ffn_sh); put(r.sx_sh, T * 4u); put(r.xq_own, T * 3u * d.hidden); put(r.sx_own, T * 4u);
+    put(r.item_u, (P + 8u) * 4u); put(r.item_p0, (P + 8u) * 4u); put(r.n_items, 16); put(r.work, 16);
+    if (m) { m->ticket = m->work + 2; m->tc_err = m->work + 3; }
+    return w;
+}
+
 namespace rc {
 const uint32_t *moe_last_ids_device(const redcuda_moe *m) { return m->ids; }
 void moe_set_ids_mirror(redcuda_moe *m, uint32_t *dev_ptr) { m->ids_mirror = dev_ptr; }
 }
+static redcuda_moe *moe_create_impl(const redcuda_moe_desc *desc, void *shared_ws);
+namespace rc {
+// One workspace for many layers: legal when the calls of those layers are ordered on one stream (the engine's are), and
+// what keeps a 2048-token prefill chunk affordable (the workspace grows with max_tokens * top_k * hidden).
+size_t moe_workspace_bytes(const redcuda_moe_desc *d) { return moe_ws_layout(*d, nullptr, nullptr); }
+redcuda_moe *moe_create_shared(const redcuda_moe_desc *d, void *workspace) { return moe_create_impl(d, workspace); }
+}
 
-extern "C" {
-
-redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
+static redcuda_moe *moe_create_impl(const redcuda_moe_desc *desc, void *shared_ws) {
     if (!require_device()) return nullptr;
     if (!desc) { set_error("moe create: null descriptor"); return nullptr; }
     const redcuda_moe_desc &d = *desc;
@@ -539,28 +607,14 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
     }
     if (!ok) return bail();
 
-    // workspace
-    const size_t T = d.max_tokens, P = T * d.top_k;
-    m->max_pairs = (uint32_t)P;
-    size_t w = 0;
-    auto take = [&](size_t bytes) { const size_t o = w; w = align_up(w + bytes, 256); return o; };
-    const size_t o_x = take(T * d.hidden * 4u), o_log = take(T * d.n_expert * 4u), o_wk = take(P * 4u), o_sca = take(T * 4u),
-                 o_sha = take(T * d.ffn_sh * 4u), o_sho = take(T * d.hidden * 4u), o_act = take(P * d.ffn * 4u), o_tmp = take(P * d.hidden * 4u),
-                 o_out = take(T * d.hidden * 4u), o_ids = take(P * 4u), o_sorted = take(P * 4u), o_uexp = take((size_t)(d.expert_count + 1u) * 4u),
-                 o_ustart = take((size_t)(d.expert_count + 2u) * 4u), o_nu = take(16), o_bad = take(16),
-                 o_xqx = take(P * 3u * d.hidden), o_sxx = take(P * 4u), o_xqa = take(P * 3u * d.ffn), o_sxa = take(P * 4u),
-                 o_xqs = take(T * 3u * d.ffn_sh), o_sxs = take(T * 4u), o_xqo = take(T * 3u * d.hidden), o_sxo = take(T * 4u), o_iu = take((P + 8u) * 4u), o_ip = take((P + 8u) * 4u), o_ni = take(16), o_wk2 = take(16);
-    if (!m->ws.alloc(w)) return bail();
-    uint8_t *B = m->ws.as<uint8_t>();
-    m->x = (float *)(B + o_x); m->logits = (float *)(B + o_log); m->wk = (float *)(B + o_wk); m->scalar = (float *)(B + o_sca);
-    m->sh_act = (float *)(B + o_sha); m->sh_out = (float *)(B + o_sho); m->act = (float *)(B + o_act); m->tmp = (float *)(B + o_tmp);
-    m->out = (float *)(B + o_out); m->ids = (uint32_t *)(B + o_ids); m->sorted = (uint32_t *)(B + o_sorted); m->uexp = (uint32_t *)(B + o_uexp);
-    m->ustart = (uint32_t *)(B + o_ustart); m->n_unique = (uint32_t *)(B + o_nu); m->bad = (uint32_t *)(B + o_bad);
-    m->xq_x = (int8_t *)(B + o_xqx); m->sx_x = (float *)(B + o_sxx); m->xq_act = (int8_t *)(B + o_xqa); m->sx_act = (float *)(B + o_sxa);
-    m->xq_sh = (int8_t *)(B + o_xqs); m->sx_sh = (float *)(B + o_sxs); m->item_u = (uint32_t *)(B + o_iu); m->item_p0 = (uint32_t *)(B + o_ip);
-    m->n_items = (uint32_t *)(B + o_ni);
-    m->xq_own = (int8_t *)(B + o_xqo); m->sx_own = (float *)(B + o_sxo);
-    m->work = (uint32_t *)(B + o_wk2); m->ticket = m->work + 2;
+    // workspace: this layer's own, or the caller's (shared by layers whose calls are ordered on one stream)
+    m->max_pairs = d.max_tokens * d.top_k;
+    const size_t w = moe_ws_layout(d, nullptr, nullptr);
+    uint8_t *B = static_cast<uint8_t *>(shared_ws);
+    if (B) m->ws_shared = true;
+    else { if (!m->ws.alloc(w)) return bail(); B = m->ws.as<uint8_t>(); }
+    moe_ws_layout(d, m, B);
+    m->tc_ok = m->nib && tcx_shape_ok(d.ffn, d.hidden) && tcx_shape_ok(d.hidden, d.ffn);
     {   // RC_MOE_PATH=cuda keeps the IQ2_XXS experts on the CUDA-core kernels (A/B switch for profiling)
         const char *pth = getenv("RC_MOE_PATH");
         m->use_mma = !(pth && pth[0] == 'c');
@@ -572,6 +626,10 @@ redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) {
     m->d.router = nullptr; m->d.gate_exps = m->d.up_exps = m->d.down_exps = nullptr; m->d.sh_gate_inp = nullptr; m->d.sh_gate = m->d.sh_up = m->d.sh_down = nullptr;
     return m;
 }
+
+extern "C" {
+
+redcuda_moe *redcuda_moe_create(const redcuda_moe_desc *desc) { return moe_create_impl(desc, nullptr); }
 
 void redcuda_moe_destroy(redcuda_moe *m) {
     if (!m) return;
@@ -621,6 +679,8 @@ int redcuda_moe_experts_device(redcuda_moe *m, uint32_t npairs, const float *pai
     RC_REQUIRE(m && pair_x_dev && pair_expert_dev && pair_out_dev, "moe experts: null argument");
     if (!npairs) return 1;
     cudaStream_t s = (cudaStream_t)stream;
+    RC_REQUIRE(npairs <= m->max_pairs, "moe experts: %u pairs exceed the workspace (%u)", npairs, m->max_pairs);
+    moe_choose_path(m, npairs, true);
     if (!moe_group(m, pair_expert_dev, npairs, false, s)) return 0;
     if (!moe_launch_experts(m, true, npairs, false, pair_x_dev, m->d.hidden, 1u, false, m->act, m->d.ffn, s)) return 0;
     return moe_launch_experts(m, false, npairs, false, m->act, m->d.ffn, 1u, false, pair_out_dev, m->d.hidden, s);
@@ -646,7 +706,8 @@ int redcuda_moe_partial_device(redcuda_moe *m, uint32_t ntok, const float *x_dev
     RC_REQUIRE(x_stride >= m->d.hidden && x_stride % 4u == 0 && meta_stride >= m->d.top_k, "moe partial: bad row strides (%u, %u)", x_stride, meta_stride);
     cudaStream_t s = (cudaStream_t)stream;
     const uint32_t k = m->d.top_k, npairs = ntok * k;
-    const bool xq = moe_experts_mma(m);
+    moe_choose_path(m, npairs, false);
+    const bool xq = moe_experts_mma(m) && !m->tc_now;
     if (xq && !launch_quant_act(x_dev, x_stride, ntok, m->d.hidden, m->xq_x, m->sx_x, s)) return 0;
     prof_begin("moe_mask_weights", s);
     RC_LAUNCH((k_mask_weights), (npairs + 255u) / 256u, 256, 0, s, ids_dev, weights_dev, ntok, k, meta_stride, m->d.expert_begin, m->d.expert_stride, m->d.expert_count, m->ids, m->wk);

@@ -39,6 +39,14 @@ uint32_t mma_item_tokens(bool few_tokens, uint32_t npairs = 0u, uint32_t n_exper
 // max_items = upper bound of work items (grid.y); item_tok: the size the items were cut with (2, 8 or 16)
 int launch_moe_mma(MmaArgs &A, uint32_t max_items, uint32_t item_tok, cudaStream_t s);
 // ---- nibble layout of IQ2_XXS expert matrices (redcuda_moe_nib.cu): 138 bytes per 256 weights, table-free decode ----
+constexpr uint32_t NIB_BLOCK_BYTES = 138u;
+// one record = one 16-row tile x one 256-column block
+constexpr uint32_t NIB_SC_OFF = 2048u, NIB_D_OFF = 2176u, NIB_REC = 2208u;
+// byte offset of code word (t, kg) of row rr inside a record (16-byte pieces of odd rows pairwise swapped)
+__host__ __device__ __forceinline__ uint32_t nib_code_off(uint32_t rr, uint32_t t, uint32_t kg) {
+    const uint32_t piece = (2u * t + (kg >> 2)) ^ (rr & 1u);
+    return rr * 128u + piece * 16u + (kg & 3u) * 4u;
+}
 uint64_t nib_matrix_bytes(uint32_t nrows, uint32_t ncols);
 bool nib_shape_ok(uint32_t nrows, uint32_t ncols);
 // planar IQ2_XXS matrix -> nibble layout (dst: nib_matrix_bytes, 16-byte aligned)

@@ -40,15 +40,6 @@
 
 namespace rc {
 
-constexpr uint32_t NIB_BLOCK_BYTES = 138u;
-// one record = one 16-row tile x one 256-column block
-constexpr uint32_t NIB_SC_OFF = 2048u, NIB_D_OFF = 2176u, NIB_REC = 2208u;
-// byte offset of code word (t, kg) of row rr inside a record (16-byte pieces of odd rows pairwise swapped)
-__host__ __device__ __forceinline__ uint32_t nib_code_off(uint32_t rr, uint32_t t, uint32_t kg) {
-    const uint32_t piece = (2u * t + (kg >> 2)) ^ (rr & 1u);
-    return rr * 128u + piece * 16u + (kg & 3u) * 4u;
-}
-
 uint64_t nib_matrix_bytes(uint32_t nrows, uint32_t ncols) { return (uint64_t)nrows * (ncols / 256u) * NIB_BLOCK_BYTES; }
 bool nib_shape_ok(uint32_t nrows, uint32_t ncols) { return nrows % 16u == 0 && (ncols == 256u || ncols == 512u || ncols == 1024u || ncols == 2048u); }
 

@@ -35,43 +35,6 @@
 
 namespace rc {
 
-constexpr uint32_t TC_M = 128u, TC_KS = 64u, TC_THREADS = 512u, TC_WARPS = TC_THREADS / 32u;
-constexpr uint32_t TC_A_DIGIT = TC_M * TC_KS * 2u;            // bytes of one weight digit tile of a stage (16 KB)
-constexpr uint32_t TC_SPIN_LIMIT = 4u * 1000u * 1000u;        // polls of ~50 ns: far beyond any legitimate wait
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-// shared-memory matrix descriptor: K-major, no swizzle, core matrix = 8 rows x 16 bytes stored as 128 contiguous bytes;
-// lbo = byte distance between the two 16-byte k-chunks of one MMA, sbo = byte distance between 8-row groups
-__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo >> 4) & 0x3fffu) << 16) | ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
-}
-
-// instruction descriptor, kind::f16: D = f32, A = B = f16, both K-major, M = 128, N = n
-__device__ __forceinline__ uint32_t tc_idesc(uint32_t n) { return (1u << 4) | ((n >> 3) << 17) | ((TC_M >> 4) << 24); }
-
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-        :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-
-__device__ __forceinline__ void tc_commit(uint32_t mbar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(mbar) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
-    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-                     : "=r"(done) : "r"(mbar), "r"(parity) : "memory");
-        if (done) return true;
-        __nanosleep(32);
-    }
-    return false;
-}
-
 __device__ __forceinline__ uint32_t tc_d_plane(uint32_t type, uint64_t nb) {
     return (uint32_t)(type == RC_Q6_K ? rc_q6_d(nb) : type == RC_IQ2_XXS ? rc_iq2_d(nb) : rc_iq3_d(nb));
 }

@@ -44,6 +44,7 @@ def _bind():
     L = lib()
     if getattr(L, "_engine_bound", False):
         return L
+    L.rl_engine_config_default.argtypes = [C.POINTER(RlEngineConfig)]
     L.rl_engine_open.restype = C.c_void_p
     L.rl_engine_open.argtypes = [C.c_char_p, C.POINTER(RlEngineConfig), C.c_char_p, C.c_size_t]
     L.rl_engine_close.argtypes = [C.c_void_p]

@@ -121,10 +121,11 @@ class EpMoeLayer:
         return out
 
 
-def gather_moe_forward(packed: torch.Tensor, hidden: int, top_k: int, world: int, partial_fn, shared_fn, group=None):
+def gather_moe_forward(packed: torch.Tensor, hidden: int, top_k: int, world: int, partial_fn, shared_fn, group=None, mark=None):
     """All-gather form of one layer. packed [T, hidden + 2*top_k] float32: the token's activation row followed by its
     router ids (int32 bits) and weights. partial_fn(all_packed [world*T, hidden + 2*top_k]) -> [world*T, hidden] partial
     sums of this rank's experts; shared_fn(packed) -> [T, hidden] or None (runs while the all-gather is in flight).
+    mark(name), when given, is called at the phase boundaries (a caller records CUDA events there).
     Returns routed [T, hidden] (+ shared)."""
     T = packed.shape[0]
     if world > 1:
@@ -135,12 +136,18 @@ def gather_moe_forward(packed: torch.Tensor, hidden: int, top_k: int, world: int
     else:
         all_packed = packed
         shared = shared_fn(packed) if shared_fn is not None else None
+    if mark:
+        mark("all_gather")
     partial = partial_fn(all_packed)
+    if mark:
+        mark("experts")
     if world > 1:
         routed = partial.new_empty((T, hidden))
         dist.reduce_scatter_tensor(routed, partial, op=dist.ReduceOp.SUM, group=group)
     else:
         routed = partial
+    if mark:
+        mark("reduce_scatter")
     return routed if shared is None else routed.add_(shared)
 
 
@@ -161,7 +168,8 @@ class EpGatherMoeLayer:
         self.partial = torch.empty(world * tokens, d.hidden, dtype=torch.float32, device=dev)
         self.side = torch.cuda.Stream(device=dev)
 
-    def forward(self, x: torch.Tensor, logits: torch.Tensor | None = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, logits: torch.Tensor | None = None, mark=None) -> torch.Tensor:
+        """mark(name): optional callback at the phase boundaries route+pack / all_gather / experts / reduce_scatter / add."""
         d, T = self.dims, self.T
         st = torch.cuda.current_stream().cuda_stream
         self.packed[:, :d.hidden].copy_(x)
@@ -183,6 +191,11 @@ class EpGatherMoeLayer:
                 self.m.shared_device(T, x.data_ptr(), self.shared.data_ptr(), self.side.cuda_stream)
             return None
 
-        routed = gather_moe_forward(self.packed, d.hidden, d.top_k, self.world, partial_fn, shared_fn, self.group)
+        if mark:
+            mark("route_pack")
+        routed = gather_moe_forward(self.packed, d.hidden, d.top_k, self.world, partial_fn, shared_fn, self.group, mark)
         torch.cuda.current_stream().wait_stream(self.side)
-        return routed.add_(self.shared)
+        out = routed.add_(self.shared)
+        if mark:
+            mark("add")
+        return out

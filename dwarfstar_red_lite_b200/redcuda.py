@@ -74,11 +74,15 @@ def lib():
     L.redcuda_moe_combine_device.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.redcuda_moe_partial_device.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
     L.redcuda_quant_dequant_rows.argtypes = [C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]
+    L.redcuda_nib_dequant_rows.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]
     L.redcuda_quant_matvec.argtypes = [C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
     L.redcuda_quant_matmul_tc.argtypes = [C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
     L.redcuda_router_select_softmax_topk.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]
     L.redcuda_deltanet_step.argtypes = [C.POINTER(DeltanetParams), C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.redcuda_deltanet_step_noalloc.argtypes = [C.POINTER(DeltanetParams), C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    L.redcuda_profile_enable.argtypes = [C.c_int]
+    L.redcuda_profile_report.argtypes = [C.c_char_p, C.c_size_t]
+    L.redcuda_set_device.argtypes = [C.c_int]
     L.redcuda_set_codebooks.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32]
     _lib = L
     return L

@@ -163,15 +163,21 @@ def test_non_finite_router_logits_are_an_error_not_an_address():
         m.close()
 
 
-def _check_moe(layer, x, logits_in=None, threads=8):
+def _check_moe(layer, x, logits_in=None, threads=8, rows=None, expect_kernel=None):
     d = layer.dims
     m = rc.MoeLayer(layer, max_tokens=x.shape[0])
     try:
+        if expect_kernel:           # one pass with per-kernel timing on (single stream) to see which kernels ran
+            rc.redcuda.profile_enable(True)
+            m.forward(x, logits_in=logits_in)
+            names = rc.redcuda.profile_report()
+            rc.redcuda.profile_enable(False)
+            assert expect_kernel in names, sorted(names)
         out, ids, w, logits = m.forward(x, logits_in=logits_in, want_routing=True)
     finally:
         m.close()
     view = ol.moe_layer_c(layer)
-    for t in range(x.shape[0]):
+    for t in (range(x.shape[0]) if rows is None else rows):
         ro, rid, rw, rl = ol.moe_ffn(layer, x[t], threads=threads, logits_in=None if logits_in is None else logits_in[t], view=view)
         if logits_in is None:
             assert np.array_equal(logits[t].view(np.uint32), rl.view(np.uint32)), "router logits differ"
@@ -206,6 +212,25 @@ def test_moe_layer_config1_ragged_zipf(full_layer):
     x = np.random.default_rng(10).normal(0, 1, size=(64, 2048)).astype(np.float32)
     logits = synth.zipf_routing_logits(77, 64)
     _check_moe(full_layer, x, logits_in=logits)
+
+
+def test_moe_chunk_on_tcgen05_small(monkeypatch):
+    """A chunk large enough for the tcgen05 expert kernel (>= 16 pairs per expert): 8 experts, 160 tokens, so that experts
+    get more than one 64-pair work item and ragged last items."""
+    monkeypatch.setenv("RC_MOE_TC_MIN", "16")
+    dims = synth.MoeDims(hidden=512, n_expert=8, top_k=2, ffn=256, ffn_sh=256)
+    layer = synth.moe_layer(31, dims, expert_scale=0.5)
+    x = np.random.default_rng(4).normal(0, 1, size=(160, dims.hidden)).astype(np.float32)
+    _check_moe(layer, x, expect_kernel="moe_gateup_tc")
+
+
+def test_moe_chunk_on_tcgen05_full_size(full_layer, monkeypatch):
+    """1024 tokens through the full-size layer with Zipf-skewed routing: the popular experts see hundreds of pairs (many
+    work items each), the tail ones a handful. Every 16th token is compared with the oracle."""
+    monkeypatch.setenv("RC_MOE_TC_MIN", "16")
+    x = np.random.default_rng(12).normal(0, 1, size=(1024, 2048)).astype(np.float32)
+    logits = synth.zipf_routing_logits(79, 1024)
+    _check_moe(full_layer, x, logits_in=logits, rows=range(0, 1024, 16), expect_kernel="moe_down_tc")
 
 
 def test_moe_linearity_of_routed_part(full_layer):
