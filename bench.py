@@ -197,7 +197,7 @@ def run_ep(args, world, rank, local):
         tens = synth_device.moe_layer_tensors(1000 + l, dims, dev, expert_begin=rank * ec, expert_count=ec)
         m = rc.MoeLayer(device_tensors=tens, dims=dims, max_tokens=T * world, expert_begin=rank * ec if contiguous else rank, expert_count=ec,
                         expert_stride=1 if contiguous else world)
-        layers.append(ep.EpGatherMoeLayer(m, rank, world, T))
+        layers.append(m if args.ep_impl == "c" else ep.EpGatherMoeLayer(m, rank, world, T))
         del tens
 
     def drawn_logits(l, r):
@@ -210,13 +210,21 @@ def run_ep(args, world, rank, local):
     x_d = torch.randn(L, T, dims.hidden, device=dev, generator=gx)
     logits_d = torch.from_numpy(np.ascontiguousarray(logits_h)).to(dev)
 
-    def step(mark=None):
-        for l in range(L):
-            layers[l].forward(x_d[l], logits=logits_d[l], mark=mark)
+    if args.ep_impl == "c":          # one C call per step: every launch and both collectives of every layer queued by the library
+        ctx = ep.EpStep(layers, rank, world, T)
+        ctx.bind(x_d, logits_d)
+
+        def step(mark=None):
+            ctx.step()
+    else:
+
+        def step(mark=None):
+            for l in range(L):
+                layers[l].forward(x_d[l], logits=logits_d[l], mark=mark)
 
     # ---- parity on the devices: layer 0's output of rank 0's first tokens against the oracle port of ffn()
     parity = None
-    out0 = layers[0].forward(x_d[0], logits=logits_d[0]).clone()
+    out0 = (ctx.layer_forward(0, x_d[0], logits_d[0]) if args.ep_impl == "c" else layers[0].forward(x_d[0], logits=logits_d[0])).clone()
     torch.cuda.synchronize()
     dist.barrier()
     if rank == 0 and not args.no_cpu:
@@ -276,10 +284,18 @@ def run_ep(args, world, rank, local):
             ev.record(side)
             marks.append((name, ev))
 
-        mark("begin")
-        step(mark)
-        side.synchronize()
-    phases = {}
+        phases = {}
+        if args.ep_impl == "c":       # per-kernel CUDA events of the library around one more step (collectives included)
+            rcm.profile_enable(True)
+            step()
+            side.synchronize()
+            for name, (_, ms_k) in rcm.profile_report().items():
+                phases[name] = ms_k
+            rcm.profile_enable(False)
+        else:
+            mark("begin")
+            step(mark)
+            side.synchronize()
     for (_, a), (name, bb) in zip(marks[:-1], marks[1:]):
         phases[name] = phases.get(name, 0.0) + a.elapsed_time(bb)
     ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
@@ -307,6 +323,7 @@ def run_ep(args, world, rank, local):
                                expert_placement="contiguous (expert e on rank e // (512 / N))" if contiguous else "interleaved (expert e on rank e % N)",
                                routing_ids_permuted=bool(args.ep_permute),
                                pairs_served_per_rank_per_layer=[float(p.item()) for p in allpairs], cuda_graph=False,
+                               step_driver="one C call per step (redcuda_ep_step)" if args.ep_impl == "c" else "Python loop over torch.distributed calls",
                                exchange="per layer: NCCL all-gather of the token rows (fp32 activations + router ids/weights), reduce-scatter of the partial outputs; no host synchronisation"),
                 "roofline": None, "cpu_baseline": None, "parity": parity,
                 "breakdown": {"host_enqueue_ms_per_step_max_over_ranks": float(enq.item()), "device_ms_per_step": ms_per_step,
@@ -720,6 +737,7 @@ def main():
     ap.add_argument("--prefill-batch", type=int, default=0, help="prefill: tokens per chunk (0 = engine default)")
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--ep-placement", default="interleaved", choices=["interleaved", "contiguous"], help="N > 1: which rank holds which expert")
+    ap.add_argument("--ep-impl", default="c", choices=["c", "python"], help="N > 1: the library's one-call step, or the per-operation Python loop")
     ap.add_argument("--ep-permute", action="store_true", help="N > 1: draw the routing over a random permutation of the expert ids")
     args = ap.parse_args()
     if args.workload == "decode48":

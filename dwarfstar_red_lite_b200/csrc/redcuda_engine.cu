@@ -430,7 +430,7 @@ static int eng_proj(rl_engine *e, const DMat *mats, float *const *outs, uint32_t
         uint32_t row_tiles = 0;
         for (uint32_t i = 0; i < n; ++i) row_tiles += tc_row_tiles(mats[i].nrows);
         const uint32_t tn = tc_token_tile(ntok, row_tiles);
-        if (!launch_tc_prep_x(x, mats[0].ncols, ntok, mats[0].ncols, tn, e->tc_xs, e->tc_xinv, e->stream)) return 0;
+        if (!launch_tc_prep_x(x, nullptr, mats[0].ncols, ntok, mats[0].ncols, tn, e->tc_xs, e->tc_xinv, e->stream)) return 0;
         TcArgs A{};
         A.njobs = n; A.ncols = mats[0].ncols; A.ntok = ntok; A.xs = e->tc_xs; A.x_inv = e->tc_xinv; A.err = e->tc_err;
         for (uint32_t i = 0; i < n; ++i) A.job[i] = TcJob{mats[i].base, mats[i].nb, mats[i].type, mats[i].nrows, outs[i], mats[i].nrows, 0u};

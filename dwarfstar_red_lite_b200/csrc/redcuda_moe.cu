@@ -203,6 +203,32 @@ __global__ void __launch_bounds__(256) k_moe_combine(const float *__restrict__ p
     *reinterpret_cast<float4 *>(out + (size_t)t * hidden + r) = acc;
 }
 
+// Combine of the all-gather form of expert parallelism: every rank holds every token's ids / weights;
+// out[t] = sum over the pairs of token t whose expert THIS shard holds of w * pair_out[t * top_k + k], plus add[t - add_begin]
+// for the add_count tokens from add_begin on (the rank's own tokens: their shared-expert part rides along in the
+// reduce-scatter). A token without local pairs gets zeros (or its add row).
+__global__ void __launch_bounds__(256) k_ep_combine(const float *__restrict__ pair_out, const uint32_t *__restrict__ ids, const float *__restrict__ w, uint32_t top_k,
+                                                    uint32_t begin, uint32_t stride, uint32_t count, const float *__restrict__ add, uint32_t add_begin, uint32_t add_count,
+                                                    float *__restrict__ out, uint32_t hidden) {
+    pdl_prologue();
+    const uint32_t t = blockIdx.y;
+    const uint32_t r = (blockIdx.x * 256u + threadIdx.x) * 4u;
+    if (r >= hidden) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t k = 0; k < top_k; ++k) {
+        const size_t p = (size_t)t * top_k + k;
+        if (shard_local(ids[p], begin, stride, count) == 0xffffffffu) continue;       // another shard computes this pair; its row here was never written
+        const float wk = w[p];
+        const float4 v = *reinterpret_cast<const float4 *>(pair_out + p * hidden + r);
+        acc.x += wk * v.x; acc.y += wk * v.y; acc.z += wk * v.z; acc.w += wk * v.w;
+    }
+    if (add && t >= add_begin && t - add_begin < add_count) {
+        const float4 v = *reinterpret_cast<const float4 *>(add + (size_t)(t - add_begin) * hidden + r);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4 *>(out + (size_t)t * hidden + r) = acc;
+}
+
 }  // namespace rc
 
 using namespace rc;
@@ -224,12 +250,14 @@ struct redcuda_moe {
     // digits of the token rows for redcuda_moe_shared_device alone: under expert parallelism it runs on another stream
     // than redcuda_moe_partial_device, which fills xq_x / sx_x with the gathered rows of every rank at the same time
     int8_t *xq_own = nullptr; float *sx_own = nullptr;
+    const int8_t *xq_ext = nullptr; const float *sx_ext = nullptr;   // digits of the gate/up input supplied by the caller for one call (rc::moe_partial_gathered)
     uint32_t max_pairs = 0;
     bool use_mma = false;      // IQ2_XXS experts (and the Q6_K shared expert of a batch) on the integer tensor-core path
     bool nib = false;          // routed experts held in the nibble layout (redcuda_moe_nib.cu) instead of planar IQ2_XXS
     uint32_t *work = nullptr;  // two unit counters of the persistent expert kernels (gate/up, down)
     uint32_t *ticket = nullptr; // ticket counter of the single-token GEMV's routing tail (zero between launches)
-    uint32_t *tc_err = nullptr; // timeout flag of the tcgen05 expert kernel
+    uint32_t *tc_err = nullptr; // timeout flag of the tcgen05 kernels
+    __half *sh_xs = nullptr; float *sh_xinv = nullptr;   // shared expert on the tcgen05 GEMM: activation digits and inverse scales
     bool tc_ok = false;         // the tcgen05 expert kernel can serve this layer's shapes
     bool tc_now = false;        // ... and serves the call in progress (set by moe_choose_path, read by the grouping and the launches)
     bool ws_shared = false;     // the workspace belongs to the caller (rc::moe_create_shared)
@@ -266,6 +294,25 @@ static bool moe_shared_mma(const redcuda_moe *m, uint32_t ntok) {
     return m->use_mma && m->d.type_sh == RC_Q6_K && ntok >= 3u && m->d.ffn_sh % 16u == 0 && m->d.hidden % 16u == 0;
 }
 
+// tcgen05 GEMM for the shared expert: from RC_SH_TC_MIN tokens on (default 128; 0 = never). Needs room for the "up"
+// half of the gate/up pair in sh_out (ffn_sh <= hidden).
+static bool moe_shared_tc(const redcuda_moe *m, uint32_t ntok) {
+    const char *v = getenv("RC_SH_TC_MIN");
+    const uint32_t min_tok = v ? (uint32_t)atoi(v) : 128u;
+    return min_tok && ntok >= min_tok && rc_is_quant(m->d.type_sh) && m->d.ffn_sh <= m->d.hidden && m->d.hidden % 256u == 0 && m->d.ffn_sh % 256u == 0;
+}
+// out[j][t][row] = W_j x[t] for one or two matrices that share x (x2: the input is SiLU(x) * x2)
+static int moe_shared_tc_gemm(redcuda_moe *m, uint32_t ntok, const float *x, const float *x2, uint32_t ncols, const DMat *w0, float *out0, const DMat *w1, float *out1,
+                              const char *tag, cudaStream_t s) {
+    const uint32_t tn = tc_token_tile(ntok, tc_row_tiles(w0->nrows) + (w1 ? tc_row_tiles(w1->nrows) : 0u));
+    if (!launch_tc_prep_x(x, x2, ncols, ntok, ncols, tn, m->sh_xs, m->sh_xinv, s)) return 0;
+    TcArgs A{};
+    A.njobs = w1 ? 2u : 1u; A.ncols = ncols; A.ntok = ntok; A.xs = m->sh_xs; A.x_inv = m->sh_xinv; A.err = m->tc_err;
+    A.job[0] = TcJob{w0->base, w0->nb, w0->type, w0->nrows, out0, w0->nrows, 0u};
+    if (w1) A.job[1] = TcJob{w1->base, w1->nb, w1->type, w1->nrows, out1, w1->nrows, 0u};
+    return launch_tc_gemm(A, tn, tag, s);
+}
+
 // x_quantised: xq_x / sx_x already hold the digits of x
 static int moe_gemv_pre(redcuda_moe *m, uint32_t ntok, const float *x, bool with_router, bool with_shared, bool x_quantised, cudaStream_t s,
                         const int8_t *xq = nullptr, const float *sx = nullptr, const RouteTail *tail = nullptr) {
@@ -285,7 +332,9 @@ static int moe_gemv_pre(redcuda_moe *m, uint32_t ntok, const float *x, bool with
         } else add(m->router, nullptr, m->logits, m->d.n_expert, GEMV_STORE);
     }
     if (with_shared) {
-        if (moe_shared_mma(m, ntok) && x_quantised) {
+        if (moe_shared_tc(m, ntok)) {       // gate -> sh_act, up -> sh_out; moe_shared_down applies SiLU(gate) * up
+            if (!moe_shared_tc_gemm(m, ntok, x, nullptr, m->d.hidden, &m->sh_gate, m->sh_act, &m->sh_up, m->sh_out, "moe_shared_gateup_tc", s)) return 0;
+        } else if (moe_shared_mma(m, ntok) && x_quantised) {
             if (!launch_q6k_mma(m->sh_gate.base, m->sh_up.base, m->sh_gate.nb, m->d.ffn_sh, m->d.hidden, ntok, xq, sx, m->sh_act, m->d.ffn_sh,
                                 "moe_shared_gateup_mma", s)) return 0;
         } else add(m->sh_gate, &m->sh_up, m->sh_act, m->d.ffn_sh, GEMV_PAIR_SILU);
@@ -301,6 +350,7 @@ static int moe_gemv_pre(redcuda_moe *m, uint32_t ntok, const float *x, bool with
 }
 
 static int moe_shared_down(redcuda_moe *m, uint32_t ntok, cudaStream_t s) {
+    if (moe_shared_tc(m, ntok)) return moe_shared_tc_gemm(m, ntok, m->sh_act, m->sh_out, m->d.ffn_sh, &m->sh_down, m->sh_out, nullptr, nullptr, "moe_shared_down_tc", s);
     if (moe_shared_mma(m, ntok)) {
         if (!launch_quant_act(m->sh_act, m->d.ffn_sh, ntok, m->d.ffn_sh, m->xq_sh, m->sx_sh, s)) return 0;
         return launch_q6k_mma(m->sh_down.base, nullptr, m->sh_down.nb, m->d.hidden, m->d.ffn_sh, ntok, m->xq_sh, m->sx_sh, m->sh_out, m->d.hidden,
@@ -341,12 +391,14 @@ static int moe_launch_experts(redcuda_moe *m, bool gateup, uint32_t npairs, bool
         int8_t *xq = gateup ? m->xq_x : m->xq_act;
         float *sx = gateup ? m->sx_x : m->sx_act;
         if (!x_quantised && !launch_quant_act(x, x_stride, (npairs + x_div - 1u) / x_div, ncols, xq, sx, s)) return 0;
+        const int8_t *xq_in = gateup && m->xq_ext ? m->xq_ext : xq;
+        const float *sx_in = gateup && m->sx_ext ? m->sx_ext : sx;
         MmaArgs M{};
         M.w0 = gateup ? m->gate : m->down; M.w1 = gateup ? m->up : nullptr;
         M.mat_bytes = gateup ? m->gu_bytes : m->down_bytes; M.nb = gateup ? m->gu_nb : m->down_nb;
         M.nrows = nrows; M.ncols = ncols; M.expert_begin = m->d.expert_begin; M.n_local = m->d.expert_count; M.status = status_words();
         M.sorted = m->sorted; M.uexp = m->uexp; M.ustart = m->ustart; M.item_u = m->item_u; M.item_p0 = m->item_p0; M.n_items = m->n_items;
-        M.xq = xq; M.sx = sx; M.x_div = x_div; M.out = out; M.out_stride = out_stride;
+        M.xq = xq_in; M.sx = sx_in; M.x_div = x_div; M.out = out; M.out_stride = out_stride;
         const uint32_t tok = moe_item_tokens(m, single_token, npairs);
         const uint32_t live = npairs < m->d.expert_count ? npairs : m->d.expert_count;
         const uint32_t max_items = single_token ? npairs : (npairs / tok + live < npairs ? npairs / tok + live : npairs);
@@ -505,6 +557,7 @@ static size_t moe_ws_layout(const redcuda_moe_desc &d, redcuda_moe *m, uint8_t *
     put(r.xq_x, P * 4u * d.hidden); put(r.sx_x, P * 4u); put(r.xq_act, P * 4u * d.ffn); put(r.sx_act, P * 4u);
     put(r.xq_sh, T * 3u * d.ffn_sh); put(r.sx_sh, T * 4u); put(r.xq_own, T * 3u * d.hidden); put(r.sx_own, T * 4u);
     put(r.item_u, (P + 8u) * 4u); put(r.item_p0, (P + 8u) * 4u); put(r.n_items, 16); put(r.work, 16);
+    put(r.sh_xs, tc_xs_halves((uint32_t)T, d.hidden > d.ffn_sh ? d.hidden : d.ffn_sh, 128u) * 2u); put(r.sh_xinv, (T + 128u) * 4u);
     if (m) { m->ticket = m->work + 2; m->tc_err = m->work + 3; }
     return w;
 }
@@ -512,6 +565,33 @@ static size_t moe_ws_layout(const redcuda_moe_desc &d, redcuda_moe *m, uint8_t *
 namespace rc {
 const uint32_t *moe_last_ids_device(const redcuda_moe *m) { return m->ids; }
 void moe_set_ids_mirror(redcuda_moe *m, uint32_t *dev_ptr) { m->ids_mirror = dev_ptr; }
+}
+namespace rc {
+// true when the routed experts read int8 activation digits (so a caller may quantise before an exchange and hand the digits in)
+bool moe_takes_digits(const redcuda_moe *m) { return moe_experts_mma(m); }
+// The shard's experts over gathered tokens: x [ntok][hidden] fp32, or (when xq is given) its digits xq [ntok][3][hidden] with
+// scales sx [ntok]; ids / w [ntok][top_k] contiguous. out [ntok][hidden] as k_ep_combine defines it.
+int moe_partial_gathered(redcuda_moe *m, uint32_t ntok, const float *x, const int8_t *xq, const float *sx, const uint32_t *ids, const float *w,
+                         const float *add, uint32_t add_begin, uint32_t add_count, float *out, cudaStream_t s) {
+    RC_REQUIRE(m && (x || (xq && sx)) && ids && w && out, "moe partial: null argument");
+    RC_REQUIRE(ntok >= 1 && ntok <= m->d.max_tokens, "moe partial: ntok %u outside [1, %u]", ntok, m->d.max_tokens);
+    const uint32_t k = m->d.top_k, npairs = ntok * k;
+    moe_choose_path(m, npairs, false);
+    const bool digits = xq && moe_experts_mma(m) && !m->tc_now;
+    RC_REQUIRE(digits || x, "moe partial: this layer's expert kernels need the fp32 rows");
+    if (!moe_group(m, ids, npairs, false, s, true)) return 0;
+    if (digits) { m->xq_ext = xq; m->sx_ext = sx; }
+    const int ok = moe_launch_experts(m, true, npairs, false, x, m->d.hidden, k, digits, m->act, m->d.ffn, s);
+    m->xq_ext = nullptr; m->sx_ext = nullptr;
+    if (!ok) return 0;
+    if (!moe_launch_experts(m, false, npairs, false, m->act, m->d.ffn, 1u, false, m->tmp, m->d.hidden, s)) return 0;
+    const dim3 grid((m->d.hidden / 4u + 255u) / 256u, ntok);
+    prof_begin("ep_combine", s);
+    RC_LAUNCH((k_ep_combine), grid, 256, 0, s, m->tmp, ids, w, k, m->d.expert_begin, m->d.expert_stride, m->d.expert_count, add, add_begin, add_count, out, m->d.hidden);
+    prof_end(s);
+    RC_LAUNCHED();
+    return 1;
+}
 }
 static redcuda_moe *moe_create_impl(const redcuda_moe_desc *desc, void *shared_ws);
 namespace rc {

@@ -28,6 +28,7 @@
 #define RC_PDL_DEFAULT 0
 #include "redcuda_common.cuh"
 #include "redcuda_formats.cuh"
+#include "redcuda_dot.cuh"
 #include "redcuda_kernels.cuh"
 #include "redcuda_tc_gemm.cuh"
 
@@ -161,17 +162,18 @@ __device__ __forceinline__ void tc_decode_stage(const uint8_t *raw, uint8_t *abu
     }
 }
 
-// x [ntok][ncols] fp32 -> fp16 digits in the order the GEMM stages consume them:
+// x [ntok][ncols] fp32 (or SiLU(x) * x2 when x2 is given) -> fp16 digits in the order the GEMM stages consume them:
 // xs[token tile][k stage][digit hi/lo][k chunk of 8 (8)][token group of 8 (TN/8)][token in group (8)][8 halves];
 // x_inv[t] = 2^-e_t undoes the per-token scale. Tokens beyond ntok are zero. grid = token tiles * TN, block = 256
-__global__ void k_tc_prep_x(const float *__restrict__ x, uint32_t x_stride, uint32_t ntok, uint32_t ncols, uint32_t tn,
+__global__ void k_tc_prep_x(const float *__restrict__ x, const float *__restrict__ x2, uint32_t x_stride, uint32_t ntok, uint32_t ncols, uint32_t tn,
                             __half *__restrict__ xs, float *__restrict__ x_inv) {
     pdl_prologue();
     __shared__ float red[8];
     const uint32_t t = blockIdx.x, tid = threadIdx.x;
     const bool live = t < ntok;
     float mx = 0.f;
-    if (live) for (uint32_t k = tid; k < ncols; k += blockDim.x) mx = fmaxf(mx, fabsf(x[(size_t)t * x_stride + k]));
+    auto val = [&](uint32_t k) { const size_t i = (size_t)t * x_stride + k; return x2 ? silu_mul(x[i], x2[i]) : x[i]; };
+    if (live) for (uint32_t k = tid; k < ncols; k += blockDim.x) mx = fmaxf(mx, fabsf(val(k)));
     for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     if ((tid & 31u) == 0) red[tid >> 5] = mx;
     __syncthreads();
@@ -189,7 +191,7 @@ __global__ void k_tc_prep_x(const float *__restrict__ x, uint32_t x_stride, uint
         __half hi[8], lo[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const float v = live ? x[(size_t)t * x_stride + c * 8u + j] * sc : 0.f;
+            const float v = live ? val(c * 8u + j) * sc : 0.f;
             hi[j] = __float2half_rn(v);
             lo[j] = __float2half_rn(v - __half2float(hi[j]));
         }
@@ -389,12 +391,12 @@ static size_t tc_smem_bytes(uint32_t tn, uint32_t raw_max) {
     return 2u * 2u * (size_t)TC_A_DIGIT + (size_t)nb * 2u * tn * TC_KS * 2u + 2u * (size_t)raw_max;
 }
 
-int launch_tc_prep_x(const float *x, uint32_t x_stride, uint32_t ntok, uint32_t ncols, uint32_t tn, __half *xs, float *x_inv, cudaStream_t s) {
+int launch_tc_prep_x(const float *x, const float *x2, uint32_t x_stride, uint32_t ntok, uint32_t ncols, uint32_t tn, __half *xs, float *x_inv, cudaStream_t s) {
     RC_REQUIRE(ncols % TC_KS == 0, "tc gemm: %u columns is not a multiple of %u", ncols, TC_KS);
     RC_REQUIRE(tn == 32u || tn == 64u || tn == 128u, "tc gemm: token tile %u is not 32, 64 or 128", tn);
     const uint32_t tiles = (ntok + tn - 1u) / tn;
     prof_begin("tc_prep_x", s);
-    RC_LAUNCH((k_tc_prep_x), tiles * tn, 256, 0, s, x, x_stride, ntok, ncols, tn, xs, x_inv);
+    RC_LAUNCH((k_tc_prep_x), tiles * tn, 256, 0, s, x, x2, x_stride, ntok, ncols, tn, xs, x_inv);
     prof_end(s);
     RC_LAUNCHED();
     return 1;
@@ -446,7 +448,7 @@ extern "C" int redcuda_quant_matmul_tc(uint32_t type, const uint8_t *w, uint32_t
     if (!upload_matrix(type, nrows, ncols, w, false, planar.as<uint8_t>(), raw.as<uint8_t>(), s)) return 0;
     RC_CUDA(cudaMemcpyAsync(xd.p, x, (size_t)ntok * ncols * 4u, cudaMemcpyHostToDevice, s));
     RC_CUDA(cudaMemsetAsync(err.p, 0, 4u, s));
-    if (!launch_tc_prep_x(xd.as<float>(), ncols, ntok, ncols, tn, xs.as<__half>(), xinv.as<float>(), s)) return 0;
+    if (!launch_tc_prep_x(xd.as<float>(), nullptr, ncols, ntok, ncols, tn, xs.as<__half>(), xinv.as<float>(), s)) return 0;
     TcArgs A{};
     A.njobs = 1; A.ncols = ncols; A.ntok = ntok; A.xs = xs.as<__half>(); A.x_inv = xinv.as<float>(); A.err = err.as<uint32_t>();
     A.job[0] = TcJob{planar.as<uint8_t>(), (uint64_t)nrows * (ncols / 256u), type, nrows, od.as<float>(), nrows, 0u};

@@ -30,7 +30,8 @@ struct TcArgs {
 size_t tc_xs_halves(uint32_t ntok, uint32_t ncols, uint32_t tn);
 uint32_t tc_row_tiles(uint32_t nrows);
 uint32_t tc_token_tile(uint32_t ntok, uint32_t row_tiles);     // row_tiles = sum of tc_row_tiles over the launch's matrices
-int launch_tc_prep_x(const float *x, uint32_t x_stride, uint32_t ntok, uint32_t ncols, uint32_t tn, __half *xs, float *x_inv, cudaStream_t s);
+// x2 (may be null): the digits are those of SiLU(x) * x2, both with rows x_stride apart
+int launch_tc_prep_x(const float *x, const float *x2, uint32_t x_stride, uint32_t ntok, uint32_t ncols, uint32_t tn, __half *xs, float *x_inv, cudaStream_t s);
 int launch_tc_gemm(TcArgs &A, uint32_t tn, const char *tag, cudaStream_t s);   // tn: the tile the digits were prepared with
 
 // ---- routed experts of a prefill chunk on the tensor cores (redcuda_tc_experts.cu) ----

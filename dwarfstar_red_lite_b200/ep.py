@@ -6,6 +6,9 @@ stay with their rank. Two forms:
   their router ids / weights (a decode batch is small: 64 tokens x 8 KB per rank), runs its own experts over the pairs
   that select them, and a reduce-scatter sums the ranks' partial outputs back to the tokens' owners. Two fixed-size
   collectives per layer, nothing data-dependent on the host, so the whole step is queued without a synchronisation.
+  EpStep runs the same form through ONE C call per step (redcuda_ep_step: every launch and both collectives of every
+  layer queued by the library), which takes the Python / torch.distributed overhead of ~12 operations per layer off the
+  host; EpGatherMoeLayer keeps the per-operation Python form for A/B runs and for the CPU (gloo) tests of the data flow.
 * dispatch form (EpMoeLayer): experts sharded contiguously (expert e on rank e // (n_expert / world)), pairs sent to
   their experts' ranks by all-to-all with data-dependent split sizes (one host synchronisation per layer).
 
@@ -199,3 +202,62 @@ class EpGatherMoeLayer:
         if mark:
             mark("add")
         return out
+
+
+class EpStep:
+    """The all-gather form through the library's own step call: one C entry per step queues route, pack, all-gather, the
+    shard's experts, reduce-scatter, shared expert and add of every layer. `shards` are redcuda MoeLayer objects created
+    with max_tokens >= world * tokens. The NCCL unique id travels from rank 0 over `group` (any backend)."""
+
+    def __init__(self, shards, rank: int, world: int, tokens: int, group=None):
+        import ctypes as C
+        import numpy as np
+        from .redcuda import RedcudaError, lib
+        self._lib, self._C = lib(), C
+        d = shards[0].dims
+        self.dims, self.T, self.world, self.shards = d, tokens, world, shards
+        dev = torch.device("cuda", torch.cuda.current_device())
+        uid = torch.zeros(128, dtype=torch.uint8)
+        if world > 1:
+            if rank == 0:
+                buf = (C.c_uint8 * 128)()
+                if self._lib.redcuda_ep_unique_id(buf) != 1:
+                    raise RedcudaError(self._lib.redcuda_last_error().decode(errors="replace"))
+                uid = torch.from_numpy(np.frombuffer(buf, dtype=np.uint8).copy())
+            uid = uid.to(dev) if dist.get_backend(group) == "nccl" else uid
+            dist.broadcast(uid, src=0, group=group)
+            uid = uid.cpu()
+        self._uid = uid.numpy().tobytes()
+        self._h = self._lib.redcuda_ep_create(rank, world, self._uid, tokens, d.hidden, d.top_k)
+        if not self._h:
+            raise RedcudaError(self._lib.redcuda_last_error().decode(errors="replace"))
+        n = len(shards)
+        self._layers = (C.c_void_p * n)(*[m.handle for m in shards])
+        self.out = torch.empty(n, tokens, d.hidden, dtype=torch.float32, device=dev)
+        self._outs = (C.c_void_p * n)(*[self.out[l].data_ptr() for l in range(n)])
+
+    def bind(self, x: torch.Tensor, logits: torch.Tensor | None = None):
+        """x [layers][tokens][hidden] (every layer its own input, as the benchmark feeds them), logits [layers][tokens][n_expert] or None"""
+        C, n = self._C, len(self.shards)
+        self._x_keep, self._lg_keep = x, logits
+        self._xs = (C.c_void_p * n)(*[x[l].data_ptr() for l in range(n)])
+        self._lgs = None if logits is None else (C.c_void_p * n)(*[logits[l].data_ptr() for l in range(n)])
+
+    def step(self):
+        from .redcuda import RedcudaError
+        st = torch.cuda.current_stream().cuda_stream
+        if self._lib.redcuda_ep_step(self._h, self._layers, len(self.shards), self._xs, self._lgs, self._outs, st) != 1:
+            raise RedcudaError(self._lib.redcuda_last_error().decode(errors="replace"))
+        return self.out
+
+    def layer_forward(self, l: int, x: torch.Tensor, logits: torch.Tensor | None = None) -> torch.Tensor:
+        from .redcuda import RedcudaError
+        st = torch.cuda.current_stream().cuda_stream
+        if self._lib.redcuda_ep_layer_forward(self._h, self.shards[l].handle, x.data_ptr(), 0 if logits is None else logits.data_ptr(), self.out[l].data_ptr(), st) != 1:
+            raise RedcudaError(self._lib.redcuda_last_error().decode(errors="replace"))
+        return self.out[l]
+
+    def close(self):
+        if self._h:
+            self._lib.redcuda_ep_destroy(self._h)
+            self._h = None

@@ -142,6 +142,23 @@ uint64_t redcuda_moe_resident_bytes(const redcuda_moe *m);
 int redcuda_moe_partial_device(redcuda_moe *m, uint32_t ntok, const float *x_dev, uint32_t x_stride, const uint32_t *ids_dev,
                                const float *weights_dev, uint32_t meta_stride, float *out_dev, void *stream);
 
+/* The all-gather form of expert parallelism as one host call per layer or per step (redcuda_ep.cu; no reference
+ * counterpart). One process per GPU; every rank keeps `tokens` tokens and a shard of every layer's experts (a redcuda_moe
+ * created with expert_begin / expert_count / expert_stride and max_tokens >= world * tokens). Rank 0 draws a unique id
+ * (128 bytes) and hands it to the other ranks by any means; create is collective (ncclCommInitRank). NCCL is loaded
+ * with dlopen("libnccl.so.2") on first use; world = 1 needs none.
+ *   layer_forward: out[t] = routed(x[t]) over all ranks' experts + shared(x[t]) * sigmoid(g.x[t]) for the rank's own
+ *                  tokens (device pointers [tokens][hidden], asynchronous on `stream`; logits_in_dev may be NULL)
+ *   step:          layer_forward for n_layers layers in order; x_dev[l] / out_dev[l] per layer (a caller that chains
+ *                  layers passes out_dev[l - 1] as x_dev[l]), logits_in_dev NULL or one pointer (or NULL) per layer */
+typedef struct redcuda_ep redcuda_ep;
+int redcuda_ep_unique_id(void *out128);
+redcuda_ep *redcuda_ep_create(int rank, int world, const void *unique_id128, uint32_t tokens, uint32_t hidden, uint32_t top_k);
+void redcuda_ep_destroy(redcuda_ep *ep);
+int redcuda_ep_layer_forward(redcuda_ep *ep, redcuda_moe *layer, const float *x_dev, const float *logits_in_dev, float *out_dev, void *stream);
+int redcuda_ep_step(redcuda_ep *ep, redcuda_moe *const *layers, uint32_t n_layers, const float *const *x_dev, const float *const *logits_in_dev,
+                    float *const *out_dev, void *stream);
+
 /* One MoE FFN pass over ntok tokens (host pointers, synchronous): out[t] = routed(x[t]) + shared(x[t]) * sigmoid(g.x[t]).
  * logits_in, when not NULL, replaces the router matvec ([ntok][n_expert], the "drawn logits" of the ragged-batch
  * workload). ids_out [ntok][top_k], weights_out [ntok][top_k], logits_out [ntok][n_expert] may be NULL. */

@@ -371,3 +371,31 @@ def test_ep_gather_layer_single_rank_matches_fused_forward(full_layer):
             assert np.max(np.abs(got.cpu().numpy() - want)) <= 4e-6 * np.max(np.abs(want))
     finally:
         m.close()
+
+
+def test_ep_step_call_single_rank_matches_fused_forward(full_layer):
+    """redcuda_ep_step with one rank (no NCCL): the library's own step call over two layer objects reproduces the fused
+    forward of each layer on its own input."""
+    import torch
+    from dwarfstar_red_lite_b200 import ep
+    rng = np.random.default_rng(18)
+    T = 24
+    x = rng.normal(0, 1, size=(2, T, 2048)).astype(np.float32)
+    logits = np.stack([synth.zipf_routing_logits(84 + l, T) for l in range(2)])
+    shards = [rc.MoeLayer(full_layer, max_tokens=T) for _ in range(2)]
+    ctx = None
+    try:
+        want = [shards[l].forward(x[l], logits_in=logits[l]) for l in range(2)]
+        dev = torch.device("cuda", 0)
+        ctx = ep.EpStep(shards, 0, 1, T)
+        ctx.bind(torch.from_numpy(x).to(dev), torch.from_numpy(logits).to(dev))
+        for _ in range(2):
+            got = ctx.step()
+            torch.cuda.synchronize()
+            for l in range(2):
+                assert np.max(np.abs(got[l].cpu().numpy() - want[l])) <= 4e-6 * np.max(np.abs(want[l]))
+    finally:
+        if ctx:
+            ctx.close()
+        for m in shards:
+            m.close()
