@@ -211,7 +211,7 @@ def run_ep(args, world, rank, local):
     logits_d = torch.from_numpy(np.ascontiguousarray(logits_h)).to(dev)
 
     if args.ep_impl == "c":          # one C call per step: every launch and both collectives of every layer queued by the library
-        ctx = ep.EpStep(layers, rank, world, T)
+        ctx = ep.EpStep(layers, rank, world, T, exchange=args.ep_exchange)
         ctx.bind(x_d, logits_d)
 
         def step(mark=None):
@@ -324,7 +324,9 @@ def run_ep(args, world, rank, local):
                                routing_ids_permuted=bool(args.ep_permute),
                                pairs_served_per_rank_per_layer=[float(p.item()) for p in allpairs], cuda_graph=False,
                                step_driver="one C call per step (redcuda_ep_step)" if args.ep_impl == "c" else "Python loop over torch.distributed calls",
-                               exchange="per layer: NCCL all-gather of the token rows (fp32 activations + router ids/weights), reduce-scatter of the partial outputs; no host synchronisation"),
+                               exchange_kind=(ctx.exchange if args.ep_impl == "c" else "nccl"),
+                               exchange="per layer: all-gather of the token rows (int8 digits + scales, router ids / weights), reduce-scatter of the partial outputs; "
+                                        "peer = stores into the other ranks' memory over NVLink with flag words inside the compute kernels, nccl = ncclAllGather / ncclReduceScatter; no host synchronisation"),
                 "roofline": None, "cpu_baseline": None, "parity": parity,
                 "breakdown": {"host_enqueue_ms_per_step_max_over_ranks": float(enq.item()), "device_ms_per_step": ms_per_step,
                               "rank0_phase_ms_per_step": {k: round(v, 3) for k, v in phases.items()},
@@ -333,6 +335,8 @@ def run_ep(args, world, rank, local):
                         "note": "multi-GPU runs keep activations on the devices; the host-buffer path is measured at N=1"},
                 "gpu_launches": int(launches_per_step * args.steps), "clocks": clocks.summary()}
         print(json.dumps(line), flush=True)
+    if args.ep_impl == "c":
+        ctx.close()
     dist.destroy_process_group()
 
 
@@ -738,6 +742,7 @@ def main():
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--ep-placement", default="interleaved", choices=["interleaved", "contiguous"], help="N > 1: which rank holds which expert")
     ap.add_argument("--ep-impl", default="c", choices=["c", "python"], help="N > 1: the library's one-call step, or the per-operation Python loop")
+    ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"], help="N > 1, --ep-impl c: exchange through peer memory or through NCCL")
     ap.add_argument("--ep-permute", action="store_true", help="N > 1: draw the routing over a random permutation of the expert ids")
     args = ap.parse_args()
     if args.workload == "decode48":

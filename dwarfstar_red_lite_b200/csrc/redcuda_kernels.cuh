@@ -61,6 +61,59 @@ int launch_deltanet_seq(const DnDims &D, uint32_t T, const float *conv_kernel, c
                     const float *qkv, const float *z, const float *ba, float *conv_state, float *rec_state,
                     float *qk, float *v, float *beta, float *gate, float *core, float *out, cudaStream_t s);
 
+// Cross-GPU flags of the peer-memory exchange (redcuda_ep.cu): a flag word holds the sequence number of the last step its
+// writer completed. ep_wait_flag spins (system-scope acquire loads, at most EP_WAIT_NS) until *flag has reached seq;
+// on a timeout, or when an earlier wait already failed (*dead != 0), it returns false at once, sets *dead and the sticky
+// ST_TIMEOUT status word.
+struct EpWait { const uint32_t *flags; uint32_t n, seq; uint32_t *dead, *status; };     // flags[i * 32] for i < n; flags == nullptr: no wait
+constexpr uint32_t EP_MAX_WORLD = 8u;
+// The exchange areas of every rank (this rank's own included) as mapped into this process, all with the same layout.
+struct EpPeers { uint8_t *base[EP_MAX_WORLD]; uint32_t world, rank; };
+// Where the combine of the all-gather form delivers: token t's partial row goes to its owner's slot
+// base[t / tokens] + off_part + ((rank * tokens + t % tokens) * hidden) * 4, and when every block has written, the flag word
+// base[p] + off_flag + rank * 128 of every rank p is set to seq. ticket: a zeroed device word, left at zero.
+struct EpPush { EpPeers peers; size_t off_part, off_flag; uint32_t tokens, seq; uint32_t *ticket; };
+#ifdef __CUDACC__
+// after a block's stores to peer memory: the last block of the grid (by ticket) publishes seq to every rank
+__device__ __forceinline__ void ep_signal_all(const EpPeers &P, size_t off_flag, uint32_t seq, uint32_t *ticket, uint32_t nblocks) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (atomicAdd(ticket, 1u) == nblocks - 1u) {
+            *ticket = 0u;
+            __threadfence_system();
+            for (uint32_t p = 0; p < P.world; ++p)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(P.base[p] + off_flag + (size_t)P.rank * 128u), "r"(seq) : "memory");
+        }
+    }
+}
+#endif
+#ifdef __CUDACC__
+constexpr unsigned long long EP_WAIT_NS = 2000000000ull;
+__device__ __forceinline__ bool ep_wait_flag(const uint32_t *flag, uint32_t seq, uint32_t *dead, uint32_t *status) {
+    if (*reinterpret_cast<volatile uint32_t *>(dead)) return false;
+    unsigned long long t0, t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if ((int32_t)(v - seq) >= 0) return true;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        if (t - t0 > EP_WAIT_NS) break;
+        __nanosleep(64);
+    }
+    *reinterpret_cast<volatile uint32_t *>(dead) = 1u;
+    if (status) status[3] = 1u;       // ST_TIMEOUT
+    return false;
+}
+// the first W.n threads of a block wait for one flag each; every thread of the block must call it
+__device__ __forceinline__ void ep_wait_all(const EpWait &W) {
+    if (!W.flags) return;
+    if (threadIdx.x < W.n) ep_wait_flag(W.flags + threadIdx.x * 32u, W.seq, W.dead, W.status);
+    __syncthreads();
+}
+#endif
+
 int launch_vec_sigmoid(const float *w, const float *x, uint32_t x_stride, uint32_t ncols, uint32_t ntok, float *out, cudaStream_t stream);
 // logits[t][e] = dot(w[e], x[t]) accumulated in double, F32 weights [n_expert][ncols]; for batches (tiled fp64 GEMM)
 int launch_router_logits(const float *w, const float *x, uint32_t x_stride, uint32_t ntok, uint32_t n_expert, uint32_t ncols, float *logits, cudaStream_t stream);

@@ -119,8 +119,9 @@ __device__ __forceinline__ uint32_t shard_local(uint32_t g, uint32_t begin, uint
 __global__ void __launch_bounds__(1024) k_group_pairs(const uint32_t *__restrict__ pair_expert, uint32_t npairs, uint32_t expert_begin, uint32_t expert_stride,
                                                       uint32_t skip_foreign, uint32_t expert_count, uint32_t item_tok, uint32_t *__restrict__ sorted, uint32_t *__restrict__ uexp,
                                                       uint32_t *__restrict__ ustart, uint32_t *__restrict__ n_unique, uint32_t *__restrict__ item_u,
-                                                      uint32_t *__restrict__ item_p0, uint32_t *__restrict__ n_items, uint32_t *__restrict__ bad, uint32_t *__restrict__ work) {
+                                                      uint32_t *__restrict__ item_p0, uint32_t *__restrict__ n_items, uint32_t *__restrict__ bad, uint32_t *__restrict__ work, const EpWait wait) {
     pdl_prologue();
+    ep_wait_all(wait);         // peer-memory exchange: the pairs' ids are written by the other ranks; wait until every rank's rows have landed
     if (work && threadIdx.x < 2u) work[threadIdx.x] = 0u;      // unit counters of the persistent expert kernels that follow
     __shared__ uint32_t cnt[1024], start[1024], wsum[32], wsum2[32], wsum3[32];
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
@@ -229,6 +230,29 @@ __global__ void __launch_bounds__(256) k_ep_combine(const float *__restrict__ pa
     *reinterpret_cast<float4 *>(out + (size_t)t * hidden + r) = acc;
 }
 
+// The same sum delivered through peer memory: token t's row is stored into the slot its owner keeps for this rank
+// (NVLink stores; zeros when no local expert served the token, so that the owner can add all slots), then the flag.
+__global__ void __launch_bounds__(256) k_ep_combine_push(const float *__restrict__ pair_out, const uint32_t *__restrict__ ids, const float *__restrict__ w, uint32_t top_k,
+                                                         uint32_t begin, uint32_t stride, uint32_t count, const __grid_constant__ EpPush P, uint32_t hidden) {
+    pdl_prologue();
+    const uint32_t t = blockIdx.y;
+    const uint32_t r = (blockIdx.x * 256u + threadIdx.x) * 4u;
+    if (r < hidden) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t k = 0; k < top_k; ++k) {
+            const size_t p = (size_t)t * top_k + k;
+            if (shard_local(ids[p], begin, stride, count) == 0xffffffffu) continue;
+            const float wk = w[p];
+            const float4 v = *reinterpret_cast<const float4 *>(pair_out + p * hidden + r);
+            acc.x += wk * v.x; acc.y += wk * v.y; acc.z += wk * v.z; acc.w += wk * v.w;
+        }
+        const uint32_t owner = t / P.tokens, tl = t - owner * P.tokens;
+        float *dst = reinterpret_cast<float *>(P.peers.base[owner] + P.off_part) + ((size_t)P.peers.rank * P.tokens + tl) * hidden + r;
+        *reinterpret_cast<float4 *>(dst) = acc;
+    }
+    ep_signal_all(P.peers, P.off_flag, P.seq, P.ticket, gridDim.x * gridDim.y);
+}
+
 }  // namespace rc
 
 using namespace rc;
@@ -250,6 +274,7 @@ struct redcuda_moe {
     // digits of the token rows for redcuda_moe_shared_device alone: under expert parallelism it runs on another stream
     // than redcuda_moe_partial_device, which fills xq_x / sx_x with the gathered rows of every rank at the same time
     int8_t *xq_own = nullptr; float *sx_own = nullptr;
+    EpWait wait{};             // set for one call by rc::moe_partial_gathered: the grouping kernel first waits for the other ranks' rows
     const int8_t *xq_ext = nullptr; const float *sx_ext = nullptr;   // digits of the gate/up input supplied by the caller for one call (rc::moe_partial_gathered)
     uint32_t max_pairs = 0;
     bool use_mma = false;      // IQ2_XXS experts (and the Q6_K shared expert of a batch) on the integer tensor-core path
@@ -446,7 +471,7 @@ static int moe_group(redcuda_moe *m, const uint32_t *pair_expert, uint32_t npair
         RC_LAUNCH((k_group_trivial), 1, 64, 0, s, pair_expert, npairs, m->sorted, m->uexp, m->ustart, m->n_unique, m->item_u, m->item_p0, m->n_items, m->work);
     } else {
         RC_LAUNCH((k_group_pairs), 1, 1024, 0, s, pair_expert, npairs, m->d.expert_begin, m->d.expert_stride, skip_foreign ? 1u : 0u, m->d.expert_count, moe_item_tokens(m, false, npairs), m->sorted, m->uexp, m->ustart,
-                                         m->n_unique, m->item_u, m->item_p0, m->n_items, m->bad, m->work);
+                                         m->n_unique, m->item_u, m->item_p0, m->n_items, m->bad, m->work, m->wait);
     }
     prof_end(s);
     RC_LAUNCHED();
@@ -571,23 +596,29 @@ namespace rc {
 bool moe_takes_digits(const redcuda_moe *m) { return moe_experts_mma(m); }
 // The shard's experts over gathered tokens: x [ntok][hidden] fp32, or (when xq is given) its digits xq [ntok][3][hidden] with
 // scales sx [ntok]; ids / w [ntok][top_k] contiguous. out [ntok][hidden] as k_ep_combine defines it.
+// wait (may be null): the grouping kernel first waits for the other ranks' rows (peer-memory exchange). push (may be
+// null): the sums go to their owners' slots in peer memory instead of out (add is then left to the owner).
 int moe_partial_gathered(redcuda_moe *m, uint32_t ntok, const float *x, const int8_t *xq, const float *sx, const uint32_t *ids, const float *w,
-                         const float *add, uint32_t add_begin, uint32_t add_count, float *out, cudaStream_t s) {
-    RC_REQUIRE(m && (x || (xq && sx)) && ids && w && out, "moe partial: null argument");
+                         const float *add, uint32_t add_begin, uint32_t add_count, float *out, cudaStream_t s, const EpWait *wait, const EpPush *push) {
+    RC_REQUIRE(m && (x || (xq && sx)) && ids && w && (out || push), "moe partial: null argument");
     RC_REQUIRE(ntok >= 1 && ntok <= m->d.max_tokens, "moe partial: ntok %u outside [1, %u]", ntok, m->d.max_tokens);
     const uint32_t k = m->d.top_k, npairs = ntok * k;
     moe_choose_path(m, npairs, false);
     const bool digits = xq && moe_experts_mma(m) && !m->tc_now;
     RC_REQUIRE(digits || x, "moe partial: this layer's expert kernels need the fp32 rows");
-    if (!moe_group(m, ids, npairs, false, s, true)) return 0;
+    if (wait) m->wait = *wait;
+    const int grouped = moe_group(m, ids, npairs, false, s, true);
+    m->wait = EpWait{};
+    if (!grouped) return 0;
     if (digits) { m->xq_ext = xq; m->sx_ext = sx; }
     const int ok = moe_launch_experts(m, true, npairs, false, x, m->d.hidden, k, digits, m->act, m->d.ffn, s);
     m->xq_ext = nullptr; m->sx_ext = nullptr;
     if (!ok) return 0;
     if (!moe_launch_experts(m, false, npairs, false, m->act, m->d.ffn, 1u, false, m->tmp, m->d.hidden, s)) return 0;
     const dim3 grid((m->d.hidden / 4u + 255u) / 256u, ntok);
-    prof_begin("ep_combine", s);
-    RC_LAUNCH((k_ep_combine), grid, 256, 0, s, m->tmp, ids, w, k, m->d.expert_begin, m->d.expert_stride, m->d.expert_count, add, add_begin, add_count, out, m->d.hidden);
+    prof_begin(push ? "ep_combine_push" : "ep_combine", s);
+    if (push) RC_LAUNCH((k_ep_combine_push), grid, 256, 0, s, m->tmp, ids, w, k, m->d.expert_begin, m->d.expert_stride, m->d.expert_count, *push, m->d.hidden);
+    else RC_LAUNCH((k_ep_combine), grid, 256, 0, s, m->tmp, ids, w, k, m->d.expert_begin, m->d.expert_stride, m->d.expert_count, add, add_begin, add_count, out, m->d.hidden);
     prof_end(s);
     RC_LAUNCHED();
     return 1;

@@ -209,11 +209,13 @@ class EpStep:
     shard's experts, reduce-scatter, shared expert and add of every layer. `shards` are redcuda MoeLayer objects created
     with max_tokens >= world * tokens. The NCCL unique id travels from rank 0 over `group` (any backend)."""
 
-    def __init__(self, shards, rank: int, world: int, tokens: int, group=None):
+    def __init__(self, shards, rank: int, world: int, tokens: int, group=None, exchange: str = "peer"):
+        """exchange: "peer" = stores into the other ranks' memory over NVLink with flag words (ranks are processes on one
+        node, 2 to 8 of them), "nccl" = ncclAllGather / ncclReduceScatter."""
         import ctypes as C
         import numpy as np
         from .redcuda import RedcudaError, lib
-        self._lib, self._C = lib(), C
+        self._lib, self._C, self._group = lib(), C, group
         d = shards[0].dims
         self.dims, self.T, self.world, self.shards = d, tokens, world, shards
         dev = torch.device("cuda", torch.cuda.current_device())
@@ -231,6 +233,20 @@ class EpStep:
         self._h = self._lib.redcuda_ep_create(rank, world, self._uid, tokens, d.hidden, d.top_k)
         if not self._h:
             raise RedcudaError(self._lib.redcuda_last_error().decode(errors="replace"))
+        self.exchange = "nccl" if world > 1 else "none"
+        if world > 1 and exchange == "peer" and world <= 8:
+            hb = (C.c_uint8 * 64)()
+            if self._lib.redcuda_ep_ipc_handle(self._h, hb) != 1:
+                raise RedcudaError(self._lib.redcuda_last_error().decode(errors="replace"))
+            mine = torch.from_numpy(np.frombuffer(hb, dtype=np.uint8).copy())
+            on_dev = dist.get_backend(group) == "nccl"
+            mine = mine.to(dev) if on_dev else mine
+            everyone = torch.empty(world * 64, dtype=torch.uint8, device=mine.device)
+            dist.all_gather_into_tensor(everyone, mine, group=group)
+            if self._lib.redcuda_ep_attach_peers(self._h, everyone.cpu().numpy().tobytes()) != 1:
+                raise RedcudaError(self._lib.redcuda_last_error().decode(errors="replace"))
+            dist.barrier(group=group)          # nobody steps before every rank has mapped every area
+            self.exchange = "peer"
         n = len(shards)
         self._layers = (C.c_void_p * n)(*[m.handle for m in shards])
         self.out = torch.empty(n, tokens, d.hidden, dtype=torch.float32, device=dev)
@@ -259,5 +275,8 @@ class EpStep:
 
     def close(self):
         if self._h:
+            if self.world > 1:
+                torch.cuda.synchronize()
+                dist.barrier(group=self._group)    # other ranks may still be writing into this rank's exchange area
             self._lib.redcuda_ep_destroy(self._h)
             self._h = None

@@ -150,9 +150,16 @@ int redcuda_moe_partial_device(redcuda_moe *m, uint32_t ntok, const float *x_dev
  *   layer_forward: out[t] = routed(x[t]) over all ranks' experts + shared(x[t]) * sigmoid(g.x[t]) for the rank's own
  *                  tokens (device pointers [tokens][hidden], asynchronous on `stream`; logits_in_dev may be NULL)
  *   step:          layer_forward for n_layers layers in order; x_dev[l] / out_dev[l] per layer (a caller that chains
- *                  layers passes out_dev[l - 1] as x_dev[l]), logits_in_dev NULL or one pointer (or NULL) per layer */
+ *                  layers passes out_dev[l - 1] as x_dev[l]), logits_in_dev NULL or one pointer (or NULL) per layer
+ *   ipc_handle / attach_peers: optional, for ranks that are processes on one node (2 to 8). Every rank exports the CUDA IPC
+ *                  handle (64 bytes) of its exchange area; attach_peers takes all ranks' handles in rank order (world x 64
+ *                  bytes) and switches the exchange from NCCL to stores into peer memory with flag words (bounded waits:
+ *                  a missing rank ends the step with the "timeout" status, not a hang). Ranks must not destroy the
+ *                  context while others may still be stepping. */
 typedef struct redcuda_ep redcuda_ep;
 int redcuda_ep_unique_id(void *out128);
+int redcuda_ep_ipc_handle(redcuda_ep *ep, void *out64);
+int redcuda_ep_attach_peers(redcuda_ep *ep, const void *handles);
 redcuda_ep *redcuda_ep_create(int rank, int world, const void *unique_id128, uint32_t tokens, uint32_t hidden, uint32_t top_k);
 void redcuda_ep_destroy(redcuda_ep *ep);
 int redcuda_ep_layer_forward(redcuda_ep *ep, redcuda_moe *layer, const float *x_dev, const float *logits_in_dev, float *out_dev, void *stream);
