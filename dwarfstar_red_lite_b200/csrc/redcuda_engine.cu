@@ -333,10 +333,18 @@ static int eng_attention(rl_engine *e, const EngLayer &L, uint32_t ntok, const u
     RC_LAUNCH((k_attn_prep<KV>), dim3(nq + 2u * nkv, ntok), hd, hd * sizeof(float), s, e->qg, e->kraw, e->vraw, L.q_norm, L.k_norm, nq, nkv, hd, in.rope_dims, in.rope_freq_base,
                                                                  in.rms_eps, pos, e->query, e->gate, kc, vc);
     prof_end(s);
+    const float scale = (float)(1.0 / sqrt((double)hd));
+    {   // a chunk of tokens: the tiled tensor-core kernel (RC_ATTN_CHUNK=0 keeps the per-token kernel, for A/B runs)
+        static const bool want = !(getenv("RC_ATTN_CHUNK") && atoi(getenv("RC_ATTN_CHUNK")) == 0);
+        if (want && ntok >= 8u && attn_chunk_ok<KV>(hd, G)) {
+            ENG_RC(launch_attn_chunk<KV>(e->query, kc, vc, nkv, G, hd, pos, ntok, scale, e->gate, e->gated, s));
+            g_launches.fetch_add(1);
+            return 1;
+        }
+    }
     uint32_t nsplit = (in.context + 31u) / 32u;                 // fixed per engine (graph replay): enough slices for a full context
     nsplit = nsplit < 1u ? 1u : nsplit > e->max_split ? e->max_split : nsplit;
     if (ntok > 1u && nsplit > e->pf_split) nsplit = e->pf_split;     // a chunk brings its own parallelism (and the partials are per token)
-    const float scale = (float)(1.0 / sqrt((double)hd));
     const size_t smem = (size_t)(8u * G * hd + 16u * G) * sizeof(float);
     const dim3 grid(nkv, nsplit, ntok);
     prof_begin("attn_decode", s);

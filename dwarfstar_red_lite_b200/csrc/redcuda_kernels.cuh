@@ -114,6 +114,12 @@ __device__ __forceinline__ void ep_wait_all(const EpWait &W) {
 }
 #endif
 
+// Causal attention of a prefill chunk on the tensor cores (redcuda_attn_chunk.cu); KV = __half or float
+template <typename KV> bool attn_chunk_ok(uint32_t hd, uint32_t G);
+template <typename KV>
+int launch_attn_chunk(const float *query, const KV *kc, const KV *vc, uint32_t n_kv, uint32_t G, uint32_t hd, const uint32_t *pos, uint32_t ntok, float scale,
+                      const float *gate, float *gated, cudaStream_t s);
+
 int launch_vec_sigmoid(const float *w, const float *x, uint32_t x_stride, uint32_t ncols, uint32_t ntok, float *out, cudaStream_t stream);
 // logits[t][e] = dot(w[e], x[t]) accumulated in double, F32 weights [n_expert][ncols]; for batches (tiled fp64 GEMM)
 int launch_router_logits(const float *w, const float *x, uint32_t x_stride, uint32_t ntok, uint32_t n_expert, uint32_t ncols, float *logits, cudaStream_t stream);
