@@ -15,12 +15,10 @@
 // Accumulation follows k_tc_gemm: the tensor core adds into fp32 without rounding to nearest, so the accumulators cover
 // one 256-column block only (one for A*hi, one for A*lo), double-buffered in tensor memory and summed in fp32 registers.
 //
-// One CTA = one item x one 128-row tile of one matrix, K in stages of 64 columns:
-//   thread 0      requests the 8 records (16 rows x 256 columns each) of the next block with cp.async.bulk on an mbarrier
-//   all 16 warps  gather the next stage's activation pieces, decode 128 x 64 weights of this stage from the records
-//   thread 0      issues 4 k-steps x 2 tcgen05.mma (128 x 64 x 16, kind::f16) and commits on the stage's mbarrier
-// Blocks beyond the item count leave at once. Every wait is bounded: on a timeout the CTA stops issuing, waits (bounded)
-// for its own copies, frees its tensor memory, raises the launch's flag and the sticky status word, and returns.
+// One CTA = one item x one 128-row tile of one matrix, K in stages of 64 columns, the warps split into roles that hand
+// tiles to each other through mbarriers (see k_tc_experts). Blocks beyond the item count leave at once. Every wait is
+// bounded: on a timeout the role raises a flag that stops the other roles at their next wait; the CTA waits (bounded) for
+// its own copies, frees its tensor memory, raises the launch's flag and the sticky status word, and returns.
 #define RC_PDL_DEFAULT 0
 #include "redcuda_common.cuh"
 #include "redcuda_dot.cuh"
@@ -94,36 +92,67 @@ __global__ void __launch_bounds__(256) k_tc_prep_rows(const float *__restrict__ 
     }
 }
 
-// LA = how many stages ahead the activation pieces are requested (LA + 2 stage buffers)
-template <int TN, int LA>
+// shared-memory matrix descriptor, K-major rows of 128 bytes (64 halves) with the 128-byte swizzle: the 16-byte chunk c of
+// row r sits at r * 128 + ((c ^ (r % 8)) * 16) of a 1024-byte aligned tile; 8-row groups are 1024 bytes apart. A k-step
+// of 16 halves is addressed by advancing the start address by 32 bytes.
+__device__ __forceinline__ uint64_t tcx_desc_sw128(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ uint32_t tcx_sw128(uint32_t r, uint32_t c) { return r * 128u + ((c ^ (r & 7u)) << 4); }
+// 128-row tiles one CTA works through: as many as keep it at 8 blocks of 256 columns (and divide the matrix)
+__host__ __device__ uint32_t tcx_tiles_per_cta(uint32_t nrows, uint32_t ncols) {
+    uint32_t tpc = 2048u / ncols;
+    const uint32_t rtiles = nrows / 128u;
+    tpc = tpc < 1u ? 1u : tpc;
+    while (tpc > 1u && rtiles % tpc) tpc >>= 1;
+    return tpc;
+}
+
+__device__ __forceinline__ void tcx_arrive(uint32_t mbar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(mbar) : "memory"); }
+
+// Roles of the 16 warps (no block-wide barrier inside the K loop; the roles meet on mbarriers):
+//   warp 0          lane 0 issues the MMAs of a stage once its weight tile and its activation tile are full, and commits
+//                   their completion to the "empty" barriers of both tiles (and, at the end of a 256-column block, to the
+//                   block's "accumulators full" barrier)
+//   warps 1-2       gather the activation pieces of stage after stage (cp.async, up to NB stages ahead of the MMAs)
+//   warp 3          lane 0 requests the records of block after block (cp.async.bulk, one block ahead of the decoders)
+//   warps 4-11      decode the weights of a stage into the fp16 tile (two (row, 8-column-pair) items per thread)
+//   warps 12-15     read a finished block's accumulators out of tensor memory (warp w owns lanes 32 (w % 4) ..) and add
+//                   them, scaled by d / 8, to their fp32 register sums; at the end they store the results
+constexpr uint32_t TCX_NB = 4u;               // activation stage buffers
+constexpr uint32_t TCX_W_GATHER = 1u, TCX_N_GATHER = 2u, TCX_W_RAW = 3u, TCX_W_DECODE = 4u, TCX_N_DECODE = 8u, TCX_W_DRAIN = 12u;
+
+template <int TN>
 __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_experts(const __grid_constant__ TcxArgs A) {
     pdl_prologue();
     const uint32_t item = blockIdx.y;
     if (item >= *A.n_items) return;                       // the grid covers the largest possible item count
-    extern __shared__ __align__(128) uint8_t smem[];
-    constexpr uint32_t NB = (uint32_t)LA + 2u;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    constexpr uint32_t NB = TCX_NB;
     constexpr uint32_t B_DIGIT = (uint32_t)TN * TC_KS * 2u, A_BUF = TC_A_DIGIT, B_BUF = 2u * B_DIGIT;
     constexpr uint32_t TMEM_COLS = 4u * (uint32_t)TN;     // two blocks in flight x (A*hi accumulator, A*lo accumulator)
-    static_assert(TMEM_COLS >= 32u && TMEM_COLS <= 512u && (TMEM_COLS & (TMEM_COLS - 1u)) == 0u, "tensor-memory allocation must be a power of two in [32, 512]");
-    __shared__ __align__(8) uint64_t mbar[2];        // MMAs that read A buffer b (and the activation buffer of the same stage) are done
-    __shared__ __align__(8) uint64_t accfull[2];     // every MMA of a 256-column block has landed in accumulator pair b
-    __shared__ __align__(8) uint64_t rawfull[2];     // the records of a 256-column block have landed in raw buffer b
+    static_assert(TN == 64, "the role split below is laid out for 64-token items");
+    __shared__ __align__(8) uint64_t a_full[2], a_empty[2], b_full[NB], b_empty[NB], acc_full[2], acc_empty[2], raw_full[2], raw_empty[2];
     __shared__ uint32_t tmem_slot;
-    __shared__ volatile uint32_t fail;               // a bounded wait ran out: no more MMAs are issued, later waits are skipped
+    __shared__ volatile uint32_t fail;               // a bounded wait ran out: every role stops at its next wait
     __shared__ uint32_t s_row[TN], s_pair[TN];       // activation row and pair of every token slot of the item (TCX_DEAD beyond its pairs)
-    __shared__ float s_xinv[TN], s_d[2][TC_M];       // inverse activation scales; d/8 of every row for the two blocks in flight
+    __shared__ float s_xinv[TN];
+    __shared__ float s_d[8][TC_M];                   // d / 8 of every row for every 256-column block (at most 8 blocks)
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
 
     const uint32_t u = A.item_u[item], p0 = A.item_p0[item], pe = A.ustart[u + 1u];
     const uint32_t nt = pe - p0 < (uint32_t)TN ? pe - p0 : (uint32_t)TN;
-    uint32_t e = A.uexp[u] - A.expert_begin;
+    const uint32_t e = A.uexp[u] - A.expert_begin;
     if (e >= A.n_local) {                                 // cannot happen with k_group_pairs' output; never an address
         if (tid == 0 && A.status) A.status[ST_EXPERT_RANGE] = 1u;
         return;
     }
-    const uint32_t rtiles = A.nrows / TC_M, mat = blockIdx.x / rtiles, rt = blockIdx.x - mat * rtiles;
-    const uint32_t bpr = A.ncols >> 8, nstage = A.ncols / TC_KS;
-    const uint8_t *wrec = A.w[mat] + (uint64_t)e * A.mat_bytes + (uint64_t)(rt * 8u) * bpr * NIB_REC;     // record (tile 8 rt + j, block c) at (j * bpr + c) * NIB_REC
+    // A CTA takes tpc consecutive 128-row tiles of one matrix, one after the other, so that 8 blocks of 256 columns pass
+    // through it whatever the row length: the set-up and the pipeline fill are paid once per CTA, not once per short row.
+    const uint32_t bpr = A.ncols >> 8, kstage = A.ncols / TC_KS, tpc = tcx_tiles_per_cta(A.nrows, A.ncols);
+    const uint32_t groups = A.nrows / TC_M / tpc, mat = blockIdx.x / groups, rt0 = (blockIdx.x - mat * groups) * tpc;
+    const uint32_t nstage = tpc * kstage, nblk = tpc * bpr;           // stages and 256-column blocks of the whole CTA
+    const uint8_t *wrec = A.w[mat] + (uint64_t)e * A.mat_bytes + (uint64_t)(rt0 * 8u) * bpr * NIB_REC;    // record (16-row tile 8 rt0 + j, block c) at (j * bpr + c) * NIB_REC
     uint8_t *a_base = smem, *b_base = smem + 2u * A_BUF, *raw_base = b_base + NB * B_BUF;
 
     if (tid < (uint32_t)TN) {
@@ -131,26 +160,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_experts(const __grid_const
         if (tid < nt) { pair = A.sorted[p0 + tid]; row = pair / A.x_div; inv = A.x_inv[row]; }
         s_row[tid] = row; s_pair[tid] = pair; s_xinv[tid] = inv;
     }
-    // the 8 records of block column c -> raw buffer c & 1 (thread 0)
-    auto issue_raw = [&](uint32_t c) {
-        const uint32_t bar = smem_u32(&rawfull[c & 1u]), dst = smem_u32(raw_base + (c & 1u) * TCX_RAW);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(TCX_RAW) : "memory");
-#pragma unroll
-        for (uint32_t j = 0; j < 8u; ++j)
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                         :: "r"(dst + j * NIB_REC), "l"(wrec + ((uint64_t)j * bpr + c) * NIB_REC), "r"(NIB_REC), "r"(bar) : "memory");
-    };
+    for (uint32_t i = tid; i < TC_M * nblk; i += TC_THREADS) {     // block scales of the CTA's rows: s_d[tile * bpr + block][row of the tile]
+        const uint32_t cb = i / TC_M, r = i - cb * TC_M, tile = cb / bpr, c = cb - tile * bpr;
+        s_d[cb][r] = 0.125f * __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short *>(wrec + ((uint64_t)(tile * 8u + (r >> 4)) * bpr + c) * NIB_REC + NIB_D_OFF + (r & 15u) * 2u))));
+    }
     if (tid == 0) {
         fail = 0u;
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&mbar[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&mbar[1])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&accfull[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&accfull[1])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&rawfull[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&rawfull[1])));
+        auto init = [](uint64_t *bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count)); };
+        for (uint32_t i = 0; i < 2u; ++i) {
+            init(&a_full[i], TCX_N_DECODE); init(&a_empty[i], 1u); init(&acc_full[i], 1u); init(&acc_empty[i], 4u);
+            init(&raw_full[i], 1u); init(&raw_empty[i], TCX_N_DECODE);
+        }
+        for (uint32_t i = 0; i < NB; ++i) { init(&b_full[i], TCX_N_GATHER); init(&b_empty[i], 1u); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        issue_raw(0u);
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
@@ -160,127 +183,179 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_experts(const __grid_const
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_slot;
-    const uint32_t idesc = tc_idesc((uint32_t)TN);
-
-    // the activation digits of a stage: 16-byte pieces of the item's rows into the core-matrix layout
-    // [digit][k chunk of 8][token group of 8][token in group][8 halves]; slots beyond the item's pairs are zero-filled
-    auto issue_b = [&](uint32_t stage) {
-        const uint32_t bb = smem_u32(b_base + (stage % NB) * B_BUF);
-#pragma unroll
-        for (uint32_t i = tid; i < 16u * (uint32_t)TN; i += TC_THREADS) {
-            const uint32_t kc = i & 7u, tt = (i >> 3) & ((uint32_t)TN - 1u), dg = i / (8u * (uint32_t)TN);
-            const uint32_t row = s_row[tt], live = row != TCX_DEAD ? 16u : 0u;
-            const __half *src = A.xd + ((size_t)(live ? row : 0u) * 2u + dg) * A.ncols + stage * TC_KS + kc * 8u;
-            const uint32_t dst = bb + dg * B_DIGIT + (kc * ((uint32_t)TN >> 3) + (tt >> 3)) * 128u + (tt & 7u) * 16u;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst), "l"(src), "r"(live) : "memory");
-        }
-    };
-#pragma unroll
-    for (uint32_t st = 0; st < (uint32_t)LA; ++st) {
-        if (st < nstage) issue_b(st);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    }
-
-    // fp32 sums over the 256-column blocks: warp w owns TMEM lanes 32*(w%4)..+31 (its quarter) and PER token columns
-    constexpr uint32_t PER = (uint32_t)TN / (TC_WARPS / 4u);
-    const uint32_t qlane = (warp & 3u) * 32u, c_begin = (warp >> 2) * PER;
-    float acc[PER];
-#pragma unroll
-    for (uint32_t j = 0; j < PER; ++j) acc[j] = 0.f;
-    auto drain = [&](uint32_t blk) {
-        if (fail) return;
-        if (!mbar_wait(smem_u32(&accfull[blk & 1u]), (blk >> 1) & 1u)) { fail = 1u; return; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const float dsc = s_d[blk & 1u][qlane + lane];
-        const uint32_t base = tmem + (qlane << 16) + (blk & 1u) * 2u * (uint32_t)TN + c_begin;
-#pragma unroll
-        for (uint32_t c = 0; c < PER; c += 8u) {
-            uint32_t m[8], x[8];
-            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                         : "=r"(m[0]), "=r"(m[1]), "=r"(m[2]), "=r"(m[3]), "=r"(m[4]), "=r"(m[5]), "=r"(m[6]), "=r"(m[7]) : "r"(base + c));
-            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                         : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]), "=r"(x[4]), "=r"(x[5]), "=r"(x[6]), "=r"(x[7]) : "r"(base + (uint32_t)TN + c));
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[c + j] = fmaf(dsc, __uint_as_float(m[j]) + __uint_as_float(x[j]), acc[c + j]);
-        }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");     // the pair is overwritten two blocks later, after barriers
+    // a wait that gives up raises the flag; every role checks it before each wait, so the CTA winds down within a few waits
+    auto wait = [&](uint64_t *bar, uint32_t parity) -> bool {
+        if (fail) return false;
+        if (mbar_wait(smem_u32(bar), parity)) return true;
+        fail = 1u;
+        return false;
     };
 
-    uint32_t raw_issued = 1u, raw_waited = 0u;           // thread 0's count of block requests; every thread's count of completed waits
-    for (uint32_t s = 0; s < nstage; ++s) {
-        const uint32_t b = s & 1u, c = s >> 2;
-        uint8_t *abuf = a_base + b * A_BUF;
-        const uint8_t *raw = raw_base + (c & 1u) * TCX_RAW;
-        if ((s & 3u) == 0u) {
-            // new block column. Its records were requested a block ago; the other raw buffer was last read in the stage
-            // before this one, which ended with a barrier, so the next block can be requested into it now
-            if (!fail) { if (!mbar_wait(smem_u32(&rawfull[c & 1u]), (c >> 1) & 1u)) fail = 1u; else raw_waited = c + 1u; }
-            if (tid == 0 && c + 1u < bpr && !fail) { issue_raw(c + 1u); raw_issued = c + 2u; }
-            if (tid < TC_M) s_d[c & 1u][tid] = 0.125f * __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(raw + (tid >> 4) * NIB_REC + NIB_D_OFF + (tid & 15u) * 2u)));
-        }
-        // the MMAs of stage s - 2 read this A buffer and the activation buffer that stage s + LA will use
-        if (s >= 2u && !fail) {
-            if (!mbar_wait(smem_u32(&mbar[b]), ((s >> 1) - 1u) & 1u)) fail = 1u;
-        }
-        if (s + (uint32_t)LA < nstage) issue_b(s + (uint32_t)LA);
-        asm volatile("cp.async.commit_group;" ::: "memory");                 // one group per stage, empty at the end
-        if ((s & 3u) == 1u && s >= 4u) drain((s >> 2) - 1u);                  // the previous block's MMAs were issued more than a stage ago
-        // ---- weights of the stage: thread -> row 8 * warp + lane / 4, code words (t, kg0) and (t, kg0 + 1), t = lane % 4
-        if (!fail) {
-            const uint32_t r = warp * 8u + (lane >> 2), t = lane & 3u, kg0 = 2u * (s & 3u);
-            const uint8_t *rec = raw + (r >> 4) * NIB_REC;
-            const uint32_t rr = r & 15u;
-            const uint2 wd = *reinterpret_cast<const uint2 *>(rec + nib_code_off(rr, t, kg0));
-            const uint32_t sc2 = *reinterpret_cast<const unsigned short *>(rec + NIB_SC_OFF + rr * 8u + kg0);
-            // k chunk of 8 inside the stage: columns 32 (kg - kg0) + 8 t  ->  chunk 4 (kg - kg0) + t
-            *reinterpret_cast<uint4 *>(abuf + t * (TC_M * 16u) + r * 16u) = tcx_decode8(wd.x, sc2 & 255u);
-            *reinterpret_cast<uint4 *>(abuf + (t + 4u) * (TC_M * 16u) + r * 16u) = tcx_decode8(wd.y, sc2 >> 8);
-        }
-        asm volatile("cp.async.wait_group %0;" :: "n"(LA) : "memory");       // this stage's activation pieces (those of the next LA stages may be in flight)
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");         // generic-proxy writes -> visible to the tensor core
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        if (tid == 0 && !fail) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_d = smem_u32(abuf), b_hi = smem_u32(b_base + (s % NB) * B_BUF), b_lo = b_hi + B_DIGIT;
-            constexpr uint32_t A_LBO = TC_M * 16u, B_LBO = (uint32_t)TN * 16u, SBO = 128u;
-            const uint32_t d_main = tmem + (c & 1u) * 2u * (uint32_t)TN, d_cross = d_main + (uint32_t)TN;
+    if (warp == 0) {
+        // ------------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            // One MMA per k-step: the hi and lo digit rows of a stage are one 128-row operand (hi rows, then lo rows), so the
+            // product lands as [A*hi | A*lo] in 2 TN accumulator columns. Descriptors differ from stage to stage only in
+            // their start address, so the loop adds a constant to a precomputed low word. This thread's latency per stage
+            // is what bounds the pipeline, so its waits are kept to the bare polls.
+            const uint32_t idesc = tc_idesc(2u * (uint32_t)TN);
+            const uint64_t desc0 = tcx_desc_sw128(0u);
+            auto ready = [&](uint64_t *bar, uint32_t parity) -> bool {
+                const uint32_t addr = smem_u32(bar);
+                uint32_t done;
+                asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                             : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+                return done ? true : wait(bar, parity);
+            };
+            for (uint32_t s = 0; s < nstage; ++s) {
+                const uint32_t b = s & 1u, jb = s % NB, c = s >> 2;
+                if (!ready(&a_full[b], (s >> 1) & 1u) || !ready(&b_full[jb], (s / NB) & 1u)) break;
+                if ((s & 3u) == 0u && c >= 2u && !ready(&acc_empty[c & 1u], ((c >> 1) - 1u) & 1u)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t da = desc0 + ((smem_u32(a_base + b * A_BUF) >> 4) & 0x3fffu), db = desc0 + ((smem_u32(b_base + jb * B_BUF) >> 4) & 0x3fffu);
+                const uint32_t d_acc = tmem + (c & 1u) * 2u * (uint32_t)TN;
 #pragma unroll
-            for (uint32_t kk = 0; kk < TC_KS / 16u; ++kk) {
-                const uint64_t da = tc_smem_desc(a_d + 2u * kk * A_LBO, A_LBO, SBO);
-                const uint64_t dbh = tc_smem_desc(b_hi + 2u * kk * B_LBO, B_LBO, SBO), dbl = tc_smem_desc(b_lo + 2u * kk * B_LBO, B_LBO, SBO);
-                const uint32_t first = ((s & 3u) | kk) ? 1u : 0u;       // a block's first MMA overwrites its accumulators
-                tc_mma(d_main, da, dbh, idesc, first);
-                tc_mma(d_cross, da, dbl, idesc, first);
+                for (uint32_t kk = 0; kk < TC_KS / 16u; ++kk)
+                    tc_mma(d_acc, da + 2u * kk, db + 2u * kk, idesc, ((s & 3u) | kk) ? 1u : 0u);       // + 32 bytes per k-step; a block's first MMA overwrites
+                tc_commit(smem_u32(&a_empty[b]));
+                tc_commit(smem_u32(&b_empty[jb]));
+                if ((s & 3u) == 3u) tc_commit(smem_u32(&acc_full[c & 1u]));
             }
-            tc_commit(smem_u32(&mbar[b]));
-            if ((s & 3u) == 3u) tc_commit(smem_u32(&accfull[c & 1u]));
         }
-    }
-    __syncthreads();
-    drain((nstage >> 2) - 1u);
-    asm volatile("cp.async.wait_all;" ::: "memory");
-    __syncthreads();
-    if (!fail) {
-        const uint32_t row = rt * TC_M + qlane + lane;
-        float *out = A.out[mat];
+    } else if (warp < TCX_W_RAW) {
+        // ------------------------------------------------------------------ activation gather (64 threads)
+        // thread g: k chunk g % 8 of the token slots g / 8 + 8 m (m < 8), both digits: 16 pieces of 16 bytes per stage
+        const uint32_t g = tid - TCX_W_GATHER * 32u, kc = g & 7u, ttb = g >> 3;
+        const __half *src[8]; uint32_t live = 0u;
 #pragma unroll
-        for (uint32_t j = 0; j < PER; ++j) {
-            const uint32_t pair = s_pair[c_begin + j];
-            if (pair != TCX_DEAD) out[(size_t)pair * A.out_stride + row] = acc[j] * s_xinv[c_begin + j];
+        for (uint32_t m = 0; m < 8u; ++m) {
+            const uint32_t row = s_row[ttb + 8u * m];
+            if (row != TCX_DEAD) live |= 1u << m;
+            src[m] = A.xd + (size_t)(row != TCX_DEAD ? row : 0u) * 2u * A.ncols + kc * 8u;
+        }
+        const uint32_t dst0 = tcx_sw128(ttb, kc);         // token slot ttb + 8 m: the same swizzle phase, 1024 bytes further per m
+        auto issue = [&](uint32_t s) {
+            const uint32_t bb = smem_u32(b_base + (s % NB) * B_BUF) + dst0;
+#pragma unroll
+            for (uint32_t m = 0; m < 8u; ++m) {
+                const uint32_t sz = (live >> m) & 1u ? 16u : 0u;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(bb + m * 1024u), "l"(src[m] + (s % kstage) * TC_KS), "r"(sz) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(bb + B_DIGIT + m * 1024u), "l"(src[m] + A.ncols + (s % kstage) * TC_KS), "r"(sz) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        // stage s is requested AHEAD stages before it is handed over, so that many groups are always in flight
+        constexpr uint32_t AHEAD = 2u;
+        bool ok = true;
+        for (uint32_t s = 0; s < nstage + AHEAD && ok; ++s) {
+            if (s < nstage) {
+                if (s >= NB) ok = wait(&b_empty[s % NB], ((s / NB) - 1u) & 1u);
+                if (ok) issue(s); else asm volatile("cp.async.commit_group;" ::: "memory");
+            } else asm volatile("cp.async.commit_group;" ::: "memory");
+            if (s >= AHEAD) {
+                asm volatile("cp.async.wait_group %0;" :: "n"(AHEAD) : "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) tcx_arrive(smem_u32(&b_full[(s - AHEAD) % NB]));
+                
+            }
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+    } else if (warp == TCX_W_RAW) {
+        // ------------------------------------------------------------------ weight records, one block ahead
+        if (lane == 0) {
+            uint32_t issued = 0u;
+            for (uint32_t c = 0; c < nblk; ++c) {       // c counts the CTA's blocks: tile c / bpr, block column c % bpr
+                if (c >= 2u && !wait(&raw_empty[c & 1u], ((c >> 1) - 1u) & 1u)) break;
+                const uint32_t tile = c / bpr, col = c - tile * bpr;
+                const uint32_t bar = smem_u32(&raw_full[c & 1u]), dst = smem_u32(raw_base + (c & 1u) * TCX_RAW);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(TCX_RAW) : "memory");
+#pragma unroll
+                for (uint32_t j = 0; j < 8u; ++j)
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 :: "r"(dst + j * NIB_REC), "l"(wrec + ((uint64_t)(tile * 8u + j) * bpr + col) * NIB_REC), "r"(NIB_REC), "r"(bar) : "memory");
+                issued = c + 1u;
+            }
+            // a copy that nobody waited for may still be writing into this CTA's shared memory: wait for the last two (bounded)
+            for (uint32_t c = issued >= 2u ? issued - 2u : 0u; c < issued; ++c) mbar_wait(smem_u32(&raw_full[c & 1u]), (c >> 1) & 1u);
+        }
+    } else if (warp < TCX_W_DRAIN) {
+        // ------------------------------------------------------------------ weight decode (256 threads)
+        const uint32_t dw = warp - TCX_W_DECODE, t = lane & 3u;
+        for (uint32_t s = 0; s < nstage; ++s) {
+            const uint32_t b = s & 1u, c = s >> 2;
+            if ((s & 3u) == 0u && !wait(&raw_full[c & 1u], (c >> 1) & 1u)) break;
+            if (s >= 2u && !wait(&a_empty[b], ((s >> 1) - 1u) & 1u)) break;
+            const uint8_t *raw = raw_base + (c & 1u) * TCX_RAW;
+            uint8_t *abuf = a_base + b * A_BUF;
+            const uint32_t kg0 = 2u * (s & 3u);
+            
+#pragma unroll
+            for (uint32_t q = 0; q < 2u; ++q) {
+                // rows 8 dw + lane / 4 and + 64; code words (t, kg0) and (t, kg0 + 1) of the row: columns 32 (kg - kg0) + 8 t of the stage
+                const uint32_t r = q * 64u + dw * 8u + (lane >> 2), rr = r & 15u;
+                const uint8_t *rec = raw + (r >> 4) * NIB_REC;
+                const uint2 wd = *reinterpret_cast<const uint2 *>(rec + nib_code_off(rr, t, kg0));
+                const uint32_t sc2 = *reinterpret_cast<const unsigned short *>(rec + NIB_SC_OFF + rr * 8u + kg0);
+                *reinterpret_cast<uint4 *>(abuf + tcx_sw128(r, t)) = tcx_decode8(wd.x, sc2 & 255u);
+                *reinterpret_cast<uint4 *>(abuf + tcx_sw128(r, t + 4u)) = tcx_decode8(wd.y, sc2 >> 8);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the tensor core
+            __syncwarp();
+            if (lane == 0) {
+                tcx_arrive(smem_u32(&a_full[b]));
+                if ((s & 3u) == 3u) tcx_arrive(smem_u32(&raw_empty[c & 1u]));     // this warp has read the block's records for the last time
+                
+            }
         }
     } else {
-        if (tid == 0) {
-            // a block request that was never waited for may still be writing into this CTA's shared memory
-            for (uint32_t c = raw_waited; c < raw_issued; ++c) mbar_wait(smem_u32(&rawfull[c & 1u]), (c >> 1) & 1u);
-            atomicExch(A.err, 1u);
-            if (A.status) A.status[ST_TIMEOUT] = 1u;
+        // ------------------------------------------------------------------ accumulator drain and epilogue (128 threads)
+        const uint32_t qlane = (warp & 3u) * 32u;
+        float acc[TN];
+#pragma unroll
+        for (uint32_t j = 0; j < (uint32_t)TN; ++j) acc[j] = 0.f;
+        bool ok = true;
+        for (uint32_t blk = 0; blk < nblk && ok; ++blk) {
+            ok = wait(&acc_full[blk & 1u], (blk >> 1) & 1u);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            
+            const float dsc = s_d[blk][qlane + lane];
+            const uint32_t base = tmem + (qlane << 16) + (blk & 1u) * 2u * (uint32_t)TN;
+#pragma unroll
+            for (uint32_t cc = 0; cc < (uint32_t)TN; cc += 16u) {
+                uint32_t m[16], x[16];
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                             : "=r"(m[0]), "=r"(m[1]), "=r"(m[2]), "=r"(m[3]), "=r"(m[4]), "=r"(m[5]), "=r"(m[6]), "=r"(m[7]),
+                               "=r"(m[8]), "=r"(m[9]), "=r"(m[10]), "=r"(m[11]), "=r"(m[12]), "=r"(m[13]), "=r"(m[14]), "=r"(m[15]) : "r"(base + cc));
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                             : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]), "=r"(x[4]), "=r"(x[5]), "=r"(x[6]), "=r"(x[7]),
+                               "=r"(x[8]), "=r"(x[9]), "=r"(x[10]), "=r"(x[11]), "=r"(x[12]), "=r"(x[13]), "=r"(x[14]), "=r"(x[15]) : "r"(base + (uint32_t)TN + cc));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[cc + j] = fmaf(dsc, __uint_as_float(m[j]) + __uint_as_float(x[j]), acc[cc + j]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tcx_arrive(smem_u32(&acc_empty[blk & 1u]));
+            if ((blk + 1u) % bpr == 0u) {            // the last block of a row tile: store it and start the next tile from zero
+                const uint32_t row = (rt0 + blk / bpr) * TC_M + qlane + lane;
+                float *out = A.out[mat];
+#pragma unroll
+                for (uint32_t j = 0; j < (uint32_t)TN; ++j) {
+                    const uint32_t pair = s_pair[j];
+                    if (pair != TCX_DEAD) out[(size_t)pair * A.out_stride + row] = acc[j] * s_xinv[j];
+                    acc[j] = 0.f;
+                }
+            }
         }
-        __syncthreads();
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (fail && tid == 0) {
+        atomicExch(A.err, 1u);
+        if (A.status) A.status[ST_TIMEOUT] = 1u;
+    }
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(TMEM_COLS) : "memory");
 }
 
@@ -300,17 +375,11 @@ int launch_tc_experts(TcxArgs &A, uint32_t max_items, const char *tag, cudaStrea
     RC_REQUIRE((A.nmat == 1u || A.nmat == 2u) && A.w[0] && (A.nmat == 1u || A.w[1]) && max_items && A.x_div, "tc experts: bad matrix count or empty launch");
     RC_REQUIRE(max_items <= 65535u, "tc experts: %u work items exceed the grid", max_items);
     constexpr uint32_t TN = TCX_TN;
-    static const int la = getenv("RC_TCX_LA") ? atoi(getenv("RC_TCX_LA")) : 2;      // A/B switch: 1 or 2 stages of lookahead
-    const size_t smem = 2u * (size_t)TC_A_DIGIT + (size_t)(la == 1 ? 3u : 4u) * 2u * TN * TC_KS * 2u + 2u * (size_t)TCX_RAW;
-    const dim3 grid(A.nmat * (A.nrows / TC_M), max_items);
+    const size_t smem = 2u * (size_t)TC_A_DIGIT + (size_t)TCX_NB * 2u * TN * TC_KS * 2u + 2u * (size_t)TCX_RAW;
+    const dim3 grid(A.nmat * (A.nrows / TC_M / tcx_tiles_per_cta(A.nrows, A.ncols)), max_items);
     prof_begin(tag, s);
-    if (la == 1) {
-        RC_CUDA(cudaFuncSetAttribute(k_tc_experts<(int)TN, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        RC_LAUNCH((k_tc_experts<(int)TN, 1>), grid, TC_THREADS, smem, s, A);
-    } else {
-        RC_CUDA(cudaFuncSetAttribute(k_tc_experts<(int)TN, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        RC_LAUNCH((k_tc_experts<(int)TN, 2>), grid, TC_THREADS, smem, s, A);
-    }
+    RC_CUDA(cudaFuncSetAttribute(k_tc_experts<(int)TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    RC_LAUNCH((k_tc_experts<(int)TN>), grid, TC_THREADS, smem, s, A);
     prof_end(s);
     RC_LAUNCHED();
     return 1;
