@@ -374,13 +374,36 @@ def run_decode48(args):
         eng.reset()
         # teacher-forced replay: both sides are fed the oracle's tokens, so one near-tie cannot hide what follows
         tok, want, agree, ties, worst_layer, worst_logit, id_mismatch, t0 = args.first_token, [], 0, [], 0.0, 0.0, 0, time.perf_counter()
+        # Every router mismatch with the margin by which the ORACLE's own logits prefer its choice (the smallest gap between an
+        # expert only the oracle selected and one only the GPU selected; for a pure order swap the gap of the swapped pair) and
+        # the layer-output error just upstream. Both sides keep their own K/V and DeltaNet states, so everything after the
+        # first mismatch also carries the flipped expert's contribution: `clean_noise` is the error measured before it.
+        margins, first_mismatch, clean_noise = [], None, 0.0
         for i in range(args.check_steps):
             gl = eng.step(tok)
             ml = om.step(tok, threads=os.cpu_count() or 1)
+            upstream = 0.0
             for l in range(info.n_layer):
                 a_, b_ = eng.layer_out(l), om.layer_out(l)
-                worst_layer = max(worst_layer, float(np.max(np.abs(a_ - b_)) / np.max(np.abs(b_))))
-                id_mismatch += int(not np.array_equal(eng.router_ids(l), om.router_ids(l)))
+                gi, ci = eng.router_ids(l), om.router_ids(l)
+                if not np.array_equal(gi, ci):
+                    id_mismatch += 1
+                    lg = om.router_logits(l)
+                    only_c, only_g = [e_ for e_ in ci if e_ not in gi], [e_ for e_ in gi if e_ not in ci]
+                    if only_c:
+                        margin = float(min(lg[e_] for e_ in only_c) - max(lg[e_] for e_ in only_g))
+                    else:
+                        swapped = [k_ for k_ in range(len(ci)) if gi[k_] != ci[k_]]
+                        margin = float(max(abs(lg[ci[k_]] - lg[gi[k_]]) for k_ in swapped))
+                    rec = {"step": i, "layer": l, "margin": margin, "same_experts": not only_c, "upstream_rel_err": upstream}
+                    margins.append(rec)
+                    if first_mismatch is None:
+                        first_mismatch = rec
+                err_l = float(np.max(np.abs(a_ - b_)) / np.max(np.abs(b_)))
+                if first_mismatch is None:
+                    clean_noise = max(clean_noise, err_l)
+                upstream = err_l
+                worst_layer = max(worst_layer, err_l)
             worst_logit = max(worst_logit, float(np.max(np.abs(gl - ml))))
             top2 = np.partition(ml, -2)[-2:]
             if int(np.argmax(gl)) == int(np.argmax(ml)):
@@ -395,6 +418,11 @@ def run_decode48(args):
         check = {"greedy_steps": args.check_steps, "free_running_tokens_equal": same, "first_difference": first_diff,
                  "teacher_forced_argmax_equal": agree, "argmax_differences": ties, "max_layer_rel_err": worst_layer, "max_logit_abs_err": worst_logit,
                  "router_id_layer_mismatches": id_mismatch, "router_selections_checked": args.check_steps * int(info.n_layer),
+                 "first_router_mismatch": first_mismatch, "max_layer_rel_err_before_first_mismatch": clean_noise,
+                 "mismatch_margins": {"count": len(margins), "max": max((m_["margin"] for m_ in margins), default=None),
+                                      "median": float(np.median([m_["margin"] for m_ in margins])) if margins else None,
+                                      "same_experts_other_order": int(sum(m_["same_experts"] for m_ in margins)),
+                                      "first_20": margins[:20]},
                  "s_per_token_both_sides": cpu_s}
         eng.reset()
         del om
@@ -482,8 +510,22 @@ def run_prefill(args):
             ml = om.step(int(t), threads=os.cpu_count() or 1)
         worst = max(float(np.max(np.abs(eng.layer_out(l) - om.layer_out(l))) / np.max(np.abs(om.layer_out(l)))) for l in range(info.n_layer))
         ids = sum(int(not np.array_equal(eng.router_ids(l), om.router_ids(l))) for l in range(info.n_layer))
+        # the first layer whose selection differs, with the margin by which the oracle's own logits prefer its choice and the
+        # error of the layers before it (what follows a flipped expert is no longer rounding noise)
+        first, clean = None, 0.0
+        for l in range(info.n_layer):
+            gi, ci = eng.router_ids(l), om.router_ids(l)
+            if not np.array_equal(gi, ci):
+                lg = om.router_logits(l)
+                only_c, only_g = [e_ for e_ in ci if e_ not in gi], [e_ for e_ in gi if e_ not in ci]
+                margin = float(min(lg[e_] for e_ in only_c) - max(lg[e_] for e_ in only_g)) if only_c else \
+                    float(max(abs(lg[ci[k_]] - lg[gi[k_]]) for k_ in range(len(ci)) if gi[k_] != ci[k_]))
+                first = {"layer": l, "margin": margin, "same_experts": not only_c}
+                break
+            clean = max(clean, float(np.max(np.abs(eng.layer_out(l) - om.layer_out(l))) / np.max(np.abs(om.layer_out(l)))))
         check = {"prompt_tokens": n, "chunk": chunk, "max_layer_rel_err_last_token": worst, "max_logit_abs_err": float(np.max(np.abs(gl - ml))),
-                 "argmax_equal": bool(int(np.argmax(gl)) == int(np.argmax(ml))), "router_id_layer_mismatches_last_token": ids}
+                 "argmax_equal": bool(int(np.argmax(gl)) == int(np.argmax(ml))), "router_id_layer_mismatches_last_token": ids,
+                 "first_router_mismatch": first, "max_layer_rel_err_before_first_mismatch": clean}
         del om
     for _ in range(args.warmup):
         eng.reset()

@@ -296,6 +296,7 @@ struct rl_engine {
     float *bx[2] = {nullptr, nullptr};           // layer input / output of a chunk (ping-pong)
     int8_t *xq = nullptr; float *sx = nullptr;   // chunk activations as digit planes for the Q6_K tensor-core projections
     uint32_t *tok_chunk_d = nullptr, *pos_chunk_d = nullptr;
+    float *dn_pd = nullptr;          // DeltaNet prefill: the 16 pair products of every group of four tokens and key head
     __half *tc_xs = nullptr; float *tc_xinv = nullptr; uint32_t *tc_err = nullptr;   // tcgen05 GEMM: activation digits, per-token inverse scales, timeout flag
     // host mirrors
     std::vector<float> embed_h, layer_out_h, final_norm_h;
@@ -491,7 +492,7 @@ static int eng_prefill_chunk(rl_engine *e, uint32_t n, bool want_logits, char *e
             float *outs[3] = {e->qkv, e->z, e->ba};
             ENG_RC(eng_proj(e, mats, outs, 3, e->normed, n, "dn_proj"));
             ENG_RC(launch_deltanet_seq(D, n, L.conv_k, L.dt, L.a, L.ssm_norm, e->qkv, e->z, e->ba, e->conv + (size_t)L.ridx * (in.d_conv - 1u) * in.channels,
-                                       e->rec + (size_t)L.ridx * in.dt_rank * in.d_state * in.d_state, e->dn_qk, e->dn_v, e->dn_beta, e->dn_gate, e->dn_core, e->ng, s));
+                                       e->rec + (size_t)L.ridx * in.dt_rank * in.d_state * in.d_state, e->dn_qk, e->dn_v, e->dn_beta, e->dn_gate, e->dn_core, e->ng, e->dn_pd, s));
             float *o1[1] = {e->branch};
             ENG_RC(eng_proj(e, &L.ssm_out, o1, 1, e->ng, n, "dn_out"));
         } else {
@@ -725,7 +726,8 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
                  o_pa = take((size_t)in.n_head * parts * in.head_dim * 4u), o_em = take(in.hidden * 4u), o_lo = take((size_t)in.n_layer * in.hidden * 4u),
                  o_fn = take(in.hidden * 4u), o_lg = take((size_t)in.vocab * 4u), o_ri = take((size_t)in.n_layer * RL_ENGINE_MAX_TOPK * 4u), o_tk = take(16), o_gt = take(4096u * 4u),
                  o_bx0 = take(T * in.hidden * 4u), o_bx1 = take(T * in.hidden * 4u), o_xq = take(T * 3u * widest), o_sx = take(T * 4u), o_tc = take(T * 4u), o_pc = take(T * 4u),
-                 o_txs = take(tc_xs_halves((uint32_t)T, widest, 128u) * 2u), o_txi = take((T + 128u) * 4u), o_ter = take(16);
+                 o_txs = take(tc_xs_halves((uint32_t)T, widest, 128u) * 2u), o_txi = take((T + 128u) * 4u), o_ter = take(16),
+                 o_pd = take((T + 4u) * in.n_group * 4u * 4u);
     if (!e->scratch.alloc(w)) ENG_FAIL("%s", redcuda_last_error());
     uint8_t *B = e->scratch.as<uint8_t>();
     ENG_CUDA(cudaMemsetAsync(B, 0, w, e->stream));
@@ -740,6 +742,7 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
     e->tok_chunk_d = (uint32_t *)(B + o_tc); e->pos_chunk_d = (uint32_t *)(B + o_pc);
     for (uint32_t l = 0; l < in.n_layer; ++l) moe_set_ids_mirror(e->layers[l].moe, e->router_ids_d + (size_t)l * RL_ENGINE_MAX_TOPK);
     e->tc_xs = (__half *)(B + o_txs); e->tc_xinv = (float *)(B + o_txi); e->tc_err = (uint32_t *)(B + o_ter);
+    e->dn_pd = (float *)(B + o_pd);
     e->embed_h.assign(in.hidden, 0.f); e->layer_out_h.assign((size_t)in.n_layer * in.hidden, 0.f); e->final_norm_h.assign(in.hidden, 0.f);
     e->router_ids_h.assign((size_t)in.n_layer * RL_ENGINE_MAX_TOPK, 0u);
     ENG_CUDA(cudaMallocHost((void **)&e->token_pin, 64u + 2u * T * 4u));      // [16 words][chunk tokens][chunk positions]

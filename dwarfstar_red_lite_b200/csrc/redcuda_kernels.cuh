@@ -56,10 +56,11 @@ struct DnDims { uint32_t d_conv, S, groups, rank, d_inner, channels; float eps; 
 int launch_deltanet(const DnDims &D, uint32_t batch, const float *conv_kernel, const float *dt_bias, const float *ssm_a, const float *norm_w,
                     const float *qkv, const float *z, const float *ba, float *conv_state, float *rec_state,
                     float *qk, float *v, float *beta, float *gate, float *core, float *out, cudaStream_t s);
-// T consecutive tokens of one sequence (prefill chunk): rows of qkv / z / ba / out and of the scratch are per token
+// T consecutive tokens of one sequence (prefill chunk): rows of qkv / z / ba / out and of the scratch are per token;
+// pairdots: scratch of T * groups * 4 floats (null: the recurrence runs token by token)
 int launch_deltanet_seq(const DnDims &D, uint32_t T, const float *conv_kernel, const float *dt_bias, const float *ssm_a, const float *norm_w,
                     const float *qkv, const float *z, const float *ba, float *conv_state, float *rec_state,
-                    float *qk, float *v, float *beta, float *gate, float *core, float *out, cudaStream_t s);
+                    float *qk, float *v, float *beta, float *gate, float *core, float *out, float *pairdots, cudaStream_t s);
 
 // Cross-GPU flags of the peer-memory exchange (redcuda_ep.cu): a flag word holds the sequence number of the last step its
 // writer completed. ep_wait_flag spins (system-scope acquire loads, at most EP_WAIT_NS) until *flag has reached seq;

@@ -171,6 +171,35 @@ def test_midsize_model_chunked_prefill(tmp_path, monkeypatch):
         eng.close()
 
 
+@pytest.mark.parametrize("which", ["tiny", "mid"])
+def test_chunked_prefill_with_grouped_deltanet_recurrence(tmp_path, which, monkeypatch):
+    """RC_DN_SCAN=grouped: the delta rule four tokens at a time (one round of reductions per group) must leave the same
+    outputs and state as the oracle's token-by-token pass; prompt lengths that are not multiples of four leave a tail for
+    the token-by-token kernel."""
+    monkeypatch.setenv("RL_KV_F16", "1")
+    monkeypatch.setenv("RC_DN_SCAN", "grouped")
+    if which == "tiny":
+        dims = synth.tiny_model_dims(n_layer=8)
+    else:
+        dims = synth.ModelDims(n_layer=4, vocab=2048, n_expert=32, top_k=10, context=48)
+    sm = synth.model(91, dims)
+    path = str(tmp_path / "m.gguf")
+    gguf_writer.write_gguf(path, sm)
+    eng = Engine(path, context=dims.context, prefill_batch=16)
+    om = ol.OracleModel(sm, kv_f16=True, context=dims.context)
+    try:
+        prompt = np.random.default_rng(10).integers(0, dims.vocab, 27).astype(np.uint32)     # 16 + 11: groups plus a tail of 3
+        gl = eng.prefill(prompt)
+        for t in prompt:
+            ml = om.step(int(t), threads=os.cpu_count() or 1)
+        _compare_last(eng, om, dims, gl, ml, which)
+        tok = int(np.argmax(ml))
+        for step in range(3):
+            tok = _compare_step(eng, om, dims, tok, step)
+    finally:
+        eng.close()
+
+
 def test_resident_engine_reports_no_expert_traffic(tmp_path, monkeypatch):
     """Every expert is resident in HBM, so what the reference's expert LRU counts (native/redlite_native_cache.c:160-323,
     surfaced through rl_engine_step_stats, native/redlite_native_engine.h:62-87) stays at zero after open: no loads, no
