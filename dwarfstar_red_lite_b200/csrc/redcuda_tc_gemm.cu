@@ -19,8 +19,10 @@
 //                 planar layout kept, so the exact decoder of the GEMV path reads them unchanged), decode 128 x 64
 //                 weights from shared memory into the two fp16 digit tiles of the stage (canonical K-major core-matrix
 //                 layout, no swizzle) and copy the stage's activation digits (laid out for the MMA by k_tc_prep_x)
-//   one thread    issues 4 k-steps x 3 tcgen05.mma (128 x TN x 16, kind::f16, fp32 accumulate) and a tcgen05.commit
-//                 on the stage buffer's mbarrier; the MMAs of a stage run while the warps decode the next one
+//   one thread    issues 4 k-steps x 2 tcgen05.mma (kind::f16, fp32 accumulate): the activation tile holds the hi rows and
+//                 then the lo rows of its tokens, so A_hi x [B_hi | B_lo] is ONE instruction of N = 2 TN and A_lo x B_hi
+//                 one of N = TN; then a tcgen05.commit on the stage buffer's mbarrier; the MMAs of a stage run while the
+//                 warps decode the next one
 //   every block   tcgen05.ld of the finished block's two accumulators (lane = weight row, column = token) into fp32
 //                 register sums, one 256-column block behind the MMAs
 //   epilogue      scaling, stores
@@ -163,7 +165,7 @@ __device__ __forceinline__ void tc_decode_stage(const uint8_t *raw, uint8_t *abu
 }
 
 // x [ntok][ncols] fp32 (or SiLU(x) * x2 when x2 is given) -> fp16 digits in the order the GEMM stages consume them:
-// xs[token tile][k stage][digit hi/lo][k chunk of 8 (8)][token group of 8 (TN/8)][token in group (8)][8 halves];
+// xs[token tile][k stage][k chunk of 8 (8)][digit hi/lo][token group of 8 (TN/8)][token in group (8)][8 halves];
 // x_inv[t] = 2^-e_t undoes the per-token scale. Tokens beyond ntok are zero. grid = token tiles * TN, block = 256
 __global__ void k_tc_prep_x(const float *__restrict__ x, const float *__restrict__ x2, uint32_t x_stride, uint32_t ntok, uint32_t ncols, uint32_t tn,
                             __half *__restrict__ xs, float *__restrict__ x_inv) {
@@ -195,9 +197,11 @@ __global__ void k_tc_prep_x(const float *__restrict__ x, const float *__restrict
             hi[j] = __float2half_rn(v);
             lo[j] = __float2half_rn(v - __half2float(hi[j]));
         }
-        __half *dst = xs + ((size_t)tile * nstage + stage) * 2u * digit + ((size_t)kc * (tn >> 3) + (tt >> 3)) * 64u + (tt & 7u) * 8u;
+        // inside a stage: [k chunk][2 tn rows: the hi digits of the tn tokens, then their lo digits][8 halves], so that one MMA
+        // of N = 2 tn takes both digits and one of N = tn the hi digits alone
+        __half *dst = xs + ((size_t)tile * nstage + stage) * 2u * digit + ((size_t)kc * (tn >> 2) + (tt >> 3)) * 64u + (tt & 7u) * 8u;
         *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(hi);
-        *reinterpret_cast<uint4 *>(dst + digit) = *reinterpret_cast<const uint4 *>(lo);
+        *reinterpret_cast<uint4 *>(dst + (size_t)tn * 8u) = *reinterpret_cast<const uint4 *>(lo);
     }
 }
 
@@ -279,7 +283,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
         we = we > 100 ? 100 : we < -100 ? -100 : we;
     }
     const float w_scale = exp2f((float)we), w_inv = exp2f((float)-we);
-    const uint32_t idesc = tc_idesc((uint32_t)TN);
+    const uint32_t idesc = tc_idesc((uint32_t)TN), idesc2 = tc_idesc(2u * (uint32_t)TN);
 
     // fp32 sums over the 256-column blocks: warp w owns TMEM lanes 32*(w%4)..+31 (its quarter) and PER token columns
     constexpr uint32_t PER = (uint32_t)TN / (TC_WARPS / 4u);              // columns per warp: 8, 16 or 32
@@ -340,17 +344,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
             if (!mbar_wait(smem_u32(&bfull[jb]), (s / NB) & 1u)) fail = 1u;
             else {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_hi = smem_u32(abuf), a_lo = a_hi + TC_A_DIGIT, b_hi = smem_u32(b_base + jb * B_BUF), b_lo = b_hi + B_DIGIT;
-                constexpr uint32_t A_LBO = TC_M * 16u, B_LBO = (uint32_t)TN * 16u, SBO = 128u;
+                // Two MMAs per k-step: A_hi x [B_hi | B_lo] (N = 2 TN: the hi*hi sums land in the first TN accumulator
+                // columns, hi*lo in the next TN) and A_lo x B_hi (N = TN, added to the cross-product columns). The issuing
+                // thread's latency per stage is on the critical path, so descriptors are a constant plus a start address.
+                constexpr uint32_t A_LBO = TC_M * 16u, B_LBO = 2u * (uint32_t)TN * 16u, SBO = 128u;
+                const uint64_t da0 = tc_smem_desc(0u, A_LBO, SBO), db0 = tc_smem_desc(0u, B_LBO, SBO);
+                const uint32_t a_hi = smem_u32(abuf) >> 4, a_lo = (smem_u32(abuf) + TC_A_DIGIT) >> 4, b_st = smem_u32(b_base + jb * B_BUF) >> 4;
+                const uint32_t d_main = tmem + ((s >> 2) & 1u) * 2u * (uint32_t)TN, d_cross = d_main + (uint32_t)TN;
 #pragma unroll
                 for (uint32_t kk = 0; kk < TC_KS / 16u; ++kk) {
-                    const uint64_t dah = tc_smem_desc(a_hi + 2u * kk * A_LBO, A_LBO, SBO), dal = tc_smem_desc(a_lo + 2u * kk * A_LBO, A_LBO, SBO);
-                    const uint64_t dbh = tc_smem_desc(b_hi + 2u * kk * B_LBO, B_LBO, SBO), dbl = tc_smem_desc(b_lo + 2u * kk * B_LBO, B_LBO, SBO);
-                    const uint32_t d_main = tmem + ((s >> 2) & 1u) * 2u * (uint32_t)TN, d_cross = d_main + (uint32_t)TN;
-                    const uint32_t first = ((s & 3u) | kk) ? 1u : 0u;       // a block's first MMA overwrites its accumulators
-                    tc_mma(d_main, dah, dbh, idesc, first);
-                    tc_mma(d_cross, dah, dbl, idesc, first);
-                    tc_mma(d_cross, dal, dbh, idesc, 1u);
+                    const uint64_t dah = da0 + ((a_hi + kk * (2u * A_LBO >> 4)) & 0x3fffu), dal = da0 + ((a_lo + kk * (2u * A_LBO >> 4)) & 0x3fffu);
+                    const uint64_t db = db0 + ((b_st + kk * (2u * B_LBO >> 4)) & 0x3fffu);
+                    tc_mma(d_main, dah, db, idesc2, ((s & 3u) | kk) ? 1u : 0u);      // a block's first MMA overwrites its accumulators
+                    tc_mma(d_cross, dal, db, idesc, 1u);
                 }
                 tc_commit(smem_u32(&mbar[b]));
                 if ((s & 3u) == 3u) tc_commit(smem_u32(&accfull[(s >> 2) & 1u]));
