@@ -577,6 +577,88 @@ def run_prefill(args):
     eng.close()
 
 
+def run_prefill_ep(args, world, rank, local):
+    """BASELINE configs[4] under expert parallelism: every rank prefills its OWN prompt through its own engine, which holds
+    the dense weights and a contiguous share of every layer's experts; per layer the chunk's token rows of all ranks are
+    exchanged (all-gather form, see run_ep). Weak scaling: N prompts of --prompt-tokens tokens. Timed per rank around the
+    whole prefill call, maximum over ranks. Rank 0 checks the first tokens against the CPU oracle."""
+    import torch
+    import torch.distributed as dist
+    import dwarfstar_red_lite_b200 as rc
+    from dwarfstar_red_lite_b200 import ep, gguf_writer, synth
+    from dwarfstar_red_lite_b200.engine import Engine
+    os.environ.setdefault("RL_KV_F16", "1")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    n_prompt = args.prompt_tokens
+    dims = synth.ModelDims(n_layer=args.layers, context=max(args.context, n_prompt + 8))
+    tmp = os.environ.get("REDCUDA_TMP", "/tmp")
+    path = os.path.join(tmp, f"redcuda_synth_{args.layers}l_seed{args.seed}.gguf")
+    if rank == 0 and not os.path.exists(path):
+        gguf_writer.write_gguf_streaming(path, args.seed, dims)
+    dist.barrier()
+    rc.set_codebooks(device=local)
+    eng = Engine(path, context=dims.context, prefill_batch=args.prefill_batch, ep_rank=rank, ep_world=world)
+    info, chunk = eng.info, eng.prefill_batch
+    ctx = ep.EpContext(rank, world, chunk, int(info.hidden), int(info.top_k), exchange=args.ep_exchange)
+    eng.attach_ep(ctx)
+    prompt = np.random.default_rng(args.seed + 100 * rank).integers(0, dims.vocab, n_prompt).astype(np.uint32)
+    check = None
+    if args.check_steps > 0:          # every rank runs the same call sequence; rank 0 compares with the oracle
+        n = args.check_steps
+        gl = eng.prefill(prompt[:n])
+        if rank == 0:
+            sys.path.insert(0, os.path.join(ROOT, "tests"))
+            import oracle_lib as ol
+            om = ol.OracleModel(gguf_writer.load_gguf(path, dims), kv_f16=True, context=dims.context)
+            for t in prompt[:n]:
+                ml = om.step(int(t), threads=os.cpu_count() or 1)
+            first, clean = None, 0.0
+            for l in range(info.n_layer):
+                err_l = float(np.max(np.abs(eng.layer_out(l) - om.layer_out(l))) / np.max(np.abs(om.layer_out(l))))
+                if not np.array_equal(eng.router_ids(l), om.router_ids(l)):
+                    first = l
+                    break
+                clean = max(clean, err_l)
+            check = {"prompt_tokens": n, "first_router_mismatch_layer": first, "max_layer_rel_err_before_first_mismatch": clean,
+                     "argmax_equal": bool(int(np.argmax(gl)) == int(np.argmax(ml))), "bound": 1e-3, "ok": bool(clean <= 1e-3)}
+            del om
+        dist.barrier()
+    for _ in range(args.warmup):
+        eng.reset()
+        eng.prefill(prompt[: min(n_prompt, 2 * chunk)])
+    times = []
+    launches0 = rc.lib().redcuda_launch_count()
+    with ClockSampler(local) as clocks:
+        for _ in range(args.steps):
+            eng.reset()
+            torch.cuda.synchronize()
+            dist.barrier()
+            t0 = time.perf_counter()
+            eng.prefill(prompt)
+            times.append((time.perf_counter() - t0) * 1e3)
+    launches = (rc.lib().redcuda_launch_count() - launches0) // max(1, args.steps)
+    ms = torch.tensor([float(np.median(times))], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms_run = float(ms.item())
+        tok_s = n_prompt * world / (ms_run * 1e-3)
+        line = {"metric": "prefill_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms_run, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": f"BASELINE configs[4] under expert parallelism: {world} prompts of {n_prompt} random tokens (one per rank), chunks of {chunk}, "
+                                       f"{info.n_layer}-layer Qwen3-Next-shaped random-init model, fp16 KV, experts sharded contiguously ({info.n_expert // world} per rank)",
+                           "exchange_kind": ctx.exchange, "l2_policy": "weights far larger than L2"},
+                "roofline": None, "cpu_baseline": None, "parity": check,
+                "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": int(n_prompt * 8), "d2h_bytes_per_step": int(info.vocab * 4 + (2 * info.n_layer + 2) * info.hidden * 4),
+                        "note": "the timed call is the host API itself on every rank: prompt ids from host memory, logits and mirrors back"},
+                "gpu_launches": int(launches), "clocks": clocks.summary()}
+        print(json.dumps(line), flush=True)
+    eng.close()
+    ctx.close()
+    dist.destroy_process_group()
+
+
 def _timed_graph(torch, step_fn, steps, warmup, device_index):
     """warm up, capture step_fn(stream) into a CUDA graph on a side stream, time `steps` replays with CUDA events"""
     side = torch.cuda.Stream()
@@ -791,6 +873,11 @@ def main():
         args.warmup = max(args.warmup, 1)
         return run_decode48(args)
     if args.workload == "prefill":
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if world > 1:
+            if args.gpus != world:
+                raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+            return run_prefill_ep(args, world, int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")))
         return run_prefill(args)
     if args.workload == "moe_b1":
         return run_moe_b1(args)

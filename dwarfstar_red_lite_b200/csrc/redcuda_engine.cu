@@ -26,6 +26,8 @@ namespace rc {
 const uint32_t *moe_last_ids_device(const redcuda_moe *m);   // redcuda_moe.cu
 void moe_set_ids_mirror(redcuda_moe *m, uint32_t *dev_ptr);   // a single token's router ids are also written to dev_ptr
 size_t moe_workspace_bytes(const redcuda_moe_desc *d);
+// expert parallelism: which contiguous share of every layer's experts the engines opened next will hold
+static thread_local int g_shard_rank = 0, g_shard_world = 1;
 redcuda_moe *moe_create_shared(const redcuda_moe_desc *d, void *workspace);   // workspace shared by layers that run on one stream
 
 static double now_ms() { return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
@@ -274,6 +276,8 @@ struct rl_engine {
     std::vector<EngLayer> layers;
     DMat tok_embd, output;
     const float *output_norm = nullptr;
+    int ep_rank = 0, ep_world = 1;       // expert shard of this engine (contiguous: experts [rank * E / world, (rank + 1) * E / world))
+    redcuda_ep *ep = nullptr;            // attached exchange context (not owned); required before the first step when ep_world > 1
     DevMem dense, state, scratch, moe_ws;      // moe_ws: the expert workspace shared by every layer
     bool kv_half = false;
     uint32_t position = 0, ffn = 0, ffn_sh = 0;
@@ -373,6 +377,7 @@ static int eng_attention(rl_engine *e, const EngLayer &L, uint32_t ntok, const u
 static int eng_step_device(rl_engine *e, bool want_logits, char *error, size_t cap) {
     const rl_engine_info &in = e->info;
     cudaStream_t s = e->stream;
+    if (e->ep_world > 1 && !e->ep) ENG_FAIL("this engine holds an expert shard: attach the exchange context first (redcuda_engine_attach_ep)");
     if (e->position >= in.context) ENG_FAIL("context of %u positions is full", in.context);
     prof_begin("embed", s);
     RC_LAUNCH((k_embed_row), 1, 256, 0, s, e->tok_embd.base, e->tok_embd.type, e->tok_embd.nb, in.hidden, in.vocab, e->token_d, books_iq2(), books_iq3s(), e->embed_d, status_words());
@@ -408,8 +413,12 @@ static int eng_step_device(rl_engine *e, bool want_logits, char *error, size_t c
         prof_end(s);
         g_launches.fetch_add(1);
         float *xo = e->layer_out_d + (size_t)l * in.hidden;
+        if (e->ep_world > 1) {
+            ENG_RC(redcuda_ep_layer_forward_n(e->ep, L.moe, 1u, e->normed, nullptr, e->resid, xo, s));
+            ENG_CUDA(cudaMemcpyAsync(e->router_ids_d + (size_t)l * RL_ENGINE_MAX_TOPK, redcuda_ep_last_ids_device(e->ep), in.top_k * sizeof(uint32_t), cudaMemcpyDeviceToDevice, s));
+        } else
         ENG_RC(redcuda_moe_forward_device(L.moe, 1u, e->normed, nullptr, e->resid, xo, s));      // its router kernel also fills router_ids_d (mirror set at open)
-        if (in.n_expert > 1024u) ENG_CUDA(cudaMemcpyAsync(e->router_ids_d + (size_t)l * RL_ENGINE_MAX_TOPK, moe_last_ids_device(L.moe), in.top_k * sizeof(uint32_t), cudaMemcpyDeviceToDevice, s));
+        if (e->ep_world == 1 && in.n_expert > 1024u) ENG_CUDA(cudaMemcpyAsync(e->router_ids_d + (size_t)l * RL_ENGINE_MAX_TOPK, moe_last_ids_device(L.moe), in.top_k * sizeof(uint32_t), cudaMemcpyDeviceToDevice, s));
         x = xo;
     }
     prof_begin("rmsnorm", s);
@@ -470,6 +479,7 @@ static int eng_proj(rl_engine *e, const DMat *mats, float *const *outs, uint32_t
 // rows and masks by position. The mirrors are left holding the last token's rows, as after n single steps
 // (the reference's chunked prefill, native/redlite_native_engine.c:600-640).
 static int eng_prefill_chunk(rl_engine *e, uint32_t n, bool want_logits, char *error, size_t cap) {
+    if (e->ep_world > 1 && !e->ep) ENG_FAIL("this engine holds an expert shard: attach the exchange context first (redcuda_engine_attach_ep)");
     const rl_engine_info &in = e->info;
     cudaStream_t s = e->stream;
     if (e->position + n > in.context) ENG_FAIL("context of %u positions is full", in.context);
@@ -509,8 +519,9 @@ static int eng_prefill_chunk(rl_engine *e, uint32_t n, bool want_logits, char *e
         prof_end(s);
         g_launches.fetch_add(1);
         float *xo = e->bx[(l + 1u) & 1u];
-        ENG_RC(redcuda_moe_forward_device(L.moe, n, e->normed, nullptr, e->resid, xo, s));
-        ENG_CUDA(cudaMemcpyAsync(e->router_ids_d + (size_t)l * RL_ENGINE_MAX_TOPK, moe_last_ids_device(L.moe) + last * in.top_k, in.top_k * sizeof(uint32_t), cudaMemcpyDeviceToDevice, s));
+        if (e->ep_world > 1) ENG_RC(redcuda_ep_layer_forward_n(e->ep, L.moe, n, e->normed, nullptr, e->resid, xo, s));
+        else ENG_RC(redcuda_moe_forward_device(L.moe, n, e->normed, nullptr, e->resid, xo, s));
+        ENG_CUDA(cudaMemcpyAsync(e->router_ids_d + (size_t)l * RL_ENGINE_MAX_TOPK, (e->ep_world > 1 ? redcuda_ep_last_ids_device(e->ep) : moe_last_ids_device(L.moe)) + last * in.top_k, in.top_k * sizeof(uint32_t), cudaMemcpyDeviceToDevice, s));
         ENG_CUDA(cudaMemcpyAsync(e->layer_out_d + (size_t)l * in.hidden, xo + last * in.hidden, in.hidden * 4u, cudaMemcpyDeviceToDevice, s));
         x = xo;
     }
@@ -617,6 +628,8 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
     // does this engine (2048 is also the ceiling). The chunk sizes the expert workspace (about 0.5 GB at 2048), which all
     // layers share: they run one after the other on the engine's stream. 1 = token by token.
     e->pb = e->cfg.prefill_batch ? std::min(e->cfg.prefill_batch, 2048u) : 2048u;
+    e->ep_rank = g_shard_rank; e->ep_world = g_shard_world;
+    if (e->ep_world > 1 && in.n_expert % (uint32_t)e->ep_world) ENG_FAIL("%u experts do not divide over %d ranks", in.n_expert, e->ep_world);
     if (e->pb > in.context) e->pb = in.context;
 
     // ---- layer kinds from tensor names (native/redlite_native_layer_map.c:114-124), sizes of the dense arena
@@ -685,8 +698,13 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
         redcuda_moe_desc d;
         memset(&d, 0, sizeof(d));
         d.hidden = in.hidden; d.n_expert = in.n_expert; d.top_k = in.top_k; d.ffn = (uint32_t)ge->shape[1]; d.ffn_sh = (uint32_t)sg->shape[1];
-        d.type_gu = ge->type; d.type_down = de->type; d.type_sh = sg->type; d.expert_begin = 0; d.expert_count = in.n_expert; d.max_tokens = e->pb; d.weights_on_device = 0;
-        d.router = (const float *)g.data(tr); d.gate_exps = g.data(ge); d.up_exps = g.data(ue); d.down_exps = g.data(de);
+        d.type_gu = ge->type; d.type_down = de->type; d.type_sh = sg->type; d.weights_on_device = 0;
+        // under expert parallelism the engine holds a contiguous share of the experts and sees the tokens of every rank
+        const uint32_t ec = in.n_expert / (uint32_t)e->ep_world, eb = (uint32_t)e->ep_rank * ec;
+        d.expert_begin = eb; d.expert_count = ec; d.max_tokens = e->pb * (uint32_t)e->ep_world;
+        d.router = (const float *)g.data(tr);
+        d.gate_exps = g.data(ge) + (size_t)eb * (ge->bytes / in.n_expert); d.up_exps = g.data(ue) + (size_t)eb * (ue->bytes / in.n_expert);
+        d.down_exps = g.data(de) + (size_t)eb * (de->bytes / in.n_expert);
         d.sh_gate_inp = (const float *)g.data(tg); d.sh_gate = g.data(sg); d.sh_up = g.data(su); d.sh_down = g.data(sd);
         e->ffn = d.ffn;
         {
@@ -800,6 +818,7 @@ int rl_engine_step(rl_engine *e, rl_engine_backend backend, uint32_t token, floa
     if (!e) { eng_err(error, cap, "null engine"); return 0; }
     if (backend != RL_BACKEND_GPU) { eng_err(error, cap, "the CPU backend is not part of this library"); return 0; }
     if (token >= e->info.vocab) { eng_err(error, cap, "token id out of range"); return 0; }
+    if (e->ep_world > 1) { eng_err(error, cap, "greedy generation on the device is not served under expert parallelism (the exchange's step counter cannot live in a replayed graph); use rl_engine_step"); return 0; }
     const double t0 = now_ms();
     if (stats) memset(stats, 0, sizeof(*stats));
     ENG_CUDA(cudaSetDevice(e->device));
@@ -852,6 +871,18 @@ int rl_engine_prefill(rl_engine *e, rl_engine_backend backend, const uint32_t *t
 }
 
 uint32_t rl_engine_prefill_batch(const rl_engine *e) { return e ? e->pb : 0u; }
+
+int redcuda_engine_shard(int rank, int world) {
+    if (world < 1 || rank < 0 || rank >= world) { set_error("engine shard: rank %d of %d", rank, world); return 0; }
+    g_shard_rank = rank; g_shard_world = world;
+    return 1;
+}
+
+int redcuda_engine_attach_ep(rl_engine *e, redcuda_ep *ep) {
+    if (!e || !ep) { set_error("engine attach: null argument"); return 0; }
+    e->ep = ep;
+    return 1;
+}
 
 int rl_engine_generate_greedy(rl_engine *e, uint32_t token, uint32_t n_new, uint32_t *out_tokens, rl_engine_step_stats *stats, char *error, size_t cap) {
     if (!e || !out_tokens || !n_new || n_new > 4096u) { eng_err(error, cap, "invalid generate arguments (1..4096 new tokens)"); return 0; }

@@ -115,19 +115,31 @@ __global__ void __launch_bounds__(256) k_ep_push(const __grid_constant__ EpPushA
     ep_signal_all(A.peers, A.off_flag, A.seq, A.ticket, gridDim.x);
 }
 
-// out[t] = shared[t] + sum over ranks r of slot[r][t], once every rank's combine has delivered. grid = (hidden / 1024, tokens)
-__global__ void __launch_bounds__(256) k_ep_reduce(const float *__restrict__ slots, const float *__restrict__ shared, uint32_t world, uint32_t tokens, uint32_t hidden,
-                                                   const EpWait wait, float *__restrict__ out) {
+// out[t] = (resid[t] +) shared[t] + sum over ranks r of slot[r][t], once every rank's combine has delivered. grid = (hidden / 1024, tokens)
+__global__ void __launch_bounds__(256) k_ep_reduce(const float *__restrict__ slots, const float *__restrict__ shared, const float *__restrict__ resid, uint32_t world, uint32_t tokens,
+                                                   uint32_t hidden, const EpWait wait, float *__restrict__ out) {
     pdl_prologue();
     ep_wait_all(wait);
     const uint32_t t = blockIdx.y, r = (blockIdx.x * 256u + threadIdx.x) * 4u;
     if (r >= hidden) return;
     float4 acc = *reinterpret_cast<const float4 *>(shared + (size_t)t * hidden + r);
+    if (resid) { const float4 v = *reinterpret_cast<const float4 *>(resid + (size_t)t * hidden + r); acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w; }
     for (uint32_t p = 0; p < world; ++p) {
         const float4 v = __ldcg(reinterpret_cast<const float4 *>(slots + ((size_t)p * tokens + t) * hidden + r));      // written by another GPU: read at L2
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     *reinterpret_cast<float4 *>(out + (size_t)t * hidden + r) = acc;
+}
+
+// io[i] += resid[i], n4 float4s (the residual of the NCCL and single-rank paths, whose sums end in the caller's buffer)
+__global__ void __launch_bounds__(256) k_ep_add_resid(float4 *__restrict__ io, const float4 *__restrict__ resid, uint32_t n4) {
+    pdl_prologue();
+    const uint32_t i = blockIdx.x * 256u + threadIdx.x;
+    if (i >= n4) return;
+    float4 a = io[i];
+    const float4 b = resid[i];
+    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    io[i] = a;
 }
 
 }  // namespace rc
@@ -153,6 +165,15 @@ struct redcuda_ep {
     bool attached = false;
     uint32_t seq = 0;
 };
+
+static int add_resid(float *io, const float *resid, uint32_t n4, cudaStream_t s) {
+    if (!resid) return 1;
+    prof_begin("ep_add_resid", s);
+    RC_LAUNCH((k_ep_add_resid), (n4 + 255u) / 256u, 256, 0, s, reinterpret_cast<float4 *>(io), reinterpret_cast<const float4 *>(resid), n4);
+    prof_end(s);
+    RC_LAUNCHED();
+    return 1;
+}
 
 extern "C" {
 
@@ -255,10 +276,11 @@ int redcuda_ep_attach_peers(redcuda_ep *ep, const void *handles) {
     return 1;
 }
 
-int redcuda_ep_layer_forward(redcuda_ep *ep, redcuda_moe *layer, const float *x_dev, const float *logits_in_dev, float *out_dev, void *stream) {
+int redcuda_ep_layer_forward_n(redcuda_ep *ep, redcuda_moe *layer, uint32_t ntok, const float *x_dev, const float *logits_in_dev, const float *resid_dev, float *out_dev, void *stream) {
     RC_REQUIRE(ep && layer && x_dev && out_dev, "ep layer: null argument");
+    RC_REQUIRE(ntok >= 1u && ntok <= ep->tokens, "ep layer: %u tokens outside [1, %u]", ntok, ep->tokens);
     cudaStream_t s = (cudaStream_t)stream;
-    const uint32_t T = ep->tokens, H = ep->hidden, k = ep->top_k, W = (uint32_t)ep->world;
+    const uint32_t T = ntok, H = ep->hidden, k = ep->top_k, W = (uint32_t)ep->world;
     // the shared expert needs neither the router nor the exchange: side stream, joined before the experts' combine
     RC_CUDA(cudaEventRecord(ep->ev_fork, s));
     RC_CUDA(cudaStreamWaitEvent(ep->side, ep->ev_fork, 0));
@@ -269,7 +291,8 @@ int redcuda_ep_layer_forward(redcuda_ep *ep, redcuda_moe *layer, const float *x_
     if (digits && !launch_quant_act(x_dev, H, T, H, ep->xq, ep->sx, s)) return 0;
     if (W == 1u) {
         RC_CUDA(cudaStreamWaitEvent(s, ep->ev_join, 0));
-        return moe_partial_gathered(layer, T, x_dev, digits ? ep->xq : nullptr, ep->sx, ep->ids, ep->w, ep->shared, 0u, T, out_dev, s, nullptr, nullptr);
+        if (!moe_partial_gathered(layer, T, x_dev, digits ? ep->xq : nullptr, ep->sx, ep->ids, ep->w, ep->shared, 0u, T, out_dev, s, nullptr, nullptr)) return 0;
+        return add_resid(out_dev, resid_dev, T * H / 4u, s);
     }
     if (ep->attached) {
         const uint32_t seq = ++ep->seq;
@@ -293,7 +316,7 @@ int redcuda_ep_layer_forward(redcuda_ep *ep, redcuda_moe *layer, const float *x_
                                   nullptr, 0u, 0u, nullptr, s, &wg, &pp)) return 0;
         RC_CUDA(cudaStreamWaitEvent(s, ep->ev_join, 0));
         prof_begin("ep_reduce", s);
-        RC_LAUNCH((k_ep_reduce), dim3((H / 4u + 255u) / 256u, T), 256, 0, s, reinterpret_cast<const float *>(X + ep->o_part), ep->shared, W, T, H, wr, out_dev);
+        RC_LAUNCH((k_ep_reduce), dim3((H / 4u + 255u) / 256u, T), 256, 0, s, reinterpret_cast<const float *>(X + ep->o_part), ep->shared, resid_dev, W, T, H, wr, out_dev);
         prof_end(s);
         RC_LAUNCHED();
         return 1;
@@ -316,8 +339,15 @@ int redcuda_ep_layer_forward(redcuda_ep *ep, redcuda_moe *layer, const float *x_
     prof_begin("ep_reduce_scatter", s);
     RC_NCCL(api, api->ReduceScatter(ep->partial, out_dev, (size_t)T * H, ncclFloat32, ncclSum, ep->comm, s));
     prof_end(s);
-    return 1;
+    return add_resid(out_dev, resid_dev, T * H / 4u, s);
 }
+
+int redcuda_ep_layer_forward(redcuda_ep *ep, redcuda_moe *layer, const float *x_dev, const float *logits_in_dev, float *out_dev, void *stream) {
+    RC_REQUIRE(ep, "ep layer: null argument");
+    return redcuda_ep_layer_forward_n(ep, layer, ep->tokens, x_dev, logits_in_dev, nullptr, out_dev, stream);
+}
+
+const uint32_t *redcuda_ep_last_ids_device(const redcuda_ep *ep) { return ep ? ep->ids : nullptr; }
 
 int redcuda_ep_step(redcuda_ep *ep, redcuda_moe *const *layers, uint32_t n_layers, const float *const *x_dev, const float *const *logits_in_dev, float *const *out_dev, void *stream) {
     RC_REQUIRE(ep && layers && n_layers && x_dev && out_dev, "ep step: null or empty argument");

@@ -80,17 +80,29 @@ def _bind():
 class Engine:
     """rl_engine on the CUDA backend over a GGUF file."""
 
-    def __init__(self, path: str, context: int = 4096, top_k: int = 0, prefill_batch: int = 0):
+    def __init__(self, path: str, context: int = 4096, top_k: int = 0, prefill_batch: int = 0, ep_rank: int = 0, ep_world: int = 1):
+        """ep_rank / ep_world: under expert parallelism the engine holds the experts [rank * E / world, (rank + 1) * E / world)
+        of every layer; attach_ep() must follow before the first prefill or step."""
         _ensure_books()
         self.L = _bind()
+        if self.L.redcuda_engine_shard(ep_rank, ep_world) != 1:
+            raise RedcudaError(self.L.redcuda_last_error().decode(errors="replace"))
         cfg = RlEngineConfig()
         self.L.rl_engine_config_default(C.byref(cfg))
         cfg.context, cfg.top_k, cfg.enable_cpu, cfg.enable_gpu, cfg.prefill_batch = context, top_k, 0, 1, prefill_batch
         self._err = C.create_string_buffer(1024)
         self._e = self.L.rl_engine_open(path.encode(), C.byref(cfg), self._err, 1024)
+        self.L.redcuda_engine_shard(0, 1)          # the setting is per open call
         if not self._e:
             raise RedcudaError("rl_engine_open: " + self._err.value.decode(errors="replace"))
         self.info = self.L.rl_engine_info_get(self._e).contents
+        self._ep = None
+
+    def attach_ep(self, ctx):
+        """ctx: an ep.EpContext created with tokens >= prefill_batch; kept alive by this object"""
+        if self.L.redcuda_engine_attach_ep(self._e, ctx.handle) != 1:
+            raise RedcudaError(self.L.redcuda_last_error().decode(errors="replace"))
+        self._ep = ctx
 
     def close(self):
         if getattr(self, "_e", None):

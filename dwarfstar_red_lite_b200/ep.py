@@ -204,49 +204,70 @@ class EpGatherMoeLayer:
         return out
 
 
+class EpContext:
+    """The library's exchange context of one rank (redcuda_ep): NCCL communicator, exchange buffers and, for ranks on one
+    node, the other ranks' exchange areas mapped through CUDA IPC. The NCCL unique id and the IPC handles travel over
+    `group` (any torch.distributed backend). exchange: "peer" = stores into the other ranks' memory over NVLink with flag
+    words (2 to 8 ranks), "nccl" = ncclAllGather / ncclReduceScatter."""
+
+    def __init__(self, rank: int, world: int, tokens: int, hidden: int, top_k: int, group=None, exchange: str = "peer"):
+        import ctypes as C
+        import numpy as np
+        from .redcuda import RedcudaError, lib
+        self._lib, self._group, self.world, self.rank, self.tokens = lib(), group, world, rank, tokens
+
+        def check(ok):
+            if not ok:
+                raise RedcudaError(self._lib.redcuda_last_error().decode(errors="replace"))
+
+        dev = torch.device("cuda", torch.cuda.current_device())
+        on_dev = world > 1 and dist.get_backend(group) == "nccl"
+        uid = torch.zeros(128, dtype=torch.uint8)
+        if world > 1:
+            if rank == 0:
+                buf = (C.c_uint8 * 128)()
+                check(self._lib.redcuda_ep_unique_id(buf) == 1)
+                uid = torch.from_numpy(np.frombuffer(buf, dtype=np.uint8).copy())
+            uid = uid.to(dev) if on_dev else uid
+            dist.broadcast(uid, src=0, group=group)
+            uid = uid.cpu()
+        self.handle = self._lib.redcuda_ep_create(rank, world, uid.numpy().tobytes(), tokens, hidden, top_k)
+        check(bool(self.handle))
+        self.exchange = "nccl" if world > 1 else "none"
+        if world > 1 and exchange == "peer" and world <= 8:
+            hb = (C.c_uint8 * 64)()
+            check(self._lib.redcuda_ep_ipc_handle(self.handle, hb) == 1)
+            mine = torch.from_numpy(np.frombuffer(hb, dtype=np.uint8).copy())
+            mine = mine.to(dev) if on_dev else mine
+            everyone = torch.empty(world * 64, dtype=torch.uint8, device=mine.device)
+            dist.all_gather_into_tensor(everyone, mine, group=group)
+            check(self._lib.redcuda_ep_attach_peers(self.handle, everyone.cpu().numpy().tobytes()) == 1)
+            dist.barrier(group=group)          # nobody steps before every rank has mapped every area
+            self.exchange = "peer"
+
+    def close(self):
+        if self.handle:
+            if self.world > 1:
+                torch.cuda.synchronize()
+                dist.barrier(group=self._group)    # other ranks may still be writing into this rank's exchange area
+            self._lib.redcuda_ep_destroy(self.handle)
+            self.handle = None
+
+
 class EpStep:
     """The all-gather form through the library's own step call: one C entry per step queues route, pack, all-gather, the
     shard's experts, reduce-scatter, shared expert and add of every layer. `shards` are redcuda MoeLayer objects created
     with max_tokens >= world * tokens. The NCCL unique id travels from rank 0 over `group` (any backend)."""
 
     def __init__(self, shards, rank: int, world: int, tokens: int, group=None, exchange: str = "peer"):
-        """exchange: "peer" = stores into the other ranks' memory over NVLink with flag words (ranks are processes on one
-        node, 2 to 8 of them), "nccl" = ncclAllGather / ncclReduceScatter."""
         import ctypes as C
-        import numpy as np
-        from .redcuda import RedcudaError, lib
-        self._lib, self._C, self._group = lib(), C, group
+        from .redcuda import lib
+        self._lib, self._C = lib(), C
         d = shards[0].dims
         self.dims, self.T, self.world, self.shards = d, tokens, world, shards
+        self.ctx = EpContext(rank, world, tokens, d.hidden, d.top_k, group, exchange)
+        self._h, self.exchange = self.ctx.handle, self.ctx.exchange
         dev = torch.device("cuda", torch.cuda.current_device())
-        uid = torch.zeros(128, dtype=torch.uint8)
-        if world > 1:
-            if rank == 0:
-                buf = (C.c_uint8 * 128)()
-                if self._lib.redcuda_ep_unique_id(buf) != 1:
-                    raise RedcudaError(self._lib.redcuda_last_error().decode(errors="replace"))
-                uid = torch.from_numpy(np.frombuffer(buf, dtype=np.uint8).copy())
-            uid = uid.to(dev) if dist.get_backend(group) == "nccl" else uid
-            dist.broadcast(uid, src=0, group=group)
-            uid = uid.cpu()
-        self._uid = uid.numpy().tobytes()
-        self._h = self._lib.redcuda_ep_create(rank, world, self._uid, tokens, d.hidden, d.top_k)
-        if not self._h:
-            raise RedcudaError(self._lib.redcuda_last_error().decode(errors="replace"))
-        self.exchange = "nccl" if world > 1 else "none"
-        if world > 1 and exchange == "peer" and world <= 8:
-            hb = (C.c_uint8 * 64)()
-            if self._lib.redcuda_ep_ipc_handle(self._h, hb) != 1:
-                raise RedcudaError(self._lib.redcuda_last_error().decode(errors="replace"))
-            mine = torch.from_numpy(np.frombuffer(hb, dtype=np.uint8).copy())
-            on_dev = dist.get_backend(group) == "nccl"
-            mine = mine.to(dev) if on_dev else mine
-            everyone = torch.empty(world * 64, dtype=torch.uint8, device=mine.device)
-            dist.all_gather_into_tensor(everyone, mine, group=group)
-            if self._lib.redcuda_ep_attach_peers(self._h, everyone.cpu().numpy().tobytes()) != 1:
-                raise RedcudaError(self._lib.redcuda_last_error().decode(errors="replace"))
-            dist.barrier(group=group)          # nobody steps before every rank has mapped every area
-            self.exchange = "peer"
         n = len(shards)
         self._layers = (C.c_void_p * n)(*[m.handle for m in shards])
         self.out = torch.empty(n, tokens, d.hidden, dtype=torch.float32, device=dev)
@@ -275,8 +296,5 @@ class EpStep:
 
     def close(self):
         if self._h:
-            if self.world > 1:
-                torch.cuda.synchronize()
-                dist.barrier(group=self._group)    # other ranks may still be writing into this rank's exchange area
-            self._lib.redcuda_ep_destroy(self._h)
+            self.ctx.close()
             self._h = None

@@ -163,6 +163,20 @@ int redcuda_ep_attach_peers(redcuda_ep *ep, const void *handles);
 redcuda_ep *redcuda_ep_create(int rank, int world, const void *unique_id128, uint32_t tokens, uint32_t hidden, uint32_t top_k);
 void redcuda_ep_destroy(redcuda_ep *ep);
 int redcuda_ep_layer_forward(redcuda_ep *ep, redcuda_moe *layer, const float *x_dev, const float *logits_in_dev, float *out_dev, void *stream);
+/* The same for ntok <= tokens tokens (the same ntok on every rank) with an optional residual: out = resid + routed + shared.
+ * last_ids_device: the router ids [ntok][top_k] of the rank's own tokens from the last call (device memory). */
+int redcuda_ep_layer_forward_n(redcuda_ep *ep, redcuda_moe *layer, uint32_t ntok, const float *x_dev, const float *logits_in_dev, const float *resid_dev,
+                               float *out_dev, void *stream);
+const uint32_t *redcuda_ep_last_ids_device(const redcuda_ep *ep);
+/* The engine under expert parallelism (config 4 across GPUs; no reference counterpart): every rank runs its own sequences
+ * through its own engine, which holds the dense weights and a contiguous share of every layer's experts.
+ * redcuda_engine_shard(rank, world) sets that share for the engines this thread opens next (rank 0 of 1 = everything);
+ * redcuda_engine_attach_ep hands the engine an exchange context created with tokens >= the prefill chunk (not owned by the
+ * engine; every rank must make the same sequence of prefill / step calls with the same token counts).
+ * rl_engine_generate_greedy is refused on a sharded engine. */
+struct rl_engine;
+int redcuda_engine_shard(int rank, int world);
+int redcuda_engine_attach_ep(struct rl_engine *e, redcuda_ep *ep);
 int redcuda_ep_step(redcuda_ep *ep, redcuda_moe *const *layers, uint32_t n_layers, const float *const *x_dev, const float *const *logits_in_dev,
                     float *const *out_dev, void *stream);
 
