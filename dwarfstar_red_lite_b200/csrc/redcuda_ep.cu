@@ -86,7 +86,7 @@ static NcclApi *nccl_api() {
 
 #define RC_NCCL(api, expr) do { ncclResult_t r_ = (expr); if (r_ != 0) { rc::set_error("%s failed: %s", #expr, (api)->GetErrorString(r_)); return 0; } } while (0)
 
-bool moe_takes_digits(const redcuda_moe *m);                  // redcuda_moe.cu
+bool moe_takes_digits(redcuda_moe *m, uint32_t ntok);          // redcuda_moe.cu
 int moe_partial_gathered(redcuda_moe *m, uint32_t ntok, const float *x, const int8_t *xq, const float *sx, const uint32_t *ids, const float *w,
                          const float *add, uint32_t add_begin, uint32_t add_count, float *out, cudaStream_t s, const EpWait *wait, const EpPush *push);
 
@@ -287,7 +287,7 @@ int redcuda_ep_layer_forward_n(redcuda_ep *ep, redcuda_moe *layer, uint32_t ntok
     if (!redcuda_moe_shared_device(layer, T, x_dev, ep->shared, ep->side)) return 0;
     RC_CUDA(cudaEventRecord(ep->ev_join, ep->side));
     if (!redcuda_moe_route_device(layer, T, x_dev, logits_in_dev, ep->ids, ep->w, s)) return 0;
-    const bool digits = moe_takes_digits(layer);
+    const bool digits = moe_takes_digits(layer, W * T);
     if (digits && !launch_quant_act(x_dev, H, T, H, ep->xq, ep->sx, s)) return 0;
     if (W == 1u) {
         RC_CUDA(cudaStreamWaitEvent(s, ep->ev_join, 0));

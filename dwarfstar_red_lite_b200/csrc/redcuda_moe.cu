@@ -593,7 +593,11 @@ void moe_set_ids_mirror(redcuda_moe *m, uint32_t *dev_ptr) { m->ids_mirror = dev
 }
 namespace rc {
 // true when the routed experts read int8 activation digits (so a caller may quantise before an exchange and hand the digits in)
-bool moe_takes_digits(const redcuda_moe *m) { return moe_experts_mma(m); }
+// (for a call over ntok gathered tokens: the tcgen05 kernel of large chunks prepares its own fp16 digits from the fp32 rows)
+bool moe_takes_digits(redcuda_moe *m, uint32_t ntok) {
+    moe_choose_path(m, ntok * m->d.top_k, false);
+    return moe_experts_mma(m) && !m->tc_now;
+}
 // The shard's experts over gathered tokens: x [ntok][hidden] fp32, or (when xq is given) its digits xq [ntok][3][hidden] with
 // scales sx [ntok]; ids / w [ntok][top_k] contiguous. out [ntok][hidden] as k_ep_combine defines it.
 // wait (may be null): the grouping kernel first waits for the other ranks' rows (peer-memory exchange). push (may be

@@ -190,6 +190,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_experts(const __grid_const
         fail = 1u;
         return false;
     };
+    // the same for roles that are far ahead of their producer (drain, record fetch, gather): they sleep longer between polls,
+    // so that their spinning does not take issue slots from the decode warps and the MMA thread
+    auto wait_idle = [&](uint64_t *bar, uint32_t parity) -> bool {
+        if (fail) return false;
+        const uint32_t addr = smem_u32(bar);
+        for (uint32_t i = 0; i < TC_SPIN_LIMIT / 8u; ++i) {
+            uint32_t done;
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+            if (done) return true;
+            __nanosleep(256);
+        }
+        fail = 1u;
+        return false;
+    };
 
     if (warp == 0) {
         // ------------------------------------------------------------------ MMA issue
@@ -249,7 +264,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_experts(const __grid_const
         bool ok = true;
         for (uint32_t s = 0; s < nstage + AHEAD && ok; ++s) {
             if (s < nstage) {
-                if (s >= NB) ok = wait(&b_empty[s % NB], ((s / NB) - 1u) & 1u);
+                if (s >= NB) ok = wait_idle(&b_empty[s % NB], ((s / NB) - 1u) & 1u);
                 if (ok) issue(s); else asm volatile("cp.async.commit_group;" ::: "memory");
             } else asm volatile("cp.async.commit_group;" ::: "memory");
             if (s >= AHEAD) {
@@ -266,7 +281,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_experts(const __grid_const
         if (lane == 0) {
             uint32_t issued = 0u;
             for (uint32_t c = 0; c < nblk; ++c) {       // c counts the CTA's blocks: tile c / bpr, block column c % bpr
-                if (c >= 2u && !wait(&raw_empty[c & 1u], ((c >> 1) - 1u) & 1u)) break;
+                if (c >= 2u && !wait_idle(&raw_empty[c & 1u], ((c >> 1) - 1u) & 1u)) break;
                 const uint32_t tile = c / bpr, col = c - tile * bpr;
                 const uint32_t bar = smem_u32(&raw_full[c & 1u]), dst = smem_u32(raw_base + (c & 1u) * TCX_RAW);
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(TCX_RAW) : "memory");
@@ -316,7 +331,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_experts(const __grid_const
         for (uint32_t j = 0; j < (uint32_t)TN; ++j) acc[j] = 0.f;
         bool ok = true;
         for (uint32_t blk = 0; blk < nblk && ok; ++blk) {
-            ok = wait(&acc_full[blk & 1u], (blk >> 1) & 1u);
+            ok = wait_idle(&acc_full[blk & 1u], (blk >> 1) & 1u);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             
