@@ -611,8 +611,10 @@ int redcuda_set_codebooks(const uint8_t *iq2xxs_grid, uint32_t iq2xxs_bytes, con
 }
 
 int redcuda_quant_dequant_rows(uint32_t type, const uint8_t *rows, uint32_t nrows, uint32_t ncols, float *out) {
-    if (!require_device() || !require_books(type)) return 0;
+    if (!require_device()) return 0;
     RC_REQUIRE(rows && out && nrows && ncols, "dequant: null or empty argument");
+    if (kq_supported(type)) return kq_dequant_rows(type, rows, nrows, ncols, out);      // Q8_0 / Q2_K / Q4_K / Q5_K: redcuda_kquants.cu
+    if (!require_books(type)) return 0;
     RC_REQUIRE(rc_type_supported(type), "dequant: unsupported ggml type %u", type);
     const uint64_t bytes = rc_matrix_bytes(type, nrows, ncols);
     RC_REQUIRE(bytes, "dequant: %u columns is not a valid row length for type %u", ncols, type);
@@ -637,8 +639,10 @@ int redcuda_quant_dequant_rows(uint32_t type, const uint8_t *rows, uint32_t nrow
 }
 
 int redcuda_quant_matvec(uint32_t type, const uint8_t *w, uint32_t nrows, uint32_t ncols, const float *x, uint32_t ntok, float *out) {
-    if (!require_device() || !require_books(type)) return 0;
+    if (!require_device()) return 0;
     RC_REQUIRE(w && x && out && nrows && ncols && ntok, "matvec: null or empty argument");
+    if (kq_supported(type)) return kq_matvec(type, w, nrows, ncols, x, ntok, out);
+    if (!require_books(type)) return 0;
     RC_REQUIRE(rc_type_supported(type), "matvec: unsupported ggml type %u", type);
     const uint64_t bytes = rc_matrix_bytes(type, nrows, ncols);
     RC_REQUIRE(bytes, "matvec: %u columns is not a valid row length for type %u", ncols, type);

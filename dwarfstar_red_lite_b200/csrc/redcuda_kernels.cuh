@@ -121,6 +121,11 @@ template <typename KV>
 int launch_attn_chunk(const float *query, const KV *kc, const KV *vc, uint32_t n_kv, uint32_t G, uint32_t hd, const uint32_t *pos, uint32_t ntok, float scale,
                       const float *gate, float *gated, cudaStream_t s);
 
+// Q8_0 / Q2_K / Q4_K / Q5_K rows in their GGUF layout (redcuda_kquants.cu): host-pointer dequantisation and matvec
+bool kq_supported(uint32_t ggml_type);
+int kq_dequant_rows(uint32_t type, const uint8_t *rows, uint32_t nrows, uint32_t ncols, float *out);
+int kq_matvec(uint32_t type, const uint8_t *w, uint32_t nrows, uint32_t ncols, const float *x, uint32_t ntok, float *out);
+
 int launch_vec_sigmoid(const float *w, const float *x, uint32_t x_stride, uint32_t ncols, uint32_t ntok, float *out, cudaStream_t stream);
 // logits[t][e] = dot(w[e], x[t]) accumulated in double, F32 weights [n_expert][ncols]; for batches (tiled fp64 GEMM)
 int launch_router_logits(const float *w, const float *x, uint32_t x_stride, uint32_t ntok, uint32_t n_expert, uint32_t ncols, float *logits, cudaStream_t stream);

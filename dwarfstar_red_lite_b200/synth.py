@@ -12,8 +12,11 @@ from dataclasses import dataclass, field
 import numpy as np
 
 F32, F16, Q6_K, IQ2_XXS, IQ3_S = 0, 1, 14, 16, 21
-BLOCK_BYTES = {Q6_K: 210, IQ2_XXS: 66, IQ3_S: 110}
-D_OFFSET = {Q6_K: 208, IQ2_XXS: 0, IQ3_S: 0}
+Q8_0, Q2_K, Q4_K, Q5_K = 8, 10, 12, 13          # further GGUF types served by the stage entry points (dequantise, matvec)
+BLOCK_BYTES = {Q6_K: 210, IQ2_XXS: 66, IQ3_S: 110, Q8_0: 34, Q2_K: 84, Q4_K: 144, Q5_K: 176}
+BLOCK_VALUES = {Q8_0: 32}                        # every other block holds 256 values
+D_OFFSET = {Q6_K: 208, IQ2_XXS: 0, IQ3_S: 0, Q8_0: 0, Q2_K: 80, Q4_K: 0, Q5_K: 0}
+DMIN_OFFSET = {Q2_K: 82, Q4_K: 2, Q5_K: 2}       # second fp16 scale (of the block minimum)
 
 
 def row_bytes(ggml_type: int, ncols: int) -> int:
@@ -21,9 +24,10 @@ def row_bytes(ggml_type: int, ncols: int) -> int:
         return ncols * 4
     if ggml_type == F16:
         return ncols * 2
-    if ncols % 256:
-        raise ValueError("quantised rows hold a multiple of 256 values")
-    return ncols // 256 * BLOCK_BYTES[ggml_type]
+    bv = BLOCK_VALUES.get(ggml_type, 256)
+    if ncols % bv:
+        raise ValueError(f"quantised rows of type {ggml_type} hold a multiple of {bv} values")
+    return ncols // bv * BLOCK_BYTES[ggml_type]
 
 
 def quant_matrix(rng: np.random.Generator, ggml_type: int, nrows: int, ncols: int, d_lo: float, d_hi: float,
@@ -31,16 +35,20 @@ def quant_matrix(rng: np.random.Generator, ggml_type: int, nrows: int, ncols: in
     """uint8 [nrows, row_bytes]: random payload bytes, fp16 block scale d ~ U(d_lo, d_hi).
 
     For Q6_K the 16 int8 sub-block scales are drawn from sub_scale_range (default the full int8 range)."""
-    nb = nrows * (ncols // 256)
+    bv = BLOCK_VALUES.get(ggml_type, 256)
+    nb = nrows * (ncols // bv)
     bb = BLOCK_BYTES[ggml_type]
     blocks = np.frombuffer(rng.bytes(nb * bb), dtype=np.uint8).reshape(nb, bb).copy()     # random payload bytes (fast path of the generator)
     d = rng.uniform(d_lo, d_hi, size=nb).astype(np.float16)
     off = D_OFFSET[ggml_type]
     blocks[:, off:off + 2] = d.view(np.uint8).reshape(nb, 2)
+    if ggml_type in DMIN_OFFSET:
+        off = DMIN_OFFSET[ggml_type]
+        blocks[:, off:off + 2] = rng.uniform(d_lo, d_hi, size=nb).astype(np.float16).view(np.uint8).reshape(nb, 2)
     if ggml_type == Q6_K and sub_scale_range is not None:
         lo, hi = sub_scale_range
         blocks[:, 192:208] = rng.integers(lo, hi + 1, size=(nb, 16)).astype(np.int8).view(np.uint8)
-    return blocks.reshape(nrows, (ncols // 256) * bb)
+    return blocks.reshape(nrows, (ncols // bv) * bb)
 
 
 @dataclass

@@ -46,7 +46,10 @@ int redcuda_set_codebooks(const uint8_t *iq2xxs_grid, uint32_t iq2xxs_bytes, con
  * Stage entry points (host pointers, synchronous). Each replaces one CPU reference function of the path.
  * ---------------------------------------------------------------------------------------------------------- */
 
-/* rl_quant_dequant_row (native/redlite_native_quant_cpu.c:155-196) for nrows rows at once: out[nrows][ncols]. */
+/* rl_quant_dequant_row (native/redlite_native_quant_cpu.c:155-196) for nrows rows at once: out[nrows][ncols].
+ * ggml types: 0 F32, 1 F16, 14 Q6_K, 16 IQ2_XXS, 21 IQ3_S (the types of the decode path), and 8 Q8_0, 10 Q2_K, 12 Q4_K,
+ * 13 Q5_K (cases 8 / 10 / 12 / 13 of the same reference function, :50-128), which this entry point and redcuda_quant_matvec
+ * serve but the engine and the expert kernels do not yet. Values are bit-identical to the reference's. */
 int redcuda_quant_dequant_rows(uint32_t ggml_type, const uint8_t *rows, uint32_t nrows, uint32_t ncols, float *out);
 
 /* The same values through the layout the routed IQ2_XXS experts are kept in (4-bit magnitude/sign codes, byte scales;

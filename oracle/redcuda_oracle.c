@@ -70,6 +70,10 @@ size_t ro_row_bytes(uint32_t type, uint32_t ncols) {
     switch (type) {
         case 0: return (size_t)ncols * 4u;
         case 1: return (size_t)ncols * 2u;
+        case 8: return ncols % 32u ? 0 : (size_t)(ncols / 32u) * 34u;           /* Q8_0 */
+        case 10: return ncols % QK ? 0 : (size_t)(ncols / QK) * 84u;            /* Q2_K */
+        case 12: return ncols % QK ? 0 : (size_t)(ncols / QK) * 144u;           /* Q4_K */
+        case 13: return ncols % QK ? 0 : (size_t)(ncols / QK) * 176u;           /* Q5_K */
         case 14: return ncols % QK ? 0 : (size_t)(ncols / QK) * Q6_K_BLOCK;
         case 16: return ncols % QK ? 0 : (size_t)(ncols / QK) * IQ2_XXS_BLOCK;
         case 21: return ncols % QK ? 0 : (size_t)(ncols / QK) * IQ3_S_BLOCK;
@@ -95,11 +99,59 @@ static void iq3s_group8(const uint8_t *bp, uint32_t g, float out[8]) {
     }
 }
 
+/* ---- the GGUF types beyond the decode path's three (quant_cpu.c:40-129): value j of one block, the float operations in
+ * the reference's order. Used by the dequantiser and (widened to double as the reference does) by the row dot. ---- */
+/* quant_cpu.c:40-46 — the packed 6-bit scale / min pairs of Q4_K and Q5_K */
+static void k4_scale_min(uint32_t j, const uint8_t *q, uint32_t *d, uint32_t *m) {
+    if (j < 4u) { *d = q[j] & 63u; *m = q[j + 4u] & 63u; }
+    else { *d = (q[j + 4u] & 0x0fu) | ((uint32_t)(q[j - 4u] >> 6) << 4); *m = (uint32_t)(q[j + 4u] >> 4) | ((uint32_t)(q[j] >> 6) << 4); }
+}
+/* integer code, scale and min factors of value j of a block: w = dscale * sc * q - dmin * mn  (Q8_0: mn = 0, sc = 1) */
+typedef struct { float d, dmin; uint32_t sc, mn; int q; } kq_parts;
+static kq_parts kq_split(uint32_t type, const uint8_t *bp, uint32_t j) {
+    kq_parts r = {0.f, 0.f, 1u, 0u, 0};
+    if (type == 8u) {                    /* quant_cpu.c:50-57: [d f16][32 x int8] */
+        r.d = ro_f16_to_f32(rd16(bp)); r.q = (int)(int8_t)bp[2u + j];
+    } else if (type == 10u) {            /* quant_cpu.c:59-82: [16 scale/min nibbles][64 x 2-bit quads][d][dmin] */
+        const uint32_t half = j / 128u, r128 = j % 128u, sub = r128 / 32u, l32 = r128 % 32u;
+        const uint8_t scb = bp[half * 8u + sub * 2u + l32 / 16u];
+        r.d = ro_f16_to_f32(rd16(bp + 80u)); r.dmin = ro_f16_to_f32(rd16(bp + 82u));
+        r.sc = scb & 0xFu; r.mn = scb >> 4;
+        r.q = (int)((bp[16u + half * 32u + l32] >> (2u * sub)) & 3u);
+    } else if (type == 12u) {            /* quant_cpu.c:84-103: [d][dmin][12 scale bytes][128 nibble bytes] */
+        const uint32_t g = j / 32u, l = j % 32u;
+        r.d = ro_f16_to_f32(rd16(bp)); r.dmin = ro_f16_to_f32(rd16(bp + 2u));
+        k4_scale_min(g, bp + 4u, &r.sc, &r.mn);
+        const uint8_t b = bp[16u + (g / 2u) * 32u + l];
+        r.q = (int)((g & 1u) ? (b >> 4) : (b & 0x0fu));
+    } else {                             /* 13, quant_cpu.c:105-128: [d][dmin][12 scale bytes][32 high-bit bytes][128 nibble bytes] */
+        const uint32_t g = j / 32u, l = j % 32u;
+        r.d = ro_f16_to_f32(rd16(bp)); r.dmin = ro_f16_to_f32(rd16(bp + 2u));
+        k4_scale_min(g, bp + 4u, &r.sc, &r.mn);
+        const uint8_t b = bp[48u + (g / 2u) * 32u + l];
+        const uint32_t hi = (bp[16u + l] >> g) & 1u;
+        r.q = (int)(((g & 1u) ? (b >> 4) : (b & 0x0fu)) + (hi ? 16u : 0u));
+    }
+    return r;
+}
+static uint32_t kq_block_values(uint32_t type) { return type == 8u ? 32u : QK; }
+static uint32_t kq_block_bytes(uint32_t type) { return type == 8u ? 34u : type == 10u ? 84u : type == 12u ? 144u : 176u; }
+
 int ro_dequant_row(uint32_t type, const uint8_t *row, uint32_t ncols, float *out) {
     if (!row || !out || !ncols) return 0;
     switch (type) {
         case 0: memcpy(out, row, (size_t)ncols * 4u); return 1;
         case 1: for (uint32_t i = 0; i < ncols; ++i) out[i] = ro_f16_to_f32(rd16(row + 2u * i)); return 1;
+        case 8: case 10: case 12: case 13: {
+            const uint32_t bv = kq_block_values(type);
+            if (ncols % bv) return 0;
+            for (uint32_t i = 0; i < ncols; ++i) {
+                const kq_parts p = kq_split(type, row + (size_t)(i / bv) * kq_block_bytes(type), i % bv);
+                if (type == 8u) out[i] = p.d * (float)p.q;                                    /* d * q */
+                else out[i] = p.d * (float)p.sc * (float)p.q - p.dmin * (float)p.mn;          /* (d * sc) * q - (dmin * mn), float */
+            }
+            return 1;
+        }
         case 14: {   /* quant_cpu.c:130-153 */
             if (ncols % QK) return 0;
             for (uint32_t ib = 0; ib < ncols / QK; ++ib) {
@@ -163,6 +215,27 @@ static int row_dot_any(uint32_t type, const uint8_t *row, const float *xf, const
     switch (type) {
         case 0: { const float *w = (const float *)row; for (uint32_t i = 0; i < ncols; ++i) acc += (double)w[i] * xin(xf, xd, i); break; }
         case 1: for (uint32_t i = 0; i < ncols; ++i) acc += (double)ro_f16_to_f32(rd16(row + 2u * i)) * xin(xf, xd, i); break;
+        case 8:      /* quant_cpu.c:205-214: x * d * q in double */
+            if (ncols % 32u) return 0;
+            for (uint32_t i = 0; i < ncols; ++i) {
+                const kq_parts p = kq_split(8u, row + (size_t)(i / 32u) * 34u, i % 32u);
+                acc += xin(xf, xd, i) * (double)p.d * (double)p.q;
+            }
+            break;
+        case 12: case 13:   /* quant_cpu.c:215-256: x * (d * sc * q - dmin * mn), the weight formed in double */
+            if (ncols % QK) return 0;
+            for (uint32_t i = 0; i < ncols; ++i) {
+                const kq_parts p = kq_split(type, row + (size_t)(i / QK) * kq_block_bytes(type), i % QK);
+                acc += xin(xf, xd, i) * ((double)p.d * p.sc * (double)p.q - (double)p.dmin * p.mn);
+            }
+            break;
+        case 10:     /* quant_cpu.c:257-265: the fp32 dequantised value times x */
+            if (ncols % QK) return 0;
+            for (uint32_t i = 0; i < ncols; ++i) {
+                const kq_parts p = kq_split(10u, row + (size_t)(i / QK) * 84u, i % QK);
+                acc += (double)(p.d * (float)p.sc * (float)p.q - p.dmin * (float)p.mn) * xin(xf, xd, i);
+            }
+            break;
         case 14: {   /* shared_exec.c:78-112 — weight formed in double */
             if (ncols % QK) return 0;
             for (uint32_t ib = 0; ib < ncols / QK; ++ib) {
