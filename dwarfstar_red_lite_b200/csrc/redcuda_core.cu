@@ -131,7 +131,7 @@ int upload_matrix(uint32_t type, uint32_t nrows, uint32_t ncols, const void *src
     RC_REQUIRE(bytes != 0, "matrix %ux%u of type %u has no valid row size", nrows, ncols, type);
     RC_REQUIRE(((uintptr_t)dst & 15u) == 0, "matrix destination is not 16-byte aligned");
     if (!rc_is_quant(type)) {
-        RC_REQUIRE(ncols % 64u == 0, "F32/F16 matrices need a row length that is a multiple of 64 (got %u)", ncols);
+        RC_REQUIRE(ncols % 64u == 0, "F32 / F16 / file-layout matrices need a row length that is a multiple of 64 (got %u)", ncols);
         RC_CUDA(cudaMemcpyAsync(dst, src, bytes, src_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, stream));
         return 1;
     }
@@ -297,6 +297,10 @@ __global__ void __launch_bounds__(256) k_gemv(const __grid_constant__ GemvArgs A
             case RC_Q6_K: gemv_tile<RC_Q6_K, NT>(J, row0, nt, tok0, A.ntok, xs, xstride, sb); break;
             case RC_IQ2_XXS: gemv_tile<RC_IQ2_XXS, NT>(J, row0, nt, tok0, A.ntok, xs, xstride, sb); break;
             case RC_IQ3_S: gemv_tile<RC_IQ3_S, NT>(J, row0, nt, tok0, A.ntok, xs, xstride, sb); break;
+            case RC_Q8_0: gemv_tile<RC_Q8_0, NT>(J, row0, nt, tok0, A.ntok, xs, xstride, sb); break;
+            case RC_Q2_K: gemv_tile<RC_Q2_K, NT>(J, row0, nt, tok0, A.ntok, xs, xstride, sb); break;
+            case RC_Q4_K: gemv_tile<RC_Q4_K, NT>(J, row0, nt, tok0, A.ntok, xs, xstride, sb); break;
+            case RC_Q5_K: gemv_tile<RC_Q5_K, NT>(J, row0, nt, tok0, A.ntok, xs, xstride, sb); break;
             default: break;
         }
     }

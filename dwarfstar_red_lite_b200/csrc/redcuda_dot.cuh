@@ -11,6 +11,7 @@
 // working on different chunks hit different bank groups with their float4 reads.
 #pragma once
 #include "redcuda_formats.cuh"
+#include "redcuda_kquants.cuh"
 
 namespace rc {
 
@@ -178,7 +179,25 @@ template <int TYPE, int NT>
 __device__ __forceinline__ void row_dot(const uint8_t *base, uint64_t nb, uint64_t row, uint32_t ncols, uint32_t lpr, uint32_t sub,
                                         const float *xs, uint32_t xstride, const SBooks &sb, float (&out)[NT]) {
     const uint32_t cpr = ncols >> 6;
-    if (TYPE == RC_F32 || TYPE == RC_F16) {
+    if (TYPE == RC_Q8_0 || TYPE == RC_Q2_K || TYPE == RC_Q4_K || TYPE == RC_Q5_K) {
+        // rows in file layout, a value at a time: correct for every type of the family, not tuned
+        float acc[NT];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) acc[t] = 0.f;
+        const uint8_t *rp = base + row * rc_row_bytes(TYPE, ncols);
+        for (uint32_t c = sub; c < cpr; c += lpr)
+            for (uint32_t j = 0; j < 64u; ++j) {
+                const uint32_t k = c * 64u + j;
+                const float w = kq_row_value(TYPE, rp, k);
+#pragma unroll
+                for (int t = 0; t < NT; ++t) acc[t] = fmaf(w, xs[t * xstride + xi(k)], acc[t]);
+            }
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            for (uint32_t o = lpr >> 1; o; o >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
+            out[t] = acc[t];
+        }
+    } else if (TYPE == RC_F32 || TYPE == RC_F16) {
         double acc[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) acc[t] = 0.0;

@@ -8,6 +8,7 @@
 // at the end of the step together with the logits.
 #include "redcuda_common.cuh"
 #include "redcuda_kernels.cuh"
+#include "redcuda_kquants.cuh"
 #include "redcuda_moe_mma.cuh"
 #include "redcuda_tc_gemm.cuh"
 #include "redcuda_gguf.h"
@@ -42,6 +43,11 @@ __global__ void k_embed_row(const uint8_t *__restrict__ base, uint32_t type, uin
     out += (size_t)blockIdx.x * ncols;
     if (type == RC_F32) { for (uint32_t i = threadIdx.x; i < ncols; i += blockDim.x) out[i] = reinterpret_cast<const float *>(base)[row * ncols + i]; return; }
     if (type == RC_F16) { for (uint32_t i = threadIdx.x; i < ncols; i += blockDim.x) out[i] = __half2float(__ushort_as_half(reinterpret_cast<const unsigned short *>(base)[row * ncols + i])); return; }
+    if (rc_is_file_layout_quant(type)) {
+        const uint8_t *rp = base + row * rc_row_bytes(type, ncols);
+        for (uint32_t i = threadIdx.x; i < ncols; i += blockDim.x) out[i] = kq_row_value(type, rp, i);
+        return;
+    }
     const RcBooks bk{iq2, iq3s};
     const uint32_t bpr = ncols >> 8;
     for (uint32_t g = threadIdx.x; g < bpr * 32u; g += blockDim.x) {

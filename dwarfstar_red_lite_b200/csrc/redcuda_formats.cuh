@@ -25,14 +25,18 @@
 #define RC_HD static inline      /* plain C++ build: the host unit test of the layout and the decoders */
 #endif
 
-enum RcType : uint32_t { RC_F32 = 0u, RC_F16 = 1u, RC_Q6_K = 14u, RC_IQ2_XXS = 16u, RC_IQ3_S = 21u };
+enum RcType : uint32_t { RC_F32 = 0u, RC_F16 = 1u, RC_Q6_K = 14u, RC_IQ2_XXS = 16u, RC_IQ3_S = 21u,
+                         RC_Q8_0 = 8u, RC_Q2_K = 10u, RC_Q4_K = 12u, RC_Q5_K = 13u };      // the last four: kept in file layout (redcuda_kquants.cuh), dense matrices only
 
 RC_HD uint32_t rc_block_bytes(uint32_t t) { return t == RC_Q6_K ? 210u : t == RC_IQ2_XXS ? 66u : t == RC_IQ3_S ? 110u : 0u; }
 RC_HD bool rc_is_quant(uint32_t t) { return rc_block_bytes(t) != 0u; }
-RC_HD bool rc_type_supported(uint32_t t) { return t == RC_F32 || t == RC_F16 || rc_is_quant(t); }
+RC_HD bool rc_is_file_layout_quant(uint32_t t) { return t == RC_Q8_0 || t == RC_Q2_K || t == RC_Q4_K || t == RC_Q5_K; }
+RC_HD bool rc_type_supported(uint32_t t) { return t == RC_F32 || t == RC_F16 || rc_is_quant(t) || rc_is_file_layout_quant(t); }
 RC_HD uint64_t rc_row_bytes(uint32_t t, uint32_t ncols) {
     if (t == RC_F32) return (uint64_t)ncols * 4u;
     if (t == RC_F16) return (uint64_t)ncols * 2u;
+    if (t == RC_Q8_0) return (ncols % 32u) ? 0u : (uint64_t)(ncols / 32u) * 34u;
+    if (rc_is_file_layout_quant(t)) return (ncols % 256u) ? 0u : (uint64_t)(ncols / 256u) * (t == RC_Q2_K ? 84u : t == RC_Q4_K ? 144u : 176u);
     return (ncols % 256u) ? 0u : (uint64_t)(ncols / 256u) * rc_block_bytes(t);
 }
 RC_HD uint64_t rc_matrix_bytes(uint32_t t, uint32_t nrows, uint32_t ncols) { return rc_row_bytes(t, ncols) * nrows; }

@@ -62,6 +62,10 @@ public:
         switch (type) {
             case 0: row = n0 * 4u; break;
             case 1: row = n0 * 2u; break;
+            case 8: if (n0 % 32u) return 0; row = n0 / 32u * 34u; break;          // Q8_0
+            case 10: if (n0 % 256u) return 0; row = n0 / 256u * 84u; break;       // Q2_K
+            case 12: if (n0 % 256u) return 0; row = n0 / 256u * 144u; break;      // Q4_K
+            case 13: if (n0 % 256u) return 0; row = n0 / 256u * 176u; break;      // Q5_K
             case 14: if (n0 % 256u) return 0; row = n0 / 256u * 210u; break;
             case 16: if (n0 % 256u) return 0; row = n0 / 256u * 66u; break;
             case 21: if (n0 % 256u) return 0; row = n0 / 256u * 110u; break;

@@ -6,47 +6,14 @@
 // they are served for dequantisation and matrix-vector products, not yet by the engine or the expert kernels.
 #include "redcuda_common.cuh"
 #include "redcuda_kernels.cuh"
+#include "redcuda_kquants.cuh"
 
 #include <cuda_fp16.h>
 
 namespace rc {
 
-enum : uint32_t { KQ_Q8_0 = 8u, KQ_Q2_K = 10u, KQ_Q4_K = 12u, KQ_Q5_K = 13u };
-
-bool kq_supported(uint32_t t) { return t == KQ_Q8_0 || t == KQ_Q2_K || t == KQ_Q4_K || t == KQ_Q5_K; }
-__host__ __device__ __forceinline__ uint32_t kq_block_values(uint32_t t) { return t == KQ_Q8_0 ? 32u : 256u; }
-__host__ __device__ __forceinline__ uint32_t kq_block_bytes(uint32_t t) { return t == KQ_Q8_0 ? 34u : t == KQ_Q2_K ? 84u : t == KQ_Q4_K ? 144u : 176u; }
+bool kq_supported(uint32_t t) { return kq_type(t); }
 uint64_t kq_row_bytes(uint32_t t, uint32_t ncols) { return ncols % kq_block_values(t) ? 0u : (uint64_t)(ncols / kq_block_values(t)) * kq_block_bytes(t); }
-
-__device__ __forceinline__ float kq_f16(const uint8_t *p) { return __half2float(__ushort_as_half((unsigned short)(p[0] | (p[1] << 8)))); }
-// the packed 6-bit scale / min pairs of Q4_K and Q5_K (quant_cpu.c:40-46)
-__device__ __forceinline__ void kq_scale_min(uint32_t j, const uint8_t *q, uint32_t &d, uint32_t &m) {
-    if (j < 4u) { d = q[j] & 63u; m = q[j + 4u] & 63u; }
-    else { d = (q[j + 4u] & 0x0fu) | ((uint32_t)(q[j - 4u] >> 6) << 4); m = (uint32_t)(q[j + 4u] >> 4) | ((uint32_t)(q[j] >> 6) << 4); }
-}
-// value j of the block at bp: (d * sc) * q - (dmin * mn), every operation rounded on its own
-__device__ __forceinline__ float kq_value(uint32_t t, const uint8_t *bp, uint32_t j) {
-    if (t == KQ_Q8_0) return __fmul_rn(kq_f16(bp), (float)(int)(int8_t)bp[2u + j]);
-    float d, dmin; uint32_t sc, mn, q;
-    if (t == KQ_Q2_K) {
-        const uint32_t half = j >> 7, r = j & 127u, sub = r >> 5, l = r & 31u;
-        const uint32_t scb = bp[half * 8u + sub * 2u + (l >> 4)];
-        d = kq_f16(bp + 80u); dmin = kq_f16(bp + 82u); sc = scb & 0xFu; mn = scb >> 4;
-        q = (bp[16u + half * 32u + l] >> (2u * sub)) & 3u;
-    } else {
-        const uint32_t g = j >> 5, l = j & 31u;
-        d = kq_f16(bp); dmin = kq_f16(bp + 2u);
-        kq_scale_min(g, bp + 4u, sc, mn);
-        if (t == KQ_Q4_K) {
-            const uint32_t b = bp[16u + (g >> 1) * 32u + l];
-            q = (g & 1u) ? (b >> 4) : (b & 0x0fu);
-        } else {
-            const uint32_t b = bp[48u + (g >> 1) * 32u + l];
-            q = ((g & 1u) ? (b >> 4) : (b & 0x0fu)) + (((bp[16u + l] >> g) & 1u) ? 16u : 0u);
-        }
-    }
-    return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)mn));
-}
 
 // out[r][c] for GGUF rows; one thread per value
 __global__ void __launch_bounds__(256) k_kq_dequant(const uint8_t *__restrict__ rows, uint32_t type, uint64_t row_bytes, uint32_t ncols, uint64_t total, float *__restrict__ out) {

@@ -17,6 +17,7 @@ BLOCK_BYTES = {Q6_K: 210, IQ2_XXS: 66, IQ3_S: 110, Q8_0: 34, Q2_K: 84, Q4_K: 144
 BLOCK_VALUES = {Q8_0: 32}                        # every other block holds 256 values
 D_OFFSET = {Q6_K: 208, IQ2_XXS: 0, IQ3_S: 0, Q8_0: 0, Q2_K: 80, Q4_K: 0, Q5_K: 0}
 DMIN_OFFSET = {Q2_K: 82, Q4_K: 2, Q5_K: 2}       # second fp16 scale (of the block minimum)
+DMIN_FACTOR = {Q2_K: 1.5, Q4_K: 7.5, Q5_K: 15.5}  # dmin ~ d x the mean code, so that d*sc*q - dmin*mn is centred on zero
 
 
 def row_bytes(ggml_type: int, ncols: int) -> int:
@@ -44,7 +45,8 @@ def quant_matrix(rng: np.random.Generator, ggml_type: int, nrows: int, ncols: in
     blocks[:, off:off + 2] = d.view(np.uint8).reshape(nb, 2)
     if ggml_type in DMIN_OFFSET:
         off = DMIN_OFFSET[ggml_type]
-        blocks[:, off:off + 2] = rng.uniform(d_lo, d_hi, size=nb).astype(np.float16).view(np.uint8).reshape(nb, 2)
+        f = DMIN_FACTOR[ggml_type]
+        blocks[:, off:off + 2] = rng.uniform(d_lo * f, d_hi * f, size=nb).astype(np.float16).view(np.uint8).reshape(nb, 2)
     if ggml_type == Q6_K and sub_scale_range is not None:
         lo, hi = sub_scale_range
         blocks[:, 192:208] = rng.integers(lo, hi + 1, size=(nb, 16)).astype(np.int8).view(np.uint8)
@@ -85,6 +87,14 @@ def expert_d_range(ggml_type: int, scale: float = 1.0) -> tuple[float, float]:
         return 5e-4 * scale, 2e-3 * scale
     if ggml_type == Q6_K:
         return 2e-5 * scale, 6e-5 * scale
+    if ggml_type == Q8_0:
+        return 1.5e-4 * scale, 4e-4 * scale
+    if ggml_type == Q4_K:
+        return 5e-5 * scale, 1.5e-4 * scale
+    if ggml_type == Q5_K:
+        return 2.5e-5 * scale, 7e-5 * scale
+    if ggml_type == Q2_K:
+        return 1e-3 * scale, 3e-3 * scale
     raise ValueError(ggml_type)
 
 

@@ -45,10 +45,10 @@ def _layer_errs(eng, om, n_layer):
     for l in range(n_layer):
         a, b = eng.layer_out(l), om.layer_out(l)
         errs.append(float(np.max(np.abs(a - b)) / np.max(np.abs(b))))
-        verdict = _ids_equal_or_near_tie(eng.router_ids(l), om.router_ids(l), om.router_logits(l))
-        if verdict == 2:
+        kind = _ids_equal_or_near_tie(eng.router_ids(l), om.router_ids(l), om.router_logits(l))
+        if kind == 2:
             bad_ids.append(l)
-        swaps += verdict == 1
+        swaps += kind == 1
     return errs, bad_ids, swaps
 
 

@@ -61,6 +61,33 @@ def test_tiny_model_stepwise(tmp_path, te, kv_f16, monkeypatch):
         eng.close()
 
 
+@pytest.mark.parametrize("td", [synth.Q4_K, synth.Q8_0, synth.Q5_K, synth.Q2_K])
+def test_tiny_model_with_file_layout_dense_types(tmp_path, td, monkeypatch):
+    """Dense matrices (embedding, projections, LM head) in further GGUF types, kept in file layout: decode steps and a
+    chunked prefill against the oracle. The routed and shared experts stay in the types their kernels are built for."""
+    monkeypatch.setenv("RL_KV_F16", "1")
+    dims = synth.tiny_model_dims(type_dense=td, n_layer=4)
+    sm = synth.model(300 + td, dims)
+    path = str(tmp_path / "tiny.gguf")
+    gguf_writer.write_gguf(path, sm)
+    eng = Engine(path, context=dims.context, prefill_batch=8)
+    om = ol.OracleModel(sm, kv_f16=True)
+    try:
+        emb = eng.embed_token(5)
+        want = ol.dequant_rows(td, sm.tensors["token_embd.weight"][2][5], dims.hidden)[0]
+        assert np.array_equal(emb.view(np.uint32), want.view(np.uint32))
+        tok = 3
+        for step in range(5):
+            tok = _compare_step(eng, om, dims, tok, step)
+        prompt = np.random.default_rng(6).integers(0, dims.vocab, 11).astype(np.uint32)
+        gl = eng.prefill(prompt)
+        for t in prompt:
+            ml = om.step(int(t), threads=os.cpu_count() or 1)
+        _compare_last(eng, om, dims, gl, ml, ("file layout", td))
+    finally:
+        eng.close()
+
+
 def test_tiny_model_greedy_60_tokens(tmp_path, monkeypatch):
     monkeypatch.setenv("RL_KV_F16", "1")
     dims = synth.tiny_model_dims(n_layer=8)
