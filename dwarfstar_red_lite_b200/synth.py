@@ -156,6 +156,7 @@ class ModelDims:
     full_attention_interval: int = 4
     context: int = 4096
     type_dense: int = Q6_K
+    type_shared: int = 0          # type of the shared expert's matrices; 0 = as type_dense
     type_experts: int = IQ2_XXS
 
     @property
@@ -228,13 +229,14 @@ def iter_model_tensors(seed: int, dims: ModelDims, expert_scale: float = 0.2):
             yield put(p + "ssm_a", F32, (dims.dt_rank,), (-np.exp(lr.normal(0.0, 0.5, size=dims.dt_rank))).astype(np.float32))
             yield put(p + "ssm_norm.weight", F32, (dims.d_state,), (1.0 + lr.normal(0, 0.1, dims.d_state)).astype(np.float32))
             yield put(p + "ssm_out.weight", td, (dims.d_inner, h), _dense(lr, td, h, dims.d_inner))
-        md = MoeDims(h, dims.n_expert, dims.top_k, dims.ffn, dims.ffn_sh, te, te, td)
+        ts = dims.type_shared or td
+        md = MoeDims(h, dims.n_expert, dims.top_k, dims.ffn, dims.ffn_sh, te, te, ts)
         ml = moe_layer(int(lr.integers(1 << 31)), md, expert_scale=expert_scale)
         yield put(p + "ffn_gate_inp.weight", F32, (h, dims.n_expert), ml.router)
         yield put(p + "ffn_gate_inp_shexp.weight", F32, (h,), ml.sh_gate_inp)
-        yield put(p + "ffn_gate_shexp.weight", td, (h, dims.ffn_sh), ml.sh_gate)
-        yield put(p + "ffn_up_shexp.weight", td, (h, dims.ffn_sh), ml.sh_up)
-        yield put(p + "ffn_down_shexp.weight", td, (dims.ffn_sh, h), ml.sh_down)
+        yield put(p + "ffn_gate_shexp.weight", ts, (h, dims.ffn_sh), ml.sh_gate)
+        yield put(p + "ffn_up_shexp.weight", ts, (h, dims.ffn_sh), ml.sh_up)
+        yield put(p + "ffn_down_shexp.weight", ts, (dims.ffn_sh, h), ml.sh_down)
         yield put(p + "ffn_gate_exps.weight", te, (h, dims.ffn, dims.n_expert), ml.gate)
         yield put(p + "ffn_up_exps.weight", te, (h, dims.ffn, dims.n_expert), ml.up)
         yield put(p + "ffn_down_exps.weight", te, (dims.ffn, h, dims.n_expert), ml.down)
@@ -266,8 +268,8 @@ def tensor_spec(dims: ModelDims) -> list:
                      (p + "ssm_dt.bias", F32, (dims.dt_rank,)), (p + "ssm_a", F32, (dims.dt_rank,)), (p + "ssm_norm.weight", F32, (dims.d_state,)),
                      (p + "ssm_out.weight", td, (dims.d_inner, h))]
         spec += [(p + "ffn_gate_inp.weight", F32, (h, dims.n_expert)), (p + "ffn_gate_inp_shexp.weight", F32, (h,)),
-                 (p + "ffn_gate_shexp.weight", td, (h, dims.ffn_sh)), (p + "ffn_up_shexp.weight", td, (h, dims.ffn_sh)),
-                 (p + "ffn_down_shexp.weight", td, (dims.ffn_sh, h)), (p + "ffn_gate_exps.weight", te, (h, dims.ffn, dims.n_expert)),
+                 (p + "ffn_gate_shexp.weight", dims.type_shared or td, (h, dims.ffn_sh)), (p + "ffn_up_shexp.weight", dims.type_shared or td, (h, dims.ffn_sh)),
+                 (p + "ffn_down_shexp.weight", dims.type_shared or td, (dims.ffn_sh, h)), (p + "ffn_gate_exps.weight", te, (h, dims.ffn, dims.n_expert)),
                  (p + "ffn_up_exps.weight", te, (h, dims.ffn, dims.n_expert)), (p + "ffn_down_exps.weight", te, (dims.ffn, h, dims.n_expert))]
     return spec
 

@@ -66,7 +66,7 @@ def test_tiny_model_with_file_layout_dense_types(tmp_path, td, monkeypatch):
     """Dense matrices (embedding, projections, LM head) in further GGUF types, kept in file layout: decode steps and a
     chunked prefill against the oracle. The routed and shared experts stay in the types their kernels are built for."""
     monkeypatch.setenv("RL_KV_F16", "1")
-    dims = synth.tiny_model_dims(type_dense=td, n_layer=4)
+    dims = synth.tiny_model_dims(type_dense=td, type_shared=synth.Q6_K, n_layer=4)
     sm = synth.model(300 + td, dims)
     path = str(tmp_path / "tiny.gguf")
     gguf_writer.write_gguf(path, sm)
