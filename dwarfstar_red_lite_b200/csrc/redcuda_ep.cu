@@ -276,6 +276,18 @@ int redcuda_ep_attach_peers(redcuda_ep *ep, const void *handles) {
     return 1;
 }
 
+// back to the NCCL exchange (a caller uses it when some other rank could not map the areas: all ranks must agree)
+int redcuda_ep_detach_peers(redcuda_ep *ep) {
+    RC_REQUIRE(ep, "ep detach: null argument");
+    if (!ep->attached) return 1;
+    RC_CUDA(cudaDeviceSynchronize());
+    for (uint32_t p = 0; p < ep->peers.world; ++p)
+        if ((int)p != ep->rank && ep->peers.base[p]) cudaIpcCloseMemHandle(ep->peers.base[p]);
+    ep->peers = EpPeers{};
+    ep->attached = false;
+    return 1;
+}
+
 int redcuda_ep_layer_forward_n(redcuda_ep *ep, redcuda_moe *layer, uint32_t ntok, const float *x_dev, const float *logits_in_dev, const float *resid_dev, float *out_dev, void *stream) {
     RC_REQUIRE(ep && layer && x_dev && out_dev, "ep layer: null argument");
     RC_REQUIRE(ntok >= 1u && ntok <= ep->tokens, "ep layer: %u tokens outside [1, %u]", ntok, ep->tokens);

@@ -241,9 +241,15 @@ class EpContext:
             mine = mine.to(dev) if on_dev else mine
             everyone = torch.empty(world * 64, dtype=torch.uint8, device=mine.device)
             dist.all_gather_into_tensor(everyone, mine, group=group)
-            check(self._lib.redcuda_ep_attach_peers(self.handle, everyone.cpu().numpy().tobytes()) == 1)
-            dist.barrier(group=group)          # nobody steps before every rank has mapped every area
-            self.exchange = "peer"
+            mapped = self._lib.redcuda_ep_attach_peers(self.handle, everyone.cpu().numpy().tobytes()) == 1
+            # every rank must use the same exchange: if one could not map the others' areas (IPC not permitted, no peer
+            # access), all fall back to NCCL. The all-reduce is also the barrier before the first step.
+            agreed = torch.tensor([1 if mapped else 0], dtype=torch.int32, device=dev if on_dev else "cpu")
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+            if int(agreed.item()) == 1:
+                self.exchange = "peer"
+            elif mapped:
+                check(self._lib.redcuda_ep_detach_peers(self.handle) == 1)
 
     def close(self):
         if self.handle:

@@ -21,7 +21,7 @@ EXPORTS = [
     "redcuda_moe_forward_device", "redcuda_moe_route_device", "redcuda_moe_experts_device", "redcuda_moe_shared_device",
     "redcuda_moe_combine_device", "redcuda_moe_partial_device",
     "redcuda_launch_count", "redcuda_profile_enable", "redcuda_profile_report",
-    "redcuda_ep_unique_id", "redcuda_ep_ipc_handle", "redcuda_ep_attach_peers", "redcuda_ep_create", "redcuda_ep_destroy", "redcuda_ep_layer_forward", "redcuda_ep_layer_forward_n", "redcuda_ep_last_ids_device", "redcuda_ep_step", "redcuda_engine_shard", "redcuda_engine_attach_ep",
+    "redcuda_ep_unique_id", "redcuda_ep_ipc_handle", "redcuda_ep_attach_peers", "redcuda_ep_detach_peers", "redcuda_ep_create", "redcuda_ep_destroy", "redcuda_ep_layer_forward", "redcuda_ep_layer_forward_n", "redcuda_ep_last_ids_device", "redcuda_ep_step", "redcuda_engine_shard", "redcuda_engine_attach_ep",
     # engine ABI (include/rl_engine.h)
     "rl_engine_config_default", "rl_engine_open", "rl_engine_close", "rl_engine_info_get", "rl_engine_reset", "rl_engine_position",
     "rl_engine_bench_set_position", "rl_engine_step", "rl_engine_prefill", "rl_engine_last_embedding", "rl_engine_last_layer_output",
@@ -84,6 +84,7 @@ def lib():
     L.redcuda_ep_unique_id.argtypes = [C.c_void_p]
     L.redcuda_ep_ipc_handle.argtypes = [C.c_void_p, C.c_void_p]
     L.redcuda_ep_attach_peers.argtypes = [C.c_void_p, C.c_void_p]
+    L.redcuda_ep_detach_peers.argtypes = [C.c_void_p]
     L.redcuda_ep_create.restype = C.c_void_p
     L.redcuda_ep_create.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32]
     L.redcuda_ep_destroy.argtypes = [C.c_void_p]

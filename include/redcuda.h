@@ -163,6 +163,7 @@ typedef struct redcuda_ep redcuda_ep;
 int redcuda_ep_unique_id(void *out128);
 int redcuda_ep_ipc_handle(redcuda_ep *ep, void *out64);
 int redcuda_ep_attach_peers(redcuda_ep *ep, const void *handles);
+int redcuda_ep_detach_peers(redcuda_ep *ep);      /* back to NCCL; every rank must do the same between steps */
 redcuda_ep *redcuda_ep_create(int rank, int world, const void *unique_id128, uint32_t tokens, uint32_t hidden, uint32_t top_k);
 void redcuda_ep_destroy(redcuda_ep *ep);
 int redcuda_ep_layer_forward(redcuda_ep *ep, redcuda_moe *layer, const float *x_dev, const float *logits_in_dev, float *out_dev, void *stream);
