@@ -285,19 +285,40 @@ __global__ void __launch_bounds__(256) k_dn_state_seq(DnDims D, uint32_t T, cons
         if (tb + 1u < nblk) stage(tb + 1u, buf ^ 1u); else asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncthreads();                                         // block tb has landed for every warp
-        for (uint32_t tt = 0; tt < n; ++tt) {
-            const float decay = expf(s_g[buf][tt]);
-            float kc[VPL];
-            float sum = 0.f;
+        // Off the token-to-token dependency chain: the block's eight decays are computed once (lane l holds token l % 8's) and
+        // the output dot products are only reduced after the eight tokens, all together.
+        const float dec_l = expf(s_g[buf][lane & (DN_TB - 1u)]);
+        float op[DN_TB];
 #pragma unroll
-            for (int t = 0; t < VPL; ++t) { kc[t] = s_k[buf][tt][lane + 32 * t]; m[t] = m[t] * decay; sum += m[t] * kc[t]; }
-            for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            const float delta = (s_v[buf][tt][warp] - sum) * s_b[buf][tt];
-            float o_acc = 0.f;
+        for (uint32_t tt = 0; tt < DN_TB; ++tt) {
+            op[tt] = 0.f;
+            if (tt < n) {
+                const float decay = __shfl_sync(0xffffffffu, dec_l, (int)tt);
+                float kc[VPL];
+                float sum = 0.f;
 #pragma unroll
-            for (int t = 0; t < VPL; ++t) { m[t] += kc[t] * delta; o_acc += m[t] * s_q[buf][tt][lane + 32 * t]; }
-            for (int o = 16; o; o >>= 1) o_acc += __shfl_xor_sync(0xffffffffu, o_acc, o);
-            if (lane == 0) core[(size_t)(tb * DN_TB + tt) * D.d_inner + (size_t)h * S + j] = o_acc * scale;
+                for (int t = 0; t < VPL; ++t) { kc[t] = s_k[buf][tt][lane + 32 * t]; m[t] = m[t] * decay; sum += m[t] * kc[t]; }
+                for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                const float delta = (s_v[buf][tt][warp] - sum) * s_b[buf][tt];
+                float o_acc = 0.f;
+#pragma unroll
+                for (int t = 0; t < VPL; ++t) { m[t] += kc[t] * delta; o_acc += m[t] * s_q[buf][tt][lane + 32 * t]; }
+                op[tt] = o_acc;
+            }
+        }
+        {   // eight sums across the warp with the pairing of the plain butterfly (16, 8, 4, 2, 1), but each exchange halves the
+            // values a lane carries: 4 + 2 + 1 + 1 + 1 shuffles instead of 8 x 5. Value i ends up in the lanes whose bits 4, 3, 2 spell i.
+            const bool hi4 = lane & 16u, hi3 = lane & 8u, hi2 = lane & 4u;
+            float a4[4], a2[2], a1;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float keep = hi4 ? op[4 + i] : op[i], send = hi4 ? op[i] : op[4 + i]; a4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16); }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) { const float keep = hi3 ? a4[2 + i] : a4[i], send = hi3 ? a4[i] : a4[2 + i]; a2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8); }
+            { const float keep = hi2 ? a2[1] : a2[0], send = hi2 ? a2[0] : a2[1]; a1 = keep + __shfl_xor_sync(0xffffffffu, send, 4); }
+            a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+            a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+            const uint32_t ti = ((lane >> 4) & 1u) * 4u + ((lane >> 3) & 1u) * 2u + ((lane >> 2) & 1u);
+            if ((lane & 3u) == 0u && ti < n) core[(size_t)(tb * DN_TB + ti) * D.d_inner + (size_t)h * S + j] = a1 * scale;
         }
         __syncthreads();                                         // buffer buf may be refilled by the next stage() call
     }
