@@ -14,6 +14,7 @@
 #include <stdlib.h>
 #include <mutex>
 #include <new>
+#include <type_traits>
 
 namespace rc {
 
@@ -326,6 +327,216 @@ __global__ void __launch_bounds__(256) k_dn_state_seq(DnDims D, uint32_t T, cons
     for (int t = 0; t < VPL; ++t) row[lane + 32 * t] = m[t];
 }
 
+// ---- the same token-by-token recurrence with a lane group per row (the default scan) -----------------------------------
+// k_dn_state_seq spreads ONE row over the 32 lanes of a warp: per token a warp issues about 50 instructions for 4 x 128
+// multiply-adds, ten of them the two five-step reductions, and every SM carries 32 such warps. Here LPR = S / CPT lanes
+// share a row (CPT columns each, as float4 pieces interleaved over the lanes so that a quarter warp reads 128 contiguous
+// bytes of k or q), a thread carries RPT rows (k and q, read from shared memory once, serve all of them: the shared-memory
+// pipe delivers 128 bytes per cycle whether or not lanes read the same address, and with one row per thread it was busier
+// than the fp32 pipe), the row's partial sums meet in ONE exchange step, and the arithmetic is packed fp32 (two columns
+// per instruction). Per element it is the reference's (decay the row, dot with k, add k * delta, dot with q:
+// native/redlite_native_engine_cpu.c:198-216); only the order of the sums inside a dot product differs. Whole blocks of
+// eight tokens run through a branch-free unrolled body; the block's decays, betas and v are fetched before its first
+// token, a token's q and the next token's k before the exchange that the chain waits for, and the eight output sums are
+// reduced together after the block. RC_DN_SCAN=warp selects k_dn_state_seq for comparison.
+template <uint32_t S, uint32_t CPT, uint32_t RPT, uint32_t WARPS>
+__global__ void __launch_bounds__(WARPS * 32u) k_dn_scan(DnDims D, uint32_t T, const float *__restrict__ qk, const float *__restrict__ v,
+                                                         const float *__restrict__ beta, const float *__restrict__ gate,
+                                                         float *__restrict__ state, float *__restrict__ core) {
+    pdl_prologue();
+    constexpr uint32_t LPR = S / CPT, RPW = 32u / LPR, RB = RPW * RPT * WARPS, NP = CPT / 4u, NT = WARPS * 32u, V4 = S / 4u;
+    static_assert(LPR == 2u || LPR == 4u || LPR == 8u || LPR == 16u || LPR == 32u, "lanes per row");
+    static_assert(S % RB == 0u && RB % 4u == 0u && DN_TB == 8u, "rows per block");
+    __shared__ __align__(16) float s_q[2][DN_TB][S], s_k[2][DN_TB][S];
+    __shared__ __align__(16) float s_v[2][RB][DN_TB];            // v by (row, token): a thread reads its row's eight values as two float4
+    __shared__ __align__(16) float s_b[2][DN_TB], s_g[2][DN_TB];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, p = lane % LPR, r = lane / LPR;
+    const uint32_t h = blockIdx.x / (S / RB), j0 = (blockIdx.x % (S / RB)) * RB;     // head, first of the block's RB rows
+    const uint32_t jr = (warp * RPW + r) * RPT;                                      // this thread's first row inside the block
+    const uint32_t kh = h / (D.rank / D.groups);
+    const size_t tok_qk = (size_t)2u * D.groups * S;
+    const float *q = qk + (size_t)kh * S, *k = qk + (size_t)(D.groups + kh) * S;
+    float *rows = state + ((size_t)h * S + j0 + jr) * S;
+    const float scale = 1.0f / sqrtf((float)S);
+
+    auto stage = [&](uint32_t tb, uint32_t buf) {               // tokens [tb * DN_TB, ...) -> buffer buf
+        const uint32_t t0 = tb * DN_TB, n = min(DN_TB, T - t0);
+        for (uint32_t i = tid; i < 2u * DN_TB * V4; i += NT) {
+            const uint32_t which = i / (DN_TB * V4), tt = (i / V4) % DN_TB, c = (i % V4) * 4u;
+            if (tt < n) {
+                const float *src = (which ? k : q) + (size_t)(t0 + tt) * tok_qk + c;
+                float *dst = (which ? &s_k[buf][tt][0] : &s_q[buf][tt][0]) + c;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+            }
+        }
+        for (uint32_t i = tid; i < DN_TB * RB; i += NT) {
+            const uint32_t tt = i / RB, rr = i % RB;
+            if (tt < n)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"((uint32_t)__cvta_generic_to_shared(&s_v[buf][rr][tt])),
+                             "l"(v + (size_t)(t0 + tt) * D.d_inner + (size_t)h * S + j0 + rr) : "memory");
+        }
+        for (uint32_t i = tid; i < DN_TB * 2u; i += NT) {
+            const uint32_t tt = i >> 1;
+            if (tt < n) {
+                const float *src = (i & 1u ? gate : beta) + (size_t)(t0 + tt) * D.rank + h;
+                float *dst = i & 1u ? &s_g[buf][tt] : &s_b[buf][tt];
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    float2 m[RPT][CPT / 2u];                                     // the rows as register pairs: the arithmetic is packed fp32 (two lanes per instruction)
+#pragma unroll
+    for (uint32_t a = 0; a < RPT; ++a)
+#pragma unroll
+        for (uint32_t i = 0; i < NP; ++i) {
+            const float4 x = *reinterpret_cast<const float4 *>(rows + (size_t)a * S + 4u * (i * LPR + p));
+            m[a][2u * i] = make_float2(x.x, x.y); m[a][2u * i + 1u] = make_float2(x.z, x.w);
+        }
+
+    auto body = [&](auto full_c, uint32_t buf, uint32_t n, uint32_t t0) {
+        constexpr bool FULL = decltype(full_c)::value;
+        // the block's scalars first, off the token-to-token chain: eight decays (lane l computes token l % 8's), betas and this
+        // thread's v (entries of tokens >= n are stale and never used)
+        float dec[DN_TB], bt[DN_TB], vv[RPT][DN_TB];
+        {
+            const float dec_l = expf(s_g[buf][lane & (DN_TB - 1u)]);
+#pragma unroll
+            for (uint32_t tt = 0; tt < DN_TB; ++tt) dec[tt] = __shfl_sync(0xffffffffu, dec_l, (int)tt);
+            const float4 b0 = *reinterpret_cast<const float4 *>(&s_b[buf][0]), b1 = *reinterpret_cast<const float4 *>(&s_b[buf][4]);
+            bt[0] = b0.x; bt[1] = b0.y; bt[2] = b0.z; bt[3] = b0.w; bt[4] = b1.x; bt[5] = b1.y; bt[6] = b1.z; bt[7] = b1.w;
+#pragma unroll
+            for (uint32_t a = 0; a < RPT; ++a) {
+                const float4 v0 = *reinterpret_cast<const float4 *>(&s_v[buf][jr + a][0]), v1 = *reinterpret_cast<const float4 *>(&s_v[buf][jr + a][4]);
+                vv[a][0] = v0.x; vv[a][1] = v0.y; vv[a][2] = v0.z; vv[a][3] = v0.w; vv[a][4] = v1.x; vv[a][5] = v1.y; vv[a][6] = v1.z; vv[a][7] = v1.w;
+            }
+        }
+        float op[RPT][DN_TB];
+        float4 kc[NP], kn[NP], qc[NP];
+#pragma unroll
+        for (uint32_t i = 0; i < NP; ++i) kc[i] = *reinterpret_cast<const float4 *>(&s_k[buf][0][4u * (i * LPR + p)]);
+#pragma unroll
+        for (uint32_t tt = 0; tt < DN_TB; ++tt) {
+#pragma unroll
+            for (uint32_t a = 0; a < RPT; ++a) op[a][tt] = 0.f;
+            if (FULL || tt < n) {
+                // this token's q and the next token's k are requested before the reduction that the chain waits for
+#pragma unroll
+                for (uint32_t i = 0; i < NP; ++i) {
+                    qc[i] = *reinterpret_cast<const float4 *>(&s_q[buf][tt][4u * (i * LPR + p)]);
+                    if (tt + 1u < DN_TB) kn[i] = *reinterpret_cast<const float4 *>(&s_k[buf][tt + 1u][4u * (i * LPR + p)]);
+                }
+                const float2 d2 = make_float2(dec[tt], dec[tt]);
+                float delta[RPT];
+#pragma unroll
+                for (uint32_t a = 0; a < RPT; ++a) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 2u * NP; ++i) m[a][i] = __fmul2_rn(m[a][i], d2);
+                    float2 s2 = __fmul2_rn(m[a][0], make_float2(kc[0].x, kc[0].y));
+                    if constexpr (NP == 1u) {
+                        s2 = __ffma2_rn(m[a][1], make_float2(kc[0].z, kc[0].w), s2);
+                    } else {
+                        float2 pb = __fmul2_rn(m[a][1], make_float2(kc[0].z, kc[0].w));
+#pragma unroll
+                        for (uint32_t i = 1; i < NP; ++i) {
+                            s2 = __ffma2_rn(m[a][2u * i], make_float2(kc[i].x, kc[i].y), s2);
+                            pb = __ffma2_rn(m[a][2u * i + 1u], make_float2(kc[i].z, kc[i].w), pb);
+                        }
+                        s2 = __fadd2_rn(s2, pb);
+                    }
+                    float sum = s2.x + s2.y;
+                    if constexpr (LPR <= 8u) {
+                        // one exchange step instead of log2(LPR) dependent ones: every lane of the row fetches all LPR partial sums
+                        // and adds them in the same order (so the row's lanes agree to the bit)
+                        float x[LPR];
+#pragma unroll
+                        for (uint32_t l = 0; l < LPR; ++l) x[l] = __shfl_sync(0xffffffffu, sum, (int)((lane & ~(LPR - 1u)) + l));
+#pragma unroll
+                        for (uint32_t w = LPR; w > 1u; w >>= 1)
+#pragma unroll
+                            for (uint32_t l = 0; l < w / 2u; ++l) x[l] = x[2u * l] + x[2u * l + 1u];
+                        sum = x[0];
+                    } else {
+#pragma unroll
+                        for (uint32_t o = LPR / 2u; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, (int)o);
+                    }
+                    delta[a] = (vv[a][tt] - sum) * bt[tt];
+                }
+#pragma unroll
+                for (uint32_t a = 0; a < RPT; ++a) {
+                    const float2 e2 = make_float2(delta[a], delta[a]);
+#pragma unroll
+                    for (uint32_t i = 0; i < NP; ++i) {
+                        m[a][2u * i] = __ffma2_rn(make_float2(kc[i].x, kc[i].y), e2, m[a][2u * i]);
+                        m[a][2u * i + 1u] = __ffma2_rn(make_float2(kc[i].z, kc[i].w), e2, m[a][2u * i + 1u]);
+                    }
+                    float2 s2 = __fmul2_rn(m[a][0], make_float2(qc[0].x, qc[0].y));
+                    if constexpr (NP == 1u) {
+                        s2 = __ffma2_rn(m[a][1], make_float2(qc[0].z, qc[0].w), s2);
+                    } else {
+                        float2 pb = __fmul2_rn(m[a][1], make_float2(qc[0].z, qc[0].w));
+#pragma unroll
+                        for (uint32_t i = 1; i < NP; ++i) {
+                            s2 = __ffma2_rn(m[a][2u * i], make_float2(qc[i].x, qc[i].y), s2);
+                            pb = __ffma2_rn(m[a][2u * i + 1u], make_float2(qc[i].z, qc[i].w), pb);
+                        }
+                        s2 = __fadd2_rn(s2, pb);
+                    }
+                    op[a][tt] = s2.x + s2.y;
+                }
+                if (tt + 1u < DN_TB) {
+#pragma unroll
+                    for (uint32_t i = 0; i < NP; ++i) kc[i] = kn[i];
+                }
+            }
+        }
+        // the eight output sums over the row's LPR lanes: while a lane carries more than one value each exchange halves them,
+        // so a lane ends with max(1, 8 / LPR) finished tokens (first token `tok`) instead of every lane reducing all eight
+        constexpr uint32_t LOW = LPR > DN_TB ? LPR / DN_TB - 1u : 0u;     // lane bits below the halving exchanges: those lanes hold copies
+#pragma unroll
+        for (uint32_t a = 0; a < RPT; ++a) {
+            uint32_t tok = 0u, cnt = DN_TB;
+#pragma unroll
+            for (uint32_t o = LPR / 2u; o; o >>= 1) {
+                if (cnt > 1u) {
+                    cnt >>= 1;
+                    const bool hi = p & o;
+#pragma unroll
+                    for (uint32_t i = 0; i < DN_TB / 2u; ++i)
+                        if (i < cnt) {
+                            const float keep = hi ? op[a][cnt + i] : op[a][i], send = hi ? op[a][i] : op[a][cnt + i];
+                            op[a][i] = keep + __shfl_xor_sync(0xffffffffu, send, (int)o);
+                        }
+                    if (hi) tok += cnt;
+                } else {
+                    op[a][0] += __shfl_xor_sync(0xffffffffu, op[a][0], (int)o);
+                }
+            }
+#pragma unroll
+            for (uint32_t i = 0; i < (LPR < DN_TB ? DN_TB / LPR : 1u); ++i)
+                if ((p & LOW) == 0u && (FULL || tok + i < n)) core[(size_t)(t0 + tok + i) * D.d_inner + (size_t)h * S + j0 + jr + a] = op[a][i] * scale;
+        }
+    };
+
+    const uint32_t nblk = (T + DN_TB - 1u) / DN_TB;
+    stage(0u, 0u);
+    for (uint32_t tb = 0; tb < nblk; ++tb) {
+        const uint32_t buf = tb & 1u, n = min(DN_TB, T - tb * DN_TB);
+        if (tb + 1u < nblk) stage(tb + 1u, buf ^ 1u); else asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();                                         // block tb has landed for every warp
+        if (n == DN_TB) body(std::true_type{}, buf, n, tb * DN_TB); else body(std::false_type{}, buf, n, tb * DN_TB);
+        __syncthreads();                                         // buffer buf may be refilled by the next stage() call
+    }
+#pragma unroll
+    for (uint32_t a = 0; a < RPT; ++a)
+#pragma unroll
+        for (uint32_t i = 0; i < NP; ++i)
+            *reinterpret_cast<float4 *>(rows + (size_t)a * S + 4u * (i * LPR + p)) =
+                make_float4(m[a][2u * i].x, m[a][2u * i].y, m[a][2u * i + 1u].x, m[a][2u * i + 1u].y);
+}
+
 // ---- the same recurrence four tokens at a time -------------------------------------------------------------------
 // Inside a group of four tokens the corrections delta_t depend on each other only through the scalars k_s . k_t, which are
 // the same for every state row of a head. With d_t the per-token decay, g_t = d_1 ... d_t, r(t,s) = d_{s+1} ... d_t and
@@ -521,7 +732,24 @@ int launch_deltanet_seq(const DnDims &D, uint32_t T, const float *conv_kernel, c
         prof_end(s);
         RC_LAUNCHED();
     }
-    if (T4 < T) {
+    const bool per_warp = scan && scan[0] == 'w';                 // RC_DN_SCAN=warp: the one-row-per-warp kernel, for comparison
+    if (T4 < T && !per_warp) {
+        const uint32_t Tr = T - T4;
+        const size_t tok_qk = (size_t)2u * D.groups * D.S;
+        const float *qk_r = qk + (size_t)T4 * tok_qk, *v_r = v + (size_t)T4 * D.d_inner, *b_r = beta + (size_t)T4 * D.rank, *g_r = gate + (size_t)T4 * D.rank;
+        float *core_r = core + (size_t)T4 * D.d_inner;
+        prof_begin("dn_state_seq", s);
+        switch (D.S) {
+            case 32: RC_LAUNCH((k_dn_scan<32, 16, 1, 2>), D.rank, 64, 0, s, D, Tr, qk_r, v_r, b_r, g_r, rec_state, core_r); break;
+            case 64: RC_LAUNCH((k_dn_scan<64, 16, 1, 8>), D.rank, 256, 0, s, D, Tr, qk_r, v_r, b_r, g_r, rec_state, core_r); break;
+            // 128-wide states: two rows per thread halve the shared-memory reads of k and q per multiply-add; measured on 2048-token
+            // chunks this tile took 0.50 ms, one row per thread 0.53-0.54 ms, wider lane groups (4 or 8 columns per thread) 0.58-0.70 ms
+            case 128: RC_LAUNCH((k_dn_scan<128, 16, 2, 4>), D.rank * 4u, 128, 0, s, D, Tr, qk_r, v_r, b_r, g_r, rec_state, core_r); break;
+            default: RC_LAUNCH((k_dn_scan<256, 32, 1, 8>), D.rank * 8u, 256, 0, s, D, Tr, qk_r, v_r, b_r, g_r, rec_state, core_r); break;
+        }
+        prof_end(s);
+        RC_LAUNCHED();
+    } else if (T4 < T) {
         const uint32_t Tr = T - T4;
         const size_t tok_qk = (size_t)2u * D.groups * D.S;
         const float *qk_r = qk + (size_t)T4 * tok_qk, *v_r = v + (size_t)T4 * D.d_inner, *b_r = beta + (size_t)T4 * D.rank, *g_r = gate + (size_t)T4 * D.rank;

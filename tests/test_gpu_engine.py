@@ -198,13 +198,14 @@ def test_midsize_model_chunked_prefill(tmp_path, monkeypatch):
         eng.close()
 
 
+@pytest.mark.parametrize("scan", ["grouped", "warp"])
 @pytest.mark.parametrize("which", ["tiny", "mid"])
-def test_chunked_prefill_with_grouped_deltanet_recurrence(tmp_path, which, monkeypatch):
-    """RC_DN_SCAN=grouped: the delta rule four tokens at a time (one round of reductions per group) must leave the same
-    outputs and state as the oracle's token-by-token pass; prompt lengths that are not multiples of four leave a tail for
-    the token-by-token kernel."""
+def test_chunked_prefill_with_alternative_deltanet_scans(tmp_path, which, scan, monkeypatch):
+    """The two scan kernels kept beside the default one. RC_DN_SCAN=grouped: the delta rule four tokens at a time (one round
+    of reductions per group) must leave the same outputs and state as the oracle's token-by-token pass; prompt lengths that
+    are not multiples of four leave a tail for the token-by-token kernel. RC_DN_SCAN=warp: one state row per warp."""
     monkeypatch.setenv("RL_KV_F16", "1")
-    monkeypatch.setenv("RC_DN_SCAN", "grouped")
+    monkeypatch.setenv("RC_DN_SCAN", scan)
     if which == "tiny":
         dims = synth.tiny_model_dims(n_layer=8)
     else:
