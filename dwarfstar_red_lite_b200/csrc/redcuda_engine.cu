@@ -308,6 +308,7 @@ struct rl_engine {
     uint32_t *tok_chunk_d = nullptr, *pos_chunk_d = nullptr;
     float *dn_pd = nullptr;          // DeltaNet prefill: the 16 pair products of every group of four tokens and key head
     __half *tc_xs = nullptr; float *tc_xinv = nullptr; uint32_t *tc_err = nullptr;   // tcgen05 GEMM: activation digits, per-token inverse scales, timeout flag
+    uint8_t *tc_wd = nullptr; float *tc_winv = nullptr; size_t tc_wd_cap = 0;        // and the weight digits of one launch (widest projection group)
     // host mirrors
     std::vector<float> embed_h, layer_out_h, final_norm_h;
     std::vector<uint32_t> router_ids_h;
@@ -457,6 +458,8 @@ static int eng_proj(rl_engine *e, const DMat *mats, float *const *outs, uint32_t
         if (!launch_tc_prep_x(x, nullptr, mats[0].ncols, ntok, mats[0].ncols, tn, e->tc_xs, e->tc_xinv, e->stream)) return 0;
         TcArgs A{};
         A.njobs = n; A.ncols = mats[0].ncols; A.ntok = ntok; A.xs = e->tc_xs; A.x_inv = e->tc_xinv; A.err = e->tc_err;
+        A.wd = e->tc_wd; A.w_inv = e->tc_winv;
+        RC_REQUIRE(tc_wd_bytes(row_tiles, mats[0].ncols) <= e->tc_wd_cap, "projection group %s: %u row tiles x %u columns exceed the weight-digit scratch", tag, row_tiles, mats[0].ncols);
         for (uint32_t i = 0; i < n; ++i) A.job[i] = TcJob{mats[i].base, mats[i].nb, mats[i].type, mats[i].nrows, outs[i], mats[i].nrows, 0u};
         return launch_tc_gemm(A, tn, tag, e->stream);
     }
@@ -743,6 +746,19 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
     const size_t T = e->pb;          // rows of every per-token buffer (decode uses row 0)
     const size_t parts = std::max<size_t>(e->max_split, T * e->pf_split);
     const uint32_t widest = std::max(std::max(in.hidden, in.d_inner), qc);
+    // weight digits of the widest projection group that the tcgen05 GEMM may be given (4 bytes per weight, rows in tiles of 128)
+    size_t wd_bytes = 0, wd_tiles = 0;
+    for (uint32_t l = 0; l < in.n_layer; ++l) {
+        const EngLayer &L = e->layers[l];
+        const DMat *groups[2][3] = {{L.recurrent ? &L.qkv : &L.q, L.recurrent ? &L.z : &L.k, L.recurrent ? &L.ba : &L.v}, {L.recurrent ? &L.ssm_out : &L.o, nullptr, nullptr}};
+        for (auto &g : groups) {
+            uint32_t tiles = 0;
+            for (const DMat *m : g) if (m) tiles += tc_row_tiles(m->nrows);
+            wd_bytes = std::max(wd_bytes, tc_wd_bytes(tiles, g[0]->ncols));
+            wd_tiles = std::max<size_t>(wd_tiles, tiles);
+        }
+    }
+    const size_t o_twd = take(wd_bytes), o_twi = take(wd_tiles * 4u);
     const size_t o_norm = take(T * in.hidden * 4u), o_br = take(T * in.hidden * 4u), o_res = take(T * in.hidden * 4u), o_qkv = take(T * in.channels * 4u), o_z = take(T * in.d_inner * 4u),
                  o_ba = take(T * 2u * in.dt_rank * 4u), o_ng = take(T * in.d_inner * 4u), o_dqk = take(T * 2u * in.n_group * in.d_state * 4u), o_dv = take(T * in.d_inner * 4u),
                  o_db = take(T * in.dt_rank * 4u), o_dg = take(T * in.dt_rank * 4u), o_dc = take(T * in.d_inner * 4u), o_qg = take(T * 2u * qc * 4u), o_kr = take(T * kvc * 4u), o_vr = take(T * kvc * 4u),
@@ -767,6 +783,7 @@ static int eng_open(rl_engine *e, const char *path, char *error, size_t cap) {
     for (uint32_t l = 0; l < in.n_layer; ++l) moe_set_ids_mirror(e->layers[l].moe, e->router_ids_d + (size_t)l * RL_ENGINE_MAX_TOPK);
     e->tc_xs = (__half *)(B + o_txs); e->tc_xinv = (float *)(B + o_txi); e->tc_err = (uint32_t *)(B + o_ter);
     e->dn_pd = (float *)(B + o_pd);
+    e->tc_wd = B + o_twd; e->tc_winv = (float *)(B + o_twi); e->tc_wd_cap = wd_bytes;
     e->embed_h.assign(in.hidden, 0.f); e->layer_out_h.assign((size_t)in.n_layer * in.hidden, 0.f); e->final_norm_h.assign(in.hidden, 0.f);
     e->router_ids_h.assign((size_t)in.n_layer * RL_ENGINE_MAX_TOPK, 0u);
     ENG_CUDA(cudaMallocHost((void **)&e->token_pin, 64u + 2u * T * 4u));      // [16 words][chunk tokens][chunk positions]

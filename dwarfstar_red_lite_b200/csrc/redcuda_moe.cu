@@ -283,6 +283,7 @@ struct redcuda_moe {
     uint32_t *ticket = nullptr; // ticket counter of the single-token GEMV's routing tail (zero between launches)
     uint32_t *tc_err = nullptr; // timeout flag of the tcgen05 kernels
     __half *sh_xs = nullptr; float *sh_xinv = nullptr;   // shared expert on the tcgen05 GEMM: activation digits and inverse scales
+    uint8_t *sh_wd = nullptr; float *sh_winv = nullptr;  // and the weight digits of one launch (gate + up, or down)
     bool tc_ok = false;         // the tcgen05 expert kernel can serve this layer's shapes
     bool tc_now = false;        // ... and serves the call in progress (set by moe_choose_path, read by the grouping and the launches)
     bool ws_shared = false;     // the workspace belongs to the caller (rc::moe_create_shared)
@@ -333,6 +334,7 @@ static int moe_shared_tc_gemm(redcuda_moe *m, uint32_t ntok, const float *x, con
     if (!launch_tc_prep_x(x, x2, ncols, ntok, ncols, tn, m->sh_xs, m->sh_xinv, s)) return 0;
     TcArgs A{};
     A.njobs = w1 ? 2u : 1u; A.ncols = ncols; A.ntok = ntok; A.xs = m->sh_xs; A.x_inv = m->sh_xinv; A.err = m->tc_err;
+    A.wd = m->sh_wd; A.w_inv = m->sh_winv;
     A.job[0] = TcJob{w0->base, w0->nb, w0->type, w0->nrows, out0, w0->nrows, 0u};
     if (w1) A.job[1] = TcJob{w1->base, w1->nb, w1->type, w1->nrows, out1, w1->nrows, 0u};
     return launch_tc_gemm(A, tn, tag, s);
@@ -583,6 +585,10 @@ static size_t moe_ws_layout(const redcuda_moe_desc &d, redcuda_moe *m, uint8_t *
     put(r.xq_sh, T * 3u * d.ffn_sh); put(r.sx_sh, T * 4u); put(r.xq_own, T * 3u * d.hidden); put(r.sx_own, T * 4u);
     put(r.item_u, (P + 8u) * 4u); put(r.item_p0, (P + 8u) * 4u); put(r.n_items, 16); put(r.work, 16);
     put(r.sh_xs, tc_xs_halves((uint32_t)T, d.hidden > d.ffn_sh ? d.hidden : d.ffn_sh, 128u) * 2u); put(r.sh_xinv, (T + 128u) * 4u);
+    {
+        const uint32_t t_up = 2u * tc_row_tiles(d.ffn_sh), t_down = tc_row_tiles(d.hidden);
+        put(r.sh_wd, std::max(tc_wd_bytes(t_up, d.hidden), tc_wd_bytes(t_down, d.ffn_sh))); put(r.sh_winv, (size_t)std::max(t_up, t_down) * 4u);
+    }
     if (m) { m->ticket = m->work + 2; m->tc_err = m->work + 3; }
     return w;
 }

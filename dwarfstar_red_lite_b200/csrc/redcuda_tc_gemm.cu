@@ -205,60 +205,20 @@ __global__ void k_tc_prep_x(const float *__restrict__ x, const float *__restrict
     }
 }
 
-// number of activation stage buffers: the bulk copy of stage s + NB - 2 is issued when stage s begins
-template <int TN> struct TcCfg { static constexpr uint32_t NB = TN >= 128 ? 3u : 4u; };
-
-template <int TN>
-__global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant__ TcArgs A) {
+// ---- weights of a launch -> fp16 digit tiles, once per launch -----------------------------------------------------------
+// wd[row tile][stage][hi 16 KB | lo 16 KB] in the layout an MMA stage reads (tc_decode_stage), w_inv[row tile] = the inverse
+// of the tile's power-of-two scale. grid = (row tiles of the launch, 256-column blocks), block = TC_THREADS.
+__global__ void __launch_bounds__(TC_THREADS) k_tc_decode_w(const __grid_constant__ TcArgs A) {
     pdl_prologue();
-    extern __shared__ __align__(128) uint8_t smem[];
-    constexpr uint32_t NB = TcCfg<TN>::NB;
-    constexpr uint32_t B_DIGIT = (uint32_t)TN * TC_KS * 2u, A_BUF = 2u * TC_A_DIGIT, B_BUF = 2u * B_DIGIT;
-    constexpr uint32_t TMEM_COLS = 4u * (uint32_t)TN;     // two blocks in flight x (hi*hi accumulator, cross-product accumulator)
-    static_assert(TMEM_COLS >= 32u && TMEM_COLS <= 512u && (TMEM_COLS & (TMEM_COLS - 1u)) == 0u, "tensor-memory allocation must be a power of two in [32, 512]");
-    __shared__ __align__(8) uint64_t mbar[2];        // MMAs that read A buffer b (and the B buffer of the same stage) are done
-    __shared__ __align__(8) uint64_t accfull[2];     // every MMA of a 256-column block has landed in accumulator pair b
-    __shared__ __align__(8) uint64_t bfull[NB];      // the activation digits of a stage have landed
-    __shared__ uint32_t tmem_slot;
-    __shared__ volatile uint32_t fail;      // a bounded wait ran out: no more MMAs are issued, later waits are skipped
+    __shared__ __align__(16) uint8_t raw[29440];          // tc_raw_bytes of the widest format
     __shared__ float red[TC_WARPS];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-
-    // which matrix of the launch this row tile belongs to
     uint32_t ji = 0;
     for (uint32_t j = 1; j < A.njobs; ++j) if (blockIdx.x >= A.job[j].tile0) ji = j;
     const TcJob &J = A.job[ji];
-    const uint32_t row0 = (blockIdx.x - J.tile0) * TC_M, t0 = blockIdx.y * (uint32_t)TN;
-    const uint32_t bpr = A.ncols >> 8, nstage = A.ncols / TC_KS;
+    const uint32_t row0 = (blockIdx.x - J.tile0) * TC_M, c = blockIdx.y, bpr = A.ncols >> 8, nstage = A.ncols / TC_KS;
     const RcBooks bk{A.iq2, A.iq3s};
-    uint8_t *a_base = smem, *b_base = smem + 2u * A_BUF, *raw_base = b_base + NB * B_BUF;
-    const __half *xs_tile = A.xs + (size_t)blockIdx.y * nstage * (B_BUF / 2u);
-
-    // one bulk copy (TMA engine, no tensor map: the digits are already laid out for the MMA) per stage
-    auto issue_b = [&](uint32_t stage) {
-        const uint32_t j = stage % NB, bar = smem_u32(&bfull[j]);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(B_BUF) : "memory");
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     :: "r"(smem_u32(b_base + j * B_BUF)), "l"(xs_tile + (size_t)stage * (B_BUF / 2u)), "r"(B_BUF), "r"(bar) : "memory");
-    };
-
-    if (tid == 0) {
-        fail = 0u;
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&mbar[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&mbar[1])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&accfull[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&accfull[1])));
-        for (uint32_t j = 0; j < NB; ++j) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&bfull[j])));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        for (uint32_t st = 0; st + 2u < NB && st < nstage; ++st) issue_b(st);
-    }
-    if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    uint8_t *raw_buf[2] = {raw_base, raw_base + tc_raw_bytes(J.type)};
-    unsigned short d_next = tc_stage_raw(J.type, J.w, J.nb, bpr, row0, J.nrows, 0u, raw_buf[0], tid);
+    const unsigned short d = tc_stage_raw(J.type, J.w, J.nb, bpr, row0, J.nrows, c, raw, tid);
     // power-of-two scale of the tile: the largest block scale d times the largest integer factor of the format
     float dmax = 0.f;
     {
@@ -270,10 +230,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
         for (int o = 16; o; o >>= 1) dmax = fmaxf(dmax, __shfl_xor_sync(0xffffffffu, dmax, o));
         if (lane == 0) red[warp] = dmax;
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    tc_put_d(J.type, raw, tid, d);
+    asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = tmem_slot;
     dmax = 0.f;
     for (uint32_t w = 0; w < TC_WARPS; ++w) dmax = fmaxf(dmax, red[w]);
     int we = 0;
@@ -282,75 +241,129 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
         if (bound > 0.f && bound < INFINITY) { int ex; frexpf(bound, &ex); we = 15 - ex; }       // |w| * 2^we < 2^15
         we = we > 100 ? 100 : we < -100 ? -100 : we;
     }
-    const float w_scale = exp2f((float)we), w_inv = exp2f((float)-we);
-    const uint32_t idesc = tc_idesc((uint32_t)TN), idesc2 = tc_idesc(2u * (uint32_t)TN);
+    const float w_scale = exp2f((float)we);
+    if (c == 0u && tid == 0) A.w_inv[blockIdx.x] = exp2f((float)-we);
+    const uint32_t rows_live = J.nrows - row0 < TC_M ? J.nrows - row0 : TC_M;
+#pragma unroll 1
+    for (uint32_t st = 0; st < 256u / TC_KS; ++st) {
+        uint8_t *dst = A.wd + ((size_t)blockIdx.x * nstage + c * (256u / TC_KS) + st) * (2u * TC_A_DIGIT);
+        if (J.type == RC_Q6_K) tc_decode_stage<RC_Q6_K>(raw, dst, st * (TC_KS / 8u), rows_live, w_scale, bk, tid);
+        else if (J.type == RC_IQ2_XXS) tc_decode_stage<RC_IQ2_XXS>(raw, dst, st * (TC_KS / 8u), rows_live, w_scale, bk, tid);
+        else tc_decode_stage<RC_IQ3_S>(raw, dst, st * (TC_KS / 8u), rows_live, w_scale, bk, tid);
+    }
+}
 
-    // fp32 sums over the 256-column blocks: warp w owns TMEM lanes 32*(w%4)..+31 (its quarter) and PER token columns
-    constexpr uint32_t PER = (uint32_t)TN / (TC_WARPS / 4u);              // columns per warp: 8, 16 or 32
-    const uint32_t qlane = (warp & 3u) * 32u, c_begin = (warp >> 2) * PER;
-    float acc[PER];
-#pragma unroll
-    for (uint32_t j = 0; j < PER; ++j) acc[j] = 0.f;
-    // adds block `blk`'s accumulators (pair blk & 1) to the register sums; every thread of the CTA calls it
-    auto drain = [&](uint32_t blk) {
-        if (fail) return;
-        if (!mbar_wait(smem_u32(&accfull[blk & 1u]), (blk >> 1) & 1u)) { fail = 1u; return; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t base = tmem + (qlane << 16) + (blk & 1u) * 2u * (uint32_t)TN + c_begin;
-#pragma unroll
-        for (uint32_t c = 0; c < PER; c += 8u) {
-            uint32_t m[8], x[8];
-            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                         : "=r"(m[0]), "=r"(m[1]), "=r"(m[2]), "=r"(m[3]), "=r"(m[4]), "=r"(m[5]), "=r"(m[6]), "=r"(m[7]) : "r"(base + c));
-            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                         : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]), "=r"(x[4]), "=r"(x[5]), "=r"(x[6]), "=r"(x[7]) : "r"(base + (uint32_t)TN + c));
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[c + j] += __uint_as_float(m[j]) + __uint_as_float(x[j]);
+// ---- the GEMM proper: one CTA = 128 weight rows (MMA M) x TN tokens (MMA N) x all columns, K in stages of 64 -------------
+//   warp 0, one thread   producer: per stage ONE mbarrier transaction of two bulk copies (the stage's weight digits from wd,
+//                        its activation digits from xs), NS stages ahead of the MMAs
+//   warp 1, one thread   issues 4 k-steps x 2 tcgen05.mma per stage (A_hi x [B_hi | B_lo], N = 2 TN; A_lo x B_hi, N = TN), a
+//                        tcgen05.commit that frees the stage's buffers, and after every fourth stage one that hands the
+//                        256-column block's accumulator pair to the drain warps
+//   warps 2..9           tcgen05.ld of a finished block's two accumulators into fp32 register sums while the next block
+//                        multiplies into the other pair; scaling and stores at the end
+// No block-wide barrier inside the loop; every wait on an mbarrier is bounded, and a wait that gives up raises a flag that
+// every role reads before its next wait, so the CTA winds down, frees its tensor memory and reports the timeout.
+constexpr uint32_t TCG_THREADS = 320u, TCG_DRAIN_WARPS = 8u;
+template <int TN> struct TcCfg { static constexpr uint32_t NS = TN >= 128 ? 3u : 4u; };
+
+template <int TN>
+__global__ void __launch_bounds__(TCG_THREADS, 1) k_tc_gemm(const __grid_constant__ TcArgs A) {
+    pdl_prologue();
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr uint32_t NS = TcCfg<TN>::NS;
+    constexpr uint32_t B_DIGIT = (uint32_t)TN * TC_KS * 2u, A_BUF = 2u * TC_A_DIGIT, B_BUF = 2u * B_DIGIT, STAGE = A_BUF + B_BUF;
+    constexpr uint32_t TMEM_COLS = 4u * (uint32_t)TN;     // two blocks in flight x (hi*hi accumulator, cross-product accumulator)
+    static_assert(TMEM_COLS >= 32u && TMEM_COLS <= 512u && (TMEM_COLS & (TMEM_COLS - 1u)) == 0u, "tensor-memory allocation must be a power of two in [32, 512]");
+    __shared__ __align__(8) uint64_t full[NS];       // both operands of a stage have landed
+    __shared__ __align__(8) uint64_t empty[NS];      // the MMAs that read a stage's buffers are done
+    __shared__ __align__(8) uint64_t acc_full[2];    // every MMA of a 256-column block has landed in accumulator pair b
+    __shared__ __align__(8) uint64_t acc_empty[2];   // the drain warps have read accumulator pair b
+    __shared__ uint32_t tmem_slot;
+    __shared__ volatile uint32_t fail;               // a bounded wait ran out
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+
+    // token tile = blockIdx.x (fastest: the CTAs that share a weight tile run together and read it from L2), row tile = blockIdx.y
+    const uint32_t rt = blockIdx.y;
+    uint32_t ji = 0;
+    for (uint32_t j = 1; j < A.njobs; ++j) if (rt >= A.job[j].tile0) ji = j;
+    const TcJob &J = A.job[ji];
+    const uint32_t row0 = (rt - J.tile0) * TC_M, t0 = blockIdx.x * (uint32_t)TN;
+    const uint32_t nstage = A.ncols / TC_KS, nblk = A.ncols >> 8;
+    const __half *xs_tile = A.xs + (size_t)blockIdx.x * nstage * (B_BUF / 2u);
+    const uint8_t *wd_tile = A.wd + (size_t)rt * nstage * A_BUF;
+
+    if (tid == 0) {
+        fail = 0u;
+        auto init = [](uint64_t *bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count)); };
+        for (uint32_t i = 0; i < NS; ++i) { init(&full[i], 1u); init(&empty[i], 1u); }
+        for (uint32_t i = 0; i < 2u; ++i) { init(&acc_full[i], 1u); init(&acc_empty[i], TCG_DRAIN_WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_slot;
+    auto wait = [&](uint64_t *bar, uint32_t parity) -> bool {
+        if (fail) return false;
+        if (mbar_wait(smem_u32(bar), parity)) return true;
+        fail = 1u;
+        return false;
+    };
+    // for the roles that are far ahead of their producer: longer sleeps between polls, so that their spinning takes no issue
+    // slots from the MMA thread
+    auto wait_idle = [&](uint64_t *bar, uint32_t parity) -> bool {
+        if (fail) return false;
+        const uint32_t addr = smem_u32(bar);
+        for (uint32_t i = 0; i < TC_SPIN_LIMIT / 8u; ++i) {
+            uint32_t done;
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+            if (done) return true;
+            __nanosleep(256);
         }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");     // the pair is overwritten two blocks later, after barriers
+        fail = 1u;
+        return false;
     };
 
-    for (uint32_t s = 0; s < nstage; ++s) {
-        const uint32_t b = s & 1u;
-        uint8_t *abuf = a_base + b * A_BUF;
-        const uint32_t c = (s * TC_KS) >> 8;                      // 256-column block of this stage
-        if (((s * TC_KS) & 255u) == 0u) {
-            // new block column: its raw bytes were requested one column ago; request the next one
-            tc_put_d(J.type, raw_buf[c & 1u], tid, d_next);
-            asm volatile("cp.async.wait_all;" ::: "memory");
-            __syncthreads();                                       // raw[c & 1] complete, raw[(c + 1) & 1] no longer read
-            if (c + 1u < bpr) d_next = tc_stage_raw(J.type, J.w, J.nb, bpr, row0, J.nrows, c + 1u, raw_buf[(c + 1u) & 1u], tid);
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            uint32_t issued = 0u;
+            for (uint32_t s = 0; s < nstage; ++s) {
+                const uint32_t j = s % NS;
+                if (s >= NS && !wait_idle(&empty[j], ((s / NS) - 1u) & 1u)) break;
+                const uint32_t bar = smem_u32(&full[j]), dst = smem_u32(smem + j * STAGE);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(STAGE) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             :: "r"(dst), "l"(wd_tile + (size_t)s * A_BUF), "r"(A_BUF), "r"(bar) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             :: "r"(dst + A_BUF), "l"(xs_tile + (size_t)s * (B_BUF / 2u)), "r"(B_BUF), "r"(bar) : "memory");
+                issued = s + 1u;
+            }
+            // after a timeout elsewhere, copies that nobody waits for may still be writing into this CTA's shared memory
+            if (fail) for (uint32_t s = issued >= NS ? issued - NS : 0u; s < issued; ++s) mbar_wait(smem_u32(&full[s % NS]), (s / NS) & 1u);
         }
-        const uint8_t *raw = raw_buf[c & 1u];
-        // the MMAs of stage s - 2 read this A buffer and the activation buffer that stage s + NB - 2 will use
-        if (s >= 2u && !fail) {
-            if (!mbar_wait(smem_u32(&mbar[b]), ((s >> 1) - 1u) & 1u)) fail = 1u;
-        }
-        if (tid == 0 && s + NB - 2u < nstage && !fail) issue_b(s + NB - 2u);
-        if ((s & 3u) == 1u && s >= 4u) drain((s >> 2) - 1u);       // the previous block's MMAs were issued more than a stage ago
-        // ---- weights of the stage -> fp16 digit tiles
-        {
-            const uint32_t g8_0 = ((s * TC_KS) & 255u) >> 3, rows_live = J.nrows - row0 < TC_M ? J.nrows - row0 : TC_M;
-            if (J.type == RC_Q6_K) tc_decode_stage<RC_Q6_K>(raw, abuf, g8_0, rows_live, w_scale, bk, tid);
-            else if (J.type == RC_IQ2_XXS) tc_decode_stage<RC_IQ2_XXS>(raw, abuf, g8_0, rows_live, w_scale, bk, tid);
-            else tc_decode_stage<RC_IQ3_S>(raw, abuf, g8_0, rows_live, w_scale, bk, tid);
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the tensor core
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        if (tid == 0 && !fail) {
-            const uint32_t jb = s % NB;
-            if (!mbar_wait(smem_u32(&bfull[jb]), (s / NB) & 1u)) fail = 1u;
-            else {
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            const uint32_t idesc = tc_idesc((uint32_t)TN), idesc2 = tc_idesc(2u * (uint32_t)TN);
+            constexpr uint32_t A_LBO = TC_M * 16u, B_LBO = 2u * (uint32_t)TN * 16u, SBO = 128u;
+            const uint64_t da0 = tc_smem_desc(0u, A_LBO, SBO), db0 = tc_smem_desc(0u, B_LBO, SBO);
+            for (uint32_t s = 0; s < nstage; ++s) {
+                const uint32_t j = s % NS, c = s >> 2;
+                if (!wait(&full[j], (s / NS) & 1u)) break;
+                if ((s & 3u) == 0u && c >= 2u && !wait(&acc_empty[c & 1u], ((c >> 1) - 1u) & 1u)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 // Two MMAs per k-step: A_hi x [B_hi | B_lo] (N = 2 TN: the hi*hi sums land in the first TN accumulator
-                // columns, hi*lo in the next TN) and A_lo x B_hi (N = TN, added to the cross-product columns). The issuing
-                // thread's latency per stage is on the critical path, so descriptors are a constant plus a start address.
-                constexpr uint32_t A_LBO = TC_M * 16u, B_LBO = 2u * (uint32_t)TN * 16u, SBO = 128u;
-                const uint64_t da0 = tc_smem_desc(0u, A_LBO, SBO), db0 = tc_smem_desc(0u, B_LBO, SBO);
-                const uint32_t a_hi = smem_u32(abuf) >> 4, a_lo = (smem_u32(abuf) + TC_A_DIGIT) >> 4, b_st = smem_u32(b_base + jb * B_BUF) >> 4;
-                const uint32_t d_main = tmem + ((s >> 2) & 1u) * 2u * (uint32_t)TN, d_cross = d_main + (uint32_t)TN;
+                // columns, hi*lo in the next TN) and A_lo x B_hi (N = TN, added to the cross-product columns).
+                const uint32_t a_st = smem_u32(smem + j * STAGE);
+                const uint32_t a_hi = a_st >> 4, a_lo = (a_st + TC_A_DIGIT) >> 4, b_st = (a_st + A_BUF) >> 4;
+                const uint32_t d_main = tmem + (c & 1u) * 2u * (uint32_t)TN, d_cross = d_main + (uint32_t)TN;
 #pragma unroll
                 for (uint32_t kk = 0; kk < TC_KS / 16u; ++kk) {
                     const uint64_t dah = da0 + ((a_hi + kk * (2u * A_LBO >> 4)) & 0x3fffu), dal = da0 + ((a_lo + kk * (2u * A_LBO >> 4)) & 0x3fffu);
@@ -358,26 +371,52 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_gemm(const __grid_constant
                     tc_mma(d_main, dah, db, idesc2, ((s & 3u) | kk) ? 1u : 0u);      // a block's first MMA overwrites its accumulators
                     tc_mma(d_cross, dal, db, idesc, 1u);
                 }
-                tc_commit(smem_u32(&mbar[b]));
-                if ((s & 3u) == 3u) tc_commit(smem_u32(&accfull[(s >> 2) & 1u]));
+                tc_commit(smem_u32(&empty[j]));
+                if ((s & 3u) == 3u) tc_commit(smem_u32(&acc_full[c & 1u]));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ accumulator drain and epilogue (256 threads)
+        // warp w reads the tensor-memory lanes of its quarter (32 * (w % 4)) and PER of the TN token columns
+        constexpr uint32_t PER = (uint32_t)TN / (TCG_DRAIN_WARPS / 4u);
+        const uint32_t qlane = (warp & 3u) * 32u, c_begin = ((warp - 2u) >> 2) * PER;
+        float acc[PER];
+#pragma unroll
+        for (uint32_t j = 0; j < PER; ++j) acc[j] = 0.f;
+        bool ok = true;
+        for (uint32_t blk = 0; blk < nblk && ok; ++blk) {
+            ok = wait_idle(&acc_full[blk & 1u], (blk >> 1) & 1u);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t base = tmem + (qlane << 16) + (blk & 1u) * 2u * (uint32_t)TN + c_begin;
+#pragma unroll
+            for (uint32_t c = 0; c < PER; c += 8u) {
+                uint32_t m[8], x[8];
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                             : "=r"(m[0]), "=r"(m[1]), "=r"(m[2]), "=r"(m[3]), "=r"(m[4]), "=r"(m[5]), "=r"(m[6]), "=r"(m[7]) : "r"(base + c));
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                             : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]), "=r"(x[4]), "=r"(x[5]), "=r"(x[6]), "=r"(x[7]) : "r"(base + (uint32_t)TN + c));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[c + j] += __uint_as_float(m[j]) + __uint_as_float(x[j]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(&acc_empty[blk & 1u])) : "memory");
+        }
+        if (ok && !fail) {
+            const uint32_t row = row0 + qlane + lane;
+            const float w_inv = A.w_inv[rt];
+#pragma unroll
+            for (uint32_t j = 0; j < PER; ++j) {
+                const uint32_t t = t0 + c_begin + j;
+                if (t < A.ntok && row < J.nrows) J.out[(size_t)t * J.out_stride + row] = acc[j] * w_inv * A.x_inv[t];
             }
         }
     }
-    // ---- the last block (a timeout of thread 0 inside the loop left a commit missing: the flag is read after a barrier
-    // and the wait inside drain is bounded as well)
-    __syncthreads();
-    drain((nstage >> 2) - 1u);
-    __syncthreads();
-    if (!fail) {
-        const uint32_t row = row0 + qlane + lane;
-#pragma unroll
-        for (uint32_t j = 0; j < PER; ++j) {
-            const uint32_t t = t0 + c_begin + j;
-            if (t < A.ntok && row < J.nrows) J.out[(size_t)t * J.out_stride + row] = acc[j] * w_inv * A.x_inv[t];
-        }
-    } else if (tid == 0) atomicExch(A.err, 1u);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (fail && tid == 0) atomicExch(A.err, 1u);
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(TMEM_COLS) : "memory");
 }
 
@@ -392,10 +431,12 @@ uint32_t tc_token_tile(uint32_t ntok, uint32_t row_tiles) {
 }
 uint32_t tc_row_tiles(uint32_t nrows) { return (nrows + TC_M - 1u) / TC_M; }
 
-static size_t tc_smem_bytes(uint32_t tn, uint32_t raw_max) {
-    const uint32_t nb = tn >= 128u ? 3u : 4u;
-    return 2u * 2u * (size_t)TC_A_DIGIT + (size_t)nb * 2u * tn * TC_KS * 2u + 2u * (size_t)raw_max;
+static size_t tc_smem_bytes(uint32_t tn) {
+    const uint32_t ns = tn >= 128u ? 3u : 4u;
+    return (size_t)ns * (2u * (size_t)TC_A_DIGIT + 2u * (size_t)tn * TC_KS * 2u);
 }
+// bytes of the weight digit scratch (TcArgs::wd) and floats of TcArgs::w_inv for a launch of row_tiles tiles
+size_t tc_wd_bytes(uint32_t row_tiles, uint32_t ncols) { return (size_t)row_tiles * TC_M * ncols * 4u; }
 
 int launch_tc_prep_x(const float *x, const float *x2, uint32_t x_stride, uint32_t ntok, uint32_t ncols, uint32_t tn, __half *xs, float *x_inv, cudaStream_t s) {
     RC_REQUIRE(ncols % TC_KS == 0, "tc gemm: %u columns is not a multiple of %u", ncols, TC_KS);
@@ -418,15 +459,19 @@ int launch_tc_gemm(TcArgs &A, uint32_t tn, const char *tag, cudaStream_t s) {
         A.job[j].tile0 = tiles;
         tiles += (A.job[j].nrows + TC_M - 1u) / TC_M;
     }
+    RC_REQUIRE(A.wd && A.w_inv, "tc gemm: no scratch for the weight digits");
     A.iq2 = books_iq2(); A.iq3s = books_iq3s();
-    const dim3 grid(tiles, (A.ntok + tn - 1u) / tn);
-    uint32_t raw_max = 0;
-    for (uint32_t j = 0; j < A.njobs; ++j) raw_max = raw_max > tc_raw_bytes(A.job[j].type) ? raw_max : tc_raw_bytes(A.job[j].type);
-    const size_t smem = tc_smem_bytes(tn, raw_max);
+    prof_begin("tc_decode_w", s);
+    RC_LAUNCH((k_tc_decode_w), dim3(tiles, A.ncols >> 8), TC_THREADS, 0, s, A);
+    prof_end(s);
+    RC_LAUNCHED();
+    const dim3 grid((A.ntok + tn - 1u) / tn, tiles);
+    RC_REQUIRE(tiles <= 65535u, "tc gemm: %u row tiles exceed the grid", tiles);
+    const size_t smem = tc_smem_bytes(tn);
     prof_begin(tag, s);
 #define RC_TC_LAUNCH(TN_) do { \
         RC_CUDA(cudaFuncSetAttribute(k_tc_gemm<TN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        RC_LAUNCH((k_tc_gemm<TN_>), grid, TC_THREADS, smem, s, A); } while (0)
+        RC_LAUNCH((k_tc_gemm<TN_>), grid, TCG_THREADS, smem, s, A); } while (0)
     if (tn == 32u) RC_TC_LAUNCH(32); else if (tn == 64u) RC_TC_LAUNCH(64); else RC_TC_LAUNCH(128);
 #undef RC_TC_LAUNCH
     prof_end(s);
@@ -447,9 +492,10 @@ extern "C" int redcuda_quant_matmul_tc(uint32_t type, const uint8_t *w, uint32_t
     RC_REQUIRE(ncols % 256u == 0, "matmul_tc: %u columns is not a multiple of 256", ncols);
     const uint64_t bytes = rc_matrix_bytes(type, nrows, ncols);
     const uint32_t tn = tc_token_tile(ntok, tc_row_tiles(nrows));
-    DevMem raw, planar, xd, od, xs, xinv, err;
+    DevMem raw, planar, xd, od, xs, xinv, err, wd, winv;
     if (!raw.alloc(bytes) || !planar.alloc(bytes) || !xd.alloc((size_t)ntok * ncols * 4u) || !od.alloc((size_t)ntok * nrows * 4u) ||
-        !xs.alloc(tc_xs_halves(ntok, ncols, tn) * 2u) || !xinv.alloc((size_t)((ntok + tn - 1u) / tn) * tn * 4u) || !err.alloc(4u)) return 0;
+        !xs.alloc(tc_xs_halves(ntok, ncols, tn) * 2u) || !xinv.alloc((size_t)((ntok + tn - 1u) / tn) * tn * 4u) || !err.alloc(4u) ||
+        !wd.alloc(tc_wd_bytes(tc_row_tiles(nrows), ncols)) || !winv.alloc((size_t)tc_row_tiles(nrows) * 4u)) return 0;
     cudaStream_t s = 0;
     if (!upload_matrix(type, nrows, ncols, w, false, planar.as<uint8_t>(), raw.as<uint8_t>(), s)) return 0;
     RC_CUDA(cudaMemcpyAsync(xd.p, x, (size_t)ntok * ncols * 4u, cudaMemcpyHostToDevice, s));
@@ -457,6 +503,7 @@ extern "C" int redcuda_quant_matmul_tc(uint32_t type, const uint8_t *w, uint32_t
     if (!launch_tc_prep_x(xd.as<float>(), nullptr, ncols, ntok, ncols, tn, xs.as<__half>(), xinv.as<float>(), s)) return 0;
     TcArgs A{};
     A.njobs = 1; A.ncols = ncols; A.ntok = ntok; A.xs = xs.as<__half>(); A.x_inv = xinv.as<float>(); A.err = err.as<uint32_t>();
+    A.wd = wd.as<uint8_t>(); A.w_inv = winv.as<float>();
     A.job[0] = TcJob{planar.as<uint8_t>(), (uint64_t)nrows * (ncols / 256u), type, nrows, od.as<float>(), nrows, 0u};
     if (!launch_tc_gemm(A, tn, "tc_gemm", s)) return 0;
     uint32_t flag = 0;

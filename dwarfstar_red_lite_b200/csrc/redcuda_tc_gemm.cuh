@@ -24,11 +24,14 @@ struct TcArgs {
     const float *x_inv;      // per-token inverse scale from launch_tc_prep_x
     const uint8_t *iq2; const uint32_t *iq3s;
     uint32_t *err;           // device flag: set to 1 when a bounded wait ran out
+    uint8_t *wd;             // scratch for the launch's weight digits: tc_wd_bytes(row tiles of the launch, ncols)
+    float *w_inv;            // scratch: one float per row tile of the launch
 };
 
 // halves of the digit buffer for ntok tokens of ncols columns with token tile tn (x_inv needs ntok rounded up to tn floats)
 size_t tc_xs_halves(uint32_t ntok, uint32_t ncols, uint32_t tn);
 uint32_t tc_row_tiles(uint32_t nrows);
+size_t tc_wd_bytes(uint32_t row_tiles, uint32_t ncols);
 uint32_t tc_token_tile(uint32_t ntok, uint32_t row_tiles);     // row_tiles = sum of tc_row_tiles over the launch's matrices
 // x2 (may be null): the digits are those of SiLU(x) * x2, both with rows x_stride apart
 int launch_tc_prep_x(const float *x, const float *x2, uint32_t x_stride, uint32_t ntok, uint32_t ncols, uint32_t tn, __half *xs, float *x_inv, cudaStream_t s);
