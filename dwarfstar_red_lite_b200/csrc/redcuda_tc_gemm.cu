@@ -14,18 +14,12 @@
 // hi*hi): they are double-buffered in tensor memory, read back with tcgen05.ld while the next block multiplies, and
 // summed over the blocks in fp32 registers with ordinary rounding.
 //
-// One CTA = 128 weight rows (MMA M) x TN tokens (MMA N) x all columns, K in stages of 64:
-//   all 8 warps   stage the raw quant blocks of the 128 rows one 256-column block ahead (cp.async, 16-byte pieces, the
-//                 planar layout kept, so the exact decoder of the GEMV path reads them unchanged), decode 128 x 64
-//                 weights from shared memory into the two fp16 digit tiles of the stage (canonical K-major core-matrix
-//                 layout, no swizzle) and copy the stage's activation digits (laid out for the MMA by k_tc_prep_x)
-//   one thread    issues 4 k-steps x 2 tcgen05.mma (kind::f16, fp32 accumulate): the activation tile holds the hi rows and
-//                 then the lo rows of its tokens, so A_hi x [B_hi | B_lo] is ONE instruction of N = 2 TN and A_lo x B_hi
-//                 one of N = TN; then a tcgen05.commit on the stage buffer's mbarrier; the MMAs of a stage run while the
-//                 warps decode the next one
-//   every block   tcgen05.ld of the finished block's two accumulators (lane = weight row, column = token) into fp32
-//                 register sums, one 256-column block behind the MMAs
-//   epilogue      scaling, stores
+// Two kernels per launch. k_tc_decode_w turns the launch's weights into fp16 digit tiles once (the exact decoder of the
+// GEMV path on raw blocks staged by cp.async, canonical K-major core-matrix layout, no swizzle; 4 bytes per weight in a
+// scratch that the caller sizes for its widest launch), so that the GEMM decodes nothing: before, every token tile of a
+// 2048-token chunk decoded the whole matrix again behind a block barrier per stage. k_tc_gemm then streams a stage's
+// weight digits and activation digits (laid out for the MMA by k_tc_prep_x) with two bulk copies on one mbarrier and is
+// split into roles (producer thread, MMA thread, drain warps) that meet only on mbarriers; see the kernel's own header.
 // Every wait on an mbarrier is bounded; on a timeout the kernel raises a flag, frees its tensor memory and returns.
 #define RC_PDL_DEFAULT 0
 #include "redcuda_common.cuh"
