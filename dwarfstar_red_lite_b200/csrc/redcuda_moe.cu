@@ -284,6 +284,7 @@ struct redcuda_moe {
     uint32_t *tc_err = nullptr; // timeout flag of the tcgen05 kernels
     __half *sh_xs = nullptr; float *sh_xinv = nullptr;   // shared expert on the tcgen05 GEMM: activation digits and inverse scales
     uint8_t *sh_wd = nullptr; float *sh_winv = nullptr;  // and the weight digits of one launch (gate + up, or down)
+    __half *rt_xs = nullptr; float *rt_xinv = nullptr; uint8_t *rt_wd = nullptr; float *rt_winv = nullptr;   // the same for the router logits of a large chunk
     bool tc_ok = false;         // the tcgen05 expert kernel can serve this layer's shapes
     bool tc_now = false;        // ... and serves the call in progress (set by moe_choose_path, read by the grouping and the launches)
     bool ws_shared = false;     // the workspace belongs to the caller (rc::moe_create_shared)
@@ -327,6 +328,15 @@ static bool moe_shared_tc(const redcuda_moe *m, uint32_t ntok) {
     const uint32_t min_tok = v ? (uint32_t)atoi(v) : 128u;
     return min_tok && ntok >= min_tok && rc_is_quant(m->d.type_sh) && m->d.ffn_sh <= m->d.hidden && m->d.hidden % 256u == 0 && m->d.ffn_sh % 256u == 0;
 }
+// Router logits on the tcgen05 GEMM: only with RC_ROUTER_TC_MIN=<tokens> (off by default). Measured on 2048-token chunks it
+// takes 78 us instead of the fp64 GEMM's 242 us, but the softmax turns the ABSOLUTE error of a logit into a RELATIVE error of
+// the expert weights: a split-fp16 product is good to about 1e-6 of sum |w x|, i.e. some 5e-5 of the weights, and the layer-48
+// error of a 64-token chunk of the deep test model rose from 4.4e-5 to 2.0e-4. The double-precision sums stay the default.
+static bool moe_router_tc(const redcuda_moe *m, uint32_t ntok) {
+    const char *v = getenv("RC_ROUTER_TC_MIN");
+    const uint32_t min_tok = v ? (uint32_t)atoi(v) : 0u;
+    return min_tok && ntok >= min_tok && m->router.type == RC_F32 && m->d.hidden % 256u == 0 && m->rt_wd;
+}
 // out[j][t][row] = W_j x[t] for one or two matrices that share x (x2: the input is SiLU(x) * x2)
 static int moe_shared_tc_gemm(redcuda_moe *m, uint32_t ntok, const float *x, const float *x2, uint32_t ncols, const DMat *w0, float *out0, const DMat *w1, float *out1,
                               const char *tag, cudaStream_t s) {
@@ -354,7 +364,16 @@ static int moe_gemv_pre(redcuda_moe *m, uint32_t ntok, const float *x, bool with
     };
     if (with_router) {
         // batches: the tiled fp64 GEMM (one pass over the router matrix per 16 tokens of a block, from shared memory)
-        if (ntok >= 8u && m->router.type == RC_F32 && m->d.hidden % 64u == 0) {
+        if (moe_router_tc(m, ntok)) {
+            // opt-in: the logits as a split-fp16 product on the tcgen05 GEMM (see moe_router_tc)
+            const uint32_t tn = tc_token_tile(ntok, tc_row_tiles(m->d.n_expert));
+            if (!launch_tc_prep_x(x, nullptr, m->d.hidden, ntok, m->d.hidden, tn, m->rt_xs, m->rt_xinv, s)) return 0;
+            TcArgs T{};
+            T.njobs = 1u; T.ncols = m->d.hidden; T.ntok = ntok; T.xs = m->rt_xs; T.x_inv = m->rt_xinv; T.err = m->tc_err;
+            T.wd = m->rt_wd; T.w_inv = m->rt_winv;
+            T.job[0] = TcJob{m->router.base, 0u, RC_F32, m->d.n_expert, m->logits, m->d.n_expert, 0u};
+            if (!launch_tc_gemm(T, tn, "moe_router_logits_tc", s)) return 0;
+        } else if (ntok >= 8u && m->router.type == RC_F32 && m->d.hidden % 64u == 0) {
             if (!launch_router_logits((const float *)m->router.base, x, m->d.hidden, ntok, m->d.n_expert, m->d.hidden, m->logits, s)) return 0;
         } else add(m->router, nullptr, m->logits, m->d.n_expert, GEMV_STORE);
     }
@@ -588,6 +607,10 @@ static size_t moe_ws_layout(const redcuda_moe_desc &d, redcuda_moe *m, uint8_t *
     {
         const uint32_t t_up = 2u * tc_row_tiles(d.ffn_sh), t_down = tc_row_tiles(d.hidden);
         put(r.sh_wd, std::max(tc_wd_bytes(t_up, d.hidden), tc_wd_bytes(t_down, d.ffn_sh))); put(r.sh_winv, (size_t)std::max(t_up, t_down) * 4u);
+    }
+    if (d.hidden % 256u == 0) {
+        put(r.rt_xs, tc_xs_halves((uint32_t)T, d.hidden, 128u) * 2u); put(r.rt_xinv, (T + 128u) * 4u);
+        put(r.rt_wd, tc_wd_bytes(tc_row_tiles(d.n_expert), d.hidden)); put(r.rt_winv, (size_t)tc_row_tiles(d.n_expert) * 4u);
     }
     if (m) { m->ticket = m->work + 2; m->tc_err = m->work + 3; }
     return w;

@@ -158,6 +158,24 @@ __device__ __forceinline__ void tc_decode_stage(const uint8_t *raw, uint8_t *abu
     }
 }
 
+// the same for a plain fp32 matrix (router weights): rows of ncols floats, stage = columns [col0, col0 + 64)
+__device__ __forceinline__ void tc_decode_stage_f32(const float *w, uint32_t ncols, uint32_t row0, uint32_t col0, uint8_t *abuf, uint32_t rows_live, float scale, uint32_t tid) {
+#pragma unroll
+    for (uint32_t it = 0; it < (TC_M * 8u) / TC_THREADS; ++it) {
+        const uint32_t item = it * TC_THREADS + tid, kc = item & 7u, r = item >> 3;      // 8 lanes read 256 contiguous bytes of a row
+        uint4 hi = make_uint4(0u, 0u, 0u, 0u), lo = hi;
+        if (r < rows_live) {
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(row0 + r) * ncols + col0 + kc * 8u));
+            const float4 b = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(row0 + r) * ncols + col0 + kc * 8u + 4u));
+            tc_split2(a.x * scale, a.y * scale, hi.x, lo.x); tc_split2(a.z * scale, a.w * scale, hi.y, lo.y);
+            tc_split2(b.x * scale, b.y * scale, hi.z, lo.z); tc_split2(b.z * scale, b.w * scale, hi.w, lo.w);
+        }
+        const uint32_t off = kc * (TC_M * 16u) + r * 16u;
+        *reinterpret_cast<uint4 *>(abuf + off) = hi;
+        *reinterpret_cast<uint4 *>(abuf + TC_A_DIGIT + off) = lo;
+    }
+}
+
 // x [ntok][ncols] fp32 (or SiLU(x) * x2 when x2 is given) -> fp16 digits in the order the GEMM stages consume them:
 // xs[token tile][k stage][k chunk of 8 (8)][digit hi/lo][token group of 8 (TN/8)][token in group (8)][8 halves];
 // x_inv[t] = 2^-e_t undoes the per-token scale. Tokens beyond ntok are zero. grid = token tiles * TN, block = 256
@@ -212,10 +230,21 @@ __global__ void __launch_bounds__(TC_THREADS) k_tc_decode_w(const __grid_constan
     const TcJob &J = A.job[ji];
     const uint32_t row0 = (blockIdx.x - J.tile0) * TC_M, c = blockIdx.y, bpr = A.ncols >> 8, nstage = A.ncols / TC_KS;
     const RcBooks bk{A.iq2, A.iq3s};
-    const unsigned short d = tc_stage_raw(J.type, J.w, J.nb, bpr, row0, J.nrows, c, raw, tid);
-    // power-of-two scale of the tile: the largest block scale d times the largest integer factor of the format
+    const bool f32 = J.type == RC_F32;
+    const unsigned short d = f32 ? (unsigned short)0 : tc_stage_raw(J.type, J.w, J.nb, bpr, row0, J.nrows, c, raw, tid);
+    // power-of-two scale of the tile: the largest block scale d times the largest integer factor of the format (fp32 rows:
+    // the largest magnitude of the tile itself)
     float dmax = 0.f;
-    {
+    if (f32) {
+        const float *wf = reinterpret_cast<const float *>(J.w);
+        const uint32_t rows = J.nrows - row0 < TC_M ? J.nrows - row0 : TC_M;
+        for (uint32_t i = tid; i < rows * (A.ncols >> 2); i += TC_THREADS) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(wf + (size_t)row0 * A.ncols) + i);
+            dmax = fmaxf(fmaxf(dmax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+        }
+        for (int o = 16; o; o >>= 1) dmax = fmaxf(dmax, __shfl_xor_sync(0xffffffffu, dmax, o));
+        if (lane == 0) red[warp] = dmax;
+    } else {
         const unsigned short *dp = reinterpret_cast<const unsigned short *>(J.w + tc_d_plane(J.type, J.nb));
         for (uint32_t i = tid; i < TC_M * bpr; i += TC_THREADS) {
             const uint32_t r = row0 + i / bpr;
@@ -224,14 +253,14 @@ __global__ void __launch_bounds__(TC_THREADS) k_tc_decode_w(const __grid_constan
         for (int o = 16; o; o >>= 1) dmax = fmaxf(dmax, __shfl_xor_sync(0xffffffffu, dmax, o));
         if (lane == 0) red[warp] = dmax;
     }
-    tc_put_d(J.type, raw, tid, d);
+    if (!f32) tc_put_d(J.type, raw, tid, d);
     asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
     dmax = 0.f;
     for (uint32_t w = 0; w < TC_WARPS; ++w) dmax = fmaxf(dmax, red[w]);
     int we = 0;
     {
-        const float bound = dmax * (J.type == RC_Q6_K ? 4096.f : J.type == RC_IQ2_XXS ? 256.f : 512.f);
+        const float bound = dmax * (f32 ? 1.f : J.type == RC_Q6_K ? 4096.f : J.type == RC_IQ2_XXS ? 256.f : 512.f);
         if (bound > 0.f && bound < INFINITY) { int ex; frexpf(bound, &ex); we = 15 - ex; }       // |w| * 2^we < 2^15
         we = we > 100 ? 100 : we < -100 ? -100 : we;
     }
@@ -241,7 +270,8 @@ __global__ void __launch_bounds__(TC_THREADS) k_tc_decode_w(const __grid_constan
 #pragma unroll 1
     for (uint32_t st = 0; st < 256u / TC_KS; ++st) {
         uint8_t *dst = A.wd + ((size_t)blockIdx.x * nstage + c * (256u / TC_KS) + st) * (2u * TC_A_DIGIT);
-        if (J.type == RC_Q6_K) tc_decode_stage<RC_Q6_K>(raw, dst, st * (TC_KS / 8u), rows_live, w_scale, bk, tid);
+        if (f32) tc_decode_stage_f32(reinterpret_cast<const float *>(J.w), A.ncols, row0, c * 256u + st * TC_KS, dst, rows_live, w_scale, tid);
+        else if (J.type == RC_Q6_K) tc_decode_stage<RC_Q6_K>(raw, dst, st * (TC_KS / 8u), rows_live, w_scale, bk, tid);
         else if (J.type == RC_IQ2_XXS) tc_decode_stage<RC_IQ2_XXS>(raw, dst, st * (TC_KS / 8u), rows_live, w_scale, bk, tid);
         else tc_decode_stage<RC_IQ3_S>(raw, dst, st * (TC_KS / 8u), rows_live, w_scale, bk, tid);
     }
@@ -449,7 +479,7 @@ int launch_tc_gemm(TcArgs &A, uint32_t tn, const char *tag, cudaStream_t s) {
     RC_REQUIRE(A.ncols % 256u == 0, "tc gemm: %u columns is not a multiple of 256", A.ncols);
     uint32_t tiles = 0;
     for (uint32_t j = 0; j < A.njobs; ++j) {
-        RC_REQUIRE(rc_is_quant(A.job[j].type), "tc gemm: matrix type %u is not a block-quantised format", A.job[j].type);
+        RC_REQUIRE(rc_is_quant(A.job[j].type) || A.job[j].type == RC_F32, "tc gemm: matrix type %u is neither a block-quantised format nor fp32", A.job[j].type);
         A.job[j].tile0 = tiles;
         tiles += (A.job[j].nrows + TC_M - 1u) / TC_M;
     }

@@ -173,10 +173,14 @@ def test_tiny_model_chunked_prefill(tmp_path, chunk, monkeypatch):
         eng.close()
 
 
-def test_midsize_model_chunked_prefill(tmp_path, monkeypatch):
+@pytest.mark.parametrize("router_tc", [None, "8"])
+def test_midsize_model_chunked_prefill(tmp_path, router_tc, monkeypatch):
     """Full-size head shapes: the chunk takes the tensor-core projections (Q6_K dense matrices, >= 3 tokens), the in-register
-    DeltaNet scan over 128-wide states and the batched GQA attention."""
+    DeltaNet scan over 128-wide states and the batched GQA attention. router_tc: the opt-in form of the router logits on
+    the tcgen05 GEMM (fp32 weight rows through the same digit decoder), here from 8 tokens on."""
     monkeypatch.setenv("RL_KV_F16", "1")
+    if router_tc:
+        monkeypatch.setenv("RC_ROUTER_TC_MIN", router_tc)
     dims = synth.ModelDims(n_layer=4, vocab=2048, n_expert=32, top_k=10, context=48)
     sm = synth.model(56, dims)
     path = str(tmp_path / "mid.gguf")
