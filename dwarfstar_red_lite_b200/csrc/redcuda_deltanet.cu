@@ -174,49 +174,57 @@ __global__ void __launch_bounds__(256) k_dn_state_tail(DnDims D, const float *__
 }
 
 // ---- sequence form: T consecutive tokens of ONE sequence (a prefill chunk) ----
-// k_dn_prep_seq   grid (2*groups + d_inner/S + 1, T): token t's conv window is the d_conv-1 samples before it (the conv
+// k_dn_prep_seq   grid (2*groups + d_inner/S + 1, T / 8): token t's conv window is the d_conv-1 samples before it (the conv
 //                 state for times before the chunk, chunk rows after); the state itself is rolled by k_dn_conv_roll
 // k_dn_state_seq  the delta rule over the T tokens with the state row held in registers: one read and one write of
 //                 the state per chunk instead of per token; the next token's q/k/v/beta/gate are fetched while the
 //                 current one is reduced
 // the tail kernel is k_dn_tail with the token as its batch index
-__global__ void k_dn_prep_seq(DnDims D, const float *__restrict__ conv_kernel, const float *__restrict__ dt_bias, const float *__restrict__ ssm_a,
+// a block serves DN_PREP_TOK consecutive tokens of its channel group (one token per block left the kernel bound by block
+// scheduling: 133,000 blocks of 128 threads for a 2048-token chunk)
+constexpr uint32_t DN_PREP_TOK = 8u;
+__global__ void k_dn_prep_seq(DnDims D, uint32_t T, const float *__restrict__ conv_kernel, const float *__restrict__ dt_bias, const float *__restrict__ ssm_a,
                               const float *__restrict__ qkv, const float *__restrict__ ba, const float *__restrict__ conv_state,
                               float *__restrict__ qk, float *__restrict__ v, float *__restrict__ beta, float *__restrict__ gate) {
     pdl_prologue();
-    __shared__ double red[32];
-    const uint32_t ti = blockIdx.y, tid = threadIdx.x, S = D.S, ns = D.d_conv - 1u;
+    __shared__ double red[2][32];
+    const uint32_t tid = threadIdx.x, S = D.S, ns = D.d_conv - 1u;
     const uint32_t n_qk = 2u * D.groups, n_v = D.d_inner / S;
+    const uint32_t t_begin = blockIdx.y * DN_PREP_TOK, t_end = min(T, t_begin + DN_PREP_TOK);
     if (blockIdx.x == n_qk + n_v) {
         const uint32_t width = D.rank / D.groups, stride = 2u * width;
-        for (uint32_t h = tid; h < D.rank; h += blockDim.x) {
-            const uint32_t g = h / width, l = h - g * width;
-            const float *b = ba + (size_t)ti * 2u * D.rank;
-            beta[(size_t)ti * D.rank + h] = (float)sigmoid_stable((double)b[g * stride + l]);
-            gate[(size_t)ti * D.rank + h] = (float)(softplus_stable((double)b[g * stride + width + l] + (double)dt_bias[h]) * (double)ssm_a[h]);
-        }
+        for (uint32_t ti = t_begin; ti < t_end; ++ti)
+            for (uint32_t h = tid; h < D.rank; h += blockDim.x) {
+                const uint32_t g = h / width, l = h - g * width;
+                const float *b = ba + (size_t)ti * 2u * D.rank;
+                beta[(size_t)ti * D.rank + h] = (float)sigmoid_stable((double)b[g * stride + l]);
+                gate[(size_t)ti * D.rank + h] = (float)(softplus_stable((double)b[g * stride + width + l] + (double)dt_bias[h]) * (double)ssm_a[h]);
+            }
         return;
     }
     const uint32_t c = blockIdx.x * S + tid;
     const float *cs = conv_state + (size_t)c * ns;
     const float *kr = conv_kernel + (size_t)c * D.d_conv;
-    double acc = 0.0;
-    for (uint32_t j = 0; j < ns; ++j) {
-        const int tau = (int)ti + (int)j - (int)ns;        // time of tap j relative to the chunk start
-        const float smp = tau < 0 ? cs[(int)ns + tau] : qkv[(size_t)tau * D.channels + c];
-        acc += (double)smp * (double)kr[j];
+    for (uint32_t ti = t_begin; ti < t_end; ++ti) {
+        double acc = 0.0;
+        for (uint32_t j = 0; j < ns; ++j) {
+            const int tau = (int)ti + (int)j - (int)ns;        // time of tap j relative to the chunk start
+            const float smp = tau < 0 ? cs[(int)ns + tau] : qkv[(size_t)tau * D.channels + c];
+            acc += (double)smp * (double)kr[j];
+        }
+        acc += (double)qkv[(size_t)ti * D.channels + c] * (double)kr[ns];
+        const float y = (float)(acc / (1.0 + exp(-acc)));
+        if (blockIdx.x >= n_qk) { v[(size_t)ti * D.d_inner + (c - n_qk * S)] = y; continue; }
+        double ss = (double)y * (double)y;
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        double *rd = red[ti & 1u];                             // alternating buffers: one barrier per token
+        if ((tid & 31u) == 0) rd[tid >> 5] = ss;
+        __syncthreads();
+        double tot = 0.0;
+        for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) tot += rd[w];
+        const double inv = 1.0 / fmax(sqrt(tot), (double)D.eps);
+        qk[(size_t)ti * n_qk * S + c] = (float)((double)y * inv);
     }
-    acc += (double)qkv[(size_t)ti * D.channels + c] * (double)kr[ns];
-    const float y = (float)(acc / (1.0 + exp(-acc)));
-    if (blockIdx.x >= n_qk) { v[(size_t)ti * D.d_inner + (c - n_qk * S)] = y; return; }
-    double ss = (double)y * (double)y;
-    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if ((tid & 31u) == 0) red[tid >> 5] = ss;
-    __syncthreads();
-    double tot = 0.0;
-    for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
-    const double inv = 1.0 / fmax(sqrt(tot), (double)D.eps);
-    qk[(size_t)ti * n_qk * S + c] = (float)((double)y * inv);
 }
 
 // conv state <- the last d_conv-1 samples of [state, chunk]; one thread per channel
@@ -702,7 +710,7 @@ int launch_deltanet_seq(const DnDims &D, uint32_t T, const float *conv_kernel, c
                "deltanet: inconsistent dimensions");
     if (!T) return 1;
     prof_begin("dn_prep_seq", s);
-    RC_LAUNCH((k_dn_prep_seq), dim3(2u * D.groups + D.d_inner / D.S + 1u, T), D.S, 0, s, D, conv_kernel, dt_bias, ssm_a, qkv, ba, (const float *)conv_state, qk, v, beta, gate);
+    RC_LAUNCH((k_dn_prep_seq), dim3(2u * D.groups + D.d_inner / D.S + 1u, (T + DN_PREP_TOK - 1u) / DN_PREP_TOK), D.S, 0, s, D, T, conv_kernel, dt_bias, ssm_a, qkv, ba, (const float *)conv_state, qk, v, beta, gate);
     prof_end(s);
     RC_LAUNCHED();
     prof_begin("dn_conv_roll", s);
