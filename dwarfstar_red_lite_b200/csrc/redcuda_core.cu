@@ -474,59 +474,86 @@ __global__ void __launch_bounds__(256) k_vec_sigmoid(const float *__restrict__ w
 // Router logits of a batch: logits[t][e] = (float) sum_k (double) x[t][k] * (double) w[e][k], F32 weights
 // (rl_quant_row_dot on an F32 row accumulates in double, native/redlite_native_quant_cpu.c:198-212, and the top-k that
 // follows must not depend on a summation order). The multi-token GEMV re-reads the matrix for every four tokens; this
-// is a small tiled fp64 GEMM instead: block = 16 tokens x 32 experts, K in tiles of 64 staged as doubles in shared
-// memory (the next tile is fetched into registers while the current one is multiplied); each of the 8 warps owns one
-// 8 x 8 tile of the result and advances it with the fp64 tensor-core instruction (mma.sync.m8n8k4.f64: one 8-byte
-// shared load per operand and lane per 256 multiply-adds; the row pitch of 68 doubles keeps those loads conflict-free).
-constexpr uint32_t RL_TT = 16u, RL_TE = 32u, RL_KT = 64u, RL_PITCH = RL_KT + 4u;
+// is a small tiled fp64 GEMM instead: block = 32 tokens x 64 experts, K in tiles of 64 staged as doubles in shared
+// memory (the next tile is fetched into registers while the current one is multiplied); each of the 8 warps owns a
+// 16 x 16 tile of the result as 2 x 2 fragments of the fp64 tensor-core instruction (mma.sync.m8n8k4.f64: four 8-byte
+// shared loads per four instructions; the row pitch of 68 doubles keeps those loads conflict-free). Batches that do
+// not fill half of that tile take a block of 16 tokens x 32 experts with one fragment per warp.
+constexpr uint32_t RL_KT = 64u, RL_PITCH = RL_KT + 4u;
+template <uint32_t FR>            // fragments per warp and direction: block = 16 FR tokens x 32 FR experts
 __global__ void __launch_bounds__(256) k_router_logits(const float *__restrict__ w, const float *__restrict__ x, uint32_t x_stride, uint32_t ntok,
                                                        uint32_t n_expert, uint32_t ncols, float *__restrict__ logits) {
     pdl_prologue();
-    __shared__ double xs[RL_TT * RL_PITCH], ws[RL_TE * RL_PITCH];
+    constexpr uint32_t TT = 16u * FR, TE = 32u * FR;
+    extern __shared__ __align__(16) double rl_smem[];
+    double *xs = rl_smem, *ws = rl_smem + TT * RL_PITCH;
     const uint32_t tid = threadIdx.x;
-    const uint32_t t0 = blockIdx.x * RL_TT, e0 = blockIdx.y * RL_TE;
-    // staging roles: the weight tile is 32 rows x 64 floats = 512 float4 (two per thread), the token tile 16 x 64 = 256 float4
-    const uint32_t wr = tid >> 4, wc = (tid & 15u) * 4u;               // rows wr and wr + 16
-    const uint32_t xr = tid >> 4, xc = (tid & 15u) * 4u;
-    const bool w_ok0 = e0 + wr < n_expert, w_ok1 = e0 + wr + 16u < n_expert, x_ok = t0 + xr < ntok;
-    const float *wp0 = w + (size_t)(e0 + wr) * ncols + wc, *wp1 = w + (size_t)(e0 + wr + 16u) * ncols + wc;
-    const float *xp = x + (size_t)(t0 + xr) * x_stride + xc;
+    const uint32_t t0 = blockIdx.x * TT, e0 = blockIdx.y * TE;
+    // staging roles: a tile row is 64 floats = 16 float4; thread -> (row tid / 16 + 16 i, float4 tid % 16)
+    const uint32_t sr = tid >> 4, sc = (tid & 15u) * 4u;
+    constexpr uint32_t NW = TE / 16u, NX = TT / 16u;
     const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 rw0 = w_ok0 ? __ldg(reinterpret_cast<const float4 *>(wp0)) : zero, rw1 = w_ok1 ? __ldg(reinterpret_cast<const float4 *>(wp1)) : zero;
-    float4 rx = x_ok ? *reinterpret_cast<const float4 *>(xp) : zero;
-    // warp -> (token half, expert quarter); lane -> A element (row lane/4, k lane%4), B element (k lane%4, column lane/4),
-    // C elements (row lane/4, columns 2*(lane%4), +1)
+    float4 rw[NW], rx[NX];
+    auto fetch = [&](uint32_t k0) {
+#pragma unroll
+        for (uint32_t i = 0; i < NW; ++i) rw[i] = e0 + sr + 16u * i < n_expert ? __ldg(reinterpret_cast<const float4 *>(w + (size_t)(e0 + sr + 16u * i) * ncols + k0 + sc)) : zero;
+#pragma unroll
+        for (uint32_t i = 0; i < NX; ++i) rx[i] = t0 + sr + 16u * i < ntok ? *reinterpret_cast<const float4 *>(x + (size_t)(t0 + sr + 16u * i) * x_stride + k0 + sc) : zero;
+    };
+    fetch(0u);
+    // warp -> (token group of 8 FR, expert group of 8 FR); lane -> A element (row lane/4, k lane%4), B element (k lane%4,
+    // column lane/4), C elements (row lane/4, columns 2*(lane%4), +1)
     const uint32_t warp = tid >> 5, lane = tid & 31u, th = warp >> 2, eq = warp & 3u, fr = lane >> 2, fk = lane & 3u;
-    double acc0 = 0.0, acc1 = 0.0;
+    double acc[FR][FR][2];
+#pragma unroll
+    for (uint32_t i = 0; i < FR; ++i)
+#pragma unroll
+        for (uint32_t j = 0; j < FR; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
     for (uint32_t k0 = 0; k0 < ncols; k0 += RL_KT) {
         __syncthreads();                                   // the previous tile is no longer read
-        double *d0 = ws + wr * RL_PITCH + wc, *d1 = ws + (wr + 16u) * RL_PITCH + wc, *dx = xs + xr * RL_PITCH + xc;
-        d0[0] = rw0.x; d0[1] = rw0.y; d0[2] = rw0.z; d0[3] = rw0.w;
-        d1[0] = rw1.x; d1[1] = rw1.y; d1[2] = rw1.z; d1[3] = rw1.w;
-        dx[0] = rx.x; dx[1] = rx.y; dx[2] = rx.z; dx[3] = rx.w;
-        __syncthreads();
-        if (k0 + RL_KT < ncols) {
-            rw0 = w_ok0 ? __ldg(reinterpret_cast<const float4 *>(wp0 + k0 + RL_KT)) : zero;
-            rw1 = w_ok1 ? __ldg(reinterpret_cast<const float4 *>(wp1 + k0 + RL_KT)) : zero;
-            rx = x_ok ? *reinterpret_cast<const float4 *>(xp + k0 + RL_KT) : zero;
-        }
-        const double *a = xs + (th * 8u + fr) * RL_PITCH + fk, *b = ws + (eq * 8u + fr) * RL_PITCH + fk;
 #pragma unroll
-        for (uint32_t kk = 0; kk < RL_KT; kk += 4u)
-            asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};" : "+d"(acc0), "+d"(acc1) : "d"(a[kk]), "d"(b[kk]));
+        for (uint32_t i = 0; i < NW; ++i) { double *d = ws + (sr + 16u * i) * RL_PITCH + sc; d[0] = rw[i].x; d[1] = rw[i].y; d[2] = rw[i].z; d[3] = rw[i].w; }
+#pragma unroll
+        for (uint32_t i = 0; i < NX; ++i) { double *d = xs + (sr + 16u * i) * RL_PITCH + sc; d[0] = rx[i].x; d[1] = rx[i].y; d[2] = rx[i].z; d[3] = rx[i].w; }
+        __syncthreads();
+        if (k0 + RL_KT < ncols) fetch(k0 + RL_KT);
+        const double *a = xs + (th * 8u * FR + fr) * RL_PITCH + fk, *b = ws + (eq * 8u * FR + fr) * RL_PITCH + fk;
+#pragma unroll
+        for (uint32_t kk = 0; kk < RL_KT; kk += 4u) {
+            double av[FR], bv[FR];
+#pragma unroll
+            for (uint32_t i = 0; i < FR; ++i) { av[i] = a[i * 8u * RL_PITCH + kk]; bv[i] = b[i * 8u * RL_PITCH + kk]; }
+#pragma unroll
+            for (uint32_t i = 0; i < FR; ++i)
+#pragma unroll
+                for (uint32_t j = 0; j < FR; ++j)
+                    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};" : "+d"(acc[i][j][0]), "+d"(acc[i][j][1]) : "d"(av[i]), "d"(bv[j]));
+        }
     }
-    const uint32_t t = t0 + th * 8u + fr, e = e0 + eq * 8u + 2u * fk;
-    if (t < ntok) {
-        if (e < n_expert) logits[(size_t)t * n_expert + e] = (float)acc0;
-        if (e + 1u < n_expert) logits[(size_t)t * n_expert + e + 1u] = (float)acc1;
-    }
+#pragma unroll
+    for (uint32_t i = 0; i < FR; ++i)
+#pragma unroll
+        for (uint32_t j = 0; j < FR; ++j) {
+            const uint32_t t = t0 + (th * FR + i) * 8u + fr, e = e0 + (eq * FR + j) * 8u + 2u * fk;
+            if (t < ntok) {
+                if (e < n_expert) logits[(size_t)t * n_expert + e] = (float)acc[i][j][0];
+                if (e + 1u < n_expert) logits[(size_t)t * n_expert + e + 1u] = (float)acc[i][j][1];
+            }
+        }
 }
 
 int launch_router_logits(const float *w, const float *x, uint32_t x_stride, uint32_t ntok, uint32_t n_expert, uint32_t ncols, float *logits, cudaStream_t stream) {
     RC_REQUIRE(ncols % RL_KT == 0 && x_stride % 4u == 0, "router logits: %u columns (stride %u) is not a multiple of %u", ncols, x_stride, RL_KT);
     if (!ntok) return 1;
     prof_begin("moe_router_logits", stream);
-    RC_LAUNCH((k_router_logits), dim3((ntok + RL_TT - 1u) / RL_TT, (n_expert + RL_TE - 1u) / RL_TE), 256, 0, stream, w, x, x_stride, ntok, n_expert, ncols, logits);
+    if (ntok >= 256u && n_expert >= 64u) {
+        const size_t smem = (size_t)(32u + 64u) * RL_PITCH * sizeof(double);
+        RC_CUDA(cudaFuncSetAttribute(k_router_logits<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        RC_LAUNCH((k_router_logits<2>), dim3((ntok + 31u) / 32u, (n_expert + 63u) / 64u), 256, smem, stream, w, x, x_stride, ntok, n_expert, ncols, logits);
+    } else {
+        const size_t smem = (size_t)(16u + 32u) * RL_PITCH * sizeof(double);
+        RC_LAUNCH((k_router_logits<1>), dim3((ntok + 15u) / 16u, (n_expert + 31u) / 32u), 256, smem, stream, w, x, x_stride, ntok, n_expert, ncols, logits);
+    }
     prof_end(stream);
     RC_LAUNCHED();
     return 1;

@@ -225,6 +225,15 @@ def test_moe_chunk_on_tcgen05_small(monkeypatch):
     _check_moe(layer, x, expect_kernel="moe_gateup_tc")
 
 
+def test_router_logits_of_a_large_batch_are_the_double_sums():
+    """300 tokens x 96 experts: the fp64 GEMM with 32 x 64 block tiles (ragged in both directions) must give the logits of
+    the oracle's double-precision row dots bit for bit, and so the same selection."""
+    dims = synth.MoeDims(hidden=512, n_expert=96, top_k=4, ffn=256, ffn_sh=256)
+    layer = synth.moe_layer(57, dims, expert_scale=0.5)
+    x = np.random.default_rng(8).normal(0, 1, size=(300, dims.hidden)).astype(np.float32)
+    _check_moe(layer, x, rows=list(range(0, 300, 7)) + [299], expect_kernel="moe_router_logits")
+
+
 def test_moe_chunk_on_tcgen05_full_size(full_layer, monkeypatch):
     """1024 tokens through the full-size layer with Zipf-skewed routing: the popular experts see hundreds of pairs (many
     work items each), the tail ones a handful. Every 16th token is compared with the oracle."""
