@@ -866,9 +866,13 @@ def main():
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--ep-placement", default="interleaved", choices=["interleaved", "contiguous"], help="N > 1: which rank holds which expert")
     ap.add_argument("--ep-impl", default="c", choices=["c", "python"], help="N > 1: the library's one-call step, or the per-operation Python loop")
-    ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"], help="N > 1, --ep-impl c: exchange through peer memory or through NCCL")
+    ap.add_argument("--ep-exchange", default="auto", choices=["auto", "peer", "nccl"],
+                    help="N > 1, --ep-impl c: exchange through peer memory or through NCCL; auto = peer memory up to 4 ranks, NCCL above "
+                         "(measured: 0.85 / 0.80 against 0.75 / 0.72 at 2 / 4 ranks, 0.57 against 0.60 at 8, where waits inside kernels make rank skew cost more)")
     ap.add_argument("--ep-permute", action="store_true", help="N > 1: draw the routing over a random permutation of the expert ids")
     args = ap.parse_args()
+    if args.ep_exchange == "auto":
+        args.ep_exchange = "peer" if int(os.environ.get("WORLD_SIZE", "1")) <= 4 else "nccl"
     if args.workload == "decode48":
         args.warmup = max(args.warmup, 1)
         return run_decode48(args)
