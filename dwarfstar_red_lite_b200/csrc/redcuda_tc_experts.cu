@@ -15,7 +15,7 @@
 // Accumulation follows k_tc_gemm: the tensor core adds into fp32 without rounding to nearest, so the accumulators cover
 // one 256-column block only (one for A*hi, one for A*lo), double-buffered in tensor memory and summed in fp32 registers.
 //
-// One CTA = one item x one 128-row tile of one matrix, K in stages of 64 columns, the warps split into roles that hand
+// One CTA = one item x one 128-row tile of one matrix, K in stages of 128 columns, the warps split into roles that hand
 // tiles to each other through mbarriers (see k_tc_experts). Blocks beyond the item count leave at once. Every wait is
 // bounded: on a timeout the role raises a flag that stops the other roles at their next wait; the CTA waits (bounded) for
 // its own copies, frees its tensor memory, raises the launch's flag and the sticky status word, and returns.
@@ -111,7 +111,7 @@ __host__ __device__ uint32_t tcx_tiles_per_cta(uint32_t nrows, uint32_t ncols) {
 __device__ __forceinline__ void tcx_arrive(uint32_t mbar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(mbar) : "memory"); }
 
 // Roles of the 16 warps (no block-wide barrier inside the K loop; the roles meet on mbarriers):
-//   warp 0          lane 0 issues the MMAs of a stage once its weight tile and its activation tile are full, and commits
+//   warp 0          lane 0 issues the 8 MMAs of a stage once its weight tiles and its activation tiles are full, and commits
 //                   their completion to the "empty" barriers of both tiles (and, at the end of a 256-column block, to the
 //                   block's "accumulators full" barrier)
 //   warps 1-2       gather the activation pieces of stage after stage (cp.async, up to NB stages ahead of the MMAs)
@@ -119,7 +119,10 @@ __device__ __forceinline__ void tcx_arrive(uint32_t mbar) { asm volatile("mbarri
 //   warps 4-11      decode the weights of a stage into the fp16 tile (two (row, 8-column-pair) items per thread)
 //   warps 12-15     read a finished block's accumulators out of tensor memory (warp w owns lanes 32 (w % 4) ..) and add
 //                   them, scaled by d / 8, to their fp32 register sums; at the end they store the results
-constexpr uint32_t TCX_NB = 4u;               // activation stage buffers
+constexpr uint32_t TCX_NB = 3u;               // activation stage buffers
+// A stage is 128 columns: two 64-column operand tiles (the 128-byte swizzle spans 64 halves) side by side in one buffer, so the
+// issuing thread's waits, fence and commits - which, not the tensor pipe, bound this kernel - are paid once per 8 MMAs.
+constexpr uint32_t TCX_KS = 128u, TCX_SUBS = TCX_KS / TC_KS, TCX_SPB = 256u / TCX_KS;      // stage width, tiles per stage, stages per 256-column block
 constexpr uint32_t TCX_W_GATHER = 1u, TCX_N_GATHER = 2u, TCX_W_RAW = 3u, TCX_W_DECODE = 4u, TCX_N_DECODE = 8u, TCX_W_DRAIN = 12u;
 
 template <int TN>
@@ -129,7 +132,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_experts(const __grid_const
     if (item >= *A.n_items) return;                       // the grid covers the largest possible item count
     extern __shared__ __align__(1024) uint8_t smem[];
     constexpr uint32_t NB = TCX_NB;
-    constexpr uint32_t B_DIGIT = (uint32_t)TN * TC_KS * 2u, A_BUF = TC_A_DIGIT, B_BUF = 2u * B_DIGIT;
+    constexpr uint32_t B_DIGIT = (uint32_t)TN * TC_KS * 2u, A_SUB = TC_A_DIGIT, B_SUB = 2u * B_DIGIT, A_BUF = TCX_SUBS * A_SUB, B_BUF = TCX_SUBS * B_SUB;
     constexpr uint32_t TMEM_COLS = 4u * (uint32_t)TN;     // two blocks in flight x (A*hi accumulator, A*lo accumulator)
     static_assert(TN == 64, "the role split below is laid out for 64-token items");
     __shared__ __align__(8) uint64_t a_full[2], a_empty[2], b_full[NB], b_empty[NB], acc_full[2], acc_empty[2], raw_full[2], raw_empty[2];
@@ -149,7 +152,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_experts(const __grid_const
     }
     // A CTA takes tpc consecutive 128-row tiles of one matrix, one after the other, so that 8 blocks of 256 columns pass
     // through it whatever the row length: the set-up and the pipeline fill are paid once per CTA, not once per short row.
-    const uint32_t bpr = A.ncols >> 8, kstage = A.ncols / TC_KS, tpc = tcx_tiles_per_cta(A.nrows, A.ncols);
+    const uint32_t bpr = A.ncols >> 8, kstage = A.ncols / TCX_KS, tpc = tcx_tiles_per_cta(A.nrows, A.ncols);
     const uint32_t groups = A.nrows / TC_M / tpc, mat = blockIdx.x / groups, rt0 = (blockIdx.x - mat * groups) * tpc;
     const uint32_t nstage = tpc * kstage, nblk = tpc * bpr;           // stages and 256-column blocks of the whole CTA
     const uint8_t *wrec = A.w[mat] + (uint64_t)e * A.mat_bytes + (uint64_t)(rt0 * 8u) * bpr * NIB_REC;    // record (16-row tile 8 rt0 + j, block c) at (j * bpr + c) * NIB_REC
@@ -223,23 +226,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_experts(const __grid_const
                 return done ? true : wait(bar, parity);
             };
             for (uint32_t s = 0; s < nstage; ++s) {
-                const uint32_t b = s & 1u, jb = s % NB, c = s >> 2;
+                const uint32_t b = s & 1u, jb = s % NB, c = s / TCX_SPB, sb = s % TCX_SPB;
                 if (!ready(&a_full[b], (s >> 1) & 1u) || !ready(&b_full[jb], (s / NB) & 1u)) break;
-                if ((s & 3u) == 0u && c >= 2u && !ready(&acc_empty[c & 1u], ((c >> 1) - 1u) & 1u)) break;
+                if (sb == 0u && c >= 2u && !ready(&acc_empty[c & 1u], ((c >> 1) - 1u) & 1u)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t da = desc0 + ((smem_u32(a_base + b * A_BUF) >> 4) & 0x3fffu), db = desc0 + ((smem_u32(b_base + jb * B_BUF) >> 4) & 0x3fffu);
                 const uint32_t d_acc = tmem + (c & 1u) * 2u * (uint32_t)TN;
 #pragma unroll
-                for (uint32_t kk = 0; kk < TC_KS / 16u; ++kk)
-                    tc_mma(d_acc, da + 2u * kk, db + 2u * kk, idesc, ((s & 3u) | kk) ? 1u : 0u);       // + 32 bytes per k-step; a block's first MMA overwrites
+                for (uint32_t kk = 0; kk < TCX_KS / 16u; ++kk) {     // + 32 bytes per k-step inside a tile, the next tile after four; a block's first MMA overwrites
+                    const uint32_t sub = kk >> 2, k4 = kk & 3u;
+                    tc_mma(d_acc, da + sub * (A_SUB >> 4) + 2u * k4, db + sub * (B_SUB >> 4) + 2u * k4, idesc, (sb | kk) ? 1u : 0u);
+                }
                 tc_commit(smem_u32(&a_empty[b]));
                 tc_commit(smem_u32(&b_empty[jb]));
-                if ((s & 3u) == 3u) tc_commit(smem_u32(&acc_full[c & 1u]));
+                if (sb == TCX_SPB - 1u) tc_commit(smem_u32(&acc_full[c & 1u]));
             }
         }
     } else if (warp < TCX_W_RAW) {
         // ------------------------------------------------------------------ activation gather (64 threads)
-        // thread g: k chunk g % 8 of the token slots g / 8 + 8 m (m < 8), both digits: 16 pieces of 16 bytes per stage
+        // thread g: k chunk g % 8 of the token slots g / 8 + 8 m (m < 8), both digits, both tiles of the stage: 32 pieces of 16 bytes per stage
         const uint32_t g = tid - TCX_W_GATHER * 32u, kc = g & 7u, ttb = g >> 3;
         const __half *src[8]; uint32_t live = 0u;
 #pragma unroll
@@ -252,15 +257,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_experts(const __grid_const
         auto issue = [&](uint32_t s) {
             const uint32_t bb = smem_u32(b_base + (s % NB) * B_BUF) + dst0;
 #pragma unroll
-            for (uint32_t m = 0; m < 8u; ++m) {
-                const uint32_t sz = (live >> m) & 1u ? 16u : 0u;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(bb + m * 1024u), "l"(src[m] + (s % kstage) * TC_KS), "r"(sz) : "memory");
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(bb + B_DIGIT + m * 1024u), "l"(src[m] + A.ncols + (s % kstage) * TC_KS), "r"(sz) : "memory");
-            }
+            for (uint32_t sub = 0; sub < TCX_SUBS; ++sub)
+#pragma unroll
+                for (uint32_t m = 0; m < 8u; ++m) {
+                    const uint32_t sz = (live >> m) & 1u ? 16u : 0u;
+                    const __half *sp = src[m] + (s % kstage) * TCX_KS + sub * TC_KS;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(bb + sub * B_SUB + m * 1024u), "l"(sp), "r"(sz) : "memory");
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(bb + sub * B_SUB + B_DIGIT + m * 1024u), "l"(sp + A.ncols), "r"(sz) : "memory");
+                }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        // stage s is requested AHEAD stages before it is handed over, so that many groups are always in flight
-        constexpr uint32_t AHEAD = 2u;
+        // stage s is requested AHEAD stages before it is handed over; AHEAD <= NB - 2, so that handing over stage s - AHEAD never
+        // waits for the MMAs of the stage just before it (the wait at the top of an iteration is for stage s - NB)
+        constexpr uint32_t AHEAD = NB - 2u;
         bool ok = true;
         for (uint32_t s = 0; s < nstage + AHEAD && ok; ++s) {
             if (s < nstage) {
@@ -298,28 +307,31 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_tc_experts(const __grid_const
         // ------------------------------------------------------------------ weight decode (256 threads)
         const uint32_t dw = warp - TCX_W_DECODE, t = lane & 3u;
         for (uint32_t s = 0; s < nstage; ++s) {
-            const uint32_t b = s & 1u, c = s >> 2;
-            if ((s & 3u) == 0u && !wait(&raw_full[c & 1u], (c >> 1) & 1u)) break;
+            const uint32_t b = s & 1u, c = s / TCX_SPB, sb = s % TCX_SPB;
+            if (sb == 0u && !wait(&raw_full[c & 1u], (c >> 1) & 1u)) break;
             if (s >= 2u && !wait(&a_empty[b], ((s >> 1) - 1u) & 1u)) break;
             const uint8_t *raw = raw_base + (c & 1u) * TCX_RAW;
             uint8_t *abuf = a_base + b * A_BUF;
-            const uint32_t kg0 = 2u * (s & 3u);
+            const uint32_t kg0 = 4u * sb;                 // the stage's four 32-column groups
             
 #pragma unroll
             for (uint32_t q = 0; q < 2u; ++q) {
-                // rows 8 dw + lane / 4 and + 64; code words (t, kg0) and (t, kg0 + 1) of the row: columns 32 (kg - kg0) + 8 t of the stage
+                // rows 8 dw + lane / 4 and + 64; code words (t, kg0 .. kg0 + 3) of the row (one 16-byte piece): columns
+                // 32 (kg - kg0) + 8 t of the stage, i.e. chunk t or t + 4 of tile (kg - kg0) / 2
                 const uint32_t r = q * 64u + dw * 8u + (lane >> 2), rr = r & 15u;
                 const uint8_t *rec = raw + (r >> 4) * NIB_REC;
-                const uint2 wd = *reinterpret_cast<const uint2 *>(rec + nib_code_off(rr, t, kg0));
-                const uint32_t sc2 = *reinterpret_cast<const unsigned short *>(rec + NIB_SC_OFF + rr * 8u + kg0);
-                *reinterpret_cast<uint4 *>(abuf + tcx_sw128(r, t)) = tcx_decode8(wd.x, sc2 & 255u);
-                *reinterpret_cast<uint4 *>(abuf + tcx_sw128(r, t + 4u)) = tcx_decode8(wd.y, sc2 >> 8);
+                const uint4 wd = *reinterpret_cast<const uint4 *>(rec + nib_code_off(rr, t, kg0));
+                const uint32_t sc4 = *reinterpret_cast<const uint32_t *>(rec + NIB_SC_OFF + rr * 8u + kg0);
+                *reinterpret_cast<uint4 *>(abuf + tcx_sw128(r, t)) = tcx_decode8(wd.x, sc4 & 255u);
+                *reinterpret_cast<uint4 *>(abuf + tcx_sw128(r, t + 4u)) = tcx_decode8(wd.y, (sc4 >> 8) & 255u);
+                *reinterpret_cast<uint4 *>(abuf + A_SUB + tcx_sw128(r, t)) = tcx_decode8(wd.z, (sc4 >> 16) & 255u);
+                *reinterpret_cast<uint4 *>(abuf + A_SUB + tcx_sw128(r, t + 4u)) = tcx_decode8(wd.w, sc4 >> 24);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the tensor core
             __syncwarp();
             if (lane == 0) {
                 tcx_arrive(smem_u32(&a_full[b]));
-                if ((s & 3u) == 3u) tcx_arrive(smem_u32(&raw_empty[c & 1u]));     // this warp has read the block's records for the last time
+                if (sb == TCX_SPB - 1u) tcx_arrive(smem_u32(&raw_empty[c & 1u]));     // this warp has read the block's records for the last time
                 
             }
         }
@@ -390,7 +402,7 @@ int launch_tc_experts(TcxArgs &A, uint32_t max_items, const char *tag, cudaStrea
     RC_REQUIRE((A.nmat == 1u || A.nmat == 2u) && A.w[0] && (A.nmat == 1u || A.w[1]) && max_items && A.x_div, "tc experts: bad matrix count or empty launch");
     RC_REQUIRE(max_items <= 65535u, "tc experts: %u work items exceed the grid", max_items);
     constexpr uint32_t TN = TCX_TN;
-    const size_t smem = 2u * (size_t)TC_A_DIGIT + (size_t)TCX_NB * 2u * TN * TC_KS * 2u + 2u * (size_t)TCX_RAW;
+    const size_t smem = 2u * (size_t)TCX_SUBS * TC_A_DIGIT + (size_t)TCX_NB * TCX_SUBS * 2u * TN * TC_KS * 2u + 2u * (size_t)TCX_RAW;
     const dim3 grid(A.nmat * (A.nrows / TC_M / tcx_tiles_per_cta(A.nrows, A.ncols)), max_items);
     prof_begin(tag, s);
     RC_CUDA(cudaFuncSetAttribute(k_tc_experts<(int)TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
