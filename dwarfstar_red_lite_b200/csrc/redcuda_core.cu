@@ -641,6 +641,15 @@ int redcuda_set_codebooks(const uint8_t *iq2xxs_grid, uint32_t iq2xxs_bytes, con
     return 1;
 }
 
+int redcuda_set_codebooks_ext(const uint32_t *iq3xxs_grid, uint32_t iq3xxs_count, const uint64_t *iq2s_grid, uint32_t iq2s_count,
+                              const int8_t *iq4nl_values, uint32_t iq4nl_count) {
+    if (!require_device()) return 0;
+    RC_REQUIRE(iq3xxs_grid && iq3xxs_count == 256u, "IQ3_XXS grid must be 256 entries");
+    RC_REQUIRE(iq2s_grid && iq2s_count == 1024u, "IQ2_S grid must be 1024 entries");
+    RC_REQUIRE(iq4nl_values && iq4nl_count == 16u, "IQ4_NL values must be 16 entries");
+    return kq_set_iq_tables(iq3xxs_grid, iq2s_grid, iq4nl_values);
+}
+
 int redcuda_quant_dequant_rows(uint32_t type, const uint8_t *rows, uint32_t nrows, uint32_t ncols, float *out) {
     if (!require_device()) return 0;
     RC_REQUIRE(rows && out && nrows && ncols, "dequant: null or empty argument");

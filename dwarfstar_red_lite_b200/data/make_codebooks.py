@@ -8,6 +8,13 @@ oracle/_ref/libredlite_ref.so, then stores them as raw little-endian bytes:
     [0, 2048)      IQ2_XXS grid, 256 entries x 8 magnitudes (uint8)
     [2048, 4096)   IQ3_S grid, 512 entries x 4 packed magnitudes (uint32)
 
+and, for the further types of the same family (IQ3_XXS, IQ2_S, IQ4_XS: native/redlite_native_iq3.c:53-110), a second
+file codebooks_iq3family.bin:
+
+    [0, 1024)      IQ3_XXS grid, 256 entries x 4 packed magnitudes (uint32)
+    [1024, 9216)   IQ2_S grid, 1024 entries x 8 packed magnitudes (uint64)
+    [9216, 9232)   IQ4_NL values, 16 x int8
+
 Usage: make -C oracle ref && python dwarfstar_red_lite_b200/data/make_codebooks.py
 """
 import ctypes
@@ -28,3 +35,18 @@ iq3s = bytes(ctypes.cast(p, ctypes.POINTER(ctypes.c_uint8 * 2048)).contents)
 with open(os.path.join(here, "codebooks.bin"), "wb") as f:
     f.write(bytes(grid) + iq3s)
 print("wrote codebooks.bin", 4096, "bytes")
+
+
+def table(name, ctype, count):
+    fn = getattr(ref, name)
+    fn.restype = ctypes.POINTER(ctype)
+    n = ctypes.c_size_t(0)
+    p = fn(ctypes.byref(n))
+    assert n.value == count, (name, n.value)
+    return bytes(ctypes.cast(p, ctypes.POINTER(ctypes.c_uint8 * (count * ctypes.sizeof(ctype)))).contents)
+
+
+fam = table("redcuda_ref_iq3xxs_grid", ctypes.c_uint32, 256) + table("redcuda_ref_iq2s_grid", ctypes.c_uint64, 1024) + table("redcuda_ref_iq4nl_values", ctypes.c_int8, 16)
+with open(os.path.join(here, "codebooks_iq3family.bin"), "wb") as f:
+    f.write(fam)
+print("wrote codebooks_iq3family.bin", len(fam), "bytes")

@@ -14,7 +14,7 @@ LIB_PATH = os.environ.get("REDCUDA_LIB") or os.path.join(HERE, "libredcuda.so") 
 u8p, f32p, u32p = C.POINTER(C.c_uint8), C.POINTER(C.c_float), C.POINTER(C.c_uint32)
 
 EXPORTS = [
-    "redcuda_abi_version", "redcuda_last_error", "redcuda_device_count", "redcuda_set_device", "redcuda_set_codebooks",
+    "redcuda_abi_version", "redcuda_last_error", "redcuda_device_count", "redcuda_set_device", "redcuda_set_codebooks", "redcuda_set_codebooks_ext",
     "redcuda_quant_dequant_rows", "redcuda_nib_dequant_rows", "redcuda_quant_matvec", "redcuda_quant_matmul_tc", "redcuda_router_select_softmax_topk", "redcuda_deltanet_step",
     "redcuda_deltanet_step_noalloc",
     "redcuda_moe_create", "redcuda_moe_destroy", "redcuda_moe_resident_bytes", "redcuda_moe_forward",
@@ -99,6 +99,7 @@ def lib():
     L.redcuda_profile_report.argtypes = [C.c_char_p, C.c_size_t]
     L.redcuda_set_device.argtypes = [C.c_int]
     L.redcuda_set_codebooks.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32]
+    L.redcuda_set_codebooks_ext.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32]
     _lib = L
     return L
 
@@ -128,8 +129,26 @@ def default_codebooks() -> tuple[np.ndarray, np.ndarray]:
     return raw[:2048].copy(), raw[2048:].view(np.uint32).copy()
 
 
+def default_codebooks_ext() -> tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """IQ3_XXS grid (256 x uint32), IQ2_S grid (1024 x uint64), IQ4_NL values (16 x int8) from data/codebooks_iq3family.bin."""
+    raw = np.fromfile(os.path.join(HERE, "data", "codebooks_iq3family.bin"), dtype=np.uint8)
+    return raw[:1024].view(np.uint32).copy(), raw[1024:9216].view(np.uint64).copy(), raw[9216:9232].view(np.int8).copy()
+
+
+def set_codebooks_ext(iq3xxs_grid: np.ndarray | None = None, iq2s_grid: np.ndarray | None = None, iq4nl_values: np.ndarray | None = None):
+    """Hand the tables of IQ3_XXS / IQ2_S / IQ4_XS to the current device (defaults: data/codebooks_iq3family.bin)."""
+    if iq3xxs_grid is None or iq2s_grid is None or iq4nl_values is None:
+        iq3xxs_grid, iq2s_grid, iq4nl_values = default_codebooks_ext()
+    a = np.ascontiguousarray(iq3xxs_grid, np.uint32)
+    b = np.ascontiguousarray(iq2s_grid, np.uint64)
+    c = np.ascontiguousarray(iq4nl_values, np.int8)
+    _check(lib().redcuda_set_codebooks_ext(a.ctypes.data, a.size, b.ctypes.data, b.size, c.ctypes.data, c.size))
+
+
 def set_codebooks(iq2xxs_grid: np.ndarray | None = None, iq3s_grid: np.ndarray | None = None, device: int | None = None):
-    """Hand the IQ2_XXS / IQ3_S codebooks to the current device (defaults: data/codebooks.bin)."""
+    """Hand the IQ2_XXS / IQ3_S codebooks to the current device (defaults: data/codebooks.bin); with the defaults the tables
+    of IQ3_XXS / IQ2_S / IQ4_XS go along."""
+    ext = iq2xxs_grid is None or iq3s_grid is None
     if iq2xxs_grid is None or iq3s_grid is None:
         iq2xxs_grid, iq3s_grid = default_codebooks()
     g2 = np.ascontiguousarray(iq2xxs_grid, np.uint8)
@@ -137,6 +156,8 @@ def set_codebooks(iq2xxs_grid: np.ndarray | None = None, iq3s_grid: np.ndarray |
     if device is not None:
         _check(lib().redcuda_set_device(C.c_int(device)))
     _check(lib().redcuda_set_codebooks(g2.ctypes.data, g2.size, g3.ctypes.data, g3.size))
+    if ext:
+        set_codebooks_ext()
     _books_devices.add(-1 if device is None else device)
 
 

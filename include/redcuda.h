@@ -42,13 +42,23 @@ int redcuda_set_device(int device);
  */
 int redcuda_set_codebooks(const uint8_t *iq2xxs_grid, uint32_t iq2xxs_bytes, const uint32_t *iq3s_grid, uint32_t iq3s_count);
 
+/*
+ * Tables of three further types of the same family (rl_iq3_group8, native/redlite_native_iq3.c:53-110): iq3xxs_grid =
+ * 256 packed entries (rl_iq3xxs_grid), iq2s_grid = 1024 packed entries (rl_iq2s_grid), iq4nl_values = 16 values
+ * (rl_kvalues_iq4nl), all of native/redlite_native_iq3_tables.h. Once per device before IQ3_XXS (18), IQ2_S (22) or
+ * IQ4_XS (23) rows are handed to redcuda_quant_dequant_rows / redcuda_quant_matvec.
+ */
+int redcuda_set_codebooks_ext(const uint32_t *iq3xxs_grid, uint32_t iq3xxs_count, const uint64_t *iq2s_grid, uint32_t iq2s_count,
+                              const int8_t *iq4nl_values, uint32_t iq4nl_count);
+
 /* ------------------------------------------------------------------------------------------------------------
  * Stage entry points (host pointers, synchronous). Each replaces one CPU reference function of the path.
  * ---------------------------------------------------------------------------------------------------------- */
 
 /* rl_quant_dequant_row (native/redlite_native_quant_cpu.c:155-196) for nrows rows at once: out[nrows][ncols].
  * ggml types: 0 F32, 1 F16, 14 Q6_K, 16 IQ2_XXS, 21 IQ3_S (the types of the decode path), and 8 Q8_0, 10 Q2_K, 12 Q4_K,
- * 13 Q5_K (cases 8 / 10 / 12 / 13 of the same reference function, :50-128), which this entry point and redcuda_quant_matvec
+ * 13 Q5_K (cases 8 / 10 / 12 / 13 of the same reference function, :50-128) and 18 IQ3_XXS, 22 IQ2_S, 23 IQ4_XS (its
+ * rl_iq3_dequant_row branch, :193; native/redlite_native_iq3.c:53-118), which this entry point and redcuda_quant_matvec
  * serve but the engine and the expert kernels do not yet. Values are bit-identical to the reference's. */
 int redcuda_quant_dequant_rows(uint32_t ggml_type, const uint8_t *rows, uint32_t nrows, uint32_t ncols, float *out);
 

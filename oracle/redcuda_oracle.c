@@ -29,6 +29,18 @@ int ro_set_codebooks(const uint8_t *iq2xxs_grid_2048, const uint32_t *iq3s_grid_
     return 1;
 }
 
+/* tables of the further types of the IQ3 family (iq3.c:53-110): IQ3_XXS grid (256 x 4 packed bytes), IQ2_S grid (1024 x 8
+ * packed bytes), IQ4_NL values (16 x int8) */
+static const uint32_t *g_iq3xxs_grid = NULL;
+static const uint64_t *g_iq2s_grid = NULL;
+static const int8_t *g_iq4nl = NULL;
+int ro_set_codebooks_ext(const uint32_t *iq3xxs_grid_256, const uint64_t *iq2s_grid_1024, const int8_t *iq4nl_16) {
+    g_iq3xxs_grid = iq3xxs_grid_256;
+    g_iq2s_grid = iq2s_grid_1024;
+    g_iq4nl = iq4nl_16;
+    return 1;
+}
+
 static uint16_t rd16(const uint8_t *p) { return (uint16_t)((uint16_t)p[0] | ((uint16_t)p[1] << 8)); }
 static uint32_t rd32(const uint8_t *p) { return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24); }
 
@@ -76,7 +88,10 @@ size_t ro_row_bytes(uint32_t type, uint32_t ncols) {
         case 13: return ncols % QK ? 0 : (size_t)(ncols / QK) * 176u;           /* Q5_K */
         case 14: return ncols % QK ? 0 : (size_t)(ncols / QK) * Q6_K_BLOCK;
         case 16: return ncols % QK ? 0 : (size_t)(ncols / QK) * IQ2_XXS_BLOCK;
+        case 18: return ncols % QK ? 0 : (size_t)(ncols / QK) * 98u;            /* IQ3_XXS */
         case 21: return ncols % QK ? 0 : (size_t)(ncols / QK) * IQ3_S_BLOCK;
+        case 22: return ncols % QK ? 0 : (size_t)(ncols / QK) * 82u;            /* IQ2_S */
+        case 23: return ncols % QK ? 0 : (size_t)(ncols / QK) * 136u;           /* IQ4_XS */
         default: return 0;
     }
 }
@@ -96,6 +111,41 @@ static void iq3s_group8(const uint8_t *bp, uint32_t g, float out[8]) {
     for (uint32_t j = 0; j < 4u; ++j) {
         out[j + 0u] = db * (float)((g1 >> (8u * j)) & 255u) * ((signs[l] & (1u << (j + 0u))) ? -1.f : 1.f);
         out[j + 4u] = db * (float)((g2 >> (8u * j)) & 255u) * ((signs[l] & (1u << (j + 4u))) ? -1.f : 1.f);
+    }
+}
+
+/* iq3.c:70-81, 92-109 — eight consecutive values of group g in [0,32) of an IQ3_XXS (18, 98 bytes), IQ2_S (22, 82 bytes) or
+ * IQ4_XS (23, 136 bytes) block. The magnitude product is rounded once, the sign is an exact factor. */
+static uint32_t iq3fam_block(uint32_t type) { return type == 18u ? 98u : type == 22u ? 82u : 136u; }
+static int iq3fam_ready(uint32_t type) { return type == 18u ? g_iq3xxs_grid != NULL : type == 22u ? g_iq2s_grid != NULL : g_iq4nl != NULL; }
+static void iq3fam_group8(uint32_t type, const uint8_t *bp, uint32_t g, float out[8]) {
+    const float d = ro_f16_to_f32(rd16(bp));
+    const uint32_t ib32 = g / 4u, l = g % 4u;
+    if (type == 18u) {
+        const uint8_t *qs = bp + 2u + 8u * ib32;
+        const uint32_t aux = rd32(bp + 66u + 4u * ib32);
+        const float db = d * (0.5f + (float)(aux >> 28)) * 0.5f;
+        const uint32_t s8 = sign8_of((aux >> (7u * l)) & 127u);
+        const uint32_t g1 = g_iq3xxs_grid[qs[2u * l]], g2 = g_iq3xxs_grid[qs[2u * l + 1u]];
+        for (uint32_t j = 0; j < 4u; ++j) {
+            out[j] = db * (float)((g1 >> (8u * j)) & 255u) * ((s8 & (1u << j)) ? -1.f : 1.f);
+            out[j + 4u] = db * (float)((g2 >> (8u * j)) & 255u) * ((s8 & (1u << (j + 4u))) ? -1.f : 1.f);
+        }
+    } else if (type == 22u) {
+        const uint8_t *qs = bp + 2u, *signs = bp + 34u, *qh = bp + 66u, *scales = bp + 74u;
+        const uint32_t nib = (l < 2u ? scales[ib32] : (uint32_t)(scales[ib32] >> 4)) & 0xfu;
+        const float dl = d * (0.5f + (float)nib) * 0.25f;
+        const uint32_t idx = qs[4u * ib32 + l] | (((uint32_t)qh[ib32] << (8u - 2u * l)) & 0x300u);
+        const uint64_t gv = g_iq2s_grid[idx];
+        const uint32_t sg = signs[4u * ib32 + l];
+        for (uint32_t j = 0; j < 8u; ++j) out[j] = dl * (float)((gv >> (8u * j)) & 255u) * ((sg & (1u << j)) ? -1.f : 1.f);
+    } else {
+        const uint32_t scales_h = rd16(bp + 2u);
+        const uint8_t *scales_l = bp + 4u, *qs = bp + 8u + 16u * ib32;
+        const int ls = (int)((scales_l[ib32 / 2u] >> (4u * (ib32 % 2u))) & 0xfu) | (int)(((scales_h >> (2u * ib32)) & 3u) << 4);
+        const float dl = d * (float)(ls - 32);
+        const uint32_t base = 8u * (l % 2u);
+        for (uint32_t j = 0; j < 8u; ++j) out[j] = dl * (float)g_iq4nl[l < 2u ? (qs[base + j] & 0xfu) : (qs[base + j] >> 4)];
     }
 }
 
@@ -202,6 +252,12 @@ int ro_dequant_row(uint32_t type, const uint8_t *row, uint32_t ncols, float *out
                 for (uint32_t g = 0; g < 32u; ++g) iq3s_group8(row + (size_t)b * IQ3_S_BLOCK, g, out + (size_t)b * QK + 8u * g);
             return 1;
         }
+        case 18: case 22: case 23: {   /* iq3.c:112-118 */
+            if (ncols % QK || !iq3fam_ready(type)) return 0;
+            for (uint32_t b = 0; b < ncols / QK; ++b)
+                for (uint32_t g = 0; g < 32u; ++g) iq3fam_group8(type, row + (size_t)b * iq3fam_block(type), g, out + (size_t)b * QK + 8u * g);
+            return 1;
+        }
         default: return 0;
     }
 }
@@ -288,6 +344,17 @@ static int row_dot_any(uint32_t type, const uint8_t *row, const float *xf, const
             for (uint32_t b = 0; b < ncols / QK; ++b)
                 for (uint32_t g = 0; g < 32u; ++g) {
                     iq3s_group8(row + (size_t)b * IQ3_S_BLOCK, g, v);
+                    const uint32_t xb = b * QK + 8u * g;
+                    for (uint32_t j = 0; j < 8u; ++j) acc += (double)v[j] * xin(xf, xd, xb + j);
+                }
+            break;
+        }
+        case 18: case 22: case 23: {   /* iq3.c:120-148 — fp32 dequantised group, double products */
+            if (ncols % QK || !iq3fam_ready(type)) return 0;
+            float v[8];
+            for (uint32_t b = 0; b < ncols / QK; ++b)
+                for (uint32_t g = 0; g < 32u; ++g) {
+                    iq3fam_group8(type, row + (size_t)b * iq3fam_block(type), g, v);
                     const uint32_t xb = b * QK + 8u * g;
                     for (uint32_t j = 0; j < 8u; ++j) acc += (double)v[j] * xin(xf, xd, xb + j);
                 }

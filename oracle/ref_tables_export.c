@@ -12,3 +12,5 @@
 
 const uint32_t *redcuda_ref_iq3s_grid(size_t *count) { if (count) *count = sizeof(rl_iq3s_grid) / sizeof(rl_iq3s_grid[0]); return rl_iq3s_grid; }
 const uint32_t *redcuda_ref_iq3xxs_grid(size_t *count) { if (count) *count = sizeof(rl_iq3xxs_grid) / sizeof(rl_iq3xxs_grid[0]); return rl_iq3xxs_grid; }
+const uint64_t *redcuda_ref_iq2s_grid(size_t *count) { if (count) *count = sizeof(rl_iq2s_grid) / sizeof(rl_iq2s_grid[0]); return rl_iq2s_grid; }
+const int8_t *redcuda_ref_iq4nl_values(size_t *count) { if (count) *count = sizeof(rl_kvalues_iq4nl) / sizeof(rl_kvalues_iq4nl[0]); return rl_kvalues_iq4nl; }

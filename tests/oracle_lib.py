@@ -29,6 +29,13 @@ def codebooks() -> tuple[np.ndarray, np.ndarray]:
     return raw[:2048].copy(), raw[2048:].view(np.uint32).copy()
 
 
+def codebooks_ext() -> tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """IQ3_XXS grid (256 x uint32), IQ2_S grid (1024 x uint64), IQ4_NL values (16 x int8)."""
+    raw = np.fromfile(os.path.join(ROOT, "dwarfstar_red_lite_b200", "data", "codebooks_iq3family.bin"), dtype=np.uint8)
+    assert raw.size == 9232
+    return raw[:1024].view(np.uint32).copy(), raw[1024:9216].view(np.uint64).copy(), raw[9216:].view(np.int8).copy()
+
+
 class MoeLayerC(C.Structure):
     _fields_ = [("hidden", C.c_uint32), ("n_expert", C.c_uint32), ("top_k", C.c_uint32), ("ffn", C.c_uint32), ("ffn_sh", C.c_uint32),
                 ("type_gu", C.c_uint32), ("type_down", C.c_uint32), ("type_sh", C.c_uint32),
@@ -98,8 +105,10 @@ def own():
     lib.ro_state_conv.argtypes = [C.c_void_p, C.c_uint32]
     lib.ro_model_step.argtypes = [C.POINTER(ModelC), C.c_void_p, C.c_uint32, f32p, C.c_int]
     g2, g3 = codebooks()
-    lib._keep = (g2, g3)
+    x3, s2, n4 = codebooks_ext()
+    lib._keep = (g2, g3, x3, s2, n4)
     assert lib.ro_set_codebooks(ptr(g2, u8p), ptr(g3, u32p)) == 1
+    assert lib.ro_set_codebooks_ext(x3.ctypes.data_as(C.c_void_p), s2.ctypes.data_as(C.c_void_p), n4.ctypes.data_as(C.c_void_p)) == 1
     _own = lib
     return lib
 

@@ -98,7 +98,8 @@ def test_kat_deltanet_state_s2():
 
 # ---- bit-for-bit against the reference library
 @needs_ref
-@pytest.mark.parametrize("t", [synth.Q6_K, synth.IQ2_XXS, synth.IQ3_S, synth.F32, synth.F16, synth.Q8_0, synth.Q2_K, synth.Q4_K, synth.Q5_K])
+@pytest.mark.parametrize("t", [synth.Q6_K, synth.IQ2_XXS, synth.IQ3_S, synth.F32, synth.F16, synth.Q8_0, synth.Q2_K, synth.Q4_K, synth.Q5_K,
+                               synth.IQ3_XXS, synth.IQ2_S, synth.IQ4_XS])
 def test_dequant_and_dot_match_reference(t):
     rng = np.random.default_rng(100 + t)
     g2, _ = ol.codebooks()
