@@ -650,6 +650,13 @@ int redcuda_set_codebooks_ext(const uint32_t *iq3xxs_grid, uint32_t iq3xxs_count
     return kq_set_iq_tables(iq3xxs_grid, iq2s_grid, iq4nl_values);
 }
 
+int redcuda_set_codebooks_xs(const int8_t *iq2xs_grid, uint32_t iq2xs_count, const int8_t *iq1m_grid, uint32_t iq1m_count) {
+    if (!require_device()) return 0;
+    RC_REQUIRE(iq2xs_grid && iq2xs_count == 4096u, "IQ2_XS grid must be 512 x 8 values");
+    RC_REQUIRE(iq1m_grid && iq1m_count == 16384u, "IQ1_M grid must be 2048 x 8 values");
+    return kq_set_xs_tables(iq2xs_grid, iq1m_grid);
+}
+
 int redcuda_quant_dequant_rows(uint32_t type, const uint8_t *rows, uint32_t nrows, uint32_t ncols, float *out) {
     if (!require_device()) return 0;
     RC_REQUIRE(rows && out && nrows && ncols, "dequant: null or empty argument");

@@ -124,6 +124,7 @@ int launch_attn_chunk(const float *query, const KV *kc, const KV *vc, uint32_t n
 // Q8_0 / Q2_K / Q4_K / Q5_K rows in their GGUF layout (redcuda_kquants.cu): host-pointer dequantisation and matvec
 bool kq_supported(uint32_t ggml_type);
 int kq_set_iq_tables(const uint32_t *iq3xxs_grid_256, const uint64_t *iq2s_grid_1024, const int8_t *iq4nl_16);     // current device
+int kq_set_xs_tables(const int8_t *iq2xs_grid_4096, const int8_t *iq1m_grid_16384);                                 // current device
 int kq_dequant_rows(uint32_t type, const uint8_t *rows, uint32_t nrows, uint32_t ncols, float *out);
 int kq_matvec(uint32_t type, const uint8_t *w, uint32_t nrows, uint32_t ncols, const float *x, uint32_t ntok, float *out);
 

@@ -1,6 +1,7 @@
 // Further GGUF block types behind the stage entry points: Q8_0, Q2_K, Q4_K, Q5_K (the reference's
 // rl_quant_dequant_row / rl_quant_row_dot cases 8, 10, 12, 13: native/redlite_native_quant_cpu.c:40-128, 198-265) and the
-// codebook types IQ3_XXS, IQ2_S, IQ4_XS (cases 18, 22, 23 through rl_iq3_group8: native/redlite_native_iq3.c:53-148).
+// codebook types IQ3_XXS, IQ2_S, IQ4_XS (cases 18, 22, 23 through rl_iq3_group8: native/redlite_native_iq3.c:53-148) and
+// IQ2_XS, IQ1_M (17, 29: the weights of rl_native_quant_row_dot, native/redlite_native_reference.c:116-176).
 // Rows stay in their GGUF layout; values are decoded with the reference's float operations in the reference's order
 // (explicit round-to-nearest multiplies and subtractions, so that no fused multiply-add changes a bit). These types are
 // not on the decode path of the Qwen3-Next model files this library was built for (those use Q6_K / IQ2_XXS / IQ3_S);
@@ -24,7 +25,9 @@ uint64_t kq_row_bytes(uint32_t t, uint32_t ncols) { return ncols % kq_any_block_
 __device__ uint32_t d_iq3xxs_grid[256];
 __device__ uint64_t d_iq2s_grid[1024];
 __device__ int8_t d_iq4nl[16];
-static bool g_iq_tabs_set[64];
+__device__ int8_t d_iq2xs_grid[4096];
+__device__ int8_t d_iq1m_grid[16384];
+static bool g_iq_tabs_set[64], g_xs_tabs_set[64];
 static KqIqTabs g_iq_tabs[64];
 static std::mutex g_iq_mu;
 
@@ -40,18 +43,34 @@ int kq_set_iq_tables(const uint32_t *iq3xxs, const uint64_t *iq2s, const int8_t 
     RC_CUDA(cudaGetSymbolAddress(&b, d_iq2s_grid));
     RC_CUDA(cudaGetSymbolAddress(&c, d_iq4nl));
     std::lock_guard<std::mutex> lk(g_iq_mu);
-    g_iq_tabs[dev] = KqIqTabs{(const uint32_t *)a, (const uint64_t *)b, (const int8_t *)c};
+    g_iq_tabs[dev].iq3xxs = (const uint32_t *)a; g_iq_tabs[dev].iq2s = (const uint64_t *)b; g_iq_tabs[dev].iq4nl = (const int8_t *)c;
     g_iq_tabs_set[dev] = true;
+    return 1;
+}
+int kq_set_xs_tables(const int8_t *iq2xs, const int8_t *iq1m) {
+    int dev = 0;
+    RC_CUDA(cudaGetDevice(&dev));
+    RC_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
+    RC_CUDA(cudaMemcpyToSymbol(d_iq2xs_grid, iq2xs, sizeof(d_iq2xs_grid)));
+    RC_CUDA(cudaMemcpyToSymbol(d_iq1m_grid, iq1m, sizeof(d_iq1m_grid)));
+    void *a = nullptr, *b = nullptr;
+    RC_CUDA(cudaGetSymbolAddress(&a, d_iq2xs_grid));
+    RC_CUDA(cudaGetSymbolAddress(&b, d_iq1m_grid));
+    std::lock_guard<std::mutex> lk(g_iq_mu);
+    g_iq_tabs[dev].iq2xs = (const int8_t *)a; g_iq_tabs[dev].iq1m = (const int8_t *)b;
+    g_xs_tabs_set[dev] = true;
     return 1;
 }
 // the current device's tables; fails (with a message) for an IQ3-family type before they were set
 static int kq_tabs_for(uint32_t type, KqIqTabs &T) {
-    T = KqIqTabs{nullptr, nullptr, nullptr};
+    T = KqIqTabs{nullptr, nullptr, nullptr, nullptr, nullptr};
     if (!kq_iq_type(type)) return 1;
     int dev = 0;
     RC_CUDA(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lk(g_iq_mu);
-    RC_REQUIRE(dev >= 0 && dev < 64 && g_iq_tabs_set[dev], "type %u needs the IQ3-family tables on device %d: call redcuda_set_codebooks_ext first", type, dev);
+    RC_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
+    if (kq_iq_family3(type)) RC_REQUIRE(g_iq_tabs_set[dev], "type %u needs the IQ3-family tables on device %d: call redcuda_set_codebooks_ext first", type, dev);
+    else RC_REQUIRE(g_xs_tabs_set[dev], "type %u needs the IQ2_XS / IQ1_M grids on device %d: call redcuda_set_codebooks_xs first", type, dev);
     T = g_iq_tabs[dev];
     return 1;
 }

@@ -1,14 +1,18 @@
-// Value decode of three further codebook types of the GGML IQ3 family, kept in their file layout: IQ3_XXS (18, 98-byte
-// blocks), IQ2_S (22, 82 bytes), IQ4_XS (23, 136 bytes). The float operations and their order are those of the reference's
-// rl_iq3_group8 (native/redlite_native_iq3.c:53-110): the scale product is rounded factor by factor, the magnitude product
-// once, and the sign is an exact factor. Host and device compile the same function, so the decode can be checked against
-// the CPU checker without a GPU. The tables are data of the formats and are handed in by the caller.
+// Value decode of five further codebook types, kept in their file layout. IQ3_XXS (18, 98-byte blocks), IQ2_S (22, 82 bytes),
+// IQ4_XS (23, 136 bytes): the float operations and their order are those of the reference's rl_iq3_group8
+// (native/redlite_native_iq3.c:53-110): the scale product is rounded factor by factor, the magnitude product once, and the
+// sign is an exact factor. IQ2_XS (17, 74 bytes) and IQ1_M (29, 56 bytes): the reference forms these weights in double inside
+// its row dot (native/redlite_native_reference.c:116-176); every factor is a short integer or a power of two (at most 22
+// significant bits in all), so the same products in float are exact and equal the double value. Host and device compile the
+// same function, so the decode can be checked against the CPU checker without a GPU. The tables are data of the formats
+// and are handed in by the caller.
 #pragma once
 #include <stdint.h>
 
 namespace rc {
 
-struct KqIqTabs { const uint32_t *iq3xxs; const uint64_t *iq2s; const int8_t *iq4nl; };   // 256 x 4 packed bytes, 1024 x 8 packed bytes, 16 values
+// iq3xxs: 256 x 4 packed bytes, iq2s: 1024 x 8 packed bytes, iq4nl: 16 values, iq2xs: 512 x 8 magnitudes, iq1m: 2048 x 8 values
+struct KqIqTabs { const uint32_t *iq3xxs; const uint64_t *iq2s; const int8_t *iq4nl; const int8_t *iq2xs; const int8_t *iq1m; };
 
 #if defined(__CUDA_ARCH__)
 #define RC_KQ_MUL(a, b) __fmul_rn((a), (b))
@@ -16,8 +20,9 @@ struct KqIqTabs { const uint32_t *iq3xxs; const uint64_t *iq2s; const int8_t *iq
 #define RC_KQ_MUL(a, b) ((a) * (b))
 #endif
 
-__host__ __device__ inline bool kq_iq_type(uint32_t t) { return t == 18u || t == 22u || t == 23u; }
-__host__ __device__ inline uint32_t kq_iq_block_bytes(uint32_t t) { return t == 18u ? 98u : t == 22u ? 82u : 136u; }
+__host__ __device__ inline bool kq_iq_type(uint32_t t) { return t == 17u || t == 18u || t == 22u || t == 23u || t == 29u; }
+__host__ __device__ inline bool kq_iq_family3(uint32_t t) { return t == 18u || t == 22u || t == 23u; }       // tables of redcuda_set_codebooks_ext
+__host__ __device__ inline uint32_t kq_iq_block_bytes(uint32_t t) { return t == 17u ? 74u : t == 18u ? 98u : t == 22u ? 82u : t == 23u ? 136u : 56u; }
 
 // exact binary16 -> binary32, subnormals included
 __host__ __device__ inline float kq_iq_f16(const uint8_t *p) {
@@ -36,6 +41,31 @@ __host__ __device__ inline uint32_t kq_iq_sign8(uint32_t s7) {
 
 // value j in [0, 256) of the block at bp
 __host__ __device__ inline float kq_iq_value(uint32_t t, const uint8_t *bp, uint32_t j, const KqIqTabs &T) {
+    if (t == 17u) {
+        const float d = kq_iq_f16(bp);
+        const uint32_t group = j >> 4, part = (j >> 3) & 1u, jj = j & 7u;
+        const uint32_t scale = ((uint32_t)bp[66u + (group >> 1)] >> (4u * (group & 1u))) & 0xfu;
+        const float db = RC_KQ_MUL(RC_KQ_MUL(d, 0.5f + (float)scale), 0.25f);
+        const uint8_t *qp = bp + 2u + 2u * (2u * group + part);
+        const uint32_t q = (uint32_t)qp[0] | ((uint32_t)qp[1] << 8);
+        const float v = RC_KQ_MUL(db, (float)T.iq2xs[(q & 0x1ffu) * 8u + jj]);
+        return ((kq_iq_sign8((q >> 9) & 127u) >> jj) & 1u) ? -v : v;
+    }
+    if (t == 29u) {
+        uint32_t sc[4];
+#pragma unroll
+        for (uint32_t i = 0; i < 4u; ++i) sc[i] = (uint32_t)bp[48u + 2u * i] | ((uint32_t)bp[49u + 2u * i] << 8);
+        const uint32_t d_bits = (sc[0] >> 12) | ((sc[1] >> 8) & 0x00f0u) | ((sc[2] >> 4) & 0x0f00u) | (sc[3] & 0xf000u);
+        const uint8_t db2[2] = {(uint8_t)(d_bits & 255u), (uint8_t)(d_bits >> 8)};
+        const float d = kq_iq_f16(db2);
+        const uint32_t group = j >> 3, jj = j & 7u;
+        const uint32_t nibble = ((uint32_t)bp[32u + (group >> 1)] >> (4u * (group & 1u))) & 0xfu;
+        const uint32_t grid_index = (uint32_t)bp[group] | ((nibble & 7u) << 8);
+        const uint32_t scale_index = group >> 1;
+        const uint32_t scale = (sc[scale_index >> 2] >> (3u * (scale_index & 3u))) & 7u;
+        const float dl = RC_KQ_MUL(d, (float)(2u * scale + 1u));
+        return RC_KQ_MUL(dl, (float)T.iq1m[grid_index * 8u + jj] + ((nibble & 8u) ? -0.125f : 0.125f));
+    }
     const float d = kq_iq_f16(bp);
     const uint32_t g = j >> 3, jj = j & 7u, ib32 = g >> 2, l = g & 3u;
     float v; uint32_t neg;

@@ -15,6 +15,12 @@ file codebooks_iq3family.bin:
     [1024, 9216)   IQ2_S grid, 1024 entries x 8 packed magnitudes (uint64)
     [9216, 9232)   IQ4_NL values, 16 x int8
 
+and, for the two types of the reference's routed-expert checker (IQ2_XS, IQ1_M: native/redlite_native_reference.c:116-176,
+grids built by rl_native_quant_tables_init, native/redlite_native_tables.c:229), codebooks_iq2xs_iq1m.bin:
+
+    [0, 4096)      IQ2_XS grid, 512 entries x 8 magnitudes (int8)
+    [4096, 20480)  IQ1_M grid, 2048 entries x 8 values in {-1, 0, 1} (int8)
+
 Usage: make -C oracle ref && python dwarfstar_red_lite_b200/data/make_codebooks.py
 """
 import ctypes
@@ -50,3 +56,16 @@ fam = table("redcuda_ref_iq3xxs_grid", ctypes.c_uint32, 256) + table("redcuda_re
 with open(os.path.join(here, "codebooks_iq3family.bin"), "wb") as f:
     f.write(fam)
 print("wrote codebooks_iq3family.bin", len(fam), "bytes")
+
+
+class Tables(ctypes.Structure):
+    _fields_ = [("iq2_xs", ctypes.POINTER(ctypes.c_int8)), ("iq1_m", ctypes.POINTER(ctypes.c_int8))]
+
+
+tabs = Tables()
+assert ref.rl_native_quant_tables_init(ctypes.byref(tabs), err, 256) == 1, err.value
+two = bytes(ctypes.cast(tabs.iq2_xs, ctypes.POINTER(ctypes.c_uint8 * 4096)).contents) + bytes(ctypes.cast(tabs.iq1_m, ctypes.POINTER(ctypes.c_uint8 * 16384)).contents)
+ref.rl_native_quant_tables_free(ctypes.byref(tabs))
+with open(os.path.join(here, "codebooks_iq2xs_iq1m.bin"), "wb") as f:
+    f.write(two)
+print("wrote codebooks_iq2xs_iq1m.bin", len(two), "bytes")

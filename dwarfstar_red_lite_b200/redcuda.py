@@ -14,7 +14,7 @@ LIB_PATH = os.environ.get("REDCUDA_LIB") or os.path.join(HERE, "libredcuda.so") 
 u8p, f32p, u32p = C.POINTER(C.c_uint8), C.POINTER(C.c_float), C.POINTER(C.c_uint32)
 
 EXPORTS = [
-    "redcuda_abi_version", "redcuda_last_error", "redcuda_device_count", "redcuda_set_device", "redcuda_set_codebooks", "redcuda_set_codebooks_ext",
+    "redcuda_abi_version", "redcuda_last_error", "redcuda_device_count", "redcuda_set_device", "redcuda_set_codebooks", "redcuda_set_codebooks_ext", "redcuda_set_codebooks_xs",
     "redcuda_quant_dequant_rows", "redcuda_nib_dequant_rows", "redcuda_quant_matvec", "redcuda_quant_matmul_tc", "redcuda_router_select_softmax_topk", "redcuda_deltanet_step",
     "redcuda_deltanet_step_noalloc",
     "redcuda_moe_create", "redcuda_moe_destroy", "redcuda_moe_resident_bytes", "redcuda_moe_forward",
@@ -100,6 +100,7 @@ def lib():
     L.redcuda_set_device.argtypes = [C.c_int]
     L.redcuda_set_codebooks.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32]
     L.redcuda_set_codebooks_ext.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32]
+    L.redcuda_set_codebooks_xs.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32]
     _lib = L
     return L
 
@@ -145,9 +146,19 @@ def set_codebooks_ext(iq3xxs_grid: np.ndarray | None = None, iq2s_grid: np.ndarr
     _check(lib().redcuda_set_codebooks_ext(a.ctypes.data, a.size, b.ctypes.data, b.size, c.ctypes.data, c.size))
 
 
+def set_codebooks_xs(iq2xs_grid: np.ndarray | None = None, iq1m_grid: np.ndarray | None = None):
+    """Hand the IQ2_XS / IQ1_M grids to the current device (defaults: data/codebooks_iq2xs_iq1m.bin)."""
+    if iq2xs_grid is None or iq1m_grid is None:
+        raw = np.fromfile(os.path.join(HERE, "data", "codebooks_iq2xs_iq1m.bin"), dtype=np.int8)
+        iq2xs_grid, iq1m_grid = raw[:4096].copy(), raw[4096:20480].copy()
+    a = np.ascontiguousarray(iq2xs_grid, np.int8)
+    b = np.ascontiguousarray(iq1m_grid, np.int8)
+    _check(lib().redcuda_set_codebooks_xs(a.ctypes.data, a.size, b.ctypes.data, b.size))
+
+
 def set_codebooks(iq2xxs_grid: np.ndarray | None = None, iq3s_grid: np.ndarray | None = None, device: int | None = None):
     """Hand the IQ2_XXS / IQ3_S codebooks to the current device (defaults: data/codebooks.bin); with the defaults the tables
-    of IQ3_XXS / IQ2_S / IQ4_XS go along."""
+    of IQ3_XXS / IQ2_S / IQ4_XS and the IQ2_XS / IQ1_M grids go along."""
     ext = iq2xxs_grid is None or iq3s_grid is None
     if iq2xxs_grid is None or iq3s_grid is None:
         iq2xxs_grid, iq3s_grid = default_codebooks()
@@ -158,6 +169,7 @@ def set_codebooks(iq2xxs_grid: np.ndarray | None = None, iq3s_grid: np.ndarray |
     _check(lib().redcuda_set_codebooks(g2.ctypes.data, g2.size, g3.ctypes.data, g3.size))
     if ext:
         set_codebooks_ext()
+        set_codebooks_xs()
     _books_devices.add(-1 if device is None else device)
 
 

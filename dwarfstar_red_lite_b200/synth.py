@@ -14,9 +14,10 @@ import numpy as np
 F32, F16, Q6_K, IQ2_XXS, IQ3_S = 0, 1, 14, 16, 21
 Q8_0, Q2_K, Q4_K, Q5_K = 8, 10, 12, 13          # further GGUF types served by the stage entry points (dequantise, matvec)
 IQ3_XXS, IQ2_S, IQ4_XS = 18, 22, 23             # and three more of the IQ3 family (codebook types), stage entry points only
-BLOCK_BYTES = {Q6_K: 210, IQ2_XXS: 66, IQ3_S: 110, Q8_0: 34, Q2_K: 84, Q4_K: 144, Q5_K: 176, IQ3_XXS: 98, IQ2_S: 82, IQ4_XS: 136}
+IQ2_XS, IQ1_M = 17, 29                          # the two types of the reference's routed-expert checker, stage entry points only
+BLOCK_BYTES = {Q6_K: 210, IQ2_XXS: 66, IQ3_S: 110, Q8_0: 34, Q2_K: 84, Q4_K: 144, Q5_K: 176, IQ3_XXS: 98, IQ2_S: 82, IQ4_XS: 136, IQ2_XS: 74, IQ1_M: 56}
 BLOCK_VALUES = {Q8_0: 32}                        # every other block holds 256 values
-D_OFFSET = {Q6_K: 208, IQ2_XXS: 0, IQ3_S: 0, Q8_0: 0, Q2_K: 80, Q4_K: 0, Q5_K: 0, IQ3_XXS: 0, IQ2_S: 0, IQ4_XS: 0}
+D_OFFSET = {Q6_K: 208, IQ2_XXS: 0, IQ3_S: 0, Q8_0: 0, Q2_K: 80, Q4_K: 0, Q5_K: 0, IQ3_XXS: 0, IQ2_S: 0, IQ4_XS: 0, IQ2_XS: 0}
 DMIN_OFFSET = {Q2_K: 82, Q4_K: 2, Q5_K: 2}       # second fp16 scale (of the block minimum)
 DMIN_FACTOR = {Q2_K: 1.5, Q4_K: 7.5, Q5_K: 15.5}  # dmin ~ d x the mean code, so that d*sc*q - dmin*mn is centred on zero
 
@@ -42,6 +43,12 @@ def quant_matrix(rng: np.random.Generator, ggml_type: int, nrows: int, ncols: in
     bb = BLOCK_BYTES[ggml_type]
     blocks = np.frombuffer(rng.bytes(nb * bb), dtype=np.uint8).reshape(nb, bb).copy()     # random payload bytes (fast path of the generator)
     d = rng.uniform(d_lo, d_hi, size=nb).astype(np.float16)
+    if ggml_type == IQ1_M:
+        # the block scale is spread over the top nibbles of the four 16-bit scale words at bytes 48..55
+        bits = d.view(np.uint16).astype(np.uint32)
+        for k in range(4):
+            blocks[:, 49 + 2 * k] = (blocks[:, 49 + 2 * k] & 0x0F) | (((bits >> (4 * k)) & 0xF) << 4).astype(np.uint8)
+        return blocks.reshape(nrows, (ncols // bv) * bb)
     off = D_OFFSET[ggml_type]
     blocks[:, off:off + 2] = d.view(np.uint8).reshape(nb, 2)
     if ggml_type in DMIN_OFFSET:

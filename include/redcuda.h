@@ -51,6 +51,14 @@ int redcuda_set_codebooks(const uint8_t *iq2xxs_grid, uint32_t iq2xxs_bytes, con
 int redcuda_set_codebooks_ext(const uint32_t *iq3xxs_grid, uint32_t iq3xxs_count, const uint64_t *iq2s_grid, uint32_t iq2s_count,
                               const int8_t *iq4nl_values, uint32_t iq4nl_count);
 
+/*
+ * The two grids the reference hands to its Metal pool (iq2_xs_grid / iq1_m_grid of redmetal_topk_pool_create,
+ * native/redmetal_topk.h:16-24; built by rl_native_quant_tables_init, native/redlite_native_tables.c:229): 512 x 8 and
+ * 2048 x 8 int8 values (RL_IQ2_XS_GRID_COUNT, RL_IQ1_M_GRID_COUNT). Once per device before IQ2_XS (17) or IQ1_M (29) rows
+ * are handed to redcuda_quant_dequant_rows / redcuda_quant_matvec.
+ */
+int redcuda_set_codebooks_xs(const int8_t *iq2xs_grid, uint32_t iq2xs_count, const int8_t *iq1m_grid, uint32_t iq1m_count);
+
 /* ------------------------------------------------------------------------------------------------------------
  * Stage entry points (host pointers, synchronous). Each replaces one CPU reference function of the path.
  * ---------------------------------------------------------------------------------------------------------- */
@@ -59,7 +67,9 @@ int redcuda_set_codebooks_ext(const uint32_t *iq3xxs_grid, uint32_t iq3xxs_count
  * ggml types: 0 F32, 1 F16, 14 Q6_K, 16 IQ2_XXS, 21 IQ3_S (the types of the decode path), and 8 Q8_0, 10 Q2_K, 12 Q4_K,
  * 13 Q5_K (cases 8 / 10 / 12 / 13 of the same reference function, :50-128) and 18 IQ3_XXS, 22 IQ2_S, 23 IQ4_XS (its
  * rl_iq3_dequant_row branch, :193; native/redlite_native_iq3.c:53-118), which this entry point and redcuda_quant_matvec
- * serve but the engine and the expert kernels do not yet. Values are bit-identical to the reference's. */
+ * serve but the engine and the expert kernels do not yet. Values are bit-identical to the reference's. Also 17 IQ2_XS and
+ * 29 IQ1_M, for which the reference has no dequantiser: the value is the weight its row dot forms in double
+ * (native/redlite_native_reference.c:116-176), which is exactly a float. */
 int redcuda_quant_dequant_rows(uint32_t ggml_type, const uint8_t *rows, uint32_t nrows, uint32_t ncols, float *out);
 
 /* The same values through the layout the routed IQ2_XXS experts are kept in (4-bit magnitude/sign codes, byte scales;

@@ -40,6 +40,13 @@ int ro_set_codebooks_ext(const uint32_t *iq3xxs_grid_256, const uint64_t *iq2s_g
     g_iq4nl = iq4nl_16;
     return 1;
 }
+/* grids of IQ2_XS (512 x 8 magnitudes) and IQ1_M (2048 x 8 values), the two types of reference.c:116-176 */
+static const int8_t *g_iq2xs_grid = NULL, *g_iq1m_grid = NULL;
+int ro_set_codebooks_xs(const int8_t *iq2xs_grid_4096, const int8_t *iq1m_grid_16384) {
+    g_iq2xs_grid = iq2xs_grid_4096;
+    g_iq1m_grid = iq1m_grid_16384;
+    return 1;
+}
 
 static uint16_t rd16(const uint8_t *p) { return (uint16_t)((uint16_t)p[0] | ((uint16_t)p[1] << 8)); }
 static uint32_t rd32(const uint8_t *p) { return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24); }
@@ -88,10 +95,12 @@ size_t ro_row_bytes(uint32_t type, uint32_t ncols) {
         case 13: return ncols % QK ? 0 : (size_t)(ncols / QK) * 176u;           /* Q5_K */
         case 14: return ncols % QK ? 0 : (size_t)(ncols / QK) * Q6_K_BLOCK;
         case 16: return ncols % QK ? 0 : (size_t)(ncols / QK) * IQ2_XXS_BLOCK;
+        case 17: return ncols % QK ? 0 : (size_t)(ncols / QK) * 74u;            /* IQ2_XS */
         case 18: return ncols % QK ? 0 : (size_t)(ncols / QK) * 98u;            /* IQ3_XXS */
         case 21: return ncols % QK ? 0 : (size_t)(ncols / QK) * IQ3_S_BLOCK;
         case 22: return ncols % QK ? 0 : (size_t)(ncols / QK) * 82u;            /* IQ2_S */
         case 23: return ncols % QK ? 0 : (size_t)(ncols / QK) * 136u;           /* IQ4_XS */
+        case 29: return ncols % QK ? 0 : (size_t)(ncols / QK) * 56u;            /* IQ1_M */
         default: return 0;
     }
 }
@@ -148,6 +157,35 @@ static void iq3fam_group8(uint32_t type, const uint8_t *bp, uint32_t g, float ou
         for (uint32_t j = 0; j < 8u; ++j) out[j] = dl * (float)g_iq4nl[l < 2u ? (qs[base + j] & 0xfu) : (qs[base + j] >> 4)];
     }
 }
+
+/* reference.c:116-176 — weight j in [0,256) of an IQ2_XS (17, 74 bytes) or IQ1_M (29, 56 bytes) block, formed in double as the
+ * reference's row dot forms it (it has no dequantiser for these two types) */
+static double xs_weight(uint32_t type, const uint8_t *bp, uint32_t j) {
+    if (type == 17u) {
+        const double d = (double)ro_f16_to_f32(rd16(bp));
+        const uint32_t group = j >> 4, part = (j >> 3) & 1u, jj = j & 7u;
+        const uint32_t scale = (bp[66u + (group >> 1)] >> (4u * (group & 1u))) & 0x0fu;
+        const double db = d * (0.5 + (double)scale) * 0.25;
+        const uint32_t q = rd16(bp + 2u + 2u * (2u * group + part));
+        const uint32_t s8 = sign8_of((q >> 9) & 127u);
+        const double sign = (s8 & (1u << jj)) ? -1.0 : 1.0;
+        return db * (double)g_iq2xs_grid[(q & 0x1ffu) * 8u + jj] * sign;
+    }
+    uint16_t sc[4];
+    for (uint32_t i = 0; i < 4u; ++i) sc[i] = rd16(bp + 48u + 2u * i);
+    const uint16_t d_bits = (uint16_t)((sc[0] >> 12) | ((sc[1] >> 8) & 0x00f0u) | ((sc[2] >> 4) & 0x0f00u) | (sc[3] & 0xf000u));
+    const double d = (double)ro_f16_to_f32(d_bits);
+    const uint32_t group = j >> 3, jj = j & 7u;
+    const uint32_t nibble = (bp[32u + (group >> 1)] >> (4u * (group & 1u))) & 0x0fu;
+    const uint32_t grid_index = (uint32_t)bp[group] | ((nibble & 7u) << 8);
+    const double delta = (nibble & 8u) ? -0.125 : 0.125;
+    const uint32_t scale_index = group >> 1;
+    const uint32_t scale = (sc[scale_index >> 2] >> (3u * (scale_index & 3u))) & 7u;
+    const double dl = d * (double)(2u * scale + 1u);
+    return dl * ((double)g_iq1m_grid[grid_index * 8u + jj] + delta);
+}
+static uint32_t xs_block(uint32_t type) { return type == 17u ? 74u : 56u; }
+static int xs_ready(uint32_t type) { return type == 17u ? g_iq2xs_grid != NULL : g_iq1m_grid != NULL; }
 
 /* ---- the GGUF types beyond the decode path's three (quant_cpu.c:40-129): value j of one block, the float operations in
  * the reference's order. Used by the dequantiser and (widened to double as the reference does) by the row dot. ---- */
@@ -258,6 +296,11 @@ int ro_dequant_row(uint32_t type, const uint8_t *row, uint32_t ncols, float *out
                 for (uint32_t g = 0; g < 32u; ++g) iq3fam_group8(type, row + (size_t)b * iq3fam_block(type), g, out + (size_t)b * QK + 8u * g);
             return 1;
         }
+        case 17: case 29: {   /* the double weight of reference.c:116-176, rounded to float (it is exact there: at most 22 significant bits) */
+            if (ncols % QK || !xs_ready(type)) return 0;
+            for (uint32_t i = 0; i < ncols; ++i) out[i] = (float)xs_weight(type, row + (size_t)(i / QK) * xs_block(type), i % QK);
+            return 1;
+        }
         default: return 0;
     }
 }
@@ -349,6 +392,10 @@ static int row_dot_any(uint32_t type, const uint8_t *row, const float *xf, const
                 }
             break;
         }
+        case 17: case 29:   /* reference.c:116-176: x * weight, the weight formed in double */
+            if (ncols % QK || !xs_ready(type)) return 0;
+            for (uint32_t i = 0; i < ncols; ++i) acc += xin(xf, xd, i) * xs_weight(type, row + (size_t)(i / QK) * xs_block(type), i % QK);
+            break;
         case 18: case 22: case 23: {   /* iq3.c:120-148 — fp32 dequantised group, double products */
             if (ncols % QK || !iq3fam_ready(type)) return 0;
             float v[8];

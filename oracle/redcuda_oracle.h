@@ -27,6 +27,8 @@ extern "C" {
 int ro_set_codebooks(const uint8_t *iq2xxs_grid_2048, const uint32_t *iq3s_grid_512);
 /* tables of IQ3_XXS (18), IQ2_S (22) and IQ4_XS (23); the pointers must stay valid */
 int ro_set_codebooks_ext(const uint32_t *iq3xxs_grid_256, const uint64_t *iq2s_grid_1024, const int8_t *iq4nl_16);
+/* grids of IQ2_XS (17) and IQ1_M (29); the pointers must stay valid */
+int ro_set_codebooks_xs(const int8_t *iq2xs_grid_4096, const int8_t *iq1m_grid_16384);
 
 float ro_f16_to_f32(uint16_t h);                                   /* quant_cpu.c:20-38 */
 float ro_round_half(float f);                                      /* engine_cpu.c:29-38 */

@@ -36,6 +36,13 @@ def codebooks_ext() -> tuple[np.ndarray, np.ndarray, np.ndarray]:
     return raw[:1024].view(np.uint32).copy(), raw[1024:9216].view(np.uint64).copy(), raw[9216:].view(np.int8).copy()
 
 
+def codebooks_xs() -> tuple[np.ndarray, np.ndarray]:
+    """IQ2_XS grid (512 x 8 int8), IQ1_M grid (2048 x 8 int8)."""
+    raw = np.fromfile(os.path.join(ROOT, "dwarfstar_red_lite_b200", "data", "codebooks_iq2xs_iq1m.bin"), dtype=np.int8)
+    assert raw.size == 20480
+    return raw[:4096].copy(), raw[4096:].copy()
+
+
 class MoeLayerC(C.Structure):
     _fields_ = [("hidden", C.c_uint32), ("n_expert", C.c_uint32), ("top_k", C.c_uint32), ("ffn", C.c_uint32), ("ffn_sh", C.c_uint32),
                 ("type_gu", C.c_uint32), ("type_down", C.c_uint32), ("type_sh", C.c_uint32),
@@ -106,7 +113,9 @@ def own():
     lib.ro_model_step.argtypes = [C.POINTER(ModelC), C.c_void_p, C.c_uint32, f32p, C.c_int]
     g2, g3 = codebooks()
     x3, s2, n4 = codebooks_ext()
-    lib._keep = (g2, g3, x3, s2, n4)
+    xs, m1 = codebooks_xs()
+    lib._keep = (g2, g3, x3, s2, n4, xs, m1)
+    assert lib.ro_set_codebooks_xs(xs.ctypes.data_as(C.c_void_p), m1.ctypes.data_as(C.c_void_p)) == 1
     assert lib.ro_set_codebooks(ptr(g2, u8p), ptr(g3, u32p)) == 1
     assert lib.ro_set_codebooks_ext(x3.ctypes.data_as(C.c_void_p), s2.ctypes.data_as(C.c_void_p), n4.ctypes.data_as(C.c_void_p)) == 1
     _own = lib

@@ -24,12 +24,13 @@ def _rows(rng, t, nrows, ncols):
     if t == synth.F16:
         return rng.uniform(-1, 1, size=(nrows, ncols)).astype(np.float16).view(np.uint8).reshape(nrows, -1)
     lo, hi = {synth.Q6_K: (1e-3, 5e-3), synth.IQ2_XXS: (1e-2, 6e-2), synth.IQ3_S: (2e-3, 1.2e-2), synth.Q8_0: (1e-3, 8e-3), synth.Q2_K: (2e-2, 8e-2),
-              synth.Q4_K: (1e-3, 5e-3), synth.Q5_K: (1e-3, 5e-3), synth.IQ3_XXS: (2e-3, 1.2e-2), synth.IQ2_S: (1e-2, 6e-2), synth.IQ4_XS: (1e-3, 5e-3)}[t]
+              synth.Q4_K: (1e-3, 5e-3), synth.Q5_K: (1e-3, 5e-3), synth.IQ3_XXS: (2e-3, 1.2e-2), synth.IQ2_S: (1e-2, 6e-2), synth.IQ4_XS: (1e-3, 5e-3),
+              synth.IQ2_XS: (1e-2, 6e-2), synth.IQ1_M: (2e-2, 1e-1)}[t]
     return synth.quant_matrix(rng, t, nrows, ncols, lo, hi)
 
 
 @pytest.mark.parametrize("t", [synth.Q6_K, synth.IQ2_XXS, synth.IQ3_S, synth.F16, synth.Q8_0, synth.Q2_K, synth.Q4_K, synth.Q5_K,
-                               synth.IQ3_XXS, synth.IQ2_S, synth.IQ4_XS])
+                               synth.IQ3_XXS, synth.IQ2_S, synth.IQ4_XS, synth.IQ2_XS, synth.IQ1_M])
 def test_dequant_bit_exact(t):
     rng = np.random.default_rng(1000 + t)
     for ncols in SELFTEST_COLS:
@@ -65,7 +66,7 @@ def test_dequant_subnormal_block_scale():
 
 
 @pytest.mark.parametrize("t", [synth.Q6_K, synth.IQ2_XXS, synth.IQ3_S, synth.F32, synth.F16, synth.Q8_0, synth.Q2_K, synth.Q4_K, synth.Q5_K,
-                               synth.IQ3_XXS, synth.IQ2_S, synth.IQ4_XS])
+                               synth.IQ3_XXS, synth.IQ2_S, synth.IQ4_XS, synth.IQ2_XS, synth.IQ1_M])
 @pytest.mark.parametrize("ntok", [1, 3, 9])
 def test_matvec_selftest_protocol(t, ntok):
     rng = np.random.default_rng(2000 + t + ntok)

@@ -122,6 +122,40 @@ def test_dequant_and_dot_match_reference(t):
 
 
 @needs_ref
+@pytest.mark.parametrize("t", [synth.IQ2_XS, synth.IQ1_M])
+def test_routed_checker_types_match_reference(t):
+    """IQ2_XS and IQ1_M exist in the reference only as the row dot of its routed-expert checker
+    (rl_native_quant_row_dot, native/redlite_native_reference.c:182-195): dots bit for bit, and every dequantised value
+    against the dot with a unit vector (the only way that function shows a single weight)."""
+    rng = np.random.default_rng(400 + t)
+    xs, m1 = ol.codebooks_xs()
+    grid = xs if t == synth.IQ2_XS else m1
+    REF.rl_native_quant_row_dot.argtypes = [C.c_void_p, C.c_size_t, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_size_t, C.POINTER(C.c_double), C.c_char_p, C.c_size_t]
+    err = C.create_string_buffer(256)
+
+    def ref_dot(row, x, ncols):
+        d = C.c_double()
+        assert REF.rl_native_quant_row_dot(row.ctypes.data, row.size, t, x.ctypes.data, ncols, grid.ctypes.data, grid.size, C.byref(d), err, 256) == 1, err.value
+        return d.value
+
+    for ncols in (256, 768, 2048):
+        rows = synth.quant_matrix(rng, t, 5, ncols, 1e-2, 6e-2)
+        x = rng.normal(0, 1, ncols).astype(np.float32)
+        dots = ol.rows_dot(t, rows, x)
+        for r in range(5):
+            assert ref_dot(np.ascontiguousarray(rows[r]), x, ncols) == dots[r]
+    rows = synth.quant_matrix(rng, t, 3, 256, 1e-2, 6e-2)
+    mine = ol.dequant_rows(t, rows, 256)
+    for r in range(3):
+        row = np.ascontiguousarray(rows[r])
+        for i in range(256):
+            e = np.zeros(256, np.float32)
+            e[i] = 1.0
+            w = ref_dot(row, e, 256)
+            assert np.float32(w) == mine[r, i] and float(mine[r, i]) == w      # the double weight is exactly a float
+
+
+@needs_ref
 def test_f16_and_round_half_match_reference():
     lib = ol.own()
     for h in list(range(0, 2048)) + list(range(0x7b00, 0x7c02)) + [0x8001, 0xfbff, 0x3c00, 0xbc00]:
