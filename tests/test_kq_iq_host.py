@@ -17,7 +17,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def test_codebook_type_decoder_on_the_host(tmp_path):
     ol.own()                                   # builds / loads the oracle library
     exe = str(tmp_path / "kq_iq_host_check")
-    src = os.path.join(ROOT, "tests", "native", "kq_iq_host_check.cu")
+    src = os.path.join(ROOT, "tests", "kq_iq_host_check.cu")
     inc = os.path.join(ROOT, "dwarfstar_red_lite_b200", "csrc")
     subprocess.run(["nvcc", "-O2", "-std=c++17", "-Wno-deprecated-gpu-targets", "-Xcompiler", "-ffp-contract=off", "-I", inc, "-o", exe, src, "-ldl"],
                    check=True, capture_output=True, text=True)
