@@ -20,7 +20,11 @@ sys.path.insert(0, os.path.dirname(HERE))
 import oracle_lib as ol  # noqa: E402
 from dwarfstar_red_lite_b200 import gguf_writer, synth  # noqa: E402
 
-QUANT_CASES = [(synth.Q6_K, 256), (synth.Q6_K, 2048), (synth.IQ2_XXS, 256), (synth.IQ2_XXS, 2048), (synth.IQ3_S, 768), (synth.IQ3_S, 2048)]
+QUANT_CASES = [(synth.Q6_K, 256), (synth.Q6_K, 2048), (synth.IQ2_XXS, 256), (synth.IQ2_XXS, 2048), (synth.IQ3_S, 768), (synth.IQ3_S, 2048),
+               # the further types that stay in file layout (stage entry points)
+               (synth.Q8_0, 256), (synth.Q2_K, 768), (synth.Q4_K, 2048), (synth.Q5_K, 256), (synth.IQ3_XXS, 768), (synth.IQ2_S, 256), (synth.IQ4_XS, 2048)]
+# IQ2_XS / IQ1_M: the reference has them only as the row dot of its routed-expert checker (rl_native_quant_row_dot)
+XS_CASES = [(synth.IQ2_XS, 256), (synth.IQ2_XS, 2048), (synth.IQ1_M, 256), (synth.IQ1_M, 768)]
 ROWS = 6
 
 
@@ -62,6 +66,29 @@ def main():
             dots[r] = d.value
         out[f"deq_{t}_{ncols}"] = deq
         out[f"dot_{t}_{ncols}"] = dots
+    xs, m1 = ol.codebooks_xs()
+    ref.rl_native_quant_row_dot.argtypes = [C.c_void_p, C.c_size_t, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_size_t, C.POINTER(C.c_double), C.c_char_p, C.c_size_t]
+    msg = C.create_string_buffer(256)
+    for t, ncols in XS_CASES:
+        rows, x = quant_inputs(t, ncols)
+        grid = xs if t == synth.IQ2_XS else m1
+
+        def dot(row, vec):
+            d = C.c_double()
+            assert ref.rl_native_quant_row_dot(row.ctypes.data, row.size, t, vec.ctypes.data, ncols, grid.ctypes.data, grid.size, C.byref(d), msg, 256) == 1, msg.value
+            return d.value
+
+        dots = np.array([dot(np.ascontiguousarray(rows[r]), x) for r in range(ROWS)], np.float64)
+        out[f"dot_{t}_{ncols}"] = dots
+        if ncols == 256:      # every single weight of the first two rows, through dots with unit vectors
+            w = np.empty((2, ncols), np.float64)
+            for r in range(2):
+                row = np.ascontiguousarray(rows[r])
+                for i in range(ncols):
+                    e = np.zeros(ncols, np.float32)
+                    e[i] = 1.0
+                    w[r, i] = dot(row, e)
+            out[f"weights_{t}_{ncols}"] = w
     logits = router_inputs()
     k = 10
     ids = np.empty((logits.shape[0], k), np.uint32)

@@ -25,6 +25,16 @@ def test_oracle_dequant_and_dot_equal_reference_outputs(t, ncols):
     assert np.array_equal(ol.rows_dot(t, rows, x), GOLD[f"dot_{t}_{ncols}"])
 
 
+@pytest.mark.parametrize("t,ncols", mg.XS_CASES)
+def test_oracle_routed_checker_types_equal_reference_outputs(t, ncols):
+    rows, x = mg.quant_inputs(t, ncols)
+    assert np.array_equal(ol.rows_dot(t, rows, x), GOLD[f"dot_{t}_{ncols}"])
+    if ncols == 256:
+        w = GOLD[f"weights_{t}_{ncols}"]
+        deq = ol.dequant_rows(t, rows[:2], ncols)
+        assert np.array_equal(deq.astype(np.float64), w)          # the reference's double weights are exactly floats
+
+
 def test_oracle_router_equals_reference_outputs():
     logits = mg.router_inputs()
     for c in range(logits.shape[0]):
@@ -42,6 +52,19 @@ def test_oracle_engine_decode_equals_reference_outputs():
         for l in range(dims.n_layer):
             assert np.array_equal(om.router_ids(l), GOLD["engine_router_ids"][step][l])
             assert np.array_equal(om.layer_out(l).view(np.uint32), GOLD["engine_layer_out"][step][l].view(np.uint32))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("t,ncols", mg.XS_CASES)
+def test_cuda_routed_checker_types_against_reference_outputs(t, ncols):
+    import dwarfstar_red_lite_b200 as rc
+    rows, x = mg.quant_inputs(t, ncols)
+    deq = rc.quant_dequant_rows(t, rows, ncols).reshape(mg.ROWS, ncols)
+    if ncols == 256:
+        assert np.array_equal(deq[:2].astype(np.float64), GOLD[f"weights_{t}_{ncols}"])
+    dots = rc.quant_matvec(t, rows, mg.ROWS, ncols, x)
+    mag = np.abs(deq.astype(np.float64) * x.astype(np.float64)).sum(axis=1) + 1e-30
+    assert np.max(np.abs(dots.astype(np.float64) - GOLD[f"dot_{t}_{ncols}"]) / mag) <= 2e-5
 
 
 @pytest.mark.gpu
